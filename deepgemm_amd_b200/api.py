@@ -1,0 +1,492 @@
+"""Host-side mirror of the reference's operator interface for the block-scaled GEMM path.
+
+Same names, keyword arguments, defaults and error behaviour as the functions the reference
+registers in csrc/apis/gemm.hpp:835-995, csrc/apis/layout.hpp:119-141 and csrc/apis/config.hpp:9-47
+(a failed check raises RuntimeError carrying "Assertion error ..."), on top of the C ABI in
+include/deepgemm_b200.h.  torch is used for tensors, the current stream and allocation of the
+transformed scale tensors only; all compute runs in the library's CUDA kernels.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Tuple, Union
+
+import torch
+
+from . import _lib
+from ._lib import GemmArgs, GemmConfig, check, lib
+
+kPackedFP4 = torch.int8          # csrc/utils/math.hpp:11
+Recipe3 = Tuple[int, int, int]
+Recipe2 = Tuple[int, int]
+
+
+def _require(cond: bool, what: str) -> None:
+    if not cond:
+        raise RuntimeError(f"Assertion error (deepgemm_amd_b200/api.py): {what}")
+
+
+def ceil_div(x: int, y: int) -> int:
+    return (x + y - 1) // y
+
+
+def align(x: int, y: int) -> int:
+    return ceil_div(x, y) * y
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+# ------------------------------------------------------------------------------------------------
+# Settings (csrc/apis/config.hpp:9-47, csrc/apis/layout.hpp:133-141)
+# ------------------------------------------------------------------------------------------------
+def init(library_root_path: Optional[str] = None) -> None:
+    check(lib.dg_init((library_root_path or _lib.PKG_DIR).encode()))
+
+
+def shutdown() -> None:
+    check(lib.dg_shutdown())
+
+
+def set_num_sms(num_sms: int) -> None:
+    check(lib.dg_set_num_sms(int(num_sms)))
+
+
+def get_num_sms() -> int:
+    return lib.dg_get_num_sms()
+
+
+def set_tc_util(tc_util: int) -> None:
+    check(lib.dg_set_tc_util(int(tc_util)))
+
+
+def get_tc_util() -> int:
+    return lib.dg_get_tc_util()
+
+
+def set_pdl(enabled: bool) -> None:
+    check(lib.dg_set_pdl(int(bool(enabled))))
+
+
+def get_pdl() -> bool:
+    return bool(lib.dg_get_pdl())
+
+
+_host_settings = {"deterministic": False, "ignore_compile_dims": False, "block_multiple_of": (1, 1)}
+
+
+def use_deterministic_algorithms(enabled: bool) -> None:
+    """Accepted for API parity; these kernels have one accumulation order per configuration
+    (no split-K), so results are bitwise reproducible either way."""
+    _host_settings["deterministic"] = bool(enabled)
+
+
+def set_ignore_compile_dims(value: bool) -> None:
+    """Accepted for API parity: M, N and K are always run-time kernel arguments here."""
+    _host_settings["ignore_compile_dims"] = bool(value)
+
+
+def set_block_size_multiple_of(value: Union[int, Tuple[int, int]]) -> None:
+    _host_settings["block_multiple_of"] = (value, value) if isinstance(value, int) else tuple(value)
+
+
+def set_mk_alignment_for_contiguous_layout(value: int) -> None:
+    check(lib.dg_set_mk_alignment_for_contiguous_layout(int(value)))
+
+
+def get_mk_alignment_for_contiguous_layout() -> int:
+    return lib.dg_get_mk_alignment_for_contiguous_layout()
+
+
+def get_theoretical_mk_alignment_for_contiguous_layout(expected_m: Optional[int] = None) -> int:
+    return lib.dg_get_theoretical_mk_alignment_for_contiguous_layout(-1 if expected_m is None else int(expected_m))
+
+
+get_m_alignment_for_contiguous_layout = get_mk_alignment_for_contiguous_layout
+get_k_alignment_for_contiguous_layout = get_mk_alignment_for_contiguous_layout
+
+
+# ------------------------------------------------------------------------------------------------
+# Scaling-factor layout (csrc/apis/layout.hpp:11-87, csrc/utils/layout.hpp:85-140)
+# ------------------------------------------------------------------------------------------------
+def get_tma_aligned_size(x: int, element_size: int) -> int:
+    r = lib.dg_get_tma_aligned_size(int(x), int(element_size))
+    if r < 0:
+        raise RuntimeError(_lib.last_error())
+    return r
+
+
+def _preprocess_sf(sf: torch.Tensor):
+    _require(sf.dim() in (2, 3), "dim == 2 or dim == 3")
+    _require(sf.dtype == torch.float, "sf.scalar_type() == torch::kFloat")
+    _require(sf.is_cuda, "t.is_cuda()")
+    batched = sf.unsqueeze(0) if sf.dim() == 2 else sf
+    return sf.dim(), batched
+
+
+def get_mn_major_tma_aligned_tensor(sf: torch.Tensor) -> torch.Tensor:
+    """FP32 scales -> MN-major with pitch align(mn, 4) (csrc/jit_kernels/impls/smxx_layout.hpp:60-106)."""
+    dim, b = _preprocess_sf(sf)
+    g, mn, sf_k = b.shape
+    amn = get_tma_aligned_size(mn, 4)
+    if (b.stride(0) == amn * sf_k or dim == 2) and b.stride(1) == 1 and b.stride(2) == amn:
+        return b.squeeze(0) if dim == 2 else b
+    out = torch.empty_strided((g, mn, sf_k), (amn * sf_k, 1, amn), dtype=torch.float, device=sf.device)
+    check(lib.dg_transpose_fp32_mn_major(b.data_ptr(), out.data_ptr(), g, mn, sf_k,
+                                         b.stride(0), b.stride(1), b.stride(2), _stream()))
+    return out.squeeze(0) if dim == 2 else out
+
+
+def _pack(sf: torch.Tensor, mn: int, gran_mn: int) -> torch.Tensor:
+    dim, b = _preprocess_sf(sf)
+    g, _, sf_k = b.shape
+    amn, packed_k = get_tma_aligned_size(mn, 4), ceil_div(sf_k, 4)
+    out = torch.empty_strided((g, mn, packed_k), (packed_k * amn, 1, amn), dtype=torch.int, device=sf.device)
+    check(lib.dg_pack_fp32_into_ue8m0(b.data_ptr(), out.data_ptr(), g, mn, sf_k, gran_mn,
+                                      b.stride(0), b.stride(1), b.stride(2), _stream()))
+    return out.squeeze(0) if dim == 2 else out
+
+
+def get_mn_major_tma_aligned_packed_ue8m0_tensor(sf: torch.Tensor, psum_layout: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """FP32 power-of-two scales [G?, mn, sf_k] -> packed UE8M0 int32 [G?, mn, ceil(sf_k/4)] with strides
+    (ceil(sf_k/4) * align(mn,4), 1, align(mn,4)) (csrc/jit_kernels/impls/smxx_layout.hpp:133-216)."""
+    if psum_layout is not None:
+        raise RuntimeError("psum layout is not built (deepgemm_amd_b200): pass the per-row grouped layout instead")
+    return _pack(sf, sf.size(-2), 1)
+
+
+def _check_sf_layout(sf, mn, k, gran_mn, gran_k, num_groups, tma_stride_check=False, type_check=None):
+    """csrc/utils/layout.hpp:101-140."""
+    if type_check is not None:
+        _require(sf.dtype == type_check, "sf.scalar_type() == type_check.value()")
+    _require(sf.dtype in (torch.float, torch.int), "sf_dtype == torch::kFloat or sf_dtype == torch::kInt")
+    _require(sf.dim() == int(num_groups is not None) + 2, "sf.dim() == static_cast<int>(num_groups.has_value()) + 2")
+    if num_groups is not None:
+        _require(sf.size(-3) == num_groups, "sf.size(-3) == num_groups.value()")
+    _require(sf.size(-2) == ceil_div(mn, gran_mn), "sf.size(-2) == ceil_div(mn, gran_mn)")
+    _require(sf.size(-1) == ceil_div(k, gran_k * (1 if sf.dtype == torch.float else 4)),
+             "sf.size(-1) == ceil_div(k, gran_k * (sf_dtype == torch::kFloat ? 1 : 4))")
+    if tma_stride_check:
+        if num_groups is not None:
+            _require(sf.stride(-3) == sf.stride(-1) * sf.size(-1), "sf.stride(-3) == sf.stride(-1) * sf.size(-1)")
+        _require(sf.stride(-2) == 1 or mn == 1, "sf.stride(-2) == 1 or mn == 1")
+        _require(sf.stride(-1) >= get_tma_aligned_size(mn, sf.element_size()), "sf.stride(-1) >= compact_stride")
+        _require(sf.stride(-1) % 4 == 0, "sf.stride(-1) % 4 == 0")
+    return sf
+
+
+def transform_sf_into_required_layout(sf: torch.Tensor, mn: int, k: int, recipe: Union[Recipe3, Recipe2],
+                                      num_groups: Optional[int] = None, is_sfa: Optional[bool] = None,
+                                      disable_ue8m0_cast: bool = False,
+                                      psum_layout: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """csrc/apis/layout.hpp:11-58, for sm_100: FP32 scales are broadcast along MN and packed to UE8M0;
+    int32 scales are validated only."""
+    recipe = tuple(recipe)
+    if len(recipe) == 3:
+        _require(is_sfa is not None, "is_sfa.has_value()")
+        gran_mn, gran_k = (recipe[0] if is_sfa else recipe[1]), recipe[2]
+    elif len(recipe) == 2:
+        _require(is_sfa is None, "not is_sfa.has_value()")
+        gran_mn, gran_k = recipe
+    else:
+        raise RuntimeError("Invalid recipe")
+    _check_sf_layout(sf, mn, k, gran_mn, gran_k, num_groups)
+    if disable_ue8m0_cast:
+        raise RuntimeError("disable_ue8m0_cast selects the FP32-scale (SM90) kernels, which this sm_100-only library does not build")
+    if psum_layout is not None:
+        raise RuntimeError("psum layout is not built (deepgemm_amd_b200)")
+    if sf.dtype == torch.float and gran_k in (32, 128):
+        return _pack(sf, mn, gran_mn)
+    if sf.dtype == torch.int and gran_mn == 1 and gran_k in (32, 128):
+        return _check_sf_layout(sf, mn, k, gran_mn, gran_k, num_groups, tma_stride_check=True, type_check=torch.int)
+    raise RuntimeError("Unknown SF transformation")
+
+
+def _default_recipe(sfa_dtype, sfb_dtype) -> Recipe3:
+    """csrc/utils/layout.hpp:85-98 (arch 10)."""
+    _require(sfb_dtype in (torch.float, torch.int), "sfb_dtype == torch::kFloat or sfb_dtype == torch::kInt")
+    return (1, 128, 128) if sfb_dtype == torch.float else (1, 1, 128)
+
+
+def _transform_sf_pair(sfa, sfb, m, n, k, recipe, recipe_a, recipe_b, num_groups_a, num_groups_b, disable_ue8m0_cast):
+    """csrc/apis/layout.hpp:60-87."""
+    if recipe_a is None and recipe is None:
+        recipe = _default_recipe(sfa.dtype, sfb.dtype)
+    _require((recipe_a is None) == (recipe_b is None), "recipe_a.has_value() == recipe_b.has_value()")
+    _require((recipe_a is None) != (recipe is None), "recipe_a.has_value() != recipe.has_value()")
+    if recipe is not None:
+        tsfa = transform_sf_into_required_layout(sfa, m, k, recipe, num_groups_a, True, disable_ue8m0_cast)
+        tsfb = transform_sf_into_required_layout(sfb, n, k, recipe, num_groups_b, False, disable_ue8m0_cast)
+        return tsfa, tsfb, recipe[2], recipe[2]
+    tsfa = transform_sf_into_required_layout(sfa, m, k, recipe_a, num_groups_a, None, disable_ue8m0_cast)
+    tsfb = transform_sf_into_required_layout(sfb, n, k, recipe_b, num_groups_b, None, disable_ue8m0_cast)
+    return tsfa, tsfb, recipe_a[1], recipe_b[1]
+
+
+# ------------------------------------------------------------------------------------------------
+# GEMMs (csrc/apis/gemm.hpp:78-318)
+# ------------------------------------------------------------------------------------------------
+def _major_check(t: torch.Tensor) -> None:
+    """csrc/utils/layout.hpp:19-27."""
+    _require(t.dim() in (2, 3), "dim == 2 or dim == 3")
+    if t.dim() == 3:
+        _require(t.stride(0) == t.size(-2) * t.size(-1), "t.stride(0) == t.size(-2) * t.size(-1)")
+    _require(t.stride(-2) == 1 or t.stride(-1) == 1, "t.stride(-2) == 1 or t.stride(-1) == 1")
+
+
+def _major_ab(t: torch.Tensor) -> int:
+    _major_check(t)
+    return _lib.DG_MAJOR_K if t.stride(-1) == 1 else _lib.DG_MAJOR_MN
+
+
+def _check_cd(t: torch.Tensor) -> None:
+    _major_check(t)
+    _require(t.stride(-1) == 1, "t.stride(-1) == 1")
+
+
+def _ab_dtype(t: torch.Tensor) -> int:
+    if t.dtype == torch.float8_e4m3fn:
+        return _lib.DG_FP8_E4M3
+    _require(t.dtype == kPackedFP4, "ab.scalar_type() == kPackedFP4 and arch_major == 10")
+    return _lib.DG_FP4_E2M1_X2
+
+
+def _logical_mn_k(t: torch.Tensor, major: int):
+    """Logical (mn, k) of a 2-D/3-D operand; packed FP4 doubles the contiguous dimension
+    (csrc/utils/layout.hpp:66-83)."""
+    _require(t.is_cuda, "t.is_cuda()")
+    mn, k = t.size(-2), t.size(-1)
+    if t.dtype != torch.float8_e4m3fn:
+        if major == _lib.DG_MAJOR_K:
+            k *= 2
+        else:
+            mn *= 2
+    return mn, k
+
+
+def _d_dtype(d: torch.Tensor) -> int:
+    return _lib.DG_BF16 if d.dtype == torch.bfloat16 else _lib.DG_FP32
+
+
+def _ld(t: torch.Tensor, major: int) -> int:
+    return t.stride(-2) if major == _lib.DG_MAJOR_K else t.stride(-1)
+
+
+def _fill_args(a, sfa, b, sfb, d, m, n, k, groups, major_a, major_b, gran_k_a, gran_k_b,
+               accumulate=False, alpha=None, layout=None, expected_m=0) -> GemmArgs:
+    args = GemmArgs()
+    args.a, args.sfa, args.b, args.sfb, args.d = a.data_ptr(), sfa.data_ptr(), b.data_ptr(), sfb.data_ptr(), d.data_ptr()
+    args.m, args.n, args.k, args.num_groups = m, n, k, groups
+    args.a_dtype, args.b_dtype, args.d_dtype = _ab_dtype(a), _ab_dtype(b), _d_dtype(d)
+    args.major_a, args.major_b = major_a, major_b
+    args.lda, args.ldb, args.ldd = _ld(a, major_a), _ld(b, major_b), d.stride(-2)
+    args.sfa_pitch, args.sfb_pitch = sfa.stride(-1), sfb.stride(-1)
+    args.gran_k_a, args.gran_k_b = gran_k_a, gran_k_b
+    args.accumulate = int(accumulate)
+    args.has_alpha = int(alpha is not None)
+    args.alpha = float(alpha) if alpha is not None else 1.0
+    args.grouped_layout = layout.data_ptr() if layout is not None else None
+    args.expected_m = int(expected_m)
+    args.stream = _stream()
+    return args
+
+
+def _resolve_alpha(alpha, epilogue):
+    """Only the Identity and Alpha epilogues are built (csrc/jit_kernels/impls/epilogue_class.hpp:111-127)."""
+    if epilogue is not None:
+        from .epilogue import Alpha, Identity
+        if isinstance(epilogue, Identity):
+            return alpha
+        if isinstance(epilogue, Alpha):
+            _require(alpha is None, "alpha and an Alpha epilogue are mutually exclusive")
+            return epilogue.alpha
+        raise RuntimeError(f"epilogue {type(epilogue).__name__} is not built (deepgemm_amd_b200): Identity and Alpha are")
+    return alpha
+
+
+def fp8_fp4_gemm_nt(a, b, d, c=None, recipe=None, recipe_a=None, recipe_b=None, compiled_dims: str = "nk",
+                    disable_ue8m0_cast: bool = False, alpha: Optional[float] = None, epilogue=None) -> None:
+    """D[M,N] = C + alpha * A[M,K] @ B[N,K]^T with a = (data, sf), b = (data, sf) (csrc/apis/gemm.hpp:78-133)."""
+    (a_data, a_sf), (b_data, b_sf) = a, b
+    major_a, major_b = _major_ab(a_data), _major_ab(b_data)
+    if a_data.dtype == kPackedFP4 and b_data.dtype == kPackedFP4:
+        _require(major_a == _lib.DG_MAJOR_K and major_b == _lib.DG_MAJOR_K, "major == cute::UMMA::Major::K")
+    _check_cd(d)
+    _ab_dtype(a_data), _ab_dtype(b_data)
+    m, k = _logical_mn_k(a_data, major_a)
+    n, k_ = _logical_mn_k(b_data, major_b)
+    _require(d.is_cuda and d.dim() == 2, "t.dim() == N")
+    _require(m == d.size(0) and n == d.size(1) and k == k_, "m == m_ and n == n_ and k == k_")
+    _require(d.dtype in (torch.bfloat16, torch.float), "d.scalar_type() == torch::kBFloat16 or d.scalar_type() == torch::kFloat")
+
+    # early_return (gemm.hpp:17-53)
+    if m == 0 or n == 0:
+        return
+    is_cd_same = c is not None and c.data_ptr() == d.data_ptr()
+    if is_cd_same:
+        _require(c.shape == d.shape and c.stride() == d.stride(), "c->sizes() == d.sizes() and c->strides() == d.strides()")
+    if c is not None:
+        _check_cd(c)
+        _require(d.dtype == c.dtype, "d.scalar_type() == c.value().scalar_type()")
+    if k == 0:
+        if not is_cd_same:
+            d.copy_(c) if c is not None else d.zero_()
+        return
+    if c is not None and not is_cd_same:
+        d.copy_(c)
+
+    sfa, sfb, gran_k_a, gran_k_b = _transform_sf_pair(a_sf, b_sf, m, n, k, recipe, recipe_a, recipe_b, None, None,
+                                                      disable_ue8m0_cast)
+    alpha = _resolve_alpha(alpha, epilogue)
+    args = _fill_args(a_data, sfa, b_data, sfb, d, m, n, k, 1, major_a, major_b, gran_k_a, gran_k_b,
+                      accumulate=c is not None, alpha=alpha)
+    check(lib.dg_fp8_fp4_gemm(C.byref(args)))
+
+
+def _t(x):
+    return (x[0].transpose(-1, -2), x[1].transpose(-1, -2))
+
+
+def fp8_fp4_gemm_nn(a, b, d, c=None, recipe=None, recipe_a=None, recipe_b=None, compiled_dims: str = "nk",
+                    disable_ue8m0_cast: bool = False, alpha=None, epilogue=None) -> None:
+    """csrc/apis/gemm.hpp:135-149."""
+    fp8_fp4_gemm_nt(a, _t(b), d, c, recipe, recipe_a, recipe_b, compiled_dims, disable_ue8m0_cast, alpha, epilogue)
+
+
+def fp8_fp4_gemm_tn(a, b, d, c=None, recipe=None, recipe_a=None, recipe_b=None, compiled_dims: str = "mn",
+                    disable_ue8m0_cast: bool = False, alpha=None, epilogue=None) -> None:
+    """csrc/apis/gemm.hpp:151-165."""
+    fp8_fp4_gemm_nt(_t(a), _t(b), d, c, recipe, recipe_a, recipe_b, compiled_dims, disable_ue8m0_cast, alpha, epilogue)
+
+
+def fp8_fp4_gemm_tt(a, b, d, c=None, recipe=None, recipe_a=None, recipe_b=None, compiled_dims: str = "mn",
+                    disable_ue8m0_cast: bool = False, alpha=None, epilogue=None) -> None:
+    """csrc/apis/gemm.hpp:167-179."""
+    fp8_fp4_gemm_nt(_t(a), b, d, c, recipe, recipe_a, recipe_b, compiled_dims, disable_ue8m0_cast, alpha, epilogue)
+
+
+def m_grouped_fp8_fp4_gemm_nt_contiguous(a, b, d, grouped_layout, recipe=None, recipe_a=None, recipe_b=None,
+                                         compiled_dims: str = "nk", disable_ue8m0_cast: bool = False,
+                                         use_psum_layout: bool = False, ensure_zero_padding: bool = True,
+                                         expected_m_for_psum_layout: Optional[int] = None, epilogue=None) -> None:
+    """D[M_total,N] = A[M_total,K] @ B[g(row),N,K]^T, expert id per row in grouped_layout (-1 on padding rows)
+    (csrc/apis/gemm.hpp:181-250)."""
+    (a_data, a_sf), (b_data, b_sf) = a, b
+    major_a, major_b = _major_ab(a_data), _major_ab(b_data)
+    _require(major_a == _lib.DG_MAJOR_K, "major_a == cute::UMMA::Major::K")
+    _require(grouped_layout.is_contiguous(), "grouped_layout.is_contiguous()")
+    m, k = _logical_mn_k(a_data, major_a)
+    _require(b_data.dim() == 3, "t.dim() == N")
+    n, k_ = _logical_mn_k(b_data, major_b)
+    num_groups = b_data.size(0)
+    _require(d.is_cuda and d.dim() == 2, "t.dim() == N")
+    _require(m == d.size(0) and n == d.size(1) and k == k_, "m == m_ and n == n_ and k == k_")
+    _require(n > 0 and k > 0 and num_groups > 0, "n > 0 and k > 0 and num_groups > 0")
+    _require(d.dtype == torch.bfloat16, "d.scalar_type() == torch::kBFloat16")
+    _require(grouped_layout.dtype == torch.int, "grouped_layout.scalar_type() == torch::kInt")
+    if use_psum_layout:
+        raise RuntimeError("use_psum_layout is not built (deepgemm_amd_b200): pass the per-row grouped layout")
+    _require(grouped_layout.dim() == 1 and grouped_layout.size(0) == m, "m == m__")
+    _require(expected_m_for_psum_layout is None, "not expected_m_for_psum_layout.has_value()")
+    _check_cd(d)
+    if m == 0:
+        return
+    sfa, sfb, gran_k_a, gran_k_b = _transform_sf_pair(a_sf, b_sf, m, n, k, recipe, recipe_a, recipe_b, None, num_groups,
+                                                      disable_ue8m0_cast)
+    _require(_resolve_alpha(None, epilogue) is None, "grouped GEMMs take the Identity epilogue only")
+    args = _fill_args(a_data, sfa, b_data, sfb, d, m, n, k, num_groups, major_a, major_b, gran_k_a, gran_k_b,
+                      layout=grouped_layout)
+    check(lib.dg_m_grouped_fp8_fp4_gemm_contiguous(C.byref(args)))
+
+
+def m_grouped_fp8_fp4_gemm_nn_contiguous(a, b, d, grouped_layout, recipe=None, recipe_a=None, recipe_b=None,
+                                         compiled_dims: str = "nk", disable_ue8m0_cast: bool = False,
+                                         use_psum_layout: bool = False, ensure_zero_padding: bool = True,
+                                         epilogue=None) -> None:
+    """csrc/apis/gemm.hpp:252-267."""
+    m_grouped_fp8_fp4_gemm_nt_contiguous(a, _t(b), d, grouped_layout, recipe, recipe_a, recipe_b, compiled_dims,
+                                         disable_ue8m0_cast, use_psum_layout, ensure_zero_padding, None, epilogue)
+
+
+def m_grouped_fp8_fp4_gemm_nt_masked(a, b, d, masked_m, expected_m: int, recipe=None, recipe_a=None, recipe_b=None,
+                                     compiled_dims: str = "nk", disable_ue8m0_cast: bool = False, epilogue=None) -> None:
+    """D[g,:masked_m[g],:] = A[g,:masked_m[g],:] @ B[g]^T; masked_m stays on the device, so the call is
+    capturable in a CUDA graph; rows at or beyond masked_m[g] are not written (csrc/apis/gemm.hpp:269-318)."""
+    (a_data, a_sf), (b_data, b_sf) = a, b
+    major_a, major_b = _major_ab(a_data), _major_ab(b_data)
+    _require(major_a == _lib.DG_MAJOR_K and major_b == _lib.DG_MAJOR_K,
+             "major_a == cute::UMMA::Major::K and major_b == cute::UMMA::Major::K")
+    _require(masked_m.is_contiguous(), "masked_m.is_contiguous()")
+    _require(a_data.dim() == 3 and b_data.dim() == 3 and d.dim() == 3, "t.dim() == N")
+    m, k = _logical_mn_k(a_data, major_a)
+    n, k_ = _logical_mn_k(b_data, major_b)
+    g = a_data.size(0)
+    _require(g == b_data.size(0) == d.size(0) == masked_m.numel(),
+             "num_groups == num_groups_ and num_groups == num_groups__ and num_groups == num_groups___")
+    _require(m == d.size(1) and n == d.size(2) and k == k_, "m == m_ and n == n_ and k == k_")
+    _require(expected_m > 0 and m > 0 and n > 0 and k > 0 and g > 0,
+             "expected_m > 0 and m > 0 and n > 0 and k > 0 and num_groups > 0")
+    _require(d.dtype == torch.bfloat16, "d.scalar_type() == torch::kBFloat16")
+    _require(masked_m.dtype == torch.int, "masked_m.scalar_type() == torch::kInt")
+    _check_cd(d)
+    sfa, sfb, gran_k_a, gran_k_b = _transform_sf_pair(a_sf, b_sf, m, n, k, recipe, recipe_a, recipe_b, g, g, disable_ue8m0_cast)
+    _require(_resolve_alpha(None, epilogue) is None, "grouped GEMMs take the Identity epilogue only")
+    args = _fill_args(a_data, sfa, b_data, sfb, d, m, n, k, g, major_a, major_b, gran_k_a, gran_k_b,
+                      layout=masked_m, expected_m=expected_m)
+    check(lib.dg_m_grouped_fp8_fp4_gemm_masked(C.byref(args)))
+
+
+# Aliases registered by the reference (csrc/apis/gemm.hpp:922-930)
+fp8_gemm_nt, fp8_gemm_nn, fp8_gemm_tn, fp8_gemm_tt = fp8_fp4_gemm_nt, fp8_fp4_gemm_nn, fp8_fp4_gemm_tn, fp8_fp4_gemm_tt
+fp4_gemm_nt = fp8_fp4_gemm_nt
+m_grouped_fp8_gemm_nt_contiguous = m_grouped_fp8_fp4_gemm_nt_contiguous
+m_grouped_fp8_gemm_nn_contiguous = m_grouped_fp8_fp4_gemm_nn_contiguous
+m_grouped_fp4_gemm_nt_contiguous = m_grouped_fp8_fp4_gemm_nt_contiguous
+m_grouped_fp8_gemm_nt_masked = m_grouped_fp8_fp4_gemm_nt_masked
+m_grouped_fp4_gemm_nt_masked = m_grouped_fp8_fp4_gemm_nt_masked
+
+
+# ------------------------------------------------------------------------------------------------
+# Introspection used by the tests and the benchmark
+# ------------------------------------------------------------------------------------------------
+def get_gemm_config(kind: int, m: int, n: int, k: int, num_groups: int = 1, expected_m: int = 0,
+                    b_is_fp4: bool = False, d_is_fp32: bool = False, gran_k_a: int = 128, gran_k_b: int = 128) -> dict:
+    """The tile configuration the heuristics choose for a problem (host only, needs no GPU)."""
+    args = GemmArgs()
+    args.m, args.n, args.k, args.num_groups = m, n, k, num_groups
+    args.a_dtype, args.b_dtype = _lib.DG_FP8_E4M3, (_lib.DG_FP4_E2M1_X2 if b_is_fp4 else _lib.DG_FP8_E4M3)
+    args.d_dtype = _lib.DG_FP32 if d_is_fp32 else _lib.DG_BF16
+    args.lda, args.ldb, args.ldd = k, (k // 2 if b_is_fp4 else k), n
+    args.sfa_pitch, args.sfb_pitch = align(m, 4), align(n, 4)
+    args.gran_k_a, args.gran_k_b = gran_k_a, gran_k_b
+    args.expected_m = expected_m
+    cfg = GemmConfig()
+    check(lib.dg_get_gemm_config(kind, C.byref(args), C.byref(cfg)))
+    return cfg.as_dict()
+
+
+def precompile_gemm(kind: int, m: int, n: int, k: int, num_groups: int = 1, expected_m: int = 0,
+                    b_is_fp4: bool = False, d_is_fp32: bool = False, accumulate: bool = False,
+                    gran_k_a: int = 128, gran_k_b: int = 128) -> None:
+    """Compile the kernel a GEMM of this shape would use into the cache (needs nvcc, no GPU)."""
+    args = GemmArgs()
+    args.m, args.n, args.k, args.num_groups = m, n, k, num_groups
+    args.a_dtype, args.b_dtype = _lib.DG_FP8_E4M3, (_lib.DG_FP4_E2M1_X2 if b_is_fp4 else _lib.DG_FP8_E4M3)
+    args.d_dtype = _lib.DG_FP32 if d_is_fp32 else _lib.DG_BF16
+    args.lda, args.ldb, args.ldd = k, (k // 2 if b_is_fp4 else k), n
+    args.sfa_pitch, args.sfb_pitch = align(m, 4), align(n, 4)
+    args.gran_k_a, args.gran_k_b = gran_k_a, gran_k_b
+    args.expected_m = expected_m
+    args.accumulate = int(accumulate)
+    check(lib.dg_gemm_precompile(kind, C.byref(args)))
+
+
+def kernel_status() -> int:
+    """Status word written by a kernel whose bounded wait ran out (0 = none).  Synchronises the device first."""
+    torch.cuda.synchronize()
+    return lib.dg_kernel_status() & 0xFFFFFFFF
+
+
+def reset_kernel_status() -> None:
+    lib.dg_reset_kernel_status()

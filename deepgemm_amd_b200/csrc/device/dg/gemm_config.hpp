@@ -1,0 +1,58 @@
+// Shared-memory and tensor-memory budget of the GEMM kernel as constexpr arithmetic, included by the
+// device code (with the DG_* macros as arguments) and by the host heuristics (with candidate values),
+// so the two can never disagree about a byte offset.
+#pragma once
+
+#include <cstdint>
+
+#if defined(__CUDACC__)
+#define DG_HDC __host__ __device__ constexpr
+#else
+#define DG_HDC constexpr
+#endif
+
+namespace dg {
+
+constexpr uint32_t kSmemCapacity = 232448;      // largest dynamic shared memory per CTA on sm_100 (227 KB)
+constexpr uint32_t kTmemCapacityCols = 512;
+
+struct GemmLayout {
+    uint32_t block_m, block_n, block_k, num_stages, d_elem_bytes;
+
+    DG_HDC uint32_t sf_block_n() const { return (block_n + 127) / 128 * 128; }
+    // Row width of one D staging buffer / TMA store: the widest swizzle span that divides a tile row
+    DG_HDC uint32_t store_row_bytes() const {
+        return (block_n * d_elem_bytes) % 128 == 0 ? 128 : ((block_n * d_elem_bytes) % 64 == 0 ? 64 : 32);
+    }
+    DG_HDC uint32_t store_cols() const { return store_row_bytes() / d_elem_bytes; }
+    DG_HDC uint32_t num_stores() const { return block_n / store_cols(); }
+    DG_HDC uint32_t store_stage_bytes() const { return block_m * store_row_bytes(); }
+    DG_HDC uint32_t num_store_stages() const { return 2; }
+
+    DG_HDC uint32_t a_bytes() const { return block_m * block_k; }        // one byte per element (FP8, or FP4 in 16-byte containers)
+    DG_HDC uint32_t b_bytes() const { return block_n * block_k; }
+    DG_HDC uint32_t sfa_bytes() const { return 128 * 4; }
+    DG_HDC uint32_t sfb_bytes() const { return sf_block_n() * 4; }
+
+    DG_HDC uint32_t off_d() const { return 0; }
+    DG_HDC uint32_t off_a() const { return (num_store_stages() * store_stage_bytes() + 1023) / 1024 * 1024; }
+    DG_HDC uint32_t off_b() const { return off_a() + num_stages * a_bytes(); }
+    DG_HDC uint32_t off_sfa() const { return off_b() + num_stages * b_bytes(); }
+    DG_HDC uint32_t off_sfb() const { return off_sfa() + num_stages * sfa_bytes(); }
+    DG_HDC uint32_t off_barriers() const { return off_sfb() + num_stages * sfb_bytes(); }
+    DG_HDC uint32_t num_barriers() const { return 3 * num_stages + 2 * 2; }
+    DG_HDC uint32_t off_misc() const { return off_barriers() + num_barriers() * 8; }
+    DG_HDC uint32_t total_bytes() const { return off_misc() + 16; }
+    DG_HDC uint32_t bytes_per_stage() const { return a_bytes() + b_bytes() + sfa_bytes() + sfb_bytes() + 3 * 8; }
+
+    // Tensor memory: two accumulator stages, then SFA (4 columns per 128 rows) and SFB
+    DG_HDC uint32_t tmem_col_sfa() const { return 2 * block_n; }
+    DG_HDC uint32_t tmem_col_sfb() const { return tmem_col_sfa() + 128 / 32; }
+    DG_HDC uint32_t tmem_cols_used() const { return tmem_col_sfb() + sf_block_n() / 32; }
+    DG_HDC uint32_t tmem_cols_alloc() const {
+        const uint32_t u = tmem_cols_used();
+        return u <= 32 ? 32 : u <= 64 ? 64 : u <= 128 ? 128 : u <= 256 ? 256 : 512;
+    }
+};
+
+}  // namespace dg

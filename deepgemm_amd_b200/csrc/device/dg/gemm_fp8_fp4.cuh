@@ -1,0 +1,404 @@
+// Persistent, warp-specialised block-scaled GEMM for sm_100a:
+//     D[M,N] (+)= alpha * (SFA . A[M,K]) (SFB . B[N,K])^T
+// A, B: float8_e4m3 or packed float4_e2m1, K-major; SFA / SFB: packed UE8M0 (four exponents per
+// int32, MN-major) with one scale per 128 or per 32 elements of K; D: bf16 or fp32, row-major.
+//
+// It serves the same operations as the reference kernel sm100_fp8_fp4_gemm_1d1d_impl
+// (deep_gemm/include/deep_gemm/impls/sm100_fp8_fp4_gemm_1d1d.cuh:38) for GemmType Normal,
+// MGroupedContiguous and MGroupedMasked, with its own structure:
+//
+//   warp 0      TMA producer: fills a ring of kNumStages {A, B, SFA, SFB} shared-memory stages
+//   warp 1      MMA issuer: one thread issues tcgen05.cp (scales -> tensor memory) and
+//               tcgen05.mma.kind::mxf8f6f4.block_scale into one of two accumulator stages
+//   warp 2      allocates tensor memory; rearranges each scale chunk for tcgen05.cp
+//   warp 3      idle
+//   warps 4-7   epilogue: tcgen05.ld -> alpha -> bf16/fp32 -> swizzled staging -> TMA store
+//               (row-predicated direct stores for ragged tiles of the masked layout)
+//
+// The configuration arrives as DG_* macros set by the host-side code generator:
+//   DG_GEMM_TYPE (0 dense, 1 m-grouped contiguous, 2 m-grouped masked), DG_BLOCK_N, DG_NUM_STAGES,
+//   DG_A_FP4, DG_B_FP4, DG_GRAN_K_A, DG_GRAN_K_B, DG_D_FP32, DG_ACCUMULATE, DG_RASTER_GROUP.
+#pragma once
+
+#include <cuda_bf16.h>
+
+#include "gemm_config.hpp"
+#include "ptx.cuh"
+#include "tile_scheduler.cuh"
+
+namespace dg {
+
+#ifndef DG_GEMM_TYPE
+#error "DG_GEMM_TYPE and the other DG_* configuration macros must be defined by the code generator"
+#endif
+
+constexpr uint32_t kGemmType   = DG_GEMM_TYPE;
+constexpr uint32_t BLOCK_M     = 128;
+constexpr uint32_t BLOCK_N     = DG_BLOCK_N;
+constexpr uint32_t BLOCK_K     = 128;
+constexpr uint32_t kNumStages  = DG_NUM_STAGES;
+constexpr bool     kAIsFP4     = DG_A_FP4 != 0;
+constexpr bool     kBIsFP4     = DG_B_FP4 != 0;
+constexpr uint32_t kGranKA     = DG_GRAN_K_A;
+constexpr uint32_t kGranKB     = DG_GRAN_K_B;
+constexpr bool     kDIsFP32    = DG_D_FP32 != 0;
+constexpr bool     kAccumulate = DG_ACCUMULATE != 0;
+constexpr uint32_t kRasterGroup = DG_RASTER_GROUP;
+
+constexpr uint32_t UMMA_M = 128, UMMA_N = BLOCK_N, UMMA_K = 32;
+constexpr uint32_t kNumThreads = 256, kNumEpilogueThreads = 128, kEpilogueWarpBase = 4;
+constexpr uint32_t kNumAccumStages = 2;
+
+static_assert(BLOCK_N % 16 == 0 && BLOCK_N >= 16 && BLOCK_N <= 240, "UMMA_N must be a multiple of 16 that leaves room for the scales");
+static_assert(kGranKA == 32 || kGranKA == 128, "one scale per 32 or 128 elements of K");
+static_assert(kGranKB == 32 || kGranKB == 128, "one scale per 32 or 128 elements of K");
+static_assert(kNumStages >= 2 && kNumStages <= 32, "pipeline depth");
+
+// Scales: a packed int32 holds 4 scales.  With one scale per 128 K it spans 4 K-blocks, so the
+// chunk is fetched on every 4th K-block; with one per 32 K it spans exactly one K-block.
+constexpr uint32_t kSFAPeriod = kGranKA == 128 ? 4 : 1;
+constexpr uint32_t kSFBPeriod = kGranKB == 128 ? 4 : 1;
+constexpr uint32_t SF_BLOCK_M = 128;
+constexpr uint32_t SF_BLOCK_N = (BLOCK_N + 127) / 128 * 128;
+
+// Shared memory and tensor memory maps (every operand stage starts on a 1024-byte boundary, as the
+// 128-byte swizzle requires); the arithmetic lives in gemm_config.hpp, shared with the host heuristics
+constexpr uint32_t kDElemBytes = kDIsFP32 ? 4 : 2;
+constexpr GemmLayout kLayout{BLOCK_M, BLOCK_N, BLOCK_K, kNumStages, kDElemBytes};
+constexpr uint32_t kStoreRowBytes   = kLayout.store_row_bytes();
+constexpr uint32_t kStoreCols       = kLayout.store_cols();          // columns of D per TMA store
+constexpr uint32_t kNumStores       = kLayout.num_stores();
+constexpr uint32_t kNumStoreStages  = kLayout.num_store_stages();
+constexpr uint32_t kStoreStageBytes = kLayout.store_stage_bytes();
+constexpr uint32_t kSmemD   = kLayout.off_d();
+constexpr uint32_t kSmemA   = kLayout.off_a();
+constexpr uint32_t kABytes  = kLayout.a_bytes();
+constexpr uint32_t kBBytes  = kLayout.b_bytes();
+constexpr uint32_t kSmemB   = kLayout.off_b();
+constexpr uint32_t kSFABytes = kLayout.sfa_bytes();
+constexpr uint32_t kSFBBytes = kLayout.sfb_bytes();
+constexpr uint32_t kSmemSFA = kLayout.off_sfa();
+constexpr uint32_t kSmemSFB = kLayout.off_sfb();
+constexpr uint32_t kSmemBar = kLayout.off_barriers();   // full, sf_full, empty per stage; tmem_full, tmem_empty per accumulator
+constexpr uint32_t kSmemMisc = kLayout.off_misc();      // tensor-memory base address, abort flag
+constexpr uint32_t kSmemTotal = kLayout.total_bytes();
+static_assert(kBBytes % 1024 == 0, "B stage must keep 1024-byte alignment");
+static_assert(kSmemTotal <= kSmemCapacity, "shared memory budget exceeded");
+static_assert(kStoreCols % 16 == 0 || kDIsFP32, "a store covers whole 16-column tensor-memory loads");
+
+// Bytes the TMA engine reports per stage (packed FP4 counts its global-memory bytes)
+constexpr uint32_t kTxBytesAB = kABytes / (kAIsFP4 ? 2 : 1) + kBBytes / (kBIsFP4 ? 2 : 1);
+
+constexpr uint32_t kTmemColSFA = kLayout.tmem_col_sfa();
+constexpr uint32_t kTmemColSFB = kLayout.tmem_col_sfb();
+constexpr uint32_t kTmemCols = kLayout.tmem_cols_alloc();
+static_assert(kLayout.tmem_cols_used() <= kTmemCapacityCols, "tensor memory budget exceeded");
+
+enum Role : uint32_t { kRoleProducer = 1, kRoleMma = 2, kRoleSF = 3, kRoleEpilogue = 4 };
+
+struct GemmParams {
+    const int* grouped_layout;   // contiguous: expert id per row (-1 = padding); masked: rows used per group
+    void* d;                     // D base pointer (for the direct-store path of ragged masked tiles)
+    int* status;                 // host-visible status word, 0 = ok
+    uint32_t shape_m;            // dense / contiguous: rows of A;  masked: max_m (rows per group)
+    uint32_t shape_n;
+    uint32_t shape_k;
+    uint32_t num_groups;
+    uint32_t ldd;                // row pitch of D in elements
+    float alpha;
+};
+
+}  // namespace dg
+
+extern "C" __global__ void __launch_bounds__(dg::kNumThreads, 1)
+dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
+                const __grid_constant__ CUtensorMap tm_b,
+                const __grid_constant__ CUtensorMap tm_sfa,
+                const __grid_constant__ CUtensorMap tm_sfb,
+                const __grid_constant__ CUtensorMap tm_d,
+                const dg::GemmParams p) {
+    using namespace dg;
+    extern __shared__ __align__(1024) uint8_t smem[];
+
+    const uint32_t warp_idx = __shfl_sync(0xFFFFFFFFu, threadIdx.x / 32, 0);
+    const uint32_t lane = lane_id();
+    const uint32_t smem_base = smem_u32(smem);
+
+    auto full_bar     = [&](uint32_t s) { return smem_base + kSmemBar + s * 8; };
+    auto sf_full_bar  = [&](uint32_t s) { return smem_base + kSmemBar + (kNumStages + s) * 8; };
+    auto empty_bar    = [&](uint32_t s) { return smem_base + kSmemBar + (2 * kNumStages + s) * 8; };
+    auto tmem_full_bar  = [&](uint32_t a) { return smem_base + kSmemBar + (3 * kNumStages + a) * 8; };
+    auto tmem_empty_bar = [&](uint32_t a) { return smem_base + kSmemBar + (3 * kNumStages + kNumAccumStages + a) * 8; };
+    volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(smem + kSmemMisc);
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + kSmemMisc + 4);
+    const AbortCtx ctx{abort_flag, p.status};
+
+    // ---- set-up -------------------------------------------------------------------------------
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        prefetch_tensormap(&tm_a);
+        prefetch_tensormap(&tm_b);
+        prefetch_tensormap(&tm_sfa);
+        prefetch_tensormap(&tm_sfb);
+        prefetch_tensormap(&tm_d);
+    }
+    if (warp_idx == 1 && lane == 0) {
+        for (uint32_t s = 0; s < kNumStages; ++s) {
+            mbar_init(full_bar(s), 1 + 32);      // producer's expect_tx arrive + the 32 lanes of the scale warp
+            mbar_init(sf_full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);          // tcgen05.commit
+        }
+        for (uint32_t a = 0; a < kNumAccumStages; ++a) {
+            mbar_init(tmem_full_bar(a), 1);      // tcgen05.commit
+            mbar_init(tmem_empty_bar(a), kNumEpilogueThreads);
+        }
+        fence_mbar_init();
+    } else if (warp_idx == 2) {
+        tmem_alloc<1>(smem_u32(const_cast<uint32_t*>(tmem_base_slot)), kTmemCols);
+        tmem_relinquish<1>();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_base_slot;
+
+    const uint32_t num_k_blocks = (p.shape_k + BLOCK_K - 1) / BLOCK_K;
+    const uint32_t sfa_rows_per_group = (p.shape_k + kGranKA * 4 - 1) / (kGranKA * 4);   // packed K extent of SFA
+    const uint32_t sfb_rows_per_group = (p.shape_k + kGranKB * 4 - 1) / (kGranKB * 4);
+
+    TileScheduler<kGemmType> sched(BLOCK_M, BLOCK_N, kRasterGroup, p.shape_m, p.shape_n, p.num_groups, p.grouped_layout,
+                                   blockIdx.x, gridDim.x);
+    Tile tile;
+    uint32_t stage = 0, phase = 0;
+    auto advance_stage = [&]() {
+        stage = stage + 1 == kNumStages ? 0 : stage + 1;
+        phase ^= (stage == 0);
+    };
+
+    if (warp_idx == 0) {
+        // ================= TMA producer =================
+        if (lane == 0) {
+            bool ok = true;
+            while (ok && sched.next(tile)) {
+                // Row coordinates of this tile in the 2-D views of A, B and the scale tensors
+                const uint32_t a_row = tile.a_row_base + tile.m_block * BLOCK_M;
+                const uint32_t b_row = tile.group * p.shape_n + tile.n_block * BLOCK_N;
+                const uint32_t sfa_mn = tile.sfa_mn_base + tile.m_block * BLOCK_M;
+                const uint32_t sfa_row0 = tile.sfa_group * sfa_rows_per_group;
+                const uint32_t sfb_row0 = tile.group * sfb_rows_per_group;
+                for (uint32_t kb = 0; kb < num_k_blocks; ++kb, advance_stage()) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1, ctx, kRoleProducer, 1)) { ok = false; break; }
+                    uint32_t sf_bytes = 0;
+                    if (kb % kSFAPeriod == 0) sf_bytes += kSFABytes;
+                    if (kb % kSFBPeriod == 0) sf_bytes += kSFBBytes;
+                    mbar_arrive_expect_tx(sf_full_bar(stage), sf_bytes);
+                    if (kb % kSFAPeriod == 0)
+                        tma_load_2d(smem_base + kSmemSFA + stage * kSFABytes, &tm_sfa, sf_full_bar(stage),
+                                    static_cast<int32_t>(sfa_mn), static_cast<int32_t>(sfa_row0 + kb / kSFAPeriod));
+                    if (kb % kSFBPeriod == 0)
+                        tma_load_2d(smem_base + kSmemSFB + stage * kSFBBytes, &tm_sfb, sf_full_bar(stage),
+                                    static_cast<int32_t>(tile.n_block * BLOCK_N), static_cast<int32_t>(sfb_row0 + kb / kSFBPeriod));
+                    mbar_arrive_expect_tx(full_bar(stage), kTxBytesAB);
+                    tma_load_2d(smem_base + kSmemA + stage * kABytes, &tm_a, full_bar(stage),
+                                static_cast<int32_t>(kb * BLOCK_K), static_cast<int32_t>(a_row));
+                    tma_load_2d(smem_base + kSmemB + stage * kBBytes, &tm_b, full_bar(stage),
+                                static_cast<int32_t>(kb * BLOCK_K), static_cast<int32_t>(b_row));
+                }
+            }
+        }
+    } else if (warp_idx == 1) {
+        // ================= MMA issuer =================
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_instr_desc_block_scaled(kAIsFP4 ? kFmtE2M1 : kFmtE4M3, kBIsFP4 ? kFmtE2M1 : kFmtE4M3,
+                                                                    0, 0, UMMA_M, UMMA_N);
+            bool ok = true;
+            uint32_t tile_iter = 0;
+            while (ok && sched.next(tile)) {
+                const uint32_t accum = tile_iter & 1, accum_phase = (tile_iter >> 1) & 1;
+                ++tile_iter;
+                if (!mbar_wait(tmem_empty_bar(accum), accum_phase ^ 1, ctx, kRoleMma, 1)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t tmem_d = tmem_base + accum * UMMA_N;
+                for (uint32_t kb = 0; kb < num_k_blocks; ++kb, advance_stage()) {
+                    if (!mbar_wait(full_bar(stage), phase, ctx, kRoleMma, 2)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    // Scales: shared memory (rearranged by warp 2) -> tensor memory
+                    if (kb % kSFAPeriod == 0)
+                        tc_cp_32x128b_warpx4<1>(tmem_base + kTmemColSFA,
+                                                make_smem_desc(smem_base + kSmemSFA + stage * kSFABytes, 0, 128, kSwizzleNone));
+                    if (kb % kSFBPeriod == 0) {
+                        #pragma unroll
+                        for (uint32_t i = 0; i < SF_BLOCK_N / 128; ++i)
+                            tc_cp_32x128b_warpx4<1>(tmem_base + kTmemColSFB + i * 4,
+                                                    make_smem_desc(smem_base + kSmemSFB + stage * kSFBBytes + i * 512, 0, 128, kSwizzleNone));
+                    }
+                    const uint64_t a_desc = make_smem_desc(smem_base + kSmemA + stage * kABytes, 0, 1024, kSwizzle128B);
+                    const uint64_t b_desc = make_smem_desc(smem_base + kSmemB + stage * kBBytes, 0, 1024, kSwizzle128B);
+                    #pragma unroll
+                    for (uint32_t j = 0; j < BLOCK_K / UMMA_K; ++j) {
+                        // Which byte of the packed scale word applies to these 32 elements of K
+                        const uint32_t sfa_id = kGranKA == 32 ? j : (kb % 4);
+                        const uint32_t sfb_id = kGranKB == 32 ? j : (kb % 4);
+                        // Advancing K by 32 bytes inside the 128-byte swizzle atom = +2 in the (>>4) address field
+                        tc_mma_mxf8f6f4<1>(tmem_d, a_desc + j * (UMMA_K >> 4), b_desc + j * (UMMA_K >> 4),
+                                           instr_desc_with_sf_ids(idesc, sfa_id, sfb_id),
+                                           tmem_base + kTmemColSFA, tmem_base + kTmemColSFB, (kb | j) != 0);
+                    }
+                    tc_commit(empty_bar(stage));                       // releases the stage once its MMAs have read it
+                    if (kb + 1 == num_k_blocks)
+                        tc_commit(tmem_full_bar(accum));               // accumulator complete
+                }
+            }
+        }
+    } else if (warp_idx == 2) {
+        // ================= scale rearrangement =================
+        // tcgen05.cp reads 32 rows x 16 bytes and writes row r to lane r: the scale word of tile row
+        // (c * 32 + r) has to sit at word (r * 4 + c).  TMA delivered the 128 words in row order.
+        auto rearrange = [&](uint32_t chunk_addr) {
+            uint32_t v[4];
+            #pragma unroll
+            for (uint32_t c = 0; c < 4; ++c)
+                v[c] = ld_shared_u32(chunk_addr + (c * 32 + lane) * 4);
+            __syncwarp();
+            st_shared_v4(chunk_addr + lane * 16, v[0], v[1], v[2], v[3]);
+        };
+        bool ok = true;
+        while (ok && sched.next(tile)) {
+            for (uint32_t kb = 0; kb < num_k_blocks; ++kb, advance_stage()) {
+                if (!mbar_wait(sf_full_bar(stage), phase, ctx, kRoleSF, 1)) { ok = false; break; }
+                if (kb % kSFAPeriod == 0)
+                    rearrange(smem_base + kSmemSFA + stage * kSFABytes);
+                if (kb % kSFBPeriod == 0) {
+                    #pragma unroll
+                    for (uint32_t i = 0; i < SF_BLOCK_N / 128; ++i)
+                        rearrange(smem_base + kSmemSFB + stage * kSFBBytes + i * 512);
+                }
+                fence_proxy_async_smem();
+                mbar_arrive(full_bar(stage));
+            }
+        }
+    } else if (warp_idx >= kEpilogueWarpBase) {
+        // ================= epilogue =================
+        const uint32_t quarter = warp_idx - kEpilogueWarpBase;        // tensor-memory lanes [32q, 32q+32)
+        const uint32_t row_in_tile = quarter * 32 + lane;
+        const uint32_t epi_tid = threadIdx.x - kEpilogueWarpBase * 32;
+        bool ok = true;
+        uint32_t tile_iter = 0, store_iter = 0;
+        while (ok && sched.next(tile)) {
+            const uint32_t accum = tile_iter & 1, accum_phase = (tile_iter >> 1) & 1;
+            ++tile_iter;
+            if (!mbar_wait(tmem_full_bar(accum), accum_phase, ctx, kRoleEpilogue, 1)) { ok = false; break; }
+            tc_fence_after_sync();
+
+            const uint32_t d_row0 = tile.d_row_base + tile.m_block * BLOCK_M;
+            const uint32_t n0 = tile.n_block * BLOCK_N;
+            const uint32_t tmem_row_addr = tmem_base + ((quarter * 32) << 16) + accum * UMMA_N;
+            const bool direct = kGemmType == 2 && tile.valid_rows < BLOCK_M;
+
+            #pragma unroll 1
+            for (uint32_t s = 0; s < kNumStores; ++s) {
+                constexpr uint32_t kLoadsPerStore = kStoreCols / 16;
+                uint32_t v[kLoadsPerStore][16];
+                #pragma unroll
+                for (uint32_t l = 0; l < kLoadsPerStore; ++l)
+                    tmem_ld_32x32b_x16(tmem_row_addr + s * kStoreCols + l * 16, v[l]);
+                tmem_ld_wait();
+                if (s + 1 == kNumStores) {
+                    // The accumulator is in registers: hand the tensor-memory stage back to the MMA warp
+                    tc_fence_before_sync();
+                    mbar_arrive(tmem_empty_bar(accum));
+                }
+                #pragma unroll
+                for (uint32_t l = 0; l < kLoadsPerStore; ++l)
+                    #pragma unroll
+                    for (uint32_t i = 0; i < 16; ++i)
+                        v[l][i] = __float_as_uint(__uint_as_float(v[l][i]) * p.alpha);
+
+                if (!direct) {
+                    const uint32_t sb = store_iter & 1;
+                    ++store_iter;
+                    // The staging buffer is free once the TMA store issued two stores ago has read it
+                    if (epi_tid == 0) tma_store_wait_read<kNumStoreStages - 1>();
+                    named_barrier_sync(1, kNumEpilogueThreads);
+                    const uint32_t stage_addr = smem_base + kSmemD + sb * kStoreStageBytes;
+                    const uint32_t row_off = row_in_tile * kStoreRowBytes;
+                    constexpr uint32_t kSwizzleMask = kStoreRowBytes == 128 ? 7 : (kStoreRowBytes == 64 ? 3 : 1);
+                    if constexpr (!kDIsFP32) {
+                        #pragma unroll
+                        for (uint32_t c = 0; c < kStoreRowBytes / 16; ++c) {        // 16-byte chunk = 8 bf16
+                            const uint32_t l = c / 2, i0 = (c % 2) * 8;
+                            const uint32_t off = row_off + c * 16;
+                            const uint32_t phys = off ^ (((off >> 7) & kSwizzleMask) << 4);
+                            st_shared_v4(stage_addr + phys,
+                                         pack_bf16x2(__uint_as_float(v[l][i0 + 0]), __uint_as_float(v[l][i0 + 1])),
+                                         pack_bf16x2(__uint_as_float(v[l][i0 + 2]), __uint_as_float(v[l][i0 + 3])),
+                                         pack_bf16x2(__uint_as_float(v[l][i0 + 4]), __uint_as_float(v[l][i0 + 5])),
+                                         pack_bf16x2(__uint_as_float(v[l][i0 + 6]), __uint_as_float(v[l][i0 + 7])));
+                        }
+                    } else {
+                        #pragma unroll
+                        for (uint32_t c = 0; c < kStoreRowBytes / 16; ++c) {        // 16-byte chunk = 4 fp32
+                            const uint32_t l = c / 4, i0 = (c % 4) * 4;
+                            const uint32_t off = row_off + c * 16;
+                            const uint32_t phys = off ^ (((off >> 7) & kSwizzleMask) << 4);
+                            st_shared_v4(stage_addr + phys, v[l][i0], v[l][i0 + 1], v[l][i0 + 2], v[l][i0 + 3]);
+                        }
+                    }
+                    fence_proxy_async_smem();
+                    named_barrier_sync(1, kNumEpilogueThreads);
+                    if (epi_tid == 0) {
+                        if constexpr (kAccumulate)
+                            tma_reduce_add_2d(&tm_d, stage_addr, static_cast<int32_t>(n0 + s * kStoreCols), static_cast<int32_t>(d_row0));
+                        else
+                            tma_store_2d(&tm_d, stage_addr, static_cast<int32_t>(n0 + s * kStoreCols), static_cast<int32_t>(d_row0));
+                        tma_store_commit();
+                    }
+                } else {
+                    // Ragged tile of the masked layout: rows at or beyond the group's row count stay untouched
+                    if (row_in_tile < tile.valid_rows) {
+                        const uint32_t col0 = n0 + s * kStoreCols;
+                        if constexpr (!kDIsFP32) {
+                            __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.d) +
+                                                  static_cast<size_t>(d_row0 + row_in_tile) * p.ldd;
+                            #pragma unroll
+                            for (uint32_t c = 0; c < kStoreCols / 8; ++c) {
+                                const uint32_t l = c / 2, i0 = (c % 2) * 8, col = col0 + c * 8;
+                                if (col + 8 <= p.shape_n) {
+                                    uint4 q;
+                                    q.x = pack_bf16x2(__uint_as_float(v[l][i0 + 0]), __uint_as_float(v[l][i0 + 1]));
+                                    q.y = pack_bf16x2(__uint_as_float(v[l][i0 + 2]), __uint_as_float(v[l][i0 + 3]));
+                                    q.z = pack_bf16x2(__uint_as_float(v[l][i0 + 4]), __uint_as_float(v[l][i0 + 5]));
+                                    q.w = pack_bf16x2(__uint_as_float(v[l][i0 + 6]), __uint_as_float(v[l][i0 + 7]));
+                                    *reinterpret_cast<uint4*>(drow + col) = q;
+                                } else {
+                                    for (uint32_t e = 0; e < 8 && col + e < p.shape_n; ++e)
+                                        drow[col + e] = __float2bfloat16_rn(__uint_as_float(v[l][i0 + e]));
+                                }
+                            }
+                        } else {
+                            float* drow = reinterpret_cast<float*>(p.d) + static_cast<size_t>(d_row0 + row_in_tile) * p.ldd;
+                            #pragma unroll
+                            for (uint32_t c = 0; c < kStoreCols; ++c)
+                                if (col0 + c < p.shape_n) drow[col0 + c] = __uint_as_float(v[c / 16][c % 16]);
+                        }
+                    }
+                }
+            }
+        }
+        // Every byte of D must be in global memory before the grid completes
+        if (epi_tid == 0) tma_store_wait<0>();
+    }
+
+    // ---- tear-down ------------------------------------------------------------------------------
+    __syncthreads();
+    if (*abort_flag != 0) {
+        // A wait ran out somewhere in this CTA: give copies that are still in flight time to land
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 200000) { }
+        __syncthreads();
+    }
+    if (warp_idx == 2) {
+        tc_fence_after_sync();
+        tmem_dealloc<1>(tmem_base, kTmemCols);
+    }
+}

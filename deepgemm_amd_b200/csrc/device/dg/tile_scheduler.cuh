@@ -1,0 +1,105 @@
+// Persistent tile scheduler shared by every warp role of the GEMM kernel and by the host-side
+// model that the CPU tests walk.  CTA c processes tiles c, c + num_ctas, c + 2 num_ctas, ...
+// of one global tile order:
+//
+//   dense / m-grouped contiguous : the (m_blocks x n_blocks) grid, rasterised in bands of
+//       `raster_group` row blocks (n outer, m inner inside a band) so that the tiles a wave runs
+//       together share A rows and B rows in L2.  For the contiguous layout the expert of a row
+//       block is grouped_layout[first row of the block] (-1, a padding row, maps to expert 0 as in
+//       deep_gemm/include/deep_gemm/scheduler/gemm.cuh:151-153).
+//   m-grouped masked : groups in order; group g contributes ceil(masked_m[g] / 128) row blocks,
+//       read on the device (no host synchronisation, so a captured graph follows new counts);
+//       same contract as scheduler/gemm.cuh:188-204.
+#pragma once
+
+#include <cstdint>
+
+#if defined(__CUDACC__)
+#define DG_HD __host__ __device__ __forceinline__
+#else
+#define DG_HD inline
+#endif
+
+namespace dg {
+
+enum GemmKind : uint32_t { kDense = 0, kMGroupedContiguous = 1, kMGroupedMasked = 2 };
+
+struct Tile {
+    uint32_t m_block;       // row block inside the group (masked) or inside A (dense / contiguous)
+    uint32_t n_block;
+    uint32_t group;         // which B[g] / SFB[g] this tile multiplies with
+    uint32_t a_row_base;    // first row of the group in the 2-D view of A
+    uint32_t d_row_base;    // first row of the group in the 2-D view of D
+    uint32_t sfa_mn_base;   // first row of the group along the MN axis of SFA
+    uint32_t sfa_group;     // group index along the packed-K axis of SFA
+    uint32_t valid_rows;    // rows of this tile that may be written (128 unless a ragged masked tile)
+};
+
+// Tile sizes are constructor arguments (literal constants in the kernel, which the compiler folds;
+// run-time values in the host model).
+template <uint32_t kKind>
+struct TileScheduler {
+    uint32_t kBlockM, kRasterGroup;
+    uint32_t shape_m, num_groups;
+    uint32_t num_m_blocks, num_n_blocks;
+    const int* layout;
+    uint32_t cta, num_ctas, iter;
+    // masked layout only
+    uint32_t cur_group, group_first_tile;
+
+    DG_HD TileScheduler(uint32_t block_m_, uint32_t block_n_, uint32_t raster_group_,
+                        uint32_t shape_m_, uint32_t shape_n_, uint32_t num_groups_, const int* layout_,
+                        uint32_t cta_, uint32_t num_ctas_)
+        : kBlockM(block_m_), kRasterGroup(raster_group_), shape_m(shape_m_), num_groups(num_groups_),
+          num_m_blocks((shape_m_ + block_m_ - 1) / block_m_), num_n_blocks((shape_n_ + block_n_ - 1) / block_n_),
+          layout(layout_), cta(cta_), num_ctas(num_ctas_), iter(0), cur_group(0), group_first_tile(0) {}
+
+    // Linear index inside an (mb x num_n_blocks) grid -> (m, n)
+    DG_HD void rasterise(uint32_t idx, uint32_t mb, uint32_t& m, uint32_t& n) const {
+        const uint32_t per_band = kRasterGroup * num_n_blocks;
+        const uint32_t band = idx / per_band;
+        const uint32_t first_m = band * kRasterGroup;
+        const uint32_t rem = idx - band * per_band;
+        const uint32_t rows = mb - first_m < kRasterGroup ? mb - first_m : kRasterGroup;
+        m = first_m + rem % rows;
+        n = rem / rows;
+    }
+
+    DG_HD bool next(Tile& t) {
+        const uint32_t tile_id = iter * num_ctas + cta;
+        ++iter;
+        if constexpr (kKind == kMGroupedMasked) {
+            uint32_t mb = 0, rows = 0;
+            while (true) {
+                if (cur_group >= num_groups) return false;
+                const int r = layout[cur_group];
+                rows = r < 0 ? 0u : (static_cast<uint32_t>(r) > shape_m ? shape_m : static_cast<uint32_t>(r));
+                mb = (rows + kBlockM - 1) / kBlockM;
+                if (tile_id < group_first_tile + mb * num_n_blocks) break;
+                group_first_tile += mb * num_n_blocks;
+                ++cur_group;
+            }
+            rasterise(tile_id - group_first_tile, mb, t.m_block, t.n_block);
+            t.group = cur_group;
+            t.a_row_base = t.d_row_base = cur_group * shape_m;
+            t.sfa_mn_base = 0;
+            t.sfa_group = cur_group;
+            const uint32_t left = rows - t.m_block * kBlockM;
+            t.valid_rows = left < kBlockM ? left : kBlockM;
+            return true;
+        } else {
+            if (tile_id >= num_m_blocks * num_n_blocks) return false;
+            rasterise(tile_id, num_m_blocks, t.m_block, t.n_block);
+            t.group = 0;
+            if constexpr (kKind == kMGroupedContiguous) {
+                const int g = layout[t.m_block * kBlockM];
+                t.group = g < 0 ? 0u : static_cast<uint32_t>(g);
+            }
+            t.a_row_base = t.d_row_base = t.sfa_mn_base = t.sfa_group = 0;
+            t.valid_rows = kBlockM;
+            return true;
+        }
+    }
+};
+
+}  // namespace dg

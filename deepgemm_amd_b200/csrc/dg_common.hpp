@@ -1,0 +1,92 @@
+// Shared host-side helpers: error reporting, lazily loaded CUDA driver entry points, process state.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstdlib>
+#include <mutex>
+#include <string>
+
+#include "../../include/deepgemm_b200.h"
+
+namespace dg {
+
+// ---- errors -------------------------------------------------------------------------------------
+std::string& last_error();
+int fail(int code, const char* fmt, ...) __attribute__((format(printf, 2, 3)));
+
+// The reference reports a failed check as "Assertion error (file:line): cond"
+// (csrc/utils/exception.hpp:13-41); the same text is kept so callers can match on it.
+#define DG_REQUIRE(cond)                                                                              \
+    do {                                                                                              \
+        if (!(cond))                                                                                  \
+            return ::dg::fail(DG_ERR_INVALID_ARGUMENT, "Assertion error (%s:%d): %s", __FILE__, __LINE__, #cond); \
+    } while (0)
+
+#define DG_CUDA_RT(call)                                                                              \
+    do {                                                                                              \
+        cudaError_t e_ = (call);                                                                      \
+        if (e_ != cudaSuccess)                                                                        \
+            return ::dg::fail(DG_ERR_CUDA, "CUDA runtime error (%s:%d): %s: %s", __FILE__, __LINE__, #call, cudaGetErrorString(e_)); \
+    } while (0)
+
+// ---- CUDA driver, loaded on first use so that the library loads on machines without a GPU ---------
+struct Driver {
+    CUresult (*cuInit)(unsigned int) = nullptr;
+    CUresult (*cuGetErrorString)(CUresult, const char**) = nullptr;
+    CUresult (*cuCtxGetCurrent)(CUcontext*) = nullptr;
+    CUresult (*cuModuleLoadData)(CUmodule*, const void*) = nullptr;
+    CUresult (*cuModuleGetFunction)(CUfunction*, CUmodule, const char*) = nullptr;
+    CUresult (*cuFuncSetAttribute)(CUfunction, CUfunction_attribute, int) = nullptr;
+    CUresult (*cuLaunchKernelEx)(const CUlaunchConfig*, CUfunction, void**, void**) = nullptr;
+    CUresult (*cuTensorMapEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                       const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                       CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill) = nullptr;
+    bool ok = false;
+    std::string why;
+};
+const Driver& driver();
+std::string cu_error(CUresult r);
+
+#define DG_CUDA_DRV(call)                                                                             \
+    do {                                                                                              \
+        CUresult r_ = (call);                                                                         \
+        if (r_ != CUDA_SUCCESS)                                                                       \
+            return ::dg::fail(DG_ERR_CUDA, "CUDA driver error (%s:%d): %s: %s", __FILE__, __LINE__, #call, ::dg::cu_error(r_).c_str()); \
+    } while (0)
+
+// ---- process-wide state (csrc/runtime/runtime.hpp:20-104, heuristics/runtime.hpp:10-67) ------------
+struct State {
+    std::mutex mu;
+    std::string library_root;
+    int num_sms_override = 0;
+    int tc_util = 100;
+    int pdl = 0;
+    int mk_alignment = 128;
+    int* status_host = nullptr;      // pinned, mapped: kernels write failure codes here
+    int* status_device = nullptr;
+};
+State& state();
+int device_num_sms();                // SM count of the current device, 0 if there is none
+int ensure_status_word();            // allocates the host-mapped status word on first GPU use
+
+inline int env_int(const char* name, int dflt = 0) {
+    // DG_ prefix first, then DJ_ as the reference's runtime does (README.md:166)
+    const char* v = std::getenv((std::string("DG_") + name).c_str());
+    if (v == nullptr) v = std::getenv((std::string("DJ_") + name).c_str());
+    return v ? std::atoi(v) : dflt;
+}
+inline std::string env_str(const char* name) {
+    const char* v = std::getenv((std::string("DG_") + name).c_str());
+    if (v == nullptr) v = std::getenv((std::string("DJ_") + name).c_str());
+    return v ? std::string(v) : std::string();
+}
+
+template <typename T> static inline T ceil_div(T a, T b) { return (a + b - 1) / b; }
+template <typename T> static inline T align_up(T a, T b) { return ceil_div(a, b) * b; }
+
+}  // namespace dg

@@ -1,0 +1,319 @@
+// GEMM entry points: argument checks of the reference's API layer (csrc/apis/gemm.hpp:78-318,
+// csrc/utils/layout.hpp:101-140), tile-shape heuristics for B200, tensor maps, kernel source
+// generation and launch (the work of csrc/jit_kernels/impls/sm100_fp8_fp4_gemm_1d1d.hpp:101-323 and
+// csrc/jit_kernels/impls/runtime_utils.hpp:119-159,325-408 in the reference).
+#include "dg_common.hpp"
+
+#include <algorithm>
+#include <cstring>
+#include <sstream>
+
+#include "device/dg/gemm_config.hpp"
+#include "device/dg/tile_scheduler.cuh"
+
+namespace dg {
+namespace {
+
+// Mirror of dg::GemmParams in device/dg/gemm_fp8_fp4.cuh (kernel argument, passed by value)
+struct GemmParams {
+    const int* grouped_layout;
+    void* d;
+    int* status;
+    uint32_t shape_m, shape_n, shape_k, num_groups, ldd;
+    float alpha;
+};
+
+struct Problem {
+    int kind;
+    int m, n, k, groups;
+    bool a_fp4, b_fp4, d_fp32, accumulate;
+    int gran_k_a, gran_k_b;
+    int expected_m;
+};
+
+int validate(int kind, const dg_gemm_args_t* a, bool need_pointers, Problem* p) {
+    DG_REQUIRE(a != nullptr);
+    DG_REQUIRE(kind == DG_GEMM_DENSE || kind == DG_GEMM_M_GROUPED_CONTIGUOUS || kind == DG_GEMM_M_GROUPED_MASKED);
+    DG_REQUIRE(a->a_dtype == DG_FP8_E4M3 || a->a_dtype == DG_FP4_E2M1_X2);
+    DG_REQUIRE(a->b_dtype == DG_FP8_E4M3 || a->b_dtype == DG_FP4_E2M1_X2);
+    DG_REQUIRE(a->d_dtype == DG_BF16 || a->d_dtype == DG_FP32);
+    if (kind != DG_GEMM_DENSE) DG_REQUIRE(a->d_dtype == DG_BF16);            // gemm.hpp:209,299
+    DG_REQUIRE(a->m >= 0 && a->n >= 0 && a->k >= 0);
+    DG_REQUIRE(a->gran_k_a == 32 || a->gran_k_a == 128);
+    DG_REQUIRE(a->gran_k_b == 32 || a->gran_k_b == 128);
+    if (kind == DG_GEMM_DENSE) {
+        DG_REQUIRE(a->num_groups == 1);
+    } else {
+        DG_REQUIRE(a->n > 0 && a->k > 0 && a->num_groups > 0);                // gemm.hpp:208,296
+        DG_REQUIRE(a->major_a == DG_MAJOR_K);                                 // gemm.hpp:197,285
+        DG_REQUIRE(!a->accumulate);
+    }
+    if (kind == DG_GEMM_M_GROUPED_MASKED) {
+        DG_REQUIRE(a->major_b == DG_MAJOR_K);                                 // gemm.hpp:285
+        DG_REQUIRE(a->expected_m > 0 && a->m > 0);                            // gemm.hpp:296
+    }
+    // FP4 x FP4 needs the MXF4 MMA kind (K-major only, csrc/utils/layout.hpp:42-45)
+    if (a->a_dtype == DG_FP4_E2M1_X2 && a->b_dtype == DG_FP4_E2M1_X2)
+        return fail(DG_ERR_UNSUPPORTED, "FP4 x FP4 (kind::mxf4) is not built; FP8 x FP8 and FP8 x FP4 are");
+    if (a->a_dtype == DG_FP4_E2M1_X2)
+        return fail(DG_ERR_UNSUPPORTED, "FP4 A with FP8 B is not built; use FP8 A with FP4 B");
+    if (a->major_a != DG_MAJOR_K || a->major_b != DG_MAJOR_K)
+        return fail(DG_ERR_UNSUPPORTED, "MN-major operands (nn / tn / tt) are not built yet; pass K-major A and B");
+    p->kind = kind;
+    p->m = a->m; p->n = a->n; p->k = a->k; p->groups = a->num_groups;
+    p->a_fp4 = a->a_dtype == DG_FP4_E2M1_X2;
+    p->b_fp4 = a->b_dtype == DG_FP4_E2M1_X2;
+    p->d_fp32 = a->d_dtype == DG_FP32;
+    p->accumulate = a->accumulate != 0;
+    p->gran_k_a = a->gran_k_a; p->gran_k_b = a->gran_k_b;
+    p->expected_m = a->expected_m;
+    if (a->m == 0 || a->n == 0 || a->k == 0) return DG_OK;                    // handled by the caller (gemm.hpp:17-53)
+
+    if (p->a_fp4 || p->b_fp4) DG_REQUIRE(a->k % 128 == 0);                   // runtime_utils.hpp:133-135
+    if (need_pointers) {
+        DG_REQUIRE(a->a != nullptr && a->b != nullptr && a->sfa != nullptr && a->sfb != nullptr && a->d != nullptr);
+        const auto aligned = [](const void* ptr, uintptr_t al) { return reinterpret_cast<uintptr_t>(ptr) % al == 0; };
+        DG_REQUIRE(aligned(a->a, p->a_fp4 ? 32 : 16));                        // runtime_utils.hpp:126
+        DG_REQUIRE(aligned(a->b, p->b_fp4 ? 32 : 16));
+        DG_REQUIRE(aligned(a->sfa, 16) && aligned(a->sfb, 16) && aligned(a->d, 16));
+        if (kind != DG_GEMM_DENSE) DG_REQUIRE(a->grouped_layout != nullptr);
+    }
+    const int64_t k_bytes_a = p->a_fp4 ? a->k / 2 : a->k, k_bytes_b = p->b_fp4 ? a->k / 2 : a->k;
+    DG_REQUIRE(a->lda >= k_bytes_a && a->lda % (p->a_fp4 ? 32 : 16) == 0);   // TMA: strides are multiples of 16 bytes
+    DG_REQUIRE(a->ldb >= k_bytes_b && a->ldb % (p->b_fp4 ? 32 : 16) == 0);
+    const int d_elem = p->d_fp32 ? 4 : 2;
+    DG_REQUIRE(a->ldd >= a->n && (a->ldd * d_elem) % 16 == 0);
+    // Packed scale tensors: csrc/utils/layout.hpp:121-130
+    DG_REQUIRE(a->sfa_pitch >= align_up<int64_t>(a->m, 4) && a->sfa_pitch % 4 == 0);
+    DG_REQUIRE(a->sfb_pitch >= align_up<int64_t>(a->n, 4) && a->sfb_pitch % 4 == 0);
+    if (kind == DG_GEMM_M_GROUPED_CONTIGUOUS) {
+        // Every expert segment is padded to the alignment, which the row blocks must divide
+        DG_REQUIRE(state().mk_alignment % 128 == 0);
+        DG_REQUIRE(a->m % 128 == 0);
+    }
+    return DG_OK;
+}
+
+// ---- heuristics ------------------------------------------------------------------------------------
+// Tiles are 128 x block_n x 128 per CTA with block_n in 16..240.  The choice minimises a cycle model of
+// the whole launch:  waves x (k_blocks x max(MMA, shared-memory feed, L2 feed) + per-tile epilogue).
+// Constants are per-SM, per-clock figures of B200: 8192 FP8 MACs, 128 B of shared memory, and a
+// measured ~64 B from L2.
+int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
+    const int num_sms = dg_get_num_sms();
+    const int d_elem = p.d_fp32 ? 4 : 2;
+    const int64_t k_blocks = ceil_div(p.k, 128);
+    int64_t m_blocks;
+    if (p.kind == DG_GEMM_M_GROUPED_MASKED)
+        m_blocks = static_cast<int64_t>(p.groups) * ceil_div(std::min(std::max(p.expected_m, 1), p.m), 128);
+    else
+        m_blocks = ceil_div(p.m, 128);
+
+    double best_cost = 0;
+    int best_bn = 0;
+    const int forced_bn = env_int("FORCE_BLOCK_N");
+    for (int bn = 16; bn <= 240; bn += 16) {
+        if (forced_bn && bn != forced_bn) continue;
+        const int64_t tiles = m_blocks * ceil_div(p.n, bn);
+        const int64_t waves = ceil_div<int64_t>(tiles, num_sms);
+        const double mma = 2.0 * bn;
+        const double smem_feed = 128.0 + bn;
+        const double l2_feed = (16384.0 + 128.0 * bn) / 64.0;
+        const GemmLayout lay{128, static_cast<uint32_t>(bn), 128, 2, static_cast<uint32_t>(d_elem)};
+        const double epilogue = 300.0 + 40.0 * lay.num_stores() + bn * 2.0;
+        // The epilogue of a tile overlaps the next tile's main loop; it is exposed once per CTA
+        const double per_tile = static_cast<double>(k_blocks) * std::max(mma, std::max(smem_feed, l2_feed));
+        const double cost = static_cast<double>(waves) * std::max(per_tile, epilogue) + epilogue + 2000.0;
+        if (best_bn == 0 || cost < best_cost - 1e-9 || (std::abs(cost - best_cost) <= 1e-9 && bn > best_bn)) {
+            best_cost = cost;
+            best_bn = bn;
+        }
+    }
+    if (best_bn == 0) return fail(DG_ERR_INVALID_ARGUMENT, "DG_FORCE_BLOCK_N must be a multiple of 16 in [16, 240]");
+
+    GemmLayout lay{128, static_cast<uint32_t>(best_bn), 128, 2, static_cast<uint32_t>(d_elem)};
+    int stages = 2;
+    while (stages < 32) {
+        GemmLayout next = lay;
+        next.num_stages = stages + 1;
+        if (next.total_bytes() > kSmemCapacity) break;
+        ++stages;
+    }
+    const int forced_stages = env_int("FORCE_NUM_STAGES");
+    if (forced_stages >= 2 && forced_stages <= stages) stages = forced_stages;
+    // No point in more stages than K-blocks of two tiles
+    stages = static_cast<int>(std::max<int64_t>(2, std::min<int64_t>(stages, 2 * k_blocks)));
+    lay.num_stages = stages;
+
+    const int64_t tiles = m_blocks * ceil_div(p.n, best_bn);
+    cfg->block_m = 128;
+    cfg->block_n = best_bn;
+    cfg->block_k = 128;
+    cfg->num_stages = stages;
+    cfg->cluster_size = 1;
+    const int forced_raster = env_int("FORCE_RASTER_GROUP");
+    cfg->raster_group = forced_raster > 0 ? forced_raster : 16;
+    cfg->num_ctas = p.kind == DG_GEMM_M_GROUPED_MASKED ? num_sms
+                                                        : static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(num_sms, tiles)));
+    cfg->smem_bytes = static_cast<int>(lay.total_bytes());
+    cfg->tmem_cols = static_cast<int>(lay.tmem_cols_alloc());
+    cfg->num_tiles = static_cast<int>(tiles);
+    cfg->waves_x100 = static_cast<int>(tiles * 100 / num_sms);
+    return DG_OK;
+}
+
+std::string generate_source(const Problem& p, const dg_gemm_config_t& cfg) {
+    std::ostringstream s;
+    s << "// generated: block-scaled GEMM instantiation\n"
+      << "#define DG_GEMM_TYPE " << p.kind << "\n"
+      << "#define DG_BLOCK_N " << cfg.block_n << "\n"
+      << "#define DG_NUM_STAGES " << cfg.num_stages << "\n"
+      << "#define DG_A_FP4 " << (p.a_fp4 ? 1 : 0) << "\n"
+      << "#define DG_B_FP4 " << (p.b_fp4 ? 1 : 0) << "\n"
+      << "#define DG_GRAN_K_A " << p.gran_k_a << "\n"
+      << "#define DG_GRAN_K_B " << p.gran_k_b << "\n"
+      << "#define DG_D_FP32 " << (p.d_fp32 ? 1 : 0) << "\n"
+      << "#define DG_ACCUMULATE " << (p.accumulate ? 1 : 0) << "\n"
+      << "#define DG_RASTER_GROUP " << cfg.raster_group << "\n"
+      << "#include <dg/gemm_fp8_fp4.cuh>\n";
+    return s.str();
+}
+
+int encode_2d(CUtensorMap* map, CUtensorMapDataType dtype, const void* base, uint64_t inner, uint64_t outer,
+              uint64_t outer_stride_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swizzle) {
+    const Driver& drv = driver();
+    if (!drv.ok) return fail(DG_ERR_CUDA, "CUDA driver unavailable: %s", drv.why.c_str());
+    const cuuint64_t dims[2] = {inner, outer};
+    const cuuint64_t strides[1] = {outer_stride_bytes};
+    const cuuint32_t box[2] = {box_inner, box_outer};
+    const cuuint32_t elem_strides[2] = {1, 1};
+    if (env_int("PRINT_CONFIGS"))
+        fprintf(stderr, "[dg] tensor map: dtype %d dims (%llu, %llu) stride %llu B box (%u, %u) swizzle %d base %p\n",
+                static_cast<int>(dtype), static_cast<unsigned long long>(inner), static_cast<unsigned long long>(outer),
+                static_cast<unsigned long long>(outer_stride_bytes), box_inner, box_outer, static_cast<int>(swizzle), base);
+    const CUresult r = drv.cuTensorMapEncodeTiled(map, dtype, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
+                                                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(DG_ERR_CUDA, "cuTensorMapEncodeTiled failed: %s (dims %llu x %llu, stride %llu, box %u x %u)", cu_error(r).c_str(),
+                    static_cast<unsigned long long>(inner), static_cast<unsigned long long>(outer),
+                    static_cast<unsigned long long>(outer_stride_bytes), box_inner, box_outer);
+    return DG_OK;
+}
+
+int get_kernel(const Problem& p, const dg_gemm_config_t& cfg, dg_kernel_t* kernel) {
+    static const char* names[3] = {"gemm_fp8_fp4_dense", "gemm_fp8_fp4_m_grouped_contiguous", "gemm_fp8_fp4_m_grouped_masked"};
+    const std::string src = generate_source(p, cfg);
+    return dg_jit_compile(names[p.kind], "dg_gemm_fp8_fp4", src.c_str(), "", kernel);
+}
+
+int run_gemm(int kind, const dg_gemm_args_t* a) {
+    Problem p;
+    int rc = validate(kind, a, true, &p);
+    if (rc != DG_OK) return rc;
+    if (p.m == 0 || p.n == 0) return DG_OK;
+    if (p.k == 0) return fail(DG_ERR_INVALID_ARGUMENT, "k == 0 must be handled by the caller (zero or copy D)");
+
+    dg_gemm_config_t cfg;
+    if ((rc = choose_config(p, &cfg)) != DG_OK) return rc;
+    if (env_int("PRINT_CONFIGS"))
+        fprintf(stderr, "[dg] kind %d m %d n %d k %d groups %d -> block_n %d stages %d ctas %d smem %d tiles %d\n", kind, p.m, p.n, p.k,
+                p.groups, cfg.block_n, cfg.num_stages, cfg.num_ctas, cfg.smem_bytes, cfg.num_tiles);
+    dg_kernel_t kernel = nullptr;
+    if ((rc = get_kernel(p, cfg, &kernel)) != DG_OK) return rc;
+    if ((rc = ensure_status_word()) != DG_OK) return rc;
+
+    const GemmLayout lay{128, static_cast<uint32_t>(cfg.block_n), 128, static_cast<uint32_t>(cfg.num_stages),
+                         static_cast<uint32_t>(p.d_fp32 ? 4 : 2)};
+    const uint64_t a_rows = kind == DG_GEMM_M_GROUPED_MASKED ? static_cast<uint64_t>(p.groups) * p.m : p.m;
+    const uint64_t b_rows = static_cast<uint64_t>(p.groups) * p.n;
+    const uint64_t sfa_k = ceil_div(p.k, p.gran_k_a * 4), sfb_k = ceil_div(p.k, p.gran_k_b * 4);
+    const uint64_t sfa_rows = kind == DG_GEMM_M_GROUPED_MASKED ? sfa_k * p.groups : sfa_k;
+    const uint64_t sfb_rows = sfb_k * p.groups;
+
+    CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb, tm_d;
+    // A, B: K (elements) x rows; box = one 128-element K-block x the tile's rows; 128-byte swizzle
+    if ((rc = encode_2d(&tm_a, p.a_fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, a->a,
+                        p.k, a_rows, a->lda, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B)) != DG_OK) return rc;
+    if ((rc = encode_2d(&tm_b, p.b_fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, a->b,
+                        p.k, b_rows, a->ldb, 128, cfg.block_n, CU_TENSOR_MAP_SWIZZLE_128B)) != DG_OK) return rc;
+    // Scales: MN (int32) x packed-K rows; the MN extent is the true row count, so reads past it are zero-filled
+    if ((rc = encode_2d(&tm_sfa, CU_TENSOR_MAP_DATA_TYPE_INT32, a->sfa, p.m, sfa_rows, a->sfa_pitch * 4, 128, 1,
+                        CU_TENSOR_MAP_SWIZZLE_NONE)) != DG_OK) return rc;
+    if ((rc = encode_2d(&tm_sfb, CU_TENSOR_MAP_DATA_TYPE_INT32, a->sfb, p.n, sfb_rows, a->sfb_pitch * 4, lay.sf_block_n(), 1,
+                        CU_TENSOR_MAP_SWIZZLE_NONE)) != DG_OK) return rc;
+    const CUtensorMapSwizzle d_swizzle = lay.store_row_bytes() == 128 ? CU_TENSOR_MAP_SWIZZLE_128B :
+                                         lay.store_row_bytes() == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
+    if ((rc = encode_2d(&tm_d, p.d_fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, a->d,
+                        p.n, a_rows, a->ldd * (p.d_fp32 ? 4 : 2), lay.store_cols(), 128, d_swizzle)) != DG_OK) return rc;
+
+    GemmParams params;
+    params.grouped_layout = a->grouped_layout;
+    params.d = a->d;
+    params.status = state().status_device;
+    params.shape_m = p.m; params.shape_n = p.n; params.shape_k = p.k;
+    params.num_groups = p.groups;
+    params.ldd = static_cast<uint32_t>(a->ldd);
+    params.alpha = a->has_alpha ? a->alpha : 1.0f;
+    void* kargs[6] = {&tm_a, &tm_b, &tm_sfa, &tm_sfb, &tm_d, &params};
+    return dg_jit_launch(kernel, cfg.num_ctas, 256, cfg.cluster_size, cfg.smem_bytes, state().pdl, a->stream, kargs);
+}
+
+}  // namespace
+}  // namespace dg
+
+using namespace dg;
+
+extern "C" {
+
+int dg_fp8_fp4_gemm(const dg_gemm_args_t* args) { return run_gemm(DG_GEMM_DENSE, args); }
+int dg_m_grouped_fp8_fp4_gemm_contiguous(const dg_gemm_args_t* args) { return run_gemm(DG_GEMM_M_GROUPED_CONTIGUOUS, args); }
+int dg_m_grouped_fp8_fp4_gemm_masked(const dg_gemm_args_t* args) { return run_gemm(DG_GEMM_M_GROUPED_MASKED, args); }
+
+int dg_get_gemm_config(int kind, const dg_gemm_args_t* args, dg_gemm_config_t* config) {
+    DG_REQUIRE(config != nullptr);
+    Problem p;
+    const int rc = validate(kind, args, false, &p);
+    if (rc != DG_OK) return rc;
+    DG_REQUIRE(p.m > 0 && p.n > 0 && p.k > 0);
+    return choose_config(p, config);
+}
+
+int dg_gemm_precompile(int kind, const dg_gemm_args_t* args) {
+    Problem p;
+    int rc = validate(kind, args, false, &p);
+    if (rc != DG_OK) return rc;
+    DG_REQUIRE(p.m > 0 && p.n > 0 && p.k > 0);
+    dg_gemm_config_t cfg;
+    if ((rc = choose_config(p, &cfg)) != DG_OK) return rc;
+    dg_kernel_t kernel = nullptr;
+    return get_kernel(p, cfg, &kernel);
+}
+
+int dg_enumerate_tiles(int kind, int block_n, int raster_group, int shape_m, int shape_n, int num_groups,
+                       const int32_t* layout_host, int cta, int num_ctas, uint32_t* out, int max_tiles) {
+    if (!(block_n > 0 && raster_group > 0 && num_ctas > 0 && cta >= 0 && cta < num_ctas && shape_m >= 0 && shape_n >= 0)) {
+        fail(DG_ERR_INVALID_ARGUMENT, "Assertion error (%s:%d): bad scheduler arguments", __FILE__, __LINE__);
+        return -DG_ERR_INVALID_ARGUMENT;
+    }
+    int count = 0;
+    Tile t;
+    auto emit = [&]() {
+        if (count < max_tiles && out != nullptr) {
+            out[4 * count + 0] = t.m_block; out[4 * count + 1] = t.n_block;
+            out[4 * count + 2] = t.group;   out[4 * count + 3] = t.valid_rows;
+        }
+        ++count;
+    };
+    auto walk = [&](auto sched) { while (sched.next(t)) emit(); };
+    const uint32_t bn = block_n, rg = raster_group, sm = shape_m, sn = shape_n, ng = num_groups, c = cta, nc = num_ctas;
+    switch (kind) {
+        case DG_GEMM_DENSE: walk(TileScheduler<kDense>(128, bn, rg, sm, sn, ng, layout_host, c, nc)); break;
+        case DG_GEMM_M_GROUPED_CONTIGUOUS: walk(TileScheduler<kMGroupedContiguous>(128, bn, rg, sm, sn, ng, layout_host, c, nc)); break;
+        case DG_GEMM_M_GROUPED_MASKED: walk(TileScheduler<kMGroupedMasked>(128, bn, rg, sm, sn, ng, layout_host, c, nc)); break;
+        default: fail(DG_ERR_INVALID_ARGUMENT, "unknown GEMM kind"); return -DG_ERR_INVALID_ARGUMENT;
+    }
+    return count;
+}
+
+}  // extern "C"

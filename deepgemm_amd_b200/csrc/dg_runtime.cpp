@@ -1,0 +1,143 @@
+// Process state, error strings, lazily loaded driver entry points and the settings API
+// (counterpart of csrc/apis/config.hpp:9-47 and csrc/runtime/runtime.hpp:20-104 of the reference).
+#include "dg_common.hpp"
+
+#include <dlfcn.h>
+
+namespace dg {
+
+std::string& last_error() {
+    static thread_local std::string e;
+    return e;
+}
+
+int fail(int code, const char* fmt, ...) {
+    char buf[4096];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    last_error() = buf;
+    return code;
+}
+
+State& state() {
+    static State s;
+    return s;
+}
+
+const Driver& driver() {
+    static Driver d;
+    static std::once_flag once;
+    std::call_once(once, []() {
+        void* h = dlopen("libcuda.so.1", RTLD_NOW | RTLD_GLOBAL);
+        if (h == nullptr) h = dlopen("libcuda.so", RTLD_NOW | RTLD_GLOBAL);
+        if (h == nullptr) {
+            d.why = std::string("cannot load libcuda.so.1: ") + dlerror();
+            return;
+        }
+        auto sym = [&](const char* name, auto& fn) {
+            fn = reinterpret_cast<std::remove_reference_t<decltype(fn)>>(dlsym(h, name));
+            if (fn == nullptr && d.why.empty()) d.why = std::string("libcuda lacks ") + name;
+        };
+        sym("cuInit", d.cuInit);
+        sym("cuGetErrorString", d.cuGetErrorString);
+        sym("cuCtxGetCurrent", d.cuCtxGetCurrent);
+        sym("cuModuleLoadData", d.cuModuleLoadData);
+        sym("cuModuleGetFunction", d.cuModuleGetFunction);
+        sym("cuFuncSetAttribute", d.cuFuncSetAttribute);
+        sym("cuLaunchKernelEx", d.cuLaunchKernelEx);
+        sym("cuTensorMapEncodeTiled", d.cuTensorMapEncodeTiled);
+        d.ok = d.why.empty();
+    });
+    return d;
+}
+
+std::string cu_error(CUresult r) {
+    const char* s = nullptr;
+    if (driver().ok && driver().cuGetErrorString(r, &s) == CUDA_SUCCESS && s != nullptr) return s;
+    return "CUresult " + std::to_string(static_cast<int>(r));
+}
+
+int device_num_sms() {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return 0; }
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) { cudaGetLastError(); return 0; }
+    return n;
+}
+
+int ensure_status_word() {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mu);
+    if (s.status_host != nullptr) return DG_OK;
+    int* h = nullptr;
+    DG_CUDA_RT(cudaHostAlloc(reinterpret_cast<void**>(&h), 64, cudaHostAllocMapped | cudaHostAllocPortable));
+    *h = 0;
+    int* d = nullptr;
+    DG_CUDA_RT(cudaHostGetDevicePointer(reinterpret_cast<void**>(&d), h, 0));
+    s.status_host = h;
+    s.status_device = d;
+    return DG_OK;
+}
+
+}  // namespace dg
+
+using namespace dg;
+
+extern "C" {
+
+const char* dg_last_error(void) { return last_error().c_str(); }
+
+int dg_init(const char* library_root) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mu);
+    s.library_root = library_root ? library_root : "";
+    return DG_OK;
+}
+
+int dg_shutdown(void) { return DG_OK; }
+
+int dg_set_num_sms(int num_sms) {
+    DG_REQUIRE(num_sms > 0 && num_sms % 2 == 0);
+    const int dev = device_num_sms();
+    if (dev > 0) DG_REQUIRE(num_sms <= dev);
+    state().num_sms_override = num_sms;
+    return DG_OK;
+}
+
+int dg_get_num_sms(void) {
+    if (state().num_sms_override > 0) return state().num_sms_override;
+    const int dev = device_num_sms();
+    return dev > 0 ? dev : 148;
+}
+
+int dg_set_tc_util(int percent) {
+    DG_REQUIRE(percent > 0 && percent <= 100);
+    state().tc_util = percent;
+    return DG_OK;
+}
+int dg_get_tc_util(void) { return state().tc_util; }
+int dg_set_pdl(int enabled) { state().pdl = enabled != 0; return DG_OK; }
+int dg_get_pdl(void) { return state().pdl; }
+
+int dg_set_mk_alignment_for_contiguous_layout(int alignment) { state().mk_alignment = alignment; return DG_OK; }
+int dg_get_mk_alignment_for_contiguous_layout(void) { return state().mk_alignment; }
+int dg_get_theoretical_mk_alignment_for_contiguous_layout(int) { return 256; }
+
+int dg_get_tma_aligned_size(int x, int element_size) {
+    if (element_size <= 0 || 16 % element_size != 0) {
+        fail(DG_ERR_INVALID_ARGUMENT, "Assertion error (%s:%d): kNumTMAAlignmentBytes %% element_size == 0", __FILE__, __LINE__);
+        return -1;
+    }
+    return align_up(x, 16 / element_size);
+}
+
+int dg_kernel_status(void) {
+    return state().status_host ? *reinterpret_cast<volatile int*>(state().status_host) : 0;
+}
+int dg_reset_kernel_status(void) {
+    if (state().status_host) *reinterpret_cast<volatile int*>(state().status_host) = 0;
+    return DG_OK;
+}
+
+}  // extern "C"

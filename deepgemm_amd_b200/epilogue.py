@@ -1,0 +1,26 @@
+"""Epilogue selectors of the reference's `deep_gemm.epilogue` submodule
+(csrc/jit_kernels/impls/epilogue_class.hpp:19-127).  Identity and Alpha are built; the FP8-quantising and
+stochastic-rounding epilogues are declared so that callers get a clear error instead of an AttributeError."""
+from __future__ import annotations
+
+
+class Epilogue:
+    pass
+
+
+class Identity(Epilogue):
+    pass
+
+
+class Alpha(Epilogue):
+    def __init__(self, alpha: float):
+        self.alpha = float(alpha)
+
+
+class FP8Quantization(Epilogue):
+    def __init__(self, sfd):
+        self.sfd = sfd
+
+
+class BF16StochasticRounding(Epilogue):
+    pass

@@ -1,0 +1,51 @@
+"""Timing and comparison helpers with the method of the reference's deep_gemm/testing
+(bench.py:7-33: CUDA events around repeated calls with an L2 flush before each; numeric.py:5-21)."""
+from __future__ import annotations
+
+import torch
+
+
+def calc_diff(x: torch.Tensor, y: torch.Tensor) -> float:
+    """1 - 2<x,y> / (|x|^2 + |y|^2) in float64."""
+    x, y = x.double(), y.double()
+    denom = (x * x + y * y).sum()
+    if denom == 0:
+        return 0.0
+    return float(1 - 2 * (x * y).sum() / denom)
+
+
+def count_bytes(*tensors) -> int:
+    total = 0
+    for t in tensors:
+        if isinstance(t, (tuple, list)):
+            total += count_bytes(*t)
+        elif t is not None:
+            total += t.numel() * t.element_size()
+    return total
+
+
+def assert_bitwise_equal(x: torch.Tensor, y: torch.Tensor, label: str = "") -> None:
+    assert x.shape == y.shape and x.dtype == y.dtype, label
+    xb, yb = x.contiguous().view(torch.uint8), y.contiguous().view(torch.uint8)
+    if not torch.equal(xb, yb):
+        bad = (xb != yb).flatten().nonzero()
+        raise AssertionError(f"bitwise mismatch ({label}): {bad.numel()} bytes differ, first at byte {int(bad[0])}")
+
+
+def bench(fn, num_warmups: int = 5, num_tests: int = 20, flush_l2_bytes: int = 256 << 20) -> float:
+    """Mean device seconds of fn(), each call preceded by a write of `flush_l2_bytes` (larger than the
+    126 MB L2) that is excluded from the timing."""
+    flush = torch.empty(flush_l2_bytes // 4, dtype=torch.int, device="cuda") if flush_l2_bytes else None
+    for _ in range(num_warmups):
+        fn()
+    torch.cuda.synchronize()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(num_tests)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(num_tests)]
+    for i in range(num_tests):
+        if flush is not None:
+            flush.zero_()
+        starts[i].record()
+        fn()
+        ends[i].record()
+    torch.cuda.synchronize()
+    return sum(s.elapsed_time(e) for s, e in zip(starts, ends)) / num_tests / 1e3

@@ -1,0 +1,189 @@
+/*
+ * C ABI of the B200 (sm_100a) block-scaled FP8 / FP8xFP4 GEMM library.
+ *
+ * Plain pointers and sizes only.  Every pointer named "device" is a CUDA device pointer of the
+ * current device; `stream` is a cudaStream_t / CUstream passed as void*.  All functions return
+ * DG_OK (0) or a dg_status_t error code; dg_last_error() gives the message of the last failure on
+ * the calling thread.  Nothing here synchronises the host with the device unless it says so.
+ *
+ * Each entry point names the interface of the reference (DeepGEMM 2.8.1 tree, paths relative to
+ * its root) that it stands in for.
+ */
+#ifndef DEEPGEMM_B200_H_
+#define DEEPGEMM_B200_H_
+
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define DG_API __attribute__((visibility("default")))
+#else
+#define DG_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum dg_status {
+    DG_OK = 0,
+    DG_ERR_INVALID_ARGUMENT = 1,   /* an assertion of the reference's API layer would have fired */
+    DG_ERR_CUDA = 2,               /* a CUDA driver / runtime call failed */
+    DG_ERR_JIT = 3,                /* nvcc failed or the kernel image could not be loaded */
+    DG_ERR_UNSUPPORTED = 4,        /* valid for the reference, not built here (message says what) */
+    DG_ERR_KERNEL = 5              /* a kernel reported a failed bounded wait through the status word */
+} dg_status_t;
+
+typedef enum dg_dtype {
+    DG_FP8_E4M3 = 0,               /* torch.float8_e4m3fn */
+    DG_FP4_E2M1_X2 = 1,            /* two e2m1 codes per byte, even K in the low nibble (torch.int8 in the reference, csrc/utils/math.hpp:11) */
+    DG_BF16 = 2,
+    DG_FP32 = 3
+} dg_dtype_t;
+
+typedef enum dg_major { DG_MAJOR_K = 0, DG_MAJOR_MN = 1 } dg_major_t;
+
+typedef enum dg_gemm_kind {
+    DG_GEMM_DENSE = 0,
+    DG_GEMM_M_GROUPED_CONTIGUOUS = 1,
+    DG_GEMM_M_GROUPED_MASKED = 2
+} dg_gemm_kind_t;
+
+DG_API const char* dg_last_error(void);
+
+/* ---- library life cycle and process-wide settings: csrc/apis/config.hpp:9-47 ------------------ */
+
+/* init(library_root_path): where the device headers (csrc/device) and the in-tree kernel cache live.
+ * Touches no CUDA context (deep_gemm/__init__.py:122, tests/test_lazy_init.py:18-19). */
+DG_API int dg_init(const char* library_root);
+DG_API int dg_shutdown(void);
+DG_API int dg_set_num_sms(int num_sms);          /* must be even and at most the device's SM count (heuristics/config.hpp:60) */
+DG_API int dg_get_num_sms(void);                 /* the override, else the device's SM count, else 148 without a device */
+DG_API int dg_set_tc_util(int percent);          /* csrc/runtime/runtime.hpp:88-100; kept for API parity, unused by these kernels */
+DG_API int dg_get_tc_util(void);
+DG_API int dg_set_pdl(int enabled);              /* programmatic dependent launch attribute on every GEMM launch */
+DG_API int dg_get_pdl(void);
+
+/* ---- m-grouped contiguous layout alignment: csrc/apis/layout.hpp:133-141 ----------------------- */
+DG_API int dg_set_mk_alignment_for_contiguous_layout(int alignment);        /* unvalidated, like the reference */
+DG_API int dg_get_mk_alignment_for_contiguous_layout(void);                 /* default 128 (heuristics/runtime.hpp:12,18) */
+DG_API int dg_get_theoretical_mk_alignment_for_contiguous_layout(int expected_m_or_negative);  /* 256 on sm_100 (heuristics/runtime.hpp:57-64) */
+
+/* ---- scaling-factor layout: csrc/apis/layout.hpp:11-58, csrc/jit_kernels/impls/smxx_layout.hpp ---- */
+
+/* get_tma_aligned_size(x, element_size): csrc/utils/math.hpp:23-27.  Returns the aligned size, or -1. */
+DG_API int dg_get_tma_aligned_size(int x, int element_size);
+
+/* FP32 power-of-two scales [num_groups, ceil(mn / gran_mn), sf_k] with element strides (in_stride_*)
+ * -> packed UE8M0 int32 [num_groups, mn, ceil(sf_k / 4)] with element strides
+ * (ceil(sf_k/4) * align(mn,4), 1, align(mn,4)); rows are broadcast along MN by gran_mn.
+ * Replaces index_select + get_mn_major_tma_aligned_packed_ue8m0_tensor (csrc/apis/layout.hpp:44-50,
+ * smxx_layout.hpp:133-216; kernels deep_gemm/include/deep_gemm/impls/smxx_layout.cuh:78,195).
+ * `out` must hold num_groups * ceil(sf_k/4) * align(mn,4) int32 (device). */
+DG_API int dg_pack_fp32_into_ue8m0(const float* sf_device, int32_t* out_device,
+                            int num_groups, int mn, int sf_k, int gran_mn,
+                            int64_t in_stride_group, int64_t in_stride_mn, int64_t in_stride_k,
+                            void* stream);
+
+/* FP32 scales [num_groups, mn, sf_k] (any strides) -> same values MN-major with pitch align(mn,4):
+ * get_mn_major_tma_aligned_tensor (smxx_layout.hpp:60-106; kernel smxx_layout.cuh:13).
+ * `out` must hold num_groups * sf_k * align(mn,4) floats (device). */
+DG_API int dg_transpose_fp32_mn_major(const float* sf_device, float* out_device,
+                               int num_groups, int mn, int sf_k,
+                               int64_t in_stride_group, int64_t in_stride_mn, int64_t in_stride_k,
+                               void* stream);
+
+/* ---- GEMMs: csrc/apis/gemm.hpp:78-318 ----------------------------------------------------------- */
+
+typedef struct dg_gemm_args {
+    /* operands (device).  SFs are the packed UE8M0 int32 tensors of docs/scaling-factor-format.md:42-63:
+     * [groups?, mn, ceil(k / (4 gran_k))], MN contiguous, K pitch = sf*_pitch (>= align(mn,4), % 4 == 0),
+     * groups packed tightly (group stride = pitch * ceil(k / (4 gran_k))). */
+    const void* a;
+    const void* sfa;
+    const void* b;
+    const void* sfb;
+    void* d;
+    int32_t m;                 /* dense/contiguous: rows of A; masked: max_m (rows per group) */
+    int32_t n;
+    int32_t k;                 /* logical K (twice the byte count of a packed FP4 row) */
+    int32_t num_groups;        /* 1 for dense */
+    int32_t a_dtype;           /* dg_dtype_t: DG_FP8_E4M3 or DG_FP4_E2M1_X2 */
+    int32_t b_dtype;
+    int32_t d_dtype;           /* DG_BF16 or DG_FP32 (dense only) */
+    int32_t major_a;           /* dg_major_t; K-major: rows of K contiguous */
+    int32_t major_b;
+    int64_t lda;               /* pitch between rows (K-major) or between K slices (MN-major), in storage elements (bytes) */
+    int64_t ldb;
+    int64_t ldd;               /* row pitch of D in elements */
+    int64_t sfa_pitch;         /* stride(-1) of SFA in int32 elements */
+    int64_t sfb_pitch;
+    int32_t gran_k_a;          /* 32 or 128 */
+    int32_t gran_k_b;
+    int32_t accumulate;        /* non-zero: D += alpha A B^T (the reference's c == d case, gemm.hpp:17-53) */
+    int32_t has_alpha;
+    float alpha;               /* used when has_alpha != 0 (epilogue Alpha, csrc/jit_kernels/impls/epilogue_class.hpp:111-127) */
+    const int32_t* grouped_layout; /* contiguous: int32[m] expert id per row, -1 on padding; masked: int32[num_groups] rows used */
+    int32_t expected_m;        /* masked: heuristic hint only (gemm.hpp:269-318) */
+    void* stream;
+} dg_gemm_args_t;
+
+/* fp8_fp4_gemm_nt and, through major_a / major_b, nn / tn / tt (gemm.hpp:78-179). */
+DG_API int dg_fp8_fp4_gemm(const dg_gemm_args_t* args);
+/* m_grouped_fp8_fp4_gemm_nt_contiguous / nn (gemm.hpp:181-267). */
+DG_API int dg_m_grouped_fp8_fp4_gemm_contiguous(const dg_gemm_args_t* args);
+/* m_grouped_fp8_fp4_gemm_nt_masked (gemm.hpp:269-318). */
+DG_API int dg_m_grouped_fp8_fp4_gemm_masked(const dg_gemm_args_t* args);
+
+/* Compile (but do not load or launch) the kernel the call above would use, so that a later call
+ * finds it in the cache.  Needs nvcc, not a GPU.  Device pointers in `args` may be null. */
+DG_API int dg_gemm_precompile(int kind, const dg_gemm_args_t* args);
+
+/* ---- heuristics: csrc/jit_kernels/heuristics/{common,sm100}.hpp -------------------------------- */
+
+typedef struct dg_gemm_config {
+    int32_t block_m, block_n, block_k;
+    int32_t num_stages;
+    int32_t cluster_size;      /* CTAs per cluster (1 or 2) */
+    int32_t raster_group;      /* row blocks per band of the tile order */
+    int32_t num_ctas;          /* grid size */
+    int32_t smem_bytes;
+    int32_t tmem_cols;
+    int32_t num_tiles;         /* dense / contiguous: exact; masked: estimated from expected_m */
+    int32_t waves_x100;
+} dg_gemm_config_t;
+
+/* get_best_config<SM100ArchSpec> (heuristics/common.hpp:17-56, sm100.hpp:30-301).  Host only. */
+DG_API int dg_get_gemm_config(int kind, const dg_gemm_args_t* args, dg_gemm_config_t* config);
+
+/* Host model of the device tile scheduler (scheduler/gemm.cuh:108-204 in the reference): lists the
+ * tiles CTA `cta` of `num_ctas` visits, four uint32 per tile {m_block, n_block, group, valid_rows}.
+ * `layout` is a HOST pointer here.  Returns the number of tiles (may exceed max_tiles; only
+ * max_tiles are written) or a negative dg_status_t. */
+DG_API int dg_enumerate_tiles(int kind, int block_n, int raster_group, int shape_m, int shape_n, int num_groups,
+                       const int32_t* layout_host, int cta, int num_ctas, uint32_t* out, int max_tiles);
+
+/* ---- JIT runtime: csrc/runtime/jit.hpp + third-party/deep_jit (README.md:164-191) --------------- */
+
+typedef struct dg_kernel* dg_kernel_t;
+
+/* Compile `source` (CUDA C++, entry point `entry`, extern "C") to an sm_100a cubin, or find it in the
+ * cache (key: source + flags + compiler version).  Cache: $DG_JIT_CACHE_DIR, else <library_root>/_jit_cache
+ * if writable, else $HOME/.deepgemm_b200.  Honours DG_JIT_DEBUG, DG_JIT_PRINT_COMPILER_COMMAND,
+ * DG_JIT_PTXAS_VERBOSE, DG_JIT_WITH_LINEINFO, DG_JIT_NVCC_COMPILER. */
+DG_API int dg_jit_compile(const char* name, const char* entry, const char* source, const char* extra_flags, dg_kernel_t* kernel);
+/* Path of the cached cubin of a compiled kernel. */
+DG_API const char* dg_jit_kernel_path(dg_kernel_t kernel);
+/* cuLaunchKernelEx on `stream`; loads the module into the current context on first use. */
+DG_API int dg_jit_launch(dg_kernel_t kernel, uint32_t grid_x, uint32_t block_x, uint32_t cluster_x,
+                  uint32_t smem_bytes, int enable_pdl, void* stream, void** kernel_args);
+
+/* ---- kernel status word ------------------------------------------------------------------------- */
+/* Every wait inside the kernels is bounded; a wait that runs out writes a code here and the kernel
+ * unwinds.  Returns the word (0 = no failure) WITHOUT synchronising: call after the stream is idle. */
+DG_API int dg_kernel_status(void);
+DG_API int dg_reset_kernel_status(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif  /* DEEPGEMM_B200_H_ */
