@@ -1,0 +1,344 @@
+#!/usr/bin/env python
+"""Benchmark of the block-scaled FP8 GEMM hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--detail]
+
+A *step* is one pass over the six DeepSeek-V3-shaped dense FP8 GEMMs with M = 4096 that BASELINE.json's
+metric is quoted on (its config 2): D[M,N] = A[M,K] @ B[N,K]^T, A quantised per token per 128 of K, B per
+128 x 128 block, UE8M0 scales pre-packed, BF16 output, synthetic N(0,1) data.  `value` is the aggregate
+TFLOP/s (2 M N K over the six shapes / device time) with operands resident in HBM; `e2e` is the same pass
+through the public Python API with host buffers (pinned host -> device copies of A, SFA, B, SFB and a
+device -> host read of D inside the timed region).  With N > 1 (torchrun) every rank runs the same
+per-GPU workload on its own shard-shaped data (column-parallel shards of an N-times wider problem) and no
+collective runs in the timed region: weak scaling, value = sum over ranks.
+
+`--impl reference` times the reference path's CPU implementation (the numpy port of its torch
+dequantise-then-matmul, oracle/) on the host cores on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+M_DENSE = 4096
+DENSE_NK = [(2112, 7168), (24576, 1536), (32768, 512), (7168, 16384), (4096, 7168), (7168, 2048)]
+NOMINAL_FP8_TFLOPS = 4500.0
+CPU_SAMPLE_NK = (2112, 7168)          # the bounded sample the CPU arm times (1 of the 6 shapes)
+
+
+def flops_of(m, n, k):
+    return 2.0 * m * n * k
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_burst": p["bf16_tflops"], "bf16_sustained": p["bf16_tflops_sustained"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_burst": 1590.0, "bf16_sustained": 1400.0, "source": "fallback"}
+
+
+# ----------------------------------------------------------------------------------------------------
+# Clock sampling during the timed region (NVML reads only)
+# ----------------------------------------------------------------------------------------------------
+class ClockSampler:
+    def __init__(self, index: int, period_s: float = 0.02):
+        self.index, self.period, self.samples, self.reasons = index, period_s, [], set()
+        self.max_mhz, self._stop, self._thread, self._nvml = None, threading.Event(), None, None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nvml = None
+
+    def _run(self):
+        nv = self._nvml
+        names = {"hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+                 "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+                 "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+                 "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4)}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                get = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+                mask = get(self._h)
+                for name, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def __enter__(self):
+        if self._nvml is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+# ----------------------------------------------------------------------------------------------------
+# CPU arm: the reference path's dequantise-then-matmul on the host cores (numpy port in oracle/)
+# ----------------------------------------------------------------------------------------------------
+def cpu_sample_inputs(seed=0):
+    import numpy as np
+    import oracle
+    n, k = CPU_SAMPLE_NK
+    rng = np.random.default_rng(seed)
+    a = oracle.bf16_round(rng.standard_normal((M_DENSE, k)).astype(np.float32))
+    b = oracle.bf16_round(rng.standard_normal((n, k)).astype(np.float32))
+    qa, sfa = oracle.per_token_cast_to_fp8(a, True, 128)
+    qb, sfb = oracle.per_block_cast_to_fp8(b, True)
+    return qa, sfa, qb, oracle.broadcast_sf_along_mn(sfb, n, 128)
+
+
+def cpu_step(inputs):
+    import oracle
+    qa, sfa, qb, sfb = inputs
+    return oracle.bf16_round(oracle.dequant_gemm_nt(qa, sfa, qb, sfb))
+
+
+def cpu_threads():
+    try:
+        from threadpoolctl import threadpool_info
+        blas = [p["num_threads"] for p in threadpool_info() if p.get("user_api") == "blas"]
+        if blas:
+            return max(blas)
+    except Exception:
+        pass
+    return os.cpu_count() or 1
+
+
+def time_cpu(steps, warmup):
+    import numpy  # noqa: F401  (make sure BLAS is loaded before counting threads)
+    inputs = cpu_sample_inputs()
+    for _ in range(warmup):
+        cpu_step(inputs)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu_step(inputs)
+    dt = (time.perf_counter() - t0) / max(steps, 1)
+    n, k = CPU_SAMPLE_NK
+    return flops_of(M_DENSE, n, k) / dt / 1e12, dt
+
+
+def run_reference_arm(args, rank):
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 8))           # bounded: each CPU step is ~0.5-3 s
+    warm = max(1, min(args.warmup, 2))
+    tflops, dt = time_cpu(steps, warm)
+    n, k = CPU_SAMPLE_NK
+    sample = f"M={M_DENSE},N={n},K={k} (1 of the 6 dense shapes), dequantise + FP32 matmul, {steps} steps"
+    line = {
+        "impl": "reference", "metric": "dense_fp8_gemm_tflops", "value": round(tflops, 4), "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": warm, "ms_per_step": round(dt * 1e3, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "dense_fp8_gemm_nt_m4096 (config 2), bounded sample", "sample": sample},
+        "cpu_baseline": {"value": round(tflops, 4), "unit": "TFLOP/s", "cores": cpu_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": round(tflops, 4), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------------------------------
+# GPU arm
+# ----------------------------------------------------------------------------------------------------
+def make_dense_case(m, n, k, seed, torch, dg):
+    from deepgemm_amd_b200.utils import per_block_cast_to_fp8, per_token_cast_to_fp8
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    a = torch.randn((m, k), device="cuda", dtype=torch.bfloat16, generator=g)
+    b = torch.randn((n, k), device="cuda", dtype=torch.bfloat16, generator=g)
+    qa, sfa = per_token_cast_to_fp8(a, True, 128)
+    qb, sfb = per_block_cast_to_fp8(b, True)
+    sfa = dg.transform_sf_into_required_layout(sfa, m, k, (1, 128))
+    sfb = dg.transform_sf_into_required_layout(sfb, n, k, (128, 128))
+    d = torch.empty((m, n), device="cuda", dtype=torch.bfloat16)
+    return {"m": m, "n": n, "k": k, "a": (qa, sfa), "b": (qb, sfb), "d": d}
+
+
+def flat_storage(t, torch):
+    """The whole allocation behind a (possibly strided) tensor as a flat view, for host <-> device copies."""
+    span = 1 + sum((s - 1) * st for s, st in zip(t.shape, t.stride()))
+    return torch.as_strided(t, (span,), (1,))
+
+
+def time_events(fn, steps, torch, dist_barrier):
+    dist_barrier()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        fn()
+    end.record()
+    torch.cuda.synchronize()
+    dist_barrier()
+    return start.elapsed_time(end) / 1e3
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--detail", action="store_true", help="also time each shape of configs 2-5 on its own (rank 0)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--shapes", default="", help="comma-separated NxK subset of the six dense shapes (profiling runs)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+    import deepgemm_amd_b200 as dg
+    from deepgemm_amd_b200.dist import init_dist
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the GEMM path has no CPU fallback (use --impl reference for the CPU arm)")
+    rank, world, local_rank = init_dist()
+    torch.cuda.set_device(local_rank)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    nk_list = DENSE_NK
+    if args.shapes:
+        nk_list = [tuple(int(v) for v in s.split("x")) for s in args.shapes.split(",")]
+    cases = [make_dense_case(M_DENSE, n, k, 1000 * rank + i, torch, dg) for i, (n, k) in enumerate(nk_list)]
+    step_flops = sum(flops_of(c["m"], c["n"], c["k"]) for c in cases)
+
+    def step():
+        for c in cases:
+            dg.fp8_gemm_nt(c["a"], c["b"], c["d"], recipe=(1, 1, 128))
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    if dg.kernel_status() != 0:
+        raise SystemExit(f"kernel reported status {dg.kernel_status():#x}")
+
+    with ClockSampler(local_rank) as clocks:
+        dt = time_events(step, args.steps, torch, barrier)
+    t = torch.tensor([dt], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dt_max = float(t.item())
+    value = world * step_flops * args.steps / dt_max / 1e12
+
+    # ---- end to end through the public API with host buffers ---------------------------------------
+    host, dev_flat = [], []
+    for c in ([] if args.no_e2e else cases):
+        tensors = [c["a"][0], c["a"][1], c["b"][0], c["b"][1]]
+        flats = [flat_storage(x, torch) for x in tensors]
+        flats = [f.view(torch.uint8) if f.dtype == torch.float8_e4m3fn else f for f in flats]
+        host.append([f.cpu().pin_memory() for f in flats] + [torch.empty(c["d"].shape, dtype=c["d"].dtype).pin_memory()])
+        dev_flat.append(flats)
+    h2d = sum(h.numel() * h.element_size() for hs in host for h in hs[:-1])
+    d2h = sum(hs[-1].numel() * hs[-1].element_size() for hs in host)
+
+    def e2e_step():
+        for c, hs, fs in zip(cases, host, dev_flat):
+            for h, f in zip(hs[:-1], fs):
+                f.copy_(h, non_blocking=True)
+            dg.fp8_gemm_nt(c["a"], c["b"], c["d"], recipe=(1, 1, 128))
+            hs[-1].copy_(c["d"], non_blocking=True)
+
+    e2e_steps = max(1, min(args.steps, 5))
+    e2e_value = None
+    if not args.no_e2e:
+        e2e_step()
+        e2e_dt = time_events(e2e_step, e2e_steps, torch, barrier)
+        te = torch.tensor([e2e_dt], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        e2e_value = world * step_flops * e2e_steps / float(te.item()) / 1e12
+
+    if rank != 0:
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
+    peaks = load_peaks()
+    clk = clocks.summary()
+    per_gpu = value / world
+    # The dominant (only) kernel of the step is the tcgen05 GEMM; FP8 runs at twice the BF16 tensor rate, so the
+    # measured denominator is 2 x the cuBLAS BF16 figure (sustained: the kernel is timed inside a long loop).
+    peak_fp8 = 2.0 * peaks["bf16_sustained"]
+    line = {
+        "metric": "dense_fp8_gemm_tflops", "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt_max / args.steps * 1e3, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate, bf16 out)",
+        "data": "synthetic",
+        "config": {"workload": "dense_fp8_gemm_nt_m4096 (BASELINE config 2, the six (N,K) at M=4096)",
+                   "shapes_mnk": [[c["m"], c["n"], c["k"]] for c in cases],
+                   "scales": "UE8M0 packed int32, A 1x128, B 128x128 pre-broadcast",
+                   "l2": "no flush: one step streams 1.0 GB through six different shapes, 8x the 126 MB L2",
+                   "parallelism": f"replicated shards x{world}, no collective in the timed region"},
+        "pct_of_nominal_fp8_peak": round(100.0 * per_gpu / NOMINAL_FP8_TFLOPS, 2),
+        "roofline": {"bound": "tensor", "achieved": round(per_gpu, 2), "peak": round(peak_fp8, 1), "unit": "TFLOP/s",
+                     "frac": round(per_gpu / peak_fp8, 4), "traffic": None,
+                     "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peaks['source']}); nominal FP8 dense 4500",
+                     "frac_of_nominal": round(per_gpu / NOMINAL_FP8_TFLOPS, 4)},
+        "clocks": clk,
+        "e2e": {"value": None if e2e_value is None else round(e2e_value, 3), "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "steps": e2e_steps},
+        "gpu_launches": args.steps * len(cases),
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        tflops, cdt = time_cpu(2, 1)
+        n, k = CPU_SAMPLE_NK
+        line["cpu_baseline"] = {"value": round(tflops, 4), "unit": "TFLOP/s", "cores": cpu_threads(), "kind": "port",
+                                "sample": f"M={M_DENSE},N={n},K={k} (1 of the 6 shapes), 2 steps of {cdt:.2f} s"}
+    if args.detail:
+        line["detail"] = detail_rows(torch, dg)
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def detail_rows(torch, dg):
+    """Per-shape device times (L2 flushed before every call) for BASELINE configs 2-5."""
+    from deepgemm_amd_b200.testing import bench
+    rows = []
+    for m in (64, 128, 4096):
+        for i, (n, k) in enumerate(DENSE_NK):
+            c = make_dense_case(m, n, k, 77 + i, torch, dg)
+            t = bench(lambda: dg.fp8_gemm_nt(c["a"], c["b"], c["d"], recipe=(1, 1, 128)), 3, 10)
+            byts = m * k + n * k + m * n * 2 + (m + n) * (k // 128)
+            rows.append({"case": f"dense m{m} n{n} k{k}", "us": round(t * 1e6, 1), "tflops": round(flops_of(m, n, k) / t / 1e12, 1),
+                         "gbs": round(byts / t / 1e9, 0)})
+    return rows
+
+
+if __name__ == "__main__":
+    main()

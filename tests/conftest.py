@@ -4,12 +4,19 @@ import sys
 import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-if ROOT not in sys.path:
-    sys.path.insert(0, ROOT)
+for p in (ROOT, os.path.join(ROOT, "tests")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
 
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (sm_100a)")
+
+
+def pytest_sessionstart(session):
+    # The C-ABI library is built in-tree (nvcc cross-compiles without a GPU); build it if it is not there yet.
+    from deepgemm_amd_b200.build import build_library
+    build_library()
 
 
 @pytest.fixture(scope="session")

@@ -1,0 +1,203 @@
+"""CPU-side checks of the C-ABI library: exported symbols, settings, argument validation, heuristics
+invariants, the host model of the tile scheduler, and the JIT runtime's compile / cache / error paths.
+No compute call is made; no GPU is needed."""
+import ctypes as C
+import os
+import re
+import shutil
+
+import numpy as np
+import pytest
+
+import deepgemm_amd_b200 as dg
+from deepgemm_amd_b200 import _lib
+from deepgemm_amd_b200._lib import GemmArgs, GemmConfig, lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "deepgemm_b200.h")).read()
+    declared = set(re.findall(r"DG_API\s+[\w\s\*]+?\b(dg_\w+)\s*\(", header))
+    assert len(declared) >= 25
+    raw = C.CDLL(_lib.LIB_PATH)
+    for name in declared:
+        assert hasattr(raw, name), f"{name} is declared in include/deepgemm_b200.h but not exported"
+    assert declared == set(_lib.SIGNATURES), declared ^ set(_lib.SIGNATURES)
+
+
+def test_settings_defaults_and_setters():
+    # defaults of the reference: alignment 128, theoretical 256 on sm_100, tc_util 100
+    assert dg.get_mk_alignment_for_contiguous_layout() == 128
+    assert dg.get_theoretical_mk_alignment_for_contiguous_layout() == 256
+    assert dg.get_theoretical_mk_alignment_for_contiguous_layout(64) == 256
+    assert dg.get_tc_util() == 100 and dg.get_pdl() is False
+    dg.set_mk_alignment_for_contiguous_layout(256)
+    assert dg.get_m_alignment_for_contiguous_layout() == 256 == dg.get_k_alignment_for_contiguous_layout()
+    dg.set_mk_alignment_for_contiguous_layout(128)
+    assert dg.get_num_sms() == 148            # no device here: B200's SM count
+    with pytest.raises(RuntimeError, match="Assertion error"):
+        dg.set_num_sms(147)                   # must be even (heuristics/config.hpp:60)
+    dg.set_num_sms(132)
+    assert dg.get_num_sms() == 132
+    lib.dg_set_num_sms  # restore
+    _lib.check(lib.dg_set_num_sms(148))
+    dg.set_tc_util(80)
+    assert dg.get_tc_util() == 80
+    dg.set_tc_util(100)
+    dg.set_pdl(True)
+    assert dg.get_pdl() is True
+    dg.set_pdl(False)
+    assert dg.get_tma_aligned_size(4097, 4) == 4100 and dg.get_tma_aligned_size(129, 1) == 144
+    with pytest.raises(RuntimeError):
+        dg.get_tma_aligned_size(10, 3)
+
+
+def _args(m=256, n=512, k=1024, groups=1, **kw):
+    a = GemmArgs()
+    a.m, a.n, a.k, a.num_groups = m, n, k, groups
+    a.a_dtype, a.b_dtype, a.d_dtype = _lib.DG_FP8_E4M3, _lib.DG_FP8_E4M3, _lib.DG_BF16
+    a.lda, a.ldb, a.ldd = k, k, n
+    a.sfa_pitch, a.sfb_pitch = (m + 3) // 4 * 4, (n + 3) // 4 * 4
+    a.gran_k_a = a.gran_k_b = 128
+    a.expected_m = 64
+    for key, v in kw.items():
+        setattr(a, key, v)
+    return a
+
+
+@pytest.mark.parametrize("kw,kind,pattern", [
+    (dict(gran_k_a=64), 0, "gran_k_a == 32"),
+    (dict(d_dtype=_lib.DG_FP8_E4M3), 0, "d_dtype == DG_BF16"),
+    (dict(ldd=500), 0, "ldd >= a->n"),
+    (dict(n=513, ldd=513), 0, "% 16 == 0"),
+    (dict(sfa_pitch=254), 0, "sfa_pitch"),
+    (dict(sfb_pitch=514), 0, "sfb_pitch % 4"),
+    (dict(lda=1000), 0, "lda >= k_bytes_a"),
+    (dict(num_groups=2), 0, "num_groups == 1"),
+    (dict(d_dtype=_lib.DG_FP32, num_groups=2), 1, "d_dtype == DG_BF16"),
+    (dict(m=200, num_groups=2), 1, "m % 128 == 0"),
+    (dict(num_groups=2, expected_m=0), 2, "expected_m > 0"),
+    (dict(num_groups=2, accumulate=1), 2, "!a->accumulate"),
+])
+def test_argument_validation_fails_like_the_reference_asserts(kw, kind, pattern):
+    cfg = GemmConfig()
+    rc = lib.dg_get_gemm_config(kind, C.byref(_args(**kw)), C.byref(cfg))
+    assert rc == 1, _lib.last_error()
+    assert _lib.last_error().startswith("Assertion error (") and pattern in _lib.last_error(), _lib.last_error()
+
+
+def test_unsupported_combinations_say_so():
+    cfg = GemmConfig()
+    rc = lib.dg_get_gemm_config(0, C.byref(_args(a_dtype=_lib.DG_FP4_E2M1_X2, b_dtype=_lib.DG_FP4_E2M1_X2)), C.byref(cfg))
+    assert rc == 4 and "FP4 x FP4" in _lib.last_error()
+
+
+SHAPES = [(m, n, k) for m in (1, 64, 128, 129, 4096) for (n, k) in
+          ((2112, 7168), (576, 7168), (24576, 1536), (32768, 512), (7168, 16384), (4096, 7168), (7168, 2048), (16, 128))]
+
+
+@pytest.mark.parametrize("fp32", [False, True])
+def test_heuristics_invariants(fp32):
+    for m, n, k in SHAPES:
+        cfg = dg.get_gemm_config(0, m, n, k, d_is_fp32=fp32)
+        assert cfg["block_m"] == 128 and cfg["block_k"] == 128
+        assert cfg["block_n"] % 16 == 0 and 16 <= cfg["block_n"] <= 240
+        assert cfg["smem_bytes"] <= 232448, (m, n, k, cfg)
+        assert cfg["tmem_cols"] in (32, 64, 128, 256, 512) and 2 * cfg["block_n"] + 4 + 4 * ((cfg["block_n"] + 127) // 128) <= cfg["tmem_cols"]
+        assert 2 <= cfg["num_stages"] <= 32
+        assert 1 <= cfg["num_ctas"] <= 148
+        assert cfg["num_tiles"] == -(-m // 128) * -(-n // cfg["block_n"])
+    for kind, groups in ((1, 32), (2, 16)):
+        cfg = dg.get_gemm_config(kind, 256 if kind == 2 else 32 * 1024, 4096, 7168, num_groups=groups, expected_m=64)
+        assert cfg["smem_bytes"] <= 232448 and cfg["num_ctas"] <= 148
+
+
+def _enumerate(kind, bn, rg, m, n, groups, layout, num_ctas):
+    tiles = []
+    lay = np.ascontiguousarray(layout, dtype=np.int32) if layout is not None else None
+    ptr = lay.ctypes.data_as(C.c_void_p) if lay is not None else None
+    for cta in range(num_ctas):
+        buf = (C.c_uint32 * (4 * 8192))()
+        cnt = lib.dg_enumerate_tiles(kind, bn, rg, m, n, groups, ptr, cta, num_ctas, buf, 8192)
+        assert 0 <= cnt <= 8192
+        tiles += [tuple(buf[4 * i: 4 * i + 4]) + (cta, i) for i in range(cnt)]
+    return tiles
+
+
+@pytest.mark.parametrize("m,n,bn,rg,ctas", [(4096, 4096, 240, 16, 148), (129, 2112, 16, 16, 132), (1, 16, 16, 16, 1),
+                                            (1000, 1000, 64, 4, 7), (4096, 7168, 224, 8, 148)])
+def test_scheduler_dense_visits_every_tile_once(m, n, bn, rg, ctas):
+    tiles = _enumerate(0, bn, rg, m, n, 1, None, ctas)
+    seen = sorted((t[0], t[1]) for t in tiles)
+    want = sorted((i, j) for i in range(-(-m // 128)) for j in range(-(-n // bn)))
+    assert seen == want
+    assert all(t[2] == 0 and t[3] == 128 for t in tiles)
+    # static round-robin: CTA c's i-th tile is global tile i * ctas + c, so loads are balanced to within one tile
+    per_cta = np.bincount([t[4] for t in tiles], minlength=ctas)
+    assert per_cta.max() - per_cta.min() <= 1
+
+
+def test_scheduler_contiguous_maps_row_blocks_to_experts():
+    import oracle
+    m, actual, aligned, layout = oracle.make_contiguous_layout(6, 300, 128, seed=2)
+    tiles = _enumerate(1, 128, 16, m, 512, 6, layout, 20)
+    assert sorted((t[0], t[1]) for t in tiles) == sorted((i, j) for i in range(m // 128) for j in range(4))
+    for mb, nb, group, valid, _, _ in tiles:
+        assert group == max(0, int(layout[mb * 128])) and valid == 128
+    # with alignment 256 every second block may start on padding (-1): it still belongs to the expert before it
+    m2, _, aligned2, layout2 = oracle.make_contiguous_layout(3, 100, 256, actual_ms=[100, 0, 300])
+    tiles2 = _enumerate(1, 64, 16, m2, 128, 3, layout2, 3)
+    blocks = {t[0]: t[2] for t in tiles2}
+    assert blocks[0] == 0 and blocks[1] == 0 and blocks[2] == 2 and blocks[3] == 2 and blocks[4] == 2
+
+
+@pytest.mark.parametrize("counts,max_m", [((45, 83, 0, 256, 129), 256), ((0, 0, 0), 128), ((300, 1), 256), ((64,) * 16, 256)])
+def test_scheduler_masked_follows_device_counts(counts, max_m):
+    n, bn = 4096, 240
+    tiles = _enumerate(2, bn, 16, max_m, n, len(counts), counts, 148)
+    want = {}
+    for g, c in enumerate(counts):
+        c = min(c, max_m)
+        for mb in range(-(-c // 128)):
+            for nb in range(-(-n // bn)):
+                want[(g, mb, nb)] = min(128, c - mb * 128)
+    got = {(t[2], t[0], t[1]): t[3] for t in tiles}
+    assert len(tiles) == len(got) == len(want) and got == want      # each tile exactly once, none beyond masked_m
+
+
+TRIVIAL = 'extern "C" __global__ void k(int* p) { if (p) *p = %d; }\n'
+
+
+def test_jit_compile_cache_and_errors(tmp_path, monkeypatch):
+    monkeypatch.setenv("DG_JIT_CACHE_DIR", str(tmp_path))
+    h1, h2, h3 = C.c_void_p(), C.c_void_p(), C.c_void_p()
+    _lib.check(lib.dg_jit_compile(b"trivial", b"k", (TRIVIAL % 1).encode(), b"", C.byref(h1)))
+    path = lib.dg_jit_kernel_path(h1).decode()
+    assert path.startswith(str(tmp_path)) and os.path.getsize(path) > 0
+    assert not [d for d in os.listdir(tmp_path) if d.startswith("tmp.")]       # published by rename, no leftovers
+    mtime = os.path.getmtime(path)
+    _lib.check(lib.dg_jit_compile(b"trivial", b"k", (TRIVIAL % 1).encode(), b"", C.byref(h2)))
+    assert h1.value == h2.value and os.path.getmtime(path) == mtime             # cache hit
+    _lib.check(lib.dg_jit_compile(b"trivial", b"k", (TRIVIAL % 2).encode(), b"", C.byref(h3)))
+    assert lib.dg_jit_kernel_path(h3).decode() != path                          # different source, different key
+    bad = C.c_void_p()
+    rc = lib.dg_jit_compile(b"broken", b"k", b"this is not CUDA", b"", C.byref(bad))
+    assert rc == 3 and "nvcc failed" in _lib.last_error() and "error" in _lib.last_error()
+    assert not [d for d in os.listdir(tmp_path) if d.startswith("tmp.")]
+    # launching needs a driver: without one the call fails cleanly instead of crashing
+    import torch
+    if not torch.cuda.is_available():
+        rc = lib.dg_jit_launch(h1, 1, 32, 1, 0, 0, None, None)
+        assert rc == 2 and "driver" in _lib.last_error().lower()
+
+
+def test_gemm_kernel_source_compiles_for_every_family(tmp_path, monkeypatch):
+    monkeypatch.setenv("DG_JIT_CACHE_DIR", str(tmp_path))
+    dg.precompile_gemm(0, 128, 2112, 7168)
+    dg.precompile_gemm(0, 4096, 4096, 7168, d_is_fp32=True, accumulate=True)
+    dg.precompile_gemm(1, 1024, 4096, 7168, num_groups=4)
+    dg.precompile_gemm(2, 256, 4096, 7168, num_groups=16, expected_m=64)
+    dg.precompile_gemm(0, 4096, 7168, 2048, b_is_fp4=True, gran_k_b=32)
+    kinds = sorted(d.split(".")[1] for d in os.listdir(tmp_path))
+    assert kinds == sorted(["gemm_fp8_fp4_dense"] * 3 + ["gemm_fp8_fp4_m_grouped_contiguous", "gemm_fp8_fp4_m_grouped_masked"])

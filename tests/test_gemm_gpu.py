@@ -1,0 +1,358 @@
+"""GPU parity tests: the CUDA path, called through the C ABI (via the Python host layer), against the
+numpy oracle on the same seeded inputs.  Thresholds follow the reference's own tests
+(tests/test_fp8_fp4.py:54-57, tests/generators.py:69-74): calc_diff < 1e-3 against the
+dequantise-then-matmul value for every format; exact indexing for the grouped layouts."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from gpu_helpers import (diff_report, fp4_cuda, fp8_cuda, packed_sf_cuda, quantise_dense, seeded_bf16, upload_strided)
+
+pytestmark = pytest.mark.gpu
+
+dg = pytest.importorskip("deepgemm_amd_b200")
+
+MAX_DIFF = 1e-3          # BASELINE criterion against the dequantised reference; measured values are ~1.4e-6
+
+
+def _run_dense(qa, sfa_rows, qb, sfb_rows, b_fp4=False, gran_k_a=128, gran_k_b=128, out_dtype=torch.bfloat16, c=None, alpha=None):
+    m, n = qa.shape[0], qb.shape[0]
+    a = (fp8_cuda(qa), packed_sf_cuda(sfa_rows))
+    b = (fp4_cuda(qb) if b_fp4 else fp8_cuda(qb), packed_sf_cuda(sfb_rows))
+    d = torch.full((m, n), float("nan"), dtype=out_dtype, device="cuda") if c is None else c
+    dg.reset_kernel_status()
+    dg.fp8_fp4_gemm_nt(a, b, d, c=c, recipe_a=(1, gran_k_a), recipe_b=(1, gran_k_b), alpha=alpha)
+    assert dg.kernel_status() == 0
+    return d
+
+
+@pytest.mark.parametrize("m,n,k", [
+    (128, 128, 128),            # one tile, one K-block
+    (128, 128, 512),            # all four scale bytes of a packed word
+    (128, 128, 640),            # K tail inside the second packed word
+    (1, 128, 128), (129, 256, 256),     # M tails
+    (200, 304, 640), (64, 2112, 1024),  # N tails, multi-tile
+    (128, 2112, 7168),          # BASELINE config 1
+    (4096, 576, 7168 // 4),
+])
+def test_dense_fp8_matches_oracle(m, n, k):
+    qa, sfa, qb, sfb, _ = quantise_dense(seeded_bf16((m, k), 1), seeded_bf16((n, k), 2))
+    d = _run_dense(qa, sfa, qb, sfb).float().cpu().numpy()
+    ref = oracle.dequant_gemm_nt(qa, sfa, qb, sfb)
+    assert not np.isnan(d).any()
+    assert oracle.calc_diff(d, ref) < MAX_DIFF, diff_report(d, ref)
+    assert oracle.calc_diff(d, oracle.bf16_round(ref)) < 1e-5, diff_report(d, ref)   # only accumulation order differs
+
+
+def test_dense_fp8_matches_reference_python_golden(golden):
+    a = (golden["gemm_a_bits"].astype(np.uint32) << 16).view(np.float32)
+    b = (golden["gemm_b_bits"].astype(np.uint32) << 16).view(np.float32)
+    qa, sfa, qb, sfb, _ = quantise_dense(a, b)
+    d = _run_dense(qa, sfa, qb, sfb, out_dtype=torch.float).cpu().numpy()
+    ref = golden["gemm_fp8_ref_dequant"]                          # torch result of the reference's cast_back @ cast_back
+    assert oracle.calc_diff(d, ref) < 1e-9, diff_report(d, ref)
+    assert np.allclose(d, ref, rtol=2e-5, atol=2e-4)
+    qb4, sfb4 = oracle.per_token_cast_to_fp4(b, True, 32)
+    d4 = _run_dense(qa, sfa, qb4, sfb4, b_fp4=True, gran_k_b=32, out_dtype=torch.float).cpu().numpy()
+    # K = 384 is a multiple of 128 as the FP4 tensor map requires
+    assert oracle.calc_diff(d4, golden["gemm_fp4_ref_dequant"]) < 1e-9
+
+
+@pytest.mark.parametrize("forced_bn", [16, 48, 96, 160, 224, 240])
+def test_every_store_width_and_scale_chunking(forced_bn, monkeypatch):
+    monkeypatch.setenv("DG_FORCE_BLOCK_N", str(forced_bn))
+    m, n, k = 256, 720, 1152
+    qa, sfa, qb, sfb, _ = quantise_dense(seeded_bf16((m, k), 3), seeded_bf16((n, k), 4))
+    d = _run_dense(qa, sfa, qb, sfb).float().cpu().numpy()
+    ref = oracle.dequant_gemm_nt(qa, sfa, qb, sfb)
+    assert oracle.calc_diff(d, ref) < 1e-5, diff_report(d, ref)
+
+
+def test_fp32_output_accumulation_and_alpha():
+    m, n, k = 192, 320, 768
+    qa, sfa, qb, sfb, _ = quantise_dense(seeded_bf16((m, k), 5), seeded_bf16((n, k), 6))
+    ref = oracle.dequant_gemm_nt(qa, sfa, qb, sfb)
+    d32 = _run_dense(qa, sfa, qb, sfb, out_dtype=torch.float).cpu().numpy()
+    assert oracle.calc_diff(d32, ref) < 1e-9 and np.allclose(d32, ref, rtol=2e-5, atol=2e-3)
+    # BF16 output is the FP32 output rounded once (tests/utils.py:20-38)
+    d16 = _run_dense(qa, sfa, qb, sfb)
+    assert torch.equal(d16.cpu(), torch.from_numpy(d32).bfloat16())
+    # alpha scales in FP32 before rounding
+    da = _run_dense(qa, sfa, qb, sfb, out_dtype=torch.float, alpha=0.25).cpu().numpy()
+    assert np.array_equal(da, d32 * np.float32(0.25))
+    # D = C + A B^T with c is d (tests/generators.py:358-363), FP32 and BF16
+    c0 = torch.from_numpy(seeded_bf16((m, n), 7, 32.0)).cuda()
+    c = c0.clone()
+    out = _run_dense(qa, sfa, qb, sfb, out_dtype=torch.float, c=c)
+    assert out.data_ptr() == c.data_ptr()
+    assert np.allclose(out.cpu().numpy(), d32 + c0.cpu().numpy(), rtol=1e-6, atol=1e-4)
+    cb = c0.bfloat16().clone()
+    outb = _run_dense(qa, sfa, qb, sfb, c=cb).float().cpu().numpy()
+    assert oracle.calc_diff(outb, ref + c0.cpu().numpy()) < 1e-4
+    # c different from d: copied first
+    d_new = torch.empty((m, n), dtype=torch.float, device="cuda")
+    a = (fp8_cuda(qa), packed_sf_cuda(sfa)); b = (fp8_cuda(qb), packed_sf_cuda(sfb))
+    dg.fp8_gemm_nt(a, b, d_new, c=c0, recipe=(1, 1, 128))
+    assert np.allclose(d_new.cpu().numpy(), d32 + c0.cpu().numpy(), rtol=1e-6, atol=1e-4)
+
+
+def test_fp32_scales_are_transformed_on_the_fly_like_the_legacy_recipe():
+    # float32 SFA [m, k/128] and SFB [n/128, k/128] with the default recipe (1, 128, 128) (csrc/utils/layout.hpp:85-98)
+    m, n, k = 128, 2112, 1024
+    qa, sfa, qb, sfb_rows, sfb_raw = quantise_dense(seeded_bf16((m, k), 8), seeded_bf16((n, k), 9))
+    d = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    dg.fp8_gemm_nt((fp8_cuda(qa), torch.from_numpy(sfa).cuda()), (fp8_cuda(qb), torch.from_numpy(sfb_raw).cuda()), d)
+    ref = oracle.dequant_gemm_nt(qa, sfa, qb, sfb_rows)
+    assert oracle.calc_diff(d.float().cpu().numpy(), ref) < 1e-5
+
+
+def test_bitwise_determinism_over_reruns():
+    m, n, k = 512, 2112, 2048
+    qa, sfa, qb, sfb, _ = quantise_dense(seeded_bf16((m, k), 10), seeded_bf16((n, k), 11))
+    first = _run_dense(qa, sfa, qb, sfb).clone()
+    for _ in range(20):                                           # tests/test_fp8_fp4.py:78-82
+        assert torch.equal(_run_dense(qa, sfa, qb, sfb).view(torch.int16), first.view(torch.int16))
+
+
+def test_scale_pitch_padding_is_never_read():
+    """Scales with a K pitch larger than align(mn, 4) and the padding poisoned with 0xFF (the UE8M0 NaN):
+    the result must be bitwise the same (tests/test_fp8_fp4.py:83-94, tests/utils.py:41-50)."""
+    m, n, k = 130, 260, 1024
+    qa, sfa, qb, sfb, _ = quantise_dense(seeded_bf16((m, k), 12), seeded_bf16((n, k), 13))
+    base = _run_dense(qa, sfa, qb, sfb)
+
+    def poisoned(sf_rows):
+        view, strides = oracle.mn_major_tma_aligned_packed_ue8m0(sf_rows)
+        mn, pk = view.shape
+        pitch = strides[1] + 8
+        storage = np.full((pk, pitch), -1, dtype=np.int32)
+        storage[:, :mn] = view.T
+        t = torch.from_numpy(storage).cuda()
+        return torch.as_strided(t, (mn, pk), (1, pitch))
+    d = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    dg.fp8_gemm_nt((fp8_cuda(qa), poisoned(sfa)), (fp8_cuda(qb), poisoned(sfb)), d, recipe=(1, 1, 128))
+    assert torch.equal(d.view(torch.int16), base.view(torch.int16))
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 512), (4096, 512, 2048), (64, 7168, 2048)])
+def test_fp8_x_fp4_matches_oracle_and_its_fp8_reencoding(m, n, k):
+    a, b = seeded_bf16((m, k), 14), seeded_bf16((n, k), 15)
+    qa, sfa = oracle.per_token_cast_to_fp8(a, True, 128)
+    qb4, sfb4 = oracle.per_token_cast_to_fp4(b, True, 32)
+    d4 = _run_dense(qa, sfa, qb4, sfb4, b_fp4=True, gran_k_b=32)
+    ref = oracle.dequant_gemm_nt(qa, sfa, qb4, sfb4, 128, 32, False, True)
+    out = d4.float().cpu().numpy()
+    assert oracle.calc_diff(out, ref) < MAX_DIFF, diff_report(out, ref)
+    # the reference's own bound against the unquantised product for FP8 x FP4 is 1e-2 (tests/generators.py:69-74)
+    assert oracle.calc_diff(out, a.astype(np.float64) @ b.astype(np.float64).T) < 1e-2
+    # the same B re-encoded as E4M3 (exact) must give the same result (tests/test_fp8_fp4.py:95-100)
+    d8 = _run_dense(qa, sfa, oracle.fp4_to_e4m3_bytes(qb4), sfb4, gran_k_b=32)
+    assert oracle.calc_diff(d8.float().cpu().numpy(), out) < 1e-14
+    assert torch.equal(d8.view(torch.int16), d4.view(torch.int16))
+
+
+# ---------------------------------------------------------------------------------------------------
+# m-grouped contiguous
+# ---------------------------------------------------------------------------------------------------
+def _grouped_inputs(g, n, k, a, b_fp4=False):
+    b = seeded_bf16((g, n, k), 21)
+    qa, sfa = oracle.per_token_cast_to_fp8(a, True, 128)
+    if b_fp4:
+        qs = [oracle.per_token_cast_to_fp4(b[i], True, 32) for i in range(g)]
+        qb, sfb = np.stack([q for q, _ in qs]), np.stack([s for _, s in qs])
+    else:
+        qs = [oracle.per_block_cast_to_fp8(b[i], True) for i in range(g)]
+        qb = np.stack([q for q, _ in qs])
+        sfb = np.stack([oracle.broadcast_sf_along_mn(s, n, 128) for _, s in qs])
+    return qa, sfa, qb, sfb
+
+
+@pytest.mark.parametrize("alignment", [128, 256])
+@pytest.mark.parametrize("b_fp4", [False, True])
+def test_m_grouped_contiguous(alignment, b_fp4):
+    g, n, k = 5, 1024, 1024
+    dg.set_mk_alignment_for_contiguous_layout(alignment)
+    try:
+        m, actual, aligned, layout = oracle.make_contiguous_layout(g, 200, alignment, actual_ms=[130, 0, 256, 77, 300])
+        a = seeded_bf16((m, k), 20)
+        a[layout < 0] = 0                                           # tests/generators.py:406
+        qa, sfa, qb, sfb = _grouped_inputs(g, n, k, a, b_fp4)
+        gk = 32 if b_fp4 else 128
+        ref = oracle.m_grouped_contiguous_ref(qa, sfa, qb, sfb, aligned, 128, gk, b_fp4)
+        d = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+        dg.reset_kernel_status()
+        dg.m_grouped_fp8_fp4_gemm_nt_contiguous((fp8_cuda(qa), packed_sf_cuda(sfa)),
+                                                (fp4_cuda(qb) if b_fp4 else fp8_cuda(qb), packed_sf_cuda(sfb)), d,
+                                                torch.from_numpy(layout).cuda(), recipe_a=(1, 128), recipe_b=(1, gk))
+        assert dg.kernel_status() == 0
+        out = d.float().cpu().numpy()
+        assert not np.isnan(out).any()
+        valid = layout >= 0
+        assert oracle.calc_diff(out[valid], ref[valid]) < MAX_DIFF, diff_report(out, ref)
+        assert oracle.calc_diff(out[valid], oracle.bf16_round(ref[valid])) < 1e-5
+        assert (out[~valid] == 0).all()                             # zero A padding gives zero D padding
+    finally:
+        dg.set_mk_alignment_for_contiguous_layout(128)
+
+
+# ---------------------------------------------------------------------------------------------------
+# m-grouped masked
+# ---------------------------------------------------------------------------------------------------
+def _masked_case(counts, max_m, n, k):
+    g = len(counts)
+    a = seeded_bf16((g, max_m, k), 30)
+    b = seeded_bf16((g, n, k), 31)
+    qa = np.stack([oracle.per_token_cast_to_fp8(a[i], True, 128)[0] for i in range(g)])
+    sfa = np.stack([oracle.per_token_cast_to_fp8(a[i], True, 128)[1] for i in range(g)])
+    for i, c in enumerate(counts):
+        sfa[i, c:] = 0                                              # tests/generators.py:475-478
+    qs = [oracle.per_block_cast_to_fp8(b[i], True) for i in range(g)]
+    qb = np.stack([q for q, _ in qs])
+    sfb = np.stack([oracle.broadcast_sf_along_mn(s, n, 128) for _, s in qs])
+    return qa, sfa, qb, sfb
+
+
+SENTINEL = -7.0
+
+
+def test_m_grouped_masked_leaves_rows_beyond_masked_m_untouched():
+    counts, max_m, n, k = (45, 83, 0, 256, 129, 1), 256, 1000 // 8 * 8, 1024
+    qa, sfa, qb, sfb = _masked_case(counts, max_m, n, k)
+    ref = oracle.m_grouped_masked_ref(qa, sfa, qb, sfb, counts)
+    d = torch.full((len(counts), max_m, n), SENTINEL, dtype=torch.bfloat16, device="cuda")
+    dg.reset_kernel_status()
+    dg.m_grouped_fp8_gemm_nt_masked((fp8_cuda(qa), packed_sf_cuda(sfa)), (fp8_cuda(qb), packed_sf_cuda(sfb)), d,
+                                    torch.tensor(counts, dtype=torch.int, device="cuda"), 64, recipe=(1, 1, 128))
+    assert dg.kernel_status() == 0
+    out = d.float().cpu().numpy()
+    valid = ~np.isnan(ref)
+    assert oracle.calc_diff(out[valid], ref[valid]) < MAX_DIFF
+    assert oracle.calc_diff(out[valid], oracle.bf16_round(ref[valid])) < 1e-5
+    assert (out[~valid] == SENTINEL).all()                          # bit-unchanged sentinel
+
+
+def test_m_grouped_masked_in_a_cuda_graph_follows_new_counts():
+    max_m, n, k = 256, 512, 512
+    counts_a, counts_b = (64, 200, 3, 0), (130, 0, 256, 17)
+    qa, sfa, qb, sfb = _masked_case((max_m,) * 4, max_m, n, k)      # scales valid for every row
+    a = (fp8_cuda(qa), packed_sf_cuda(sfa)); b = (fp8_cuda(qb), packed_sf_cuda(sfb))
+    masked = torch.tensor(counts_a, dtype=torch.int, device="cuda")
+    d = torch.full((4, max_m, n), SENTINEL, dtype=torch.bfloat16, device="cuda")
+    dg.m_grouped_fp8_gemm_nt_masked(a, b, d, masked, 64, recipe=(1, 1, 128))     # warm the kernel cache
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            dg.m_grouped_fp8_gemm_nt_masked(a, b, d, masked, 64, recipe=(1, 1, 128))
+    for counts in (counts_a, counts_b):
+        masked.copy_(torch.tensor(counts, dtype=torch.int))
+        d.fill_(SENTINEL)
+        dg.reset_kernel_status()
+        graph.replay()
+        assert dg.kernel_status() == 0
+        ref = oracle.m_grouped_masked_ref(qa, sfa, qb, sfb, counts)
+        out = d.float().cpu().numpy()
+        valid = ~np.isnan(ref)
+        assert oracle.calc_diff(out[valid], ref[valid]) < 1e-5
+        assert (out[~valid] == SENTINEL).all()
+
+
+# ---------------------------------------------------------------------------------------------------
+# scale layout kernels and quantisation helpers
+# ---------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("mn,k,groups,gran_k", [(4096, 128, 1, 128), (4097, 7168, 1, 128), (4097, 7296, 2, 32),
+                                                (8192, 7296, 4, 128), (130, 96, 3, 32), (4096, 1211 * 32, 1, 32)])
+@pytest.mark.parametrize("mn_major_input", [False, True])
+def test_packed_scale_layout_matches_oracle_bits_and_strides(mn, k, groups, gran_k, mn_major_input):
+    """tests/test_layout.py:45-60 and tests/generators.py:276-290: values, shape and strides."""
+    rng = np.random.default_rng(mn + k)
+    sf_k = -(-k // gran_k)
+    shape = (groups, mn, sf_k) if groups > 1 else (mn, sf_k)
+    sf = np.exp2(rng.integers(-30, 30, size=shape)).astype(np.float32)
+    t = torch.from_numpy(sf).cuda()
+    if mn_major_input:
+        t = t.transpose(-1, -2).contiguous().transpose(-1, -2)
+    dg.reset_kernel_status()
+    got = dg.get_mn_major_tma_aligned_packed_ue8m0_tensor(t)
+    assert dg.kernel_status() == 0
+    want, strides = oracle.mn_major_tma_aligned_packed_ue8m0(sf)
+    assert got.dtype == torch.int and tuple(got.shape) == want.shape and tuple(got.stride()) == tuple(strides)
+    assert np.array_equal(got.cpu().numpy(), want)
+    assert not (got.contiguous().view(torch.uint8) == 0xFF).any()
+    # the GEMM entry points accept it as pre-transformed (int32) scales
+    chk = dg.transform_sf_into_required_layout(got, mn, k, (1, gran_k), groups if groups > 1 else None)
+    assert chk.data_ptr() == got.data_ptr()
+
+
+def test_transform_broadcasts_coarse_mn_granularity_and_rejects_bad_recipes():
+    n, k = 2112, 7168
+    sf = np.exp2(np.random.default_rng(0).integers(-10, 10, size=(-(-n // 128), k // 128))).astype(np.float32)
+    got = dg.transform_sf_into_required_layout(torch.from_numpy(sf).cuda(), n, k, (1, 128, 128), is_sfa=False)
+    want, strides = oracle.mn_major_tma_aligned_packed_ue8m0(oracle.broadcast_sf_along_mn(sf, n, 128))
+    assert np.array_equal(got.cpu().numpy(), want) and tuple(got.stride()) == tuple(strides)
+    with pytest.raises(RuntimeError, match="is_sfa"):
+        dg.transform_sf_into_required_layout(torch.from_numpy(sf).cuda(), n, k, (1, 128, 128))
+    with pytest.raises(RuntimeError, match="is_sfa"):
+        dg.transform_sf_into_required_layout(torch.from_numpy(sf).cuda(), n, k, (128, 128), is_sfa=False)
+    with pytest.raises(RuntimeError, match="Assertion error"):
+        dg.transform_sf_into_required_layout(torch.from_numpy(sf).cuda(), n + 128, k, (128, 128))
+    with pytest.raises(RuntimeError):                                # int32 scales must already be per row
+        dg.transform_sf_into_required_layout(got, n, k, (128, 128))
+
+
+def test_fp32_mn_major_transpose():
+    sf = np.random.default_rng(1).standard_normal((3, 4097, 57)).astype(np.float32)
+    got = dg.get_mn_major_tma_aligned_tensor(torch.from_numpy(sf).cuda())
+    want, strides = oracle.mn_major_tma_aligned_fp32(sf)
+    assert tuple(got.stride()) == tuple(strides) and np.array_equal(got.cpu().numpy(), want)
+    again = dg.get_mn_major_tma_aligned_tensor(got)
+    assert again.data_ptr() == got.data_ptr()                        # already in the required layout
+
+
+def test_torch_quantisers_match_oracle():
+    from deepgemm_amd_b200.utils import per_block_cast_to_fp8, per_token_cast_to_fp4, per_token_cast_to_fp8
+    x = seeded_bf16((200, 300), 40)
+    x[0] = 0
+    x[1, :4] = [1e-6, -3e-5, 448.0, -448.0]
+    x = oracle.bf16_round(x)
+    xt = torch.from_numpy(x).cuda().bfloat16()
+    for gran_k in (32, 128):
+        q, sf = per_token_cast_to_fp8(xt, True, gran_k)
+        oq, osf = oracle.per_token_cast_to_fp8(x, True, gran_k)
+        assert np.array_equal(q.view(torch.uint8).cpu().numpy(), oq) and np.array_equal(sf.cpu().numpy(), osf)
+        q4, sf4 = per_token_cast_to_fp4(xt, True, gran_k)
+        oq4, osf4 = oracle.per_token_cast_to_fp4(x, True, gran_k)
+        assert np.array_equal(q4.cpu().numpy(), oq4) and np.array_equal(sf4.cpu().numpy(), osf4)
+        _, psf = per_token_cast_to_fp8(xt, True, gran_k, use_packed_ue8m0=True)
+        assert np.array_equal(psf.cpu().numpy(), oracle.per_token_cast_to_fp8(x, True, gran_k, True)[1])
+    qb, sfb = per_block_cast_to_fp8(xt, True)
+    oqb, osfb = oracle.per_block_cast_to_fp8(x, True)
+    assert np.array_equal(qb.view(torch.uint8).cpu().numpy(), oqb) and np.array_equal(sfb.cpu().numpy(), osfb)
+
+
+# ---------------------------------------------------------------------------------------------------
+# API behaviour
+# ---------------------------------------------------------------------------------------------------
+def test_api_rejects_what_the_reference_rejects():
+    m, n, k = 128, 256, 256
+    qa, sfa, qb, sfb, _ = quantise_dense(seeded_bf16((m, k), 50), seeded_bf16((n, k), 51))
+    a = (fp8_cuda(qa), packed_sf_cuda(sfa)); b = (fp8_cuda(qb), packed_sf_cuda(sfb))
+    d = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError, match="Assertion error"):
+        dg.fp8_gemm_nt(a, b, torch.empty((m, n + 8), dtype=torch.bfloat16, device="cuda"), recipe=(1, 1, 128))
+    with pytest.raises(RuntimeError, match="Assertion error"):
+        dg.fp8_gemm_nt(a, b, torch.empty((m, n), dtype=torch.half, device="cuda"), recipe=(1, 1, 128))
+    with pytest.raises(RuntimeError, match="Assertion error"):      # both recipe forms
+        dg.fp8_gemm_nt(a, b, d, recipe=(1, 1, 128), recipe_a=(1, 128), recipe_b=(1, 128))
+    with pytest.raises(RuntimeError, match="Assertion error"):      # int32 scales need gran_mn == 1
+        dg.fp8_gemm_nt(a, b, d, recipe=(1, 128, 128))
+    with pytest.raises(RuntimeError, match="Assertion error"):      # column-major D
+        dg.fp8_gemm_nt(a, b, torch.empty((n, m), dtype=torch.bfloat16, device="cuda").T, recipe=(1, 1, 128))
+    # empty problems are no-ops; k == 0 zeroes D (csrc/apis/gemm.hpp:17-53)
+    dg.fp8_gemm_nt((a[0][:0], a[1][:0]), b, d[:0], recipe=(1, 1, 128))
+    dz = torch.ones((m, n), dtype=torch.bfloat16, device="cuda")
+    empty_sf = torch.empty((m, 0), dtype=torch.int, device="cuda")
+    dg.fp8_gemm_nt((a[0][:, :0], empty_sf), (b[0][:, :0], torch.empty((n, 0), dtype=torch.int, device="cuda")), dz, recipe=(1, 1, 128))
+    assert (dz == 0).all()
