@@ -17,7 +17,14 @@
 //
 // The configuration arrives as DG_* macros set by the host-side code generator:
 //   DG_GEMM_TYPE (0 dense, 1 m-grouped contiguous, 2 m-grouped masked), DG_BLOCK_N, DG_NUM_STAGES,
-//   DG_A_FP4, DG_B_FP4, DG_GRAN_K_A, DG_GRAN_K_B, DG_D_FP32, DG_ACCUMULATE, DG_RASTER_GROUP.
+//   DG_CLUSTER, DG_A_FP4, DG_B_FP4, DG_GRAN_K_A, DG_GRAN_K_B, DG_D_FP32, DG_ACCUMULATE, DG_RASTER_GROUP.
+//
+// DG_CLUSTER == 2 pairs two CTAs (a cluster of two SMs) on one 256 x BLOCK_N tile with
+// tcgen05.mma.cta_group::2: each CTA loads its own 128 rows of A and one half of the B tile, CTA 0 issues
+// the MMAs for both, each CTA keeps the accumulator of its own 128 rows in its tensor memory and runs its
+// own epilogue.  B crosses L2 -> shared memory once per pair, and a stage is a third smaller, so the ring is deeper.
+// Barriers that gather arrivals from both CTAs (full, tmem_empty) live in CTA 0; the peer reaches them
+// through their shared::cluster addresses.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -37,6 +44,7 @@ constexpr uint32_t BLOCK_M     = 128;
 constexpr uint32_t BLOCK_N     = DG_BLOCK_N;
 constexpr uint32_t BLOCK_K     = 128;
 constexpr uint32_t kNumStages  = DG_NUM_STAGES;
+constexpr uint32_t kCluster    = DG_CLUSTER;       // CTAs cooperating on one tile (1 or 2)
 constexpr bool     kAIsFP4     = DG_A_FP4 != 0;
 constexpr bool     kBIsFP4     = DG_B_FP4 != 0;
 constexpr uint32_t kGranKA     = DG_GRAN_K_A;
@@ -45,7 +53,9 @@ constexpr bool     kDIsFP32    = DG_D_FP32 != 0;
 constexpr bool     kAccumulate = DG_ACCUMULATE != 0;
 constexpr uint32_t kRasterGroup = DG_RASTER_GROUP;
 
-constexpr uint32_t UMMA_M = 128, UMMA_N = BLOCK_N, UMMA_K = 32;
+constexpr uint32_t UMMA_M = 128 * kCluster, UMMA_N = BLOCK_N, UMMA_K = 32;
+constexpr uint32_t LOAD_BLOCK_N = BLOCK_N / kCluster;      // rows of B each CTA loads
+constexpr uint32_t TILE_M = BLOCK_M * kCluster;            // rows of D per scheduled tile
 constexpr uint32_t kNumThreads = 256, kNumEpilogueThreads = 128, kEpilogueWarpBase = 4;
 constexpr uint32_t kNumAccumStages = 2;
 
@@ -53,6 +63,7 @@ static_assert(BLOCK_N % 16 == 0 && BLOCK_N >= 16 && BLOCK_N <= 240, "UMMA_N must
 static_assert(kGranKA == 32 || kGranKA == 128, "one scale per 32 or 128 elements of K");
 static_assert(kGranKB == 32 || kGranKB == 128, "one scale per 32 or 128 elements of K");
 static_assert(kNumStages >= 2 && kNumStages <= 32, "pipeline depth");
+static_assert(kCluster == 1 || kCluster == 2, "one CTA or a CTA pair per tile");
 
 // Scales: a packed int32 holds 4 scales.  With one scale per 128 K it spans 4 K-blocks, so the
 // chunk is fetched on every 4th K-block; with one per 32 K it spans exactly one K-block.
@@ -64,7 +75,7 @@ constexpr uint32_t SF_BLOCK_N = (BLOCK_N + 127) / 128 * 128;
 // Shared memory and tensor memory maps (every operand stage starts on a 1024-byte boundary, as the
 // 128-byte swizzle requires); the arithmetic lives in gemm_config.hpp, shared with the host heuristics
 constexpr uint32_t kDElemBytes = kDIsFP32 ? 4 : 2;
-constexpr GemmLayout kLayout{BLOCK_M, BLOCK_N, BLOCK_K, kNumStages, kDElemBytes};
+constexpr GemmLayout kLayout{BLOCK_M, BLOCK_N, BLOCK_K, kNumStages, kDElemBytes, kCluster};
 constexpr uint32_t kStoreRowBytes   = kLayout.store_row_bytes();
 constexpr uint32_t kStoreCols       = kLayout.store_cols();          // columns of D per TMA store
 constexpr uint32_t kNumStores       = kLayout.num_stores();
@@ -86,8 +97,9 @@ static_assert(kBBytes % 1024 == 0, "B stage must keep 1024-byte alignment");
 static_assert(kSmemTotal <= kSmemCapacity, "shared memory budget exceeded");
 static_assert(kStoreCols % 16 == 0 || kDIsFP32, "a store covers whole 16-column tensor-memory loads");
 
-// Bytes the TMA engine reports per stage (packed FP4 counts its global-memory bytes)
-constexpr uint32_t kTxBytesAB = kABytes / (kAIsFP4 ? 2 : 1) + kBBytes / (kBIsFP4 ? 2 : 1);
+// Bytes the TMA engine reports per stage, summed over the CTAs of the cluster (packed FP4 counts its
+// global-memory bytes)
+constexpr uint32_t kTxBytesAB = kCluster * (kABytes / (kAIsFP4 ? 2 : 1) + kBBytes / (kBIsFP4 ? 2 : 1));
 
 constexpr uint32_t kTmemColSFA = kLayout.tmem_col_sfa();
 constexpr uint32_t kTmemColSFB = kLayout.tmem_col_sfb();
@@ -106,7 +118,24 @@ struct GemmParams {
     uint32_t num_groups;
     uint32_t ldd;                // row pitch of D in elements
     float alpha;
+    unsigned long long* profile; // optional cycle counters (kernels built with DG_PROFILE only), else null
 };
+
+// Wait-time accounting for tuning: with DG_PROFILE defined every role adds the cycles it spent inside each
+// of its waits, and in its whole loop, to profile[slot]; without it the calls compile to nothing.
+enum ProfileSlot : uint32_t {
+    kProfProducerWaitEmpty = 0, kProfProducerTotal = 1, kProfMmaWaitFull = 2, kProfMmaWaitTmemEmpty = 3, kProfMmaTotal = 4,
+    kProfSFWait = 5, kProfSFTotal = 6, kProfEpiWaitTmemFull = 7, kProfEpiTotal = 8, kProfEpiStoreWait = 9, kProfNumSlots = 16
+};
+#if defined(DG_PROFILE) && DG_PROFILE
+#define DG_PROF_BEGIN(var) const long long var = clock64()
+#define DG_PROF_ADD(acc, var) acc += clock64() - var
+#define DG_PROF_FLUSH(slot, acc) do { if (p.profile != nullptr) atomicAdd(p.profile + (slot), static_cast<unsigned long long>(acc)); } while (0)
+#else
+#define DG_PROF_BEGIN(var) do { } while (0)
+#define DG_PROF_ADD(acc, var) do { } while (0)
+#define DG_PROF_FLUSH(slot, acc) do { } while (0)
+#endif
 
 }  // namespace dg
 
@@ -123,12 +152,16 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
     const uint32_t warp_idx = __shfl_sync(0xFFFFFFFFu, threadIdx.x / 32, 0);
     const uint32_t lane = lane_id();
     const uint32_t smem_base = smem_u32(smem);
+    const uint32_t cta_rank = kCluster == 1 ? 0u : cluster_ctarank();
+    const bool is_leader = cta_rank == 0;
 
     auto full_bar     = [&](uint32_t s) { return smem_base + kSmemBar + s * 8; };
     auto sf_full_bar  = [&](uint32_t s) { return smem_base + kSmemBar + (kNumStages + s) * 8; };
     auto empty_bar    = [&](uint32_t s) { return smem_base + kSmemBar + (2 * kNumStages + s) * 8; };
     auto tmem_full_bar  = [&](uint32_t a) { return smem_base + kSmemBar + (3 * kNumStages + a) * 8; };
     auto tmem_empty_bar = [&](uint32_t a) { return smem_base + kSmemBar + (3 * kNumStages + kNumAccumStages + a) * 8; };
+    // shared::cluster address of a barrier of CTA 0 (the local address when there is no cluster)
+    auto in_leader = [&](uint32_t bar) { return kCluster == 1 ? bar : map_to_cta(bar, 0); };
     volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(smem + kSmemMisc);
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + kSmemMisc + 4);
     const AbortCtx ctx{abort_flag, p.status};
@@ -144,21 +177,35 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
     }
     if (warp_idx == 1 && lane == 0) {
         for (uint32_t s = 0; s < kNumStages; ++s) {
-            mbar_init(full_bar(s), 1 + 32);      // producer's expect_tx arrive + the 32 lanes of the scale warp
+            // per CTA of the cluster: the producer's arrive + the 32 lanes of the scale warp (used in CTA 0 only)
+            mbar_init(full_bar(s), kCluster * (1 + 32));
             mbar_init(sf_full_bar(s), 1);
             mbar_init(empty_bar(s), 1);          // tcgen05.commit
         }
         for (uint32_t a = 0; a < kNumAccumStages; ++a) {
             mbar_init(tmem_full_bar(a), 1);      // tcgen05.commit
-            mbar_init(tmem_empty_bar(a), kNumEpilogueThreads);
+            mbar_init(tmem_empty_bar(a), kCluster * kNumEpilogueThreads);   // used in CTA 0 only
         }
         fence_mbar_init();
-    } else if (warp_idx == 2) {
-        tmem_alloc<1>(smem_u32(const_cast<uint32_t*>(tmem_base_slot)), kTmemCols);
-        tmem_relinquish<1>();
+    }
+    __syncwarp();
+    if constexpr (kCluster > 1) {
+        // Both CTAs must be resident before the paired tensor-memory allocation
+        cluster_arrive_relaxed();
+        cluster_wait();
+    }
+    if (warp_idx == 2) {
+        tmem_alloc<kCluster>(smem_u32(const_cast<uint32_t*>(tmem_base_slot)), kTmemCols);
+        tmem_relinquish<kCluster>();
     }
     tc_fence_before_sync();
-    __syncthreads();
+    if constexpr (kCluster > 1) {
+        // Barriers of both CTAs are initialised before either CTA signals the other
+        cluster_arrive();
+        cluster_wait();
+    } else {
+        __syncthreads();
+    }
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_base_slot;
 
@@ -166,8 +213,9 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
     const uint32_t sfa_rows_per_group = (p.shape_k + kGranKA * 4 - 1) / (kGranKA * 4);   // packed K extent of SFA
     const uint32_t sfb_rows_per_group = (p.shape_k + kGranKB * 4 - 1) / (kGranKB * 4);
 
-    TileScheduler<kGemmType> sched(BLOCK_M, BLOCK_N, kRasterGroup, p.shape_m, p.shape_n, p.num_groups, p.grouped_layout,
-                                   blockIdx.x, gridDim.x);
+    // A cluster walks the tile list as one unit
+    TileScheduler<kGemmType> sched(TILE_M, BLOCK_N, kRasterGroup, p.shape_m, p.shape_n, p.num_groups, p.grouped_layout,
+                                   blockIdx.x / kCluster, gridDim.x / kCluster);
     Tile tile;
     uint32_t stage = 0, phase = 0;
     auto advance_stage = [&]() {
@@ -176,18 +224,22 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
     };
 
     if (warp_idx == 0) {
-        // ================= TMA producer =================
+        // ================= TMA producer (every CTA loads its own rows of A and its share of B) =================
         if (lane == 0) {
             bool ok = true;
+            long long prof_wait = 0; (void)prof_wait;
+            DG_PROF_BEGIN(prof_t0);
             while (ok && sched.next(tile)) {
-                // Row coordinates of this tile in the 2-D views of A, B and the scale tensors
-                const uint32_t a_row = tile.a_row_base + tile.m_block * BLOCK_M;
-                const uint32_t b_row = tile.group * p.shape_n + tile.n_block * BLOCK_N;
-                const uint32_t sfa_mn = tile.sfa_mn_base + tile.m_block * BLOCK_M;
+                // Row coordinates of this CTA's part of the tile in the 2-D views of A, B and the scale tensors
+                const uint32_t a_row = tile.a_row_base + tile.m_block * TILE_M + cta_rank * BLOCK_M;
+                const uint32_t b_row = tile.group * p.shape_n + tile.n_block * BLOCK_N + cta_rank * LOAD_BLOCK_N;
+                const uint32_t sfa_mn = tile.sfa_mn_base + tile.m_block * TILE_M + cta_rank * BLOCK_M;
                 const uint32_t sfa_row0 = tile.sfa_group * sfa_rows_per_group;
                 const uint32_t sfb_row0 = tile.group * sfb_rows_per_group;
                 for (uint32_t kb = 0; kb < num_k_blocks; ++kb, advance_stage()) {
+                    DG_PROF_BEGIN(prof_w);
                     if (!mbar_wait(empty_bar(stage), phase ^ 1, ctx, kRoleProducer, 1)) { ok = false; break; }
+                    DG_PROF_ADD(prof_wait, prof_w);
                     uint32_t sf_bytes = 0;
                     if (kb % kSFAPeriod == 0) sf_bytes += kSFABytes;
                     if (kb % kSFBPeriod == 0) sf_bytes += kSFBBytes;
@@ -198,39 +250,69 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                     if (kb % kSFBPeriod == 0)
                         tma_load_2d(smem_base + kSmemSFB + stage * kSFBBytes, &tm_sfb, sf_full_bar(stage),
                                     static_cast<int32_t>(tile.n_block * BLOCK_N), static_cast<int32_t>(sfb_row0 + kb / kSFBPeriod));
-                    mbar_arrive_expect_tx(full_bar(stage), kTxBytesAB);
-                    tma_load_2d(smem_base + kSmemA + stage * kABytes, &tm_a, full_bar(stage),
-                                static_cast<int32_t>(kb * BLOCK_K), static_cast<int32_t>(a_row));
-                    tma_load_2d(smem_base + kSmemB + stage * kBBytes, &tm_b, full_bar(stage),
-                                static_cast<int32_t>(kb * BLOCK_K), static_cast<int32_t>(b_row));
+                    if constexpr (kCluster == 1) {
+                        mbar_arrive_expect_tx(full_bar(stage), kTxBytesAB);
+                        tma_load_2d(smem_base + kSmemA + stage * kABytes, &tm_a, full_bar(stage),
+                                    static_cast<int32_t>(kb * BLOCK_K), static_cast<int32_t>(a_row));
+                        tma_load_2d(smem_base + kSmemB + stage * kBBytes, &tm_b, full_bar(stage),
+                                    static_cast<int32_t>(kb * BLOCK_K), static_cast<int32_t>(b_row));
+                    } else {
+                        // The copies land in this CTA; their bytes are counted on CTA 0's barrier, which expects both CTAs' bytes
+                        const uint32_t leader_full = in_leader(full_bar(stage));
+                        if (is_leader) mbar_arrive_expect_tx(full_bar(stage), kTxBytesAB);
+                        else mbar_arrive_cluster(leader_full);
+                        tma_load_2d_2cta(smem_base + kSmemA + stage * kABytes, &tm_a, leader_full,
+                                         static_cast<int32_t>(kb * BLOCK_K), static_cast<int32_t>(a_row));
+                        tma_load_2d_2cta(smem_base + kSmemB + stage * kBBytes, &tm_b, leader_full,
+                                         static_cast<int32_t>(kb * BLOCK_K), static_cast<int32_t>(b_row));
+                    }
                 }
             }
+            long long prof_total = 0; (void)prof_total;
+            DG_PROF_ADD(prof_total, prof_t0);
+            DG_PROF_FLUSH(kProfProducerWaitEmpty, prof_wait);
+            DG_PROF_FLUSH(kProfProducerTotal, prof_total);
         }
     } else if (warp_idx == 1) {
-        // ================= MMA issuer =================
-        if (lane == 0) {
+        // ================= MMA issuer (CTA 0 of the cluster only) =================
+        if (lane == 0 && is_leader) {
             constexpr uint32_t idesc = make_instr_desc_block_scaled(kAIsFP4 ? kFmtE2M1 : kFmtE4M3, kBIsFP4 ? kFmtE2M1 : kFmtE4M3,
                                                                     0, 0, UMMA_M, UMMA_N);
+            // A commit reaches the barrier at the same offset in every CTA of the cluster
+            auto commit_all = [&](uint32_t bar) {
+                if constexpr (kCluster == 1) {
+                    tc_commit(bar);
+                } else {
+                    tc_commit_2cta(map_to_cta(bar, 0));
+                    tc_commit_2cta(map_to_cta(bar, 1));
+                }
+            };
             bool ok = true;
             uint32_t tile_iter = 0;
+            long long prof_full = 0, prof_tmem = 0; (void)prof_full; (void)prof_tmem;
+            DG_PROF_BEGIN(prof_t0);
             while (ok && sched.next(tile)) {
                 const uint32_t accum = tile_iter & 1, accum_phase = (tile_iter >> 1) & 1;
                 ++tile_iter;
+                DG_PROF_BEGIN(prof_w0);
                 if (!mbar_wait(tmem_empty_bar(accum), accum_phase ^ 1, ctx, kRoleMma, 1)) { ok = false; break; }
+                DG_PROF_ADD(prof_tmem, prof_w0);
                 tc_fence_after_sync();
                 const uint32_t tmem_d = tmem_base + accum * UMMA_N;
                 for (uint32_t kb = 0; kb < num_k_blocks; ++kb, advance_stage()) {
+                    DG_PROF_BEGIN(prof_w1);
                     if (!mbar_wait(full_bar(stage), phase, ctx, kRoleMma, 2)) { ok = false; break; }
+                    DG_PROF_ADD(prof_full, prof_w1);
                     tc_fence_after_sync();
-                    // Scales: shared memory (rearranged by warp 2) -> tensor memory
+                    // Scales: shared memory (rearranged by warp 2) -> tensor memory, in every CTA of the cluster
                     if (kb % kSFAPeriod == 0)
-                        tc_cp_32x128b_warpx4<1>(tmem_base + kTmemColSFA,
-                                                make_smem_desc(smem_base + kSmemSFA + stage * kSFABytes, 0, 128, kSwizzleNone));
+                        tc_cp_32x128b_warpx4<kCluster>(tmem_base + kTmemColSFA,
+                                                       make_smem_desc(smem_base + kSmemSFA + stage * kSFABytes, 0, 128, kSwizzleNone));
                     if (kb % kSFBPeriod == 0) {
                         #pragma unroll
                         for (uint32_t i = 0; i < SF_BLOCK_N / 128; ++i)
-                            tc_cp_32x128b_warpx4<1>(tmem_base + kTmemColSFB + i * 4,
-                                                    make_smem_desc(smem_base + kSmemSFB + stage * kSFBBytes + i * 512, 0, 128, kSwizzleNone));
+                            tc_cp_32x128b_warpx4<kCluster>(tmem_base + kTmemColSFB + i * 4,
+                                                           make_smem_desc(smem_base + kSmemSFB + stage * kSFBBytes + i * 512, 0, 128, kSwizzleNone));
                     }
                     const uint64_t a_desc = make_smem_desc(smem_base + kSmemA + stage * kABytes, 0, 1024, kSwizzle128B);
                     const uint64_t b_desc = make_smem_desc(smem_base + kSmemB + stage * kBBytes, 0, 1024, kSwizzle128B);
@@ -240,15 +322,20 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                         const uint32_t sfa_id = kGranKA == 32 ? j : (kb % 4);
                         const uint32_t sfb_id = kGranKB == 32 ? j : (kb % 4);
                         // Advancing K by 32 bytes inside the 128-byte swizzle atom = +2 in the (>>4) address field
-                        tc_mma_mxf8f6f4<1>(tmem_d, a_desc + j * (UMMA_K >> 4), b_desc + j * (UMMA_K >> 4),
-                                           instr_desc_with_sf_ids(idesc, sfa_id, sfb_id),
-                                           tmem_base + kTmemColSFA, tmem_base + kTmemColSFB, (kb | j) != 0);
+                        tc_mma_mxf8f6f4<kCluster>(tmem_d, a_desc + j * (UMMA_K >> 4), b_desc + j * (UMMA_K >> 4),
+                                                  instr_desc_with_sf_ids(idesc, sfa_id, sfb_id),
+                                                  tmem_base + kTmemColSFA, tmem_base + kTmemColSFB, (kb | j) != 0);
                     }
-                    tc_commit(empty_bar(stage));                       // releases the stage once its MMAs have read it
+                    commit_all(empty_bar(stage));                      // releases the stage once its MMAs have read it
                     if (kb + 1 == num_k_blocks)
-                        tc_commit(tmem_full_bar(accum));               // accumulator complete
+                        commit_all(tmem_full_bar(accum));              // accumulator complete
                 }
             }
+            long long prof_total = 0; (void)prof_total;
+            DG_PROF_ADD(prof_total, prof_t0);
+            DG_PROF_FLUSH(kProfMmaWaitFull, prof_full);
+            DG_PROF_FLUSH(kProfMmaWaitTmemEmpty, prof_tmem);
+            DG_PROF_FLUSH(kProfMmaTotal, prof_total);
         }
     } else if (warp_idx == 2) {
         // ================= scale rearrangement =================
@@ -263,9 +350,13 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
             st_shared_v4(chunk_addr + lane * 16, v[0], v[1], v[2], v[3]);
         };
         bool ok = true;
+        long long prof_wait = 0; (void)prof_wait;
+        DG_PROF_BEGIN(prof_t0);
         while (ok && sched.next(tile)) {
             for (uint32_t kb = 0; kb < num_k_blocks; ++kb, advance_stage()) {
+                DG_PROF_BEGIN(prof_w);
                 if (!mbar_wait(sf_full_bar(stage), phase, ctx, kRoleSF, 1)) { ok = false; break; }
+                DG_PROF_ADD(prof_wait, prof_w);
                 if (kb % kSFAPeriod == 0)
                     rearrange(smem_base + kSmemSFA + stage * kSFABytes);
                 if (kb % kSFBPeriod == 0) {
@@ -274,26 +365,41 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                         rearrange(smem_base + kSmemSFB + stage * kSFBBytes + i * 512);
                 }
                 fence_proxy_async_smem();
-                mbar_arrive(full_bar(stage));
+                if (kCluster == 1 || is_leader) mbar_arrive(full_bar(stage));
+                else mbar_arrive_cluster(in_leader(full_bar(stage)));
             }
         }
+        if (lane == 0) {
+            long long prof_total = 0; (void)prof_total;
+            DG_PROF_ADD(prof_total, prof_t0);
+            DG_PROF_FLUSH(kProfSFWait, prof_wait);
+            DG_PROF_FLUSH(kProfSFTotal, prof_total);
+        }
     } else if (warp_idx >= kEpilogueWarpBase) {
-        // ================= epilogue =================
+        // ================= epilogue (every CTA drains the accumulator of its own 128 rows) =================
         const uint32_t quarter = warp_idx - kEpilogueWarpBase;        // tensor-memory lanes [32q, 32q+32)
         const uint32_t row_in_tile = quarter * 32 + lane;
         const uint32_t epi_tid = threadIdx.x - kEpilogueWarpBase * 32;
         bool ok = true;
         uint32_t tile_iter = 0, store_iter = 0;
+        long long prof_wait = 0, prof_store = 0; (void)prof_wait; (void)prof_store;
+        DG_PROF_BEGIN(prof_t0);
         while (ok && sched.next(tile)) {
             const uint32_t accum = tile_iter & 1, accum_phase = (tile_iter >> 1) & 1;
             ++tile_iter;
+            DG_PROF_BEGIN(prof_w);
             if (!mbar_wait(tmem_full_bar(accum), accum_phase, ctx, kRoleEpilogue, 1)) { ok = false; break; }
+            DG_PROF_ADD(prof_wait, prof_w);
             tc_fence_after_sync();
 
-            const uint32_t d_row0 = tile.d_row_base + tile.m_block * BLOCK_M;
+            const uint32_t d_row0 = tile.d_row_base + tile.m_block * TILE_M + cta_rank * BLOCK_M;
             const uint32_t n0 = tile.n_block * BLOCK_N;
             const uint32_t tmem_row_addr = tmem_base + ((quarter * 32) << 16) + accum * UMMA_N;
-            const bool direct = kGemmType == 2 && tile.valid_rows < BLOCK_M;
+            // Rows of this CTA's half that may be written (fewer than 128 only in a ragged tile of the masked layout)
+            const uint32_t rows_before = cta_rank * BLOCK_M;
+            const uint32_t valid_rows = tile.valid_rows <= rows_before ? 0u :
+                                        (tile.valid_rows - rows_before < BLOCK_M ? tile.valid_rows - rows_before : BLOCK_M);
+            const bool direct = kGemmType == 2 && valid_rows < BLOCK_M;
 
             #pragma unroll 1
             for (uint32_t s = 0; s < kNumStores; ++s) {
@@ -306,7 +412,8 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                 if (s + 1 == kNumStores) {
                     // The accumulator is in registers: hand the tensor-memory stage back to the MMA warp
                     tc_fence_before_sync();
-                    mbar_arrive(tmem_empty_bar(accum));
+                    if (kCluster == 1 || is_leader) mbar_arrive(tmem_empty_bar(accum));
+                    else mbar_arrive_cluster(in_leader(tmem_empty_bar(accum)));
                 }
                 #pragma unroll
                 for (uint32_t l = 0; l < kLoadsPerStore; ++l)
@@ -318,8 +425,10 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                     const uint32_t sb = store_iter & 1;
                     ++store_iter;
                     // The staging buffer is free once the TMA store issued two stores ago has read it
+                    DG_PROF_BEGIN(prof_s);
                     if (epi_tid == 0) tma_store_wait_read<kNumStoreStages - 1>();
                     named_barrier_sync(1, kNumEpilogueThreads);
+                    DG_PROF_ADD(prof_store, prof_s);
                     const uint32_t stage_addr = smem_base + kSmemD + sb * kStoreStageBytes;
                     const uint32_t row_off = row_in_tile * kStoreRowBytes;
                     constexpr uint32_t kSwizzleMask = kStoreRowBytes == 128 ? 7 : (kStoreRowBytes == 64 ? 3 : 1);
@@ -355,7 +464,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                     }
                 } else {
                     // Ragged tile of the masked layout: rows at or beyond the group's row count stay untouched
-                    if (row_in_tile < tile.valid_rows) {
+                    if (row_in_tile < valid_rows) {
                         const uint32_t col0 = n0 + s * kStoreCols;
                         if constexpr (!kDIsFP32) {
                             __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.d) +
@@ -385,6 +494,13 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                 }
             }
         }
+        if (epi_tid == 0) {
+            long long prof_total = 0; (void)prof_total;
+            DG_PROF_ADD(prof_total, prof_t0);
+            DG_PROF_FLUSH(kProfEpiWaitTmemFull, prof_wait);
+            DG_PROF_FLUSH(kProfEpiStoreWait, prof_store);
+            DG_PROF_FLUSH(kProfEpiTotal, prof_total);
+        }
         // Every byte of D must be in global memory before the grid completes
         if (epi_tid == 0) tma_store_wait<0>();
     }
@@ -397,8 +513,14 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
         while (global_timer_ns() - t0 < 200000) { }
         __syncthreads();
     }
+    if constexpr (kCluster > 1) {
+        // Neither CTA may exit (or free tensor memory) while its peer can still signal its barriers
+        tc_fence_before_sync();
+        cluster_arrive();
+        cluster_wait();
+    }
     if (warp_idx == 2) {
         tc_fence_after_sync();
-        tmem_dealloc<1>(tmem_base, kTmemCols);
+        tmem_dealloc<kCluster>(tmem_base, kTmemCols);
     }
 }

@@ -97,8 +97,11 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 }
 
 // Arrive on a barrier that lives in another CTA of the cluster (address from map_to_cta).
+// Default (release, CTA scope) semantics on purpose: what crosses CTAs here is only "my asynchronous copies
+// were issued / my tensor-memory reads are done"; the data itself moves through the async proxy.  Cluster-scope
+// release/acquire on these barriers halved the MMA issue rate when measured.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" :: "r"(cluster_bar) : "memory");
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" :: "r"(cluster_bar) : "memory");
 }
 
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
@@ -115,22 +118,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Same, but acquiring at cluster scope (the arrivals may come from the peer CTA).
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-
 // Bounded wait.  Returns false if this CTA is unwinding (another role failed) or the wait ran out.
-template <bool kClusterScope = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const AbortCtx& ctx,
                                           uint32_t role, uint32_t site) {
-    auto poll = [&]() { return kClusterScope ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity); };
+    auto poll = [&]() { return mbar_try_wait(bar, parity); };
     #pragma unroll 1
     for (int i = 0; i < 64; ++i)
         if (poll()) return true;

@@ -21,7 +21,15 @@ struct GemmParams {
     int* status;
     uint32_t shape_m, shape_n, shape_k, num_groups, ldd;
     float alpha;
+    unsigned long long* profile;
 };
+
+// Tuning aid (DG_PROFILE=1): a device buffer of per-role wait-cycle counters, printed after every launch
+unsigned long long* profile_buffer() {
+    static unsigned long long* buf = nullptr;
+    if (buf == nullptr && cudaMalloc(reinterpret_cast<void**>(&buf), 16 * sizeof(unsigned long long)) != cudaSuccess) buf = nullptr;
+    return buf;
+}
 
 struct Problem {
     int kind;
@@ -95,43 +103,59 @@ int validate(int kind, const dg_gemm_args_t* a, bool need_pointers, Problem* p) 
 }
 
 // ---- heuristics ------------------------------------------------------------------------------------
-// Tiles are 128 x block_n x 128 per CTA with block_n in 16..240.  The choice minimises a cycle model of
-// the whole launch:  waves x (k_blocks x max(MMA, shared-memory feed, L2 feed) + per-tile epilogue).
-// Constants are per-SM, per-clock figures of B200: 8192 FP8 MACs, 128 B of shared memory, and a
-// measured ~64 B from L2.
+// A CTA works on 128 x block_n x 128 sub-tiles with block_n in 16..240; with cluster_size 2 a CTA pair
+// shares one 256 x block_n tile (tcgen05 cta_group::2) and each CTA loads only half of the B tile.
+// The choice minimises a cycle model of the whole launch:
+//     waves x (k_blocks x max(MMA, shared-memory feed, L2 feed)) + exposed epilogue + launch
+// with per-SM, per-clock figures of B200: 8192 FP8 MACs, 128 B out of shared memory, and ~67 B from L2 into
+// shared memory (the rate measured on this kernel's own loads: 1-CTA tiles of any width ran at that feed rate).
+// The CTA-pair variant is built and tested, but under B200's power cap it measured no faster than one CTA per
+// tile (2.15 vs 2.22 PFLOP/s sustained at M = N = 4096, K = 7168), so it is used only on request (DG_FORCE_CLUSTER=2).
+bool cluster_allowed(const Problem&, int cluster) { return cluster == 1; }
+
 int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
     const int num_sms = dg_get_num_sms();
     const int d_elem = p.d_fp32 ? 4 : 2;
     const int64_t k_blocks = ceil_div(p.k, 128);
-    int64_t m_blocks;
-    if (p.kind == DG_GEMM_M_GROUPED_MASKED)
-        m_blocks = static_cast<int64_t>(p.groups) * ceil_div(std::min(std::max(p.expected_m, 1), p.m), 128);
-    else
-        m_blocks = ceil_div(p.m, 128);
+    const int forced_bn = env_int("FORCE_BLOCK_N"), forced_cluster = env_int("FORCE_CLUSTER");
 
     double best_cost = 0;
-    int best_bn = 0;
-    const int forced_bn = env_int("FORCE_BLOCK_N");
-    for (int bn = 16; bn <= 240; bn += 16) {
-        if (forced_bn && bn != forced_bn) continue;
-        const int64_t tiles = m_blocks * ceil_div(p.n, bn);
-        const int64_t waves = ceil_div<int64_t>(tiles, num_sms);
-        const double mma = 2.0 * bn;
-        const double smem_feed = 128.0 + bn;
-        const double l2_feed = (16384.0 + 128.0 * bn) / 64.0;
-        const GemmLayout lay{128, static_cast<uint32_t>(bn), 128, 2, static_cast<uint32_t>(d_elem)};
-        const double epilogue = 300.0 + 40.0 * lay.num_stores() + bn * 2.0;
-        // The epilogue of a tile overlaps the next tile's main loop; it is exposed once per CTA
-        const double per_tile = static_cast<double>(k_blocks) * std::max(mma, std::max(smem_feed, l2_feed));
-        const double cost = static_cast<double>(waves) * std::max(per_tile, epilogue) + epilogue + 2000.0;
-        if (best_bn == 0 || cost < best_cost - 1e-9 || (std::abs(cost - best_cost) <= 1e-9 && bn > best_bn)) {
-            best_cost = cost;
-            best_bn = bn;
+    int best_bn = 0, best_cluster = 1;
+    int64_t best_tiles = 0;
+    for (int cluster = 1; cluster <= 2; ++cluster) {
+        if (forced_cluster ? cluster != forced_cluster : !cluster_allowed(p, cluster)) continue;
+        if (cluster == 2 && (num_sms % 2 != 0 || (p.kind == DG_GEMM_M_GROUPED_CONTIGUOUS && p.m % 256 != 0))) continue;
+        const int tile_m = 128 * cluster, units = num_sms / cluster;
+        int64_t m_blocks;
+        if (p.kind == DG_GEMM_M_GROUPED_MASKED)
+            m_blocks = static_cast<int64_t>(p.groups) * ceil_div(std::min(std::max(p.expected_m, 1), p.m), tile_m);
+        else
+            m_blocks = ceil_div(p.m, tile_m);
+        for (int bn = 16; bn <= 240; bn += 16) {
+            if (forced_bn && bn != forced_bn) continue;
+            const int64_t tiles = m_blocks * ceil_div(p.n, bn);
+            const int64_t waves = ceil_div<int64_t>(tiles, units);
+            const double mma = 2.0 * bn;
+            const double smem_feed = 128.0 + static_cast<double>(bn) / cluster;
+            const double l2_feed = (16384.0 + 128.0 * bn / cluster) / 67.0;
+            const GemmLayout lay{128, static_cast<uint32_t>(bn), 128, 2, static_cast<uint32_t>(d_elem), static_cast<uint32_t>(cluster)};
+            const double epilogue = 300.0 + 40.0 * lay.num_stores() + bn * 2.0;
+            // The epilogue of a tile overlaps the next tile's main loop; it is exposed once per CTA
+            const double per_tile = static_cast<double>(k_blocks) * std::max(mma, std::max(smem_feed, l2_feed));
+            const double cost = static_cast<double>(waves) * std::max(per_tile, epilogue) + epilogue + 2000.0;
+            if (best_bn == 0 || cost < best_cost - 1e-9 || (std::abs(cost - best_cost) <= 1e-9 && bn > best_bn)) {
+                best_cost = cost;
+                best_bn = bn;
+                best_cluster = cluster;
+                best_tiles = tiles;
+            }
         }
     }
-    if (best_bn == 0) return fail(DG_ERR_INVALID_ARGUMENT, "DG_FORCE_BLOCK_N must be a multiple of 16 in [16, 240]");
+    if (best_bn == 0)
+        return fail(DG_ERR_INVALID_ARGUMENT, "no tile configuration: DG_FORCE_BLOCK_N must be a multiple of 16 in [16, 240], "
+                                             "DG_FORCE_CLUSTER 1 or 2 (2 needs an even SM count and, for the contiguous layout, m %% 256 == 0)");
 
-    GemmLayout lay{128, static_cast<uint32_t>(best_bn), 128, 2, static_cast<uint32_t>(d_elem)};
+    GemmLayout lay{128, static_cast<uint32_t>(best_bn), 128, 2, static_cast<uint32_t>(d_elem), static_cast<uint32_t>(best_cluster)};
     int stages = 2;
     while (stages < 32) {
         GemmLayout next = lay;
@@ -145,20 +169,20 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
     stages = static_cast<int>(std::max<int64_t>(2, std::min<int64_t>(stages, 2 * k_blocks)));
     lay.num_stages = stages;
 
-    const int64_t tiles = m_blocks * ceil_div(p.n, best_bn);
+    const int units = num_sms / best_cluster;
     cfg->block_m = 128;
     cfg->block_n = best_bn;
     cfg->block_k = 128;
     cfg->num_stages = stages;
-    cfg->cluster_size = 1;
+    cfg->cluster_size = best_cluster;
     const int forced_raster = env_int("FORCE_RASTER_GROUP");
-    cfg->raster_group = forced_raster > 0 ? forced_raster : 16;
-    cfg->num_ctas = p.kind == DG_GEMM_M_GROUPED_MASKED ? num_sms
-                                                        : static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(num_sms, tiles)));
+    cfg->raster_group = forced_raster > 0 ? forced_raster : (best_cluster == 2 ? 8 : 16);
+    cfg->num_ctas = best_cluster * (p.kind == DG_GEMM_M_GROUPED_MASKED
+                                        ? units : static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(units, best_tiles))));
     cfg->smem_bytes = static_cast<int>(lay.total_bytes());
     cfg->tmem_cols = static_cast<int>(lay.tmem_cols_alloc());
-    cfg->num_tiles = static_cast<int>(tiles);
-    cfg->waves_x100 = static_cast<int>(tiles * 100 / num_sms);
+    cfg->num_tiles = static_cast<int>(best_tiles);
+    cfg->waves_x100 = static_cast<int>(best_tiles * 100 / units);
     return DG_OK;
 }
 
@@ -168,6 +192,7 @@ std::string generate_source(const Problem& p, const dg_gemm_config_t& cfg) {
       << "#define DG_GEMM_TYPE " << p.kind << "\n"
       << "#define DG_BLOCK_N " << cfg.block_n << "\n"
       << "#define DG_NUM_STAGES " << cfg.num_stages << "\n"
+      << "#define DG_CLUSTER " << cfg.cluster_size << "\n"
       << "#define DG_A_FP4 " << (p.a_fp4 ? 1 : 0) << "\n"
       << "#define DG_B_FP4 " << (p.b_fp4 ? 1 : 0) << "\n"
       << "#define DG_GRAN_K_A " << p.gran_k_a << "\n"
@@ -175,6 +200,7 @@ std::string generate_source(const Problem& p, const dg_gemm_config_t& cfg) {
       << "#define DG_D_FP32 " << (p.d_fp32 ? 1 : 0) << "\n"
       << "#define DG_ACCUMULATE " << (p.accumulate ? 1 : 0) << "\n"
       << "#define DG_RASTER_GROUP " << cfg.raster_group << "\n"
+      << "#define DG_PROFILE " << env_int("PROFILE") << "\n"
       << "#include <dg/gemm_fp8_fp4.cuh>\n";
     return s.str();
 }
@@ -217,14 +243,14 @@ int run_gemm(int kind, const dg_gemm_args_t* a) {
     dg_gemm_config_t cfg;
     if ((rc = choose_config(p, &cfg)) != DG_OK) return rc;
     if (env_int("PRINT_CONFIGS"))
-        fprintf(stderr, "[dg] kind %d m %d n %d k %d groups %d -> block_n %d stages %d ctas %d smem %d tiles %d\n", kind, p.m, p.n, p.k,
-                p.groups, cfg.block_n, cfg.num_stages, cfg.num_ctas, cfg.smem_bytes, cfg.num_tiles);
+        fprintf(stderr, "[dg] kind %d m %d n %d k %d groups %d -> block_n %d cluster %d stages %d ctas %d smem %d tiles %d\n", kind, p.m, p.n,
+                p.k, p.groups, cfg.block_n, cfg.cluster_size, cfg.num_stages, cfg.num_ctas, cfg.smem_bytes, cfg.num_tiles);
     dg_kernel_t kernel = nullptr;
     if ((rc = get_kernel(p, cfg, &kernel)) != DG_OK) return rc;
     if ((rc = ensure_status_word()) != DG_OK) return rc;
 
     const GemmLayout lay{128, static_cast<uint32_t>(cfg.block_n), 128, static_cast<uint32_t>(cfg.num_stages),
-                         static_cast<uint32_t>(p.d_fp32 ? 4 : 2)};
+                         static_cast<uint32_t>(p.d_fp32 ? 4 : 2), static_cast<uint32_t>(cfg.cluster_size)};
     const uint64_t a_rows = kind == DG_GEMM_M_GROUPED_MASKED ? static_cast<uint64_t>(p.groups) * p.m : p.m;
     const uint64_t b_rows = static_cast<uint64_t>(p.groups) * p.n;
     const uint64_t sfa_k = ceil_div(p.k, p.gran_k_a * 4), sfb_k = ceil_div(p.k, p.gran_k_b * 4);
@@ -236,7 +262,7 @@ int run_gemm(int kind, const dg_gemm_args_t* a) {
     if ((rc = encode_2d(&tm_a, p.a_fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, a->a,
                         p.k, a_rows, a->lda, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B)) != DG_OK) return rc;
     if ((rc = encode_2d(&tm_b, p.b_fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, a->b,
-                        p.k, b_rows, a->ldb, 128, cfg.block_n, CU_TENSOR_MAP_SWIZZLE_128B)) != DG_OK) return rc;
+                        p.k, b_rows, a->ldb, 128, cfg.block_n / cfg.cluster_size, CU_TENSOR_MAP_SWIZZLE_128B)) != DG_OK) return rc;
     // Scales: MN (int32) x packed-K rows; the MN extent is the true row count, so reads past it are zero-filled
     if ((rc = encode_2d(&tm_sfa, CU_TENSOR_MAP_DATA_TYPE_INT32, a->sfa, p.m, sfa_rows, a->sfa_pitch * 4, 128, 1,
                         CU_TENSOR_MAP_SWIZZLE_NONE)) != DG_OK) return rc;
@@ -255,7 +281,25 @@ int run_gemm(int kind, const dg_gemm_args_t* a) {
     params.num_groups = p.groups;
     params.ldd = static_cast<uint32_t>(a->ldd);
     params.alpha = a->has_alpha ? a->alpha : 1.0f;
+    params.profile = nullptr;
     void* kargs[6] = {&tm_a, &tm_b, &tm_sfa, &tm_sfb, &tm_d, &params};
+    if (env_int("PROFILE")) {
+        // synchronous, printing path for tuning only
+        params.profile = profile_buffer();
+        if (params.profile == nullptr) return fail(DG_ERR_CUDA, "cannot allocate the profile buffer");
+        DG_CUDA_RT(cudaMemsetAsync(params.profile, 0, 16 * sizeof(unsigned long long), static_cast<cudaStream_t>(a->stream)));
+        rc = dg_jit_launch(kernel, cfg.num_ctas, 256, cfg.cluster_size, cfg.smem_bytes, state().pdl, a->stream, kargs);
+        if (rc != DG_OK) return rc;
+        unsigned long long h[16];
+        DG_CUDA_RT(cudaMemcpyAsync(h, params.profile, sizeof(h), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(a->stream)));
+        DG_CUDA_RT(cudaStreamSynchronize(static_cast<cudaStream_t>(a->stream)));
+        const double ctas = cfg.num_ctas, leaders = ctas / cfg.cluster_size;
+        fprintf(stderr, "[dg profile] cycles per CTA: producer wait_empty %.0f / %.0f | mma wait_full %.0f wait_tmem_empty %.0f / %.0f | "
+                        "sf wait %.0f / %.0f | epilogue wait_tmem_full %.0f store_wait %.0f / %.0f\n",
+                h[0] / ctas, h[1] / ctas, h[2] / leaders, h[3] / leaders, h[4] / leaders, h[5] / ctas, h[6] / ctas,
+                h[7] / ctas, h[9] / ctas, h[8] / ctas);
+        return DG_OK;
+    }
     return dg_jit_launch(kernel, cfg.num_ctas, 256, cfg.cluster_size, cfg.smem_bytes, state().pdl, a->stream, kargs);
 }
 

@@ -69,6 +69,24 @@ def test_every_store_width_and_scale_chunking(forced_bn, monkeypatch):
     assert oracle.calc_diff(d, ref) < 1e-5, diff_report(d, ref)
 
 
+@pytest.mark.parametrize("m,n,k,bn", [(256, 480, 512, 240), (129, 256, 256, 64), (128, 128, 128, 128), (1024, 1152, 1792, 224)])
+@pytest.mark.parametrize("b_fp4", [False, True])
+def test_cta_pair_variant_matches_oracle(m, n, k, bn, b_fp4, monkeypatch):
+    """tcgen05 cta_group::2: two CTAs share a 256-row tile (also with the second CTA entirely out of range)."""
+    monkeypatch.setenv("DG_FORCE_CLUSTER", "2")
+    monkeypatch.setenv("DG_FORCE_BLOCK_N", str(bn))
+    assert dg.get_gemm_config(0, m, n, k, b_is_fp4=b_fp4, gran_k_b=32 if b_fp4 else 128)["cluster_size"] == 2
+    qa, sfa, qb, sfb, _ = quantise_dense(seeded_bf16((m, k), 3), seeded_bf16((n, k), 4), b_fp4=b_fp4)
+    gk = 32 if b_fp4 else 128
+    d = _run_dense(qa, sfa, qb, sfb, b_fp4=b_fp4, gran_k_b=gk).float().cpu().numpy()
+    ref = oracle.dequant_gemm_nt(qa, sfa, qb, sfb, 128, gk, False, b_fp4)
+    assert oracle.calc_diff(d, ref) < 1e-5, diff_report(d, ref)
+    # same bits as the one-CTA-per-tile kernel: the K accumulation order per output element is the same
+    monkeypatch.setenv("DG_FORCE_CLUSTER", "1")
+    d1 = _run_dense(qa, sfa, qb, sfb, b_fp4=b_fp4, gran_k_b=gk).float().cpu().numpy()
+    assert np.array_equal(d, d1)
+
+
 def test_fp32_output_accumulation_and_alpha():
     m, n, k = 192, 320, 768
     qa, sfa, qb, sfb, _ = quantise_dense(seeded_bf16((m, k), 5), seeded_bf16((n, k), 6))
@@ -118,7 +136,7 @@ def test_bitwise_determinism_over_reruns():
 def test_scale_pitch_padding_is_never_read():
     """Scales with a K pitch larger than align(mn, 4) and the padding poisoned with 0xFF (the UE8M0 NaN):
     the result must be bitwise the same (tests/test_fp8_fp4.py:83-94, tests/utils.py:41-50)."""
-    m, n, k = 130, 260, 1024
+    m, n, k = 130, 264, 1024
     qa, sfa, qb, sfb, _ = quantise_dense(seeded_bf16((m, k), 12), seeded_bf16((n, k), 13))
     base = _run_dense(qa, sfa, qb, sfb)
 
@@ -168,10 +186,11 @@ def _grouped_inputs(g, n, k, a, b_fp4=False):
     return qa, sfa, qb, sfb
 
 
-@pytest.mark.parametrize("alignment", [128, 256])
+@pytest.mark.parametrize("alignment,cluster", [(128, 1), (256, 1), (256, 2)])
 @pytest.mark.parametrize("b_fp4", [False, True])
-def test_m_grouped_contiguous(alignment, b_fp4):
+def test_m_grouped_contiguous(alignment, cluster, b_fp4, monkeypatch):
     g, n, k = 5, 1024, 1024
+    monkeypatch.setenv("DG_FORCE_CLUSTER", str(cluster))
     dg.set_mk_alignment_for_contiguous_layout(alignment)
     try:
         m, actual, aligned, layout = oracle.make_contiguous_layout(g, 200, alignment, actual_ms=[130, 0, 256, 77, 300])
@@ -216,7 +235,9 @@ def _masked_case(counts, max_m, n, k):
 SENTINEL = -7.0
 
 
-def test_m_grouped_masked_leaves_rows_beyond_masked_m_untouched():
+@pytest.mark.parametrize("cluster", [1, 2])
+def test_m_grouped_masked_leaves_rows_beyond_masked_m_untouched(cluster, monkeypatch):
+    monkeypatch.setenv("DG_FORCE_CLUSTER", str(cluster))
     counts, max_m, n, k = (45, 83, 0, 256, 129, 1), 256, 1000 // 8 * 8, 1024
     qa, sfa, qb, sfb = _masked_case(counts, max_m, n, k)
     ref = oracle.m_grouped_masked_ref(qa, sfa, qb, sfb, counts)
