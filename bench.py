@@ -49,7 +49,7 @@ def load_peaks():
 # Clock sampling during the timed region (NVML reads only)
 # ----------------------------------------------------------------------------------------------------
 class ClockSampler:
-    def __init__(self, index: int, period_s: float = 0.02):
+    def __init__(self, index: int, period_s: float = 0.002):
         self.index, self.period, self.samples, self.reasons = index, period_s, [], set()
         self.max_mhz, self._stop, self._thread, self._nvml = None, threading.Event(), None, None
         try:

@@ -19,6 +19,7 @@ constexpr uint32_t kTmemCapacityCols = 512;
 struct GemmLayout {
     uint32_t block_m, block_n, block_k, num_stages, d_elem_bytes;
     uint32_t cluster = 1;                          // CTAs sharing one B tile (each loads block_n / cluster rows of B)
+    uint32_t b_mn_major = 0;                       // B stored with N contiguous: staged as 128-column atoms of [128 K][128 B]
 
     DG_HDC uint32_t sf_block_n() const { return (block_n + 127) / 128 * 128; }
     // Row width of one D staging buffer / TMA store: the widest swizzle span that divides a tile row
@@ -31,7 +32,9 @@ struct GemmLayout {
     DG_HDC uint32_t num_store_stages() const { return 2; }
 
     DG_HDC uint32_t a_bytes() const { return block_m * block_k; }        // one byte per element (FP8, or FP4 in 16-byte containers)
-    DG_HDC uint32_t b_bytes() const { return block_n / cluster * block_k; }
+    DG_HDC uint32_t load_block_n() const { return block_n / cluster; }
+    DG_HDC uint32_t b_atoms() const { return (load_block_n() + 127) / 128; }      // MN-major only
+    DG_HDC uint32_t b_bytes() const { return b_mn_major ? b_atoms() * 128 * block_k : load_block_n() * block_k; }
     DG_HDC uint32_t sfa_bytes() const { return 128 * 4; }
     DG_HDC uint32_t sfb_bytes() const { return sf_block_n() * 4; }
 

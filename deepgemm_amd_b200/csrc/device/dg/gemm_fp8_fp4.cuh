@@ -17,7 +17,12 @@
 //
 // The configuration arrives as DG_* macros set by the host-side code generator:
 //   DG_GEMM_TYPE (0 dense, 1 m-grouped contiguous, 2 m-grouped masked), DG_BLOCK_N, DG_NUM_STAGES,
-//   DG_CLUSTER, DG_A_FP4, DG_B_FP4, DG_GRAN_K_A, DG_GRAN_K_B, DG_D_FP32, DG_ACCUMULATE, DG_RASTER_GROUP.
+//   DG_CLUSTER, DG_A_FP4, DG_B_FP4, DG_MAJOR_A, DG_MAJOR_B (0 K-major, 1 MN-major), DG_GRAN_K_A, DG_GRAN_K_B,
+//   DG_D_FP32, DG_ACCUMULATE, DG_RASTER_GROUP.
+//
+// MN-major operands (the nn / tn / tt variants): the tile is staged as [128 of K][128 B of MN] atoms with the
+// same 128-byte swizzle (one TMA box per 128 columns of MN), the descriptor's leading-dimension offset steps
+// between atoms, and a step of 32 along K is 32 rows = 4096 B.
 //
 // DG_CLUSTER == 2 pairs two CTAs (a cluster of two SMs) on one 256 x BLOCK_N tile with
 // tcgen05.mma.cta_group::2: each CTA loads its own 128 rows of A and one half of the B tile, CTA 0 issues
@@ -47,6 +52,8 @@ constexpr uint32_t kNumStages  = DG_NUM_STAGES;
 constexpr uint32_t kCluster    = DG_CLUSTER;       // CTAs cooperating on one tile (1 or 2)
 constexpr bool     kAIsFP4     = DG_A_FP4 != 0;
 constexpr bool     kBIsFP4     = DG_B_FP4 != 0;
+constexpr bool     kAMnMajor   = DG_MAJOR_A != 0;
+constexpr bool     kBMnMajor   = DG_MAJOR_B != 0;
 constexpr uint32_t kGranKA     = DG_GRAN_K_A;
 constexpr uint32_t kGranKB     = DG_GRAN_K_B;
 constexpr bool     kDIsFP32    = DG_D_FP32 != 0;
@@ -64,6 +71,8 @@ static_assert(kGranKA == 32 || kGranKA == 128, "one scale per 32 or 128 elements
 static_assert(kGranKB == 32 || kGranKB == 128, "one scale per 32 or 128 elements of K");
 static_assert(kNumStages >= 2 && kNumStages <= 32, "pipeline depth");
 static_assert(kCluster == 1 || kCluster == 2, "one CTA or a CTA pair per tile");
+static_assert(!(kAIsFP4 && kAMnMajor) && !(kBIsFP4 && kBMnMajor), "packed FP4 operands must be K-major");
+static_assert(!kBMnMajor || (BLOCK_N / kCluster) % 16 == 0, "an MN-major B load must start on a 16-byte boundary");
 
 // Scales: a packed int32 holds 4 scales.  With one scale per 128 K it spans 4 K-blocks, so the
 // chunk is fetched on every 4th K-block; with one per 32 K it spans exactly one K-block.
@@ -75,7 +84,8 @@ constexpr uint32_t SF_BLOCK_N = (BLOCK_N + 127) / 128 * 128;
 // Shared memory and tensor memory maps (every operand stage starts on a 1024-byte boundary, as the
 // 128-byte swizzle requires); the arithmetic lives in gemm_config.hpp, shared with the host heuristics
 constexpr uint32_t kDElemBytes = kDIsFP32 ? 4 : 2;
-constexpr GemmLayout kLayout{BLOCK_M, BLOCK_N, BLOCK_K, kNumStages, kDElemBytes, kCluster};
+constexpr GemmLayout kLayout{BLOCK_M, BLOCK_N, BLOCK_K, kNumStages, kDElemBytes, kCluster, kBMnMajor ? 1u : 0u};
+constexpr uint32_t kBAtoms = kLayout.b_atoms();            // 128-column atoms of an MN-major B tile
 constexpr uint32_t kStoreRowBytes   = kLayout.store_row_bytes();
 constexpr uint32_t kStoreCols       = kLayout.store_cols();          // columns of D per TMA store
 constexpr uint32_t kNumStores       = kLayout.num_stores();
@@ -250,21 +260,25 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                     if (kb % kSFBPeriod == 0)
                         tma_load_2d(smem_base + kSmemSFB + stage * kSFBBytes, &tm_sfb, sf_full_bar(stage),
                                     static_cast<int32_t>(tile.n_block * BLOCK_N), static_cast<int32_t>(sfb_row0 + kb / kSFBPeriod));
-                    if constexpr (kCluster == 1) {
-                        mbar_arrive_expect_tx(full_bar(stage), kTxBytesAB);
-                        tma_load_2d(smem_base + kSmemA + stage * kABytes, &tm_a, full_bar(stage),
-                                    static_cast<int32_t>(kb * BLOCK_K), static_cast<int32_t>(a_row));
-                        tma_load_2d(smem_base + kSmemB + stage * kBBytes, &tm_b, full_bar(stage),
-                                    static_cast<int32_t>(kb * BLOCK_K), static_cast<int32_t>(b_row));
+                    // With a cluster the copies land in this CTA and their bytes are counted on CTA 0's barrier,
+                    // which expects both CTAs' bytes
+                    const uint32_t load_bar = kCluster == 1 ? full_bar(stage) : in_leader(full_bar(stage));
+                    if (kCluster == 1 || is_leader) mbar_arrive_expect_tx(full_bar(stage), kTxBytesAB);
+                    else mbar_arrive_cluster(load_bar);
+                    auto load = [&](uint32_t dst, const CUtensorMap* map, uint32_t x, uint32_t y) {
+                        if constexpr (kCluster == 1) tma_load_2d(dst, map, load_bar, static_cast<int32_t>(x), static_cast<int32_t>(y));
+                        else tma_load_2d_2cta(dst, map, load_bar, static_cast<int32_t>(x), static_cast<int32_t>(y));
+                    };
+                    // K-major: x = K, y = row.  MN-major: x = row (column of the stored matrix), y = K (+ the group's K offset)
+                    if constexpr (!kAMnMajor) load(smem_base + kSmemA + stage * kABytes, &tm_a, kb * BLOCK_K, a_row);
+                    else load(smem_base + kSmemA + stage * kABytes, &tm_a, a_row, kb * BLOCK_K);
+                    if constexpr (!kBMnMajor) {
+                        load(smem_base + kSmemB + stage * kBBytes, &tm_b, kb * BLOCK_K, b_row);
                     } else {
-                        // The copies land in this CTA; their bytes are counted on CTA 0's barrier, which expects both CTAs' bytes
-                        const uint32_t leader_full = in_leader(full_bar(stage));
-                        if (is_leader) mbar_arrive_expect_tx(full_bar(stage), kTxBytesAB);
-                        else mbar_arrive_cluster(leader_full);
-                        tma_load_2d_2cta(smem_base + kSmemA + stage * kABytes, &tm_a, leader_full,
-                                         static_cast<int32_t>(kb * BLOCK_K), static_cast<int32_t>(a_row));
-                        tma_load_2d_2cta(smem_base + kSmemB + stage * kBBytes, &tm_b, leader_full,
-                                         static_cast<int32_t>(kb * BLOCK_K), static_cast<int32_t>(b_row));
+                        #pragma unroll
+                        for (uint32_t i = 0; i < kBAtoms; ++i)
+                            load(smem_base + kSmemB + stage * kBBytes + i * 128 * BLOCK_K, &tm_b,
+                                 tile.n_block * BLOCK_N + cta_rank * LOAD_BLOCK_N + i * 128, tile.group * p.shape_k + kb * BLOCK_K);
                     }
                 }
             }
@@ -277,7 +291,11 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
         // ================= MMA issuer (CTA 0 of the cluster only) =================
         if (lane == 0 && is_leader) {
             constexpr uint32_t idesc = make_instr_desc_block_scaled(kAIsFP4 ? kFmtE2M1 : kFmtE4M3, kBIsFP4 ? kFmtE2M1 : kFmtE4M3,
-                                                                    0, 0, UMMA_M, UMMA_N);
+                                                                    kAMnMajor, kBMnMajor, UMMA_M, UMMA_N);
+            // K-major: 8-row groups of 128-byte rows (SBO 1024), +32 B per UMMA along K.
+            // MN-major: atoms of [128 K][128 B]; SBO 1024 = eight K rows, LBO = one atom, +32 rows (4096 B) per UMMA along K.
+            constexpr uint32_t kALbo = kAMnMajor ? 128 * BLOCK_K : 0, kBLbo = kBMnMajor ? 128 * BLOCK_K : 0;
+            constexpr uint32_t kAStepK = (kAMnMajor ? UMMA_K * 128 : UMMA_K) >> 4, kBStepK = (kBMnMajor ? UMMA_K * 128 : UMMA_K) >> 4;
             // A commit reaches the barrier at the same offset in every CTA of the cluster
             auto commit_all = [&](uint32_t bar) {
                 if constexpr (kCluster == 1) {
@@ -314,15 +332,15 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                             tc_cp_32x128b_warpx4<kCluster>(tmem_base + kTmemColSFB + i * 4,
                                                            make_smem_desc(smem_base + kSmemSFB + stage * kSFBBytes + i * 512, 0, 128, kSwizzleNone));
                     }
-                    const uint64_t a_desc = make_smem_desc(smem_base + kSmemA + stage * kABytes, 0, 1024, kSwizzle128B);
-                    const uint64_t b_desc = make_smem_desc(smem_base + kSmemB + stage * kBBytes, 0, 1024, kSwizzle128B);
+                    const uint64_t a_desc = make_smem_desc(smem_base + kSmemA + stage * kABytes, kALbo, 1024, kSwizzle128B);
+                    const uint64_t b_desc = make_smem_desc(smem_base + kSmemB + stage * kBBytes, kBLbo, 1024, kSwizzle128B);
                     #pragma unroll
                     for (uint32_t j = 0; j < BLOCK_K / UMMA_K; ++j) {
                         // Which byte of the packed scale word applies to these 32 elements of K
                         const uint32_t sfa_id = kGranKA == 32 ? j : (kb % 4);
                         const uint32_t sfb_id = kGranKB == 32 ? j : (kb % 4);
-                        // Advancing K by 32 bytes inside the 128-byte swizzle atom = +2 in the (>>4) address field
-                        tc_mma_mxf8f6f4<kCluster>(tmem_d, a_desc + j * (UMMA_K >> 4), b_desc + j * (UMMA_K >> 4),
+                        // Advancing K moves the start address: +32 B inside the swizzle atom (K-major) or +32 rows (MN-major)
+                        tc_mma_mxf8f6f4<kCluster>(tmem_d, a_desc + j * kAStepK, b_desc + j * kBStepK,
                                                   instr_desc_with_sf_ids(idesc, sfa_id, sfb_id),
                                                   tmem_base + kTmemColSFA, tmem_base + kTmemColSFB, (kb | j) != 0);
                     }

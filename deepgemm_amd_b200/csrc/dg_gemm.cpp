@@ -34,7 +34,7 @@ unsigned long long* profile_buffer() {
 struct Problem {
     int kind;
     int m, n, k, groups;
-    bool a_fp4, b_fp4, d_fp32, accumulate;
+    bool a_fp4, b_fp4, d_fp32, accumulate, a_mn_major, b_mn_major;
     int gran_k_a, gran_k_b;
     int expected_m;
 };
@@ -65,9 +65,12 @@ int validate(int kind, const dg_gemm_args_t* a, bool need_pointers, Problem* p) 
         return fail(DG_ERR_UNSUPPORTED, "FP4 x FP4 (kind::mxf4) is not built; FP8 x FP8 and FP8 x FP4 are");
     if (a->a_dtype == DG_FP4_E2M1_X2)
         return fail(DG_ERR_UNSUPPORTED, "FP4 A with FP8 B is not built; use FP8 A with FP4 B");
-    if (a->major_a != DG_MAJOR_K || a->major_b != DG_MAJOR_K)
-        return fail(DG_ERR_UNSUPPORTED, "MN-major operands (nn / tn / tt) are not built yet; pass K-major A and B");
+    DG_REQUIRE((a->major_a == DG_MAJOR_K || a->major_a == DG_MAJOR_MN) && (a->major_b == DG_MAJOR_K || a->major_b == DG_MAJOR_MN));
+    if ((a->major_a == DG_MAJOR_MN && a->a_dtype == DG_FP4_E2M1_X2) || (a->major_b == DG_MAJOR_MN && a->b_dtype == DG_FP4_E2M1_X2))
+        return fail(DG_ERR_UNSUPPORTED, "MN-major packed FP4 operands are not built; FP4 must be K-major");
     p->kind = kind;
+    p->a_mn_major = a->major_a == DG_MAJOR_MN;
+    p->b_mn_major = a->major_b == DG_MAJOR_MN;
     p->m = a->m; p->n = a->n; p->k = a->k; p->groups = a->num_groups;
     p->a_fp4 = a->a_dtype == DG_FP4_E2M1_X2;
     p->b_fp4 = a->b_dtype == DG_FP4_E2M1_X2;
@@ -86,7 +89,9 @@ int validate(int kind, const dg_gemm_args_t* a, bool need_pointers, Problem* p) 
         DG_REQUIRE(aligned(a->sfa, 16) && aligned(a->sfb, 16) && aligned(a->d, 16));
         if (kind != DG_GEMM_DENSE) DG_REQUIRE(a->grouped_layout != nullptr);
     }
-    const int64_t k_bytes_a = p->a_fp4 ? a->k / 2 : a->k, k_bytes_b = p->b_fp4 ? a->k / 2 : a->k;
+    // Pitch of the non-contiguous dimension: rows of K bytes (K-major) or K-slices of MN bytes (MN-major)
+    const int64_t k_bytes_a = p->a_mn_major ? a->m : (p->a_fp4 ? a->k / 2 : a->k);
+    const int64_t k_bytes_b = p->b_mn_major ? a->n : (p->b_fp4 ? a->k / 2 : a->k);
     DG_REQUIRE(a->lda >= k_bytes_a && a->lda % (p->a_fp4 ? 32 : 16) == 0);   // TMA: strides are multiples of 16 bytes
     DG_REQUIRE(a->ldb >= k_bytes_b && a->ldb % (p->b_fp4 ? 32 : 16) == 0);
     const int d_elem = p->d_fp32 ? 4 : 2;
@@ -133,12 +138,14 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
             m_blocks = ceil_div(p.m, tile_m);
         for (int bn = 16; bn <= 240; bn += 16) {
             if (forced_bn && bn != forced_bn) continue;
+            if (p.b_mn_major && (bn / cluster) % 16 != 0) continue;       // an MN-major B load starts on a 16-byte boundary
             const int64_t tiles = m_blocks * ceil_div(p.n, bn);
             const int64_t waves = ceil_div<int64_t>(tiles, units);
             const double mma = 2.0 * bn;
             const double smem_feed = 128.0 + static_cast<double>(bn) / cluster;
             const double l2_feed = (16384.0 + 128.0 * bn / cluster) / 67.0;
-            const GemmLayout lay{128, static_cast<uint32_t>(bn), 128, 2, static_cast<uint32_t>(d_elem), static_cast<uint32_t>(cluster)};
+            const GemmLayout lay{128, static_cast<uint32_t>(bn), 128, 2, static_cast<uint32_t>(d_elem), static_cast<uint32_t>(cluster),
+                                 p.b_mn_major ? 1u : 0u};
             const double epilogue = 300.0 + 40.0 * lay.num_stores() + bn * 2.0;
             // The epilogue of a tile overlaps the next tile's main loop; it is exposed once per CTA
             const double per_tile = static_cast<double>(k_blocks) * std::max(mma, std::max(smem_feed, l2_feed));
@@ -155,7 +162,8 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
         return fail(DG_ERR_INVALID_ARGUMENT, "no tile configuration: DG_FORCE_BLOCK_N must be a multiple of 16 in [16, 240], "
                                              "DG_FORCE_CLUSTER 1 or 2 (2 needs an even SM count and, for the contiguous layout, m %% 256 == 0)");
 
-    GemmLayout lay{128, static_cast<uint32_t>(best_bn), 128, 2, static_cast<uint32_t>(d_elem), static_cast<uint32_t>(best_cluster)};
+    GemmLayout lay{128, static_cast<uint32_t>(best_bn), 128, 2, static_cast<uint32_t>(d_elem), static_cast<uint32_t>(best_cluster),
+                   p.b_mn_major ? 1u : 0u};
     int stages = 2;
     while (stages < 32) {
         GemmLayout next = lay;
@@ -195,6 +203,8 @@ std::string generate_source(const Problem& p, const dg_gemm_config_t& cfg) {
       << "#define DG_CLUSTER " << cfg.cluster_size << "\n"
       << "#define DG_A_FP4 " << (p.a_fp4 ? 1 : 0) << "\n"
       << "#define DG_B_FP4 " << (p.b_fp4 ? 1 : 0) << "\n"
+      << "#define DG_MAJOR_A " << (p.a_mn_major ? 1 : 0) << "\n"
+      << "#define DG_MAJOR_B " << (p.b_mn_major ? 1 : 0) << "\n"
       << "#define DG_GRAN_K_A " << p.gran_k_a << "\n"
       << "#define DG_GRAN_K_B " << p.gran_k_b << "\n"
       << "#define DG_D_FP32 " << (p.d_fp32 ? 1 : 0) << "\n"
@@ -250,7 +260,7 @@ int run_gemm(int kind, const dg_gemm_args_t* a) {
     if ((rc = ensure_status_word()) != DG_OK) return rc;
 
     const GemmLayout lay{128, static_cast<uint32_t>(cfg.block_n), 128, static_cast<uint32_t>(cfg.num_stages),
-                         static_cast<uint32_t>(p.d_fp32 ? 4 : 2), static_cast<uint32_t>(cfg.cluster_size)};
+                         static_cast<uint32_t>(p.d_fp32 ? 4 : 2), static_cast<uint32_t>(cfg.cluster_size), p.b_mn_major ? 1u : 0u};
     const uint64_t a_rows = kind == DG_GEMM_M_GROUPED_MASKED ? static_cast<uint64_t>(p.groups) * p.m : p.m;
     const uint64_t b_rows = static_cast<uint64_t>(p.groups) * p.n;
     const uint64_t sfa_k = ceil_div(p.k, p.gran_k_a * 4), sfb_k = ceil_div(p.k, p.gran_k_b * 4);
@@ -258,11 +268,22 @@ int run_gemm(int kind, const dg_gemm_args_t* a) {
     const uint64_t sfb_rows = sfb_k * p.groups;
 
     CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb, tm_d;
-    // A, B: K (elements) x rows; box = one 128-element K-block x the tile's rows; 128-byte swizzle
-    if ((rc = encode_2d(&tm_a, p.a_fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, a->a,
-                        p.k, a_rows, a->lda, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B)) != DG_OK) return rc;
-    if ((rc = encode_2d(&tm_b, p.b_fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, a->b,
-                        p.k, b_rows, a->ldb, 128, cfg.block_n / cfg.cluster_size, CU_TENSOR_MAP_SWIZZLE_128B)) != DG_OK) return rc;
+    // K-major A, B: K (elements) x rows; box = one 128-element K-block x the tile's rows; 128-byte swizzle.
+    // MN-major (FP8 only): MN x (groups x K); box = 128 columns of MN x one K-block.
+    if (!p.a_mn_major) {
+        if ((rc = encode_2d(&tm_a, p.a_fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, a->a,
+                            p.k, a_rows, a->lda, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B)) != DG_OK) return rc;
+    } else {
+        if ((rc = encode_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->a, p.m, p.k, a->lda, 128, 128,
+                            CU_TENSOR_MAP_SWIZZLE_128B)) != DG_OK) return rc;
+    }
+    if (!p.b_mn_major) {
+        if ((rc = encode_2d(&tm_b, p.b_fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, a->b,
+                            p.k, b_rows, a->ldb, 128, cfg.block_n / cfg.cluster_size, CU_TENSOR_MAP_SWIZZLE_128B)) != DG_OK) return rc;
+    } else {
+        if ((rc = encode_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->b, p.n, static_cast<uint64_t>(p.groups) * p.k, a->ldb, 128, 128,
+                            CU_TENSOR_MAP_SWIZZLE_128B)) != DG_OK) return rc;
+    }
     // Scales: MN (int32) x packed-K rows; the MN extent is the true row count, so reads past it are zero-filled
     if ((rc = encode_2d(&tm_sfa, CU_TENSOR_MAP_DATA_TYPE_INT32, a->sfa, p.m, sfa_rows, a->sfa_pitch * 4, 128, 1,
                         CU_TENSOR_MAP_SWIZZLE_NONE)) != DG_OK) return rc;

@@ -87,6 +87,30 @@ def test_cta_pair_variant_matches_oracle(m, n, k, bn, b_fp4, monkeypatch):
     assert np.array_equal(d, d1)
 
 
+@pytest.mark.parametrize("variant", ["nn", "tn", "tt"])
+@pytest.mark.parametrize("m,n,k,cluster", [(128, 256, 512, 1), (208, 720, 1152, 1), (256, 2112, 1024, 1), (384, 704, 640, 2)])
+def test_mn_major_operands_through_the_nn_tn_tt_entry_points(variant, m, n, k, cluster, monkeypatch):
+    """tests/test_fp8_fp4.py:41-53: the aliases take the transposed (contiguous) storage of an MN-major operand."""
+    monkeypatch.setenv("DG_FORCE_CLUSTER", str(cluster))
+    qa, sfa, qb, sfb_rows, sfb_raw = quantise_dense(seeded_bf16((m, k), 16), seeded_bf16((n, k), 17))
+    ref = oracle.dequant_gemm_nt(qa, sfa, qb, sfb_rows)
+    a_t = variant in ("tn", "tt")                  # A is stored [K, M]
+    b_t = variant in ("nn", "tn")                  # B is stored [K, N]
+    a = (fp8_cuda(qa.T.copy()), torch.from_numpy(sfa).cuda().T) if a_t else (fp8_cuda(qa), torch.from_numpy(sfa).cuda())
+    b = (fp8_cuda(qb.T.copy()), torch.from_numpy(sfb_raw).cuda().T) if b_t else (fp8_cuda(qb), torch.from_numpy(sfb_raw).cuda())
+    assert a[0].is_contiguous() and b[0].is_contiguous()
+    d = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    dg.reset_kernel_status()
+    getattr(dg, f"fp8_fp4_gemm_{variant}")(a, b, d)                # default recipe (1, 128, 128) for FP32 scales
+    assert dg.kernel_status() == 0
+    out = d.float().cpu().numpy()
+    assert oracle.calc_diff(out, ref) < 1e-5, diff_report(out, ref)
+    # identical bits to the K-major call: same products, same accumulation order
+    d_nt = torch.empty_like(d)
+    dg.fp8_gemm_nt((fp8_cuda(qa), torch.from_numpy(sfa).cuda()), (fp8_cuda(qb), torch.from_numpy(sfb_raw).cuda()), d_nt)
+    assert torch.equal(d.view(torch.int16), d_nt.view(torch.int16))
+
+
 def test_fp32_output_accumulation_and_alpha():
     m, n, k = 192, 320, 768
     qa, sfa, qb, sfb, _ = quantise_dense(seeded_bf16((m, k), 5), seeded_bf16((n, k), 6))
@@ -215,6 +239,25 @@ def test_m_grouped_contiguous(alignment, cluster, b_fp4, monkeypatch):
         dg.set_mk_alignment_for_contiguous_layout(128)
 
 
+def test_m_grouped_contiguous_nn_takes_mn_major_weights():
+    g, n, k = 3, 640, 768
+    m, actual, aligned, layout = oracle.make_contiguous_layout(g, 200, 128, actual_ms=[130, 256, 77])
+    a = seeded_bf16((m, k), 22)
+    a[layout < 0] = 0
+    qa, sfa, qb, sfb = _grouped_inputs(g, n, k, a)
+    ref = oracle.m_grouped_contiguous_ref(qa, sfa, qb, sfb, aligned)
+    b_kn = fp8_cuda(np.ascontiguousarray(qb.transpose(0, 2, 1)))                 # [G, K, N]
+    sfb_kn = torch.from_numpy(sfb).cuda().transpose(1, 2).contiguous()           # FP32 [G, K/128, N]
+    d = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    dg.reset_kernel_status()
+    dg.m_grouped_fp8_gemm_nn_contiguous((fp8_cuda(qa), torch.from_numpy(sfa).cuda()), (b_kn, sfb_kn), d,
+                                        torch.from_numpy(layout).cuda(), recipe=(1, 1, 128))
+    assert dg.kernel_status() == 0
+    out = d.float().cpu().numpy()
+    valid = layout >= 0
+    assert oracle.calc_diff(out[valid], ref[valid]) < 1e-5, diff_report(out, ref)
+
+
 # ---------------------------------------------------------------------------------------------------
 # m-grouped masked
 # ---------------------------------------------------------------------------------------------------
@@ -301,7 +344,7 @@ def test_packed_scale_layout_matches_oracle_bits_and_strides(mn, k, groups, gran
     want, strides = oracle.mn_major_tma_aligned_packed_ue8m0(sf)
     assert got.dtype == torch.int and tuple(got.shape) == want.shape and tuple(got.stride()) == tuple(strides)
     assert np.array_equal(got.cpu().numpy(), want)
-    assert not (got.contiguous().view(torch.uint8) == 0xFF).any()
+    assert not (np.ascontiguousarray(got.cpu().numpy()).view(np.uint8) == 0xFF).any()
     # the GEMM entry points accept it as pre-transformed (int32) scales
     chk = dg.transform_sf_into_required_layout(got, mn, k, (1, gran_k), groups if groups > 1 else None)
     assert chk.data_ptr() == got.data_ptr()
