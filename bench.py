@@ -326,17 +326,95 @@ def main():
         dist.destroy_process_group()
 
 
+def make_grouped_b(groups, n, k, fp4, torch, dg):
+    from deepgemm_amd_b200.utils import per_block_cast_to_fp8, per_token_cast_to_fp4
+    b = torch.randn((groups, n, k), device="cuda", dtype=torch.bfloat16)
+    if fp4:
+        qs = [per_token_cast_to_fp4(b[g], True, 32) for g in range(groups)]
+        recipe = (1, 32)
+    else:
+        qs = [per_block_cast_to_fp8(b[g], True) for g in range(groups)]
+        recipe = (128, 128)
+    qb = torch.stack([q for q, _ in qs])
+    sfb = dg.transform_sf_into_required_layout(torch.stack([s for _, s in qs]), n, k, recipe, groups)
+    return qb, sfb
+
+
 def detail_rows(torch, dg):
-    """Per-shape device times (L2 flushed before every call) for BASELINE configs 2-5."""
+    """Per-case device times (256 MB L2 flush before every call) for BASELINE configs 2-5.  TFLOP/s counts valid
+    rows only and GB/s the bytes of A, B, D and scales, as the reference's tests print them
+    (tests/test_fp8_fp4.py:108-111,170-174,229-237)."""
+    import random
     from deepgemm_amd_b200.testing import bench
+    from deepgemm_amd_b200.utils import per_token_cast_to_fp4, per_token_cast_to_fp8
     rows = []
+
+    def add(case, t, flops, byts):
+        rows.append({"case": case, "us": round(t * 1e6, 1), "tflops": round(flops / t / 1e12, 1), "gbs": round(byts / t / 1e9, 0)})
+
+    # config 2: dense sweep
     for m in (64, 128, 4096):
         for i, (n, k) in enumerate(DENSE_NK):
             c = make_dense_case(m, n, k, 77 + i, torch, dg)
             t = bench(lambda: dg.fp8_gemm_nt(c["a"], c["b"], c["d"], recipe=(1, 1, 128)), 3, 10)
-            byts = m * k + n * k + m * n * 2 + (m + n) * (k // 128)
-            rows.append({"case": f"dense m{m} n{n} k{k}", "us": round(t * 1e6, 1), "tflops": round(flops_of(m, n, k) / t / 1e12, 1),
-                         "gbs": round(byts / t / 1e9, 0)})
+            add(f"dense m{m} n{n} k{k}", t, flops_of(m, n, k), m * k + n * k + m * n * 2 + (m + n) * (k // 128))
+    # config 5 (dense): FP8 x FP4
+    for n, k in ((7168, 2048), (4096, 7168)):
+        a = torch.randn((M_DENSE, k), device="cuda", dtype=torch.bfloat16)
+        w = torch.randn((n, k), device="cuda", dtype=torch.bfloat16)
+        qa, sfa = per_token_cast_to_fp8(a, True, 128)
+        qb, sfb = per_token_cast_to_fp4(w, True, 32)
+        sfa = dg.transform_sf_into_required_layout(sfa, M_DENSE, k, (1, 128))
+        sfb = dg.transform_sf_into_required_layout(sfb, n, k, (1, 32))
+        d = torch.empty((M_DENSE, n), device="cuda", dtype=torch.bfloat16)
+        t = bench(lambda: dg.fp8_fp4_gemm_nt((qa, sfa), (qb, sfb), d, recipe_a=(1, 128), recipe_b=(1, 32)), 3, 10)
+        add(f"fp8xfp4 dense m{M_DENSE} n{n} k{k}", t, flops_of(M_DENSE, n, k), M_DENSE * k + n * k // 2 + M_DENSE * n * 2)
+        del a, w, qa, qb, d
+    # configs 3 and 5 (grouped): 32 experts, tokens per expert int(8192 U(0.7, 1.3)) aligned to 128
+    rng = random.Random(0)
+    groups = 32
+    actual = [int(8192 * rng.uniform(0.7, 1.3)) for _ in range(groups)]
+    aligned = [-(-x // 128) * 128 for x in actual]
+    m_total, valid = sum(aligned), sum(actual)
+    layout = torch.full((m_total,), -1, dtype=torch.int, device="cuda")
+    start = 0
+    for g, (am, al) in enumerate(zip(actual, aligned)):
+        layout[start:start + am] = g
+        start += al
+    for n, k in ((4096, 7168), (7168, 2048)):
+        a = torch.randn((m_total, k), device="cuda", dtype=torch.bfloat16)
+        a[layout < 0] = 0
+        qa, sfa = per_token_cast_to_fp8(a, True, 128)
+        del a
+        sfa = dg.transform_sf_into_required_layout(sfa, m_total, k, (1, 128))
+        d = torch.empty((m_total, n), device="cuda", dtype=torch.bfloat16)
+        for fp4 in (False, True):
+            qb, sfb = make_grouped_b(groups, n, k, fp4, torch, dg)
+            rb = (1, 32) if fp4 else (1, 128)
+            t = bench(lambda: dg.m_grouped_fp8_fp4_gemm_nt_contiguous((qa, sfa), (qb, sfb), d, layout, recipe_a=(1, 128), recipe_b=rb), 2, 5)
+            add(f"{'fp8xfp4 ' if fp4 else ''}m-grouped contiguous G{groups} M{m_total} (valid {valid}) n{n} k{k}", t,
+                flops_of(valid, n, k), m_total * k + groups * n * k // (2 if fp4 else 1) + m_total * n * 2)
+            del qb, sfb
+        del qa, sfa, d
+    # config 4: masked decode GEMM replayed from a CUDA graph
+    groups, max_m, n, k = 16, 256, 4096, 7168
+    masked = torch.tensor([rng.randint(45, 83) for _ in range(groups)], dtype=torch.int, device="cuda")
+    a = torch.randn((groups * max_m, k), device="cuda", dtype=torch.bfloat16)
+    qa, sfa = per_token_cast_to_fp8(a, True, 128)
+    qa, sfa = qa.view(groups, max_m, k), dg.transform_sf_into_required_layout(sfa.view(groups, max_m, -1), max_m, k, (1, 128), groups)
+    qb, sfb = make_grouped_b(groups, n, k, False, torch, dg)
+    d = torch.empty((groups, max_m, n), device="cuda", dtype=torch.bfloat16)
+    call = lambda: dg.m_grouped_fp8_gemm_nt_masked((qa, sfa), (qb, sfb), d, masked, 64, recipe=(1, 1, 128))
+    call()
+    torch.cuda.synchronize()
+    graph, stream = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            call()
+    t = bench(graph.replay, 3, 20)
+    vm = int(masked.sum().item())
+    add(f"m-grouped masked (CUDA graph) G{groups} max_m{max_m} valid {vm} n{n} k{k}", t, flops_of(vm, n, k),
+        vm * k + groups * n * k + vm * n * 2)
     return rows
 
 

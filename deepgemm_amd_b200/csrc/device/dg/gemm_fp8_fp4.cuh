@@ -135,7 +135,8 @@ struct GemmParams {
 // of its waits, and in its whole loop, to profile[slot]; without it the calls compile to nothing.
 enum ProfileSlot : uint32_t {
     kProfProducerWaitEmpty = 0, kProfProducerTotal = 1, kProfMmaWaitFull = 2, kProfMmaWaitTmemEmpty = 3, kProfMmaTotal = 4,
-    kProfSFWait = 5, kProfSFTotal = 6, kProfEpiWaitTmemFull = 7, kProfEpiTotal = 8, kProfEpiStoreWait = 9, kProfNumSlots = 16
+    kProfSFWait = 5, kProfSFTotal = 6, kProfEpiWaitTmemFull = 7, kProfEpiTotal = 8, kProfEpiStoreWait = 9,
+    kProfMmaIssueCp = 10, kProfMmaIssueMma = 11, kProfMmaIssueCommit = 12, kProfNumSlots = 16
 };
 #if defined(DG_PROFILE) && DG_PROFILE
 #define DG_PROF_BEGIN(var) const long long var = clock64()
@@ -307,7 +308,8 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
             };
             bool ok = true;
             uint32_t tile_iter = 0;
-            long long prof_full = 0, prof_tmem = 0; (void)prof_full; (void)prof_tmem;
+            long long prof_full = 0, prof_tmem = 0, prof_cp = 0, prof_mma = 0, prof_commit = 0;
+            (void)prof_full; (void)prof_tmem; (void)prof_cp; (void)prof_mma; (void)prof_commit;
             DG_PROF_BEGIN(prof_t0);
             while (ok && sched.next(tile)) {
                 const uint32_t accum = tile_iter & 1, accum_phase = (tile_iter >> 1) & 1;
@@ -323,6 +325,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                     DG_PROF_ADD(prof_full, prof_w1);
                     tc_fence_after_sync();
                     // Scales: shared memory (rearranged by warp 2) -> tensor memory, in every CTA of the cluster
+                    DG_PROF_BEGIN(prof_i0);
                     if (kb % kSFAPeriod == 0)
                         tc_cp_32x128b_warpx4<kCluster>(tmem_base + kTmemColSFA,
                                                        make_smem_desc(smem_base + kSmemSFA + stage * kSFABytes, 0, 128, kSwizzleNone));
@@ -332,6 +335,8 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                             tc_cp_32x128b_warpx4<kCluster>(tmem_base + kTmemColSFB + i * 4,
                                                            make_smem_desc(smem_base + kSmemSFB + stage * kSFBBytes + i * 512, 0, 128, kSwizzleNone));
                     }
+                    DG_PROF_ADD(prof_cp, prof_i0);
+                    DG_PROF_BEGIN(prof_i1);
                     const uint64_t a_desc = make_smem_desc(smem_base + kSmemA + stage * kABytes, kALbo, 1024, kSwizzle128B);
                     const uint64_t b_desc = make_smem_desc(smem_base + kSmemB + stage * kBBytes, kBLbo, 1024, kSwizzle128B);
                     #pragma unroll
@@ -344,9 +349,12 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                                                   instr_desc_with_sf_ids(idesc, sfa_id, sfb_id),
                                                   tmem_base + kTmemColSFA, tmem_base + kTmemColSFB, (kb | j) != 0);
                     }
+                    DG_PROF_ADD(prof_mma, prof_i1);
+                    DG_PROF_BEGIN(prof_i2);
                     commit_all(empty_bar(stage));                      // releases the stage once its MMAs have read it
                     if (kb + 1 == num_k_blocks)
                         commit_all(tmem_full_bar(accum));              // accumulator complete
+                    DG_PROF_ADD(prof_commit, prof_i2);
                 }
             }
             long long prof_total = 0; (void)prof_total;
@@ -354,6 +362,9 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
             DG_PROF_FLUSH(kProfMmaWaitFull, prof_full);
             DG_PROF_FLUSH(kProfMmaWaitTmemEmpty, prof_tmem);
             DG_PROF_FLUSH(kProfMmaTotal, prof_total);
+            DG_PROF_FLUSH(kProfMmaIssueCp, prof_cp);
+            DG_PROF_FLUSH(kProfMmaIssueMma, prof_mma);
+            DG_PROF_FLUSH(kProfMmaIssueCommit, prof_commit);
         }
     } else if (warp_idx == 2) {
         // ================= scale rearrangement =================

@@ -315,10 +315,10 @@ int run_gemm(int kind, const dg_gemm_args_t* a) {
         DG_CUDA_RT(cudaMemcpyAsync(h, params.profile, sizeof(h), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(a->stream)));
         DG_CUDA_RT(cudaStreamSynchronize(static_cast<cudaStream_t>(a->stream)));
         const double ctas = cfg.num_ctas, leaders = ctas / cfg.cluster_size;
-        fprintf(stderr, "[dg profile] cycles per CTA: producer wait_empty %.0f / %.0f | mma wait_full %.0f wait_tmem_empty %.0f / %.0f | "
-                        "sf wait %.0f / %.0f | epilogue wait_tmem_full %.0f store_wait %.0f / %.0f\n",
-                h[0] / ctas, h[1] / ctas, h[2] / leaders, h[3] / leaders, h[4] / leaders, h[5] / ctas, h[6] / ctas,
-                h[7] / ctas, h[9] / ctas, h[8] / ctas);
+        fprintf(stderr, "[dg profile] cycles per CTA: producer wait_empty %.0f / %.0f | mma wait_full %.0f wait_tmem_empty %.0f "
+                        "issue cp %.0f mma %.0f commit %.0f / %.0f | sf wait %.0f / %.0f | epilogue wait_tmem_full %.0f store_wait %.0f / %.0f\n",
+                h[0] / ctas, h[1] / ctas, h[2] / leaders, h[3] / leaders, h[10] / leaders, h[11] / leaders, h[12] / leaders,
+                h[4] / leaders, h[5] / ctas, h[6] / ctas, h[7] / ctas, h[9] / ctas, h[8] / ctas);
         return DG_OK;
     }
     return dg_jit_launch(kernel, cfg.num_ctas, 256, cfg.cluster_size, cfg.smem_bytes, state().pdl, a->stream, kargs);
