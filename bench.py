@@ -117,7 +117,12 @@ def cpu_step(inputs):
     return oracle.bf16_round(oracle.dequant_gemm_nt(qa, sfa, qb, sfb))
 
 
+_CPU_THREADS_USED = None
+
+
 def cpu_threads():
+    if _CPU_THREADS_USED is not None:
+        return _CPU_THREADS_USED
     try:
         from threadpoolctl import threadpool_info
         blas = [p["num_threads"] for p in threadpool_info() if p.get("user_api") == "blas"]
@@ -131,12 +136,26 @@ def cpu_threads():
 def time_cpu(steps, warmup):
     import numpy  # noqa: F401  (make sure BLAS is loaded before counting threads)
     inputs = cpu_sample_inputs()
+    # Use every host core this process may run on (torchrun exports OMP_NUM_THREADS=1 for its workers)
+    try:
+        ncpu = len(os.sched_getaffinity(0))
+    except AttributeError:
+        ncpu = os.cpu_count() or 1
+    try:
+        from threadpoolctl import threadpool_limits
+        limiter = threadpool_limits(limits=ncpu)
+    except Exception:
+        limiter = None
     for _ in range(warmup):
         cpu_step(inputs)
     t0 = time.perf_counter()
     for _ in range(steps):
         cpu_step(inputs)
     dt = (time.perf_counter() - t0) / max(steps, 1)
+    global _CPU_THREADS_USED
+    _CPU_THREADS_USED = cpu_threads()
+    if limiter is not None:
+        limiter.restore_original_limits()
     n, k = CPU_SAMPLE_NK
     return flops_of(M_DENSE, n, k) / dt / 1e12, dt
 
@@ -245,6 +264,7 @@ def main():
     if dg.kernel_status() != 0:
         raise SystemExit(f"kernel reported status {dg.kernel_status():#x}")
 
+    barrier()                      # first collective initialises NCCL: keep that out of the sampled region
     with ClockSampler(local_rank) as clocks:
         dt = time_events(step, args.steps, torch, barrier)
     t = torch.tensor([dt], dtype=torch.float64, device="cuda")

@@ -28,7 +28,10 @@ struct GemmLayout {
     }
     DG_HDC uint32_t store_cols() const { return store_row_bytes() / d_elem_bytes; }
     DG_HDC uint32_t num_stores() const { return block_n / store_cols(); }
-    DG_HDC uint32_t store_stage_bytes() const { return block_m * store_row_bytes(); }
+    // The epilogue drains 128 bytes of every D row per synchronisation ("group"): 1, 2 or 4 store boxes side by side
+    DG_HDC uint32_t group_cols() const { return 128 / d_elem_bytes; }
+    DG_HDC uint32_t num_groups() const { return (block_n + group_cols() - 1) / group_cols(); }
+    DG_HDC uint32_t store_stage_bytes() const { return block_m * 128; }
     DG_HDC uint32_t num_store_stages() const { return 2; }
 
     DG_HDC uint32_t a_bytes() const { return block_m * block_k; }        // one byte per element (FP8, or FP4 in 16-byte containers)

@@ -12,8 +12,9 @@
 //               tcgen05.mma.kind::mxf8f6f4.block_scale into one of two accumulator stages
 //   warp 2      allocates tensor memory; rearranges each scale chunk for tcgen05.cp
 //   warp 3      idle
-//   warps 4-7   epilogue: tcgen05.ld -> alpha -> bf16/fp32 -> swizzled staging -> TMA store
-//               (row-predicated direct stores for ragged tiles of the masked layout)
+//   warps 4-7   epilogue: tcgen05.ld -> alpha -> bf16/fp32 -> swizzled staging -> TMA store, 128 bytes of every
+//               row (1, 2 or 4 store boxes) per synchronisation (row-predicated direct stores for ragged tiles
+//               of the masked layout)
 //
 // The configuration arrives as DG_* macros set by the host-side code generator:
 //   DG_GEMM_TYPE (0 dense, 1 m-grouped contiguous, 2 m-grouped masked), DG_BLOCK_N, DG_NUM_STAGES,
@@ -89,6 +90,9 @@ constexpr uint32_t kBAtoms = kLayout.b_atoms();            // 128-column atoms o
 constexpr uint32_t kStoreRowBytes   = kLayout.store_row_bytes();
 constexpr uint32_t kStoreCols       = kLayout.store_cols();          // columns of D per TMA store
 constexpr uint32_t kNumStores       = kLayout.num_stores();
+constexpr uint32_t kGroupCols       = kLayout.group_cols();          // columns of D drained per epilogue synchronisation
+constexpr uint32_t kNumGroups       = kLayout.num_groups();
+constexpr uint32_t kStoreBoxBytes   = BLOCK_M * kStoreRowBytes;      // one TMA store box in the staging buffer
 constexpr uint32_t kNumStoreStages  = kLayout.num_store_stages();
 constexpr uint32_t kStoreStageBytes = kLayout.store_stage_bytes();
 constexpr uint32_t kSmemD   = kLayout.off_d();
@@ -139,10 +143,12 @@ enum ProfileSlot : uint32_t {
     kProfMmaIssueCp = 10, kProfMmaIssueMma = 11, kProfMmaIssueCommit = 12, kProfNumSlots = 16
 };
 #if defined(DG_PROFILE) && DG_PROFILE
+#define DG_PROF_VAR(name) long long name = 0
 #define DG_PROF_BEGIN(var) const long long var = clock64()
 #define DG_PROF_ADD(acc, var) acc += clock64() - var
 #define DG_PROF_FLUSH(slot, acc) do { if (p.profile != nullptr) atomicAdd(p.profile + (slot), static_cast<unsigned long long>(acc)); } while (0)
 #else
+#define DG_PROF_VAR(name) do { } while (0)
 #define DG_PROF_BEGIN(var) do { } while (0)
 #define DG_PROF_ADD(acc, var) do { } while (0)
 #define DG_PROF_FLUSH(slot, acc) do { } while (0)
@@ -238,7 +244,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
         // ================= TMA producer (every CTA loads its own rows of A and its share of B) =================
         if (lane == 0) {
             bool ok = true;
-            long long prof_wait = 0; (void)prof_wait;
+            DG_PROF_VAR(prof_wait);
             DG_PROF_BEGIN(prof_t0);
             while (ok && sched.next(tile)) {
                 // Row coordinates of this CTA's part of the tile in the 2-D views of A, B and the scale tensors
@@ -283,7 +289,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                     }
                 }
             }
-            long long prof_total = 0; (void)prof_total;
+            DG_PROF_VAR(prof_total);
             DG_PROF_ADD(prof_total, prof_t0);
             DG_PROF_FLUSH(kProfProducerWaitEmpty, prof_wait);
             DG_PROF_FLUSH(kProfProducerTotal, prof_total);
@@ -308,8 +314,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
             };
             bool ok = true;
             uint32_t tile_iter = 0;
-            long long prof_full = 0, prof_tmem = 0, prof_cp = 0, prof_mma = 0, prof_commit = 0;
-            (void)prof_full; (void)prof_tmem; (void)prof_cp; (void)prof_mma; (void)prof_commit;
+            DG_PROF_VAR(prof_full); DG_PROF_VAR(prof_tmem); DG_PROF_VAR(prof_cp); DG_PROF_VAR(prof_mma); DG_PROF_VAR(prof_commit);
             DG_PROF_BEGIN(prof_t0);
             while (ok && sched.next(tile)) {
                 const uint32_t accum = tile_iter & 1, accum_phase = (tile_iter >> 1) & 1;
@@ -357,7 +362,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                     DG_PROF_ADD(prof_commit, prof_i2);
                 }
             }
-            long long prof_total = 0; (void)prof_total;
+            DG_PROF_VAR(prof_total);
             DG_PROF_ADD(prof_total, prof_t0);
             DG_PROF_FLUSH(kProfMmaWaitFull, prof_full);
             DG_PROF_FLUSH(kProfMmaWaitTmemEmpty, prof_tmem);
@@ -379,7 +384,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
             st_shared_v4(chunk_addr + lane * 16, v[0], v[1], v[2], v[3]);
         };
         bool ok = true;
-        long long prof_wait = 0; (void)prof_wait;
+        DG_PROF_VAR(prof_wait);
         DG_PROF_BEGIN(prof_t0);
         while (ok && sched.next(tile)) {
             for (uint32_t kb = 0; kb < num_k_blocks; ++kb, advance_stage()) {
@@ -399,7 +404,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
             }
         }
         if (lane == 0) {
-            long long prof_total = 0; (void)prof_total;
+            DG_PROF_VAR(prof_total);
             DG_PROF_ADD(prof_total, prof_t0);
             DG_PROF_FLUSH(kProfSFWait, prof_wait);
             DG_PROF_FLUSH(kProfSFTotal, prof_total);
@@ -411,7 +416,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
         const uint32_t epi_tid = threadIdx.x - kEpilogueWarpBase * 32;
         bool ok = true;
         uint32_t tile_iter = 0, store_iter = 0;
-        long long prof_wait = 0, prof_store = 0; (void)prof_wait; (void)prof_store;
+        DG_PROF_VAR(prof_wait); DG_PROF_VAR(prof_store);
         DG_PROF_BEGIN(prof_t0);
         while (ok && sched.next(tile)) {
             const uint32_t accum = tile_iter & 1, accum_phase = (tile_iter >> 1) & 1;
@@ -430,101 +435,111 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                                         (tile.valid_rows - rows_before < BLOCK_M ? tile.valid_rows - rows_before : BLOCK_M);
             const bool direct = kGemmType == 2 && valid_rows < BLOCK_M;
 
-            #pragma unroll 1
-            for (uint32_t s = 0; s < kNumStores; ++s) {
-                constexpr uint32_t kLoadsPerStore = kStoreCols / 16;
-                uint32_t v[kLoadsPerStore][16];
+            #pragma unroll
+            for (uint32_t g = 0; g < kNumGroups; ++g) {
+                // Columns [g * kGroupCols, + kCols) of the tile: up to 128 bytes of every row
+                const uint32_t kCols = (g + 1) * kGroupCols <= BLOCK_N ? kGroupCols : BLOCK_N - g * kGroupCols;
+                constexpr uint32_t kMaxLoads = kGroupCols / 16;
+                uint32_t v[kMaxLoads][16];
                 #pragma unroll
-                for (uint32_t l = 0; l < kLoadsPerStore; ++l)
-                    tmem_ld_32x32b_x16(tmem_row_addr + s * kStoreCols + l * 16, v[l]);
+                for (uint32_t l = 0; l < kMaxLoads; ++l)
+                    if (l * 16 < kCols) tmem_ld_32x32b_x16(tmem_row_addr + g * kGroupCols + l * 16, v[l]);
                 tmem_ld_wait();
-                if (s + 1 == kNumStores) {
+                if (g + 1 == kNumGroups) {
                     // The accumulator is in registers: hand the tensor-memory stage back to the MMA warp
                     tc_fence_before_sync();
                     if (kCluster == 1 || is_leader) mbar_arrive(tmem_empty_bar(accum));
                     else mbar_arrive_cluster(in_leader(tmem_empty_bar(accum)));
                 }
                 #pragma unroll
-                for (uint32_t l = 0; l < kLoadsPerStore; ++l)
-                    #pragma unroll
-                    for (uint32_t i = 0; i < 16; ++i)
-                        v[l][i] = __float_as_uint(__uint_as_float(v[l][i]) * p.alpha);
+                for (uint32_t l = 0; l < kMaxLoads; ++l)
+                    if (l * 16 < kCols) {
+                        #pragma unroll
+                        for (uint32_t i = 0; i < 16; ++i)
+                            v[l][i] = __float_as_uint(__uint_as_float(v[l][i]) * p.alpha);
+                    }
+                const uint32_t col0 = n0 + g * kGroupCols;
 
                 if (!direct) {
                     const uint32_t sb = store_iter & 1;
                     ++store_iter;
-                    // The staging buffer is free once the TMA store issued two stores ago has read it
+                    // The staging buffer is free once the TMA stores issued two groups ago have read it
                     DG_PROF_BEGIN(prof_s);
                     if (epi_tid == 0) tma_store_wait_read<kNumStoreStages - 1>();
                     named_barrier_sync(1, kNumEpilogueThreads);
                     DG_PROF_ADD(prof_store, prof_s);
                     const uint32_t stage_addr = smem_base + kSmemD + sb * kStoreStageBytes;
-                    const uint32_t row_off = row_in_tile * kStoreRowBytes;
                     constexpr uint32_t kSwizzleMask = kStoreRowBytes == 128 ? 7 : (kStoreRowBytes == 64 ? 3 : 1);
-                    if constexpr (!kDIsFP32) {
-                        #pragma unroll
-                        for (uint32_t c = 0; c < kStoreRowBytes / 16; ++c) {        // 16-byte chunk = 8 bf16
-                            const uint32_t l = c / 2, i0 = (c % 2) * 8;
-                            const uint32_t off = row_off + c * 16;
+                    constexpr uint32_t kElemsPerChunk = 16 / kDElemBytes;                 // 8 bf16 or 4 fp32 per 16 bytes
+                    #pragma unroll
+                    for (uint32_t c = 0; c < kGroupCols / kElemsPerChunk; ++c) {
+                        if (c * kElemsPerChunk < kCols) {
+                            // chunk c of the row lives in store box (c * 16 / row bytes), at swizzled chunk position
+                            const uint32_t box = (c * 16) / kStoreRowBytes, in_row = (c * 16) % kStoreRowBytes;
+                            const uint32_t off = row_in_tile * kStoreRowBytes + in_row;
                             const uint32_t phys = off ^ (((off >> 7) & kSwizzleMask) << 4);
-                            st_shared_v4(stage_addr + phys,
-                                         pack_bf16x2(__uint_as_float(v[l][i0 + 0]), __uint_as_float(v[l][i0 + 1])),
-                                         pack_bf16x2(__uint_as_float(v[l][i0 + 2]), __uint_as_float(v[l][i0 + 3])),
-                                         pack_bf16x2(__uint_as_float(v[l][i0 + 4]), __uint_as_float(v[l][i0 + 5])),
-                                         pack_bf16x2(__uint_as_float(v[l][i0 + 6]), __uint_as_float(v[l][i0 + 7])));
-                        }
-                    } else {
-                        #pragma unroll
-                        for (uint32_t c = 0; c < kStoreRowBytes / 16; ++c) {        // 16-byte chunk = 4 fp32
-                            const uint32_t l = c / 4, i0 = (c % 4) * 4;
-                            const uint32_t off = row_off + c * 16;
-                            const uint32_t phys = off ^ (((off >> 7) & kSwizzleMask) << 4);
-                            st_shared_v4(stage_addr + phys, v[l][i0], v[l][i0 + 1], v[l][i0 + 2], v[l][i0 + 3]);
+                            const uint32_t e0 = c * kElemsPerChunk, l = e0 / 16, i0 = e0 % 16;
+                            if constexpr (!kDIsFP32)
+                                st_shared_v4(stage_addr + box * kStoreBoxBytes + phys,
+                                             pack_bf16x2(__uint_as_float(v[l][i0 + 0]), __uint_as_float(v[l][i0 + 1])),
+                                             pack_bf16x2(__uint_as_float(v[l][i0 + 2]), __uint_as_float(v[l][i0 + 3])),
+                                             pack_bf16x2(__uint_as_float(v[l][i0 + 4]), __uint_as_float(v[l][i0 + 5])),
+                                             pack_bf16x2(__uint_as_float(v[l][i0 + 6]), __uint_as_float(v[l][i0 + 7])));
+                            else
+                                st_shared_v4(stage_addr + box * kStoreBoxBytes + phys, v[l][i0], v[l][i0 + 1], v[l][i0 + 2], v[l][i0 + 3]);
                         }
                     }
                     fence_proxy_async_smem();
                     named_barrier_sync(1, kNumEpilogueThreads);
                     if (epi_tid == 0) {
-                        if constexpr (kAccumulate)
-                            tma_reduce_add_2d(&tm_d, stage_addr, static_cast<int32_t>(n0 + s * kStoreCols), static_cast<int32_t>(d_row0));
-                        else
-                            tma_store_2d(&tm_d, stage_addr, static_cast<int32_t>(n0 + s * kStoreCols), static_cast<int32_t>(d_row0));
+                        #pragma unroll
+                        for (uint32_t box = 0; box < kGroupCols / kStoreCols; ++box) {
+                            if (box * kStoreCols < kCols) {
+                                if constexpr (kAccumulate)
+                                    tma_reduce_add_2d(&tm_d, stage_addr + box * kStoreBoxBytes, static_cast<int32_t>(col0 + box * kStoreCols),
+                                                      static_cast<int32_t>(d_row0));
+                                else
+                                    tma_store_2d(&tm_d, stage_addr + box * kStoreBoxBytes, static_cast<int32_t>(col0 + box * kStoreCols),
+                                                 static_cast<int32_t>(d_row0));
+                            }
+                        }
                         tma_store_commit();
                     }
                 } else {
                     // Ragged tile of the masked layout: rows at or beyond the group's row count stay untouched
                     if (row_in_tile < valid_rows) {
-                        const uint32_t col0 = n0 + s * kStoreCols;
                         if constexpr (!kDIsFP32) {
                             __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.d) +
                                                   static_cast<size_t>(d_row0 + row_in_tile) * p.ldd;
                             #pragma unroll
-                            for (uint32_t c = 0; c < kStoreCols / 8; ++c) {
-                                const uint32_t l = c / 2, i0 = (c % 2) * 8, col = col0 + c * 8;
-                                if (col + 8 <= p.shape_n) {
-                                    uint4 q;
-                                    q.x = pack_bf16x2(__uint_as_float(v[l][i0 + 0]), __uint_as_float(v[l][i0 + 1]));
-                                    q.y = pack_bf16x2(__uint_as_float(v[l][i0 + 2]), __uint_as_float(v[l][i0 + 3]));
-                                    q.z = pack_bf16x2(__uint_as_float(v[l][i0 + 4]), __uint_as_float(v[l][i0 + 5]));
-                                    q.w = pack_bf16x2(__uint_as_float(v[l][i0 + 6]), __uint_as_float(v[l][i0 + 7]));
-                                    *reinterpret_cast<uint4*>(drow + col) = q;
-                                } else {
-                                    for (uint32_t e = 0; e < 8 && col + e < p.shape_n; ++e)
-                                        drow[col + e] = __float2bfloat16_rn(__uint_as_float(v[l][i0 + e]));
+                            for (uint32_t c = 0; c < kGroupCols / 8; ++c) {
+                                if (c * 8 < kCols) {
+                                    const uint32_t l = c / 2, i0 = (c % 2) * 8, col = col0 + c * 8;
+                                    if (col + 8 <= p.shape_n) {
+                                        uint4 q;
+                                        q.x = pack_bf16x2(__uint_as_float(v[l][i0 + 0]), __uint_as_float(v[l][i0 + 1]));
+                                        q.y = pack_bf16x2(__uint_as_float(v[l][i0 + 2]), __uint_as_float(v[l][i0 + 3]));
+                                        q.z = pack_bf16x2(__uint_as_float(v[l][i0 + 4]), __uint_as_float(v[l][i0 + 5]));
+                                        q.w = pack_bf16x2(__uint_as_float(v[l][i0 + 6]), __uint_as_float(v[l][i0 + 7]));
+                                        *reinterpret_cast<uint4*>(drow + col) = q;
+                                    } else {
+                                        for (uint32_t e = 0; e < 8 && col + e < p.shape_n; ++e)
+                                            drow[col + e] = __float2bfloat16_rn(__uint_as_float(v[l][i0 + e]));
+                                    }
                                 }
                             }
                         } else {
                             float* drow = reinterpret_cast<float*>(p.d) + static_cast<size_t>(d_row0 + row_in_tile) * p.ldd;
                             #pragma unroll
-                            for (uint32_t c = 0; c < kStoreCols; ++c)
-                                if (col0 + c < p.shape_n) drow[col0 + c] = __uint_as_float(v[c / 16][c % 16]);
+                            for (uint32_t c = 0; c < kGroupCols; ++c)
+                                if (c < kCols && col0 + c < p.shape_n) drow[col0 + c] = __uint_as_float(v[c / 16][c % 16]);
                         }
                     }
                 }
             }
         }
         if (epi_tid == 0) {
-            long long prof_total = 0; (void)prof_total;
+            DG_PROF_VAR(prof_total);
             DG_PROF_ADD(prof_total, prof_t0);
             DG_PROF_FLUSH(kProfEpiWaitTmemFull, prof_wait);
             DG_PROF_FLUSH(kProfEpiStoreWait, prof_store);

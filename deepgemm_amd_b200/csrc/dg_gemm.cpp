@@ -146,7 +146,7 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
             const double l2_feed = (16384.0 + 128.0 * bn / cluster) / 67.0;
             const GemmLayout lay{128, static_cast<uint32_t>(bn), 128, 2, static_cast<uint32_t>(d_elem), static_cast<uint32_t>(cluster),
                                  p.b_mn_major ? 1u : 0u};
-            const double epilogue = 300.0 + 40.0 * lay.num_stores() + bn * 2.0;
+            const double epilogue = 300.0 + 150.0 * lay.num_groups() + 20.0 * lay.num_stores() + bn * 2.0;
             // The epilogue of a tile overlaps the next tile's main loop; it is exposed once per CTA
             const double per_tile = static_cast<double>(k_blocks) * std::max(mma, std::max(smem_feed, l2_feed));
             const double cost = static_cast<double>(waves) * std::max(per_tile, epilogue) + epilogue + 2000.0;
