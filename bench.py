@@ -31,6 +31,10 @@ M_DENSE = 4096
 DENSE_NK = [(2112, 7168), (24576, 1536), (32768, 512), (7168, 16384), (4096, 7168), (7168, 2048)]
 NOMINAL_FP8_TFLOPS = 4500.0
 CPU_SAMPLE_NK = (2112, 7168)          # the bounded sample the CPU arm times (1 of the 6 shapes)
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of dg_gemm_fp8_fp4 at M = 4096, from one ncu capture of this
+# script (profiles/dg_gemm_fp8_fp4_dense_m4096.md); D written late in a launch may still sit in L2 when it ends.
+NCU_DRAM_BYTES = {(2112, 7168): 46445824, (24576, 1536): 228799232, (32768, 512): 247536128,
+                  (7168, 16384): 480479232, (4096, 7168): 73676288, (7168, 2048): 31463680}
 
 
 def flops_of(m, n, k):
@@ -313,6 +317,9 @@ def main():
     # The dominant (only) kernel of the step is the tcgen05 GEMM; FP8 runs at twice the BF16 tensor rate, so the
     # measured denominator is 2 x the cuBLAS BF16 figure (sustained: the kernel is timed inside a long loop).
     peak_fp8 = 2.0 * peaks["bf16_sustained"]
+    known = [NCU_DRAM_BYTES.get((c["n"], c["k"])) for c in cases]
+    traffic = None if any(v is None for v in known) else round(sum(known) / len(known))
+    algorithmic = sum(c["m"] * c["k"] + c["n"] * c["k"] + c["m"] * c["n"] * 2 + (c["m"] + c["n"]) * (c["k"] // 128) for c in cases) / len(cases)
     line = {
         "metric": "dense_fp8_gemm_tflops", "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt_max / args.steps * 1e3, 4),
@@ -325,7 +332,8 @@ def main():
                    "parallelism": f"replicated shards x{world}, no collective in the timed region"},
         "pct_of_nominal_fp8_peak": round(100.0 * per_gpu / NOMINAL_FP8_TFLOPS, 2),
         "roofline": {"bound": "tensor", "achieved": round(per_gpu, 2), "peak": round(peak_fp8, 1), "unit": "TFLOP/s",
-                     "frac": round(per_gpu / peak_fp8, 4), "traffic": None,
+                     "frac": round(per_gpu / peak_fp8, 4), "traffic": traffic, "traffic_unit": "bytes per launch (mean of the step's launches)",
+                     "algorithmic_bytes_per_launch": round(algorithmic),
                      "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peaks['source']}); nominal FP8 dense 4500",
                      "frac_of_nominal": round(per_gpu / NOMINAL_FP8_TFLOPS, 4)},
         "clocks": clk,
