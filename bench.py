@@ -369,13 +369,19 @@ def make_grouped_b(groups, n, k, fp4, torch, dg):
 
 
 def detail_rows(torch, dg):
-    """Per-case device times (256 MB L2 flush before every call) for BASELINE configs 2-5.  TFLOP/s counts valid
+    """Per-case kernel times (torch profiler records, 256 MB L2 flush before every call) for BASELINE configs 2-5.  TFLOP/s counts valid
     rows only and GB/s the bytes of A, B, D and scales, as the reference's tests print them
     (tests/test_fp8_fp4.py:108-111,170-174,229-237)."""
     import random
-    from deepgemm_amd_b200.testing import bench
+    from deepgemm_amd_b200.testing import bench_kineto
     from deepgemm_amd_b200.utils import per_token_cast_to_fp4, per_token_cast_to_fp8
     rows = []
+    kernels = ("dg_gemm_fp8_fp4", "splitk_reduce_kernel")      # the split-K second pass counts as part of the GEMM
+
+    def bench(fn, warmups, tests):
+        for _ in range(warmups):
+            fn()
+        return bench_kineto(fn, kernels, tests)
 
     def add(case, t, flops, byts):
         rows.append({"case": case, "us": round(t * 1e6, 1), "tflops": round(flops / t / 1e12, 1), "gbs": round(byts / t / 1e9, 0)})

@@ -49,7 +49,7 @@ struct GemmLayout {
     DG_HDC uint32_t off_barriers() const { return off_sfb() + num_stages * sfb_bytes(); }
     DG_HDC uint32_t num_barriers() const { return 3 * num_stages + 2 * 2; }
     DG_HDC uint32_t off_misc() const { return off_barriers() + num_barriers() * 8; }
-    DG_HDC uint32_t total_bytes() const { return off_misc() + 16; }
+    DG_HDC uint32_t total_bytes() const { return off_misc() + 16; }      // tensor-memory base, abort flag
     DG_HDC uint32_t bytes_per_stage() const { return a_bytes() + b_bytes() + sfa_bytes() + sfb_bytes() + 3 * 8; }
 
     // Tensor memory: two accumulator stages, then SFA (4 columns per 128 rows) and SFB

@@ -19,7 +19,13 @@
 // The configuration arrives as DG_* macros set by the host-side code generator:
 //   DG_GEMM_TYPE (0 dense, 1 m-grouped contiguous, 2 m-grouped masked), DG_BLOCK_N, DG_NUM_STAGES,
 //   DG_CLUSTER, DG_A_FP4, DG_B_FP4, DG_MAJOR_A, DG_MAJOR_B (0 K-major, 1 MN-major), DG_GRAN_K_A, DG_GRAN_K_B,
-//   DG_D_FP32, DG_ACCUMULATE, DG_RASTER_GROUP.
+//   DG_D_FP32, DG_ACCUMULATE, DG_RASTER_GROUP, DG_SPLIT_K.
+//
+// DG_SPLIT_K (dense only, for shapes with too few output tiles to fill the GPU): every output tile becomes
+// num_splits work items over slices of K, and the kernel's D is an FP32 workspace of num_splits stacked
+// [rows x N] panels: work item (tile, slice) stores its partial tile into panel `slice`.  A separate kernel
+// (dg_splitk.cu) then adds the panels in slice order, applies alpha and converts, so the result does not
+// depend on which CTA finished first.
 //
 // MN-major operands (the nn / tn / tt variants): the tile is staged as [128 of K][128 B of MN] atoms with the
 // same 128-byte swizzle (one TMA box per 128 columns of MN), the descriptor's leading-dimension offset steps
@@ -60,6 +66,7 @@ constexpr uint32_t kGranKB     = DG_GRAN_K_B;
 constexpr bool     kDIsFP32    = DG_D_FP32 != 0;
 constexpr bool     kAccumulate = DG_ACCUMULATE != 0;
 constexpr uint32_t kRasterGroup = DG_RASTER_GROUP;
+constexpr bool     kSplitK     = DG_SPLIT_K != 0;
 
 constexpr uint32_t UMMA_M = 128 * kCluster, UMMA_N = BLOCK_N, UMMA_K = 32;
 constexpr uint32_t LOAD_BLOCK_N = BLOCK_N / kCluster;      // rows of B each CTA loads
@@ -74,6 +81,7 @@ static_assert(kNumStages >= 2 && kNumStages <= 32, "pipeline depth");
 static_assert(kCluster == 1 || kCluster == 2, "one CTA or a CTA pair per tile");
 static_assert(!(kAIsFP4 && kAMnMajor) && !(kBIsFP4 && kBMnMajor), "packed FP4 operands must be K-major");
 static_assert(!kBMnMajor || (BLOCK_N / kCluster) % 16 == 0, "an MN-major B load must start on a 16-byte boundary");
+static_assert(!kSplitK || (kGemmType == 0 && kDIsFP32 && !kAccumulate), "split-K serves the plain dense GEMM and writes FP32 partials");
 
 // Scales: a packed int32 holds 4 scales.  With one scale per 128 K it spans 4 K-blocks, so the
 // chunk is fetched on every 4th K-block; with one per 32 K it spans exactly one K-block.
@@ -133,6 +141,9 @@ struct GemmParams {
     uint32_t ldd;                // row pitch of D in elements
     float alpha;
     unsigned long long* profile; // optional cycle counters (kernels built with DG_PROFILE only), else null
+    uint32_t num_splits;         // slices of K per output tile (1 = no split)
+    uint32_t kb_per_split;       // K-blocks per slice, a multiple of 4 so every slice starts on a packed scale word
+    uint32_t split_panel_rows;   // split-K: rows between consecutive slices' panels in the workspace D points to
 };
 
 // Wait-time accounting for tuning: with DG_PROFILE defined every role adds the cycles it spent inside each
@@ -147,7 +158,10 @@ enum ProfileSlot : uint32_t {
 #define DG_PROF_BEGIN(var) const long long var = clock64()
 #define DG_PROF_ADD(acc, var) acc += clock64() - var
 #define DG_PROF_FLUSH(slot, acc) do { if (p.profile != nullptr) atomicAdd(p.profile + (slot), static_cast<unsigned long long>(acc)); } while (0)
+// Timeline of CTA 0 in nanoseconds (globaltimer): slots 16.. hold absolute stamps, first writer wins
+#define DG_PROF_STAMP(slot) do { if (p.profile != nullptr && blockIdx.x == 0) atomicCAS(p.profile + 16 + (slot), 0ull, global_timer_ns()); } while (0)
 #else
+#define DG_PROF_STAMP(slot) do { } while (0)
 #define DG_PROF_VAR(name) do { } while (0)
 #define DG_PROF_BEGIN(var) do { } while (0)
 #define DG_PROF_ADD(acc, var) do { } while (0)
@@ -185,6 +199,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
 
     // ---- set-up -------------------------------------------------------------------------------
     if (threadIdx.x == 0) {
+        DG_PROF_STAMP(0);                                   // kernel entry
         *abort_flag = 0;
         prefetch_tensormap(&tm_a);
         prefetch_tensormap(&tm_b);
@@ -225,6 +240,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
     }
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_base_slot;
+    if (threadIdx.x == 0) DG_PROF_STAMP(1);                 // set-up done (barriers, tensor memory)
 
     const uint32_t num_k_blocks = (p.shape_k + BLOCK_K - 1) / BLOCK_K;
     const uint32_t sfa_rows_per_group = (p.shape_k + kGranKA * 4 - 1) / (kGranKA * 4);   // packed K extent of SFA
@@ -232,7 +248,14 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
 
     // A cluster walks the tile list as one unit
     TileScheduler<kGemmType> sched(TILE_M, BLOCK_N, kRasterGroup, p.shape_m, p.shape_n, p.num_groups, p.grouped_layout,
-                                   blockIdx.x / kCluster, gridDim.x / kCluster);
+                                   blockIdx.x / kCluster, gridDim.x / kCluster, kSplitK ? p.num_splits : 1u);
+    // K-blocks [kb_begin, kb_end) of a work item: all of K unless the GEMM is split
+    auto kb_begin = [&](const Tile& t) { return kSplitK ? t.split * p.kb_per_split : 0u; };
+    auto kb_end = [&](const Tile& t) {
+        if constexpr (!kSplitK) return num_k_blocks;
+        const uint32_t e = (t.split + 1) * p.kb_per_split;
+        return e < num_k_blocks ? e : num_k_blocks;
+    };
     Tile tile;
     uint32_t stage = 0, phase = 0;
     auto advance_stage = [&]() {
@@ -253,7 +276,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                 const uint32_t sfa_mn = tile.sfa_mn_base + tile.m_block * TILE_M + cta_rank * BLOCK_M;
                 const uint32_t sfa_row0 = tile.sfa_group * sfa_rows_per_group;
                 const uint32_t sfb_row0 = tile.group * sfb_rows_per_group;
-                for (uint32_t kb = 0; kb < num_k_blocks; ++kb, advance_stage()) {
+                for (uint32_t kb = kb_begin(tile), kb1 = kb_end(tile); kb < kb1; ++kb, advance_stage()) {
                     DG_PROF_BEGIN(prof_w);
                     if (!mbar_wait(empty_bar(stage), phase ^ 1, ctx, kRoleProducer, 1)) { ok = false; break; }
                     DG_PROF_ADD(prof_wait, prof_w);
@@ -324,10 +347,12 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                 DG_PROF_ADD(prof_tmem, prof_w0);
                 tc_fence_after_sync();
                 const uint32_t tmem_d = tmem_base + accum * UMMA_N;
-                for (uint32_t kb = 0; kb < num_k_blocks; ++kb, advance_stage()) {
+                const uint32_t kb0 = kb_begin(tile), kb1 = kb_end(tile);
+                for (uint32_t kb = kb0; kb < kb1; ++kb, advance_stage()) {
                     DG_PROF_BEGIN(prof_w1);
                     if (!mbar_wait(full_bar(stage), phase, ctx, kRoleMma, 2)) { ok = false; break; }
                     DG_PROF_ADD(prof_full, prof_w1);
+                    DG_PROF_STAMP(2);                       // first stage arrived
                     tc_fence_after_sync();
                     // Scales: shared memory (rearranged by warp 2) -> tensor memory, in every CTA of the cluster
                     DG_PROF_BEGIN(prof_i0);
@@ -352,12 +377,12 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                         // Advancing K moves the start address: +32 B inside the swizzle atom (K-major) or +32 rows (MN-major)
                         tc_mma_mxf8f6f4<kCluster>(tmem_d, a_desc + j * kAStepK, b_desc + j * kBStepK,
                                                   instr_desc_with_sf_ids(idesc, sfa_id, sfb_id),
-                                                  tmem_base + kTmemColSFA, tmem_base + kTmemColSFB, (kb | j) != 0);
+                                                  tmem_base + kTmemColSFA, tmem_base + kTmemColSFB, ((kb - kb0) | j) != 0);
                     }
                     DG_PROF_ADD(prof_mma, prof_i1);
                     DG_PROF_BEGIN(prof_i2);
                     commit_all(empty_bar(stage));                      // releases the stage once its MMAs have read it
-                    if (kb + 1 == num_k_blocks)
+                    if (kb + 1 == kb1)
                         commit_all(tmem_full_bar(accum));              // accumulator complete
                     DG_PROF_ADD(prof_commit, prof_i2);
                 }
@@ -387,7 +412,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
         DG_PROF_VAR(prof_wait);
         DG_PROF_BEGIN(prof_t0);
         while (ok && sched.next(tile)) {
-            for (uint32_t kb = 0; kb < num_k_blocks; ++kb, advance_stage()) {
+            for (uint32_t kb = kb_begin(tile), kb1 = kb_end(tile); kb < kb1; ++kb, advance_stage()) {
                 DG_PROF_BEGIN(prof_w);
                 if (!mbar_wait(sf_full_bar(stage), phase, ctx, kRoleSF, 1)) { ok = false; break; }
                 DG_PROF_ADD(prof_wait, prof_w);
@@ -426,7 +451,8 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
             DG_PROF_ADD(prof_wait, prof_w);
             tc_fence_after_sync();
 
-            const uint32_t d_row0 = tile.d_row_base + tile.m_block * TILE_M + cta_rank * BLOCK_M;
+            const uint32_t d_row0 = tile.d_row_base + tile.m_block * TILE_M + cta_rank * BLOCK_M +
+                                    (kSplitK ? tile.split * p.split_panel_rows : 0u);
             const uint32_t n0 = tile.n_block * BLOCK_N;
             const uint32_t tmem_row_addr = tmem_base + ((quarter * 32) << 16) + accum * UMMA_N;
             // Rows of this CTA's half that may be written (fewer than 128 only in a ragged tile of the masked layout)
@@ -546,7 +572,9 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
             DG_PROF_FLUSH(kProfEpiTotal, prof_total);
         }
         // Every byte of D must be in global memory before the grid completes
+        if (epi_tid == 0) DG_PROF_STAMP(4);                 // last store issued
         if (epi_tid == 0) tma_store_wait<0>();
+        if (epi_tid == 0) DG_PROF_STAMP(5);                 // stores complete
     }
 
     // ---- tear-down ------------------------------------------------------------------------------
@@ -567,4 +595,5 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
         tc_fence_after_sync();
         tmem_dealloc<kCluster>(tmem_base, kTmemCols);
     }
+    if (threadIdx.x == 0) DG_PROF_STAMP(6);                 // exit
 }

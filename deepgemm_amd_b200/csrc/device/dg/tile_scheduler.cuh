@@ -33,6 +33,8 @@ struct Tile {
     uint32_t sfa_mn_base;   // first row of the group along the MN axis of SFA
     uint32_t sfa_group;     // group index along the packed-K axis of SFA
     uint32_t valid_rows;    // rows of this tile that may be written (128 unless a ragged masked tile)
+    uint32_t split;         // which slice of K this work item covers (0 unless the GEMM is split along K)
+    uint32_t mn_index;      // linear index of the output tile (slot of its split-K partials and counter)
 };
 
 // Tile sizes are constructor arguments (literal constants in the kernel, which the compiler folds;
@@ -44,15 +46,17 @@ struct TileScheduler {
     uint32_t num_m_blocks, num_n_blocks;
     const int* layout;
     uint32_t cta, num_ctas, iter;
+    uint32_t num_splits;    // dense only: every output tile is computed as num_splits work items over slices of K
     // masked layout only
     uint32_t cur_group, group_first_tile;
 
     DG_HD TileScheduler(uint32_t block_m_, uint32_t block_n_, uint32_t raster_group_,
                         uint32_t shape_m_, uint32_t shape_n_, uint32_t num_groups_, const int* layout_,
-                        uint32_t cta_, uint32_t num_ctas_)
+                        uint32_t cta_, uint32_t num_ctas_, uint32_t num_splits_ = 1)
         : kBlockM(block_m_), kRasterGroup(raster_group_), shape_m(shape_m_), num_groups(num_groups_),
           num_m_blocks((shape_m_ + block_m_ - 1) / block_m_), num_n_blocks((shape_n_ + block_n_ - 1) / block_n_),
-          layout(layout_), cta(cta_), num_ctas(num_ctas_), iter(0), cur_group(0), group_first_tile(0) {}
+          layout(layout_), cta(cta_), num_ctas(num_ctas_), iter(0), num_splits(num_splits_ == 0 ? 1 : num_splits_),
+          cur_group(0), group_first_tile(0) {}
 
     // Linear index inside an (mb x num_n_blocks) grid -> (m, n)
     DG_HD void rasterise(uint32_t idx, uint32_t mb, uint32_t& m, uint32_t& n) const {
@@ -86,10 +90,16 @@ struct TileScheduler {
             t.sfa_group = cur_group;
             const uint32_t left = rows - t.m_block * kBlockM;
             t.valid_rows = left < kBlockM ? left : kBlockM;
+            t.split = 0;
+            t.mn_index = tile_id;
             return true;
         } else {
-            if (tile_id >= num_m_blocks * num_n_blocks) return false;
-            rasterise(tile_id, num_m_blocks, t.m_block, t.n_block);
+            // Work items of one output tile are consecutive, so CTAs that share a tile run at the same time
+            const uint32_t mn = kKind == kDense ? tile_id / num_splits : tile_id;
+            if (mn >= num_m_blocks * num_n_blocks) return false;
+            rasterise(mn, num_m_blocks, t.m_block, t.n_block);
+            t.split = kKind == kDense ? tile_id - mn * num_splits : 0;
+            t.mn_index = mn;
             t.group = 0;
             if constexpr (kKind == kMGroupedContiguous) {
                 const int g = layout[t.m_block * kBlockM];

@@ -6,12 +6,17 @@
 
 #include <algorithm>
 #include <cstring>
+#include <map>
 #include <sstream>
 
 #include "device/dg/gemm_config.hpp"
 #include "device/dg/tile_scheduler.cuh"
 
 namespace dg {
+
+int launch_splitk_reduce(const float* ws, void* d, int m, int n, int64_t ld_ws, int64_t panel_rows, int64_t ldd, int num_splits,
+                         float alpha, bool d_fp32, cudaStream_t stream);      // dg_splitk.cu
+
 namespace {
 
 // Mirror of dg::GemmParams in device/dg/gemm_fp8_fp4.cuh (kernel argument, passed by value)
@@ -22,12 +27,35 @@ struct GemmParams {
     uint32_t shape_m, shape_n, shape_k, num_groups, ldd;
     float alpha;
     unsigned long long* profile;
+    uint32_t num_splits, kb_per_split, split_panel_rows;
 };
 
-// Tuning aid (DG_PROFILE=1): a device buffer of per-role wait-cycle counters, printed after every launch
+// Split-K scratch: num_splits stacked FP32 [rows x N] panels.  One buffer per device, shared by every stream (a
+// captured graph may replay on any stream, so a per-stream buffer would promise nothing): split-K GEMMs that overlap
+// on the GPU from different streams would race on it; set DG_FORCE_SPLIT_K=1 to keep such workloads unsplit.  The
+// buffer only grows; growing allocates, so the first call of a shape must not be inside a stream capture.
+int split_workspace(size_t bytes, float** out) {
+    static std::mutex mu;
+    static std::map<int, std::pair<float*, size_t>> per_device;
+    std::lock_guard<std::mutex> lock(mu);
+    int device = 0;
+    DG_CUDA_RT(cudaGetDevice(&device));
+    auto& w = per_device[device];
+    if (w.second < bytes) {
+        if (w.first != nullptr) DG_CUDA_RT(cudaFree(w.first));
+        w = {nullptr, 0};
+        const size_t rounded = align_up<size_t>(bytes, 1 << 20);
+        DG_CUDA_RT(cudaMalloc(reinterpret_cast<void**>(&w.first), rounded));
+        w.second = rounded;
+    }
+    *out = w.first;
+    return DG_OK;
+}
+
+// Tuning aid (DG_PROFILE=1): a device buffer of per-role wait-cycle counters and timeline stamps, printed after every launch
 unsigned long long* profile_buffer() {
     static unsigned long long* buf = nullptr;
-    if (buf == nullptr && cudaMalloc(reinterpret_cast<void**>(&buf), 16 * sizeof(unsigned long long)) != cudaSuccess) buf = nullptr;
+    if (buf == nullptr && cudaMalloc(reinterpret_cast<void**>(&buf), 32 * sizeof(unsigned long long)) != cudaSuccess) buf = nullptr;
     return buf;
 }
 
@@ -122,10 +150,10 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
     const int num_sms = dg_get_num_sms();
     const int d_elem = p.d_fp32 ? 4 : 2;
     const int64_t k_blocks = ceil_div(p.k, 128);
-    const int forced_bn = env_int("FORCE_BLOCK_N"), forced_cluster = env_int("FORCE_CLUSTER");
+    const int forced_bn = env_int("FORCE_BLOCK_N"), forced_cluster = env_int("FORCE_CLUSTER"), forced_splits = env_int("FORCE_SPLIT_K");
 
     double best_cost = 0;
-    int best_bn = 0, best_cluster = 1;
+    int best_bn = 0, best_cluster = 1, best_splits = 1, best_kb_per_split = static_cast<int>(k_blocks);
     int64_t best_tiles = 0;
     for (int cluster = 1; cluster <= 2; ++cluster) {
         if (forced_cluster ? cluster != forced_cluster : !cluster_allowed(p, cluster)) continue;
@@ -136,25 +164,45 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
             m_blocks = static_cast<int64_t>(p.groups) * ceil_div(std::min(std::max(p.expected_m, 1), p.m), tile_m);
         else
             m_blocks = ceil_div(p.m, tile_m);
+        // Slicing K: dense GEMMs whose output has too few tiles to occupy the GPU.  Every CTA ingests at most ~67 B per
+        // clock from L2, so what matters is the bytes a CTA has to pull in; slicing K lets wide tiles (little re-reading
+        // of A) still spread over all SMs.  Slices hold a multiple of 4 K-blocks (one packed scale word); all work
+        // items run in one wave; the second pass costs a launch plus S FP32 panels of traffic.
+        const bool can_split = p.kind == DG_GEMM_DENSE && !p.accumulate && cluster == 1 && forced_splits != 1 && k_blocks >= 16;
         for (int bn = 16; bn <= 240; bn += 16) {
             if (forced_bn && bn != forced_bn) continue;
             if (p.b_mn_major && (bn / cluster) % 16 != 0) continue;       // an MN-major B load starts on a 16-byte boundary
-            const int64_t tiles = m_blocks * ceil_div(p.n, bn);
-            const int64_t waves = ceil_div<int64_t>(tiles, units);
-            const double mma = 2.0 * bn;
-            const double smem_feed = 128.0 + static_cast<double>(bn) / cluster;
-            const double l2_feed = (16384.0 + 128.0 * bn / cluster) / 67.0;
-            const GemmLayout lay{128, static_cast<uint32_t>(bn), 128, 2, static_cast<uint32_t>(d_elem), static_cast<uint32_t>(cluster),
-                                 p.b_mn_major ? 1u : 0u};
-            const double epilogue = 300.0 + 150.0 * lay.num_groups() + 20.0 * lay.num_stores() + bn * 2.0;
-            // The epilogue of a tile overlaps the next tile's main loop; it is exposed once per CTA
-            const double per_tile = static_cast<double>(k_blocks) * std::max(mma, std::max(smem_feed, l2_feed));
-            const double cost = static_cast<double>(waves) * std::max(per_tile, epilogue) + epilogue + 2000.0;
-            if (best_bn == 0 || cost < best_cost - 1e-9 || (std::abs(cost - best_cost) <= 1e-9 && bn > best_bn)) {
-                best_cost = cost;
-                best_bn = bn;
-                best_cluster = cluster;
-                best_tiles = tiles;
+            const int64_t mn_tiles = m_blocks * ceil_div(p.n, bn);
+            const int max_splits = can_split ? static_cast<int>(std::min<int64_t>(units / std::max<int64_t>(mn_tiles, 1), k_blocks / 8)) : 1;
+            for (int want = 1; want <= std::max(1, max_splits); ++want) {
+                if (forced_splits > 1 && want != std::min(forced_splits, std::max(1, max_splits))) continue;
+                int splits = 1, kb_per = static_cast<int>(k_blocks);
+                if (want > 1) {
+                    kb_per = static_cast<int>(align_up<int64_t>(ceil_div<int64_t>(k_blocks, want), 4));
+                    splits = static_cast<int>(ceil_div<int64_t>(k_blocks, kb_per));
+                    if (splits != want) continue;                          // same slicing as a smaller request
+                }
+                const int64_t tiles = mn_tiles * splits;
+                const int64_t waves = ceil_div<int64_t>(tiles, units);
+                const double mma = 2.0 * bn;
+                const double smem_feed = 128.0 + static_cast<double>(bn) / cluster;
+                const double l2_feed = (16384.0 + 128.0 * bn / cluster) / 67.0;
+                const GemmLayout lay{128, static_cast<uint32_t>(bn), 128, 2, static_cast<uint32_t>(splits > 1 ? 4 : d_elem),
+                                     static_cast<uint32_t>(cluster), p.b_mn_major ? 1u : 0u};
+                const double epilogue = 300.0 + 150.0 * lay.num_groups() + 20.0 * lay.num_stores() + bn * 2.0;
+                // The epilogue of a tile overlaps the next tile's main loop; it is exposed once per CTA
+                const double per_tile = static_cast<double>(kb_per) * std::max(mma, std::max(smem_feed, l2_feed));
+                double cost = static_cast<double>(waves) * std::max(per_tile, epilogue) + epilogue + 2000.0;
+                if (splits > 1)   // second launch + reading S panels and writing D at a few TB/s (~2000 B per SM clock over the GPU)
+                    cost += 6000.0 + static_cast<double>(splits + 1) * p.m * p.n * 4.0 / 2000.0;
+                if (best_bn == 0 || cost < best_cost - 1e-9 || (std::abs(cost - best_cost) <= 1e-9 && bn > best_bn)) {
+                    best_cost = cost;
+                    best_bn = bn;
+                    best_cluster = cluster;
+                    best_tiles = tiles;
+                    best_splits = splits;
+                    best_kb_per_split = kb_per;
+                }
             }
         }
     }
@@ -162,8 +210,8 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
         return fail(DG_ERR_INVALID_ARGUMENT, "no tile configuration: DG_FORCE_BLOCK_N must be a multiple of 16 in [16, 240], "
                                              "DG_FORCE_CLUSTER 1 or 2 (2 needs an even SM count and, for the contiguous layout, m %% 256 == 0)");
 
-    GemmLayout lay{128, static_cast<uint32_t>(best_bn), 128, 2, static_cast<uint32_t>(d_elem), static_cast<uint32_t>(best_cluster),
-                   p.b_mn_major ? 1u : 0u};
+    GemmLayout lay{128, static_cast<uint32_t>(best_bn), 128, 2, static_cast<uint32_t>(best_splits > 1 ? 4 : d_elem),
+                   static_cast<uint32_t>(best_cluster), p.b_mn_major ? 1u : 0u};
     int stages = 2;
     while (stages < 32) {
         GemmLayout next = lay;
@@ -174,10 +222,12 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
     const int forced_stages = env_int("FORCE_NUM_STAGES");
     if (forced_stages >= 2 && forced_stages <= stages) stages = forced_stages;
     // No point in more stages than K-blocks of two tiles
-    stages = static_cast<int>(std::max<int64_t>(2, std::min<int64_t>(stages, 2 * k_blocks)));
+    stages = static_cast<int>(std::max<int64_t>(2, std::min<int64_t>(stages, 2 * best_kb_per_split)));
     lay.num_stages = stages;
 
     const int units = num_sms / best_cluster;
+    cfg->num_splits = best_splits;
+    cfg->kb_per_split = best_kb_per_split;
     cfg->block_m = 128;
     cfg->block_n = best_bn;
     cfg->block_k = 128;
@@ -207,9 +257,10 @@ std::string generate_source(const Problem& p, const dg_gemm_config_t& cfg) {
       << "#define DG_MAJOR_B " << (p.b_mn_major ? 1 : 0) << "\n"
       << "#define DG_GRAN_K_A " << p.gran_k_a << "\n"
       << "#define DG_GRAN_K_B " << p.gran_k_b << "\n"
-      << "#define DG_D_FP32 " << (p.d_fp32 ? 1 : 0) << "\n"
+      << "#define DG_D_FP32 " << ((p.d_fp32 || cfg.num_splits > 1) ? 1 : 0) << "\n"
       << "#define DG_ACCUMULATE " << (p.accumulate ? 1 : 0) << "\n"
       << "#define DG_RASTER_GROUP " << cfg.raster_group << "\n"
+      << "#define DG_SPLIT_K " << (cfg.num_splits > 1 ? 1 : 0) << "\n"
       << "#define DG_PROFILE " << env_int("PROFILE") << "\n"
       << "#include <dg/gemm_fp8_fp4.cuh>\n";
     return s.str();
@@ -253,14 +304,22 @@ int run_gemm(int kind, const dg_gemm_args_t* a) {
     dg_gemm_config_t cfg;
     if ((rc = choose_config(p, &cfg)) != DG_OK) return rc;
     if (env_int("PRINT_CONFIGS"))
-        fprintf(stderr, "[dg] kind %d m %d n %d k %d groups %d -> block_n %d cluster %d stages %d ctas %d smem %d tiles %d\n", kind, p.m, p.n,
-                p.k, p.groups, cfg.block_n, cfg.cluster_size, cfg.num_stages, cfg.num_ctas, cfg.smem_bytes, cfg.num_tiles);
+        fprintf(stderr, "[dg] kind %d m %d n %d k %d groups %d -> block_n %d cluster %d stages %d ctas %d smem %d tiles %d splits %d x %d\n",
+                kind, p.m, p.n, p.k, p.groups, cfg.block_n, cfg.cluster_size, cfg.num_stages, cfg.num_ctas, cfg.smem_bytes, cfg.num_tiles,
+                cfg.num_splits, cfg.kb_per_split);
     dg_kernel_t kernel = nullptr;
     if ((rc = get_kernel(p, cfg, &kernel)) != DG_OK) return rc;
     if ((rc = ensure_status_word()) != DG_OK) return rc;
 
+    const bool split = cfg.num_splits > 1;
+    const bool kernel_d_fp32 = p.d_fp32 || split;
     const GemmLayout lay{128, static_cast<uint32_t>(cfg.block_n), 128, static_cast<uint32_t>(cfg.num_stages),
-                         static_cast<uint32_t>(p.d_fp32 ? 4 : 2), static_cast<uint32_t>(cfg.cluster_size), p.b_mn_major ? 1u : 0u};
+                         static_cast<uint32_t>(kernel_d_fp32 ? 4 : 2), static_cast<uint32_t>(cfg.cluster_size), p.b_mn_major ? 1u : 0u};
+    // Split-K: the kernel's D is the workspace, num_splits panels of [align(m, 128)][align(n, 4)] FP32
+    float* workspace = nullptr;
+    const int64_t panel_rows = align_up<int64_t>(p.m, 128), ld_ws = align_up<int64_t>(p.n, 4);
+    if (split && (rc = split_workspace(static_cast<size_t>(cfg.num_splits) * panel_rows * ld_ws * sizeof(float), &workspace)) != DG_OK)
+        return rc;
     const uint64_t a_rows = kind == DG_GEMM_M_GROUPED_MASKED ? static_cast<uint64_t>(p.groups) * p.m : p.m;
     const uint64_t b_rows = static_cast<uint64_t>(p.groups) * p.n;
     const uint64_t sfa_k = ceil_div(p.k, p.gran_k_a * 4), sfb_k = ceil_div(p.k, p.gran_k_b * 4);
@@ -291,27 +350,36 @@ int run_gemm(int kind, const dg_gemm_args_t* a) {
                         CU_TENSOR_MAP_SWIZZLE_NONE)) != DG_OK) return rc;
     const CUtensorMapSwizzle d_swizzle = lay.store_row_bytes() == 128 ? CU_TENSOR_MAP_SWIZZLE_128B :
                                          lay.store_row_bytes() == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
-    if ((rc = encode_2d(&tm_d, p.d_fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, a->d,
-                        p.n, a_rows, a->ldd * (p.d_fp32 ? 4 : 2), lay.store_cols(), 128, d_swizzle)) != DG_OK) return rc;
+    if (!split) {
+        if ((rc = encode_2d(&tm_d, p.d_fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, a->d,
+                            p.n, a_rows, a->ldd * (p.d_fp32 ? 4 : 2), lay.store_cols(), 128, d_swizzle)) != DG_OK) return rc;
+    } else {
+        if ((rc = encode_2d(&tm_d, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, workspace, p.n, static_cast<uint64_t>(cfg.num_splits) * panel_rows,
+                            ld_ws * 4, lay.store_cols(), 128, d_swizzle)) != DG_OK) return rc;
+    }
 
     GemmParams params;
     params.grouped_layout = a->grouped_layout;
-    params.d = a->d;
+    params.d = split ? static_cast<void*>(workspace) : a->d;
     params.status = state().status_device;
     params.shape_m = p.m; params.shape_n = p.n; params.shape_k = p.k;
     params.num_groups = p.groups;
-    params.ldd = static_cast<uint32_t>(a->ldd);
-    params.alpha = a->has_alpha ? a->alpha : 1.0f;
+    params.ldd = static_cast<uint32_t>(split ? ld_ws : a->ldd);
+    const float alpha = a->has_alpha ? a->alpha : 1.0f;
+    params.alpha = split ? 1.0f : alpha;              // split-K applies alpha in the reduction pass
     params.profile = nullptr;
+    params.num_splits = cfg.num_splits;
+    params.kb_per_split = cfg.kb_per_split;
+    params.split_panel_rows = static_cast<uint32_t>(panel_rows);
     void* kargs[6] = {&tm_a, &tm_b, &tm_sfa, &tm_sfb, &tm_d, &params};
     if (env_int("PROFILE")) {
         // synchronous, printing path for tuning only
         params.profile = profile_buffer();
         if (params.profile == nullptr) return fail(DG_ERR_CUDA, "cannot allocate the profile buffer");
-        DG_CUDA_RT(cudaMemsetAsync(params.profile, 0, 16 * sizeof(unsigned long long), static_cast<cudaStream_t>(a->stream)));
+        DG_CUDA_RT(cudaMemsetAsync(params.profile, 0, 32 * sizeof(unsigned long long), static_cast<cudaStream_t>(a->stream)));
         rc = dg_jit_launch(kernel, cfg.num_ctas, 256, cfg.cluster_size, cfg.smem_bytes, state().pdl, a->stream, kargs);
         if (rc != DG_OK) return rc;
-        unsigned long long h[16];
+        unsigned long long h[32];
         DG_CUDA_RT(cudaMemcpyAsync(h, params.profile, sizeof(h), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(a->stream)));
         DG_CUDA_RT(cudaStreamSynchronize(static_cast<cudaStream_t>(a->stream)));
         const double ctas = cfg.num_ctas, leaders = ctas / cfg.cluster_size;
@@ -319,9 +387,20 @@ int run_gemm(int kind, const dg_gemm_args_t* a) {
                         "issue cp %.0f mma %.0f commit %.0f / %.0f | sf wait %.0f / %.0f | epilogue wait_tmem_full %.0f store_wait %.0f / %.0f\n",
                 h[0] / ctas, h[1] / ctas, h[2] / leaders, h[3] / leaders, h[10] / leaders, h[11] / leaders, h[12] / leaders,
                 h[4] / leaders, h[5] / ctas, h[6] / ctas, h[7] / ctas, h[9] / ctas, h[8] / ctas);
+        fprintf(stderr, "[dg profile] CTA 0 timeline (ns after entry): set-up %lld | first stage %lld | first accumulator %lld | "
+                        "last store issued %lld | stores complete %lld | exit %lld\n",
+                (long long)(h[17] - h[16]), (long long)(h[18] - h[16]), (long long)(h[19] - h[16]), (long long)(h[20] - h[16]),
+                (long long)(h[21] - h[16]), (long long)(h[22] - h[16]));
+        if (split)
+            return launch_splitk_reduce(workspace, a->d, p.m, p.n, ld_ws, panel_rows, a->ldd, cfg.num_splits, alpha, p.d_fp32,
+                                        static_cast<cudaStream_t>(a->stream));
         return DG_OK;
     }
-    return dg_jit_launch(kernel, cfg.num_ctas, 256, cfg.cluster_size, cfg.smem_bytes, state().pdl, a->stream, kargs);
+    if ((rc = dg_jit_launch(kernel, cfg.num_ctas, 256, cfg.cluster_size, cfg.smem_bytes, state().pdl, a->stream, kargs)) != DG_OK) return rc;
+    if (split)
+        return launch_splitk_reduce(workspace, a->d, p.m, p.n, ld_ws, panel_rows, a->ldd, cfg.num_splits, alpha, p.d_fp32,
+                                    static_cast<cudaStream_t>(a->stream));
+    return DG_OK;
 }
 
 }  // namespace

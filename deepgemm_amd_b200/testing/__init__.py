@@ -1,1 +1,1 @@
-from .bench import bench, calc_diff, count_bytes, assert_bitwise_equal  # noqa: F401
+from .bench import bench, bench_kineto, calc_diff, count_bytes, assert_bitwise_equal  # noqa: F401

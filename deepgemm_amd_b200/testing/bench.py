@@ -49,3 +49,26 @@ def bench(fn, num_warmups: int = 5, num_tests: int = 20, flush_l2_bytes: int = 2
         ends[i].record()
     torch.cuda.synchronize()
     return sum(s.elapsed_time(e) for s, e in zip(starts, ends)) / num_tests / 1e3
+
+
+def bench_kineto(fn, kernel_names, num_tests: int = 20, flush_l2_bytes: int = 256 << 20) -> float:
+    """Mean device seconds per call of fn(), counting only kernels whose name contains one of `kernel_names`
+    (a string or a tuple), from the torch profiler's kernel records, with an L2 flush before every call: the method
+    of the reference's deep_gemm/testing/bench.py:79-146.  Unlike event timing it excludes launch gaps, which
+    matter for kernels of a few microseconds."""
+    names = (kernel_names,) if isinstance(kernel_names, str) else tuple(kernel_names)
+    flush = torch.empty(flush_l2_bytes // 4, dtype=torch.int, device="cuda") if flush_l2_bytes else None
+    fn()
+    torch.cuda.synchronize()
+    with torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CUDA]) as prof:
+        for _ in range(num_tests):
+            if flush is not None:
+                flush.zero_()
+            fn()
+        torch.cuda.synchronize()
+    total_us = 0.0
+    for evt in prof.events():
+        if evt.device_type == torch.autograd.DeviceType.CUDA and any(n in evt.name for n in names):
+            total_us += evt.device_time_total if hasattr(evt, "device_time_total") else evt.cuda_time_total
+    assert total_us > 0, f"no kernel matching {names} was recorded"
+    return total_us / num_tests / 1e6

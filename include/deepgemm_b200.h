@@ -150,6 +150,8 @@ typedef struct dg_gemm_config {
     int32_t tmem_cols;
     int32_t num_tiles;         /* dense / contiguous: exact; masked: estimated from expected_m */
     int32_t waves_x100;
+    int32_t num_splits;        /* slices of K per output tile (dense GEMMs with few tiles); 1 = not split */
+    int32_t kb_per_split;      /* K-blocks (128 of K) per slice */
 } dg_gemm_config_t;
 
 /* get_best_config<SM100ArchSpec> (heuristics/common.hpp:17-56, sm100.hpp:30-301).  Host only. */

@@ -107,7 +107,15 @@ def test_heuristics_invariants(fp32):
         assert cfg["tmem_cols"] in (32, 64, 128, 256, 512) and 2 * cfg["block_n"] + 4 + 4 * ((cfg["block_n"] + 127) // 128) <= cfg["tmem_cols"]
         assert 2 <= cfg["num_stages"] <= 32
         assert 1 <= cfg["num_ctas"] <= 148
-        assert cfg["num_tiles"] == -(-m // 128) * -(-n // cfg["block_n"])
+        assert cfg["num_tiles"] == -(-m // 128) * -(-n // cfg["block_n"]) * cfg["num_splits"]
+        kb = -(-k // 128)
+        if cfg["num_splits"] > 1:
+            # slices start on a packed scale word (4 K-blocks), cover K exactly once, and none is empty
+            assert cfg["kb_per_split"] % 4 == 0 and cfg["kb_per_split"] >= 8
+            assert (cfg["num_splits"] - 1) * cfg["kb_per_split"] < kb <= cfg["num_splits"] * cfg["kb_per_split"]
+            assert cfg["num_tiles"] <= 148
+        else:
+            assert cfg["kb_per_split"] == kb
     for kind, groups in ((1, 32), (2, 16)):
         cfg = dg.get_gemm_config(kind, 256 if kind == 2 else 32 * 1024, 4096, 7168, num_groups=groups, expected_m=64)
         assert cfg["smem_bytes"] <= 232448 and cfg["num_ctas"] <= 148

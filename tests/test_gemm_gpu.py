@@ -111,6 +111,52 @@ def test_mn_major_operands_through_the_nn_tn_tt_entry_points(variant, m, n, k, c
     assert torch.equal(d.view(torch.int16), d_nt.view(torch.int16))
 
 
+@pytest.mark.parametrize("m,n,k,splits", [(128, 2112, 7168, None), (64, 4096, 7168, None), (100, 264, 2176, 2), (128, 128, 4096, 4),
+                                          (129, 512, 3200, 3)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float])
+def test_split_k_matches_oracle_and_is_reproducible(m, n, k, splits, out_dtype, monkeypatch):
+    """Few-tile shapes are sliced along K; the last slice to arrive sums the FP32 partials in slice order."""
+    if splits is not None:
+        monkeypatch.setenv("DG_FORCE_SPLIT_K", str(splits))
+    cfg = dg.get_gemm_config(0, m, n, k, d_is_fp32=out_dtype == torch.float)
+    assert cfg["num_splits"] >= 2, cfg
+    qa, sfa, qb, sfb, _ = quantise_dense(seeded_bf16((m, k), 18), seeded_bf16((n, k), 19))
+    ref = oracle.dequant_gemm_nt(qa, sfa, qb, sfb, alpha=0.5)
+    outs = []
+    for _ in range(3):                       # repeated launches reuse the workspace: counters must be back at zero
+        d = _run_dense(qa, sfa, qb, sfb, out_dtype=out_dtype, alpha=0.5)
+        outs.append(d.clone())
+    out = outs[0].float().cpu().numpy()
+    assert not np.isnan(out).any()
+    assert oracle.calc_diff(out, ref) < 1e-5, diff_report(out, ref)
+    assert all(torch.equal(o.view(torch.int32 if out_dtype == torch.float else torch.int16),
+                           outs[0].view(torch.int32 if out_dtype == torch.float else torch.int16)) for o in outs[1:])
+    # against the unsplit kernel: same products, different FP32 summation order
+    monkeypatch.setenv("DG_FORCE_SPLIT_K", "1")
+    assert dg.get_gemm_config(0, m, n, k, d_is_fp32=out_dtype == torch.float)["num_splits"] == 1
+    d1 = _run_dense(qa, sfa, qb, sfb, out_dtype=out_dtype, alpha=0.5).float().cpu().numpy()
+    assert oracle.calc_diff(out, d1) < 1e-6
+
+
+def test_split_k_inside_a_cuda_graph():
+    m, n, k = 128, 2112, 7168
+    qa, sfa, qb, sfb, _ = quantise_dense(seeded_bf16((m, k), 23), seeded_bf16((n, k), 24))
+    a = (fp8_cuda(qa), packed_sf_cuda(sfa)); b = (fp8_cuda(qb), packed_sf_cuda(sfb))
+    d = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    dg.fp8_gemm_nt(a, b, d, recipe=(1, 1, 128))                   # first call allocates the workspace: outside the capture
+    torch.cuda.synchronize()
+    want = d.clone()
+    stream, graph = torch.cuda.Stream(), torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            dg.fp8_gemm_nt(a, b, d, recipe=(1, 1, 128))
+    for _ in range(3):
+        d.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(d.view(torch.int16), want.view(torch.int16))
+
+
 def test_fp32_output_accumulation_and_alpha():
     m, n, k = 192, 320, 768
     qa, sfa, qb, sfb, _ = quantise_dense(seeded_bf16((m, k), 5), seeded_bf16((n, k), 6))
