@@ -60,6 +60,7 @@ SIGNATURES = {
     "dg_transpose_fp32_mn_major": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                              C.c_int64, C.c_int64, C.c_int64, C.c_void_p]),
     "dg_fp8_fp4_gemm": (C.c_int, [C.POINTER(GemmArgs)]),
+    "dg_fp8_fp4_gemm_noalloc": (C.c_int, [C.POINTER(GemmArgs)]),
     "dg_m_grouped_fp8_fp4_gemm_contiguous": (C.c_int, [C.POINTER(GemmArgs)]),
     "dg_m_grouped_fp8_fp4_gemm_masked": (C.c_int, [C.POINTER(GemmArgs)]),
     "dg_gemm_precompile": (C.c_int, [C.c_int, C.POINTER(GemmArgs)]),
@@ -78,10 +79,13 @@ SIGNATURES = {
 def _load():
     if not os.path.isfile(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m deepgemm_amd_b200.build` "
+            f"{LIB_PATH} is missing: build it with `python deepgemm_amd_b200/build.py` "
             "(there is no CPU or PyTorch fallback for the GEMM path)")
     lib = C.CDLL(LIB_PATH)
     for name, (restype, argtypes) in SIGNATURES.items():
+        if not hasattr(lib, name):
+            raise ImportError(f"{LIB_PATH} is older than the sources (no symbol {name}): rebuild it with "
+                              "`python deepgemm_amd_b200/build.py --force`")
         fn = getattr(lib, name)
         fn.restype = restype
         fn.argtypes = argtypes

@@ -1,7 +1,9 @@
 """Builds lib/libdeepgemm_b200.so (the C-ABI library) in-tree with nvcc for sm_100a.
 
-    python -m deepgemm_amd_b200.build            # build if sources are newer than the library
-    python -m deepgemm_amd_b200.build --force
+    python deepgemm_amd_b200/build.py            # build if sources are newer than the library
+    python deepgemm_amd_b200/build.py --force
+
+(run it as a script: `python -m deepgemm_amd_b200.build` would import the package, which needs the library)
 
 nvcc cross-compiles without a GPU.  The GEMM kernels themselves are compiled at run time by the
 library's JIT runtime (or ahead of time by ``prebuild_kernels``) into ``_jit_cache/``.

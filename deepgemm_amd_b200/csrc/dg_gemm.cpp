@@ -294,7 +294,14 @@ int get_kernel(const Problem& p, const dg_gemm_config_t& cfg, dg_kernel_t* kerne
     return dg_jit_compile(names[p.kind], "dg_gemm_fp8_fp4", src.c_str(), "", kernel);
 }
 
-int run_gemm(int kind, const dg_gemm_args_t* a) {
+// `fixed_scratch`, when given, replaces the library-owned split-K workspace with a caller-provided device buffer of
+// fixed size and turns off everything else that would allocate (the status word is used only if it already exists).
+struct FixedScratch {
+    float* ptr;
+    size_t bytes;
+};
+
+int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratch = nullptr) {
     Problem p;
     int rc = validate(kind, a, true, &p);
     if (rc != DG_OK) return rc;
@@ -309,7 +316,7 @@ int run_gemm(int kind, const dg_gemm_args_t* a) {
                 cfg.num_splits, cfg.kb_per_split);
     dg_kernel_t kernel = nullptr;
     if ((rc = get_kernel(p, cfg, &kernel)) != DG_OK) return rc;
-    if ((rc = ensure_status_word()) != DG_OK) return rc;
+    if (fixed_scratch == nullptr && (rc = ensure_status_word()) != DG_OK) return rc;
 
     const bool split = cfg.num_splits > 1;
     const bool kernel_d_fp32 = p.d_fp32 || split;
@@ -318,8 +325,17 @@ int run_gemm(int kind, const dg_gemm_args_t* a) {
     // Split-K: the kernel's D is the workspace, num_splits panels of [align(m, 128)][align(n, 4)] FP32
     float* workspace = nullptr;
     const int64_t panel_rows = align_up<int64_t>(p.m, 128), ld_ws = align_up<int64_t>(p.n, 4);
-    if (split && (rc = split_workspace(static_cast<size_t>(cfg.num_splits) * panel_rows * ld_ws * sizeof(float), &workspace)) != DG_OK)
+    const size_t workspace_bytes = split ? static_cast<size_t>(cfg.num_splits) * panel_rows * ld_ws * sizeof(float) : 0;
+    if (split && fixed_scratch != nullptr) {
+        if (workspace_bytes > fixed_scratch->bytes)
+            return fail(DG_ERR_INVALID_ARGUMENT,
+                        "this GEMM (m %d, n %d, k %d) is sliced %d ways along K and needs %zu bytes of scratch, more than the %zu bytes "
+                        "of the built-in buffer: call dg_fp8_fp4_gemm instead, or set DG_FORCE_SPLIT_K=1 to run it unsliced",
+                        p.m, p.n, p.k, cfg.num_splits, workspace_bytes, fixed_scratch->bytes);
+        workspace = fixed_scratch->ptr;
+    } else if (split && (rc = split_workspace(workspace_bytes, &workspace)) != DG_OK) {
         return rc;
+    }
     const uint64_t a_rows = kind == DG_GEMM_M_GROUPED_MASKED ? static_cast<uint64_t>(p.groups) * p.m : p.m;
     const uint64_t b_rows = static_cast<uint64_t>(p.groups) * p.n;
     const uint64_t sfa_k = ceil_div(p.k, p.gran_k_a * 4), sfb_k = ceil_div(p.k, p.gran_k_b * 4);
@@ -404,6 +420,13 @@ int run_gemm(int kind, const dg_gemm_args_t* a) {
 }
 
 }  // namespace
+
+// Called by the no-allocation entry point in dg_splitk.cu, which owns the fixed buffer
+int run_dense_gemm_with_fixed_scratch(const dg_gemm_args_t* args, float* scratch, size_t scratch_bytes) {
+    const FixedScratch fixed{scratch, scratch_bytes};
+    return run_gemm(DG_GEMM_DENSE, args, &fixed);
+}
+
 }  // namespace dg
 
 using namespace dg;

@@ -62,4 +62,47 @@ int launch_splitk_reduce(const float* ws, void* d, int m, int n, int64_t ld_ws, 
     return DG_OK;
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Dense GEMM for callers that must not allocate
+// ---------------------------------------------------------------------------------------------------------------
+// Some callers run where device allocation is off the table: inside a CUDA stream capture, on a real-time serving
+// thread that may not take the allocator's locks, under a memory budget that was handed out in full at start-up, or
+// in a process that has forbidden cudaMalloc after initialisation so that its footprint stays fixed.  The sliced (split-K) dense
+// GEMM normally parks its FP32 partial panels in a library-owned buffer that grows on demand; for those callers the
+// panels go into this fixed array instead.  It is part of the library image: every GPU that loads the library holds
+// these 16 MiB until the process exits.
+constexpr size_t kFixedScratchBytes = 16u << 20;
+static __device__ __align__(256) float g_fixed_splitk_scratch[kFixedScratchBytes / sizeof(float)];
+
+int run_dense_gemm_with_fixed_scratch(const dg_gemm_args_t* args, float* scratch, size_t scratch_bytes);   // dg_gemm.cpp
+
+namespace {
+
+// In host code the array's name is only a handle; the device address has to be asked for, once per device, with that
+// device current.
+int fixed_scratch_address(float** out) {
+    constexpr int kMaxDevices = 64;
+    static std::mutex mu;
+    static float* address[kMaxDevices] = {};
+    int device = 0;
+    DG_CUDA_RT(cudaGetDevice(&device));
+    if (device < 0 || device >= kMaxDevices) return fail(DG_ERR_INVALID_ARGUMENT, "device ordinal %d out of range", device);
+    std::lock_guard<std::mutex> lock(mu);
+    if (address[device] == nullptr) {
+        void* ptr = nullptr;
+        DG_CUDA_RT(cudaGetSymbolAddress(&ptr, g_fixed_splitk_scratch));
+        address[device] = static_cast<float*>(ptr);
+    }
+    *out = address[device];
+    return DG_OK;
+}
+
+}  // namespace
 }  // namespace dg
+
+extern "C" int dg_fp8_fp4_gemm_noalloc(const dg_gemm_args_t* args) {
+    float* scratch = nullptr;
+    const int rc = dg::fixed_scratch_address(&scratch);
+    if (rc != DG_OK) return rc;
+    return dg::run_dense_gemm_with_fixed_scratch(args, scratch, dg::kFixedScratchBytes);
+}

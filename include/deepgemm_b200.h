@@ -134,6 +134,19 @@ DG_API int dg_m_grouped_fp8_fp4_gemm_contiguous(const dg_gemm_args_t* args);
 /* m_grouped_fp8_fp4_gemm_nt_masked (gemm.hpp:269-318). */
 DG_API int dg_m_grouped_fp8_fp4_gemm_masked(const dg_gemm_args_t* args);
 
+/* Same operation and arguments as dg_fp8_fp4_gemm, for callers that cannot allocate device memory (inside a stream
+ * capture, on a thread that must not block on the allocator, or in a process that freezes its memory footprint after
+ * start-up).  It has no counterpart in the reference.  The scratch of the K-sliced path (FP32 partial panels) lives in
+ * a 16 MiB array inside the library image, which every GPU that loads the library keeps until exit; the call performs
+ * no cudaMalloc / cudaFree / cudaHostAlloc.  A GEMM whose slicing needs more than 16 MiB of panels
+ * (num_splits * align(m,128) * align(n,4) * 4 bytes) is rejected with DG_ERR_INVALID_ARGUMENT.  The first call on a
+ * device looks up the array's address (and, like every entry point, the first call of a tile configuration loads its
+ * kernel image): make that first call before any stream capture.  All calls share the array and it keeps the last
+ * call's panels; nothing in it has to start at zero (every element that is read is written first by the same call),
+ * but two calls that overlap on the GPU, from different streams or devices' peers, race on it.  Failed bounded waits
+ * are reported through the status word only if another entry point has already created it. */
+DG_API int dg_fp8_fp4_gemm_noalloc(const dg_gemm_args_t* args);
+
 /* Compile (but do not load or launch) the kernel the call above would use, so that a later call
  * finds it in the cache.  Needs nvcc, not a GPU.  Device pointers in `args` may be null. */
 DG_API int dg_gemm_precompile(int kind, const dg_gemm_args_t* args);

@@ -15,8 +15,11 @@ def pytest_configure(config):
 
 def pytest_sessionstart(session):
     # The C-ABI library is built in-tree (nvcc cross-compiles without a GPU); build it if it is not there yet.
-    from deepgemm_amd_b200.build import build_library
-    build_library()
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("_dg_build", os.path.join(ROOT, "deepgemm_amd_b200", "build.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    mod.build_library()
 
 
 @pytest.fixture(scope="session")
