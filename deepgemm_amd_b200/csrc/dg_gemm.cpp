@@ -191,7 +191,9 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
                                      static_cast<uint32_t>(cluster), p.b_mn_major ? 1u : 0u};
                 const double epilogue = 300.0 + 150.0 * lay.num_groups() + 20.0 * lay.num_stores() + bn * 2.0;
                 // The epilogue of a tile overlaps the next tile's main loop; it is exposed once per CTA
-                const double per_tile = static_cast<double>(kb_per) * std::max(mma, std::max(smem_feed, l2_feed));
+                // + ~1500 cycles per tile that do not shrink with K (tile hand-over, first loads of a new tile), measured
+                // on the K = 512 and K = 1536 shapes
+                const double per_tile = static_cast<double>(kb_per) * std::max(mma, std::max(smem_feed, l2_feed)) + 1500.0;
                 double cost = static_cast<double>(waves) * std::max(per_tile, epilogue) + epilogue + 2000.0;
                 if (splits > 1)   // second launch + reading S panels and writing D at a few TB/s (~2000 B per SM clock over the GPU)
                     cost += 6000.0 + static_cast<double>(splits + 1) * p.m * p.n * 4.0 / 2000.0;
