@@ -392,6 +392,13 @@ def detail_rows(torch, dg):
             c = make_dense_case(m, n, k, 77 + i, torch, dg)
             t = bench(lambda: dg.fp8_gemm_nt(c["a"], c["b"], c["d"], recipe=(1, 1, 128)), 3, 10)
             add(f"dense m{m} n{n} k{k}", t, flops_of(m, n, k), m * k + n * k + m * n * 2 + (m + n) * (k // 128))
+    # the step before the GEMM: per-token cast of BF16 activations straight to the packed scale layout (HBM-bound)
+    for m, k in ((4096, 7168), (32768, 7168)):
+        x = torch.randn((m, k), device="cuda", dtype=torch.bfloat16)
+        t = bench_kineto(lambda: dg.per_token_cast(x, "e4m3", 128), "per_token_cast_kernel", 10)
+        rows.append({"case": f"per-token cast bf16->e4m3 + packed UE8M0 m{m} k{k}", "us": round(t * 1e6, 1), "tflops": 0.0,
+                     "gbs": round((m * k * 3 + m * k // 128) / t / 1e9, 0)})
+        del x
     # config 5 (dense): FP8 x FP4
     for n, k in ((7168, 2048), (4096, 7168)):
         a = torch.randn((M_DENSE, k), device="cuda", dtype=torch.bfloat16)

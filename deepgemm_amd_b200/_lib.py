@@ -59,6 +59,8 @@ SIGNATURES = {
                                           C.c_int64, C.c_int64, C.c_int64, C.c_void_p]),
     "dg_transpose_fp32_mn_major": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                              C.c_int64, C.c_int64, C.c_int64, C.c_void_p]),
+    "dg_per_token_cast": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int, C.c_int,
+                                    C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "dg_fp8_fp4_gemm": (C.c_int, [C.POINTER(GemmArgs)]),
     "dg_fp8_fp4_gemm_noalloc": (C.c_int, [C.POINTER(GemmArgs)]),
     "dg_m_grouped_fp8_fp4_gemm_contiguous": (C.c_int, [C.POINTER(GemmArgs)]),

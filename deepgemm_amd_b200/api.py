@@ -77,8 +77,8 @@ _host_settings = {"deterministic": False, "ignore_compile_dims": False, "block_m
 
 
 def use_deterministic_algorithms(enabled: bool) -> None:
-    """Accepted for API parity; these kernels have one accumulation order per configuration
-    (no split-K), so results are bitwise reproducible either way."""
+    """Accepted for API parity; these kernels have one accumulation order per configuration (the K-sliced path
+    adds its partial panels in slice order), so results are bitwise reproducible either way."""
     _host_settings["deterministic"] = bool(enabled)
 
 
@@ -222,6 +222,31 @@ def _transform_sf_pair(sfa, sfb, m, n, k, recipe, recipe_a, recipe_b, num_groups
     tsfa = transform_sf_into_required_layout(sfa, m, k, recipe_a, num_groups_a, None, disable_ue8m0_cast)
     tsfb = transform_sf_into_required_layout(sfb, n, k, recipe_b, num_groups_b, None, disable_ue8m0_cast)
     return tsfa, tsfb, recipe_a[1], recipe_b[1]
+
+
+def per_token_cast(x: torch.Tensor, fmt: str = "e4m3", gran_k: int = 128, use_packed_ue8m0: bool = True,
+                   use_ue8m0: bool = True):
+    """CUDA per-token cast of BF16 activations [m, k]: returns (data, sf) with data float8_e4m3fn [m, k] (fmt "e4m3") or
+    packed e2m1 int8 [m, k/2] (fmt "e2m1"), and sf either FP32 [m, ceil(k/gran_k)] or (use_packed_ue8m0) the packed,
+    MN-major int32 tensor the GEMMs take as pre-transformed scales, so no transform kernel runs at GEMM time.
+    Bit-identical to per_token_cast_to_fp8 / per_token_cast_to_fp4 of deep_gemm/utils/math.py:26-49,99-125."""
+    _require(x.is_cuda and x.dim() == 2 and x.dtype == torch.bfloat16, "x is a 2-D CUDA bfloat16 tensor")
+    _require(x.stride(1) == 1, "x.stride(-1) == 1")
+    _require(fmt in ("e4m3", "e2m1"), "fmt is 'e4m3' or 'e2m1'")
+    m, k = x.shape
+    fp4 = fmt == "e2m1"
+    q = torch.empty((m, k // 2), dtype=torch.int8, device=x.device) if fp4 else \
+        torch.empty((m, k), dtype=torch.float8_e4m3fn, device=x.device)
+    if use_packed_ue8m0:
+        amn, packed_k = get_tma_aligned_size(m, 4), ceil_div(k, gran_k * 4)
+        sf = torch.zeros((packed_k, amn), dtype=torch.int, device=x.device).t()[:m]      # [m, packed_k], strides (1, amn)
+        pitch = amn
+    else:
+        sf = torch.empty((m, ceil_div(k, gran_k)), dtype=torch.float, device=x.device)
+        pitch = sf.stride(0)
+    check(lib.dg_per_token_cast(x.data_ptr(), x.stride(0), q.data_ptr(), q.stride(0), sf.data_ptr(), pitch, m, k,
+                                _lib.DG_FP4_E2M1_X2 if fp4 else _lib.DG_FP8_E4M3, gran_k, int(use_packed_ue8m0), int(use_ue8m0), _stream()))
+    return q, sf
 
 
 # ------------------------------------------------------------------------------------------------

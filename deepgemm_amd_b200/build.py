@@ -18,7 +18,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_DIR = os.path.join(PKG_DIR, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libdeepgemm_b200.so")
-SOURCES = ["dg_runtime.cpp", "dg_jit.cpp", "dg_gemm.cpp", "dg_layout.cu", "dg_splitk.cu"]
+SOURCES = ["dg_runtime.cpp", "dg_jit.cpp", "dg_gemm.cpp", "dg_layout.cu", "dg_splitk.cu", "dg_quant.cu"]
 
 
 def _nvcc() -> str:

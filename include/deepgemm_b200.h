@@ -92,6 +92,15 @@ DG_API int dg_transpose_fp32_mn_major(const float* sf_device, float* out_device,
                                int64_t in_stride_group, int64_t in_stride_mn, int64_t in_stride_k,
                                void* stream);
 
+/* Per-token (1 x gran_k) cast of BF16 activations [m, k] (row pitch ldx elements) to float8_e4m3 [m, k] or packed
+ * float4_e2m1 [m, k/2] (row pitch ldq bytes), with the scales written either as FP32 [m, ceil(k/gran_k)] (row pitch
+ * sf_pitch floats) or, with packed_ue8m0 != 0, directly as the packed UE8M0 int32 tensor the GEMMs take
+ * ([m, ceil(k/(4 gran_k))], MN contiguous, K pitch sf_pitch >= align(m,4) int32): the "produce pre-transformed SFs in
+ * the cast kernel" path of docs/scaling-factor-format.md:123-139.  Same arithmetic as per_token_cast_to_fp8 /
+ * per_token_cast_to_fp4 of deep_gemm/utils/math.py:26-49,99-125.  k must be a multiple of 16. */
+DG_API int dg_per_token_cast(const void* x_bf16_device, int64_t ldx, void* q_device, int64_t ldq, void* sf_device, int64_t sf_pitch,
+                             int m, int k, int out_dtype, int gran_k, int packed_ue8m0, int use_ue8m0, void* stream);
+
 /* ---- GEMMs: csrc/apis/gemm.hpp:78-318 ----------------------------------------------------------- */
 
 typedef struct dg_gemm_args {

@@ -442,6 +442,47 @@ def test_torch_quantisers_match_oracle():
     assert np.array_equal(qb.view(torch.uint8).cpu().numpy(), oqb) and np.array_equal(sfb.cpu().numpy(), osfb)
 
 
+@pytest.mark.parametrize("m,k", [(1, 128), (37, 304), (200, 7168), (4096, 2048), (130, 16)])
+@pytest.mark.parametrize("gran_k", [32, 128])
+@pytest.mark.parametrize("fmt", ["e4m3", "e2m1"])
+def test_cuda_per_token_cast_is_bit_identical_to_the_oracle(m, k, gran_k, fmt):
+    x = seeded_bf16((m, k), 80, 3.0)
+    x[0] = 0                                                       # all-zero row: the 1e-4 clamp
+    if k >= 8:
+        x[m // 2, :8] = [1e-6, -3e-5, 448.0, -448.0, 0.25, -0.25, 5.0, -1.75]
+    x = oracle.bf16_round(x)
+    xt = torch.from_numpy(x).cuda().bfloat16()
+    cast = oracle.per_token_cast_to_fp4 if fmt == "e2m1" else oracle.per_token_cast_to_fp8
+    want_q, want_sf = cast(x, True, gran_k)
+    # FP32 scales
+    q, sf = dg.per_token_cast(xt, fmt, gran_k, use_packed_ue8m0=False)
+    assert np.array_equal(q.view(torch.uint8).cpu().numpy(), want_q.view(np.uint8))
+    assert np.array_equal(sf.cpu().numpy(), want_sf)
+    # packed UE8M0 scales, straight into the GEMM's layout
+    q2, psf = dg.per_token_cast(xt, fmt, gran_k, use_packed_ue8m0=True)
+    want_packed, strides = oracle.mn_major_tma_aligned_packed_ue8m0(want_sf)
+    assert torch.equal(q2.view(torch.uint8), q.view(torch.uint8))
+    assert tuple(psf.shape) == want_packed.shape and tuple(psf.stride()) == tuple(strides)
+    assert np.array_equal(psf.cpu().numpy(), want_packed)
+    # non power-of-two scales (use_ue8m0=False) for the FP32 form
+    q3, sf3 = dg.per_token_cast(xt, fmt, gran_k, use_packed_ue8m0=False, use_ue8m0=False)
+    want_q3, want_sf3 = cast(x, False, gran_k)
+    assert np.array_equal(sf3.cpu().numpy(), want_sf3)
+    if fmt == "e2m1":
+        assert np.array_equal(q3.view(torch.uint8).cpu().numpy(), want_q3.view(np.uint8))
+
+
+def test_cast_kernel_feeds_the_gemm_without_a_scale_transform():
+    m, n, k = 256, 512, 1024
+    a, b = seeded_bf16((m, k), 81), seeded_bf16((n, k), 82)
+    qa, sfa, qb, sfb, _ = quantise_dense(a, b)
+    a_cuda = dg.per_token_cast(torch.from_numpy(a).cuda().bfloat16(), "e4m3", 128)
+    d = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    dg.fp8_gemm_nt(a_cuda, (fp8_cuda(qb), packed_sf_cuda(sfb)), d, recipe=(1, 1, 128))
+    d_ref = _run_dense(qa, sfa, qb, sfb)
+    assert torch.equal(d.view(torch.int16), d_ref.view(torch.int16))
+
+
 # ---------------------------------------------------------------------------------------------------
 # API behaviour
 # ---------------------------------------------------------------------------------------------------
