@@ -22,12 +22,15 @@ struct GemmLayout {
     uint32_t b_mn_major = 0;                       // B stored with N contiguous: staged as 128-column atoms of [128 K][128 B]
 
     DG_HDC uint32_t sf_block_n() const { return (block_n + 127) / 128 * 128; }
-    // Row width of one D staging buffer / TMA store: the widest swizzle span that divides a tile row
-    DG_HDC uint32_t store_row_bytes() const {
-        return (block_n * d_elem_bytes) % 128 == 0 ? 128 : ((block_n * d_elem_bytes) % 64 == 0 ? 64 : 32);
+    // D leaves through TMA store boxes of 128 rows.  Complete 128-byte groups of a tile row use a 128-byte-wide box; the
+    // remainder of the row (when block_n * element size is not a multiple of 128) uses boxes of the widest swizzle
+    // span that divides it.
+    DG_HDC uint32_t tail_bytes() const { return (block_n * d_elem_bytes) % 128; }
+    DG_HDC uint32_t store_row_bytes() const {          // row width of the boxes that cover the tail (128 when there is none)
+        return tail_bytes() == 0 ? 128 : (tail_bytes() % 64 == 0 ? 64 : 32);
     }
     DG_HDC uint32_t store_cols() const { return store_row_bytes() / d_elem_bytes; }
-    DG_HDC uint32_t num_stores() const { return block_n / store_cols(); }
+    DG_HDC uint32_t num_stores() const { return block_n * d_elem_bytes / 128 + tail_bytes() / store_row_bytes(); }
     // The epilogue drains 128 bytes of every D row per synchronisation ("group"): 1, 2 or 4 store boxes side by side
     DG_HDC uint32_t group_cols() const { return 128 / d_elem_bytes; }
     DG_HDC uint32_t num_groups() const { return (block_n + group_cols() - 1) / group_cols(); }

@@ -95,12 +95,11 @@ constexpr uint32_t SF_BLOCK_N = (BLOCK_N + 127) / 128 * 128;
 constexpr uint32_t kDElemBytes = kDIsFP32 ? 4 : 2;
 constexpr GemmLayout kLayout{BLOCK_M, BLOCK_N, BLOCK_K, kNumStages, kDElemBytes, kCluster, kBMnMajor ? 1u : 0u};
 constexpr uint32_t kBAtoms = kLayout.b_atoms();            // 128-column atoms of an MN-major B tile
-constexpr uint32_t kStoreRowBytes   = kLayout.store_row_bytes();
-constexpr uint32_t kStoreCols       = kLayout.store_cols();          // columns of D per TMA store
+constexpr uint32_t kStoreRowBytes   = kLayout.store_row_bytes();     // row width of the boxes covering the ragged end of a tile row
+constexpr uint32_t kStoreCols       = kLayout.store_cols();          // columns of D per such box
 constexpr uint32_t kNumStores       = kLayout.num_stores();
 constexpr uint32_t kGroupCols       = kLayout.group_cols();          // columns of D drained per epilogue synchronisation
 constexpr uint32_t kNumGroups       = kLayout.num_groups();
-constexpr uint32_t kStoreBoxBytes   = BLOCK_M * kStoreRowBytes;      // one TMA store box in the staging buffer
 constexpr uint32_t kNumStoreStages  = kLayout.num_store_stages();
 constexpr uint32_t kStoreStageBytes = kLayout.store_stage_bytes();
 constexpr uint32_t kSmemD   = kLayout.off_d();
@@ -176,6 +175,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                 const __grid_constant__ CUtensorMap tm_sfa,
                 const __grid_constant__ CUtensorMap tm_sfb,
                 const __grid_constant__ CUtensorMap tm_d,
+                const __grid_constant__ CUtensorMap tm_d_full,       // D again, with 128-byte-wide store boxes
                 const dg::GemmParams p) {
     using namespace dg;
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -206,6 +206,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
         prefetch_tensormap(&tm_sfa);
         prefetch_tensormap(&tm_sfb);
         prefetch_tensormap(&tm_d);
+        prefetch_tensormap(&tm_d_full);
     }
     if (warp_idx == 1 && lane == 0) {
         for (uint32_t s = 0; s < kNumStages; ++s) {
@@ -495,37 +496,44 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                     named_barrier_sync(1, kNumEpilogueThreads);
                     DG_PROF_ADD(prof_store, prof_s);
                     const uint32_t stage_addr = smem_base + kSmemD + sb * kStoreStageBytes;
-                    constexpr uint32_t kSwizzleMask = kStoreRowBytes == 128 ? 7 : (kStoreRowBytes == 64 ? 3 : 1);
+                    // A complete group is one box of 128-byte rows; the ragged last group of a tile row is split into
+                    // narrower boxes (rows of kStoreRowBytes)
+                    const bool full_group = kCols == kGroupCols;
+                    const uint32_t row_bytes = full_group ? 128u : kStoreRowBytes;
+                    const uint32_t box_bytes = BLOCK_M * row_bytes;
+                    const uint32_t swizzle_mask = row_bytes == 128 ? 7u : (row_bytes == 64 ? 3u : 1u);
                     constexpr uint32_t kElemsPerChunk = 16 / kDElemBytes;                 // 8 bf16 or 4 fp32 per 16 bytes
                     #pragma unroll
                     for (uint32_t c = 0; c < kGroupCols / kElemsPerChunk; ++c) {
                         if (c * kElemsPerChunk < kCols) {
                             // chunk c of the row lives in store box (c * 16 / row bytes), at swizzled chunk position
-                            const uint32_t box = (c * 16) / kStoreRowBytes, in_row = (c * 16) % kStoreRowBytes;
-                            const uint32_t off = row_in_tile * kStoreRowBytes + in_row;
-                            const uint32_t phys = off ^ (((off >> 7) & kSwizzleMask) << 4);
+                            const uint32_t box = (c * 16) / row_bytes, in_row = (c * 16) % row_bytes;
+                            const uint32_t off = row_in_tile * row_bytes + in_row;
+                            const uint32_t phys = off ^ (((off >> 7) & swizzle_mask) << 4);
                             const uint32_t e0 = c * kElemsPerChunk, l = e0 / 16, i0 = e0 % 16;
                             if constexpr (!kDIsFP32)
-                                st_shared_v4(stage_addr + box * kStoreBoxBytes + phys,
+                                st_shared_v4(stage_addr + box * box_bytes + phys,
                                              pack_bf16x2(__uint_as_float(v[l][i0 + 0]), __uint_as_float(v[l][i0 + 1])),
                                              pack_bf16x2(__uint_as_float(v[l][i0 + 2]), __uint_as_float(v[l][i0 + 3])),
                                              pack_bf16x2(__uint_as_float(v[l][i0 + 4]), __uint_as_float(v[l][i0 + 5])),
                                              pack_bf16x2(__uint_as_float(v[l][i0 + 6]), __uint_as_float(v[l][i0 + 7])));
                             else
-                                st_shared_v4(stage_addr + box * kStoreBoxBytes + phys, v[l][i0], v[l][i0 + 1], v[l][i0 + 2], v[l][i0 + 3]);
+                                st_shared_v4(stage_addr + box * box_bytes + phys, v[l][i0], v[l][i0 + 1], v[l][i0 + 2], v[l][i0 + 3]);
                         }
                     }
                     fence_proxy_async_smem();
                     named_barrier_sync(1, kNumEpilogueThreads);
                     if (epi_tid == 0) {
+                        const uint32_t cols_per_box = full_group ? kGroupCols : kStoreCols;
+                        const CUtensorMap* map = full_group ? &tm_d_full : &tm_d;
                         #pragma unroll
                         for (uint32_t box = 0; box < kGroupCols / kStoreCols; ++box) {
-                            if (box * kStoreCols < kCols) {
+                            if (box * cols_per_box < kCols) {
                                 if constexpr (kAccumulate)
-                                    tma_reduce_add_2d(&tm_d, stage_addr + box * kStoreBoxBytes, static_cast<int32_t>(col0 + box * kStoreCols),
+                                    tma_reduce_add_2d(map, stage_addr + box * box_bytes, static_cast<int32_t>(col0 + box * cols_per_box),
                                                       static_cast<int32_t>(d_row0));
                                 else
-                                    tma_store_2d(&tm_d, stage_addr + box * kStoreBoxBytes, static_cast<int32_t>(col0 + box * kStoreCols),
+                                    tma_store_2d(map, stage_addr + box * box_bytes, static_cast<int32_t>(col0 + box * cols_per_box),
                                                  static_cast<int32_t>(d_row0));
                             }
                         }

@@ -344,7 +344,7 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
     const uint64_t sfa_rows = kind == DG_GEMM_M_GROUPED_MASKED ? sfa_k * p.groups : sfa_k;
     const uint64_t sfb_rows = sfb_k * p.groups;
 
-    CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb, tm_d;
+    CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb, tm_d, tm_d_full;
     // K-major A, B: K (elements) x rows; box = one 128-element K-block x the tile's rows; 128-byte swizzle.
     // MN-major (FP8 only): MN x (groups x K); box = 128 columns of MN x one K-block.
     if (!p.a_mn_major) {
@@ -368,13 +368,14 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
                         CU_TENSOR_MAP_SWIZZLE_NONE)) != DG_OK) return rc;
     const CUtensorMapSwizzle d_swizzle = lay.store_row_bytes() == 128 ? CU_TENSOR_MAP_SWIZZLE_128B :
                                          lay.store_row_bytes() == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
-    if (!split) {
-        if ((rc = encode_2d(&tm_d, p.d_fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, a->d,
-                            p.n, a_rows, a->ldd * (p.d_fp32 ? 4 : 2), lay.store_cols(), 128, d_swizzle)) != DG_OK) return rc;
-    } else {
-        if ((rc = encode_2d(&tm_d, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, workspace, p.n, static_cast<uint64_t>(cfg.num_splits) * panel_rows,
-                            ld_ws * 4, lay.store_cols(), 128, d_swizzle)) != DG_OK) return rc;
-    }
+    // Two views of D: boxes of 128-byte rows for complete groups, narrower boxes for the ragged end of a tile row
+    const CUtensorMapDataType d_type = kernel_d_fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    void* d_base = split ? static_cast<void*>(workspace) : a->d;
+    const uint64_t d_rows = split ? static_cast<uint64_t>(cfg.num_splits) * panel_rows : a_rows;
+    const uint64_t d_pitch_bytes = split ? ld_ws * 4 : a->ldd * (p.d_fp32 ? 4 : 2);
+    if ((rc = encode_2d(&tm_d, d_type, d_base, p.n, d_rows, d_pitch_bytes, lay.store_cols(), 128, d_swizzle)) != DG_OK) return rc;
+    if ((rc = encode_2d(&tm_d_full, d_type, d_base, p.n, d_rows, d_pitch_bytes, lay.group_cols(), 128, CU_TENSOR_MAP_SWIZZLE_128B)) != DG_OK)
+        return rc;
 
     GemmParams params;
     params.grouped_layout = a->grouped_layout;
@@ -389,7 +390,7 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
     params.num_splits = cfg.num_splits;
     params.kb_per_split = cfg.kb_per_split;
     params.split_panel_rows = static_cast<uint32_t>(panel_rows);
-    void* kargs[6] = {&tm_a, &tm_b, &tm_sfa, &tm_sfb, &tm_d, &params};
+    void* kargs[7] = {&tm_a, &tm_b, &tm_sfa, &tm_sfb, &tm_d, &tm_d_full, &params};
     if (env_int("PROFILE")) {
         // synchronous, printing path for tuning only
         params.profile = profile_buffer();
