@@ -17,7 +17,7 @@ constexpr uint32_t kSmemCapacity = 232448;      // largest dynamic shared memory
 constexpr uint32_t kTmemCapacityCols = 512;
 
 struct GemmLayout {
-    uint32_t block_m, block_n, block_k, num_stages, d_elem_bytes;
+    uint32_t block_m, block_n, block_k, num_stages, d_elem_bytes;   // block_m: rows of A per CTA and stage (128 or 256)
     uint32_t cluster = 1;                          // CTAs sharing one B tile (each loads block_n / cluster rows of B)
     uint32_t b_mn_major = 0;                       // B stored with N contiguous: staged as 128-column atoms of [128 K][128 B]
 
@@ -34,14 +34,14 @@ struct GemmLayout {
     // The epilogue drains 128 bytes of every D row per synchronisation ("group"): 1, 2 or 4 store boxes side by side
     DG_HDC uint32_t group_cols() const { return 128 / d_elem_bytes; }
     DG_HDC uint32_t num_groups() const { return (block_n + group_cols() - 1) / group_cols(); }
-    DG_HDC uint32_t store_stage_bytes() const { return block_m * 128; }
+    DG_HDC uint32_t store_stage_bytes() const { return 128 * 128; }      // staging holds 128 rows x 128 bytes
     DG_HDC uint32_t num_store_stages() const { return 2; }
 
     DG_HDC uint32_t a_bytes() const { return block_m * block_k; }        // one byte per element (FP8, or FP4 in 16-byte containers)
     DG_HDC uint32_t load_block_n() const { return block_n / cluster; }
     DG_HDC uint32_t b_atoms() const { return (load_block_n() + 127) / 128; }      // MN-major only
     DG_HDC uint32_t b_bytes() const { return b_mn_major ? b_atoms() * 128 * block_k : load_block_n() * block_k; }
-    DG_HDC uint32_t sfa_bytes() const { return 128 * 4; }
+    DG_HDC uint32_t sfa_bytes() const { return block_m * 4; }
     DG_HDC uint32_t sfb_bytes() const { return sf_block_n() * 4; }
 
     DG_HDC uint32_t off_d() const { return 0; }
@@ -55,9 +55,10 @@ struct GemmLayout {
     DG_HDC uint32_t total_bytes() const { return off_misc() + 16; }      // tensor-memory base, abort flag
     DG_HDC uint32_t bytes_per_stage() const { return a_bytes() + b_bytes() + sfa_bytes() + sfb_bytes() + 3 * 8; }
 
-    // Tensor memory: two accumulator stages, then SFA (4 columns per 128 rows) and SFB
+    // Tensor memory: two accumulators of block_n columns (two tiles in flight when block_m is 128, the two 128-row
+    // halves of one tile when it is 256), then SFA (4 columns per 128 rows) and SFB
     DG_HDC uint32_t tmem_col_sfa() const { return 2 * block_n; }
-    DG_HDC uint32_t tmem_col_sfb() const { return tmem_col_sfa() + 128 / 32; }
+    DG_HDC uint32_t tmem_col_sfb() const { return tmem_col_sfa() + block_m / 32; }
     DG_HDC uint32_t tmem_cols_used() const { return tmem_col_sfb() + sf_block_n() / 32; }
     DG_HDC uint32_t tmem_cols_alloc() const {
         const uint32_t u = tmem_cols_used();

@@ -17,7 +17,7 @@
 //               of the masked layout)
 //
 // The configuration arrives as DG_* macros set by the host-side code generator:
-//   DG_GEMM_TYPE (0 dense, 1 m-grouped contiguous, 2 m-grouped masked), DG_BLOCK_N, DG_NUM_STAGES,
+//   DG_GEMM_TYPE (0 dense, 1 m-grouped contiguous, 2 m-grouped masked), DG_M_HALVES, DG_BLOCK_N, DG_NUM_STAGES,
 //   DG_CLUSTER, DG_A_FP4, DG_B_FP4, DG_MAJOR_A, DG_MAJOR_B (0 K-major, 1 MN-major), DG_GRAN_K_A, DG_GRAN_K_B,
 //   DG_D_FP32, DG_ACCUMULATE, DG_RASTER_GROUP, DG_SPLIT_K.
 //
@@ -30,6 +30,13 @@
 // MN-major operands (the nn / tn / tt variants): the tile is staged as [128 of K][128 B of MN] atoms with the
 // same 128-byte swizzle (one TMA box per 128 columns of MN), the descriptor's leading-dimension offset steps
 // between atoms, and a step of 32 along K is 32 rows = 4096 B.
+//
+// DG_M_HALVES == 2 gives one CTA a 256 x BLOCK_N tile: a stage holds 256 rows of A, and every K-block is multiplied
+// as two 128-row MMAs that read the same B stage, so B leaves shared memory once per 256 rows and a K-block carries
+// twice the tensor-core time per byte loaded (the ring of stages stops limiting long-K shapes).  The two halves'
+// accumulators fill tensor memory, so a tile's MMAs start only after the epilogue has drained the previous tile.
+// In the contiguous layout a 256-row tile whose halves belong to two experts runs over K twice, once per half with
+// that half's B.
 //
 // DG_CLUSTER == 2 pairs two CTAs (a cluster of two SMs) on one 256 x BLOCK_N tile with
 // tcgen05.mma.cta_group::2: each CTA loads its own 128 rows of A and one half of the B tile, CTA 0 issues
@@ -68,32 +75,37 @@ constexpr bool     kAccumulate = DG_ACCUMULATE != 0;
 constexpr uint32_t kRasterGroup = DG_RASTER_GROUP;
 constexpr bool     kSplitK     = DG_SPLIT_K != 0;
 
+constexpr uint32_t kMHalves    = DG_M_HALVES;      // 128-row MMAs per CTA and K-block (1 or 2)
+
 constexpr uint32_t UMMA_M = 128 * kCluster, UMMA_N = BLOCK_N, UMMA_K = 32;
 constexpr uint32_t LOAD_BLOCK_N = BLOCK_N / kCluster;      // rows of B each CTA loads
-constexpr uint32_t TILE_M = BLOCK_M * kCluster;            // rows of D per scheduled tile
+constexpr uint32_t CTA_M = BLOCK_M * kMHalves;             // rows of A (and D) per CTA
+constexpr uint32_t TILE_M = CTA_M * kCluster;              // rows of D per scheduled tile
 constexpr uint32_t kNumThreads = 256, kNumEpilogueThreads = 128, kEpilogueWarpBase = 4;
-constexpr uint32_t kNumAccumStages = 2;
+// Tensor memory holds two accumulators: two tiles in flight, or the two halves of one
+constexpr uint32_t kNumAccumStages = kMHalves == 1 ? 2 : 1;
 
 static_assert(BLOCK_N % 16 == 0 && BLOCK_N >= 16 && BLOCK_N <= 240, "UMMA_N must be a multiple of 16 that leaves room for the scales");
 static_assert(kGranKA == 32 || kGranKA == 128, "one scale per 32 or 128 elements of K");
 static_assert(kGranKB == 32 || kGranKB == 128, "one scale per 32 or 128 elements of K");
 static_assert(kNumStages >= 2 && kNumStages <= 32, "pipeline depth");
 static_assert(kCluster == 1 || kCluster == 2, "one CTA or a CTA pair per tile");
+static_assert(kMHalves == 1 || (kMHalves == 2 && kCluster == 1), "256-row CTA tiles are built for single CTAs");
 static_assert(!(kAIsFP4 && kAMnMajor) && !(kBIsFP4 && kBMnMajor), "packed FP4 operands must be K-major");
 static_assert(!kBMnMajor || (BLOCK_N / kCluster) % 16 == 0, "an MN-major B load must start on a 16-byte boundary");
-static_assert(!kSplitK || (kGemmType == 0 && kDIsFP32 && !kAccumulate), "split-K serves the plain dense GEMM and writes FP32 partials");
+static_assert(!kSplitK || (kGemmType == 0 && kDIsFP32 && !kAccumulate && kMHalves == 1), "split-K serves the plain dense GEMM and writes FP32 partials");
 
 // Scales: a packed int32 holds 4 scales.  With one scale per 128 K it spans 4 K-blocks, so the
 // chunk is fetched on every 4th K-block; with one per 32 K it spans exactly one K-block.
 constexpr uint32_t kSFAPeriod = kGranKA == 128 ? 4 : 1;
 constexpr uint32_t kSFBPeriod = kGranKB == 128 ? 4 : 1;
-constexpr uint32_t SF_BLOCK_M = 128;
+constexpr uint32_t SF_BLOCK_M = CTA_M;
 constexpr uint32_t SF_BLOCK_N = (BLOCK_N + 127) / 128 * 128;
 
 // Shared memory and tensor memory maps (every operand stage starts on a 1024-byte boundary, as the
 // 128-byte swizzle requires); the arithmetic lives in gemm_config.hpp, shared with the host heuristics
 constexpr uint32_t kDElemBytes = kDIsFP32 ? 4 : 2;
-constexpr GemmLayout kLayout{BLOCK_M, BLOCK_N, BLOCK_K, kNumStages, kDElemBytes, kCluster, kBMnMajor ? 1u : 0u};
+constexpr GemmLayout kLayout{CTA_M, BLOCK_N, BLOCK_K, kNumStages, kDElemBytes, kCluster, kBMnMajor ? 1u : 0u};
 constexpr uint32_t kBAtoms = kLayout.b_atoms();            // 128-column atoms of an MN-major B tile
 constexpr uint32_t kStoreRowBytes   = kLayout.store_row_bytes();     // row width of the boxes covering the ragged end of a tile row
 constexpr uint32_t kStoreCols       = kLayout.store_cols();          // columns of D per such box
@@ -257,6 +269,9 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
         const uint32_t e = (t.split + 1) * p.kb_per_split;
         return e < num_k_blocks ? e : num_k_blocks;
     };
+    // A 256-row tile of the contiguous layout whose halves belong to different experts takes two passes over K:
+    // pass h multiplies half h with B of its own expert
+    auto num_passes_of = [&](const Tile& t) { return kGemmType == 1 && kMHalves == 2 && t.group1 != t.group ? 2u : 1u; };
     Tile tile;
     uint32_t stage = 0, phase = 0;
     auto advance_stage = [&]() {
@@ -272,11 +287,13 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
             DG_PROF_BEGIN(prof_t0);
             while (ok && sched.next(tile)) {
                 // Row coordinates of this CTA's part of the tile in the 2-D views of A, B and the scale tensors
-                const uint32_t a_row = tile.a_row_base + tile.m_block * TILE_M + cta_rank * BLOCK_M;
-                const uint32_t b_row = tile.group * p.shape_n + tile.n_block * BLOCK_N + cta_rank * LOAD_BLOCK_N;
-                const uint32_t sfa_mn = tile.sfa_mn_base + tile.m_block * TILE_M + cta_rank * BLOCK_M;
+                const uint32_t a_row = tile.a_row_base + tile.m_block * TILE_M + cta_rank * CTA_M;
+                const uint32_t sfa_mn = tile.sfa_mn_base + tile.m_block * TILE_M + cta_rank * CTA_M;
                 const uint32_t sfa_row0 = tile.sfa_group * sfa_rows_per_group;
-                const uint32_t sfb_row0 = tile.group * sfb_rows_per_group;
+                for (uint32_t pass = 0, num_passes = num_passes_of(tile); pass < num_passes && ok; ++pass) {
+                const uint32_t b_group = pass == 0 ? tile.group : tile.group1;
+                const uint32_t b_row = b_group * p.shape_n + tile.n_block * BLOCK_N + cta_rank * LOAD_BLOCK_N;
+                const uint32_t sfb_row0 = b_group * sfb_rows_per_group;
                 for (uint32_t kb = kb_begin(tile), kb1 = kb_end(tile); kb < kb1; ++kb, advance_stage()) {
                     DG_PROF_BEGIN(prof_w);
                     if (!mbar_wait(empty_bar(stage), phase ^ 1, ctx, kRoleProducer, 1)) { ok = false; break; }
@@ -301,16 +318,22 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                         else tma_load_2d_2cta(dst, map, load_bar, static_cast<int32_t>(x), static_cast<int32_t>(y));
                     };
                     // K-major: x = K, y = row.  MN-major: x = row (column of the stored matrix), y = K (+ the group's K offset)
-                    if constexpr (!kAMnMajor) load(smem_base + kSmemA + stage * kABytes, &tm_a, kb * BLOCK_K, a_row);
-                    else load(smem_base + kSmemA + stage * kABytes, &tm_a, a_row, kb * BLOCK_K);
+                    if constexpr (!kAMnMajor) {
+                        load(smem_base + kSmemA + stage * kABytes, &tm_a, kb * BLOCK_K, a_row);      // one box of CTA_M rows
+                    } else {
+                        #pragma unroll
+                        for (uint32_t h = 0; h < kMHalves; ++h)
+                            load(smem_base + kSmemA + stage * kABytes + h * BLOCK_M * BLOCK_K, &tm_a, a_row + h * BLOCK_M, kb * BLOCK_K);
+                    }
                     if constexpr (!kBMnMajor) {
                         load(smem_base + kSmemB + stage * kBBytes, &tm_b, kb * BLOCK_K, b_row);
                     } else {
                         #pragma unroll
                         for (uint32_t i = 0; i < kBAtoms; ++i)
                             load(smem_base + kSmemB + stage * kBBytes + i * 128 * BLOCK_K, &tm_b,
-                                 tile.n_block * BLOCK_N + cta_rank * LOAD_BLOCK_N + i * 128, tile.group * p.shape_k + kb * BLOCK_K);
+                                 tile.n_block * BLOCK_N + cta_rank * LOAD_BLOCK_N + i * 128, b_group * p.shape_k + kb * BLOCK_K);
                     }
+                }
                 }
             }
             DG_PROF_VAR(prof_total);
@@ -341,14 +364,14 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
             DG_PROF_VAR(prof_full); DG_PROF_VAR(prof_tmem); DG_PROF_VAR(prof_cp); DG_PROF_VAR(prof_mma); DG_PROF_VAR(prof_commit);
             DG_PROF_BEGIN(prof_t0);
             while (ok && sched.next(tile)) {
-                const uint32_t accum = tile_iter & 1, accum_phase = (tile_iter >> 1) & 1;
+                const uint32_t accum = tile_iter % kNumAccumStages, accum_phase = (tile_iter / kNumAccumStages) & 1;
                 ++tile_iter;
                 DG_PROF_BEGIN(prof_w0);
                 if (!mbar_wait(tmem_empty_bar(accum), accum_phase ^ 1, ctx, kRoleMma, 1)) { ok = false; break; }
                 DG_PROF_ADD(prof_tmem, prof_w0);
                 tc_fence_after_sync();
-                const uint32_t tmem_d = tmem_base + accum * UMMA_N;
                 const uint32_t kb0 = kb_begin(tile), kb1 = kb_end(tile);
+                for (uint32_t pass = 0, num_passes = num_passes_of(tile); pass < num_passes && ok; ++pass) {
                 for (uint32_t kb = kb0; kb < kb1; ++kb, advance_stage()) {
                     DG_PROF_BEGIN(prof_w1);
                     if (!mbar_wait(full_bar(stage), phase, ctx, kRoleMma, 2)) { ok = false; break; }
@@ -357,9 +380,12 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                     tc_fence_after_sync();
                     // Scales: shared memory (rearranged by warp 2) -> tensor memory, in every CTA of the cluster
                     DG_PROF_BEGIN(prof_i0);
-                    if (kb % kSFAPeriod == 0)
-                        tc_cp_32x128b_warpx4<kCluster>(tmem_base + kTmemColSFA,
-                                                       make_smem_desc(smem_base + kSmemSFA + stage * kSFABytes, 0, 128, kSwizzleNone));
+                    if (kb % kSFAPeriod == 0) {
+                        #pragma unroll
+                        for (uint32_t i = 0; i < SF_BLOCK_M / 128; ++i)
+                            tc_cp_32x128b_warpx4<kCluster>(tmem_base + kTmemColSFA + i * 4,
+                                                           make_smem_desc(smem_base + kSmemSFA + stage * kSFABytes + i * 512, 0, 128, kSwizzleNone));
+                    }
                     if (kb % kSFBPeriod == 0) {
                         #pragma unroll
                         for (uint32_t i = 0; i < SF_BLOCK_N / 128; ++i)
@@ -371,21 +397,29 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                     const uint64_t a_desc = make_smem_desc(smem_base + kSmemA + stage * kABytes, kALbo, 1024, kSwizzle128B);
                     const uint64_t b_desc = make_smem_desc(smem_base + kSmemB + stage * kBBytes, kBLbo, 1024, kSwizzle128B);
                     #pragma unroll
-                    for (uint32_t j = 0; j < BLOCK_K / UMMA_K; ++j) {
-                        // Which byte of the packed scale word applies to these 32 elements of K
-                        const uint32_t sfa_id = kGranKA == 32 ? j : (kb % 4);
-                        const uint32_t sfb_id = kGranKB == 32 ? j : (kb % 4);
-                        // Advancing K moves the start address: +32 B inside the swizzle atom (K-major) or +32 rows (MN-major)
-                        tc_mma_mxf8f6f4<kCluster>(tmem_d, a_desc + j * kAStepK, b_desc + j * kBStepK,
-                                                  instr_desc_with_sf_ids(idesc, sfa_id, sfb_id),
-                                                  tmem_base + kTmemColSFA, tmem_base + kTmemColSFB, ((kb - kb0) | j) != 0);
+                    for (uint32_t h = 0; h < kMHalves; ++h) {
+                        if (num_passes == 2 && h != pass) continue;    // this pass carries the other half's expert
+                        // Half h: rows [128 h, 128 h + 128) of the A stage (16 KB further, in either layout), its own
+                        // accumulator and its own four columns of row scales
+                        const uint32_t tmem_d = tmem_base + (accum + h) * UMMA_N;
+                        #pragma unroll
+                        for (uint32_t j = 0; j < BLOCK_K / UMMA_K; ++j) {
+                            // Which byte of the packed scale word applies to these 32 elements of K
+                            const uint32_t sfa_id = kGranKA == 32 ? j : (kb % 4);
+                            const uint32_t sfb_id = kGranKB == 32 ? j : (kb % 4);
+                            // Advancing K moves the start address: +32 B inside the swizzle atom (K-major) or +32 rows (MN-major)
+                            tc_mma_mxf8f6f4<kCluster>(tmem_d, a_desc + h * ((BLOCK_M * BLOCK_K) >> 4) + j * kAStepK, b_desc + j * kBStepK,
+                                                      instr_desc_with_sf_ids(idesc, sfa_id, sfb_id),
+                                                      tmem_base + kTmemColSFA + h * 4, tmem_base + kTmemColSFB, ((kb - kb0) | j) != 0);
+                        }
                     }
                     DG_PROF_ADD(prof_mma, prof_i1);
                     DG_PROF_BEGIN(prof_i2);
                     commit_all(empty_bar(stage));                      // releases the stage once its MMAs have read it
-                    if (kb + 1 == kb1)
-                        commit_all(tmem_full_bar(accum));              // accumulator complete
+                    if (kb + 1 == kb1 && pass + 1 == num_passes)
+                        commit_all(tmem_full_bar(accum));              // accumulator(s) complete
                     DG_PROF_ADD(prof_commit, prof_i2);
+                }
                 }
             }
             DG_PROF_VAR(prof_total);
@@ -413,12 +447,16 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
         DG_PROF_VAR(prof_wait);
         DG_PROF_BEGIN(prof_t0);
         while (ok && sched.next(tile)) {
+            for (uint32_t pass = 0, num_passes = num_passes_of(tile); pass < num_passes && ok; ++pass)
             for (uint32_t kb = kb_begin(tile), kb1 = kb_end(tile); kb < kb1; ++kb, advance_stage()) {
                 DG_PROF_BEGIN(prof_w);
                 if (!mbar_wait(sf_full_bar(stage), phase, ctx, kRoleSF, 1)) { ok = false; break; }
                 DG_PROF_ADD(prof_wait, prof_w);
-                if (kb % kSFAPeriod == 0)
-                    rearrange(smem_base + kSmemSFA + stage * kSFABytes);
+                if (kb % kSFAPeriod == 0) {
+                    #pragma unroll
+                    for (uint32_t i = 0; i < SF_BLOCK_M / 128; ++i)
+                        rearrange(smem_base + kSmemSFA + stage * kSFABytes + i * 512);
+                }
                 if (kb % kSFBPeriod == 0) {
                     #pragma unroll
                     for (uint32_t i = 0; i < SF_BLOCK_N / 128; ++i)
@@ -445,19 +483,21 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
         DG_PROF_VAR(prof_wait); DG_PROF_VAR(prof_store);
         DG_PROF_BEGIN(prof_t0);
         while (ok && sched.next(tile)) {
-            const uint32_t accum = tile_iter & 1, accum_phase = (tile_iter >> 1) & 1;
+            const uint32_t accum = tile_iter % kNumAccumStages, accum_phase = (tile_iter / kNumAccumStages) & 1;
             ++tile_iter;
             DG_PROF_BEGIN(prof_w);
             if (!mbar_wait(tmem_full_bar(accum), accum_phase, ctx, kRoleEpilogue, 1)) { ok = false; break; }
             DG_PROF_ADD(prof_wait, prof_w);
             tc_fence_after_sync();
 
-            const uint32_t d_row0 = tile.d_row_base + tile.m_block * TILE_M + cta_rank * BLOCK_M +
-                                    (kSplitK ? tile.split * p.split_panel_rows : 0u);
             const uint32_t n0 = tile.n_block * BLOCK_N;
-            const uint32_t tmem_row_addr = tmem_base + ((quarter * 32) << 16) + accum * UMMA_N;
-            // Rows of this CTA's half that may be written (fewer than 128 only in a ragged tile of the masked layout)
-            const uint32_t rows_before = cta_rank * BLOCK_M;
+            #pragma unroll 1
+            for (uint32_t h = 0; h < kMHalves; ++h) {
+            const uint32_t d_row0 = tile.d_row_base + tile.m_block * TILE_M + cta_rank * CTA_M + h * BLOCK_M +
+                                    (kSplitK ? tile.split * p.split_panel_rows : 0u);
+            const uint32_t tmem_row_addr = tmem_base + ((quarter * 32) << 16) + (accum + h) * UMMA_N;
+            // Rows of this 128-row part that may be written (fewer than 128 only in a ragged tile of the masked layout)
+            const uint32_t rows_before = cta_rank * CTA_M + h * BLOCK_M;
             const uint32_t valid_rows = tile.valid_rows <= rows_before ? 0u :
                                         (tile.valid_rows - rows_before < BLOCK_M ? tile.valid_rows - rows_before : BLOCK_M);
             const bool direct = kGemmType == 2 && valid_rows < BLOCK_M;
@@ -472,7 +512,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                 for (uint32_t l = 0; l < kMaxLoads; ++l)
                     if (l * 16 < kCols) tmem_ld_32x32b_x16(tmem_row_addr + g * kGroupCols + l * 16, v[l]);
                 tmem_ld_wait();
-                if (g + 1 == kNumGroups) {
+                if (g + 1 == kNumGroups && h + 1 == kMHalves) {
                     // The accumulator is in registers: hand the tensor-memory stage back to the MMA warp
                     tc_fence_before_sync();
                     if (kCluster == 1 || is_leader) mbar_arrive(tmem_empty_bar(accum));
@@ -570,6 +610,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                         }
                     }
                 }
+            }
             }
         }
         if (epi_tid == 0) {

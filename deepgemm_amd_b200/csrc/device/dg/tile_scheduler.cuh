@@ -28,6 +28,7 @@ struct Tile {
     uint32_t m_block;       // row block inside the group (masked) or inside A (dense / contiguous)
     uint32_t n_block;
     uint32_t group;         // which B[g] / SFB[g] this tile multiplies with
+    uint32_t group1;        // contiguous layout with 256-row tiles: the expert of the tile's second 128 rows
     uint32_t a_row_base;    // first row of the group in the 2-D view of A
     uint32_t d_row_base;    // first row of the group in the 2-D view of D
     uint32_t sfa_mn_base;   // first row of the group along the MN axis of SFA
@@ -84,7 +85,7 @@ struct TileScheduler {
                 ++cur_group;
             }
             rasterise(tile_id - group_first_tile, mb, t.m_block, t.n_block);
-            t.group = cur_group;
+            t.group = t.group1 = cur_group;
             t.a_row_base = t.d_row_base = cur_group * shape_m;
             t.sfa_mn_base = 0;
             t.sfa_group = cur_group;
@@ -100,10 +101,15 @@ struct TileScheduler {
             rasterise(mn, num_m_blocks, t.m_block, t.n_block);
             t.split = kKind == kDense ? tile_id - mn * num_splits : 0;
             t.mn_index = mn;
-            t.group = 0;
+            t.group = t.group1 = 0;
             if constexpr (kKind == kMGroupedContiguous) {
                 const int g = layout[t.m_block * kBlockM];
-                t.group = g < 0 ? 0u : static_cast<uint32_t>(g);
+                t.group = t.group1 = g < 0 ? 0u : static_cast<uint32_t>(g);
+                // Expert segments are multiples of 128 rows, so a 256-row tile can end one expert and start the next
+                if (kBlockM == 256 && t.m_block * kBlockM + 128 < shape_m) {
+                    const int g1 = layout[t.m_block * kBlockM + 128];
+                    t.group1 = g1 < 0 ? t.group : static_cast<uint32_t>(g1);
+                }
             }
             t.a_row_base = t.d_row_base = t.sfa_mn_base = t.sfa_group = 0;
             t.valid_rows = kBlockM;

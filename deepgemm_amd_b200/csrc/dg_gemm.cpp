@@ -153,12 +153,17 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
     const int forced_bn = env_int("FORCE_BLOCK_N"), forced_cluster = env_int("FORCE_CLUSTER"), forced_splits = env_int("FORCE_SPLIT_K");
 
     double best_cost = 0;
-    int best_bn = 0, best_cluster = 1, best_splits = 1, best_kb_per_split = static_cast<int>(k_blocks);
+    int best_bn = 0, best_cluster = 1, best_halves = 1, best_splits = 1, best_kb_per_split = static_cast<int>(k_blocks);
     int64_t best_tiles = 0;
-    for (int cluster = 1; cluster <= 2; ++cluster) {
+    const int forced_block_m = env_int("FORCE_BLOCK_M");
+    for (int cluster = 1; cluster <= 2; ++cluster)
+    for (int halves = 1; halves <= 2; ++halves) {
         if (forced_cluster ? cluster != forced_cluster : !cluster_allowed(p, cluster)) continue;
         if (cluster == 2 && (num_sms % 2 != 0 || (p.kind == DG_GEMM_M_GROUPED_CONTIGUOUS && p.m % 256 != 0))) continue;
-        const int tile_m = 128 * cluster, units = num_sms / cluster;
+        // 256 rows per CTA: two 128-row MMAs per K-block on one B stage; single CTAs only, K not sliced
+        if (forced_block_m ? 128 * halves != forced_block_m : (halves == 2 && p.m <= 128)) continue;
+        if (halves == 2 && (cluster != 1 || forced_splits > 1)) continue;
+        const int tile_m = 128 * cluster * halves, units = num_sms / cluster;
         int64_t m_blocks;
         if (p.kind == DG_GEMM_M_GROUPED_MASKED)
             m_blocks = static_cast<int64_t>(p.groups) * ceil_div(std::min(std::max(p.expected_m, 1), p.m), tile_m);
@@ -168,7 +173,7 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
         // clock from L2, so what matters is the bytes a CTA has to pull in; slicing K lets wide tiles (little re-reading
         // of A) still spread over all SMs.  Slices hold a multiple of 4 K-blocks (one packed scale word); all work
         // items run in one wave; the second pass costs a launch plus S FP32 panels of traffic.
-        const bool can_split = p.kind == DG_GEMM_DENSE && !p.accumulate && cluster == 1 && forced_splits != 1 && k_blocks >= 16;
+        const bool can_split = p.kind == DG_GEMM_DENSE && !p.accumulate && cluster == 1 && halves == 1 && forced_splits != 1 && k_blocks >= 16;
         for (int bn = 16; bn <= 240; bn += 16) {
             if (forced_bn && bn != forced_bn) continue;
             if (p.b_mn_major && (bn / cluster) % 16 != 0) continue;       // an MN-major B load starts on a 16-byte boundary
@@ -184,23 +189,27 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
                 }
                 const int64_t tiles = mn_tiles * splits;
                 const int64_t waves = ceil_div<int64_t>(tiles, units);
-                const double mma = 2.0 * bn;
-                const double smem_feed = 128.0 + static_cast<double>(bn) / cluster;
-                const double l2_feed = (16384.0 + 128.0 * bn / cluster) / 67.0;
-                const GemmLayout lay{128, static_cast<uint32_t>(bn), 128, 2, static_cast<uint32_t>(splits > 1 ? 4 : d_elem),
+                const double mma = 2.0 * bn * halves;
+                const double smem_feed = 128.0 * halves + static_cast<double>(bn) / cluster;
+                const double l2_feed = (16384.0 * halves + 128.0 * bn / cluster) / 67.0;
+                const GemmLayout lay{128u * halves, static_cast<uint32_t>(bn), 128, 2, static_cast<uint32_t>(splits > 1 ? 4 : d_elem),
                                      static_cast<uint32_t>(cluster), p.b_mn_major ? 1u : 0u};
+                if (lay.tmem_cols_used() > kTmemCapacityCols || lay.total_bytes() > kSmemCapacity) continue;
                 const double epilogue = 300.0 + 150.0 * lay.num_groups() + 20.0 * lay.num_stores() + bn * 2.0;
                 // The epilogue of a tile overlaps the next tile's main loop; it is exposed once per CTA
                 // + ~1500 cycles per tile that do not shrink with K (tile hand-over, first loads of a new tile), measured
                 // on the K = 512 and K = 1536 shapes
                 const double per_tile = static_cast<double>(kb_per) * std::max(mma, std::max(smem_feed, l2_feed)) + 1500.0;
                 double cost = static_cast<double>(waves) * std::max(per_tile, epilogue) + epilogue + 2000.0;
+                // 256-row tiles have no spare accumulator: both halves are drained before the next tile's MMAs start
+                if (halves == 2) cost = static_cast<double>(waves) * (per_tile + 2.0 * epilogue) + 2000.0;
                 if (splits > 1)   // second launch + reading S panels and writing D at a few TB/s (~2000 B per SM clock over the GPU)
                     cost += 6000.0 + static_cast<double>(splits + 1) * p.m * p.n * 4.0 / 2000.0;
                 if (best_bn == 0 || cost < best_cost - 1e-9 || (std::abs(cost - best_cost) <= 1e-9 && bn > best_bn)) {
                     best_cost = cost;
                     best_bn = bn;
                     best_cluster = cluster;
+                    best_halves = halves;
                     best_tiles = tiles;
                     best_splits = splits;
                     best_kb_per_split = kb_per;
@@ -210,9 +219,10 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
     }
     if (best_bn == 0)
         return fail(DG_ERR_INVALID_ARGUMENT, "no tile configuration: DG_FORCE_BLOCK_N must be a multiple of 16 in [16, 240], "
-                                             "DG_FORCE_CLUSTER 1 or 2 (2 needs an even SM count and, for the contiguous layout, m %% 256 == 0)");
+                                             "DG_FORCE_CLUSTER 1 or 2 (2 needs an even SM count and, for the contiguous layout, m %% 256 == 0), "
+                                             "DG_FORCE_BLOCK_M 128 or 256 (256 only with one CTA per tile and K not sliced)");
 
-    GemmLayout lay{128, static_cast<uint32_t>(best_bn), 128, 2, static_cast<uint32_t>(best_splits > 1 ? 4 : d_elem),
+    GemmLayout lay{128u * best_halves, static_cast<uint32_t>(best_bn), 128, 2, static_cast<uint32_t>(best_splits > 1 ? 4 : d_elem),
                    static_cast<uint32_t>(best_cluster), p.b_mn_major ? 1u : 0u};
     int stages = 2;
     while (stages < 32) {
@@ -230,13 +240,13 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
     const int units = num_sms / best_cluster;
     cfg->num_splits = best_splits;
     cfg->kb_per_split = best_kb_per_split;
-    cfg->block_m = 128;
+    cfg->block_m = 128 * best_halves;
     cfg->block_n = best_bn;
     cfg->block_k = 128;
     cfg->num_stages = stages;
     cfg->cluster_size = best_cluster;
     const int forced_raster = env_int("FORCE_RASTER_GROUP");
-    cfg->raster_group = forced_raster > 0 ? forced_raster : (best_cluster == 2 ? 8 : 16);
+    cfg->raster_group = forced_raster > 0 ? forced_raster : (best_cluster * best_halves == 2 ? 8 : 16);
     cfg->num_ctas = best_cluster * (p.kind == DG_GEMM_M_GROUPED_MASKED
                                         ? units : static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(units, best_tiles))));
     cfg->smem_bytes = static_cast<int>(lay.total_bytes());
@@ -250,6 +260,7 @@ std::string generate_source(const Problem& p, const dg_gemm_config_t& cfg) {
     std::ostringstream s;
     s << "// generated: block-scaled GEMM instantiation\n"
       << "#define DG_GEMM_TYPE " << p.kind << "\n"
+      << "#define DG_M_HALVES " << cfg.block_m / 128 << "\n"
       << "#define DG_BLOCK_N " << cfg.block_n << "\n"
       << "#define DG_NUM_STAGES " << cfg.num_stages << "\n"
       << "#define DG_CLUSTER " << cfg.cluster_size << "\n"
@@ -313,8 +324,8 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
     dg_gemm_config_t cfg;
     if ((rc = choose_config(p, &cfg)) != DG_OK) return rc;
     if (env_int("PRINT_CONFIGS"))
-        fprintf(stderr, "[dg] kind %d m %d n %d k %d groups %d -> block_n %d cluster %d stages %d ctas %d smem %d tiles %d splits %d x %d\n",
-                kind, p.m, p.n, p.k, p.groups, cfg.block_n, cfg.cluster_size, cfg.num_stages, cfg.num_ctas, cfg.smem_bytes, cfg.num_tiles,
+        fprintf(stderr, "[dg] kind %d m %d n %d k %d groups %d -> block_m %d block_n %d cluster %d stages %d ctas %d smem %d tiles %d splits %d x %d\n",
+                kind, p.m, p.n, p.k, p.groups, cfg.block_m, cfg.block_n, cfg.cluster_size, cfg.num_stages, cfg.num_ctas, cfg.smem_bytes, cfg.num_tiles,
                 cfg.num_splits, cfg.kb_per_split);
     dg_kernel_t kernel = nullptr;
     if ((rc = get_kernel(p, cfg, &kernel)) != DG_OK) return rc;
@@ -322,7 +333,7 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
 
     const bool split = cfg.num_splits > 1;
     const bool kernel_d_fp32 = p.d_fp32 || split;
-    const GemmLayout lay{128, static_cast<uint32_t>(cfg.block_n), 128, static_cast<uint32_t>(cfg.num_stages),
+    const GemmLayout lay{static_cast<uint32_t>(cfg.block_m), static_cast<uint32_t>(cfg.block_n), 128, static_cast<uint32_t>(cfg.num_stages),
                          static_cast<uint32_t>(kernel_d_fp32 ? 4 : 2), static_cast<uint32_t>(cfg.cluster_size), p.b_mn_major ? 1u : 0u};
     // Split-K: the kernel's D is the workspace, num_splits panels of [align(m, 128)][align(n, 4)] FP32
     float* workspace = nullptr;
@@ -349,7 +360,7 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
     // MN-major (FP8 only): MN x (groups x K); box = 128 columns of MN x one K-block.
     if (!p.a_mn_major) {
         if ((rc = encode_2d(&tm_a, p.a_fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, a->a,
-                            p.k, a_rows, a->lda, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B)) != DG_OK) return rc;
+                            p.k, a_rows, a->lda, 128, cfg.block_m, CU_TENSOR_MAP_SWIZZLE_128B)) != DG_OK) return rc;
     } else {
         if ((rc = encode_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->a, p.m, p.k, a->lda, 128, 128,
                             CU_TENSOR_MAP_SWIZZLE_128B)) != DG_OK) return rc;
@@ -362,7 +373,7 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
                             CU_TENSOR_MAP_SWIZZLE_128B)) != DG_OK) return rc;
     }
     // Scales: MN (int32) x packed-K rows; the MN extent is the true row count, so reads past it are zero-filled
-    if ((rc = encode_2d(&tm_sfa, CU_TENSOR_MAP_DATA_TYPE_INT32, a->sfa, p.m, sfa_rows, a->sfa_pitch * 4, 128, 1,
+    if ((rc = encode_2d(&tm_sfa, CU_TENSOR_MAP_DATA_TYPE_INT32, a->sfa, p.m, sfa_rows, a->sfa_pitch * 4, cfg.block_m, 1,
                         CU_TENSOR_MAP_SWIZZLE_NONE)) != DG_OK) return rc;
     if ((rc = encode_2d(&tm_sfb, CU_TENSOR_MAP_DATA_TYPE_INT32, a->sfb, p.n, sfb_rows, a->sfb_pitch * 4, lay.sf_block_n(), 1,
                         CU_TENSOR_MAP_SWIZZLE_NONE)) != DG_OK) return rc;

@@ -101,13 +101,14 @@ SHAPES = [(m, n, k) for m in (1, 64, 128, 129, 4096) for (n, k) in
 def test_heuristics_invariants(fp32):
     for m, n, k in SHAPES:
         cfg = dg.get_gemm_config(0, m, n, k, d_is_fp32=fp32)
-        assert cfg["block_m"] == 128 and cfg["block_k"] == 128
+        assert cfg["block_m"] in (128, 256) and cfg["block_k"] == 128
+        assert cfg["block_m"] == 128 or (m > 128 and cfg["num_splits"] == 1 and cfg["cluster_size"] == 1)
         assert cfg["block_n"] % 16 == 0 and 16 <= cfg["block_n"] <= 240
         assert cfg["smem_bytes"] <= 232448, (m, n, k, cfg)
-        assert cfg["tmem_cols"] in (32, 64, 128, 256, 512) and 2 * cfg["block_n"] + 4 + 4 * ((cfg["block_n"] + 127) // 128) <= cfg["tmem_cols"]
+        assert cfg["tmem_cols"] in (32, 64, 128, 256, 512) and 2 * cfg["block_n"] + cfg["block_m"] // 32 + 4 * ((cfg["block_n"] + 127) // 128) <= cfg["tmem_cols"]
         assert 2 <= cfg["num_stages"] <= 32
         assert 1 <= cfg["num_ctas"] <= 148
-        assert cfg["num_tiles"] == -(-m // 128) * -(-n // cfg["block_n"]) * cfg["num_splits"]
+        assert cfg["num_tiles"] == -(-m // cfg["block_m"]) * -(-n // cfg["block_n"]) * cfg["num_splits"]
         kb = -(-k // 128)
         if cfg["num_splits"] > 1:
             # slices start on a packed scale word (4 K-blocks), cover K exactly once, and none is empty

@@ -60,9 +60,12 @@ def test_dense_fp8_matches_reference_python_golden(golden):
 
 
 @pytest.mark.parametrize("forced_bn", [16, 48, 96, 160, 224, 240])
-def test_every_store_width_and_scale_chunking(forced_bn, monkeypatch):
+@pytest.mark.parametrize("block_m", [128, 256])
+def test_every_store_width_and_scale_chunking(forced_bn, block_m, monkeypatch):
     monkeypatch.setenv("DG_FORCE_BLOCK_N", str(forced_bn))
+    monkeypatch.setenv("DG_FORCE_BLOCK_M", str(block_m))
     m, n, k = 256, 720, 1152
+    assert dg.get_gemm_config(0, m, n, k)["block_m"] == block_m
     qa, sfa, qb, sfb, _ = quantise_dense(seeded_bf16((m, k), 3), seeded_bf16((n, k), 4))
     d = _run_dense(qa, sfa, qb, sfb).float().cpu().numpy()
     ref = oracle.dequant_gemm_nt(qa, sfa, qb, sfb)
@@ -87,9 +90,31 @@ def test_cta_pair_variant_matches_oracle(m, n, k, bn, b_fp4, monkeypatch):
     assert np.array_equal(d, d1)
 
 
+@pytest.mark.parametrize("m,n,k,bn", [(256, 480, 512, 240), (129, 256, 256, 64), (384, 128, 128, 128), (1000, 1152, 1792, 224),
+                                      (4096, 720, 2048, 240)])
+@pytest.mark.parametrize("b_fp4,gran_k_a", [(False, 128), (True, 128), (False, 32)])
+def test_256_row_cta_tiles_match_oracle_and_the_128_row_kernel(m, n, k, bn, b_fp4, gran_k_a, monkeypatch):
+    """Two 128-row MMAs per K-block on one B stage (also with the second half partly or wholly out of range)."""
+    monkeypatch.setenv("DG_FORCE_BLOCK_M", "256")
+    monkeypatch.setenv("DG_FORCE_BLOCK_N", str(bn))
+    gk = 32 if b_fp4 else 128
+    assert dg.get_gemm_config(0, m, n, k, b_is_fp4=b_fp4, gran_k_a=gran_k_a, gran_k_b=gk)["block_m"] == 256
+    qa, sfa, qb, sfb, _ = quantise_dense(seeded_bf16((m, k), 5), seeded_bf16((n, k), 6), b_fp4=b_fp4, gran_k_a=gran_k_a)
+    d = _run_dense(qa, sfa, qb, sfb, b_fp4=b_fp4, gran_k_a=gran_k_a, gran_k_b=gk).float().cpu().numpy()
+    ref = oracle.dequant_gemm_nt(qa, sfa, qb, sfb, gran_k_a, gk, False, b_fp4)
+    assert oracle.calc_diff(d, ref) < 1e-5, diff_report(d, ref)
+    monkeypatch.setenv("DG_FORCE_BLOCK_M", "128")
+    d1 = _run_dense(qa, sfa, qb, sfb, b_fp4=b_fp4, gran_k_a=gran_k_a, gran_k_b=gk).float().cpu().numpy()
+    assert np.array_equal(d, d1)
+
+
 @pytest.mark.parametrize("variant", ["nn", "tn", "tt"])
-@pytest.mark.parametrize("m,n,k,cluster", [(128, 256, 512, 1), (208, 720, 1152, 1), (256, 2112, 1024, 1), (384, 704, 640, 2)])
+@pytest.mark.parametrize("m,n,k,cluster", [(128, 256, 512, 1), (208, 720, 1152, 1), (256, 2112, 1024, 1), (384, 704, 640, 2),
+                                           (400, 704, 640, -256)])
 def test_mn_major_operands_through_the_nn_tn_tt_entry_points(variant, m, n, k, cluster, monkeypatch):
+    if cluster < 0:                                                 # one CTA per tile, 256 rows each
+        monkeypatch.setenv("DG_FORCE_BLOCK_M", str(-cluster))
+        cluster = 1
     """tests/test_fp8_fp4.py:41-53: the aliases take the transposed (contiguous) storage of an MN-major operand."""
     monkeypatch.setenv("DG_FORCE_CLUSTER", str(cluster))
     qa, sfa, qb, sfb_rows, sfb_raw = quantise_dense(seeded_bf16((m, k), 16), seeded_bf16((n, k), 17))
@@ -256,11 +281,13 @@ def _grouped_inputs(g, n, k, a, b_fp4=False):
     return qa, sfa, qb, sfb
 
 
-@pytest.mark.parametrize("alignment,cluster", [(128, 1), (256, 1), (256, 2)])
+@pytest.mark.parametrize("alignment,cluster,block_m", [(128, 1, 128), (256, 1, 128), (256, 2, 128), (128, 1, 256), (256, 1, 256)])
 @pytest.mark.parametrize("b_fp4", [False, True])
-def test_m_grouped_contiguous(alignment, cluster, b_fp4, monkeypatch):
+def test_m_grouped_contiguous(alignment, cluster, block_m, b_fp4, monkeypatch):
+    """With 128-row alignment and 256-row tiles, some tiles hold the end of one expert and the start of the next."""
     g, n, k = 5, 1024, 1024
     monkeypatch.setenv("DG_FORCE_CLUSTER", str(cluster))
+    monkeypatch.setenv("DG_FORCE_BLOCK_M", str(block_m))
     dg.set_mk_alignment_for_contiguous_layout(alignment)
     try:
         m, actual, aligned, layout = oracle.make_contiguous_layout(g, 200, alignment, actual_ms=[130, 0, 256, 77, 300])
@@ -324,10 +351,11 @@ def _masked_case(counts, max_m, n, k):
 SENTINEL = -7.0
 
 
-@pytest.mark.parametrize("cluster", [1, 2])
-def test_m_grouped_masked_leaves_rows_beyond_masked_m_untouched(cluster, monkeypatch):
+@pytest.mark.parametrize("cluster,block_m,max_m", [(1, 128, 256), (2, 128, 256), (1, 256, 256), (1, 256, 384)])
+def test_m_grouped_masked_leaves_rows_beyond_masked_m_untouched(cluster, block_m, max_m, monkeypatch):
     monkeypatch.setenv("DG_FORCE_CLUSTER", str(cluster))
-    counts, max_m, n, k = (45, 83, 0, 256, 129, 1), 256, 1000 // 8 * 8, 1024
+    monkeypatch.setenv("DG_FORCE_BLOCK_M", str(block_m))
+    counts, n, k = (45, 83, 0, 256, 129, 1), 1000 // 8 * 8, 1024
     qa, sfa, qb, sfb = _masked_case(counts, max_m, n, k)
     ref = oracle.m_grouped_masked_ref(qa, sfa, qb, sfb, counts)
     d = torch.full((len(counts), max_m, n), SENTINEL, dtype=torch.bfloat16, device="cuda")
