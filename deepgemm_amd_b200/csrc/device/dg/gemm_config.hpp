@@ -22,20 +22,21 @@ struct GemmLayout {
     uint32_t b_mn_major = 0;                       // B stored with N contiguous: staged as 128-column atoms of [128 K][128 B]
 
     DG_HDC uint32_t sf_block_n() const { return (block_n + 127) / 128 * 128; }
-    // D leaves through TMA store boxes of 128 rows.  Complete 128-byte groups of a tile row use a 128-byte-wide box; the
-    // remainder of the row (when block_n * element size is not a multiple of 128) uses boxes of the widest swizzle
-    // span that divides it.
-    DG_HDC uint32_t tail_bytes() const { return (block_n * d_elem_bytes) % 128; }
-    DG_HDC uint32_t store_row_bytes() const {          // row width of the boxes that cover the tail (128 when there is none)
-        return tail_bytes() == 0 ? 128 : (tail_bytes() % 64 == 0 ? 64 : 32);
+    // D leaves through TMA store boxes of 128 rows.  The epilogue drains one "group" of every D row per synchronisation:
+    // 128 bytes with 128-row CTA tiles, 64 bytes with 256-row tiles (whose two epilogue warpgroups each double-buffer
+    // their staging inside the same 32 KB).  Complete groups use a box as wide as the group; the remainder of the tile
+    // row (when block_n * element size is not a multiple of the group) uses boxes of the widest swizzle span dividing it.
+    DG_HDC uint32_t group_bytes() const { return block_m == 256 ? 64 : 128; }
+    DG_HDC uint32_t tail_bytes() const { return (block_n * d_elem_bytes) % group_bytes(); }
+    DG_HDC uint32_t store_row_bytes() const {          // row width of the boxes that cover the tail (the group width when there is none)
+        return tail_bytes() == 0 ? group_bytes() : (tail_bytes() % 64 == 0 ? 64 : 32);
     }
     DG_HDC uint32_t store_cols() const { return store_row_bytes() / d_elem_bytes; }
-    DG_HDC uint32_t num_stores() const { return block_n * d_elem_bytes / 128 + tail_bytes() / store_row_bytes(); }
-    // The epilogue drains 128 bytes of every D row per synchronisation ("group"): 1, 2 or 4 store boxes side by side
-    DG_HDC uint32_t group_cols() const { return 128 / d_elem_bytes; }
+    DG_HDC uint32_t num_stores() const { return block_n * d_elem_bytes / group_bytes() + tail_bytes() / store_row_bytes(); }
+    DG_HDC uint32_t group_cols() const { return group_bytes() / d_elem_bytes; }
     DG_HDC uint32_t num_groups() const { return (block_n + group_cols() - 1) / group_cols(); }
-    DG_HDC uint32_t store_stage_bytes() const { return 128 * 128; }      // staging holds 128 rows x 128 bytes
-    DG_HDC uint32_t num_store_stages() const { return 2; }
+    DG_HDC uint32_t store_stage_bytes() const { return 128 * group_bytes(); }      // staging holds 128 rows of one group
+    DG_HDC uint32_t num_store_stages() const { return 2 * (block_m / 128); }       // two per epilogue warpgroup
 
     DG_HDC uint32_t a_bytes() const { return block_m * block_k; }        // one byte per element (FP8, or FP4 in 16-byte containers)
     DG_HDC uint32_t load_block_n() const { return block_n / cluster; }

@@ -15,6 +15,7 @@
 //   warps 4-7   epilogue: tcgen05.ld -> alpha -> bf16/fp32 -> swizzled staging -> TMA store, 128 bytes of every
 //               row (1, 2 or 4 store boxes) per synchronisation (row-predicated direct stores for ragged tiles
 //               of the masked layout)
+//   warps 8-11  a second epilogue warpgroup, only with 256-row tiles (DG_M_HALVES == 2)
 //
 // The configuration arrives as DG_* macros set by the host-side code generator:
 //   DG_GEMM_TYPE (0 dense, 1 m-grouped contiguous, 2 m-grouped masked), DG_M_HALVES, DG_BLOCK_N, DG_NUM_STAGES,
@@ -81,7 +82,8 @@ constexpr uint32_t UMMA_M = 128 * kCluster, UMMA_N = BLOCK_N, UMMA_K = 32;
 constexpr uint32_t LOAD_BLOCK_N = BLOCK_N / kCluster;      // rows of B each CTA loads
 constexpr uint32_t CTA_M = BLOCK_M * kMHalves;             // rows of A (and D) per CTA
 constexpr uint32_t TILE_M = CTA_M * kCluster;              // rows of D per scheduled tile
-constexpr uint32_t kNumThreads = 256, kNumEpilogueThreads = 128, kEpilogueWarpBase = 4;
+// Four role warps and one epilogue warpgroup per 128 rows of the CTA's tile
+constexpr uint32_t kNumThreads = 128 + 128 * kMHalves, kNumEpilogueThreads = 128, kEpilogueWarpBase = 4;
 // Tensor memory holds two accumulators: two tiles in flight, or the two halves of one
 constexpr uint32_t kNumAccumStages = kMHalves == 1 ? 2 : 1;
 
@@ -90,7 +92,7 @@ static_assert(kGranKA == 32 || kGranKA == 128, "one scale per 32 or 128 elements
 static_assert(kGranKB == 32 || kGranKB == 128, "one scale per 32 or 128 elements of K");
 static_assert(kNumStages >= 2 && kNumStages <= 32, "pipeline depth");
 static_assert(kCluster == 1 || kCluster == 2, "one CTA or a CTA pair per tile");
-static_assert(kMHalves == 1 || (kMHalves == 2 && kCluster == 1), "256-row CTA tiles are built for single CTAs");
+static_assert(kMHalves == 1 || kMHalves == 2, "128 or 256 rows per CTA");
 static_assert(!(kAIsFP4 && kAMnMajor) && !(kBIsFP4 && kBMnMajor), "packed FP4 operands must be K-major");
 static_assert(!kBMnMajor || (BLOCK_N / kCluster) % 16 == 0, "an MN-major B load must start on a 16-byte boundary");
 static_assert(!kSplitK || (kGemmType == 0 && kDIsFP32 && !kAccumulate && kMHalves == 1), "split-K serves the plain dense GEMM and writes FP32 partials");
@@ -229,7 +231,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
         }
         for (uint32_t a = 0; a < kNumAccumStages; ++a) {
             mbar_init(tmem_full_bar(a), 1);      // tcgen05.commit
-            mbar_init(tmem_empty_bar(a), kCluster * kNumEpilogueThreads);   // used in CTA 0 only
+            mbar_init(tmem_empty_bar(a), kCluster * kMHalves * kNumEpilogueThreads);   // used in CTA 0 only
         }
         fence_mbar_init();
     }
@@ -254,6 +256,11 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_base_slot;
     if (threadIdx.x == 0) DG_PROF_STAMP(1);                 // set-up done (barriers, tensor memory)
+    // Everything above touched no global memory, so with programmatic dependent launch it overlapped the tail of the
+    // kernel before this one; from here on its results (and its reads of D) must be complete.  The kernel after
+    // this one may begin its own set-up as soon as SMs free up.
+    griddep_wait();
+    griddep_launch_dependents();
 
     const uint32_t num_k_blocks = (p.shape_k + BLOCK_K - 1) / BLOCK_K;
     const uint32_t sfa_rows_per_group = (p.shape_k + kGranKA * 4 - 1) / (kGranKA * 4);   // packed K extent of SFA
@@ -272,6 +279,12 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
     // A 256-row tile of the contiguous layout whose halves belong to different experts takes two passes over K:
     // pass h multiplies half h with B of its own expert
     auto num_passes_of = [&](const Tile& t) { return kGemmType == 1 && kMHalves == 2 && t.group1 != t.group ? 2u : 1u; };
+    // Every role walks the same sequence of (pass, K-block) steps of a tile, one pipeline stage per step
+    struct Step { uint32_t pass, kb; };
+    auto step_of = [](uint32_t it, uint32_t kb0, uint32_t num_kb) {
+        const uint32_t pass = it >= num_kb ? 1u : 0u;
+        return Step{pass, kb0 + it - pass * num_kb};
+    };
     Tile tile;
     uint32_t stage = 0, phase = 0;
     auto advance_stage = [&]() {
@@ -279,205 +292,230 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
         phase ^= (stage == 0);
     };
 
-    if (warp_idx == 0) {
-        // ================= TMA producer (every CTA loads its own rows of A and its share of B) =================
-        if (lane == 0) {
+    // With 256-row tiles the CTA has three warpgroups and the launch gives every thread 168 registers.  The epilogue
+    // warpgroups keep whole accumulator rows in registers and the role warps need few, so the latter hand registers
+    // over (role + 2 x epilogue = 3 x 168; the contiguous layout's producer tracks two experts per tile and needs more).
+    constexpr uint32_t kRoleRegs = kGemmType == 1 ? 88 : 72, kEpilogueRegs = (3 * 168 - kRoleRegs) / 2;
+    static_assert(kEpilogueRegs % 8 == 0, "register counts move in units of 8");
+    if (warp_idx < kEpilogueWarpBase) {
+        if constexpr (kMHalves == 2) warpgroup_reg_dec<kRoleRegs>();
+        if (warp_idx == 0) {
+            // ================= TMA producer (every CTA loads its own rows of A and its share of B) =================
+            if (lane == 0) {
+                bool ok = true;
+                DG_PROF_VAR(prof_wait);
+                DG_PROF_BEGIN(prof_t0);
+                while (ok && sched.next(tile)) {
+                    // Row coordinates of this CTA's part of the tile in the 2-D views of A, B and the scale tensors
+                    const uint32_t a_row = tile.a_row_base + tile.m_block * TILE_M + cta_rank * CTA_M;
+                    const uint32_t sfa_mn = tile.sfa_mn_base + tile.m_block * TILE_M + cta_rank * CTA_M;
+                    const uint32_t sfa_row0 = tile.sfa_group * sfa_rows_per_group;
+                    const uint32_t kb0 = kb_begin(tile), num_kb = kb_end(tile) - kb0, num_steps = num_passes_of(tile) * num_kb;
+                    for (uint32_t it = 0; it < num_steps; ++it, advance_stage()) {
+                        const auto [pass, kb] = step_of(it, kb0, num_kb);
+                        const uint32_t b_group = pass == 0 ? tile.group : tile.group1;
+                        const uint32_t b_row = b_group * p.shape_n + tile.n_block * BLOCK_N + cta_rank * LOAD_BLOCK_N;
+                        const uint32_t sfb_row0 = b_group * sfb_rows_per_group;
+                        DG_PROF_BEGIN(prof_w);
+                        if (!mbar_wait(empty_bar(stage), phase ^ 1, ctx, kRoleProducer, 1)) { ok = false; break; }
+                        DG_PROF_ADD(prof_wait, prof_w);
+                        uint32_t sf_bytes = 0;
+                        if (kb % kSFAPeriod == 0) sf_bytes += kSFABytes;
+                        if (kb % kSFBPeriod == 0) sf_bytes += kSFBBytes;
+                        mbar_arrive_expect_tx(sf_full_bar(stage), sf_bytes);
+                        if (kb % kSFAPeriod == 0)
+                            tma_load_2d(smem_base + kSmemSFA + stage * kSFABytes, &tm_sfa, sf_full_bar(stage),
+                                        static_cast<int32_t>(sfa_mn), static_cast<int32_t>(sfa_row0 + kb / kSFAPeriod));
+                        if (kb % kSFBPeriod == 0)
+                            tma_load_2d(smem_base + kSmemSFB + stage * kSFBBytes, &tm_sfb, sf_full_bar(stage),
+                                        static_cast<int32_t>(tile.n_block * BLOCK_N), static_cast<int32_t>(sfb_row0 + kb / kSFBPeriod));
+                        // With a cluster the copies land in this CTA and their bytes are counted on CTA 0's barrier,
+                        // which expects both CTAs' bytes
+                        const uint32_t load_bar = kCluster == 1 ? full_bar(stage) : in_leader(full_bar(stage));
+                        if (kCluster == 1 || is_leader) mbar_arrive_expect_tx(full_bar(stage), kTxBytesAB);
+                        else mbar_arrive_cluster(load_bar);
+                        auto load = [&](uint32_t dst, const CUtensorMap* map, uint32_t x, uint32_t y) {
+                            if constexpr (kCluster == 1) tma_load_2d(dst, map, load_bar, static_cast<int32_t>(x), static_cast<int32_t>(y));
+                            else tma_load_2d_2cta(dst, map, load_bar, static_cast<int32_t>(x), static_cast<int32_t>(y));
+                        };
+                        // K-major: x = K, y = row.  MN-major: x = row (column of the stored matrix), y = K (+ the group's K offset)
+                        if constexpr (!kAMnMajor) {
+                            load(smem_base + kSmemA + stage * kABytes, &tm_a, kb * BLOCK_K, a_row);      // one box of CTA_M rows
+                        } else {
+                            #pragma unroll
+                            for (uint32_t h = 0; h < kMHalves; ++h)
+                                load(smem_base + kSmemA + stage * kABytes + h * BLOCK_M * BLOCK_K, &tm_a, a_row + h * BLOCK_M, kb * BLOCK_K);
+                        }
+                        if constexpr (!kBMnMajor) {
+                            load(smem_base + kSmemB + stage * kBBytes, &tm_b, kb * BLOCK_K, b_row);
+                        } else {
+                            #pragma unroll
+                            for (uint32_t i = 0; i < kBAtoms; ++i)
+                                load(smem_base + kSmemB + stage * kBBytes + i * 128 * BLOCK_K, &tm_b,
+                                     tile.n_block * BLOCK_N + cta_rank * LOAD_BLOCK_N + i * 128, b_group * p.shape_k + kb * BLOCK_K);
+                        }
+                    }
+                }
+                DG_PROF_VAR(prof_total);
+                DG_PROF_ADD(prof_total, prof_t0);
+                DG_PROF_FLUSH(kProfProducerWaitEmpty, prof_wait);
+                DG_PROF_FLUSH(kProfProducerTotal, prof_total);
+            }
+        } else if (warp_idx == 1) {
+            // ================= MMA issuer (CTA 0 of the cluster only) =================
+            if (lane == 0 && is_leader) {
+                constexpr uint32_t idesc = make_instr_desc_block_scaled(kAIsFP4 ? kFmtE2M1 : kFmtE4M3, kBIsFP4 ? kFmtE2M1 : kFmtE4M3,
+                                                                        kAMnMajor, kBMnMajor, UMMA_M, UMMA_N);
+                // K-major: 8-row groups of 128-byte rows (SBO 1024), +32 B per UMMA along K.
+                // MN-major: atoms of [128 K][128 B]; SBO 1024 = eight K rows, LBO = one atom, +32 rows (4096 B) per UMMA along K.
+                constexpr uint32_t kALbo = kAMnMajor ? 128 * BLOCK_K : 0, kBLbo = kBMnMajor ? 128 * BLOCK_K : 0;
+                constexpr uint32_t kAStepK = (kAMnMajor ? UMMA_K * 128 : UMMA_K) >> 4, kBStepK = (kBMnMajor ? UMMA_K * 128 : UMMA_K) >> 4;
+                // A commit reaches the barrier at the same offset in every CTA of the cluster
+                auto commit_all = [&](uint32_t bar) {
+                    if constexpr (kCluster == 1) {
+                        tc_commit(bar);
+                    } else {
+                        tc_commit_2cta(map_to_cta(bar, 0));
+                        tc_commit_2cta(map_to_cta(bar, 1));
+                    }
+                };
+                bool ok = true;
+                uint32_t tile_iter = 0;
+                DG_PROF_VAR(prof_full); DG_PROF_VAR(prof_tmem); DG_PROF_VAR(prof_cp); DG_PROF_VAR(prof_mma); DG_PROF_VAR(prof_commit);
+                DG_PROF_BEGIN(prof_t0);
+                while (ok && sched.next(tile)) {
+                    const uint32_t accum = tile_iter % kNumAccumStages, accum_phase = (tile_iter / kNumAccumStages) & 1;
+                    ++tile_iter;
+                    DG_PROF_BEGIN(prof_w0);
+                    if (!mbar_wait(tmem_empty_bar(accum), accum_phase ^ 1, ctx, kRoleMma, 1)) { ok = false; break; }
+                    DG_PROF_ADD(prof_tmem, prof_w0);
+                    tc_fence_after_sync();
+                    const uint32_t kb0 = kb_begin(tile), num_kb = kb_end(tile) - kb0;
+                    const uint32_t num_passes = num_passes_of(tile), num_steps = num_passes * num_kb;
+                    for (uint32_t it = 0; it < num_steps; ++it, advance_stage()) {
+                        const auto [pass, kb] = step_of(it, kb0, num_kb);
+                        DG_PROF_BEGIN(prof_w1);
+                        if (!mbar_wait(full_bar(stage), phase, ctx, kRoleMma, 2)) { ok = false; break; }
+                        DG_PROF_ADD(prof_full, prof_w1);
+                        DG_PROF_STAMP(2);                       // first stage arrived
+                        tc_fence_after_sync();
+                        // Scales: shared memory (rearranged by warp 2) -> tensor memory, in every CTA of the cluster
+                        DG_PROF_BEGIN(prof_i0);
+                        if (kb % kSFAPeriod == 0) {
+                            #pragma unroll
+                            for (uint32_t i = 0; i < SF_BLOCK_M / 128; ++i)
+                                tc_cp_32x128b_warpx4<kCluster>(tmem_base + kTmemColSFA + i * 4,
+                                                               make_smem_desc(smem_base + kSmemSFA + stage * kSFABytes + i * 512, 0, 128, kSwizzleNone));
+                        }
+                        if (kb % kSFBPeriod == 0) {
+                            #pragma unroll
+                            for (uint32_t i = 0; i < SF_BLOCK_N / 128; ++i)
+                                tc_cp_32x128b_warpx4<kCluster>(tmem_base + kTmemColSFB + i * 4,
+                                                               make_smem_desc(smem_base + kSmemSFB + stage * kSFBBytes + i * 512, 0, 128, kSwizzleNone));
+                        }
+                        DG_PROF_ADD(prof_cp, prof_i0);
+                        DG_PROF_BEGIN(prof_i1);
+                        const uint64_t a_desc = make_smem_desc(smem_base + kSmemA + stage * kABytes, kALbo, 1024, kSwizzle128B);
+                        const uint64_t b_desc = make_smem_desc(smem_base + kSmemB + stage * kBBytes, kBLbo, 1024, kSwizzle128B);
+                        #pragma unroll
+                        for (uint32_t h = 0; h < kMHalves; ++h) {
+                            if (num_passes == 2 && h != pass) continue;    // this pass carries the other half's expert
+                            // Half h: rows [128 h, 128 h + 128) of the A stage (16 KB further, in either layout), its own
+                            // accumulator and its own four columns of row scales
+                            const uint32_t tmem_d = tmem_base + (accum + h) * UMMA_N;
+                            #pragma unroll
+                            for (uint32_t j = 0; j < BLOCK_K / UMMA_K; ++j) {
+                                // Which byte of the packed scale word applies to these 32 elements of K
+                                const uint32_t sfa_id = kGranKA == 32 ? j : (kb % 4);
+                                const uint32_t sfb_id = kGranKB == 32 ? j : (kb % 4);
+                                // Advancing K moves the start address: +32 B inside the swizzle atom (K-major) or +32 rows (MN-major)
+                                tc_mma_mxf8f6f4<kCluster>(tmem_d, a_desc + h * ((BLOCK_M * BLOCK_K) >> 4) + j * kAStepK, b_desc + j * kBStepK,
+                                                          instr_desc_with_sf_ids(idesc, sfa_id, sfb_id),
+                                                          tmem_base + kTmemColSFA + h * 4, tmem_base + kTmemColSFB, ((kb - kb0) | j) != 0);
+                            }
+                        }
+                        DG_PROF_ADD(prof_mma, prof_i1);
+                        DG_PROF_BEGIN(prof_i2);
+                        commit_all(empty_bar(stage));                      // releases the stage once its MMAs have read it
+                        if (it + 1 == num_steps)
+                            commit_all(tmem_full_bar(accum));              // accumulator(s) complete
+                        DG_PROF_ADD(prof_commit, prof_i2);
+                    }
+                }
+                DG_PROF_VAR(prof_total);
+                DG_PROF_ADD(prof_total, prof_t0);
+                DG_PROF_FLUSH(kProfMmaWaitFull, prof_full);
+                DG_PROF_FLUSH(kProfMmaWaitTmemEmpty, prof_tmem);
+                DG_PROF_FLUSH(kProfMmaTotal, prof_total);
+                DG_PROF_FLUSH(kProfMmaIssueCp, prof_cp);
+                DG_PROF_FLUSH(kProfMmaIssueMma, prof_mma);
+                DG_PROF_FLUSH(kProfMmaIssueCommit, prof_commit);
+            }
+        } else if (warp_idx == 2) {
+            // ================= scale rearrangement =================
+            // tcgen05.cp reads 32 rows x 16 bytes and writes row r to lane r: the scale word of tile row
+            // (c * 32 + r) has to sit at word (r * 4 + c).  TMA delivered the 128 words in row order.
+            auto rearrange = [&](uint32_t chunk_addr) {
+                uint32_t v[4];
+                #pragma unroll
+                for (uint32_t c = 0; c < 4; ++c)
+                    v[c] = ld_shared_u32(chunk_addr + (c * 32 + lane) * 4);
+                __syncwarp();
+                st_shared_v4(chunk_addr + lane * 16, v[0], v[1], v[2], v[3]);
+            };
             bool ok = true;
             DG_PROF_VAR(prof_wait);
             DG_PROF_BEGIN(prof_t0);
             while (ok && sched.next(tile)) {
-                // Row coordinates of this CTA's part of the tile in the 2-D views of A, B and the scale tensors
-                const uint32_t a_row = tile.a_row_base + tile.m_block * TILE_M + cta_rank * CTA_M;
-                const uint32_t sfa_mn = tile.sfa_mn_base + tile.m_block * TILE_M + cta_rank * CTA_M;
-                const uint32_t sfa_row0 = tile.sfa_group * sfa_rows_per_group;
-                for (uint32_t pass = 0, num_passes = num_passes_of(tile); pass < num_passes && ok; ++pass) {
-                const uint32_t b_group = pass == 0 ? tile.group : tile.group1;
-                const uint32_t b_row = b_group * p.shape_n + tile.n_block * BLOCK_N + cta_rank * LOAD_BLOCK_N;
-                const uint32_t sfb_row0 = b_group * sfb_rows_per_group;
-                for (uint32_t kb = kb_begin(tile), kb1 = kb_end(tile); kb < kb1; ++kb, advance_stage()) {
+                const uint32_t kb0 = kb_begin(tile), num_kb = kb_end(tile) - kb0, num_steps = num_passes_of(tile) * num_kb;
+                for (uint32_t it = 0; it < num_steps; ++it, advance_stage()) {
+                    const uint32_t kb = step_of(it, kb0, num_kb).kb;
                     DG_PROF_BEGIN(prof_w);
-                    if (!mbar_wait(empty_bar(stage), phase ^ 1, ctx, kRoleProducer, 1)) { ok = false; break; }
+                    if (!mbar_wait(sf_full_bar(stage), phase, ctx, kRoleSF, 1)) { ok = false; break; }
                     DG_PROF_ADD(prof_wait, prof_w);
-                    uint32_t sf_bytes = 0;
-                    if (kb % kSFAPeriod == 0) sf_bytes += kSFABytes;
-                    if (kb % kSFBPeriod == 0) sf_bytes += kSFBBytes;
-                    mbar_arrive_expect_tx(sf_full_bar(stage), sf_bytes);
-                    if (kb % kSFAPeriod == 0)
-                        tma_load_2d(smem_base + kSmemSFA + stage * kSFABytes, &tm_sfa, sf_full_bar(stage),
-                                    static_cast<int32_t>(sfa_mn), static_cast<int32_t>(sfa_row0 + kb / kSFAPeriod));
-                    if (kb % kSFBPeriod == 0)
-                        tma_load_2d(smem_base + kSmemSFB + stage * kSFBBytes, &tm_sfb, sf_full_bar(stage),
-                                    static_cast<int32_t>(tile.n_block * BLOCK_N), static_cast<int32_t>(sfb_row0 + kb / kSFBPeriod));
-                    // With a cluster the copies land in this CTA and their bytes are counted on CTA 0's barrier,
-                    // which expects both CTAs' bytes
-                    const uint32_t load_bar = kCluster == 1 ? full_bar(stage) : in_leader(full_bar(stage));
-                    if (kCluster == 1 || is_leader) mbar_arrive_expect_tx(full_bar(stage), kTxBytesAB);
-                    else mbar_arrive_cluster(load_bar);
-                    auto load = [&](uint32_t dst, const CUtensorMap* map, uint32_t x, uint32_t y) {
-                        if constexpr (kCluster == 1) tma_load_2d(dst, map, load_bar, static_cast<int32_t>(x), static_cast<int32_t>(y));
-                        else tma_load_2d_2cta(dst, map, load_bar, static_cast<int32_t>(x), static_cast<int32_t>(y));
-                    };
-                    // K-major: x = K, y = row.  MN-major: x = row (column of the stored matrix), y = K (+ the group's K offset)
-                    if constexpr (!kAMnMajor) {
-                        load(smem_base + kSmemA + stage * kABytes, &tm_a, kb * BLOCK_K, a_row);      // one box of CTA_M rows
-                    } else {
-                        #pragma unroll
-                        for (uint32_t h = 0; h < kMHalves; ++h)
-                            load(smem_base + kSmemA + stage * kABytes + h * BLOCK_M * BLOCK_K, &tm_a, a_row + h * BLOCK_M, kb * BLOCK_K);
-                    }
-                    if constexpr (!kBMnMajor) {
-                        load(smem_base + kSmemB + stage * kBBytes, &tm_b, kb * BLOCK_K, b_row);
-                    } else {
-                        #pragma unroll
-                        for (uint32_t i = 0; i < kBAtoms; ++i)
-                            load(smem_base + kSmemB + stage * kBBytes + i * 128 * BLOCK_K, &tm_b,
-                                 tile.n_block * BLOCK_N + cta_rank * LOAD_BLOCK_N + i * 128, b_group * p.shape_k + kb * BLOCK_K);
-                    }
-                }
-                }
-            }
-            DG_PROF_VAR(prof_total);
-            DG_PROF_ADD(prof_total, prof_t0);
-            DG_PROF_FLUSH(kProfProducerWaitEmpty, prof_wait);
-            DG_PROF_FLUSH(kProfProducerTotal, prof_total);
-        }
-    } else if (warp_idx == 1) {
-        // ================= MMA issuer (CTA 0 of the cluster only) =================
-        if (lane == 0 && is_leader) {
-            constexpr uint32_t idesc = make_instr_desc_block_scaled(kAIsFP4 ? kFmtE2M1 : kFmtE4M3, kBIsFP4 ? kFmtE2M1 : kFmtE4M3,
-                                                                    kAMnMajor, kBMnMajor, UMMA_M, UMMA_N);
-            // K-major: 8-row groups of 128-byte rows (SBO 1024), +32 B per UMMA along K.
-            // MN-major: atoms of [128 K][128 B]; SBO 1024 = eight K rows, LBO = one atom, +32 rows (4096 B) per UMMA along K.
-            constexpr uint32_t kALbo = kAMnMajor ? 128 * BLOCK_K : 0, kBLbo = kBMnMajor ? 128 * BLOCK_K : 0;
-            constexpr uint32_t kAStepK = (kAMnMajor ? UMMA_K * 128 : UMMA_K) >> 4, kBStepK = (kBMnMajor ? UMMA_K * 128 : UMMA_K) >> 4;
-            // A commit reaches the barrier at the same offset in every CTA of the cluster
-            auto commit_all = [&](uint32_t bar) {
-                if constexpr (kCluster == 1) {
-                    tc_commit(bar);
-                } else {
-                    tc_commit_2cta(map_to_cta(bar, 0));
-                    tc_commit_2cta(map_to_cta(bar, 1));
-                }
-            };
-            bool ok = true;
-            uint32_t tile_iter = 0;
-            DG_PROF_VAR(prof_full); DG_PROF_VAR(prof_tmem); DG_PROF_VAR(prof_cp); DG_PROF_VAR(prof_mma); DG_PROF_VAR(prof_commit);
-            DG_PROF_BEGIN(prof_t0);
-            while (ok && sched.next(tile)) {
-                const uint32_t accum = tile_iter % kNumAccumStages, accum_phase = (tile_iter / kNumAccumStages) & 1;
-                ++tile_iter;
-                DG_PROF_BEGIN(prof_w0);
-                if (!mbar_wait(tmem_empty_bar(accum), accum_phase ^ 1, ctx, kRoleMma, 1)) { ok = false; break; }
-                DG_PROF_ADD(prof_tmem, prof_w0);
-                tc_fence_after_sync();
-                const uint32_t kb0 = kb_begin(tile), kb1 = kb_end(tile);
-                for (uint32_t pass = 0, num_passes = num_passes_of(tile); pass < num_passes && ok; ++pass) {
-                for (uint32_t kb = kb0; kb < kb1; ++kb, advance_stage()) {
-                    DG_PROF_BEGIN(prof_w1);
-                    if (!mbar_wait(full_bar(stage), phase, ctx, kRoleMma, 2)) { ok = false; break; }
-                    DG_PROF_ADD(prof_full, prof_w1);
-                    DG_PROF_STAMP(2);                       // first stage arrived
-                    tc_fence_after_sync();
-                    // Scales: shared memory (rearranged by warp 2) -> tensor memory, in every CTA of the cluster
-                    DG_PROF_BEGIN(prof_i0);
                     if (kb % kSFAPeriod == 0) {
                         #pragma unroll
                         for (uint32_t i = 0; i < SF_BLOCK_M / 128; ++i)
-                            tc_cp_32x128b_warpx4<kCluster>(tmem_base + kTmemColSFA + i * 4,
-                                                           make_smem_desc(smem_base + kSmemSFA + stage * kSFABytes + i * 512, 0, 128, kSwizzleNone));
+                            rearrange(smem_base + kSmemSFA + stage * kSFABytes + i * 512);
                     }
                     if (kb % kSFBPeriod == 0) {
                         #pragma unroll
                         for (uint32_t i = 0; i < SF_BLOCK_N / 128; ++i)
-                            tc_cp_32x128b_warpx4<kCluster>(tmem_base + kTmemColSFB + i * 4,
-                                                           make_smem_desc(smem_base + kSmemSFB + stage * kSFBBytes + i * 512, 0, 128, kSwizzleNone));
+                            rearrange(smem_base + kSmemSFB + stage * kSFBBytes + i * 512);
                     }
-                    DG_PROF_ADD(prof_cp, prof_i0);
-                    DG_PROF_BEGIN(prof_i1);
-                    const uint64_t a_desc = make_smem_desc(smem_base + kSmemA + stage * kABytes, kALbo, 1024, kSwizzle128B);
-                    const uint64_t b_desc = make_smem_desc(smem_base + kSmemB + stage * kBBytes, kBLbo, 1024, kSwizzle128B);
-                    #pragma unroll
-                    for (uint32_t h = 0; h < kMHalves; ++h) {
-                        if (num_passes == 2 && h != pass) continue;    // this pass carries the other half's expert
-                        // Half h: rows [128 h, 128 h + 128) of the A stage (16 KB further, in either layout), its own
-                        // accumulator and its own four columns of row scales
-                        const uint32_t tmem_d = tmem_base + (accum + h) * UMMA_N;
-                        #pragma unroll
-                        for (uint32_t j = 0; j < BLOCK_K / UMMA_K; ++j) {
-                            // Which byte of the packed scale word applies to these 32 elements of K
-                            const uint32_t sfa_id = kGranKA == 32 ? j : (kb % 4);
-                            const uint32_t sfb_id = kGranKB == 32 ? j : (kb % 4);
-                            // Advancing K moves the start address: +32 B inside the swizzle atom (K-major) or +32 rows (MN-major)
-                            tc_mma_mxf8f6f4<kCluster>(tmem_d, a_desc + h * ((BLOCK_M * BLOCK_K) >> 4) + j * kAStepK, b_desc + j * kBStepK,
-                                                      instr_desc_with_sf_ids(idesc, sfa_id, sfb_id),
-                                                      tmem_base + kTmemColSFA + h * 4, tmem_base + kTmemColSFB, ((kb - kb0) | j) != 0);
-                        }
-                    }
-                    DG_PROF_ADD(prof_mma, prof_i1);
-                    DG_PROF_BEGIN(prof_i2);
-                    commit_all(empty_bar(stage));                      // releases the stage once its MMAs have read it
-                    if (kb + 1 == kb1 && pass + 1 == num_passes)
-                        commit_all(tmem_full_bar(accum));              // accumulator(s) complete
-                    DG_PROF_ADD(prof_commit, prof_i2);
-                }
+                    fence_proxy_async_smem();
+                    if (kCluster == 1 || is_leader) mbar_arrive(full_bar(stage));
+                    else mbar_arrive_cluster(in_leader(full_bar(stage)));
                 }
             }
-            DG_PROF_VAR(prof_total);
-            DG_PROF_ADD(prof_total, prof_t0);
-            DG_PROF_FLUSH(kProfMmaWaitFull, prof_full);
-            DG_PROF_FLUSH(kProfMmaWaitTmemEmpty, prof_tmem);
-            DG_PROF_FLUSH(kProfMmaTotal, prof_total);
-            DG_PROF_FLUSH(kProfMmaIssueCp, prof_cp);
-            DG_PROF_FLUSH(kProfMmaIssueMma, prof_mma);
-            DG_PROF_FLUSH(kProfMmaIssueCommit, prof_commit);
-        }
-    } else if (warp_idx == 2) {
-        // ================= scale rearrangement =================
-        // tcgen05.cp reads 32 rows x 16 bytes and writes row r to lane r: the scale word of tile row
-        // (c * 32 + r) has to sit at word (r * 4 + c).  TMA delivered the 128 words in row order.
-        auto rearrange = [&](uint32_t chunk_addr) {
-            uint32_t v[4];
-            #pragma unroll
-            for (uint32_t c = 0; c < 4; ++c)
-                v[c] = ld_shared_u32(chunk_addr + (c * 32 + lane) * 4);
-            __syncwarp();
-            st_shared_v4(chunk_addr + lane * 16, v[0], v[1], v[2], v[3]);
-        };
-        bool ok = true;
-        DG_PROF_VAR(prof_wait);
-        DG_PROF_BEGIN(prof_t0);
-        while (ok && sched.next(tile)) {
-            for (uint32_t pass = 0, num_passes = num_passes_of(tile); pass < num_passes && ok; ++pass)
-            for (uint32_t kb = kb_begin(tile), kb1 = kb_end(tile); kb < kb1; ++kb, advance_stage()) {
-                DG_PROF_BEGIN(prof_w);
-                if (!mbar_wait(sf_full_bar(stage), phase, ctx, kRoleSF, 1)) { ok = false; break; }
-                DG_PROF_ADD(prof_wait, prof_w);
-                if (kb % kSFAPeriod == 0) {
-                    #pragma unroll
-                    for (uint32_t i = 0; i < SF_BLOCK_M / 128; ++i)
-                        rearrange(smem_base + kSmemSFA + stage * kSFABytes + i * 512);
-                }
-                if (kb % kSFBPeriod == 0) {
-                    #pragma unroll
-                    for (uint32_t i = 0; i < SF_BLOCK_N / 128; ++i)
-                        rearrange(smem_base + kSmemSFB + stage * kSFBBytes + i * 512);
-                }
-                fence_proxy_async_smem();
-                if (kCluster == 1 || is_leader) mbar_arrive(full_bar(stage));
-                else mbar_arrive_cluster(in_leader(full_bar(stage)));
+            if (lane == 0) {
+                DG_PROF_VAR(prof_total);
+                DG_PROF_ADD(prof_total, prof_t0);
+                DG_PROF_FLUSH(kProfSFWait, prof_wait);
+                DG_PROF_FLUSH(kProfSFTotal, prof_total);
             }
         }
-        if (lane == 0) {
-            DG_PROF_VAR(prof_total);
-            DG_PROF_ADD(prof_total, prof_t0);
-            DG_PROF_FLUSH(kProfSFWait, prof_wait);
-            DG_PROF_FLUSH(kProfSFTotal, prof_total);
-        }
-    } else if (warp_idx >= kEpilogueWarpBase) {
-        // ================= epilogue (every CTA drains the accumulator of its own 128 rows) =================
-        const uint32_t quarter = warp_idx - kEpilogueWarpBase;        // tensor-memory lanes [32q, 32q+32)
-        const uint32_t row_in_tile = quarter * 32 + lane;
-        const uint32_t epi_tid = threadIdx.x - kEpilogueWarpBase * 32;
+    } else {
+        if constexpr (kMHalves == 2) warpgroup_reg_inc<kEpilogueRegs>();
+        // ================= epilogue =================
+        // Warpgroup `wg` (four warps) drains the accumulator of rows [128 wg, 128 wg + 128) of this CTA's tile: one
+        // warpgroup with 128-row tiles, two working side by side with 256-row tiles.
+        const uint32_t wg = (warp_idx - kEpilogueWarpBase) / 4;
+        const uint32_t quarter = warp_idx % 4;                        // tensor-memory lanes [32q, 32q+32)
+        const uint32_t row_in_tile = quarter * 32 + lane;             // row inside the warpgroup's 128 rows
+        const uint32_t epi_tid = threadIdx.x - (kEpilogueWarpBase + 4 * wg) * 32;
+        const uint32_t bar_id = 1 + wg;
+        const bool prof_thread = epi_tid == 0 && wg == 0;
+        // The staging buffers are divided among the warpgroups, two each
+        constexpr uint32_t kBuffersPerWG = kNumStoreStages / kMHalves;
+        static_assert(kBuffersPerWG == 2, "every epilogue warpgroup double-buffers its staging");
+        const uint32_t staging = smem_base + kSmemD + wg * kBuffersPerWG * kStoreStageBytes;
+        // 256-row tiles have no spare accumulator, so the next tile's MMAs wait for this one's tensor-memory reads.
+        // With BF16 output a thread therefore first moves its whole accumulator row into registers (packed, BLOCK_N / 2
+        // of them) and hands tensor memory back before any staging or store.  Otherwise (a spare accumulator, or FP32
+        // output, whose rows would need twice the registers) the row is read group by group.
+        constexpr bool kRowInRegs = kMHalves == 2 && !kDIsFP32;
+        constexpr uint32_t kGroupBytes = kLayout.group_bytes();
         bool ok = true;
         uint32_t tile_iter = 0, store_iter = 0;
         DG_PROF_VAR(prof_wait); DG_PROF_VAR(prof_store);
@@ -491,58 +529,98 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
             tc_fence_after_sync();
 
             const uint32_t n0 = tile.n_block * BLOCK_N;
-            #pragma unroll 1
-            for (uint32_t h = 0; h < kMHalves; ++h) {
-            const uint32_t d_row0 = tile.d_row_base + tile.m_block * TILE_M + cta_rank * CTA_M + h * BLOCK_M +
+            const uint32_t d_row0 = tile.d_row_base + tile.m_block * TILE_M + cta_rank * CTA_M + wg * BLOCK_M +
                                     (kSplitK ? tile.split * p.split_panel_rows : 0u);
-            const uint32_t tmem_row_addr = tmem_base + ((quarter * 32) << 16) + (accum + h) * UMMA_N;
+            const uint32_t tmem_row_addr = tmem_base + ((quarter * 32) << 16) + (accum + wg) * UMMA_N;
             // Rows of this 128-row part that may be written (fewer than 128 only in a ragged tile of the masked layout)
-            const uint32_t rows_before = cta_rank * CTA_M + h * BLOCK_M;
+            const uint32_t rows_before = cta_rank * CTA_M + wg * BLOCK_M;
             const uint32_t valid_rows = tile.valid_rows <= rows_before ? 0u :
                                         (tile.valid_rows - rows_before < BLOCK_M ? tile.valid_rows - rows_before : BLOCK_M);
             const bool direct = kGemmType == 2 && valid_rows < BLOCK_M;
+            auto release_tmem = [&]() {
+                tc_fence_before_sync();
+                if (kCluster == 1 || is_leader) mbar_arrive(tmem_empty_bar(accum));
+                else mbar_arrive_cluster(in_leader(tmem_empty_bar(accum)));
+            };
+
+            [[maybe_unused]] uint32_t row[kRowInRegs ? BLOCK_N / 2 : 1];        // BF16 pairs: columns (2i, 2i+1) of the tile row
+            if constexpr (kRowInRegs) {
+                // 32 columns per round trip to tensor memory (more in flight cost registers the row itself needs:
+                // 48 and 64 columns spilled and measured 3-20 % slower)
+                constexpr uint32_t kLoadsPerTrip = 2;
+                #pragma unroll
+                for (uint32_t b = 0; b < BLOCK_N / 16; b += kLoadsPerTrip) {
+                    uint32_t v[kLoadsPerTrip][16];
+                    #pragma unroll
+                    for (uint32_t l = 0; l < kLoadsPerTrip; ++l)
+                        if (b + l < BLOCK_N / 16) tmem_ld_32x32b_x16(tmem_row_addr + (b + l) * 16, v[l]);
+                    tmem_ld_wait();
+                    #pragma unroll
+                    for (uint32_t l = 0; l < kLoadsPerTrip; ++l)
+                        if (b + l < BLOCK_N / 16) {
+                            #pragma unroll
+                            for (uint32_t i = 0; i < 8; ++i)
+                                row[(b + l) * 8 + i] = pack_bf16x2(__uint_as_float(v[l][2 * i]) * p.alpha,
+                                                                   __uint_as_float(v[l][2 * i + 1]) * p.alpha);
+                        }
+                }
+                release_tmem();
+            }
 
             #pragma unroll
             for (uint32_t g = 0; g < kNumGroups; ++g) {
-                // Columns [g * kGroupCols, + kCols) of the tile: up to 128 bytes of every row
+                // Columns [g * kGroupCols, + kCols) of the tile: one group (or the ragged rest) of every row
                 const uint32_t kCols = (g + 1) * kGroupCols <= BLOCK_N ? kGroupCols : BLOCK_N - g * kGroupCols;
-                constexpr uint32_t kMaxLoads = kGroupCols / 16;
-                uint32_t v[kMaxLoads][16];
-                #pragma unroll
-                for (uint32_t l = 0; l < kMaxLoads; ++l)
-                    if (l * 16 < kCols) tmem_ld_32x32b_x16(tmem_row_addr + g * kGroupCols + l * 16, v[l]);
-                tmem_ld_wait();
-                if (g + 1 == kNumGroups && h + 1 == kMHalves) {
-                    // The accumulator is in registers: hand the tensor-memory stage back to the MMA warp
-                    tc_fence_before_sync();
-                    if (kCluster == 1 || is_leader) mbar_arrive(tmem_empty_bar(accum));
-                    else mbar_arrive_cluster(in_leader(tmem_empty_bar(accum)));
+                constexpr uint32_t kMaxLoads = (kGroupCols + 15) / 16;
+                [[maybe_unused]] uint32_t v[kRowInRegs ? 1 : kMaxLoads][16];
+                if constexpr (!kRowInRegs) {
+                    #pragma unroll
+                    for (uint32_t l = 0; l < kMaxLoads; ++l)
+                        if (l * 16 < kCols) tmem_ld_32x32b_x16(tmem_row_addr + g * kGroupCols + l * 16, v[l]);
+                    tmem_ld_wait();
+                    if (g + 1 == kNumGroups) release_tmem();           // the last of the accumulator is in registers
+                    #pragma unroll
+                    for (uint32_t l = 0; l < kMaxLoads; ++l)
+                        if (l * 16 < kCols) {
+                            #pragma unroll
+                            for (uint32_t i = 0; i < 16; ++i)
+                                v[l][i] = __float_as_uint(__uint_as_float(v[l][i]) * p.alpha);
+                        }
                 }
-                #pragma unroll
-                for (uint32_t l = 0; l < kMaxLoads; ++l)
-                    if (l * 16 < kCols) {
+                // The four registers of 16-byte chunk c of this group's row: 8 BF16 or 4 FP32 values
+                constexpr uint32_t kElemsPerChunk = 16 / kDElemBytes;
+                auto chunk = [&](uint32_t c, uint32_t (&out)[4]) {
+                    if constexpr (kRowInRegs) {
                         #pragma unroll
-                        for (uint32_t i = 0; i < 16; ++i)
-                            v[l][i] = __float_as_uint(__uint_as_float(v[l][i]) * p.alpha);
+                        for (uint32_t i = 0; i < 4; ++i) out[i] = row[g * (kGroupCols / 2) + c * 4 + i];
+                    } else if constexpr (!kDIsFP32) {
+                        const uint32_t l = (c * 8) / 16, i0 = (c * 8) % 16;
+                        #pragma unroll
+                        for (uint32_t i = 0; i < 4; ++i)
+                            out[i] = pack_bf16x2(__uint_as_float(v[l][i0 + 2 * i]), __uint_as_float(v[l][i0 + 2 * i + 1]));
+                    } else {
+                        const uint32_t l = (c * 4) / 16, i0 = (c * 4) % 16;
+                        #pragma unroll
+                        for (uint32_t i = 0; i < 4; ++i) out[i] = v[l][i0 + i];
                     }
+                };
                 const uint32_t col0 = n0 + g * kGroupCols;
 
                 if (!direct) {
-                    const uint32_t sb = store_iter & 1;
+                    const uint32_t sb = store_iter % kBuffersPerWG;
                     ++store_iter;
-                    // The staging buffer is free once the TMA stores issued two groups ago have read it
+                    // The staging buffer is free once the TMA stores issued from it two groups ago have read it
                     DG_PROF_BEGIN(prof_s);
-                    if (epi_tid == 0) tma_store_wait_read<kNumStoreStages - 1>();
-                    named_barrier_sync(1, kNumEpilogueThreads);
+                    if (epi_tid == 0) tma_store_wait_read<kBuffersPerWG - 1>();
+                    named_barrier_sync(bar_id, kNumEpilogueThreads);
                     DG_PROF_ADD(prof_store, prof_s);
-                    const uint32_t stage_addr = smem_base + kSmemD + sb * kStoreStageBytes;
-                    // A complete group is one box of 128-byte rows; the ragged last group of a tile row is split into
-                    // narrower boxes (rows of kStoreRowBytes)
+                    const uint32_t stage_addr = staging + sb * kStoreStageBytes;
+                    // A complete group is one box of kGroupBytes-wide rows; the ragged last group of a tile row is split
+                    // into narrower boxes (rows of kStoreRowBytes)
                     const bool full_group = kCols == kGroupCols;
-                    const uint32_t row_bytes = full_group ? 128u : kStoreRowBytes;
+                    const uint32_t row_bytes = full_group ? kGroupBytes : kStoreRowBytes;
                     const uint32_t box_bytes = BLOCK_M * row_bytes;
                     const uint32_t swizzle_mask = row_bytes == 128 ? 7u : (row_bytes == 64 ? 3u : 1u);
-                    constexpr uint32_t kElemsPerChunk = 16 / kDElemBytes;                 // 8 bf16 or 4 fp32 per 16 bytes
                     #pragma unroll
                     for (uint32_t c = 0; c < kGroupCols / kElemsPerChunk; ++c) {
                         if (c * kElemsPerChunk < kCols) {
@@ -550,19 +628,13 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                             const uint32_t box = (c * 16) / row_bytes, in_row = (c * 16) % row_bytes;
                             const uint32_t off = row_in_tile * row_bytes + in_row;
                             const uint32_t phys = off ^ (((off >> 7) & swizzle_mask) << 4);
-                            const uint32_t e0 = c * kElemsPerChunk, l = e0 / 16, i0 = e0 % 16;
-                            if constexpr (!kDIsFP32)
-                                st_shared_v4(stage_addr + box * box_bytes + phys,
-                                             pack_bf16x2(__uint_as_float(v[l][i0 + 0]), __uint_as_float(v[l][i0 + 1])),
-                                             pack_bf16x2(__uint_as_float(v[l][i0 + 2]), __uint_as_float(v[l][i0 + 3])),
-                                             pack_bf16x2(__uint_as_float(v[l][i0 + 4]), __uint_as_float(v[l][i0 + 5])),
-                                             pack_bf16x2(__uint_as_float(v[l][i0 + 6]), __uint_as_float(v[l][i0 + 7])));
-                            else
-                                st_shared_v4(stage_addr + box * box_bytes + phys, v[l][i0], v[l][i0 + 1], v[l][i0 + 2], v[l][i0 + 3]);
+                            uint32_t q[4];
+                            chunk(c, q);
+                            st_shared_v4(stage_addr + box * box_bytes + phys, q[0], q[1], q[2], q[3]);
                         }
                     }
                     fence_proxy_async_smem();
-                    named_barrier_sync(1, kNumEpilogueThreads);
+                    named_barrier_sync(bar_id, kNumEpilogueThreads);
                     if (epi_tid == 0) {
                         const uint32_t cols_per_box = full_group ? kGroupCols : kStoreCols;
                         const CUtensorMap* map = full_group ? &tm_d_full : &tm_d;
@@ -579,41 +651,35 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                         }
                         tma_store_commit();
                     }
-                } else {
+                } else if (row_in_tile < valid_rows) {
                     // Ragged tile of the masked layout: rows at or beyond the group's row count stay untouched
-                    if (row_in_tile < valid_rows) {
-                        if constexpr (!kDIsFP32) {
-                            __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.d) +
-                                                  static_cast<size_t>(d_row0 + row_in_tile) * p.ldd;
-                            #pragma unroll
-                            for (uint32_t c = 0; c < kGroupCols / 8; ++c) {
-                                if (c * 8 < kCols) {
-                                    const uint32_t l = c / 2, i0 = (c % 2) * 8, col = col0 + c * 8;
-                                    if (col + 8 <= p.shape_n) {
-                                        uint4 q;
-                                        q.x = pack_bf16x2(__uint_as_float(v[l][i0 + 0]), __uint_as_float(v[l][i0 + 1]));
-                                        q.y = pack_bf16x2(__uint_as_float(v[l][i0 + 2]), __uint_as_float(v[l][i0 + 3]));
-                                        q.z = pack_bf16x2(__uint_as_float(v[l][i0 + 4]), __uint_as_float(v[l][i0 + 5]));
-                                        q.w = pack_bf16x2(__uint_as_float(v[l][i0 + 6]), __uint_as_float(v[l][i0 + 7]));
-                                        *reinterpret_cast<uint4*>(drow + col) = q;
-                                    } else {
-                                        for (uint32_t e = 0; e < 8 && col + e < p.shape_n; ++e)
-                                            drow[col + e] = __float2bfloat16_rn(__uint_as_float(v[l][i0 + e]));
-                                    }
+                    if constexpr (!kDIsFP32) {
+                        unsigned short* drow = reinterpret_cast<unsigned short*>(p.d) + static_cast<size_t>(d_row0 + row_in_tile) * p.ldd;
+                        #pragma unroll
+                        for (uint32_t c = 0; c < kGroupCols / 8; ++c) {
+                            if (c * 8 < kCols) {
+                                const uint32_t col = col0 + c * 8;
+                                uint32_t q[4];
+                                chunk(c, q);
+                                if (col + 8 <= p.shape_n) {
+                                    *reinterpret_cast<uint4*>(drow + col) = make_uint4(q[0], q[1], q[2], q[3]);
+                                } else {
+                                    #pragma unroll
+                                    for (uint32_t e = 0; e < 8; ++e)
+                                        if (col + e < p.shape_n) drow[col + e] = static_cast<unsigned short>(q[e / 2] >> (16 * (e % 2)));
                                 }
                             }
-                        } else {
-                            float* drow = reinterpret_cast<float*>(p.d) + static_cast<size_t>(d_row0 + row_in_tile) * p.ldd;
-                            #pragma unroll
-                            for (uint32_t c = 0; c < kGroupCols; ++c)
-                                if (c < kCols && col0 + c < p.shape_n) drow[col0 + c] = __uint_as_float(v[c / 16][c % 16]);
                         }
+                    } else {
+                        float* drow = reinterpret_cast<float*>(p.d) + static_cast<size_t>(d_row0 + row_in_tile) * p.ldd;
+                        #pragma unroll
+                        for (uint32_t c = 0; c < kGroupCols; ++c)
+                            if (c < kCols && col0 + c < p.shape_n) drow[col0 + c] = __uint_as_float(v[c / 16][c % 16]);
                     }
                 }
             }
-            }
         }
-        if (epi_tid == 0) {
+        if (prof_thread) {
             DG_PROF_VAR(prof_total);
             DG_PROF_ADD(prof_total, prof_t0);
             DG_PROF_FLUSH(kProfEpiWaitTmemFull, prof_wait);
@@ -621,9 +687,9 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
             DG_PROF_FLUSH(kProfEpiTotal, prof_total);
         }
         // Every byte of D must be in global memory before the grid completes
-        if (epi_tid == 0) DG_PROF_STAMP(4);                 // last store issued
+        if (prof_thread) DG_PROF_STAMP(4);                  // last store issued
         if (epi_tid == 0) tma_store_wait<0>();
-        if (epi_tid == 0) DG_PROF_STAMP(5);                 // stores complete
+        if (prof_thread) DG_PROF_STAMP(5);                  // stores complete
     }
 
     // ---- tear-down ------------------------------------------------------------------------------

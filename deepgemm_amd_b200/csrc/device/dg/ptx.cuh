@@ -61,6 +61,28 @@ __device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t num_thr
     asm volatile("bar.sync %0, %1;" :: "r"(id), "r"(num_threads) : "memory");
 }
 
+// Programmatic dependent launch.  A kernel launched with programmatic stream serialisation may start while the
+// kernel before it in the stream still runs: griddep_wait() returns once that kernel has completed and its writes
+// are visible; griddep_launch_dependents() lets the kernel after this one start its own preamble.  Both do nothing
+// in a normally launched kernel.
+__device__ __forceinline__ void griddep_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void griddep_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// Moves registers between the warpgroups of a CTA: every warp of a warpgroup (four consecutive warps) gives up or
+// claims registers down / up to kRegs per thread (a multiple of 8)
+template <uint32_t kRegs>
+__device__ __forceinline__ void warpgroup_reg_dec() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" :: "n"(kRegs));
+}
+template <uint32_t kRegs>
+__device__ __forceinline__ void warpgroup_reg_inc() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" :: "n"(kRegs));
+}
+
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* p) {
     asm volatile("prefetch.tensormap [%0];" :: "l"(reinterpret_cast<uint64_t>(p)) : "memory");
 }

@@ -136,14 +136,17 @@ int validate(int kind, const dg_gemm_args_t* a, bool need_pointers, Problem* p) 
 }
 
 // ---- heuristics ------------------------------------------------------------------------------------
-// A CTA works on 128 x block_n x 128 sub-tiles with block_n in 16..240; with cluster_size 2 a CTA pair
-// shares one 256 x block_n tile (tcgen05 cta_group::2) and each CTA loads only half of the B tile.
+// A CTA works on (128 or 256) x block_n x 128 sub-tiles with block_n in 16..240.  With 256 rows it issues two
+// 128-row MMAs per K-block on one B stage, so a K-block carries twice the tensor-core time for (32 KB + B) of loads;
+// with cluster_size 2 a CTA pair shares one tile (tcgen05 cta_group::2) and each CTA loads only half of the B tile.
 // The choice minimises a cycle model of the whole launch:
-//     waves x (k_blocks x max(MMA, shared-memory feed, L2 feed)) + exposed epilogue + launch
+//     waves x (k_blocks x max(MMA, shared-memory feed, L2 feed) + per-tile overhead) + exposed epilogue + launch
 // with per-SM, per-clock figures of B200: 8192 FP8 MACs, 128 B out of shared memory, and ~67 B from L2 into
-// shared memory (the rate measured on this kernel's own loads: 1-CTA tiles of any width ran at that feed rate).
-// The CTA-pair variant is built and tested, but under B200's power cap it measured no faster than one CTA per
-// tile (2.15 vs 2.22 PFLOP/s sustained at M = N = 4096, K = 7168), so it is used only on request (DG_FORCE_CLUSTER=2).
+// shared memory (the rate measured on this kernel's own loads: 128-row tiles of any width ran at that feed rate,
+// which is why 256-row tiles, needing 65 B per clock at block_n 240, are faster wherever M allows them).
+// The CTA-pair variants are built and tested, but under B200's power cap they measured no faster than single CTAs
+// (with 256 rows per CTA: 2.80 vs 2.84 PFLOP/s at M = N = 4096, K = 7168), so they are used only on request
+// (DG_FORCE_CLUSTER=2).
 bool cluster_allowed(const Problem&, int cluster) { return cluster == 1; }
 
 int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
@@ -159,10 +162,13 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
     for (int cluster = 1; cluster <= 2; ++cluster)
     for (int halves = 1; halves <= 2; ++halves) {
         if (forced_cluster ? cluster != forced_cluster : !cluster_allowed(p, cluster)) continue;
-        if (cluster == 2 && (num_sms % 2 != 0 || (p.kind == DG_GEMM_M_GROUPED_CONTIGUOUS && p.m % 256 != 0))) continue;
-        // 256 rows per CTA: two 128-row MMAs per K-block on one B stage; single CTAs only, K not sliced
+        // A CTA pair multiplies all its rows with one B: in the contiguous layout every expert segment must then be a
+        // whole number of pair tiles
+        if (cluster == 2 && (num_sms % 2 != 0 ||
+                             (p.kind == DG_GEMM_M_GROUPED_CONTIGUOUS && state().mk_alignment % (256 * halves) != 0))) continue;
+        // 256 rows per CTA: two 128-row MMAs per K-block on one B stage; K not sliced
         if (forced_block_m ? 128 * halves != forced_block_m : (halves == 2 && p.m <= 128)) continue;
-        if (halves == 2 && (cluster != 1 || forced_splits > 1)) continue;
+        if (halves == 2 && forced_splits > 1) continue;
         const int tile_m = 128 * cluster * halves, units = num_sms / cluster;
         int64_t m_blocks;
         if (p.kind == DG_GEMM_M_GROUPED_MASKED)
@@ -201,8 +207,9 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
                 // on the K = 512 and K = 1536 shapes
                 const double per_tile = static_cast<double>(kb_per) * std::max(mma, std::max(smem_feed, l2_feed)) + 1500.0;
                 double cost = static_cast<double>(waves) * std::max(per_tile, epilogue) + epilogue + 2000.0;
-                // 256-row tiles have no spare accumulator: both halves are drained before the next tile's MMAs start
-                if (halves == 2) cost = static_cast<double>(waves) * (per_tile + 2.0 * epilogue) + 2000.0;
+                // 256-row tiles have no spare accumulator: the next tile's MMAs start once the epilogue warpgroups have
+                // moved their rows from tensor memory into registers (~1400 cycles, measured)
+                if (halves == 2) cost = static_cast<double>(waves) * (per_tile + 1400.0) + epilogue + 2000.0;
                 if (splits > 1)   // second launch + reading S panels and writing D at a few TB/s (~2000 B per SM clock over the GPU)
                     cost += 6000.0 + static_cast<double>(splits + 1) * p.m * p.n * 4.0 / 2000.0;
                 if (best_bn == 0 || cost < best_cost - 1e-9 || (std::abs(cost - best_cost) <= 1e-9 && bn > best_bn)) {
@@ -219,8 +226,8 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
     }
     if (best_bn == 0)
         return fail(DG_ERR_INVALID_ARGUMENT, "no tile configuration: DG_FORCE_BLOCK_N must be a multiple of 16 in [16, 240], "
-                                             "DG_FORCE_CLUSTER 1 or 2 (2 needs an even SM count and, for the contiguous layout, m %% 256 == 0), "
-                                             "DG_FORCE_BLOCK_M 128 or 256 (256 only with one CTA per tile and K not sliced)");
+                                             "DG_FORCE_CLUSTER 1 or 2 (2 needs an even SM count and, for the contiguous layout, expert segments aligned to the pair's rows), "
+                                             "DG_FORCE_BLOCK_M 128 or 256 (256 only with K not sliced)");
 
     GemmLayout lay{128u * best_halves, static_cast<uint32_t>(best_bn), 128, 2, static_cast<uint32_t>(best_splits > 1 ? 4 : d_elem),
                    static_cast<uint32_t>(best_cluster), p.b_mn_major ? 1u : 0u};
@@ -246,7 +253,7 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
     cfg->num_stages = stages;
     cfg->cluster_size = best_cluster;
     const int forced_raster = env_int("FORCE_RASTER_GROUP");
-    cfg->raster_group = forced_raster > 0 ? forced_raster : (best_cluster * best_halves == 2 ? 8 : 16);
+    cfg->raster_group = forced_raster > 0 ? forced_raster : std::max(4, 16 / (best_cluster * best_halves));
     cfg->num_ctas = best_cluster * (p.kind == DG_GEMM_M_GROUPED_MASKED
                                         ? units : static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(units, best_tiles))));
     cfg->smem_bytes = static_cast<int>(lay.total_bytes());
@@ -379,13 +386,15 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
                         CU_TENSOR_MAP_SWIZZLE_NONE)) != DG_OK) return rc;
     const CUtensorMapSwizzle d_swizzle = lay.store_row_bytes() == 128 ? CU_TENSOR_MAP_SWIZZLE_128B :
                                          lay.store_row_bytes() == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
-    // Two views of D: boxes of 128-byte rows for complete groups, narrower boxes for the ragged end of a tile row
+    // Two views of D: boxes as wide as an epilogue group (128 or 64 bytes) for complete groups, narrower boxes for the
+    // ragged end of a tile row
     const CUtensorMapDataType d_type = kernel_d_fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     void* d_base = split ? static_cast<void*>(workspace) : a->d;
     const uint64_t d_rows = split ? static_cast<uint64_t>(cfg.num_splits) * panel_rows : a_rows;
     const uint64_t d_pitch_bytes = split ? ld_ws * 4 : a->ldd * (p.d_fp32 ? 4 : 2);
     if ((rc = encode_2d(&tm_d, d_type, d_base, p.n, d_rows, d_pitch_bytes, lay.store_cols(), 128, d_swizzle)) != DG_OK) return rc;
-    if ((rc = encode_2d(&tm_d_full, d_type, d_base, p.n, d_rows, d_pitch_bytes, lay.group_cols(), 128, CU_TENSOR_MAP_SWIZZLE_128B)) != DG_OK)
+    if ((rc = encode_2d(&tm_d_full, d_type, d_base, p.n, d_rows, d_pitch_bytes, lay.group_cols(), 128,
+                        lay.group_bytes() == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B)) != DG_OK)
         return rc;
 
     GemmParams params;
@@ -407,7 +416,7 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
         params.profile = profile_buffer();
         if (params.profile == nullptr) return fail(DG_ERR_CUDA, "cannot allocate the profile buffer");
         DG_CUDA_RT(cudaMemsetAsync(params.profile, 0, 32 * sizeof(unsigned long long), static_cast<cudaStream_t>(a->stream)));
-        rc = dg_jit_launch(kernel, cfg.num_ctas, 256, cfg.cluster_size, cfg.smem_bytes, state().pdl, a->stream, kargs);
+        rc = dg_jit_launch(kernel, cfg.num_ctas, 128 + cfg.block_m, cfg.cluster_size, cfg.smem_bytes, state().pdl, a->stream, kargs);
         if (rc != DG_OK) return rc;
         unsigned long long h[32];
         DG_CUDA_RT(cudaMemcpyAsync(h, params.profile, sizeof(h), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(a->stream)));
@@ -426,7 +435,7 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
                                         static_cast<cudaStream_t>(a->stream));
         return DG_OK;
     }
-    if ((rc = dg_jit_launch(kernel, cfg.num_ctas, 256, cfg.cluster_size, cfg.smem_bytes, state().pdl, a->stream, kargs)) != DG_OK) return rc;
+    if ((rc = dg_jit_launch(kernel, cfg.num_ctas, 128 + cfg.block_m, cfg.cluster_size, cfg.smem_bytes, state().pdl, a->stream, kargs)) != DG_OK) return rc;
     if (split)
         return launch_splitk_reduce(workspace, a->d, p.m, p.n, ld_ws, panel_rows, a->ldd, cfg.num_splits, alpha, p.d_fp32,
                                     static_cast<cudaStream_t>(a->stream));

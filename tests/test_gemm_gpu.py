@@ -93,17 +93,22 @@ def test_cta_pair_variant_matches_oracle(m, n, k, bn, b_fp4, monkeypatch):
 @pytest.mark.parametrize("m,n,k,bn", [(256, 480, 512, 240), (129, 256, 256, 64), (384, 128, 128, 128), (1000, 1152, 1792, 224),
                                       (4096, 720, 2048, 240)])
 @pytest.mark.parametrize("b_fp4,gran_k_a", [(False, 128), (True, 128), (False, 32)])
-def test_256_row_cta_tiles_match_oracle_and_the_128_row_kernel(m, n, k, bn, b_fp4, gran_k_a, monkeypatch):
-    """Two 128-row MMAs per K-block on one B stage (also with the second half partly or wholly out of range)."""
+@pytest.mark.parametrize("cluster", [1, 2])
+def test_256_row_cta_tiles_match_oracle_and_the_128_row_kernel(m, n, k, bn, b_fp4, gran_k_a, cluster, monkeypatch):
+    """Two 128-row MMAs per K-block on one B stage (also with the second half partly or wholly out of range),
+    by single CTAs and by CTA pairs (512-row tiles)."""
     monkeypatch.setenv("DG_FORCE_BLOCK_M", "256")
     monkeypatch.setenv("DG_FORCE_BLOCK_N", str(bn))
+    monkeypatch.setenv("DG_FORCE_CLUSTER", str(cluster))
     gk = 32 if b_fp4 else 128
-    assert dg.get_gemm_config(0, m, n, k, b_is_fp4=b_fp4, gran_k_a=gran_k_a, gran_k_b=gk)["block_m"] == 256
+    cfg = dg.get_gemm_config(0, m, n, k, b_is_fp4=b_fp4, gran_k_a=gran_k_a, gran_k_b=gk)
+    assert cfg["block_m"] == 256 and cfg["cluster_size"] == cluster
     qa, sfa, qb, sfb, _ = quantise_dense(seeded_bf16((m, k), 5), seeded_bf16((n, k), 6), b_fp4=b_fp4, gran_k_a=gran_k_a)
     d = _run_dense(qa, sfa, qb, sfb, b_fp4=b_fp4, gran_k_a=gran_k_a, gran_k_b=gk).float().cpu().numpy()
     ref = oracle.dequant_gemm_nt(qa, sfa, qb, sfb, gran_k_a, gk, False, b_fp4)
     assert oracle.calc_diff(d, ref) < 1e-5, diff_report(d, ref)
     monkeypatch.setenv("DG_FORCE_BLOCK_M", "128")
+    monkeypatch.setenv("DG_FORCE_CLUSTER", "1")
     d1 = _run_dense(qa, sfa, qb, sfb, b_fp4=b_fp4, gran_k_a=gran_k_a, gran_k_b=gk).float().cpu().numpy()
     assert np.array_equal(d, d1)
 
@@ -210,6 +215,31 @@ def test_fp32_output_accumulation_and_alpha():
     assert np.allclose(d_new.cpu().numpy(), d32 + c0.cpu().numpy(), rtol=1e-6, atol=1e-4)
 
 
+def test_programmatic_dependent_launch_keeps_stream_order():
+    """With set_pdl(True) a GEMM may start while the one before it still runs, but must not read or write global
+    memory before that one is complete: a chain that accumulates into one FP32 D gives the same bits either way."""
+    m, n, k = 512, 1024, 2048
+    qa, sfa, qb, sfb, _ = quantise_dense(seeded_bf16((m, k), 41), seeded_bf16((n, k), 42))
+    a = (fp8_cuda(qa), packed_sf_cuda(sfa)); b = (fp8_cuda(qb), packed_sf_cuda(sfb))
+    results = []
+    try:
+        for pdl in (False, True):
+            dg.set_pdl(pdl)
+            assert dg.get_pdl() == pdl
+            d = torch.empty((m, n), dtype=torch.float, device="cuda")
+            dg.reset_kernel_status()
+            dg.fp8_gemm_nt(a, b, d, recipe=(1, 1, 128))                      # D = A B^T
+            for _ in range(6):
+                dg.fp8_gemm_nt(a, b, d, c=d, recipe=(1, 1, 128))             # D += A B^T, each depends on the last
+            assert dg.kernel_status() == 0
+            results.append(d.cpu())
+    finally:
+        dg.set_pdl(False)
+    assert torch.equal(results[0], results[1])
+    ref = 7 * oracle.dequant_gemm_nt(qa, sfa, qb, sfb)
+    assert oracle.calc_diff(results[1].numpy(), ref) < 1e-9
+
+
 def test_fp32_scales_are_transformed_on_the_fly_like_the_legacy_recipe():
     # float32 SFA [m, k/128] and SFB [n/128, k/128] with the default recipe (1, 128, 128) (csrc/utils/layout.hpp:85-98)
     m, n, k = 128, 2112, 1024
@@ -281,7 +311,8 @@ def _grouped_inputs(g, n, k, a, b_fp4=False):
     return qa, sfa, qb, sfb
 
 
-@pytest.mark.parametrize("alignment,cluster,block_m", [(128, 1, 128), (256, 1, 128), (256, 2, 128), (128, 1, 256), (256, 1, 256)])
+@pytest.mark.parametrize("alignment,cluster,block_m", [(128, 1, 128), (256, 1, 128), (256, 2, 128), (128, 1, 256), (256, 1, 256),
+                                                       (512, 2, 256)])
 @pytest.mark.parametrize("b_fp4", [False, True])
 def test_m_grouped_contiguous(alignment, cluster, block_m, b_fp4, monkeypatch):
     """With 128-row alignment and 256-row tiles, some tiles hold the end of one expert and the start of the next."""
@@ -351,11 +382,11 @@ def _masked_case(counts, max_m, n, k):
 SENTINEL = -7.0
 
 
-@pytest.mark.parametrize("cluster,block_m,max_m", [(1, 128, 256), (2, 128, 256), (1, 256, 256), (1, 256, 384)])
+@pytest.mark.parametrize("cluster,block_m,max_m", [(1, 128, 256), (2, 128, 256), (1, 256, 256), (1, 256, 384), (2, 256, 384), (2, 256, 640)])
 def test_m_grouped_masked_leaves_rows_beyond_masked_m_untouched(cluster, block_m, max_m, monkeypatch):
     monkeypatch.setenv("DG_FORCE_CLUSTER", str(cluster))
     monkeypatch.setenv("DG_FORCE_BLOCK_M", str(block_m))
-    counts, n, k = (45, 83, 0, 256, 129, 1), 1000 // 8 * 8, 1024
+    counts, n, k = (45, 83, 0, max_m, 129, min(300, max_m)), 1000 // 8 * 8, 1024
     qa, sfa, qb, sfb = _masked_case(counts, max_m, n, k)
     ref = oracle.m_grouped_masked_ref(qa, sfa, qb, sfb, counts)
     d = torch.full((len(counts), max_m, n), SENTINEL, dtype=torch.bfloat16, device="cuda")
