@@ -20,6 +20,22 @@ struct GemmLayout {
     uint32_t block_m, block_n, block_k, num_stages, d_elem_bytes;   // block_m: rows of A per CTA and stage (128 or 256)
     uint32_t cluster = 1;                          // CTAs sharing one B tile (each loads block_n / cluster rows of B)
     uint32_t b_mn_major = 0;                       // B stored with N contiguous: staged as 128-column atoms of [128 K][128 B]
+    uint32_t gran_k_a = 128, gran_k_b = 128;       // elements of K per scale (a packed scale word holds four scales)
+    uint32_t short_k = 0;                          // a work item has fewer K-blocks than there are stages
+
+    // A packed scale word covers 4 * gran_k elements of K: it is fetched on every `period`-th K-block of a work item,
+    // into the next of a ring of buffers.  A buffer may be refilled once the fetch it held is no longer among the
+    // last num_stages pipeline steps (the producer is never further ahead of the MMAs).  num_stages consecutive steps
+    // span at most two work items when every item has at least num_stages K-blocks, and then hold at most
+    // ceil(num_stages / period) + 1 fetches; with shorter items every step may fetch.
+    DG_HDC uint32_t sfa_period() const { return 4 * gran_k_a / block_k; }
+    DG_HDC uint32_t sfb_period() const { return 4 * gran_k_b / block_k; }
+    DG_HDC uint32_t sf_buffers(uint32_t period) const {
+        const uint32_t n = (num_stages + period - 1) / period + 1;
+        return short_k || n > num_stages ? num_stages : n;
+    }
+    DG_HDC uint32_t sfa_buffers() const { return sf_buffers(sfa_period()); }
+    DG_HDC uint32_t sfb_buffers() const { return sf_buffers(sfb_period()); }
 
     DG_HDC uint32_t sf_block_n() const { return (block_n + 127) / 128 * 128; }
     // D leaves through TMA store boxes of 128 rows.  The epilogue drains one "group" of every D row per synchronisation:
@@ -49,15 +65,14 @@ struct GemmLayout {
     DG_HDC uint32_t off_a() const { return (num_store_stages() * store_stage_bytes() + 1023) / 1024 * 1024; }
     DG_HDC uint32_t off_b() const { return off_a() + num_stages * a_bytes(); }
     DG_HDC uint32_t off_sfa() const { return off_b() + num_stages * b_bytes(); }
-    DG_HDC uint32_t off_sfb() const { return off_sfa() + num_stages * sfa_bytes(); }
-    DG_HDC uint32_t off_barriers() const { return off_sfb() + num_stages * sfb_bytes(); }
+    DG_HDC uint32_t off_sfb() const { return off_sfa() + sfa_buffers() * sfa_bytes(); }
+    DG_HDC uint32_t off_barriers() const { return off_sfb() + sfb_buffers() * sfb_bytes(); }
     DG_HDC uint32_t num_barriers() const { return 3 * num_stages + 2 * 2; }
     DG_HDC uint32_t off_misc() const { return off_barriers() + num_barriers() * 8; }
     DG_HDC uint32_t total_bytes() const { return off_misc() + 16; }      // tensor-memory base, abort flag
-    DG_HDC uint32_t bytes_per_stage() const { return a_bytes() + b_bytes() + sfa_bytes() + sfb_bytes() + 3 * 8; }
 
     // Tensor memory: two accumulators of block_n columns (two tiles in flight when block_m is 128, the two 128-row
-    // halves of one tile when it is 256), then SFA (4 columns per 128 rows) and SFB
+    // halves of one tile when it is 256), then SFA (4 columns per 128 rows) and SFB (4 columns per 128 columns of the tile)
     DG_HDC uint32_t tmem_col_sfa() const { return 2 * block_n; }
     DG_HDC uint32_t tmem_col_sfb() const { return tmem_col_sfa() + block_m / 32; }
     DG_HDC uint32_t tmem_cols_used() const { return tmem_col_sfb() + sf_block_n() / 32; }

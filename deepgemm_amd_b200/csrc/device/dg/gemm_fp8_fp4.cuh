@@ -9,7 +9,7 @@
 //
 //   warp 0      TMA producer: fills a ring of kNumStages {A, B, SFA, SFB} shared-memory stages
 //   warp 1      MMA issuer: one thread issues tcgen05.cp (scales -> tensor memory) and
-//               tcgen05.mma.kind::mxf8f6f4.block_scale into one of two accumulator stages
+//               tcgen05.mma.kind::mxf8f6f4.block_scale into one of two accumulators
 //   warp 2      allocates tensor memory; rearranges each scale chunk for tcgen05.cp
 //   warp 3      idle
 //   warps 4-7   epilogue: tcgen05.ld -> alpha -> bf16/fp32 -> swizzled staging -> TMA store, 128 bytes of every
@@ -62,7 +62,7 @@ namespace dg {
 constexpr uint32_t kGemmType   = DG_GEMM_TYPE;
 constexpr uint32_t BLOCK_M     = 128;
 constexpr uint32_t BLOCK_N     = DG_BLOCK_N;
-constexpr uint32_t BLOCK_K     = 128;
+constexpr uint32_t BLOCK_K     = DG_BLOCK_K;       // elements of K per pipeline stage (64 or 128)
 constexpr uint32_t kNumStages  = DG_NUM_STAGES;
 constexpr uint32_t kCluster    = DG_CLUSTER;       // CTAs cooperating on one tile (1 or 2)
 constexpr bool     kAIsFP4     = DG_A_FP4 != 0;
@@ -91,23 +91,29 @@ static_assert(BLOCK_N % 16 == 0 && BLOCK_N >= 16 && BLOCK_N <= 240, "UMMA_N must
 static_assert(kGranKA == 32 || kGranKA == 128, "one scale per 32 or 128 elements of K");
 static_assert(kGranKB == 32 || kGranKB == 128, "one scale per 32 or 128 elements of K");
 static_assert(kNumStages >= 2 && kNumStages <= 32, "pipeline depth");
+static_assert(BLOCK_K == 128 || (BLOCK_K == 64 && !kAIsFP4 && !kBIsFP4 && !kAMnMajor && !kBMnMajor && !kSplitK),
+              "64-element stages are built for K-major FP8 operands and unsliced K");
 static_assert(kCluster == 1 || kCluster == 2, "one CTA or a CTA pair per tile");
 static_assert(kMHalves == 1 || kMHalves == 2, "128 or 256 rows per CTA");
 static_assert(!(kAIsFP4 && kAMnMajor) && !(kBIsFP4 && kBMnMajor), "packed FP4 operands must be K-major");
 static_assert(!kBMnMajor || (BLOCK_N / kCluster) % 16 == 0, "an MN-major B load must start on a 16-byte boundary");
 static_assert(!kSplitK || (kGemmType == 0 && kDIsFP32 && !kAccumulate && kMHalves == 1), "split-K serves the plain dense GEMM and writes FP32 partials");
 
-// Scales: a packed int32 holds 4 scales.  With one scale per 128 K it spans 4 K-blocks, so the
-// chunk is fetched on every 4th K-block; with one per 32 K it spans exactly one K-block.
-constexpr uint32_t kSFAPeriod = kGranKA == 128 ? 4 : 1;
-constexpr uint32_t kSFBPeriod = kGranKB == 128 ? 4 : 1;
+// Scales: a packed int32 holds 4 scales, so it spans 4 * gran_k elements of K and is fetched on every
+// (4 * gran_k / BLOCK_K)-th K-block: every 4th (8th with 64-element stages) at one scale per 128 K, every (2nd) one
+// at one per 32 K.
+constexpr uint32_t kSFAPeriod = 4 * kGranKA / BLOCK_K;
+constexpr uint32_t kSFBPeriod = 4 * kGranKB / BLOCK_K;
 constexpr uint32_t SF_BLOCK_M = CTA_M;
 constexpr uint32_t SF_BLOCK_N = (BLOCK_N + 127) / 128 * 128;
 
 // Shared memory and tensor memory maps (every operand stage starts on a 1024-byte boundary, as the
 // 128-byte swizzle requires); the arithmetic lives in gemm_config.hpp, shared with the host heuristics
 constexpr uint32_t kDElemBytes = kDIsFP32 ? 4 : 2;
-constexpr GemmLayout kLayout{CTA_M, BLOCK_N, BLOCK_K, kNumStages, kDElemBytes, kCluster, kBMnMajor ? 1u : 0u};
+constexpr GemmLayout kLayout{CTA_M, BLOCK_N, BLOCK_K, kNumStages, kDElemBytes, kCluster, kBMnMajor ? 1u : 0u, kGranKA, kGranKB,
+                             DG_SHORT_K};
+constexpr uint32_t kNumSFABuffers = kLayout.sfa_buffers(), kNumSFBBuffers = kLayout.sfb_buffers();
+static_assert(kSFAPeriod >= 1 && kSFBPeriod >= 1 && kSFAPeriod == kLayout.sfa_period() && kSFBPeriod == kLayout.sfb_period(), "scale fetch period");
 constexpr uint32_t kBAtoms = kLayout.b_atoms();            // 128-column atoms of an MN-major B tile
 constexpr uint32_t kStoreRowBytes   = kLayout.store_row_bytes();     // row width of the boxes covering the ragged end of a tile row
 constexpr uint32_t kStoreCols       = kLayout.store_cols();          // columns of D per such box
@@ -128,7 +134,7 @@ constexpr uint32_t kSmemSFB = kLayout.off_sfb();
 constexpr uint32_t kSmemBar = kLayout.off_barriers();   // full, sf_full, empty per stage; tmem_full, tmem_empty per accumulator
 constexpr uint32_t kSmemMisc = kLayout.off_misc();      // tensor-memory base address, abort flag
 constexpr uint32_t kSmemTotal = kLayout.total_bytes();
-static_assert(kBBytes % 1024 == 0, "B stage must keep 1024-byte alignment");
+static_assert(kABytes % (8 * BLOCK_K) == 0 && kBBytes % (8 * BLOCK_K) == 0, "every stage starts on a swizzle-pattern boundary (eight rows)");
 static_assert(kSmemTotal <= kSmemCapacity, "shared memory budget exceeded");
 static_assert(kStoreCols % 16 == 0 || kDIsFP32, "a store covers whole 16-column tensor-memory loads");
 
@@ -204,7 +210,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
     auto sf_full_bar  = [&](uint32_t s) { return smem_base + kSmemBar + (kNumStages + s) * 8; };
     auto empty_bar    = [&](uint32_t s) { return smem_base + kSmemBar + (2 * kNumStages + s) * 8; };
     auto tmem_full_bar  = [&](uint32_t a) { return smem_base + kSmemBar + (3 * kNumStages + a) * 8; };
-    auto tmem_empty_bar = [&](uint32_t a) { return smem_base + kSmemBar + (3 * kNumStages + kNumAccumStages + a) * 8; };
+    auto tmem_empty_bar = [&](uint32_t a) { return smem_base + kSmemBar + (3 * kNumStages + 2 + a) * 8; };
     // shared::cluster address of a barrier of CTA 0 (the local address when there is no cluster)
     auto in_leader = [&](uint32_t bar) { return kCluster == 1 ? bar : map_to_cta(bar, 0); };
     volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(smem + kSmemMisc);
@@ -229,9 +235,9 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
             mbar_init(sf_full_bar(s), 1);
             mbar_init(empty_bar(s), 1);          // tcgen05.commit
         }
-        for (uint32_t a = 0; a < kNumAccumStages; ++a) {
+        for (uint32_t a = 0; a < 2; ++a) {       // one pair per accumulator: two tiles in flight, or the halves of one
             mbar_init(tmem_full_bar(a), 1);      // tcgen05.commit
-            mbar_init(tmem_empty_bar(a), kCluster * kMHalves * kNumEpilogueThreads);   // used in CTA 0 only
+            mbar_init(tmem_empty_bar(a), kCluster * kNumEpilogueThreads);   // used in CTA 0 only
         }
         fence_mbar_init();
     }
@@ -285,6 +291,14 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
         const uint32_t pass = it >= num_kb ? 1u : 0u;
         return Step{pass, kb0 + it - pass * num_kb};
     };
+    // Scale words land in a ring of buffers, one per fetch (see GemmLayout::sf_buffers); every role counts the fetches
+    uint32_t sfa_slot = 0, sfb_slot = 0;
+    auto sfa_buffer = [&]() { return smem_base + kSmemSFA + sfa_slot * kSFABytes; };
+    auto sfb_buffer = [&]() { return smem_base + kSmemSFB + sfb_slot * kSFBBytes; };
+    auto advance_sf = [&](uint32_t kb) {
+        if (kb % kSFAPeriod == 0) sfa_slot = sfa_slot + 1 == kNumSFABuffers ? 0 : sfa_slot + 1;
+        if (kb % kSFBPeriod == 0) sfb_slot = sfb_slot + 1 == kNumSFBBuffers ? 0 : sfb_slot + 1;
+    };
     Tile tile;
     uint32_t stage = 0, phase = 0;
     auto advance_stage = [&]() {
@@ -324,10 +338,10 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                         if (kb % kSFBPeriod == 0) sf_bytes += kSFBBytes;
                         mbar_arrive_expect_tx(sf_full_bar(stage), sf_bytes);
                         if (kb % kSFAPeriod == 0)
-                            tma_load_2d(smem_base + kSmemSFA + stage * kSFABytes, &tm_sfa, sf_full_bar(stage),
+                            tma_load_2d(sfa_buffer(), &tm_sfa, sf_full_bar(stage),
                                         static_cast<int32_t>(sfa_mn), static_cast<int32_t>(sfa_row0 + kb / kSFAPeriod));
                         if (kb % kSFBPeriod == 0)
-                            tma_load_2d(smem_base + kSmemSFB + stage * kSFBBytes, &tm_sfb, sf_full_bar(stage),
+                            tma_load_2d(sfb_buffer(), &tm_sfb, sf_full_bar(stage),
                                         static_cast<int32_t>(tile.n_block * BLOCK_N), static_cast<int32_t>(sfb_row0 + kb / kSFBPeriod));
                         // With a cluster the copies land in this CTA and their bytes are counted on CTA 0's barrier,
                         // which expects both CTAs' bytes
@@ -354,6 +368,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                                 load(smem_base + kSmemB + stage * kBBytes + i * 128 * BLOCK_K, &tm_b,
                                      tile.n_block * BLOCK_N + cta_rank * LOAD_BLOCK_N + i * 128, b_group * p.shape_k + kb * BLOCK_K);
                         }
+                        advance_sf(kb);
                     }
                 }
                 DG_PROF_VAR(prof_total);
@@ -366,9 +381,12 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
             if (lane == 0 && is_leader) {
                 constexpr uint32_t idesc = make_instr_desc_block_scaled(kAIsFP4 ? kFmtE2M1 : kFmtE4M3, kBIsFP4 ? kFmtE2M1 : kFmtE4M3,
                                                                         kAMnMajor, kBMnMajor, UMMA_M, UMMA_N);
-                // K-major: 8-row groups of 128-byte rows (SBO 1024), +32 B per UMMA along K.
+                // K-major: 8-row groups of BLOCK_K-byte rows (SBO 1024 or 512, swizzle span = the row), +32 B per UMMA along K.
                 // MN-major: atoms of [128 K][128 B]; SBO 1024 = eight K rows, LBO = one atom, +32 rows (4096 B) per UMMA along K.
                 constexpr uint32_t kALbo = kAMnMajor ? 128 * BLOCK_K : 0, kBLbo = kBMnMajor ? 128 * BLOCK_K : 0;
+                constexpr uint32_t kASbo = kAMnMajor ? 1024 : 8 * BLOCK_K, kBSbo = kBMnMajor ? 1024 : 8 * BLOCK_K;
+                constexpr uint64_t kASwizzle = kAMnMajor || BLOCK_K == 128 ? kSwizzle128B : kSwizzle64B;
+                constexpr uint64_t kBSwizzle = kBMnMajor || BLOCK_K == 128 ? kSwizzle128B : kSwizzle64B;
                 constexpr uint32_t kAStepK = (kAMnMajor ? UMMA_K * 128 : UMMA_K) >> 4, kBStepK = (kBMnMajor ? UMMA_K * 128 : UMMA_K) >> 4;
                 // A commit reaches the barrier at the same offset in every CTA of the cluster
                 auto commit_all = [&](uint32_t bar) {
@@ -384,10 +402,16 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                 DG_PROF_VAR(prof_full); DG_PROF_VAR(prof_tmem); DG_PROF_VAR(prof_cp); DG_PROF_VAR(prof_mma); DG_PROF_VAR(prof_commit);
                 DG_PROF_BEGIN(prof_t0);
                 while (ok && sched.next(tile)) {
+                    // First accumulator (and barrier pair) of this tile: tiles alternate between the two, or the halves of a
+                    // 256-row tile own one each
                     const uint32_t accum = tile_iter % kNumAccumStages, accum_phase = (tile_iter / kNumAccumStages) & 1;
                     ++tile_iter;
                     DG_PROF_BEGIN(prof_w0);
-                    if (!mbar_wait(tmem_empty_bar(accum), accum_phase ^ 1, ctx, kRoleMma, 1)) { ok = false; break; }
+                    bool accum_free = true;
+                    #pragma unroll
+                    for (uint32_t h = 0; h < kMHalves; ++h)
+                        accum_free = accum_free && mbar_wait(tmem_empty_bar(accum + h), accum_phase ^ 1, ctx, kRoleMma, 1);
+                    if (!accum_free) { ok = false; break; }
                     DG_PROF_ADD(prof_tmem, prof_w0);
                     tc_fence_after_sync();
                     const uint32_t kb0 = kb_begin(tile), num_kb = kb_end(tile) - kb0;
@@ -405,29 +429,30 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                             #pragma unroll
                             for (uint32_t i = 0; i < SF_BLOCK_M / 128; ++i)
                                 tc_cp_32x128b_warpx4<kCluster>(tmem_base + kTmemColSFA + i * 4,
-                                                               make_smem_desc(smem_base + kSmemSFA + stage * kSFABytes + i * 512, 0, 128, kSwizzleNone));
+                                                               make_smem_desc(sfa_buffer() + i * 512, 0, 128, kSwizzleNone));
                         }
                         if (kb % kSFBPeriod == 0) {
                             #pragma unroll
                             for (uint32_t i = 0; i < SF_BLOCK_N / 128; ++i)
                                 tc_cp_32x128b_warpx4<kCluster>(tmem_base + kTmemColSFB + i * 4,
-                                                               make_smem_desc(smem_base + kSmemSFB + stage * kSFBBytes + i * 512, 0, 128, kSwizzleNone));
+                                                               make_smem_desc(sfb_buffer() + i * 512, 0, 128, kSwizzleNone));
                         }
                         DG_PROF_ADD(prof_cp, prof_i0);
                         DG_PROF_BEGIN(prof_i1);
-                        const uint64_t a_desc = make_smem_desc(smem_base + kSmemA + stage * kABytes, kALbo, 1024, kSwizzle128B);
-                        const uint64_t b_desc = make_smem_desc(smem_base + kSmemB + stage * kBBytes, kBLbo, 1024, kSwizzle128B);
+                        const uint64_t a_desc = make_smem_desc(smem_base + kSmemA + stage * kABytes, kALbo, kASbo, kASwizzle);
+                        const uint64_t b_desc = make_smem_desc(smem_base + kSmemB + stage * kBBytes, kBLbo, kBSbo, kBSwizzle);
                         #pragma unroll
                         for (uint32_t h = 0; h < kMHalves; ++h) {
-                            if (num_passes == 2 && h != pass) continue;    // this pass carries the other half's expert
-                            // Half h: rows [128 h, 128 h + 128) of the A stage (16 KB further, in either layout), its own
-                            // accumulator and its own four columns of row scales
+                            // In a two-pass tile (halves of different experts) pass p carries half p's expert
+                            if (num_passes == 2 && h != pass) continue;
+                            // Half h: rows [128 h, 128 h + 128) of the A stage (128 * BLOCK_K bytes further, in either layout),
+                            // its own accumulator and its own four columns of row scales
                             const uint32_t tmem_d = tmem_base + (accum + h) * UMMA_N;
                             #pragma unroll
                             for (uint32_t j = 0; j < BLOCK_K / UMMA_K; ++j) {
                                 // Which byte of the packed scale word applies to these 32 elements of K
-                                const uint32_t sfa_id = kGranKA == 32 ? j : (kb % 4);
-                                const uint32_t sfb_id = kGranKB == 32 ? j : (kb % 4);
+                                const uint32_t sfa_id = ((kb * BLOCK_K + j * UMMA_K) / kGranKA) % 4;
+                                const uint32_t sfb_id = ((kb * BLOCK_K + j * UMMA_K) / kGranKB) % 4;
                                 // Advancing K moves the start address: +32 B inside the swizzle atom (K-major) or +32 rows (MN-major)
                                 tc_mma_mxf8f6f4<kCluster>(tmem_d, a_desc + h * ((BLOCK_M * BLOCK_K) >> 4) + j * kAStepK, b_desc + j * kBStepK,
                                                           instr_desc_with_sf_ids(idesc, sfa_id, sfb_id),
@@ -437,9 +462,12 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                         DG_PROF_ADD(prof_mma, prof_i1);
                         DG_PROF_BEGIN(prof_i2);
                         commit_all(empty_bar(stage));                      // releases the stage once its MMAs have read it
-                        if (it + 1 == num_steps)
-                            commit_all(tmem_full_bar(accum));              // accumulator(s) complete
+                        if (it + 1 == num_steps) {                         // accumulator(s) complete
+                            #pragma unroll
+                            for (uint32_t h = 0; h < kMHalves; ++h) commit_all(tmem_full_bar(accum + h));
+                        }
                         DG_PROF_ADD(prof_commit, prof_i2);
+                        advance_sf(kb);
                     }
                 }
                 DG_PROF_VAR(prof_total);
@@ -476,16 +504,17 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                     if (kb % kSFAPeriod == 0) {
                         #pragma unroll
                         for (uint32_t i = 0; i < SF_BLOCK_M / 128; ++i)
-                            rearrange(smem_base + kSmemSFA + stage * kSFABytes + i * 512);
+                            rearrange(sfa_buffer() + i * 512);
                     }
                     if (kb % kSFBPeriod == 0) {
                         #pragma unroll
                         for (uint32_t i = 0; i < SF_BLOCK_N / 128; ++i)
-                            rearrange(smem_base + kSmemSFB + stage * kSFBBytes + i * 512);
+                            rearrange(sfb_buffer() + i * 512);
                     }
                     fence_proxy_async_smem();
                     if (kCluster == 1 || is_leader) mbar_arrive(full_bar(stage));
                     else mbar_arrive_cluster(in_leader(full_bar(stage)));
+                    advance_sf(kb);
                 }
             }
             if (lane == 0) {
@@ -521,7 +550,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
         DG_PROF_VAR(prof_wait); DG_PROF_VAR(prof_store);
         DG_PROF_BEGIN(prof_t0);
         while (ok && sched.next(tile)) {
-            const uint32_t accum = tile_iter % kNumAccumStages, accum_phase = (tile_iter / kNumAccumStages) & 1;
+            const uint32_t accum = tile_iter % kNumAccumStages + wg, accum_phase = (tile_iter / kNumAccumStages) & 1;
             ++tile_iter;
             DG_PROF_BEGIN(prof_w);
             if (!mbar_wait(tmem_full_bar(accum), accum_phase, ctx, kRoleEpilogue, 1)) { ok = false; break; }
@@ -531,7 +560,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
             const uint32_t n0 = tile.n_block * BLOCK_N;
             const uint32_t d_row0 = tile.d_row_base + tile.m_block * TILE_M + cta_rank * CTA_M + wg * BLOCK_M +
                                     (kSplitK ? tile.split * p.split_panel_rows : 0u);
-            const uint32_t tmem_row_addr = tmem_base + ((quarter * 32) << 16) + (accum + wg) * UMMA_N;
+            const uint32_t tmem_row_addr = tmem_base + ((quarter * 32) << 16) + accum * UMMA_N;
             // Rows of this 128-row part that may be written (fewer than 128 only in a ragged tile of the masked layout)
             const uint32_t rows_before = cta_rank * CTA_M + wg * BLOCK_M;
             const uint32_t valid_rows = tile.valid_rows <= rows_before ? 0u :

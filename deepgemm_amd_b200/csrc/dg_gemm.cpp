@@ -137,30 +137,49 @@ int validate(int kind, const dg_gemm_args_t* a, bool need_pointers, Problem* p) 
 
 // ---- heuristics ------------------------------------------------------------------------------------
 // A CTA works on (128 or 256) x block_n x 128 sub-tiles with block_n in 16..240.  With 256 rows it issues two
-// 128-row MMAs per K-block on one B stage, so a K-block carries twice the tensor-core time for (32 KB + B) of loads;
-// with cluster_size 2 a CTA pair shares one tile (tcgen05 cta_group::2) and each CTA loads only half of the B tile.
-// The choice minimises a cycle model of the whole launch:
-//     waves x (k_blocks x max(MMA, shared-memory feed, L2 feed) + per-tile overhead) + exposed epilogue + launch
-// with per-SM, per-clock figures of B200: 8192 FP8 MACs, 128 B out of shared memory, and ~67 B from L2 into
-// shared memory (the rate measured on this kernel's own loads: 128-row tiles of any width ran at that feed rate,
-// which is why 256-row tiles, needing 65 B per clock at block_n 240, are faster wherever M allows them).
-// The CTA-pair variants are built and tested, but under B200's power cap they measured no faster than single CTAs
-// (with 256 rows per CTA: 2.80 vs 2.84 PFLOP/s at M = N = 4096, K = 7168), so they are used only on request
-// (DG_FORCE_CLUSTER=2).
+// 128-row MMAs per K-block on one B stage; with cluster_size 2 a CTA pair shares one tile (tcgen05 cta_group::2) and
+// each CTA loads only half of the B tile.  The choice minimises a cycle model of the whole launch:
+//     waves x (k_blocks x max(MMA, shared-memory traffic, stage ring) + per-tile overhead) + exposed epilogue + launch
+// with per-SM, per-clock figures of B200: 8192 FP8 MACs and ~150 B through shared memory, writes by TMA and reads by
+// the tensor core together.  The latter was fitted on this kernel: seven tile widths of the 256-row kernel and the
+// 128-row kernel all ran within 5 % of (bytes written + bytes read) / 150 cycles per K-block.  It is why 256-row tiles
+// win wherever M allows them: their B stage is written once and read by two MMAs' worth of rows.
+// Measured end to end the long-K shapes then sit at the GPU's power limit: variants that need fewer cycles (a second
+// issuing thread, CTA pairs) ran at proportionally lower SM clocks and took the same time, so the CTA-pair variants
+// stay available on request only (DG_FORCE_CLUSTER=2).
 bool cluster_allowed(const Problem&, int cluster) { return cluster == 1; }
+
+// Layout of a candidate with the deepest pipeline that fits shared memory.  `item_kb` is the number of K-blocks (of
+// block_k elements) one work item walks; fewer than the stage count makes the scale ring one buffer per stage.
+GemmLayout fit_stages(GemmLayout lay, int64_t item_kb, int max_stages) {
+    GemmLayout best = lay;
+    best.num_stages = 0;
+    for (int stages = 2; stages <= max_stages; ++stages) {
+        lay.num_stages = static_cast<uint32_t>(stages);
+        lay.short_k = item_kb < stages ? 1u : 0u;
+        if (lay.total_bytes() > kSmemCapacity) break;
+        best = lay;
+    }
+    return best;
+}
 
 int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
     const int num_sms = dg_get_num_sms();
     const int d_elem = p.d_fp32 ? 4 : 2;
-    const int64_t k_blocks = ceil_div(p.k, 128);
+    const int64_t k_blocks = ceil_div(p.k, 128);           // in units of 128 elements, whatever the stage size
     const int forced_bn = env_int("FORCE_BLOCK_N"), forced_cluster = env_int("FORCE_CLUSTER"), forced_splits = env_int("FORCE_SPLIT_K");
+    const int forced_block_m = env_int("FORCE_BLOCK_M"), forced_block_k = env_int("FORCE_BLOCK_K");
+    const int forced_stages = env_int("FORCE_NUM_STAGES");
 
-    double best_cost = 0;
-    int best_bn = 0, best_cluster = 1, best_halves = 1, best_splits = 1, best_kb_per_split = static_cast<int>(k_blocks);
-    int64_t best_tiles = 0;
-    const int forced_block_m = env_int("FORCE_BLOCK_M");
+    struct Candidate {
+        double cost = 0;
+        int bn = 0, bk = 128, cluster = 1, halves = 1, splits = 1, kb_per_split = 0;
+        int64_t tiles = 0;
+        GemmLayout lay{};
+    } best;
     for (int cluster = 1; cluster <= 2; ++cluster)
-    for (int halves = 1; halves <= 2; ++halves) {
+    for (int halves = 1; halves <= 2; ++halves)
+    for (int bk = 128; bk >= 64; bk /= 2) {
         if (forced_cluster ? cluster != forced_cluster : !cluster_allowed(p, cluster)) continue;
         // A CTA pair multiplies all its rows with one B: in the contiguous layout every expert segment must then be a
         // whole number of pair tiles
@@ -169,17 +188,23 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
         // 256 rows per CTA: two 128-row MMAs per K-block on one B stage; K not sliced
         if (forced_block_m ? 128 * halves != forced_block_m : (halves == 2 && p.m <= 128)) continue;
         if (halves == 2 && forced_splits > 1) continue;
+        // Stages of 64 elements of K (twice as many, each half the bytes): K-major FP8 operands and unsliced K only.
+        // Built and tested, but it measured 0-20 % slower than 128-element stages on every shape tried (the 64-byte
+        // rows double the number of L2 requests), so it is used only on request (DG_FORCE_BLOCK_K=64).
+        if (bk != (forced_block_k ? forced_block_k : 128)) continue;
+        if (bk == 64 && (p.a_fp4 || p.b_fp4 || p.a_mn_major || p.b_mn_major || forced_splits > 1)) continue;
         const int tile_m = 128 * cluster * halves, units = num_sms / cluster;
         int64_t m_blocks;
         if (p.kind == DG_GEMM_M_GROUPED_MASKED)
             m_blocks = static_cast<int64_t>(p.groups) * ceil_div(std::min(std::max(p.expected_m, 1), p.m), tile_m);
         else
             m_blocks = ceil_div(p.m, tile_m);
-        // Slicing K: dense GEMMs whose output has too few tiles to occupy the GPU.  Every CTA ingests at most ~67 B per
-        // clock from L2, so what matters is the bytes a CTA has to pull in; slicing K lets wide tiles (little re-reading
-        // of A) still spread over all SMs.  Slices hold a multiple of 4 K-blocks (one packed scale word); all work
-        // items run in one wave; the second pass costs a launch plus S FP32 panels of traffic.
-        const bool can_split = p.kind == DG_GEMM_DENSE && !p.accumulate && cluster == 1 && halves == 1 && forced_splits != 1 && k_blocks >= 16;
+        // Slicing K: dense GEMMs whose output has too few tiles to occupy the GPU.  What matters is the bytes a CTA has
+        // to pull in; slicing K lets wide tiles (little re-reading of A) still spread over all SMs.  Slices hold a
+        // multiple of 4 K-blocks (one packed scale word); all work items run in one wave; the second pass costs a
+        // launch plus S FP32 panels of traffic.
+        const bool can_split = p.kind == DG_GEMM_DENSE && !p.accumulate && cluster == 1 && halves == 1 && bk == 128 &&
+                               forced_splits != 1 && k_blocks >= 16;
         for (int bn = 16; bn <= 240; bn += 16) {
             if (forced_bn && bn != forced_bn) continue;
             if (p.b_mn_major && (bn / cluster) % 16 != 0) continue;       // an MN-major B load starts on a 16-byte boundary
@@ -195,72 +220,80 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
                 }
                 const int64_t tiles = mn_tiles * splits;
                 const int64_t waves = ceil_div<int64_t>(tiles, units);
-                const double mma = 2.0 * bn * halves;
-                const double smem_feed = 128.0 * halves + static_cast<double>(bn) / cluster;
-                const double l2_feed = (16384.0 * halves + 128.0 * bn / cluster) / 67.0;
-                const GemmLayout lay{128u * halves, static_cast<uint32_t>(bn), 128, 2, static_cast<uint32_t>(splits > 1 ? 4 : d_elem),
-                                     static_cast<uint32_t>(cluster), p.b_mn_major ? 1u : 0u};
-                if (lay.tmem_cols_used() > kTmemCapacityCols || lay.total_bytes() > kSmemCapacity) continue;
+                // The pipeline: as deep as shared memory allows, but no deeper than the K-blocks of two work items
+                const int64_t item_kb = ceil_div<int64_t>(std::min<int64_t>(p.k, static_cast<int64_t>(kb_per) * 128), bk);
+                int max_stages = static_cast<int>(std::max<int64_t>(2, std::min<int64_t>(32, 2 * item_kb)));
+                if (forced_stages >= 2) max_stages = std::min(max_stages, forced_stages);
+                GemmLayout lay{128u * halves, static_cast<uint32_t>(bn), static_cast<uint32_t>(bk), 2,
+                               static_cast<uint32_t>(splits > 1 ? 4 : d_elem), static_cast<uint32_t>(cluster),
+                               p.b_mn_major ? 1u : 0u, static_cast<uint32_t>(p.gran_k_a), static_cast<uint32_t>(p.gran_k_b), 0u};
+                lay = fit_stages(lay, item_kb, max_stages);
+                if (lay.num_stages == 0 || lay.tmem_cols_used() > kTmemCapacityCols) continue;
+                // Cycles per pipeline stage: the MMAs; shared memory, which moved ~150 B per cycle in every configuration
+                // measured, TMA writes and tensor-core reads together (a stage is written once, its A rows are read once
+                // and its B rows once per 128-row half), and into which no configuration pulled more than ~67 B per cycle
+                // from L2; and the ring of stages, `stages` of which complete per (load latency + MMA time).
+                const double stage_frac = bk / 128.0;
+                const double mma = 2.0 * bn * halves * stage_frac;
+                const double stage_bytes = (128.0 * halves + static_cast<double>(bn) / cluster) * bk;
+                const double read_bytes = (128.0 * halves + halves * static_cast<double>(bn) / cluster) * bk;
+                const double smem_feed = std::max((stage_bytes + read_bytes) / 150.0, stage_bytes / 67.0);
+                const double ring = (1500.0 + mma) / lay.num_stages;
                 const double epilogue = 300.0 + 150.0 * lay.num_groups() + 20.0 * lay.num_stores() + bn * 2.0;
                 // The epilogue of a tile overlaps the next tile's main loop; it is exposed once per CTA
                 // + ~1500 cycles per tile that do not shrink with K (tile hand-over, first loads of a new tile), measured
                 // on the K = 512 and K = 1536 shapes
-                const double per_tile = static_cast<double>(kb_per) * std::max(mma, std::max(smem_feed, l2_feed)) + 1500.0;
+                const double per_tile = static_cast<double>(item_kb) * std::max(mma, std::max(smem_feed, ring)) + 1500.0;
                 double cost = static_cast<double>(waves) * std::max(per_tile, epilogue) + epilogue + 2000.0;
                 // 256-row tiles have no spare accumulator: the next tile's MMAs start once the epilogue warpgroups have
                 // moved their rows from tensor memory into registers (~1400 cycles, measured)
                 if (halves == 2) cost = static_cast<double>(waves) * (per_tile + 1400.0) + epilogue + 2000.0;
                 if (splits > 1)   // second launch + reading S panels and writing D at a few TB/s (~2000 B per SM clock over the GPU)
                     cost += 6000.0 + static_cast<double>(splits + 1) * p.m * p.n * 4.0 / 2000.0;
-                if (best_bn == 0 || cost < best_cost - 1e-9 || (std::abs(cost - best_cost) <= 1e-9 && bn > best_bn)) {
-                    best_cost = cost;
-                    best_bn = bn;
-                    best_cluster = cluster;
-                    best_halves = halves;
-                    best_tiles = tiles;
-                    best_splits = splits;
-                    best_kb_per_split = kb_per;
+                if (best.bn == 0 || cost < best.cost - 1e-9 || (std::abs(cost - best.cost) <= 1e-9 && bn > best.bn)) {
+                    best.cost = cost;
+                    best.bn = bn; best.bk = bk; best.cluster = cluster; best.halves = halves;
+                    best.tiles = tiles; best.splits = splits; best.kb_per_split = kb_per;
+                    best.lay = lay;
                 }
             }
         }
     }
-    if (best_bn == 0)
+    if (best.bn == 0)
         return fail(DG_ERR_INVALID_ARGUMENT, "no tile configuration: DG_FORCE_BLOCK_N must be a multiple of 16 in [16, 240], "
                                              "DG_FORCE_CLUSTER 1 or 2 (2 needs an even SM count and, for the contiguous layout, expert segments aligned to the pair's rows), "
-                                             "DG_FORCE_BLOCK_M 128 or 256 (256 only with K not sliced)");
+                                             "DG_FORCE_BLOCK_M 128 or 256 (256 only with K not sliced), "
+                                             "DG_FORCE_BLOCK_K 64 or 128 (64 only for K-major FP8 operands and K not sliced)");
 
-    GemmLayout lay{128u * best_halves, static_cast<uint32_t>(best_bn), 128, 2, static_cast<uint32_t>(best_splits > 1 ? 4 : d_elem),
-                   static_cast<uint32_t>(best_cluster), p.b_mn_major ? 1u : 0u};
-    int stages = 2;
-    while (stages < 32) {
-        GemmLayout next = lay;
-        next.num_stages = stages + 1;
-        if (next.total_bytes() > kSmemCapacity) break;
-        ++stages;
-    }
-    const int forced_stages = env_int("FORCE_NUM_STAGES");
-    if (forced_stages >= 2 && forced_stages <= stages) stages = forced_stages;
-    // No point in more stages than K-blocks of two tiles
-    stages = static_cast<int>(std::max<int64_t>(2, std::min<int64_t>(stages, 2 * best_kb_per_split)));
-    lay.num_stages = stages;
-
-    const int units = num_sms / best_cluster;
-    cfg->num_splits = best_splits;
-    cfg->kb_per_split = best_kb_per_split;
-    cfg->block_m = 128 * best_halves;
-    cfg->block_n = best_bn;
-    cfg->block_k = 128;
-    cfg->num_stages = stages;
-    cfg->cluster_size = best_cluster;
+    const int units = num_sms / best.cluster;
+    cfg->num_splits = best.splits;
+    cfg->kb_per_split = best.kb_per_split;
+    cfg->block_m = 128 * best.halves;
+    cfg->block_n = best.bn;
+    cfg->block_k = best.bk;
+    cfg->num_stages = static_cast<int>(best.lay.num_stages);
+    cfg->cluster_size = best.cluster;
     const int forced_raster = env_int("FORCE_RASTER_GROUP");
-    cfg->raster_group = forced_raster > 0 ? forced_raster : std::max(4, 16 / (best_cluster * best_halves));
-    cfg->num_ctas = best_cluster * (p.kind == DG_GEMM_M_GROUPED_MASKED
-                                        ? units : static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(units, best_tiles))));
-    cfg->smem_bytes = static_cast<int>(lay.total_bytes());
-    cfg->tmem_cols = static_cast<int>(lay.tmem_cols_alloc());
-    cfg->num_tiles = static_cast<int>(best_tiles);
-    cfg->waves_x100 = static_cast<int>(best_tiles * 100 / units);
+    cfg->raster_group = forced_raster > 0 ? forced_raster : std::max(4, 16 / (best.cluster * best.halves));
+    cfg->num_ctas = best.cluster * (p.kind == DG_GEMM_M_GROUPED_MASKED
+                                        ? units : static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(units, best.tiles))));
+    cfg->smem_bytes = static_cast<int>(best.lay.total_bytes());
+    cfg->tmem_cols = static_cast<int>(best.lay.tmem_cols_alloc());
+    cfg->num_tiles = static_cast<int>(best.tiles);
+    cfg->waves_x100 = static_cast<int>(best.tiles * 100 / units);
     return DG_OK;
+}
+
+// The layout the kernel of a configuration uses (same arithmetic as choose_config)
+GemmLayout layout_of(const Problem& p, const dg_gemm_config_t& cfg) {
+    const bool split = cfg.num_splits > 1;
+    const int64_t item_kb = ceil_div<int64_t>(std::min<int64_t>(p.k, static_cast<int64_t>(cfg.kb_per_split) * 128), cfg.block_k);
+    GemmLayout lay{static_cast<uint32_t>(cfg.block_m), static_cast<uint32_t>(cfg.block_n), static_cast<uint32_t>(cfg.block_k),
+                   static_cast<uint32_t>(cfg.num_stages), static_cast<uint32_t>((p.d_fp32 || split) ? 4 : 2),
+                   static_cast<uint32_t>(cfg.cluster_size), p.b_mn_major ? 1u : 0u,
+                   static_cast<uint32_t>(p.gran_k_a), static_cast<uint32_t>(p.gran_k_b),
+                   item_kb < cfg.num_stages ? 1u : 0u};
+    return lay;
 }
 
 std::string generate_source(const Problem& p, const dg_gemm_config_t& cfg) {
@@ -269,6 +302,8 @@ std::string generate_source(const Problem& p, const dg_gemm_config_t& cfg) {
       << "#define DG_GEMM_TYPE " << p.kind << "\n"
       << "#define DG_M_HALVES " << cfg.block_m / 128 << "\n"
       << "#define DG_BLOCK_N " << cfg.block_n << "\n"
+      << "#define DG_BLOCK_K " << cfg.block_k << "\n"
+      << "#define DG_SHORT_K " << layout_of(p, cfg).short_k << "\n"
       << "#define DG_NUM_STAGES " << cfg.num_stages << "\n"
       << "#define DG_CLUSTER " << cfg.cluster_size << "\n"
       << "#define DG_A_FP4 " << (p.a_fp4 ? 1 : 0) << "\n"
@@ -331,8 +366,8 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
     dg_gemm_config_t cfg;
     if ((rc = choose_config(p, &cfg)) != DG_OK) return rc;
     if (env_int("PRINT_CONFIGS"))
-        fprintf(stderr, "[dg] kind %d m %d n %d k %d groups %d -> block_m %d block_n %d cluster %d stages %d ctas %d smem %d tiles %d splits %d x %d\n",
-                kind, p.m, p.n, p.k, p.groups, cfg.block_m, cfg.block_n, cfg.cluster_size, cfg.num_stages, cfg.num_ctas, cfg.smem_bytes, cfg.num_tiles,
+        fprintf(stderr, "[dg] kind %d m %d n %d k %d groups %d -> block_m %d block_n %d block_k %d cluster %d stages %d ctas %d smem %d tiles %d splits %d x %d\n",
+                kind, p.m, p.n, p.k, p.groups, cfg.block_m, cfg.block_n, cfg.block_k, cfg.cluster_size, cfg.num_stages, cfg.num_ctas, cfg.smem_bytes, cfg.num_tiles,
                 cfg.num_splits, cfg.kb_per_split);
     dg_kernel_t kernel = nullptr;
     if ((rc = get_kernel(p, cfg, &kernel)) != DG_OK) return rc;
@@ -340,8 +375,7 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
 
     const bool split = cfg.num_splits > 1;
     const bool kernel_d_fp32 = p.d_fp32 || split;
-    const GemmLayout lay{static_cast<uint32_t>(cfg.block_m), static_cast<uint32_t>(cfg.block_n), 128, static_cast<uint32_t>(cfg.num_stages),
-                         static_cast<uint32_t>(kernel_d_fp32 ? 4 : 2), static_cast<uint32_t>(cfg.cluster_size), p.b_mn_major ? 1u : 0u};
+    const GemmLayout lay = layout_of(p, cfg);
     // Split-K: the kernel's D is the workspace, num_splits panels of [align(m, 128)][align(n, 4)] FP32
     float* workspace = nullptr;
     const int64_t panel_rows = align_up<int64_t>(p.m, 128), ld_ws = align_up<int64_t>(p.n, 4);
@@ -363,18 +397,19 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
     const uint64_t sfb_rows = sfb_k * p.groups;
 
     CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb, tm_d, tm_d_full;
-    // K-major A, B: K (elements) x rows; box = one 128-element K-block x the tile's rows; 128-byte swizzle.
+    // K-major A, B: K (elements) x rows; box = one K-block (128 or 64 elements) x the tile's rows, swizzled over its width.
+    const CUtensorMapSwizzle k_major_swizzle = cfg.block_k == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
     // MN-major (FP8 only): MN x (groups x K); box = 128 columns of MN x one K-block.
     if (!p.a_mn_major) {
         if ((rc = encode_2d(&tm_a, p.a_fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, a->a,
-                            p.k, a_rows, a->lda, 128, cfg.block_m, CU_TENSOR_MAP_SWIZZLE_128B)) != DG_OK) return rc;
+                            p.k, a_rows, a->lda, cfg.block_k, cfg.block_m, k_major_swizzle)) != DG_OK) return rc;
     } else {
         if ((rc = encode_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->a, p.m, p.k, a->lda, 128, 128,
                             CU_TENSOR_MAP_SWIZZLE_128B)) != DG_OK) return rc;
     }
     if (!p.b_mn_major) {
         if ((rc = encode_2d(&tm_b, p.b_fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, a->b,
-                            p.k, b_rows, a->ldb, 128, cfg.block_n / cfg.cluster_size, CU_TENSOR_MAP_SWIZZLE_128B)) != DG_OK) return rc;
+                            p.k, b_rows, a->ldb, cfg.block_k, cfg.block_n / cfg.cluster_size, k_major_swizzle)) != DG_OK) return rc;
     } else {
         if ((rc = encode_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->b, p.n, static_cast<uint64_t>(p.groups) * p.k, a->ldb, 128, 128,
                             CU_TENSOR_MAP_SWIZZLE_128B)) != DG_OK) return rc;

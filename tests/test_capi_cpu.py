@@ -101,7 +101,7 @@ SHAPES = [(m, n, k) for m in (1, 64, 128, 129, 4096) for (n, k) in
 def test_heuristics_invariants(fp32):
     for m, n, k in SHAPES:
         cfg = dg.get_gemm_config(0, m, n, k, d_is_fp32=fp32)
-        assert cfg["block_m"] in (128, 256) and cfg["block_k"] == 128
+        assert cfg["block_m"] in (128, 256) and cfg["block_k"] in (64, 128)
         assert cfg["block_m"] == 128 or (m > 128 and cfg["num_splits"] == 1 and cfg["cluster_size"] == 1)
         assert cfg["block_n"] % 16 == 0 and 16 <= cfg["block_n"] <= 240
         assert cfg["smem_bytes"] <= 232448, (m, n, k, cfg)

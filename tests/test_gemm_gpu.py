@@ -92,24 +92,46 @@ def test_cta_pair_variant_matches_oracle(m, n, k, bn, b_fp4, monkeypatch):
 
 @pytest.mark.parametrize("m,n,k,bn", [(256, 480, 512, 240), (129, 256, 256, 64), (384, 128, 128, 128), (1000, 1152, 1792, 224),
                                       (4096, 720, 2048, 240)])
-@pytest.mark.parametrize("b_fp4,gran_k_a", [(False, 128), (True, 128), (False, 32)])
+@pytest.mark.parametrize("b_fp4,gran_k_a,block_k", [(False, 128, 128), (True, 128, 128), (False, 32, 128), (False, 128, 64), (False, 32, 64)])
 @pytest.mark.parametrize("cluster", [1, 2])
-def test_256_row_cta_tiles_match_oracle_and_the_128_row_kernel(m, n, k, bn, b_fp4, gran_k_a, cluster, monkeypatch):
+def test_256_row_cta_tiles_match_oracle_and_the_128_row_kernel(m, n, k, bn, b_fp4, gran_k_a, block_k, cluster, monkeypatch):
     """Two 128-row MMAs per K-block on one B stage (also with the second half partly or wholly out of range),
-    by single CTAs and by CTA pairs (512-row tiles)."""
+    by single CTAs and by CTA pairs (512-row tiles), with stages of 128 and of 64 elements of K."""
     monkeypatch.setenv("DG_FORCE_BLOCK_M", "256")
     monkeypatch.setenv("DG_FORCE_BLOCK_N", str(bn))
+    monkeypatch.setenv("DG_FORCE_BLOCK_K", str(block_k))
     monkeypatch.setenv("DG_FORCE_CLUSTER", str(cluster))
     gk = 32 if b_fp4 else 128
     cfg = dg.get_gemm_config(0, m, n, k, b_is_fp4=b_fp4, gran_k_a=gran_k_a, gran_k_b=gk)
-    assert cfg["block_m"] == 256 and cfg["cluster_size"] == cluster
+    assert cfg["block_m"] == 256 and cfg["cluster_size"] == cluster and cfg["block_k"] == block_k
     qa, sfa, qb, sfb, _ = quantise_dense(seeded_bf16((m, k), 5), seeded_bf16((n, k), 6), b_fp4=b_fp4, gran_k_a=gran_k_a)
     d = _run_dense(qa, sfa, qb, sfb, b_fp4=b_fp4, gran_k_a=gran_k_a, gran_k_b=gk).float().cpu().numpy()
     ref = oracle.dequant_gemm_nt(qa, sfa, qb, sfb, gran_k_a, gk, False, b_fp4)
     assert oracle.calc_diff(d, ref) < 1e-5, diff_report(d, ref)
     monkeypatch.setenv("DG_FORCE_BLOCK_M", "128")
+    monkeypatch.setenv("DG_FORCE_BLOCK_K", "128")
     monkeypatch.setenv("DG_FORCE_CLUSTER", "1")
     d1 = _run_dense(qa, sfa, qb, sfb, b_fp4=b_fp4, gran_k_a=gran_k_a, gran_k_b=gk).float().cpu().numpy()
+    assert np.array_equal(d, d1)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (128, 128, 192), (200, 304, 640), (129, 256, 1088), (64, 2112, 1024), (4096, 576, 1792)])
+@pytest.mark.parametrize("block_m", [128, 256])
+def test_64_element_k_stages_match_oracle_and_the_128_element_kernel(m, n, k, block_m, monkeypatch):
+    """Half-size pipeline stages (64-byte swizzle): K tails inside a stage, scale words spanning eight stages,
+    work items shorter than the pipeline."""
+    if block_m == 256 and m <= 128:
+        pytest.skip("256-row tiles need more than 128 rows")
+    monkeypatch.setenv("DG_FORCE_BLOCK_M", str(block_m))
+    monkeypatch.setenv("DG_FORCE_BLOCK_K", "64")
+    monkeypatch.setenv("DG_FORCE_SPLIT_K", "1")
+    assert dg.get_gemm_config(0, m, n, k)["block_k"] == 64
+    qa, sfa, qb, sfb, _ = quantise_dense(seeded_bf16((m, k), 8), seeded_bf16((n, k), 9))
+    d = _run_dense(qa, sfa, qb, sfb).float().cpu().numpy()
+    ref = oracle.dequant_gemm_nt(qa, sfa, qb, sfb)
+    assert oracle.calc_diff(d, ref) < 1e-5, diff_report(d, ref)
+    monkeypatch.setenv("DG_FORCE_BLOCK_K", "128")
+    d1 = _run_dense(qa, sfa, qb, sfb).float().cpu().numpy()
     assert np.array_equal(d, d1)
 
 
@@ -312,11 +334,16 @@ def _grouped_inputs(g, n, k, a, b_fp4=False):
 
 
 @pytest.mark.parametrize("alignment,cluster,block_m", [(128, 1, 128), (256, 1, 128), (256, 2, 128), (128, 1, 256), (256, 1, 256),
-                                                       (512, 2, 256)])
+                                                       (512, 2, 256), (128, 1, -128), (128, 1, -256)])
 @pytest.mark.parametrize("b_fp4", [False, True])
 def test_m_grouped_contiguous(alignment, cluster, block_m, b_fp4, monkeypatch):
     """With 128-row alignment and 256-row tiles, some tiles hold the end of one expert and the start of the next."""
     g, n, k = 5, 1024, 1024
+    if block_m < 0:                                                 # negative: stages of 64 elements of K (FP8 only)
+        if b_fp4:
+            pytest.skip("64-element stages are built for FP8 operands")
+        monkeypatch.setenv("DG_FORCE_BLOCK_K", "64")
+        block_m = -block_m
     monkeypatch.setenv("DG_FORCE_CLUSTER", str(cluster))
     monkeypatch.setenv("DG_FORCE_BLOCK_M", str(block_m))
     dg.set_mk_alignment_for_contiguous_layout(alignment)
@@ -382,8 +409,12 @@ def _masked_case(counts, max_m, n, k):
 SENTINEL = -7.0
 
 
-@pytest.mark.parametrize("cluster,block_m,max_m", [(1, 128, 256), (2, 128, 256), (1, 256, 256), (1, 256, 384), (2, 256, 384), (2, 256, 640)])
+@pytest.mark.parametrize("cluster,block_m,max_m", [(1, 128, 256), (2, 128, 256), (1, 256, 256), (1, 256, 384), (2, 256, 384), (2, 256, 640),
+                                                   (1, -128, 256), (1, -256, 384)])
 def test_m_grouped_masked_leaves_rows_beyond_masked_m_untouched(cluster, block_m, max_m, monkeypatch):
+    if block_m < 0:                                                 # negative: stages of 64 elements of K
+        monkeypatch.setenv("DG_FORCE_BLOCK_K", "64")
+        block_m = -block_m
     monkeypatch.setenv("DG_FORCE_CLUSTER", str(cluster))
     monkeypatch.setenv("DG_FORCE_BLOCK_M", str(block_m))
     counts, n, k = (45, 83, 0, max_m, 129, min(300, max_m)), 1000 // 8 * 8, 1024
