@@ -33,8 +33,8 @@ NOMINAL_FP8_TFLOPS = 4500.0
 CPU_SAMPLE_NK = (2112, 7168)          # the bounded sample the CPU arm times (1 of the 6 shapes)
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of dg_gemm_fp8_fp4 at M = 4096, from one ncu capture of this
 # script (profiles/dg_gemm_fp8_fp4_dense_m4096.md); D written late in a launch may still sit in L2 when it ends.
-NCU_DRAM_BYTES = {(2112, 7168): 46445824, (24576, 1536): 228799232, (32768, 512): 247536128,
-                  (7168, 16384): 480479232, (4096, 7168): 73676288, (7168, 2048): 31463680}
+NCU_DRAM_BYTES = {(2112, 7168): 46332928, (24576, 1536): 231155456, (32768, 512): 247204352,
+                  (7168, 16384): 461400576, (4096, 7168): 62027264, (7168, 2048): 31307264}
 
 
 def flops_of(m, n, k):
