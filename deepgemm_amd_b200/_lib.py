@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(PKG_DIR, "lib", "libdeepgemm_b200.so")
 DG_OK = 0
 DG_FP8_E4M3, DG_FP4_E2M1_X2, DG_BF16, DG_FP32 = 0, 1, 2, 3
 DG_MAJOR_K, DG_MAJOR_MN = 0, 1
-DG_GEMM_DENSE, DG_GEMM_M_GROUPED_CONTIGUOUS, DG_GEMM_M_GROUPED_MASKED = 0, 1, 2
+DG_GEMM_DENSE, DG_GEMM_M_GROUPED_CONTIGUOUS, DG_GEMM_M_GROUPED_MASKED, DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM = 0, 1, 2, 3
 
 
 class GemmArgs(C.Structure):
@@ -28,6 +28,7 @@ class GemmArgs(C.Structure):
         ("gran_k_a", C.c_int32), ("gran_k_b", C.c_int32),
         ("accumulate", C.c_int32), ("has_alpha", C.c_int32), ("alpha", C.c_float),
         ("grouped_layout", C.c_void_p), ("expected_m", C.c_int32), ("stream", C.c_void_p),
+        ("use_psum_layout", C.c_int32), ("ensure_zero_padding", C.c_int32),
     ]
 
 
@@ -57,6 +58,8 @@ SIGNATURES = {
     "dg_get_tma_aligned_size": (C.c_int, [C.c_int, C.c_int]),
     "dg_pack_fp32_into_ue8m0": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
                                           C.c_int64, C.c_int64, C.c_int64, C.c_void_p]),
+    "dg_pack_fp32_into_ue8m0_psum": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int64, C.c_int64,
+                                               C.c_void_p, C.c_int, C.c_void_p]),
     "dg_transpose_fp32_mn_major": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                              C.c_int64, C.c_int64, C.c_int64, C.c_void_p]),
     "dg_per_token_cast": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int, C.c_int,

@@ -138,22 +138,30 @@ def get_mn_major_tma_aligned_tensor(sf: torch.Tensor) -> torch.Tensor:
     return out.squeeze(0) if dim == 2 else out
 
 
-def _pack(sf: torch.Tensor, mn: int, gran_mn: int) -> torch.Tensor:
+def _pack(sf: torch.Tensor, mn: int, gran_mn: int, psum_layout: Optional[torch.Tensor] = None) -> torch.Tensor:
     dim, b = _preprocess_sf(sf)
     g, _, sf_k = b.shape
     amn, packed_k = get_tma_aligned_size(mn, 4), ceil_div(sf_k, 4)
     out = torch.empty_strided((g, mn, packed_k), (packed_k * amn, 1, amn), dtype=torch.int, device=sf.device)
-    check(lib.dg_pack_fp32_into_ue8m0(b.data_ptr(), out.data_ptr(), g, mn, sf_k, gran_mn,
-                                      b.stride(0), b.stride(1), b.stride(2), _stream()))
+    if psum_layout is not None:
+        # Rows between groups may hold uninitialised scales: they are not read and get the code 0
+        # (csrc/jit_kernels/impls/smxx_layout.hpp:141-149)
+        _require(g == 1 and gran_mn == 1, "num_sf_batches == 1 and batched_sf.is_contiguous()")
+        _require(psum_layout.dtype == torch.int and psum_layout.is_contiguous() and psum_layout.is_cuda,
+                 "psum_layout->scalar_type() == torch::kInt and psum_layout->is_contiguous()")
+        _require(psum_layout.numel() > 0, "psum_layout->numel() > 0")
+        check(lib.dg_pack_fp32_into_ue8m0_psum(b.data_ptr(), out.data_ptr(), mn, sf_k, b.stride(1), b.stride(2),
+                                               psum_layout.data_ptr(), psum_layout.numel(), _stream()))
+    else:
+        check(lib.dg_pack_fp32_into_ue8m0(b.data_ptr(), out.data_ptr(), g, mn, sf_k, gran_mn,
+                                          b.stride(0), b.stride(1), b.stride(2), _stream()))
     return out.squeeze(0) if dim == 2 else out
 
 
 def get_mn_major_tma_aligned_packed_ue8m0_tensor(sf: torch.Tensor, psum_layout: Optional[torch.Tensor] = None) -> torch.Tensor:
     """FP32 power-of-two scales [G?, mn, sf_k] -> packed UE8M0 int32 [G?, mn, ceil(sf_k/4)] with strides
     (ceil(sf_k/4) * align(mn,4), 1, align(mn,4)) (csrc/jit_kernels/impls/smxx_layout.hpp:133-216)."""
-    if psum_layout is not None:
-        raise RuntimeError("psum layout is not built (deepgemm_amd_b200): pass the per-row grouped layout instead")
-    return _pack(sf, sf.size(-2), 1)
+    return _pack(sf, sf.size(-2), 1, psum_layout)
 
 
 def _check_sf_layout(sf, mn, k, gran_mn, gran_k, num_groups, tma_stride_check=False, type_check=None):
@@ -194,10 +202,8 @@ def transform_sf_into_required_layout(sf: torch.Tensor, mn: int, k: int, recipe:
     _check_sf_layout(sf, mn, k, gran_mn, gran_k, num_groups)
     if disable_ue8m0_cast:
         raise RuntimeError("disable_ue8m0_cast selects the FP32-scale (SM90) kernels, which this sm_100-only library does not build")
-    if psum_layout is not None:
-        raise RuntimeError("psum layout is not built (deepgemm_amd_b200)")
     if sf.dtype == torch.float and gran_k in (32, 128):
-        return _pack(sf, mn, gran_mn)
+        return _pack(sf, mn, gran_mn, psum_layout)
     if sf.dtype == torch.int and gran_mn == 1 and gran_k in (32, 128):
         return _check_sf_layout(sf, mn, k, gran_mn, gran_k, num_groups, tma_stride_check=True, type_check=torch.int)
     raise RuntimeError("Unknown SF transformation")
@@ -209,17 +215,18 @@ def _default_recipe(sfa_dtype, sfb_dtype) -> Recipe3:
     return (1, 128, 128) if sfb_dtype == torch.float else (1, 1, 128)
 
 
-def _transform_sf_pair(sfa, sfb, m, n, k, recipe, recipe_a, recipe_b, num_groups_a, num_groups_b, disable_ue8m0_cast):
+def _transform_sf_pair(sfa, sfb, m, n, k, recipe, recipe_a, recipe_b, num_groups_a, num_groups_b, disable_ue8m0_cast,
+                       psum_sfa_layout=None):
     """csrc/apis/layout.hpp:60-87."""
     if recipe_a is None and recipe is None:
         recipe = _default_recipe(sfa.dtype, sfb.dtype)
     _require((recipe_a is None) == (recipe_b is None), "recipe_a.has_value() == recipe_b.has_value()")
     _require((recipe_a is None) != (recipe is None), "recipe_a.has_value() != recipe.has_value()")
     if recipe is not None:
-        tsfa = transform_sf_into_required_layout(sfa, m, k, recipe, num_groups_a, True, disable_ue8m0_cast)
+        tsfa = transform_sf_into_required_layout(sfa, m, k, recipe, num_groups_a, True, disable_ue8m0_cast, psum_sfa_layout)
         tsfb = transform_sf_into_required_layout(sfb, n, k, recipe, num_groups_b, False, disable_ue8m0_cast)
         return tsfa, tsfb, recipe[2], recipe[2]
-    tsfa = transform_sf_into_required_layout(sfa, m, k, recipe_a, num_groups_a, None, disable_ue8m0_cast)
+    tsfa = transform_sf_into_required_layout(sfa, m, k, recipe_a, num_groups_a, None, disable_ue8m0_cast, psum_sfa_layout)
     tsfb = transform_sf_into_required_layout(sfb, n, k, recipe_b, num_groups_b, None, disable_ue8m0_cast)
     return tsfa, tsfb, recipe_a[1], recipe_b[1]
 
@@ -299,7 +306,8 @@ def _ld(t: torch.Tensor, major: int) -> int:
 
 
 def _fill_args(a, sfa, b, sfb, d, m, n, k, groups, major_a, major_b, gran_k_a, gran_k_b,
-               accumulate=False, alpha=None, layout=None, expected_m=0) -> GemmArgs:
+               accumulate=False, alpha=None, layout=None, expected_m=0, use_psum_layout=False,
+               ensure_zero_padding=False) -> GemmArgs:
     args = GemmArgs()
     args.a, args.sfa, args.b, args.sfb, args.d = a.data_ptr(), sfa.data_ptr(), b.data_ptr(), sfb.data_ptr(), d.data_ptr()
     args.m, args.n, args.k, args.num_groups = m, n, k, groups
@@ -314,6 +322,7 @@ def _fill_args(a, sfa, b, sfb, d, m, n, k, groups, major_a, major_b, gran_k_a, g
     args.grouped_layout = layout.data_ptr() if layout is not None else None
     args.expected_m = int(expected_m)
     args.stream = _stream()
+    args.use_psum_layout, args.ensure_zero_padding = int(use_psum_layout), int(ensure_zero_padding)
     return args
 
 
@@ -395,8 +404,10 @@ def m_grouped_fp8_fp4_gemm_nt_contiguous(a, b, d, grouped_layout, recipe=None, r
                                          compiled_dims: str = "nk", disable_ue8m0_cast: bool = False,
                                          use_psum_layout: bool = False, ensure_zero_padding: bool = True,
                                          expected_m_for_psum_layout: Optional[int] = None, epilogue=None) -> None:
-    """D[M_total,N] = A[M_total,K] @ B[g(row),N,K]^T, expert id per row in grouped_layout (-1 on padding rows)
-    (csrc/apis/gemm.hpp:181-250)."""
+    """D[M_total,N] = A[M_total,K] @ B[g(row),N,K]^T (csrc/apis/gemm.hpp:181-250).  grouped_layout is the expert id
+    per row (-1 on padding rows) or, with use_psum_layout, the row where each group ends: group g then occupies rows
+    [align(grouped_layout[g-1], mk_alignment), grouped_layout[g]).  With ensure_zero_padding the padding rows of D up to
+    the next aligned row are written too (zero for zero A padding); otherwise rows outside the groups are untouched."""
     (a_data, a_sf), (b_data, b_sf) = a, b
     major_a, major_b = _major_ab(a_data), _major_ab(b_data)
     _require(major_a == _lib.DG_MAJOR_K, "major_a == cute::UMMA::Major::K")
@@ -411,17 +422,19 @@ def m_grouped_fp8_fp4_gemm_nt_contiguous(a, b, d, grouped_layout, recipe=None, r
     _require(d.dtype == torch.bfloat16, "d.scalar_type() == torch::kBFloat16")
     _require(grouped_layout.dtype == torch.int, "grouped_layout.scalar_type() == torch::kInt")
     if use_psum_layout:
-        raise RuntimeError("use_psum_layout is not built (deepgemm_amd_b200): pass the per-row grouped layout")
-    _require(grouped_layout.dim() == 1 and grouped_layout.size(0) == m, "m == m__")
-    _require(expected_m_for_psum_layout is None, "not expected_m_for_psum_layout.has_value()")
+        _require(grouped_layout.dim() == 1 and grouped_layout.size(0) == num_groups, "num_groups == num_groups_")
+    else:
+        _require(grouped_layout.dim() == 1 and grouped_layout.size(0) == m, "m == m__")
+        _require(expected_m_for_psum_layout is None, "not expected_m_for_psum_layout.has_value()")
     _check_cd(d)
     if m == 0:
         return
     sfa, sfb, gran_k_a, gran_k_b = _transform_sf_pair(a_sf, b_sf, m, n, k, recipe, recipe_a, recipe_b, None, num_groups,
-                                                      disable_ue8m0_cast)
+                                                      disable_ue8m0_cast, grouped_layout if use_psum_layout else None)
     _require(_resolve_alpha(None, epilogue) is None, "grouped GEMMs take the Identity epilogue only")
     args = _fill_args(a_data, sfa, b_data, sfb, d, m, n, k, num_groups, major_a, major_b, gran_k_a, gran_k_b,
-                      layout=grouped_layout)
+                      layout=grouped_layout, expected_m=expected_m_for_psum_layout or 0, use_psum_layout=use_psum_layout,
+                      ensure_zero_padding=use_psum_layout and ensure_zero_padding)
     check(lib.dg_m_grouped_fp8_fp4_gemm_contiguous(C.byref(args)))
 
 

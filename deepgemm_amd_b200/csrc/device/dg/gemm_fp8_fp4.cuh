@@ -18,7 +18,8 @@
 //   warps 8-11  a second epilogue warpgroup, only with 256-row tiles (DG_M_HALVES == 2)
 //
 // The configuration arrives as DG_* macros set by the host-side code generator:
-//   DG_GEMM_TYPE (0 dense, 1 m-grouped contiguous, 2 m-grouped masked), DG_M_HALVES, DG_BLOCK_N, DG_NUM_STAGES,
+//   DG_GEMM_TYPE (0 dense, 1 m-grouped contiguous, 2 m-grouped masked, 3 m-grouped contiguous with a prefix-sum
+//   layout; DG_WRITE_PADDING for the latter), DG_M_HALVES, DG_BLOCK_N, DG_NUM_STAGES,
 //   DG_CLUSTER, DG_A_FP4, DG_B_FP4, DG_MAJOR_A, DG_MAJOR_B (0 K-major, 1 MN-major), DG_GRAN_K_A, DG_GRAN_K_B,
 //   DG_D_FP32, DG_ACCUMULATE, DG_RASTER_GROUP, DG_SPLIT_K.
 //
@@ -163,6 +164,7 @@ struct GemmParams {
     uint32_t num_splits;         // slices of K per output tile (1 = no split)
     uint32_t kb_per_split;       // K-blocks per slice, a multiple of 4 so every slice starts on a packed scale word
     uint32_t split_panel_rows;   // split-K: rows between consecutive slices' panels in the workspace D points to
+    uint32_t group_alignment;    // prefix-sum layout: every group starts on a multiple of this many rows
 };
 
 // Wait-time accounting for tuning: with DG_PROFILE defined every role adds the cycles it spent inside each
@@ -275,6 +277,10 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
     // A cluster walks the tile list as one unit
     TileScheduler<kGemmType> sched(TILE_M, BLOCK_N, kRasterGroup, p.shape_m, p.shape_n, p.num_groups, p.grouped_layout,
                                    blockIdx.x / kCluster, gridDim.x / kCluster, kSplitK ? p.num_splits : 1u);
+    if constexpr (kGemmType == kMGroupedPsum) {
+        sched.group_alignment = p.group_alignment;
+        sched.write_padding = DG_WRITE_PADDING;
+    }
     // K-blocks [kb_begin, kb_end) of a work item: all of K unless the GEMM is split
     auto kb_begin = [&](const Tile& t) { return kSplitK ? t.split * p.kb_per_split : 0u; };
     auto kb_end = [&](const Tile& t) {
@@ -561,11 +567,12 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
             const uint32_t d_row0 = tile.d_row_base + tile.m_block * TILE_M + cta_rank * CTA_M + wg * BLOCK_M +
                                     (kSplitK ? tile.split * p.split_panel_rows : 0u);
             const uint32_t tmem_row_addr = tmem_base + ((quarter * 32) << 16) + accum * UMMA_N;
-            // Rows of this 128-row part that may be written (fewer than 128 only in a ragged tile of the masked layout)
+            // Rows of this 128-row part that may be written
             const uint32_t rows_before = cta_rank * CTA_M + wg * BLOCK_M;
             const uint32_t valid_rows = tile.valid_rows <= rows_before ? 0u :
                                         (tile.valid_rows - rows_before < BLOCK_M ? tile.valid_rows - rows_before : BLOCK_M);
-            const bool direct = kGemmType == 2 && valid_rows < BLOCK_M;
+            // (fewer than 128 only in a ragged tile of the masked and prefix-sum layouts: those rows are stored one by one)
+            const bool direct = (kGemmType == kMGroupedMasked || kGemmType == kMGroupedPsum) && valid_rows < BLOCK_M;
             auto release_tmem = [&]() {
                 tc_fence_before_sync();
                 if (kCluster == 1 || is_leader) mbar_arrive(tmem_empty_bar(accum));

@@ -10,6 +10,10 @@
 //   m-grouped masked : groups in order; group g contributes ceil(masked_m[g] / 128) row blocks,
 //       read on the device (no host synchronisation, so a captured graph follows new counts);
 //       same contract as scheduler/gemm.cuh:188-204.
+//   m-grouped contiguous with a prefix-sum layout : layout[g] is the row where group g ends; group g
+//       starts at layout[g - 1] rounded up to the contiguous-layout alignment (row 0 for g = 0), so
+//       the rows in between are padding.  Walked on the device like the masked layout; same
+//       contract as scheduler/gemm.cuh:205-225.
 #pragma once
 
 #include <cstdint>
@@ -22,7 +26,7 @@
 
 namespace dg {
 
-enum GemmKind : uint32_t { kDense = 0, kMGroupedContiguous = 1, kMGroupedMasked = 2 };
+enum GemmKind : uint32_t { kDense = 0, kMGroupedContiguous = 1, kMGroupedMasked = 2, kMGroupedPsum = 3 };
 
 struct Tile {
     uint32_t m_block;       // row block inside the group (masked) or inside A (dense / contiguous)
@@ -48,8 +52,11 @@ struct TileScheduler {
     const int* layout;
     uint32_t cta, num_ctas, iter;
     uint32_t num_splits;    // dense only: every output tile is computed as num_splits work items over slices of K
-    // masked layout only
+    // masked and prefix-sum layouts only
     uint32_t cur_group, group_first_tile;
+    // prefix-sum layout only: first row of the current group, the alignment of group starts, and whether the
+    // padding rows up to the next aligned row count as writable (they are written as the product of zero rows)
+    uint32_t group_start, group_alignment, write_padding;
 
     DG_HD TileScheduler(uint32_t block_m_, uint32_t block_n_, uint32_t raster_group_,
                         uint32_t shape_m_, uint32_t shape_n_, uint32_t num_groups_, const int* layout_,
@@ -57,7 +64,7 @@ struct TileScheduler {
         : kBlockM(block_m_), kRasterGroup(raster_group_), shape_m(shape_m_), num_groups(num_groups_),
           num_m_blocks((shape_m_ + block_m_ - 1) / block_m_), num_n_blocks((shape_n_ + block_n_ - 1) / block_n_),
           layout(layout_), cta(cta_), num_ctas(num_ctas_), iter(0), num_splits(num_splits_ == 0 ? 1 : num_splits_),
-          cur_group(0), group_first_tile(0) {}
+          cur_group(0), group_first_tile(0), group_start(0), group_alignment(128), write_padding(0) {}
 
     // Linear index inside an (mb x num_n_blocks) grid -> (m, n)
     DG_HD void rasterise(uint32_t idx, uint32_t mb, uint32_t& m, uint32_t& n) const {
@@ -90,6 +97,30 @@ struct TileScheduler {
             t.sfa_mn_base = 0;
             t.sfa_group = cur_group;
             const uint32_t left = rows - t.m_block * kBlockM;
+            t.valid_rows = left < kBlockM ? left : kBlockM;
+            t.split = 0;
+            t.mn_index = tile_id;
+            return true;
+        } else if constexpr (kKind == kMGroupedPsum) {
+            uint32_t mb = 0, rows = 0;
+            while (true) {
+                if (cur_group >= num_groups) return false;
+                const int e = layout[cur_group];
+                uint32_t end = e < 0 ? 0u : (static_cast<uint32_t>(e) > shape_m ? shape_m : static_cast<uint32_t>(e));
+                if (end < group_start) end = group_start;
+                rows = end - group_start;
+                mb = (rows + kBlockM - 1) / kBlockM;
+                if (tile_id < group_first_tile + mb * num_n_blocks) break;
+                group_first_tile += mb * num_n_blocks;
+                group_start = (end + group_alignment - 1) / group_alignment * group_alignment;
+                ++cur_group;
+            }
+            rasterise(tile_id - group_first_tile, mb, t.m_block, t.n_block);
+            t.group = t.group1 = cur_group;
+            t.a_row_base = t.d_row_base = t.sfa_mn_base = group_start;
+            t.sfa_group = 0;
+            const uint32_t writable = write_padding ? (rows + group_alignment - 1) / group_alignment * group_alignment : rows;
+            const uint32_t left = writable - t.m_block * kBlockM;
             t.valid_rows = left < kBlockM ? left : kBlockM;
             t.split = 0;
             t.mn_index = tile_id;

@@ -28,6 +28,7 @@ struct GemmParams {
     float alpha;
     unsigned long long* profile;
     uint32_t num_splits, kb_per_split, split_panel_rows;
+    uint32_t group_alignment;
 };
 
 // Split-K scratch: num_splits stacked FP32 [rows x N] panels.  One buffer per device, shared by every stream (a
@@ -65,11 +66,13 @@ struct Problem {
     bool a_fp4, b_fp4, d_fp32, accumulate, a_mn_major, b_mn_major;
     int gran_k_a, gran_k_b;
     int expected_m;
+    bool write_padding;      // prefix-sum layout: also write the padding rows of D up to the next aligned row
 };
 
 int validate(int kind, const dg_gemm_args_t* a, bool need_pointers, Problem* p) {
     DG_REQUIRE(a != nullptr);
-    DG_REQUIRE(kind == DG_GEMM_DENSE || kind == DG_GEMM_M_GROUPED_CONTIGUOUS || kind == DG_GEMM_M_GROUPED_MASKED);
+    DG_REQUIRE(kind == DG_GEMM_DENSE || kind == DG_GEMM_M_GROUPED_CONTIGUOUS || kind == DG_GEMM_M_GROUPED_MASKED ||
+               kind == DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM);
     DG_REQUIRE(a->a_dtype == DG_FP8_E4M3 || a->a_dtype == DG_FP4_E2M1_X2);
     DG_REQUIRE(a->b_dtype == DG_FP8_E4M3 || a->b_dtype == DG_FP4_E2M1_X2);
     DG_REQUIRE(a->d_dtype == DG_BF16 || a->d_dtype == DG_FP32);
@@ -106,6 +109,7 @@ int validate(int kind, const dg_gemm_args_t* a, bool need_pointers, Problem* p) 
     p->accumulate = a->accumulate != 0;
     p->gran_k_a = a->gran_k_a; p->gran_k_b = a->gran_k_b;
     p->expected_m = a->expected_m;
+    p->write_padding = kind == DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM && a->ensure_zero_padding != 0;
     if (a->m == 0 || a->n == 0 || a->k == 0) return DG_OK;                    // handled by the caller (gemm.hpp:17-53)
 
     if (p->a_fp4 || p->b_fp4) DG_REQUIRE(a->k % 128 == 0);                   // runtime_utils.hpp:133-135
@@ -131,6 +135,11 @@ int validate(int kind, const dg_gemm_args_t* a, bool need_pointers, Problem* p) 
         // Every expert segment is padded to the alignment, which the row blocks must divide
         DG_REQUIRE(state().mk_alignment % 128 == 0);
         DG_REQUIRE(a->m % 128 == 0);
+    }
+    if (kind == DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM) {
+        DG_REQUIRE(state().mk_alignment % 128 == 0);
+        DG_REQUIRE(a->major_b == DG_MAJOR_K);
+        DG_REQUIRE(a->expected_m >= 0);
     }
     return DG_OK;
 }
@@ -183,7 +192,7 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
         if (forced_cluster ? cluster != forced_cluster : !cluster_allowed(p, cluster)) continue;
         // A CTA pair multiplies all its rows with one B: in the contiguous layout every expert segment must then be a
         // whole number of pair tiles
-        if (cluster == 2 && (num_sms % 2 != 0 ||
+        if (cluster == 2 && (num_sms % 2 != 0 || p.kind == DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM ||
                              (p.kind == DG_GEMM_M_GROUPED_CONTIGUOUS && state().mk_alignment % (256 * halves) != 0))) continue;
         // 256 rows per CTA: two 128-row MMAs per K-block on one B stage; K not sliced
         if (forced_block_m ? 128 * halves != forced_block_m : (halves == 2 && p.m <= 128)) continue;
@@ -197,6 +206,10 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
         int64_t m_blocks;
         if (p.kind == DG_GEMM_M_GROUPED_MASKED)
             m_blocks = static_cast<int64_t>(p.groups) * ceil_div(std::min(std::max(p.expected_m, 1), p.m), tile_m);
+        else if (p.kind == DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM && p.expected_m > 0)
+            m_blocks = static_cast<int64_t>(p.groups) * ceil_div(std::min(p.expected_m, p.m), tile_m);
+        else if (p.kind == DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM)   // every group may end with a partly filled tile
+            m_blocks = ceil_div(p.m, tile_m) + p.groups / 2;
         else
             m_blocks = ceil_div(p.m, tile_m);
         // Slicing K: dense GEMMs whose output has too few tiles to occupy the GPU.  What matters is the bytes a CTA has
@@ -275,7 +288,7 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
     cfg->cluster_size = best.cluster;
     const int forced_raster = env_int("FORCE_RASTER_GROUP");
     cfg->raster_group = forced_raster > 0 ? forced_raster : std::max(4, 16 / (best.cluster * best.halves));
-    cfg->num_ctas = best.cluster * (p.kind == DG_GEMM_M_GROUPED_MASKED
+    cfg->num_ctas = best.cluster * (p.kind == DG_GEMM_M_GROUPED_MASKED || p.kind == DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM
                                         ? units : static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(units, best.tiles))));
     cfg->smem_bytes = static_cast<int>(best.lay.total_bytes());
     cfg->tmem_cols = static_cast<int>(best.lay.tmem_cols_alloc());
@@ -316,6 +329,7 @@ std::string generate_source(const Problem& p, const dg_gemm_config_t& cfg) {
       << "#define DG_ACCUMULATE " << (p.accumulate ? 1 : 0) << "\n"
       << "#define DG_RASTER_GROUP " << cfg.raster_group << "\n"
       << "#define DG_SPLIT_K " << (cfg.num_splits > 1 ? 1 : 0) << "\n"
+      << "#define DG_WRITE_PADDING " << (p.write_padding ? 1 : 0) << "\n"
       << "#define DG_PROFILE " << env_int("PROFILE") << "\n"
       << "#include <dg/gemm_fp8_fp4.cuh>\n";
     return s.str();
@@ -344,7 +358,8 @@ int encode_2d(CUtensorMap* map, CUtensorMapDataType dtype, const void* base, uin
 }
 
 int get_kernel(const Problem& p, const dg_gemm_config_t& cfg, dg_kernel_t* kernel) {
-    static const char* names[3] = {"gemm_fp8_fp4_dense", "gemm_fp8_fp4_m_grouped_contiguous", "gemm_fp8_fp4_m_grouped_masked"};
+    static const char* names[4] = {"gemm_fp8_fp4_dense", "gemm_fp8_fp4_m_grouped_contiguous", "gemm_fp8_fp4_m_grouped_masked",
+                                   "gemm_fp8_fp4_m_grouped_contiguous_psum"};
     const std::string src = generate_source(p, cfg);
     return dg_jit_compile(names[p.kind], "dg_gemm_fp8_fp4", src.c_str(), "", kernel);
 }
@@ -445,6 +460,7 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
     params.num_splits = cfg.num_splits;
     params.kb_per_split = cfg.kb_per_split;
     params.split_panel_rows = static_cast<uint32_t>(panel_rows);
+    params.group_alignment = static_cast<uint32_t>(state().mk_alignment);
     void* kargs[7] = {&tm_a, &tm_b, &tm_sfa, &tm_sfb, &tm_d, &tm_d_full, &params};
     if (env_int("PROFILE")) {
         // synchronous, printing path for tuning only
@@ -492,7 +508,10 @@ using namespace dg;
 extern "C" {
 
 int dg_fp8_fp4_gemm(const dg_gemm_args_t* args) { return run_gemm(DG_GEMM_DENSE, args); }
-int dg_m_grouped_fp8_fp4_gemm_contiguous(const dg_gemm_args_t* args) { return run_gemm(DG_GEMM_M_GROUPED_CONTIGUOUS, args); }
+int dg_m_grouped_fp8_fp4_gemm_contiguous(const dg_gemm_args_t* args) {
+    const bool psum = args != nullptr && args->use_psum_layout != 0;
+    return run_gemm(psum ? DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM : DG_GEMM_M_GROUPED_CONTIGUOUS, args);
+}
 int dg_m_grouped_fp8_fp4_gemm_masked(const dg_gemm_args_t* args) { return run_gemm(DG_GEMM_M_GROUPED_MASKED, args); }
 
 int dg_get_gemm_config(int kind, const dg_gemm_args_t* args, dg_gemm_config_t* config) {
@@ -536,6 +555,13 @@ int dg_enumerate_tiles(int kind, int block_n, int raster_group, int shape_m, int
         case DG_GEMM_DENSE: walk(TileScheduler<kDense>(128, bn, rg, sm, sn, ng, layout_host, c, nc)); break;
         case DG_GEMM_M_GROUPED_CONTIGUOUS: walk(TileScheduler<kMGroupedContiguous>(128, bn, rg, sm, sn, ng, layout_host, c, nc)); break;
         case DG_GEMM_M_GROUPED_MASKED: walk(TileScheduler<kMGroupedMasked>(128, bn, rg, sm, sn, ng, layout_host, c, nc)); break;
+        case DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM: {
+            // m_block is reported as the absolute 128-row block of A (groups start on multiples of the alignment)
+            TileScheduler<kMGroupedPsum> sched(128, bn, rg, sm, sn, ng, layout_host, c, nc);
+            sched.group_alignment = static_cast<uint32_t>(state().mk_alignment);
+            while (sched.next(t)) { t.m_block += t.a_row_base / 128; emit(); }
+            break;
+        }
         default: fail(DG_ERR_INVALID_ARGUMENT, "unknown GEMM kind"); return -DG_ERR_INVALID_ARGUMENT;
     }
     return count;

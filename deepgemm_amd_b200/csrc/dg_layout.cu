@@ -15,11 +15,26 @@ namespace {
 constexpr int kTileMN = 32;
 constexpr int kTileK = 32;      // packed words along K per tile (128 scales)
 
-// Input element (g, row, k) sits at g * sg + (row / gran_mn) * sm + k * sk.
+// Prefix-sum layout of the m-grouped contiguous GEMM: group g holds rows [align(ends[g-1], alignment), ends[g]);
+// every other row is padding whose input scale may be uninitialised.
+__device__ __forceinline__ bool row_in_a_group(int row, const int* __restrict__ ends, int num_groups, int alignment) {
+    int start = 0;
+    for (int g = 0; g < num_groups; ++g) {
+        const int end = ends[g];
+        if (row < end) return row >= start;
+        start = (max(end, start) + alignment - 1) / alignment * alignment;
+    }
+    return false;
+}
+
+// Input element (g, row, k) sits at g * sg + (row / gran_mn) * sm + k * sk.  With `psum_ends` (the prefix-sum layout,
+// num_psum_groups entries) rows outside every group are not read and get the scale code 0, a finite value
+// (docs/scaling-factor-format.md 7.3 of the reference).
 __global__ void __launch_bounds__(256)
 pack_fp32_into_ue8m0_kernel(const float* __restrict__ sf, int32_t* __restrict__ out,
                             int mn, int sf_k, int packed_k, int aligned_mn, int gran_mn,
-                            int64_t sg, int64_t sm, int64_t sk, int* status) {
+                            int64_t sg, int64_t sm, int64_t sk, int* status,
+                            const int* __restrict__ psum_ends, int num_psum_groups, int psum_alignment) {
     __shared__ uint32_t tile[kTileK][kTileMN + 1];
     const int g = blockIdx.z;
     const int mn0 = blockIdx.x * kTileMN, pk0 = blockIdx.y * kTileK;
@@ -30,7 +45,8 @@ pack_fp32_into_ue8m0_kernel(const float* __restrict__ sf, int32_t* __restrict__ 
     for (int i = 0; i < kTileMN / 8; ++i) {
         const int r = mn0 + ty + 8 * i, pk = pk0 + tx;
         uint32_t word = 0;
-        if (r < mn && pk < packed_k) {
+        const bool gap = psum_ends != nullptr && r < mn && !row_in_a_group(r, psum_ends, num_psum_groups, psum_alignment);
+        if (r < mn && pk < packed_k && !gap) {
             const float* row = src + static_cast<int64_t>(r / gran_mn) * sm;
             #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -97,7 +113,25 @@ int dg_pack_fp32_into_ue8m0(const float* sf, int32_t* out, int num_groups, int m
     const dim3 grid(ceil_div(aligned_mn, kTileMN), ceil_div(packed_k, kTileK), num_groups);
     DG_REQUIRE(grid.y <= 65535);
     pack_fp32_into_ue8m0_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        sf, out, mn, sf_k, packed_k, aligned_mn, gran_mn, in_stride_group, in_stride_mn, in_stride_k, state().status_device);
+        sf, out, mn, sf_k, packed_k, aligned_mn, gran_mn, in_stride_group, in_stride_mn, in_stride_k, state().status_device,
+        nullptr, 0, 1);
+    DG_CUDA_RT(cudaGetLastError());
+    return DG_OK;
+}
+
+int dg_pack_fp32_into_ue8m0_psum(const float* sf, int32_t* out, int mn, int sf_k, int64_t in_stride_mn, int64_t in_stride_k,
+                                 const int32_t* psum_layout, int num_psum_groups, void* stream) {
+    DG_REQUIRE(mn >= 0 && sf_k >= 0 && num_psum_groups > 0);
+    if (mn == 0 || sf_k == 0) return DG_OK;
+    DG_REQUIRE(sf != nullptr && out != nullptr && psum_layout != nullptr);
+    int rc = ensure_status_word();
+    if (rc != DG_OK) return rc;
+    const int packed_k = ceil_div(sf_k, 4), aligned_mn = align_up(mn, 4);
+    const dim3 grid(ceil_div(aligned_mn, kTileMN), ceil_div(packed_k, kTileK), 1);
+    DG_REQUIRE(grid.y <= 65535);
+    pack_fp32_into_ue8m0_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        sf, out, mn, sf_k, packed_k, aligned_mn, 1, 0, in_stride_mn, in_stride_k, state().status_device,
+        psum_layout, num_psum_groups, state().mk_alignment);
     DG_CUDA_RT(cudaGetLastError());
     return DG_OK;
 }

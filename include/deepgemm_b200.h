@@ -45,7 +45,8 @@ typedef enum dg_major { DG_MAJOR_K = 0, DG_MAJOR_MN = 1 } dg_major_t;
 typedef enum dg_gemm_kind {
     DG_GEMM_DENSE = 0,
     DG_GEMM_M_GROUPED_CONTIGUOUS = 1,
-    DG_GEMM_M_GROUPED_MASKED = 2
+    DG_GEMM_M_GROUPED_MASKED = 2,
+    DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM = 3     /* the contiguous layout with use_psum_layout (for dg_get_gemm_config / dg_gemm_precompile) */
 } dg_gemm_kind_t;
 
 DG_API const char* dg_last_error(void);
@@ -83,6 +84,14 @@ DG_API int dg_pack_fp32_into_ue8m0(const float* sf_device, int32_t* out_device,
                             int num_groups, int mn, int sf_k, int gran_mn,
                             int64_t in_stride_group, int64_t in_stride_mn, int64_t in_stride_k,
                             void* stream);
+
+/* The same packing for SFA of an m-grouped contiguous GEMM with a prefix-sum layout
+ * (get_mn_major_tma_aligned_packed_ue8m0_tensor(sf, psum_layout), smxx_layout.hpp:133-184): rows that lie in no group
+ * (between the end of a group and the next multiple of the contiguous-layout alignment, and after the last group) are
+ * not read and get the scale code 0.  `psum_layout_device` holds num_psum_groups int32 row ends (device). */
+DG_API int dg_pack_fp32_into_ue8m0_psum(const float* sf_device, int32_t* out_device, int mn, int sf_k,
+                                        int64_t in_stride_mn, int64_t in_stride_k,
+                                        const int32_t* psum_layout_device, int num_psum_groups, void* stream);
 
 /* FP32 scales [num_groups, mn, sf_k] (any strides) -> same values MN-major with pitch align(mn,4):
  * get_mn_major_tma_aligned_tensor (smxx_layout.hpp:60-106; kernel smxx_layout.cuh:13).
@@ -131,14 +140,22 @@ typedef struct dg_gemm_args {
     int32_t accumulate;        /* non-zero: D += alpha A B^T (the reference's c == d case, gemm.hpp:17-53) */
     int32_t has_alpha;
     float alpha;               /* used when has_alpha != 0 (epilogue Alpha, csrc/jit_kernels/impls/epilogue_class.hpp:111-127) */
-    const int32_t* grouped_layout; /* contiguous: int32[m] expert id per row, -1 on padding; masked: int32[num_groups] rows used */
-    int32_t expected_m;        /* masked: heuristic hint only (gemm.hpp:269-318) */
+    const int32_t* grouped_layout; /* contiguous: int32[m] expert id per row, -1 on padding; masked: int32[num_groups] rows used;
+                                    * contiguous with use_psum_layout: int32[num_groups], the row where each group ends */
+    int32_t expected_m;        /* masked, and contiguous with use_psum_layout (0 = unknown): heuristic hint only (gemm.hpp:269-318) */
     void* stream;
+    /* Contiguous layout only (gemm.hpp:190-192,213-220; docs/scaling-factor-format.md 7.3).  With use_psum_layout group g
+     * occupies rows [align(grouped_layout[g-1], mk_alignment), grouped_layout[g]) of A and D (from row 0 for g = 0); the
+     * rows in between are padding.  ensure_zero_padding != 0 also writes the padding rows of D up to the next aligned
+     * row (zero when A's padding rows are zero, as the reference's assert_psum_zero_padding checks); otherwise no row
+     * outside a group is written. */
+    int32_t use_psum_layout;
+    int32_t ensure_zero_padding;
 } dg_gemm_args_t;
 
 /* fp8_fp4_gemm_nt and, through major_a / major_b, nn / tn / tt (gemm.hpp:78-179). */
 DG_API int dg_fp8_fp4_gemm(const dg_gemm_args_t* args);
-/* m_grouped_fp8_fp4_gemm_nt_contiguous / nn (gemm.hpp:181-267). */
+/* m_grouped_fp8_fp4_gemm_nt_contiguous / nn (gemm.hpp:181-267), with either form of grouped_layout. */
 DG_API int dg_m_grouped_fp8_fp4_gemm_contiguous(const dg_gemm_args_t* args);
 /* m_grouped_fp8_fp4_gemm_nt_masked (gemm.hpp:269-318). */
 DG_API int dg_m_grouped_fp8_fp4_gemm_masked(const dg_gemm_args_t* args);

@@ -89,6 +89,31 @@ def m_grouped_contiguous_ref(a, sfa, b, sfb, aligned_ms: Sequence[int], gran_k_a
     return d
 
 
+def make_psum_layout(actual_ms: Sequence[int], alignment: int):
+    """Prefix-sum form of the contiguous layout (tests/generators.py:388-404, docs/scaling-factor-format.md 7.3):
+    group i occupies rows [align(ends[i-1], alignment), ends[i]).  Returns (m_total, starts, ends int32)."""
+    starts, ends, start = [], [], 0
+    for am in actual_ms:
+        starts.append(start)
+        ends.append(start + am)
+        start = align(start + am, alignment)
+    return start, starts, np.asarray(ends, dtype=np.int32)
+
+
+def m_grouped_psum_ref(a, sfa, b, sfb, ends: Sequence[int], alignment: int, gran_k_a: int = 128, gran_k_b: int = 128,
+                       b_is_fp4: bool = False) -> np.ndarray:
+    """Rows [start_i, ends[i]) times expert i's weight; every other row is NaN (scheduler/gemm.cuh:205-225 of the
+    reference walks the same ranges)."""
+    d = np.full((a.shape[0], b.shape[1]), np.nan, dtype=np.float32)
+    start = 0
+    for i, end in enumerate(ends):
+        end = int(end)
+        if end > start:
+            d[start:end] = dequant_gemm_nt(a[start:end], sfa[start:end], b[i], sfb[i], gran_k_a, gran_k_b, False, b_is_fp4)
+        start = align(max(end, start), alignment)
+    return d
+
+
 def m_grouped_masked_ref(a, sfa, b, sfb, masked_m: Sequence[int], gran_k_a: int = 128, gran_k_b: int = 128,
                          b_is_fp4: bool = False) -> np.ndarray:
     """einsum('gmk,gnk->gmn') on the first masked_m[g] rows (tests/generators.py:453,464).

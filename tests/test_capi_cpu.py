@@ -161,6 +161,26 @@ def test_scheduler_contiguous_maps_row_blocks_to_experts():
     assert blocks[0] == 0 and blocks[1] == 0 and blocks[2] == 2 and blocks[3] == 2 and blocks[4] == 2
 
 
+@pytest.mark.parametrize("actual_ms,alignment", [((100, 150, 114), 128), ((130, 0, 256, 77, 300), 128), ((1, 1, 1), 256), ((0, 0), 128)])
+def test_scheduler_prefix_sum_layout_walks_each_group_from_its_aligned_start(actual_ms, alignment):
+    import oracle
+    import deepgemm_amd_b200 as dg
+    dg.set_mk_alignment_for_contiguous_layout(alignment)
+    try:
+        m, starts, ends = oracle.make_psum_layout(actual_ms, alignment)
+        n, bn = 1000, 112
+        tiles = _enumerate(3, bn, 16, max(m, 1), n, len(actual_ms), ends, 37)
+        want = {}
+        for g, (s0, e) in enumerate(zip(starts, ends)):
+            for mb in range(-(-(int(e) - s0) // 128)):
+                for nb in range(-(-n // bn)):
+                    want[(g, s0 // 128 + mb, nb)] = min(128, int(e) - s0 - mb * 128)
+        got = {(t[2], t[0], t[1]): t[3] for t in tiles}
+        assert len(tiles) == len(got) == len(want) and got == want
+    finally:
+        dg.set_mk_alignment_for_contiguous_layout(128)
+
+
 @pytest.mark.parametrize("counts,max_m", [((45, 83, 0, 256, 129), 256), ((0, 0, 0), 128), ((300, 1), 256), ((64,) * 16, 256)])
 def test_scheduler_masked_follows_device_counts(counts, max_m):
     n, bn = 4096, 240

@@ -370,6 +370,51 @@ def test_m_grouped_contiguous(alignment, cluster, block_m, b_fp4, monkeypatch):
         dg.set_mk_alignment_for_contiguous_layout(128)
 
 
+@pytest.mark.parametrize("alignment,block_m", [(128, 128), (128, 256), (256, 256)])
+@pytest.mark.parametrize("zero_padding", [False, True])
+@pytest.mark.parametrize("fp32_scales", [False, True])
+def test_m_grouped_contiguous_with_prefix_sum_layout(alignment, block_m, zero_padding, fp32_scales, monkeypatch):
+    """grouped_layout[g] = the row where group g ends; groups start on multiples of the alignment.  Rows in the gaps
+    are written (as zeros) only with ensure_zero_padding; their FP32 input scales may be garbage."""
+    monkeypatch.setenv("DG_FORCE_BLOCK_M", str(block_m))
+    g, n, k = 5, 1000 // 8 * 8, 1024
+    actual_ms = [130, 0, 256, 77, 300]
+    dg.set_mk_alignment_for_contiguous_layout(alignment)
+    try:
+        m, starts, ends = oracle.make_psum_layout(actual_ms, alignment)
+        in_group = np.zeros(m, dtype=bool)
+        for s0, e in zip(starts, ends):
+            in_group[s0:int(e)] = True
+        a = seeded_bf16((m, k), 23)
+        a[~in_group] = 0                                            # tests/generators.py:406
+        qa, sfa, qb, sfb = _grouped_inputs(g, n, k, a)
+        ref = oracle.m_grouped_psum_ref(qa, sfa, qb, sfb, ends, alignment)
+        if fp32_scales:
+            sfa_in = sfa.copy()
+            sfa_in[~in_group] = np.nan                              # never read: the transform writes the code 0 there
+            a_sf = torch.from_numpy(sfa_in).cuda()
+            recipe = dict(recipe_a=(1, 128), recipe_b=(1, 128))
+        else:
+            a_sf = packed_sf_cuda(sfa)
+            recipe = dict(recipe=(1, 1, 128))
+        d = torch.full((m, n), SENTINEL, dtype=torch.bfloat16, device="cuda")
+        dg.reset_kernel_status()
+        dg.m_grouped_fp8_gemm_nt_contiguous((fp8_cuda(qa), a_sf), (fp8_cuda(qb), packed_sf_cuda(sfb) if not fp32_scales
+                                            else torch.from_numpy(sfb).cuda()), d, torch.from_numpy(ends).cuda(),
+                                            use_psum_layout=True, ensure_zero_padding=zero_padding,
+                                            expected_m_for_psum_layout=200, **recipe)
+        assert dg.kernel_status() == 0
+        out = d.float().cpu().numpy()
+        assert oracle.calc_diff(out[in_group], ref[in_group]) < MAX_DIFF, diff_report(out[in_group], ref[in_group])
+        assert oracle.calc_diff(out[in_group], oracle.bf16_round(ref[in_group])) < 1e-5
+        if zero_padding:
+            assert (out[~in_group] == 0).all()                      # tests/utils.py:9-17
+        else:
+            assert (out[~in_group] == SENTINEL).all()
+    finally:
+        dg.set_mk_alignment_for_contiguous_layout(128)
+
+
 def test_m_grouped_contiguous_nn_takes_mn_major_weights():
     g, n, k = 3, 640, 768
     m, actual, aligned, layout = oracle.make_contiguous_layout(g, 200, 128, actual_ms=[130, 256, 77])
