@@ -29,6 +29,7 @@ class GemmArgs(C.Structure):
         ("accumulate", C.c_int32), ("has_alpha", C.c_int32), ("alpha", C.c_float),
         ("grouped_layout", C.c_void_p), ("expected_m", C.c_int32), ("stream", C.c_void_p),
         ("use_psum_layout", C.c_int32), ("ensure_zero_padding", C.c_int32),
+        ("sfd", C.c_void_p), ("sfd_pitch", C.c_int64),
     ]
 
 

@@ -298,7 +298,7 @@ def _logical_mn_k(t: torch.Tensor, major: int):
 
 
 def _d_dtype(d: torch.Tensor) -> int:
-    return _lib.DG_BF16 if d.dtype == torch.bfloat16 else _lib.DG_FP32
+    return {torch.bfloat16: _lib.DG_BF16, torch.float: _lib.DG_FP32, torch.float8_e4m3fn: _lib.DG_FP8_E4M3}[d.dtype]
 
 
 def _ld(t: torch.Tensor, major: int) -> int:
@@ -307,7 +307,7 @@ def _ld(t: torch.Tensor, major: int) -> int:
 
 def _fill_args(a, sfa, b, sfb, d, m, n, k, groups, major_a, major_b, gran_k_a, gran_k_b,
                accumulate=False, alpha=None, layout=None, expected_m=0, use_psum_layout=False,
-               ensure_zero_padding=False) -> GemmArgs:
+               ensure_zero_padding=False, sfd=None) -> GemmArgs:
     args = GemmArgs()
     args.a, args.sfa, args.b, args.sfb, args.d = a.data_ptr(), sfa.data_ptr(), b.data_ptr(), sfb.data_ptr(), d.data_ptr()
     args.m, args.n, args.k, args.num_groups = m, n, k, groups
@@ -323,20 +323,39 @@ def _fill_args(a, sfa, b, sfb, d, m, n, k, groups, major_a, major_b, gran_k_a, g
     args.expected_m = int(expected_m)
     args.stream = _stream()
     args.use_psum_layout, args.ensure_zero_padding = int(use_psum_layout), int(ensure_zero_padding)
+    if sfd is not None:
+        args.sfd, args.sfd_pitch = sfd.data_ptr(), sfd.stride(-1)
     return args
 
 
 def _resolve_alpha(alpha, epilogue):
-    """Only the Identity and Alpha epilogues are built (csrc/jit_kernels/impls/epilogue_class.hpp:111-127)."""
+    """The epilogue class, `alpha` and the FP8 output pair are exclusive (csrc/jit_kernels/impls/epilogue_class.hpp:111-127)."""
     if epilogue is not None:
-        from .epilogue import Alpha, Identity
-        if isinstance(epilogue, Identity):
-            return alpha
+        from .epilogue import Alpha, FP8Quantization, Identity
+        _require(alpha is None, "(epilogue_class != nullptr) + alpha.has_value() + sfd.has_value() <= 1")
+        if isinstance(epilogue, (Identity, FP8Quantization)):
+            return None
         if isinstance(epilogue, Alpha):
-            _require(alpha is None, "alpha and an Alpha epilogue are mutually exclusive")
             return epilogue.alpha
-        raise RuntimeError(f"epilogue {type(epilogue).__name__} is not built (deepgemm_amd_b200): Identity and Alpha are")
+        raise RuntimeError(f"epilogue {type(epilogue).__name__} is not built (deepgemm_amd_b200): "
+                           "Identity, Alpha and FP8Quantization are")
     return alpha
+
+
+def _resolve_sfd(epilogue, c, d, m: int, n: int):
+    """FP8Quantization: D must be e4m3 written directly (epilogue_class.hpp:84-87); its scales go to epilogue.sfd, an
+    int32 tensor [m, ceil(n / 128)] in the packed MN-major layout (four 1 x 32 scales per word)."""
+    from .epilogue import FP8Quantization
+    if not isinstance(epilogue, FP8Quantization):
+        _require(d.dtype in (torch.bfloat16, torch.float), "d.scalar_type() == torch::kBFloat16 or d.scalar_type() == torch::kFloat")
+        return None
+    sfd = epilogue.sfd
+    _require(c is None and d.dtype == torch.float8_e4m3fn, "FP8 quantization requires a direct E4M3 output")
+    _require(sfd.is_cuda and sfd.dtype == torch.int and sfd.dim() == 2, "sfd: int32 [m, ceil(n / 128)]")
+    _require(sfd.size(0) == m and sfd.size(1) == ceil_div(n, 128), "sfd: int32 [m, ceil(n / 128)]")
+    _require((sfd.stride(0) == 1 or m == 1) and sfd.stride(1) >= get_tma_aligned_size(m, 4) and sfd.stride(1) % 4 == 0,
+             "sfd must be MN-major with a TMA-aligned pitch")
+    return sfd
 
 
 def fp8_fp4_gemm_nt(a, b, d, c=None, recipe=None, recipe_a=None, recipe_b=None, compiled_dims: str = "nk",
@@ -352,7 +371,7 @@ def fp8_fp4_gemm_nt(a, b, d, c=None, recipe=None, recipe_a=None, recipe_b=None, 
     n, k_ = _logical_mn_k(b_data, major_b)
     _require(d.is_cuda and d.dim() == 2, "t.dim() == N")
     _require(m == d.size(0) and n == d.size(1) and k == k_, "m == m_ and n == n_ and k == k_")
-    _require(d.dtype in (torch.bfloat16, torch.float), "d.scalar_type() == torch::kBFloat16 or d.scalar_type() == torch::kFloat")
+    sfd = _resolve_sfd(epilogue, c, d, m, n)
 
     # early_return (gemm.hpp:17-53)
     if m == 0 or n == 0:
@@ -366,6 +385,8 @@ def fp8_fp4_gemm_nt(a, b, d, c=None, recipe=None, recipe_a=None, recipe_b=None, 
     if k == 0:
         if not is_cd_same:
             d.copy_(c) if c is not None else d.zero_()
+        if sfd is not None:
+            sfd.zero_()                 # a zero D dequantises to zero whatever the scales
         return
     if c is not None and not is_cd_same:
         d.copy_(c)
@@ -374,7 +395,7 @@ def fp8_fp4_gemm_nt(a, b, d, c=None, recipe=None, recipe_a=None, recipe_b=None, 
                                                       disable_ue8m0_cast)
     alpha = _resolve_alpha(alpha, epilogue)
     args = _fill_args(a_data, sfa, b_data, sfb, d, m, n, k, 1, major_a, major_b, gran_k_a, gran_k_b,
-                      accumulate=c is not None, alpha=alpha)
+                      accumulate=c is not None, alpha=alpha, sfd=sfd)
     check(lib.dg_fp8_fp4_gemm(C.byref(args)))
 
 
@@ -489,12 +510,14 @@ m_grouped_fp4_gemm_nt_masked = m_grouped_fp8_fp4_gemm_nt_masked
 # Introspection used by the tests and the benchmark
 # ------------------------------------------------------------------------------------------------
 def get_gemm_config(kind: int, m: int, n: int, k: int, num_groups: int = 1, expected_m: int = 0,
-                    b_is_fp4: bool = False, d_is_fp32: bool = False, gran_k_a: int = 128, gran_k_b: int = 128) -> dict:
+                    b_is_fp4: bool = False, d_is_fp32: bool = False, gran_k_a: int = 128, gran_k_b: int = 128,
+                    d_is_fp8: bool = False) -> dict:
     """The tile configuration the heuristics choose for a problem (host only, needs no GPU)."""
     args = GemmArgs()
     args.m, args.n, args.k, args.num_groups = m, n, k, num_groups
     args.a_dtype, args.b_dtype = _lib.DG_FP8_E4M3, (_lib.DG_FP4_E2M1_X2 if b_is_fp4 else _lib.DG_FP8_E4M3)
-    args.d_dtype = _lib.DG_FP32 if d_is_fp32 else _lib.DG_BF16
+    args.d_dtype = _lib.DG_FP32 if d_is_fp32 else (_lib.DG_FP8_E4M3 if d_is_fp8 else _lib.DG_BF16)
+    args.sfd_pitch = align(m, 4)
     args.lda, args.ldb, args.ldd = k, (k // 2 if b_is_fp4 else k), n
     args.sfa_pitch, args.sfb_pitch = align(m, 4), align(n, 4)
     args.gran_k_a, args.gran_k_b = gran_k_a, gran_k_b
@@ -506,12 +529,13 @@ def get_gemm_config(kind: int, m: int, n: int, k: int, num_groups: int = 1, expe
 
 def precompile_gemm(kind: int, m: int, n: int, k: int, num_groups: int = 1, expected_m: int = 0,
                     b_is_fp4: bool = False, d_is_fp32: bool = False, accumulate: bool = False,
-                    gran_k_a: int = 128, gran_k_b: int = 128) -> None:
+                    gran_k_a: int = 128, gran_k_b: int = 128, d_is_fp8: bool = False) -> None:
     """Compile the kernel a GEMM of this shape would use into the cache (needs nvcc, no GPU)."""
     args = GemmArgs()
     args.m, args.n, args.k, args.num_groups = m, n, k, num_groups
     args.a_dtype, args.b_dtype = _lib.DG_FP8_E4M3, (_lib.DG_FP4_E2M1_X2 if b_is_fp4 else _lib.DG_FP8_E4M3)
-    args.d_dtype = _lib.DG_FP32 if d_is_fp32 else _lib.DG_BF16
+    args.d_dtype = _lib.DG_FP32 if d_is_fp32 else (_lib.DG_FP8_E4M3 if d_is_fp8 else _lib.DG_BF16)
+    args.sfd_pitch = align(m, 4)
     args.lda, args.ldb, args.ldd = k, (k // 2 if b_is_fp4 else k), n
     args.sfa_pitch, args.sfb_pitch = align(m, 4), align(n, 4)
     args.gran_k_a, args.gran_k_b = gran_k_a, gran_k_b

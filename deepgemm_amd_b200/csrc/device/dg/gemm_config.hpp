@@ -17,7 +17,7 @@ constexpr uint32_t kSmemCapacity = 232448;      // largest dynamic shared memory
 constexpr uint32_t kTmemCapacityCols = 512;
 
 struct GemmLayout {
-    uint32_t block_m, block_n, block_k, num_stages, d_elem_bytes;   // block_m: rows of A per CTA and stage (128 or 256)
+    uint32_t block_m, block_n, block_k, num_stages, d_elem_bytes;   // block_m: rows of A per CTA and stage (128 or 256); D: 4, 2 or 1 byte
     uint32_t cluster = 1;                          // CTAs sharing one B tile (each loads block_n / cluster rows of B)
     uint32_t b_mn_major = 0;                       // B stored with N contiguous: staged as 128-column atoms of [128 K][128 B]
     uint32_t gran_k_a = 128, gran_k_b = 128;       // elements of K per scale (a packed scale word holds four scales)
@@ -40,9 +40,9 @@ struct GemmLayout {
     DG_HDC uint32_t sf_block_n() const { return (block_n + 127) / 128 * 128; }
     // D leaves through TMA store boxes of 128 rows.  The epilogue drains one "group" of every D row per synchronisation:
     // 128 bytes with 128-row CTA tiles, 64 bytes with 256-row tiles (whose two epilogue warpgroups each double-buffer
-    // their staging inside the same 32 KB).  Complete groups use a box as wide as the group; the remainder of the tile
+    // their staging inside the same 32 KB) and with one-byte (quantised FP8) output, so a group is never more than 64 columns.  Complete groups use a box as wide as the group; the remainder of the tile
     // row (when block_n * element size is not a multiple of the group) uses boxes of the widest swizzle span dividing it.
-    DG_HDC uint32_t group_bytes() const { return block_m == 256 ? 64 : 128; }
+    DG_HDC uint32_t group_bytes() const { return block_m == 256 || d_elem_bytes == 1 ? 64 : 128; }
     DG_HDC uint32_t tail_bytes() const { return (block_n * d_elem_bytes) % group_bytes(); }
     DG_HDC uint32_t store_row_bytes() const {          // row width of the boxes that cover the tail (the group width when there is none)
         return tail_bytes() == 0 ? group_bytes() : (tail_bytes() % 64 == 0 ? 64 : 32);

@@ -21,7 +21,13 @@
 //   DG_GEMM_TYPE (0 dense, 1 m-grouped contiguous, 2 m-grouped masked, 3 m-grouped contiguous with a prefix-sum
 //   layout; DG_WRITE_PADDING for the latter), DG_M_HALVES, DG_BLOCK_N, DG_NUM_STAGES,
 //   DG_CLUSTER, DG_A_FP4, DG_B_FP4, DG_MAJOR_A, DG_MAJOR_B (0 K-major, 1 MN-major), DG_GRAN_K_A, DG_GRAN_K_B,
-//   DG_D_FP32, DG_ACCUMULATE, DG_RASTER_GROUP, DG_SPLIT_K.
+//   DG_D_FP32, DG_D_FP8, DG_ACCUMULATE, DG_RASTER_GROUP, DG_SPLIT_K.
+//
+// DG_D_FP8 (dense only): the epilogue quantises D on the way out.  Every accumulator is first rounded to BF16, then each
+// 32 columns of a row get one UE8M0 scale (amax clamped to 1e-4, / 448, rounded up to a power of two), D is stored as
+// float8_e4m3 and the scale bytes go into a packed int32 tensor in the layout the GEMMs take for SFA (four scales per
+// word, MN-major): the same bits as a BF16 D followed by the per-token 1 x 32 cast, which is how the reference defines
+// its QuantizeToFP8 epilogue (deep_gemm/include/deep_gemm/epilogue/operators.cuh:68-92).
 //
 // DG_SPLIT_K (dense only, for shapes with too few output tiles to fill the GPU): every output tile becomes
 // num_splits work items over slices of K, and the kernel's D is an FP32 workspace of num_splits stacked
@@ -52,6 +58,7 @@
 
 #include "gemm_config.hpp"
 #include "ptx.cuh"
+#include "quant_math.cuh"
 #include "tile_scheduler.cuh"
 
 namespace dg {
@@ -73,6 +80,7 @@ constexpr bool     kBMnMajor   = DG_MAJOR_B != 0;
 constexpr uint32_t kGranKA     = DG_GRAN_K_A;
 constexpr uint32_t kGranKB     = DG_GRAN_K_B;
 constexpr bool     kDIsFP32    = DG_D_FP32 != 0;
+constexpr bool     kDIsFP8     = DG_D_FP8 != 0;
 constexpr bool     kAccumulate = DG_ACCUMULATE != 0;
 constexpr uint32_t kRasterGroup = DG_RASTER_GROUP;
 constexpr bool     kSplitK     = DG_SPLIT_K != 0;
@@ -110,7 +118,10 @@ constexpr uint32_t SF_BLOCK_N = (BLOCK_N + 127) / 128 * 128;
 
 // Shared memory and tensor memory maps (every operand stage starts on a 1024-byte boundary, as the
 // 128-byte swizzle requires); the arithmetic lives in gemm_config.hpp, shared with the host heuristics
-constexpr uint32_t kDElemBytes = kDIsFP32 ? 4 : 2;
+constexpr uint32_t kDElemBytes = kDIsFP32 ? 4 : (kDIsFP8 ? 1 : 2);
+static_assert(!(kDIsFP32 && kDIsFP8), "one output type");
+static_assert(!kDIsFP8 || (kGemmType == 0 && !kAccumulate && !kSplitK && BLOCK_N % 32 == 0),
+              "the quantising epilogue serves the plain dense GEMM with tiles of whole 32-column scale groups");
 constexpr GemmLayout kLayout{CTA_M, BLOCK_N, BLOCK_K, kNumStages, kDElemBytes, kCluster, kBMnMajor ? 1u : 0u, kGranKA, kGranKB,
                              DG_SHORT_K};
 constexpr uint32_t kNumSFABuffers = kLayout.sfa_buffers(), kNumSFBBuffers = kLayout.sfb_buffers();
@@ -165,6 +176,8 @@ struct GemmParams {
     uint32_t kb_per_split;       // K-blocks per slice, a multiple of 4 so every slice starts on a packed scale word
     uint32_t split_panel_rows;   // split-K: rows between consecutive slices' panels in the workspace D points to
     uint32_t group_alignment;    // prefix-sum layout: every group starts on a multiple of this many rows
+    uint32_t* sfd;               // quantising epilogue: packed UE8M0 scales of D, word (row, column / 128) at sfd[(column / 128) * sfd_pitch + row]
+    uint32_t sfd_pitch;
 };
 
 // Wait-time accounting for tuning: with DG_PROFILE defined every role adds the cycles it spent inside each
@@ -623,10 +636,43 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                                 v[l][i] = __float_as_uint(__uint_as_float(v[l][i]) * p.alpha);
                         }
                 }
-                // The four registers of 16-byte chunk c of this group's row: 8 BF16 or 4 FP32 values
+                // Quantised output: the group's BF16-rounded values, 32 columns per scale, as e4m3 words; the scale bytes
+                // go straight to global memory (one byte per row and 32 columns)
+                [[maybe_unused]] uint32_t q8[kDIsFP8 ? kGroupCols / 4 : 1];
+                if constexpr (kDIsFP8) {
+                    #pragma unroll
+                    for (uint32_t t = 0; t < kGroupCols / 32; ++t) {
+                        if (t * 32 < kCols) {
+                            uint32_t pairs[16];                     // BF16 pairs of the 32 columns
+                            #pragma unroll
+                            for (uint32_t i = 0; i < 16; ++i) {
+                                if constexpr (kRowInRegs) pairs[i] = row[g * (kGroupCols / 2) + t * 16 + i];
+                                else pairs[i] = pack_bf16x2(__uint_as_float(v[t * 2 + i / 8][(2 * i) % 16]),
+                                                            __uint_as_float(v[t * 2 + i / 8][(2 * i) % 16 + 1]));
+                            }
+                            float amax = 0.0f;
+                            #pragma unroll
+                            for (uint32_t i = 0; i < 16; ++i)
+                                amax = fmaxf(amax, fmaxf(fabsf(bf16_lo(pairs[i])), fabsf(bf16_hi(pairs[i]))));
+                            const float sf = e4m3_block_scale(amax), inv = 1.0f / sf;
+                            #pragma unroll
+                            for (uint32_t i = 0; i < 8; ++i)
+                                q8[t * 8 + i] = pack_e4m3x4(bf16_lo(pairs[2 * i]) * inv, bf16_hi(pairs[2 * i]) * inv,
+                                                            bf16_lo(pairs[2 * i + 1]) * inv, bf16_hi(pairs[2 * i + 1]) * inv);
+                            const uint32_t col = n0 + g * kGroupCols + t * 32, d_row = d_row0 + row_in_tile;
+                            if (d_row < p.shape_m && col < p.shape_n)
+                                reinterpret_cast<uint8_t*>(p.sfd + static_cast<size_t>(col / 128) * p.sfd_pitch + d_row)[(col / 32) % 4] =
+                                    static_cast<uint8_t>(ue8m0_code(sf));
+                        }
+                    }
+                }
+                // The four registers of 16-byte chunk c of this group's row: 16 e4m3, 8 BF16 or 4 FP32 values
                 constexpr uint32_t kElemsPerChunk = 16 / kDElemBytes;
                 auto chunk = [&](uint32_t c, uint32_t (&out)[4]) {
-                    if constexpr (kRowInRegs) {
+                    if constexpr (kDIsFP8) {
+                        #pragma unroll
+                        for (uint32_t i = 0; i < 4; ++i) out[i] = q8[c * 4 + i];
+                    } else if constexpr (kRowInRegs) {
                         #pragma unroll
                         for (uint32_t i = 0; i < 4; ++i) out[i] = row[g * (kGroupCols / 2) + c * 4 + i];
                     } else if constexpr (!kDIsFP32) {
@@ -689,7 +735,9 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                     }
                 } else if (row_in_tile < valid_rows) {
                     // Ragged tile of the masked layout: rows at or beyond the group's row count stay untouched
-                    if constexpr (!kDIsFP32) {
+                    if constexpr (kDIsFP8) {
+                        // not reached: ragged tiles exist only in the grouped layouts
+                    } else if constexpr (!kDIsFP32) {
                         unsigned short* drow = reinterpret_cast<unsigned short*>(p.d) + static_cast<size_t>(d_row0 + row_in_tile) * p.ldd;
                         #pragma unroll
                         for (uint32_t c = 0; c < kGroupCols / 8; ++c) {

@@ -29,6 +29,8 @@ struct GemmParams {
     unsigned long long* profile;
     uint32_t num_splits, kb_per_split, split_panel_rows;
     uint32_t group_alignment;
+    uint32_t* sfd;
+    uint32_t sfd_pitch;
 };
 
 // Split-K scratch: num_splits stacked FP32 [rows x N] panels.  One buffer per device, shared by every stream (a
@@ -63,7 +65,7 @@ unsigned long long* profile_buffer() {
 struct Problem {
     int kind;
     int m, n, k, groups;
-    bool a_fp4, b_fp4, d_fp32, accumulate, a_mn_major, b_mn_major;
+    bool a_fp4, b_fp4, d_fp32, d_fp8, accumulate, a_mn_major, b_mn_major;
     int gran_k_a, gran_k_b;
     int expected_m;
     bool write_padding;      // prefix-sum layout: also write the padding rows of D up to the next aligned row
@@ -75,8 +77,14 @@ int validate(int kind, const dg_gemm_args_t* a, bool need_pointers, Problem* p) 
                kind == DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM);
     DG_REQUIRE(a->a_dtype == DG_FP8_E4M3 || a->a_dtype == DG_FP4_E2M1_X2);
     DG_REQUIRE(a->b_dtype == DG_FP8_E4M3 || a->b_dtype == DG_FP4_E2M1_X2);
-    DG_REQUIRE(a->d_dtype == DG_BF16 || a->d_dtype == DG_FP32);
+    DG_REQUIRE(a->d_dtype == DG_BF16 || a->d_dtype == DG_FP32 || a->d_dtype == DG_FP8_E4M3);
     if (kind != DG_GEMM_DENSE) DG_REQUIRE(a->d_dtype == DG_BF16);            // gemm.hpp:209,299
+    if (a->d_dtype == DG_FP8_E4M3) {
+        // "FP8 quantization requires a direct E4M3 output" (epilogue_class.hpp:84-87); the epilogues do not compose
+        DG_REQUIRE(!a->accumulate && !a->has_alpha);
+        if (need_pointers) DG_REQUIRE(a->sfd != nullptr && reinterpret_cast<uintptr_t>(a->sfd) % 4 == 0);
+        DG_REQUIRE(a->sfd_pitch >= align_up<int64_t>(a->m, 4));
+    }
     DG_REQUIRE(a->m >= 0 && a->n >= 0 && a->k >= 0);
     DG_REQUIRE(a->gran_k_a == 32 || a->gran_k_a == 128);
     DG_REQUIRE(a->gran_k_b == 32 || a->gran_k_b == 128);
@@ -106,6 +114,7 @@ int validate(int kind, const dg_gemm_args_t* a, bool need_pointers, Problem* p) 
     p->a_fp4 = a->a_dtype == DG_FP4_E2M1_X2;
     p->b_fp4 = a->b_dtype == DG_FP4_E2M1_X2;
     p->d_fp32 = a->d_dtype == DG_FP32;
+    p->d_fp8 = a->d_dtype == DG_FP8_E4M3;
     p->accumulate = a->accumulate != 0;
     p->gran_k_a = a->gran_k_a; p->gran_k_b = a->gran_k_b;
     p->expected_m = a->expected_m;
@@ -126,7 +135,7 @@ int validate(int kind, const dg_gemm_args_t* a, bool need_pointers, Problem* p) 
     const int64_t k_bytes_b = p->b_mn_major ? a->n : (p->b_fp4 ? a->k / 2 : a->k);
     DG_REQUIRE(a->lda >= k_bytes_a && a->lda % (p->a_fp4 ? 32 : 16) == 0);   // TMA: strides are multiples of 16 bytes
     DG_REQUIRE(a->ldb >= k_bytes_b && a->ldb % (p->b_fp4 ? 32 : 16) == 0);
-    const int d_elem = p->d_fp32 ? 4 : 2;
+    const int d_elem = p->d_fp32 ? 4 : (p->d_fp8 ? 1 : 2);
     DG_REQUIRE(a->ldd >= a->n && (a->ldd * d_elem) % 16 == 0);
     // Packed scale tensors: csrc/utils/layout.hpp:121-130
     DG_REQUIRE(a->sfa_pitch >= align_up<int64_t>(a->m, 4) && a->sfa_pitch % 4 == 0);
@@ -174,7 +183,7 @@ GemmLayout fit_stages(GemmLayout lay, int64_t item_kb, int max_stages) {
 
 int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
     const int num_sms = dg_get_num_sms();
-    const int d_elem = p.d_fp32 ? 4 : 2;
+    const int d_elem = p.d_fp32 ? 4 : (p.d_fp8 ? 1 : 2);
     const int64_t k_blocks = ceil_div(p.k, 128);           // in units of 128 elements, whatever the stage size
     const int forced_bn = env_int("FORCE_BLOCK_N"), forced_cluster = env_int("FORCE_CLUSTER"), forced_splits = env_int("FORCE_SPLIT_K");
     const int forced_block_m = env_int("FORCE_BLOCK_M"), forced_block_k = env_int("FORCE_BLOCK_K");
@@ -216,11 +225,12 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
         // to pull in; slicing K lets wide tiles (little re-reading of A) still spread over all SMs.  Slices hold a
         // multiple of 4 K-blocks (one packed scale word); all work items run in one wave; the second pass costs a
         // launch plus S FP32 panels of traffic.
-        const bool can_split = p.kind == DG_GEMM_DENSE && !p.accumulate && cluster == 1 && halves == 1 && bk == 128 &&
+        const bool can_split = p.kind == DG_GEMM_DENSE && !p.accumulate && !p.d_fp8 && cluster == 1 && halves == 1 && bk == 128 &&
                                forced_splits != 1 && k_blocks >= 16;
         for (int bn = 16; bn <= 240; bn += 16) {
             if (forced_bn && bn != forced_bn) continue;
             if (p.b_mn_major && (bn / cluster) % 16 != 0) continue;       // an MN-major B load starts on a 16-byte boundary
+            if (p.d_fp8 && bn % 32 != 0) continue;                        // whole 32-column scale groups per tile
             const int64_t mn_tiles = m_blocks * ceil_div(p.n, bn);
             const int max_splits = can_split ? static_cast<int>(std::min<int64_t>(units / std::max<int64_t>(mn_tiles, 1), k_blocks / 8)) : 1;
             for (int want = 1; want <= std::max(1, max_splits); ++want) {
@@ -302,7 +312,7 @@ GemmLayout layout_of(const Problem& p, const dg_gemm_config_t& cfg) {
     const bool split = cfg.num_splits > 1;
     const int64_t item_kb = ceil_div<int64_t>(std::min<int64_t>(p.k, static_cast<int64_t>(cfg.kb_per_split) * 128), cfg.block_k);
     GemmLayout lay{static_cast<uint32_t>(cfg.block_m), static_cast<uint32_t>(cfg.block_n), static_cast<uint32_t>(cfg.block_k),
-                   static_cast<uint32_t>(cfg.num_stages), static_cast<uint32_t>((p.d_fp32 || split) ? 4 : 2),
+                   static_cast<uint32_t>(cfg.num_stages), static_cast<uint32_t>((p.d_fp32 || split) ? 4 : (p.d_fp8 ? 1 : 2)),
                    static_cast<uint32_t>(cfg.cluster_size), p.b_mn_major ? 1u : 0u,
                    static_cast<uint32_t>(p.gran_k_a), static_cast<uint32_t>(p.gran_k_b),
                    item_kb < cfg.num_stages ? 1u : 0u};
@@ -326,6 +336,7 @@ std::string generate_source(const Problem& p, const dg_gemm_config_t& cfg) {
       << "#define DG_GRAN_K_A " << p.gran_k_a << "\n"
       << "#define DG_GRAN_K_B " << p.gran_k_b << "\n"
       << "#define DG_D_FP32 " << ((p.d_fp32 || cfg.num_splits > 1) ? 1 : 0) << "\n"
+      << "#define DG_D_FP8 " << (p.d_fp8 ? 1 : 0) << "\n"
       << "#define DG_ACCUMULATE " << (p.accumulate ? 1 : 0) << "\n"
       << "#define DG_RASTER_GROUP " << cfg.raster_group << "\n"
       << "#define DG_SPLIT_K " << (cfg.num_splits > 1 ? 1 : 0) << "\n"
@@ -438,10 +449,11 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
                                          lay.store_row_bytes() == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
     // Two views of D: boxes as wide as an epilogue group (128 or 64 bytes) for complete groups, narrower boxes for the
     // ragged end of a tile row
-    const CUtensorMapDataType d_type = kernel_d_fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    const CUtensorMapDataType d_type = kernel_d_fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 :
+                                       p.d_fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     void* d_base = split ? static_cast<void*>(workspace) : a->d;
     const uint64_t d_rows = split ? static_cast<uint64_t>(cfg.num_splits) * panel_rows : a_rows;
-    const uint64_t d_pitch_bytes = split ? ld_ws * 4 : a->ldd * (p.d_fp32 ? 4 : 2);
+    const uint64_t d_pitch_bytes = split ? ld_ws * 4 : a->ldd * (p.d_fp32 ? 4 : (p.d_fp8 ? 1 : 2));
     if ((rc = encode_2d(&tm_d, d_type, d_base, p.n, d_rows, d_pitch_bytes, lay.store_cols(), 128, d_swizzle)) != DG_OK) return rc;
     if ((rc = encode_2d(&tm_d_full, d_type, d_base, p.n, d_rows, d_pitch_bytes, lay.group_cols(), 128,
                         lay.group_bytes() == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B)) != DG_OK)
@@ -461,6 +473,8 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
     params.kb_per_split = cfg.kb_per_split;
     params.split_panel_rows = static_cast<uint32_t>(panel_rows);
     params.group_alignment = static_cast<uint32_t>(state().mk_alignment);
+    params.sfd = static_cast<uint32_t*>(a->sfd);
+    params.sfd_pitch = static_cast<uint32_t>(a->sfd_pitch);
     void* kargs[7] = {&tm_a, &tm_b, &tm_sfa, &tm_sfb, &tm_d, &tm_d_full, &params};
     if (env_int("PROFILE")) {
         // synchronous, printing path for tuning only

@@ -114,7 +114,7 @@ const std::string& device_headers_digest() {
     static std::once_flag once;
     std::call_once(once, []() {
         std::string all;
-        for (const char* f : {"gemm_fp8_fp4.cuh", "gemm_config.hpp", "ptx.cuh", "tile_scheduler.cuh"})
+        for (const char* f : {"gemm_fp8_fp4.cuh", "gemm_config.hpp", "ptx.cuh", "tile_scheduler.cuh", "quant_math.cuh"})
             all += read_file(state().library_root + "/csrc/device/dg/" + f) + "\n//--\n";
         digest = hex_key(all);
     });

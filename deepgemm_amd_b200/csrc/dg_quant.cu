@@ -14,18 +14,13 @@
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 
+#include "device/dg/quant_math.cuh"
+
 namespace dg {
 namespace {
 
 constexpr int kRowsPerCta = 16;
 constexpr int kColsPerCta = 512;
-
-__device__ __forceinline__ float ceil_to_power_of_two(float x) {
-    const uint32_t bits = __float_as_uint(x);
-    uint32_t exponent = ((bits >> 23) & 0xFFu) + ((bits & 0x7FFFFFu) != 0 ? 1u : 0u);
-    exponent = exponent < 1u ? 1u : (exponent > 254u ? 254u : exponent);
-    return __uint_as_float(exponent << 23);
-}
 
 // e2m1 code of a value already divided by its scale: round to nearest, ties to the even mantissa, no negative zero
 __device__ __forceinline__ uint32_t e2m1_code(float x) {

@@ -127,7 +127,7 @@ typedef struct dg_gemm_args {
     int32_t num_groups;        /* 1 for dense */
     int32_t a_dtype;           /* dg_dtype_t: DG_FP8_E4M3 or DG_FP4_E2M1_X2 */
     int32_t b_dtype;
-    int32_t d_dtype;           /* DG_BF16 or DG_FP32 (dense only) */
+    int32_t d_dtype;           /* DG_BF16, DG_FP32 (dense only) or DG_FP8_E4M3 (dense only, with sfd below) */
     int32_t major_a;           /* dg_major_t; K-major: rows of K contiguous */
     int32_t major_b;
     int64_t lda;               /* pitch between rows (K-major) or between K slices (MN-major), in storage elements (bytes) */
@@ -151,6 +151,14 @@ typedef struct dg_gemm_args {
      * outside a group is written. */
     int32_t use_psum_layout;
     int32_t ensure_zero_padding;
+    /* Dense GEMM with d_dtype == DG_FP8_E4M3: the FP8Quantization epilogue (csrc/jit_kernels/impls/epilogue_class.hpp:69-92,
+     * deep_gemm/include/deep_gemm/epilogue/operators.cuh:68-92).  D [m, n] is written as float8_e4m3 (ldd in bytes) and
+     * `sfd` receives one UE8M0 scale per row and 32 columns, packed four to an int32 in the layout the GEMMs take for SFA:
+     * [m, ceil(n / 128)] int32, MN contiguous, K pitch sfd_pitch (>= align(m, 4)).  Each accumulator is rounded to BF16
+     * first, so D and sfd equal a BF16 D followed by dg_per_token_cast(gran_k 32, packed).  Not combined with accumulate
+     * or alpha; words of sfd beyond column n keep the bytes they had. */
+    void* sfd;
+    int64_t sfd_pitch;
 } dg_gemm_args_t;
 
 /* fp8_fp4_gemm_nt and, through major_a / major_b, nn / tn / tt (gemm.hpp:78-179). */

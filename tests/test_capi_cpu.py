@@ -68,7 +68,9 @@ def _args(m=256, n=512, k=1024, groups=1, **kw):
 
 @pytest.mark.parametrize("kw,kind,pattern", [
     (dict(gran_k_a=64), 0, "gran_k_a == 32"),
-    (dict(d_dtype=_lib.DG_FP8_E4M3), 0, "d_dtype == DG_BF16"),
+    (dict(d_dtype=_lib.DG_FP8_E4M3), 0, "sfd_pitch >= align_up"),                       # quantised D needs its scale tensor
+    (dict(d_dtype=_lib.DG_FP8_E4M3, sfd_pitch=256, accumulate=1), 0, "!a->accumulate"),  # and never accumulates
+    (dict(d_dtype=_lib.DG_FP8_E4M3, num_groups=2), 1, "d_dtype == DG_BF16"),
     (dict(ldd=500), 0, "ldd >= a->n"),
     (dict(n=513, ldd=513), 0, "% 16 == 0"),
     (dict(sfa_pitch=254), 0, "sfa_pitch"),

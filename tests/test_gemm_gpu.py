@@ -262,6 +262,39 @@ def test_programmatic_dependent_launch_keeps_stream_order():
     assert oracle.calc_diff(results[1].numpy(), ref) < 1e-9
 
 
+@pytest.mark.parametrize("m,n,k", [(256, 512, 1024), (129, 224, 256), (128, 96, 128), (1000, 2112, 1792), (4096, 4096, 512)])
+@pytest.mark.parametrize("block_m", [128, 256])
+def test_fp8_quantising_epilogue_equals_bf16_output_followed_by_the_1x32_cast(m, n, k, block_m, monkeypatch):
+    """FP8Quantization epilogue: D as e4m3 plus packed per-row, per-32-column UE8M0 scales, bit for bit what the BF16
+    GEMM followed by the per-token cast gives (tests/test_einsum.py:148-164 checks the reference the same way)."""
+    if block_m == 256 and m <= 128:
+        pytest.skip("256-row tiles need more than 128 rows")
+    from deepgemm_amd_b200.epilogue import FP8Quantization
+    monkeypatch.setenv("DG_FORCE_BLOCK_M", str(block_m))
+    qa, sfa, qb, sfb, _ = quantise_dense(seeded_bf16((m, k), 51), seeded_bf16((n, k), 52))
+    a = (fp8_cuda(qa), packed_sf_cuda(sfa)); b = (fp8_cuda(qb), packed_sf_cuda(sfb))
+    d_bf16 = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    dg.fp8_gemm_nt(a, b, d_bf16, recipe=(1, 1, 128))
+    want_q, want_sf = dg.per_token_cast(d_bf16, "e4m3", gran_k=32, use_packed_ue8m0=True)
+    # the cast kernel itself against the oracle on this data
+    oq, osf = oracle.per_token_cast_to_fp8(d_bf16.float().cpu().numpy(), True, 32)
+    assert np.array_equal(want_q.view(torch.uint8).cpu().numpy(), oq)
+
+    amn = dg.get_tma_aligned_size(m, 4)
+    sfd = torch.zeros((-(-n // 128), amn), dtype=torch.int, device="cuda").t()[:m]
+    d_q = torch.zeros((m, n), dtype=torch.uint8, device="cuda").view(torch.float8_e4m3fn)
+    dg.reset_kernel_status()
+    dg.fp8_gemm_nt(a, b, d_q, recipe=(1, 1, 128), epilogue=FP8Quantization(sfd))
+    assert dg.kernel_status() == 0
+    assert torch.equal(d_q.view(torch.uint8), want_q.view(torch.uint8))
+    assert torch.equal(sfd, want_sf)
+    # dequantised, it is the GEMM result to within e4m3 precision
+    deq = oracle.cast_back_from_fp8(d_q.view(torch.uint8).cpu().numpy(), osf, 32)
+    assert oracle.calc_diff(deq, oracle.dequant_gemm_nt(qa, sfa, qb, sfb)) < 2e-3
+    with pytest.raises(RuntimeError, match="direct E4M3 output"):
+        dg.fp8_gemm_nt(a, b, d_bf16, recipe=(1, 1, 128), epilogue=FP8Quantization(sfd))
+
+
 def test_fp32_scales_are_transformed_on_the_fly_like_the_legacy_recipe():
     # float32 SFA [m, k/128] and SFB [n/128, k/128] with the default recipe (1, 128, 128) (csrc/utils/layout.hpp:85-98)
     m, n, k = 128, 2112, 1024
