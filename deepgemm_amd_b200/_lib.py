@@ -15,6 +15,7 @@ DG_OK = 0
 DG_FP8_E4M3, DG_FP4_E2M1_X2, DG_BF16, DG_FP32 = 0, 1, 2, 3
 DG_MAJOR_K, DG_MAJOR_MN = 0, 1
 DG_GEMM_DENSE, DG_GEMM_M_GROUPED_CONTIGUOUS, DG_GEMM_M_GROUPED_MASKED, DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM = 0, 1, 2, 3
+DG_GEMM_K_GROUPED_CONTIGUOUS = 4
 
 
 class GemmArgs(C.Structure):
@@ -61,6 +62,8 @@ SIGNATURES = {
                                           C.c_int64, C.c_int64, C.c_int64, C.c_void_p]),
     "dg_pack_fp32_into_ue8m0_psum": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int64, C.c_int64,
                                                C.c_void_p, C.c_int, C.c_void_p]),
+    "dg_pack_k_grouped_fp32_into_ue8m0": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
+                                                    C.c_int, C.c_int, C.c_void_p]),
     "dg_transpose_fp32_mn_major": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                              C.c_int64, C.c_int64, C.c_int64, C.c_void_p]),
     "dg_per_token_cast": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int, C.c_int,
@@ -69,6 +72,7 @@ SIGNATURES = {
     "dg_fp8_fp4_gemm_noalloc": (C.c_int, [C.POINTER(GemmArgs)]),
     "dg_m_grouped_fp8_fp4_gemm_contiguous": (C.c_int, [C.POINTER(GemmArgs)]),
     "dg_m_grouped_fp8_fp4_gemm_masked": (C.c_int, [C.POINTER(GemmArgs)]),
+    "dg_k_grouped_fp8_gemm_contiguous": (C.c_int, [C.POINTER(GemmArgs)]),
     "dg_gemm_precompile": (C.c_int, [C.c_int, C.POINTER(GemmArgs)]),
     "dg_get_gemm_config": (C.c_int, [C.c_int, C.POINTER(GemmArgs), C.POINTER(GemmConfig)]),
     "dg_enumerate_tiles": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,

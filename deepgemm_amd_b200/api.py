@@ -9,7 +9,7 @@ transformed scale tensors only; all compute runs in the library's CUDA kernels.
 from __future__ import annotations
 
 import ctypes as C
-from typing import Optional, Tuple, Union
+from typing import Optional, Sequence, Tuple, Union
 
 import torch
 
@@ -397,6 +397,123 @@ def fp8_fp4_gemm_nt(a, b, d, c=None, recipe=None, recipe_a=None, recipe_b=None, 
     args = _fill_args(a_data, sfa, b_data, sfb, d, m, n, k, 1, major_a, major_b, gran_k_a, gran_k_b,
                       accumulate=c is not None, alpha=alpha, sfd=sfd)
     check(lib.dg_fp8_fp4_gemm(C.byref(args)))
+
+
+# ------------------------------------------------------------------------------------------------
+# K-grouped contiguous GEMM (csrc/apis/gemm.hpp:320-372, csrc/apis/layout.hpp:89-116)
+# ------------------------------------------------------------------------------------------------
+def _k_grouped_sizes(ks_cpu, grouped_layout, num_groups: int, use_psum_layout: bool, k_alignment: int, sum_k_if_missing: int) -> int:
+    """check_k_grouped_args (gemm.hpp:55-76): the summed (padded) K."""
+    _require(grouped_layout.is_contiguous() and grouped_layout.dtype == torch.int, "grouped_layout: contiguous int32")
+    _require(grouped_layout.numel() == num_groups, "static_cast<int>(grouped_layout.numel()) == num_groups")
+    if ks_cpu:
+        _require(len(ks_cpu) == num_groups, "static_cast<int>(ks_cpu.value().size()) == num_groups")
+        for k_i in ks_cpu:
+            _require(k_i % k_alignment == 0, "k % k_alignment == 0")
+        return int(sum(ks_cpu))
+    _require(use_psum_layout, "use_psum_layout")
+    return sum_k_if_missing
+
+
+def get_k_grouped_mn_major_tma_aligned_packed_ue8m0_tensor(sf: torch.Tensor, grouped_layout: torch.Tensor,
+                                                           ks_cpu: Optional[Sequence[int]] = None, gran_k: int = 128,
+                                                           k_alignment: Optional[int] = None,
+                                                           use_psum_layout: bool = False) -> torch.Tensor:
+    """FP32 scales [sum of sf rows, mn] of a k-grouped operand -> packed UE8M0 int32 [packed rows, mn], every group
+    starting a new packed row (csrc/jit_kernels/impls/smxx_layout.hpp:218-283, docs/scaling-factor-format.md 5.2-5.4)."""
+    k_alignment = get_mk_alignment_for_contiguous_layout() if k_alignment is None else k_alignment
+    _require(gran_k in (32, 128) and k_alignment % 128 == 0, "(gran_k == 32 or gran_k == 128) and k_alignment % 128 == 0")
+    _require(k_alignment == get_mk_alignment_for_contiguous_layout(), "k_alignment is the contiguous-layout alignment")
+    _require(sf.dim() == 2 and sf.dtype == torch.float and sf.is_contiguous() and sf.is_cuda, "sf.is_contiguous()")
+    sf_k, mn = sf.shape
+    num_groups = grouped_layout.numel()
+    _require(num_groups <= 128 and mn % 4 == 0, "num_groups <= 128 and mn % 4 == 0")
+    _require(grouped_layout.is_contiguous() and grouped_layout.dtype == torch.int, "grouped_layout: contiguous int32")
+    if ks_cpu:
+        _require(len(ks_cpu) == num_groups, "static_cast<int>(ks_cpu.value().size()) == num_groups")
+        ref_sf_k = packed = 0
+        for k_i in ks_cpu:
+            _require(k_i % k_alignment == 0 and k_i % gran_k == 0, "k % k_alignment == 0 and k % gran_k == 0")
+            ref_sf_k += k_i // gran_k
+            packed += ceil_div(k_i // gran_k, 4)
+        _require(ref_sf_k == sf_k, "ref_sf_k == sf_k")
+    else:
+        _require(use_psum_layout, "use_psum_layout")
+        packed = (sf_k + num_groups * 3) // 4          # three tail slots per group at most
+    out = torch.empty((packed, mn), dtype=torch.int, device=sf.device)
+    if packed:
+        check(lib.dg_pack_k_grouped_fp32_into_ue8m0(sf.data_ptr(), out.data_ptr(), grouped_layout.data_ptr(), num_groups, mn, sf_k,
+                                                    packed, gran_k, int(use_psum_layout), _stream()))
+    return out
+
+
+def transform_k_grouped_sf_into_required_layout(sf, ks_cpu, grouped_layout, recipe, k_alignment: int, use_psum_layout: bool):
+    """csrc/apis/layout.hpp:89-116, for sm_100: FP32 is packed; pre-packed int32 is accepted for gran_k 32 only."""
+    _require(sf.dim() == 2, "sf.dim() == 2")
+    _require(recipe[0] == 1 and recipe[1] == 1, "std::get<0>(recipe) == 1 and std::get<1>(recipe) == 1")
+    gran_k = recipe[2]
+    _require(gran_k in (32, 128) and k_alignment % 128 == 0, "(gran_k == 32 or gran_k == 128) and k_alignment % 128 == 0")
+    if sf.dtype == torch.float:
+        return get_k_grouped_mn_major_tma_aligned_packed_ue8m0_tensor(sf, grouped_layout, ks_cpu, gran_k, k_alignment, use_psum_layout)
+    if sf.dtype == torch.int and gran_k == 32:
+        _require(sf.is_contiguous() and sf.size(1) % 4 == 0, "k-grouped packed scales: contiguous [packed_sf_k, mn], mn % 4 == 0")
+        if ks_cpu:
+            _require(sf.size(0) >= sum(ceil_div(k_i, gran_k * 4) for k_i in ks_cpu), "packed_sf_k >= sum(ceil_div(k_i, gran_k * 4))")
+        return sf
+    raise RuntimeError("Unknown cases")
+
+
+def k_grouped_fp8_gemm_tn_contiguous(a, b, d, ks_cpu, grouped_layout, c=None, recipe=(1, 1, 128), compiled_dims: str = "mn",
+                                     use_psum_layout: bool = False, epilogue=None) -> None:
+    """D[g] = C[g] + A[slice g]^T @ B[slice g] for every group g, with A [sum_k, M], B [sum_k, N] (e4m3, contiguous) and
+    D [G, M, N] FP32 or BF16: the weight-gradient GEMM of a mixture of experts (csrc/apis/gemm.hpp:320-372).
+    grouped_layout (device int32 [G]) holds the slices' lengths (multiples of the contiguous-layout alignment) or, with
+    use_psum_layout, the elements where they end; padding rows of A and B must be zero."""
+    (a_data, a_sf), (b_data, b_sf) = a, b
+    recipe = tuple(recipe)
+    _require(recipe[0] == 1 and recipe[1] == 1, "std::get<0>(recipe) == 1 and std::get<1>(recipe) == 1")
+    gran_k, k_alignment = recipe[2], get_mk_alignment_for_contiguous_layout()
+    _require(gran_k in (32, 128), "gran_k == 32 or gran_k == 128")
+    _require(k_alignment % 128 == 0, "k_alignment % 128 == 0")
+    _require(d.dim() == 3 and a_data.dim() == 2 and b_data.dim() == 2, "t.dim() == N")
+    num_groups, m, n = d.shape
+    sum_k = _k_grouped_sizes(ks_cpu, grouped_layout, num_groups, use_psum_layout, k_alignment, a_data.size(0))
+    _require(a_data.dtype == torch.float8_e4m3fn and b_data.dtype == torch.float8_e4m3fn, "a, b: float8_e4m3fn")
+    _require(m == a_data.size(1) and n == b_data.size(1) and sum_k == a_data.size(0) == b_data.size(0),
+             "m == m_ and n == n_ and sum_k == sum_k_ and sum_k == sum_k__")
+    _require(a_data.is_contiguous() and b_data.is_contiguous() and d.is_contiguous(), "a.first.is_contiguous()")
+    _require(c is None or c.is_contiguous(), "not c.has_value() or c.value().is_contiguous()")
+    _require(d.dtype in (torch.bfloat16, torch.float), "d.scalar_type() == torch::kBFloat16 or d.scalar_type() == torch::kFloat")
+    _require(_resolve_alpha(None, epilogue) is None, "k-grouped GEMMs take the Identity epilogue only")
+    # early_return (gemm.hpp:17-53)
+    if m == 0 or n == 0:
+        return
+    is_cd_same = c is not None and c.data_ptr() == d.data_ptr()
+    if c is not None:
+        _require(d.dtype == c.dtype and c.shape == d.shape, "d.scalar_type() == c.value().scalar_type()")
+    if sum_k == 0:
+        if not is_cd_same:
+            d.copy_(c) if c is not None else d.zero_()
+        return
+    if c is not None and not is_cd_same:
+        d.copy_(c)
+    sfa = transform_k_grouped_sf_into_required_layout(a_sf, ks_cpu, grouped_layout, recipe, k_alignment, use_psum_layout)
+    sfb = transform_k_grouped_sf_into_required_layout(b_sf, ks_cpu, grouped_layout, recipe, k_alignment, use_psum_layout)
+    args = GemmArgs()
+    args.a, args.sfa, args.b, args.sfb, args.d = a_data.data_ptr(), sfa.data_ptr(), b_data.data_ptr(), sfb.data_ptr(), d.data_ptr()
+    args.m, args.n, args.k, args.num_groups = m, n, sum_k, num_groups
+    args.a_dtype = args.b_dtype = _lib.DG_FP8_E4M3
+    args.d_dtype = _d_dtype(d)
+    args.major_a = args.major_b = _lib.DG_MAJOR_MN
+    args.lda, args.ldb, args.ldd = m, n, n
+    args.sfa_pitch, args.sfb_pitch = m, n
+    args.gran_k_a = args.gran_k_b = gran_k
+    args.accumulate = int(c is not None)
+    args.alpha = 1.0
+    args.grouped_layout = grouped_layout.data_ptr()
+    args.use_psum_layout = int(use_psum_layout)
+    args.stream = _stream()
+    check(lib.dg_k_grouped_fp8_gemm_contiguous(C.byref(args)))
 
 
 def _t(x):

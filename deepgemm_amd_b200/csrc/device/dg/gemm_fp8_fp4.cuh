@@ -19,7 +19,7 @@
 //
 // The configuration arrives as DG_* macros set by the host-side code generator:
 //   DG_GEMM_TYPE (0 dense, 1 m-grouped contiguous, 2 m-grouped masked, 3 m-grouped contiguous with a prefix-sum
-//   layout; DG_WRITE_PADDING for the latter), DG_M_HALVES, DG_BLOCK_N, DG_NUM_STAGES,
+//   layout; DG_WRITE_PADDING for the latter, 4 k-grouped contiguous; DG_K_PSUM for its prefix-sum form), DG_M_HALVES, DG_BLOCK_N, DG_NUM_STAGES,
 //   DG_CLUSTER, DG_A_FP4, DG_B_FP4, DG_MAJOR_A, DG_MAJOR_B (0 K-major, 1 MN-major), DG_GRAN_K_A, DG_GRAN_K_B,
 //   DG_D_FP32, DG_D_FP8, DG_ACCUMULATE, DG_RASTER_GROUP, DG_SPLIT_K.
 //
@@ -28,6 +28,12 @@
 // float8_e4m3 and the scale bytes go into a packed int32 tensor in the layout the GEMMs take for SFA (four scales per
 // word, MN-major): the same bits as a BF16 D followed by the per-token 1 x 32 cast, which is how the reference defines
 // its QuantizeToFP8 epilogue (deep_gemm/include/deep_gemm/epilogue/operators.cuh:68-92).
+//
+// k-grouped (type 4; the reference's sm100_k_grouped_fp8_gemm_1d1d, csrc/jit_kernels/impls/sm100_fp8_fp4_gemm_1d1d.hpp:325-441):
+// D[g] (+)= A[slice g of K]^T B[slice g of K] for every group g, A and B being [sum K, M] and [sum K, N] (MN-major) or
+// [M, sum K] and [N, sum K] (K-major), D [G, M, N] in FP32 or BF16, the scales one packed row per 4 * gran_k elements of
+// K with every group starting a new row.  The slices are read on the device; an empty slice gives a zero D[g]
+// (nothing, when accumulating).  Rows of a tile beyond M are stored one by one so that D[g + 1] is not touched.
 //
 // DG_SPLIT_K (dense only, for shapes with too few output tiles to fill the GPU): every output tile becomes
 // num_splits work items over slices of K, and the kernel's D is an FP32 workspace of num_splits stacked
@@ -107,6 +113,7 @@ static_assert(kMHalves == 1 || kMHalves == 2, "128 or 256 rows per CTA");
 static_assert(!(kAIsFP4 && kAMnMajor) && !(kBIsFP4 && kBMnMajor), "packed FP4 operands must be K-major");
 static_assert(!kBMnMajor || (BLOCK_N / kCluster) % 16 == 0, "an MN-major B load must start on a 16-byte boundary");
 static_assert(!kSplitK || (kGemmType == 0 && kDIsFP32 && !kAccumulate && kMHalves == 1), "split-K serves the plain dense GEMM and writes FP32 partials");
+static_assert(kGemmType != kKGrouped || (BLOCK_K == 128 && kCluster == 1 && kGranKA == kGranKB), "k-grouped: one CTA per tile, 128-element stages, one scale granularity");
 
 // Scales: a packed int32 holds 4 scales, so it spans 4 * gran_k elements of K and is fetched on every
 // (4 * gran_k / BLOCK_K)-th K-block: every 4th (8th with 64-element stages) at one scale per 128 K, every (2nd) one
@@ -294,9 +301,15 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
         sched.group_alignment = p.group_alignment;
         sched.write_padding = DG_WRITE_PADDING;
     }
+    if constexpr (kGemmType == kKGrouped) {
+        sched.group_alignment = p.group_alignment;
+        sched.k_psum = DG_K_PSUM;
+        sched.k_per_sf_row = 4 * kGranKA;
+    }
     // K-blocks [kb_begin, kb_end) of a work item: all of K unless the GEMM is split
     auto kb_begin = [&](const Tile& t) { return kSplitK ? t.split * p.kb_per_split : 0u; };
     auto kb_end = [&](const Tile& t) {
+        if constexpr (kGemmType == kKGrouped) return t.num_kb;
         if constexpr (!kSplitK) return num_k_blocks;
         const uint32_t e = (t.split + 1) * p.kb_per_split;
         return e < num_k_blocks ? e : num_k_blocks;
@@ -342,13 +355,16 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                     // Row coordinates of this CTA's part of the tile in the 2-D views of A, B and the scale tensors
                     const uint32_t a_row = tile.a_row_base + tile.m_block * TILE_M + cta_rank * CTA_M;
                     const uint32_t sfa_mn = tile.sfa_mn_base + tile.m_block * TILE_M + cta_rank * CTA_M;
-                    const uint32_t sfa_row0 = tile.sfa_group * sfa_rows_per_group;
+                    const uint32_t sfa_row0 = kGemmType == kKGrouped ? tile.sf_row_base : tile.sfa_group * sfa_rows_per_group;
+                    const uint32_t k_base = kGemmType == kKGrouped ? tile.k_base : 0u;      // first element of K of this work item
                     const uint32_t kb0 = kb_begin(tile), num_kb = kb_end(tile) - kb0, num_steps = num_passes_of(tile) * num_kb;
                     for (uint32_t it = 0; it < num_steps; ++it, advance_stage()) {
                         const auto [pass, kb] = step_of(it, kb0, num_kb);
                         const uint32_t b_group = pass == 0 ? tile.group : tile.group1;
-                        const uint32_t b_row = b_group * p.shape_n + tile.n_block * BLOCK_N + cta_rank * LOAD_BLOCK_N;
-                        const uint32_t sfb_row0 = b_group * sfb_rows_per_group;
+                        // k-grouped: B is one [N, sum K] (or [sum K, N]) matrix and the group selects the slice of K
+                        const uint32_t b_row = (kGemmType == kKGrouped ? 0u : b_group * p.shape_n) + tile.n_block * BLOCK_N + cta_rank * LOAD_BLOCK_N;
+                        const uint32_t sfb_row0 = kGemmType == kKGrouped ? tile.sf_row_base : b_group * sfb_rows_per_group;
+                        const uint32_t b_k_base = kGemmType == kKGrouped ? tile.k_base : b_group * p.shape_k;   // MN-major B: row of K
                         DG_PROF_BEGIN(prof_w);
                         if (!mbar_wait(empty_bar(stage), phase ^ 1, ctx, kRoleProducer, 1)) { ok = false; break; }
                         DG_PROF_ADD(prof_wait, prof_w);
@@ -373,19 +389,19 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                         };
                         // K-major: x = K, y = row.  MN-major: x = row (column of the stored matrix), y = K (+ the group's K offset)
                         if constexpr (!kAMnMajor) {
-                            load(smem_base + kSmemA + stage * kABytes, &tm_a, kb * BLOCK_K, a_row);      // one box of CTA_M rows
+                            load(smem_base + kSmemA + stage * kABytes, &tm_a, k_base + kb * BLOCK_K, a_row);      // one box of CTA_M rows
                         } else {
                             #pragma unroll
                             for (uint32_t h = 0; h < kMHalves; ++h)
-                                load(smem_base + kSmemA + stage * kABytes + h * BLOCK_M * BLOCK_K, &tm_a, a_row + h * BLOCK_M, kb * BLOCK_K);
+                                load(smem_base + kSmemA + stage * kABytes + h * BLOCK_M * BLOCK_K, &tm_a, a_row + h * BLOCK_M, k_base + kb * BLOCK_K);
                         }
                         if constexpr (!kBMnMajor) {
-                            load(smem_base + kSmemB + stage * kBBytes, &tm_b, kb * BLOCK_K, b_row);
+                            load(smem_base + kSmemB + stage * kBBytes, &tm_b, k_base + kb * BLOCK_K, b_row);
                         } else {
                             #pragma unroll
                             for (uint32_t i = 0; i < kBAtoms; ++i)
                                 load(smem_base + kSmemB + stage * kBBytes + i * 128 * BLOCK_K, &tm_b,
-                                     tile.n_block * BLOCK_N + cta_rank * LOAD_BLOCK_N + i * 128, b_group * p.shape_k + kb * BLOCK_K);
+                                     tile.n_block * BLOCK_N + cta_rank * LOAD_BLOCK_N + i * 128, b_k_base + kb * BLOCK_K);
                         }
                         advance_sf(kb);
                     }
@@ -421,6 +437,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                 DG_PROF_VAR(prof_full); DG_PROF_VAR(prof_tmem); DG_PROF_VAR(prof_cp); DG_PROF_VAR(prof_mma); DG_PROF_VAR(prof_commit);
                 DG_PROF_BEGIN(prof_t0);
                 while (ok && sched.next(tile)) {
+                    if (kGemmType == kKGrouped && tile.num_kb == 0) continue;      // an empty group: the epilogue writes zeros
                     // First accumulator (and barrier pair) of this tile: tiles alternate between the two, or the halves of a
                     // 256-row tile own one each
                     const uint32_t accum = tile_iter % kNumAccumStages, accum_phase = (tile_iter / kNumAccumStages) & 1;
@@ -569,6 +586,26 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
         DG_PROF_VAR(prof_wait); DG_PROF_VAR(prof_store);
         DG_PROF_BEGIN(prof_t0);
         while (ok && sched.next(tile)) {
+            if (kGemmType == kKGrouped && tile.num_kb == 0) {
+                // An empty group contributes nothing: D[g] = 0 unless the GEMM accumulates into D
+                if constexpr (!kAccumulate) {
+                    const uint32_t d_row = tile.d_row_base + tile.m_block * TILE_M + wg * BLOCK_M + row_in_tile;
+                    if (tile.m_block * TILE_M + wg * BLOCK_M + row_in_tile < p.shape_m) {
+                        uint8_t* drow = reinterpret_cast<uint8_t*>(p.d) + static_cast<size_t>(d_row) * p.ldd * kDElemBytes;
+                        #pragma unroll 4
+                        for (uint32_t c = 0; c < BLOCK_N * kDElemBytes / 16; ++c) {
+                            constexpr uint32_t kPerChunk = 16 / kDElemBytes;
+                            const uint32_t col = tile.n_block * BLOCK_N + c * kPerChunk;
+                            if (col + kPerChunk <= p.shape_n) {
+                                *reinterpret_cast<uint4*>(drow + static_cast<size_t>(col) * kDElemBytes) = make_uint4(0, 0, 0, 0);
+                            } else {
+                                for (uint32_t b = col * kDElemBytes; b < p.shape_n * kDElemBytes && b < (col + kPerChunk) * kDElemBytes; ++b) drow[b] = 0;
+                            }
+                        }
+                    }
+                }
+                continue;
+            }
             const uint32_t accum = tile_iter % kNumAccumStages + wg, accum_phase = (tile_iter / kNumAccumStages) & 1;
             ++tile_iter;
             DG_PROF_BEGIN(prof_w);
@@ -585,7 +622,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
             const uint32_t valid_rows = tile.valid_rows <= rows_before ? 0u :
                                         (tile.valid_rows - rows_before < BLOCK_M ? tile.valid_rows - rows_before : BLOCK_M);
             // (fewer than 128 only in a ragged tile of the masked and prefix-sum layouts: those rows are stored one by one)
-            const bool direct = (kGemmType == kMGroupedMasked || kGemmType == kMGroupedPsum) && valid_rows < BLOCK_M;
+            const bool direct = (kGemmType == kMGroupedMasked || kGemmType == kMGroupedPsum || kGemmType == kKGrouped) && valid_rows < BLOCK_M;
             auto release_tmem = [&]() {
                 tc_fence_before_sync();
                 if (kCluster == 1 || is_leader) mbar_arrive(tmem_empty_bar(accum));
@@ -734,7 +771,9 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                         tma_store_commit();
                     }
                 } else if (row_in_tile < valid_rows) {
-                    // Ragged tile of the masked layout: rows at or beyond the group's row count stay untouched
+                    // Ragged tile of a grouped layout: rows at or beyond the group's row count stay untouched (the masked and
+                    // prefix-sum layouts never accumulate; the k-grouped GEMM may: every element belongs to one thread of
+                    // one tile, so a plain read-add-write does)
                     if constexpr (kDIsFP8) {
                         // not reached: ragged tiles exist only in the grouped layouts
                     } else if constexpr (!kDIsFP32) {
@@ -745,7 +784,16 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                                 const uint32_t col = col0 + c * 8;
                                 uint32_t q[4];
                                 chunk(c, q);
-                                if (col + 8 <= p.shape_n) {
+                                if constexpr (kAccumulate) {
+                                    #pragma unroll
+                                    for (uint32_t e = 0; e < 8; ++e) {
+                                        if (col + e < p.shape_n) {
+                                            const float sum = __uint_as_float(static_cast<uint32_t>(drow[col + e]) << 16) +
+                                                              (e % 2 ? bf16_hi(q[e / 2]) : bf16_lo(q[e / 2]));
+                                            drow[col + e] = static_cast<unsigned short>(pack_bf16x2(sum, 0.0f) & 0xFFFFu);
+                                        }
+                                    }
+                                } else if (col + 8 <= p.shape_n) {
                                     *reinterpret_cast<uint4*>(drow + col) = make_uint4(q[0], q[1], q[2], q[3]);
                                 } else {
                                     #pragma unroll
@@ -758,7 +806,8 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                         float* drow = reinterpret_cast<float*>(p.d) + static_cast<size_t>(d_row0 + row_in_tile) * p.ldd;
                         #pragma unroll
                         for (uint32_t c = 0; c < kGroupCols; ++c)
-                            if (c < kCols && col0 + c < p.shape_n) drow[col0 + c] = __uint_as_float(v[c / 16][c % 16]);
+                            if (c < kCols && col0 + c < p.shape_n)
+                                drow[col0 + c] = (kAccumulate ? drow[col0 + c] : 0.0f) + __uint_as_float(v[c / 16][c % 16]);
                     }
                 }
             }

@@ -14,6 +14,12 @@
 //       starts at layout[g - 1] rounded up to the contiguous-layout alignment (row 0 for g = 0), so
 //       the rows in between are padding.  Walked on the device like the masked layout; same
 //       contract as scheduler/gemm.cuh:205-225.
+//   k-grouped contiguous (the weight-gradient GEMM of a mixture of experts): every group g owns a slice
+//       of K and its own [shape_m x shape_n] output D[g] = A[slice]^T B[slice]; all groups have the same
+//       (m_blocks x n_blocks) tile grid, and a tile carries the slice's first element of K, its length in
+//       K-blocks and the first packed scale row of the group.  layout[g] is the slice's length (a multiple
+//       of the alignment) or, in the prefix-sum form, the element where it ends, the next slice starting
+//       at the following multiple of the alignment (scheduler/gemm.cuh:226-250 of the reference).
 #pragma once
 
 #include <cstdint>
@@ -26,7 +32,7 @@
 
 namespace dg {
 
-enum GemmKind : uint32_t { kDense = 0, kMGroupedContiguous = 1, kMGroupedMasked = 2, kMGroupedPsum = 3 };
+enum GemmKind : uint32_t { kDense = 0, kMGroupedContiguous = 1, kMGroupedMasked = 2, kMGroupedPsum = 3, kKGrouped = 4 };
 
 struct Tile {
     uint32_t m_block;       // row block inside the group (masked) or inside A (dense / contiguous)
@@ -40,6 +46,10 @@ struct Tile {
     uint32_t valid_rows;    // rows of this tile that may be written (128 unless a ragged masked tile)
     uint32_t split;         // which slice of K this work item covers (0 unless the GEMM is split along K)
     uint32_t mn_index;      // linear index of the output tile (slot of its split-K partials and counter)
+    // k-grouped only
+    uint32_t k_base;        // first element of K of the group's slice
+    uint32_t num_kb;        // 128-element K-blocks in the slice (0: an empty group)
+    uint32_t sf_row_base;   // first packed scale row of the group
 };
 
 // Tile sizes are constructor arguments (literal constants in the kernel, which the compiler folds;
@@ -57,6 +67,9 @@ struct TileScheduler {
     // prefix-sum layout only: first row of the current group, the alignment of group starts, and whether the
     // padding rows up to the next aligned row count as writable (they are written as the product of zero rows)
     uint32_t group_start, group_alignment, write_padding;
+    // k-grouped only: first element of K and first packed scale row of the current group; whether layout holds
+    // prefix sums; elements of K per packed scale row (4 scales)
+    uint32_t k_start, sf_row_start, k_psum, k_per_sf_row;
 
     DG_HD TileScheduler(uint32_t block_m_, uint32_t block_n_, uint32_t raster_group_,
                         uint32_t shape_m_, uint32_t shape_n_, uint32_t num_groups_, const int* layout_,
@@ -64,7 +77,8 @@ struct TileScheduler {
         : kBlockM(block_m_), kRasterGroup(raster_group_), shape_m(shape_m_), num_groups(num_groups_),
           num_m_blocks((shape_m_ + block_m_ - 1) / block_m_), num_n_blocks((shape_n_ + block_n_ - 1) / block_n_),
           layout(layout_), cta(cta_), num_ctas(num_ctas_), iter(0), num_splits(num_splits_ == 0 ? 1 : num_splits_),
-          cur_group(0), group_first_tile(0), group_start(0), group_alignment(128), write_padding(0) {}
+          cur_group(0), group_first_tile(0), group_start(0), group_alignment(128), write_padding(0),
+          k_start(0), sf_row_start(0), k_psum(0), k_per_sf_row(512) {}
 
     // Linear index inside an (mb x num_n_blocks) grid -> (m, n)
     DG_HD void rasterise(uint32_t idx, uint32_t mb, uint32_t& m, uint32_t& n) const {
@@ -100,6 +114,36 @@ struct TileScheduler {
             t.valid_rows = left < kBlockM ? left : kBlockM;
             t.split = 0;
             t.mn_index = tile_id;
+            return true;
+        } else if constexpr (kKind == kKGrouped) {
+            const uint32_t blocks = num_m_blocks * num_n_blocks;
+            // Length of the current group's slice, and the length it occupies in A / B and in the scale tensor
+            auto slice = [&](uint32_t& len, uint32_t& padded) {
+                const int v = layout[cur_group];
+                const uint32_t u = v < 0 ? 0u : static_cast<uint32_t>(v);
+                len = k_psum ? (u > k_start ? u - k_start : 0u) : u;
+                padded = (len + group_alignment - 1) / group_alignment * group_alignment;
+            };
+            uint32_t len = 0, padded = 0;
+            while (true) {
+                if (cur_group >= num_groups) return false;
+                slice(len, padded);
+                if (tile_id < (cur_group + 1) * blocks) break;
+                k_start += padded;
+                sf_row_start += (padded + k_per_sf_row - 1) / k_per_sf_row;
+                ++cur_group;
+            }
+            rasterise(tile_id - cur_group * blocks, num_m_blocks, t.m_block, t.n_block);
+            t.group = t.group1 = cur_group;
+            t.a_row_base = t.sfa_mn_base = t.sfa_group = 0;
+            t.d_row_base = cur_group * shape_m;
+            const uint32_t left = shape_m - t.m_block * kBlockM;
+            t.valid_rows = left < kBlockM ? left : kBlockM;
+            t.split = 0;
+            t.mn_index = tile_id;
+            t.k_base = k_start;
+            t.num_kb = (len + 127) / 128;
+            t.sf_row_base = sf_row_start;
             return true;
         } else if constexpr (kKind == kMGroupedPsum) {
             uint32_t mb = 0, rows = 0;

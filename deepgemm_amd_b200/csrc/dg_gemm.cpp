@@ -69,16 +69,19 @@ struct Problem {
     int gran_k_a, gran_k_b;
     int expected_m;
     bool write_padding;      // prefix-sum layout: also write the padding rows of D up to the next aligned row
+    bool k_psum;             // k-grouped: grouped_layout holds prefix sums
 };
 
 int validate(int kind, const dg_gemm_args_t* a, bool need_pointers, Problem* p) {
     DG_REQUIRE(a != nullptr);
     DG_REQUIRE(kind == DG_GEMM_DENSE || kind == DG_GEMM_M_GROUPED_CONTIGUOUS || kind == DG_GEMM_M_GROUPED_MASKED ||
-               kind == DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM);
+               kind == DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM || kind == DG_GEMM_K_GROUPED_CONTIGUOUS);
+    const bool k_grouped = kind == DG_GEMM_K_GROUPED_CONTIGUOUS;
     DG_REQUIRE(a->a_dtype == DG_FP8_E4M3 || a->a_dtype == DG_FP4_E2M1_X2);
     DG_REQUIRE(a->b_dtype == DG_FP8_E4M3 || a->b_dtype == DG_FP4_E2M1_X2);
     DG_REQUIRE(a->d_dtype == DG_BF16 || a->d_dtype == DG_FP32 || a->d_dtype == DG_FP8_E4M3);
-    if (kind != DG_GEMM_DENSE) DG_REQUIRE(a->d_dtype == DG_BF16);            // gemm.hpp:209,299
+    if (kind != DG_GEMM_DENSE && !k_grouped) DG_REQUIRE(a->d_dtype == DG_BF16);            // gemm.hpp:209,299
+    if (k_grouped) DG_REQUIRE(a->d_dtype == DG_BF16 || a->d_dtype == DG_FP32);
     if (a->d_dtype == DG_FP8_E4M3) {
         // "FP8 quantization requires a direct E4M3 output" (epilogue_class.hpp:84-87); the epilogues do not compose
         DG_REQUIRE(!a->accumulate && !a->has_alpha);
@@ -90,6 +93,11 @@ int validate(int kind, const dg_gemm_args_t* a, bool need_pointers, Problem* p) 
     DG_REQUIRE(a->gran_k_b == 32 || a->gran_k_b == 128);
     if (kind == DG_GEMM_DENSE) {
         DG_REQUIRE(a->num_groups == 1);
+    } else if (k_grouped) {
+        // gemm.hpp:320-372: 1-D scales of one granularity, K slices aligned to whole K-blocks, contiguous operands
+        DG_REQUIRE(a->num_groups > 0 && a->gran_k_a == a->gran_k_b);
+        DG_REQUIRE(state().mk_alignment % 128 == 0);
+        DG_REQUIRE(!a->has_alpha);
     } else {
         DG_REQUIRE(a->n > 0 && a->k > 0 && a->num_groups > 0);                // gemm.hpp:208,296
         DG_REQUIRE(a->major_a == DG_MAJOR_K);                                 // gemm.hpp:197,285
@@ -119,6 +127,7 @@ int validate(int kind, const dg_gemm_args_t* a, bool need_pointers, Problem* p) 
     p->gran_k_a = a->gran_k_a; p->gran_k_b = a->gran_k_b;
     p->expected_m = a->expected_m;
     p->write_padding = kind == DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM && a->ensure_zero_padding != 0;
+    p->k_psum = k_grouped && a->use_psum_layout != 0;
     if (a->m == 0 || a->n == 0 || a->k == 0) return DG_OK;                    // handled by the caller (gemm.hpp:17-53)
 
     if (p->a_fp4 || p->b_fp4) DG_REQUIRE(a->k % 128 == 0);                   // runtime_utils.hpp:133-135
@@ -201,7 +210,7 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
         if (forced_cluster ? cluster != forced_cluster : !cluster_allowed(p, cluster)) continue;
         // A CTA pair multiplies all its rows with one B: in the contiguous layout every expert segment must then be a
         // whole number of pair tiles
-        if (cluster == 2 && (num_sms % 2 != 0 || p.kind == DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM ||
+        if (cluster == 2 && (num_sms % 2 != 0 || p.kind == DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM || p.kind == DG_GEMM_K_GROUPED_CONTIGUOUS ||
                              (p.kind == DG_GEMM_M_GROUPED_CONTIGUOUS && state().mk_alignment % (256 * halves) != 0))) continue;
         // 256 rows per CTA: two 128-row MMAs per K-block on one B stage; K not sliced
         if (forced_block_m ? 128 * halves != forced_block_m : (halves == 2 && p.m <= 128)) continue;
@@ -209,7 +218,7 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
         // Stages of 64 elements of K (twice as many, each half the bytes): K-major FP8 operands and unsliced K only.
         // Built and tested, but it measured 0-20 % slower than 128-element stages on every shape tried (the 64-byte
         // rows double the number of L2 requests), so it is used only on request (DG_FORCE_BLOCK_K=64).
-        if (bk != (forced_block_k ? forced_block_k : 128)) continue;
+        if (bk != (forced_block_k && p.kind != DG_GEMM_K_GROUPED_CONTIGUOUS ? forced_block_k : 128)) continue;
         if (bk == 64 && (p.a_fp4 || p.b_fp4 || p.a_mn_major || p.b_mn_major || forced_splits > 1)) continue;
         const int tile_m = 128 * cluster * halves, units = num_sms / cluster;
         int64_t m_blocks;
@@ -219,6 +228,8 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
             m_blocks = static_cast<int64_t>(p.groups) * ceil_div(std::min(p.expected_m, p.m), tile_m);
         else if (p.kind == DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM)   // every group may end with a partly filled tile
             m_blocks = ceil_div(p.m, tile_m) + p.groups / 2;
+        else if (p.kind == DG_GEMM_K_GROUPED_CONTIGUOUS)        // every group has the full tile grid and a share of K
+            m_blocks = static_cast<int64_t>(p.groups) * ceil_div(p.m, tile_m);
         else
             m_blocks = ceil_div(p.m, tile_m);
         // Slicing K: dense GEMMs whose output has too few tiles to occupy the GPU.  What matters is the bytes a CTA has
@@ -244,13 +255,16 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
                 const int64_t tiles = mn_tiles * splits;
                 const int64_t waves = ceil_div<int64_t>(tiles, units);
                 // The pipeline: as deep as shared memory allows, but no deeper than the K-blocks of two work items
-                const int64_t item_kb = ceil_div<int64_t>(std::min<int64_t>(p.k, static_cast<int64_t>(kb_per) * 128), bk);
+                // (k-grouped: the groups share K; an average slice stands for all of them)
+                const int64_t item_k = p.kind == DG_GEMM_K_GROUPED_CONTIGUOUS ? std::max<int64_t>(128, p.k / p.groups)
+                                                                               : std::min<int64_t>(p.k, static_cast<int64_t>(kb_per) * 128);
+                const int64_t item_kb = ceil_div<int64_t>(item_k, bk);
                 int max_stages = static_cast<int>(std::max<int64_t>(2, std::min<int64_t>(32, 2 * item_kb)));
                 if (forced_stages >= 2) max_stages = std::min(max_stages, forced_stages);
                 GemmLayout lay{128u * halves, static_cast<uint32_t>(bn), static_cast<uint32_t>(bk), 2,
                                static_cast<uint32_t>(splits > 1 ? 4 : d_elem), static_cast<uint32_t>(cluster),
                                p.b_mn_major ? 1u : 0u, static_cast<uint32_t>(p.gran_k_a), static_cast<uint32_t>(p.gran_k_b), 0u};
-                lay = fit_stages(lay, item_kb, max_stages);
+                lay = fit_stages(lay, p.kind == DG_GEMM_K_GROUPED_CONTIGUOUS ? 0 : item_kb, max_stages);   // slices may be one K-block
                 if (lay.num_stages == 0 || lay.tmem_cols_used() > kTmemCapacityCols) continue;
                 // Cycles per pipeline stage: the MMAs; shared memory, which moved ~150 B per cycle in every configuration
                 // measured, TMA writes and tensor-core reads together (a stage is written once, its A rows are read once
@@ -310,7 +324,8 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
 // The layout the kernel of a configuration uses (same arithmetic as choose_config)
 GemmLayout layout_of(const Problem& p, const dg_gemm_config_t& cfg) {
     const bool split = cfg.num_splits > 1;
-    const int64_t item_kb = ceil_div<int64_t>(std::min<int64_t>(p.k, static_cast<int64_t>(cfg.kb_per_split) * 128), cfg.block_k);
+    const int64_t item_kb = p.kind == DG_GEMM_K_GROUPED_CONTIGUOUS ? 0 :
+                            ceil_div<int64_t>(std::min<int64_t>(p.k, static_cast<int64_t>(cfg.kb_per_split) * 128), cfg.block_k);
     GemmLayout lay{static_cast<uint32_t>(cfg.block_m), static_cast<uint32_t>(cfg.block_n), static_cast<uint32_t>(cfg.block_k),
                    static_cast<uint32_t>(cfg.num_stages), static_cast<uint32_t>((p.d_fp32 || split) ? 4 : (p.d_fp8 ? 1 : 2)),
                    static_cast<uint32_t>(cfg.cluster_size), p.b_mn_major ? 1u : 0u,
@@ -341,6 +356,7 @@ std::string generate_source(const Problem& p, const dg_gemm_config_t& cfg) {
       << "#define DG_RASTER_GROUP " << cfg.raster_group << "\n"
       << "#define DG_SPLIT_K " << (cfg.num_splits > 1 ? 1 : 0) << "\n"
       << "#define DG_WRITE_PADDING " << (p.write_padding ? 1 : 0) << "\n"
+      << "#define DG_K_PSUM " << (p.k_psum ? 1 : 0) << "\n"
       << "#define DG_PROFILE " << env_int("PROFILE") << "\n"
       << "#include <dg/gemm_fp8_fp4.cuh>\n";
     return s.str();
@@ -369,8 +385,8 @@ int encode_2d(CUtensorMap* map, CUtensorMapDataType dtype, const void* base, uin
 }
 
 int get_kernel(const Problem& p, const dg_gemm_config_t& cfg, dg_kernel_t* kernel) {
-    static const char* names[4] = {"gemm_fp8_fp4_dense", "gemm_fp8_fp4_m_grouped_contiguous", "gemm_fp8_fp4_m_grouped_masked",
-                                   "gemm_fp8_fp4_m_grouped_contiguous_psum"};
+    static const char* names[5] = {"gemm_fp8_fp4_dense", "gemm_fp8_fp4_m_grouped_contiguous", "gemm_fp8_fp4_m_grouped_masked",
+                                   "gemm_fp8_fp4_m_grouped_contiguous_psum", "gemm_fp8_fp4_k_grouped_contiguous"};
     const std::string src = generate_source(p, cfg);
     return dg_jit_compile(names[p.kind], "dg_gemm_fp8_fp4", src.c_str(), "", kernel);
 }
@@ -416,11 +432,14 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
     } else if (split && (rc = split_workspace(workspace_bytes, &workspace)) != DG_OK) {
         return rc;
     }
+    const bool k_grouped = kind == DG_GEMM_K_GROUPED_CONTIGUOUS;
     const uint64_t a_rows = kind == DG_GEMM_M_GROUPED_MASKED ? static_cast<uint64_t>(p.groups) * p.m : p.m;
-    const uint64_t b_rows = static_cast<uint64_t>(p.groups) * p.n;
+    // k-grouped: one B for all groups (the group selects a slice of K); every group starts a new packed scale row
+    const uint64_t b_rows = k_grouped ? p.n : static_cast<uint64_t>(p.groups) * p.n;
+    const uint64_t b_k_rows = k_grouped ? p.k : static_cast<uint64_t>(p.groups) * p.k;
     const uint64_t sfa_k = ceil_div(p.k, p.gran_k_a * 4), sfb_k = ceil_div(p.k, p.gran_k_b * 4);
-    const uint64_t sfa_rows = kind == DG_GEMM_M_GROUPED_MASKED ? sfa_k * p.groups : sfa_k;
-    const uint64_t sfb_rows = sfb_k * p.groups;
+    const uint64_t sfa_rows = kind == DG_GEMM_M_GROUPED_MASKED ? sfa_k * p.groups : (k_grouped ? sfa_k + p.groups : sfa_k);
+    const uint64_t sfb_rows = k_grouped ? sfb_k + p.groups : sfb_k * p.groups;
 
     CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb, tm_d, tm_d_full;
     // K-major A, B: K (elements) x rows; box = one K-block (128 or 64 elements) x the tile's rows, swizzled over its width.
@@ -437,7 +456,7 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
         if ((rc = encode_2d(&tm_b, p.b_fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, a->b,
                             p.k, b_rows, a->ldb, cfg.block_k, cfg.block_n / cfg.cluster_size, k_major_swizzle)) != DG_OK) return rc;
     } else {
-        if ((rc = encode_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->b, p.n, static_cast<uint64_t>(p.groups) * p.k, a->ldb, 128, 128,
+        if ((rc = encode_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->b, p.n, b_k_rows, a->ldb, 128, 128,
                             CU_TENSOR_MAP_SWIZZLE_128B)) != DG_OK) return rc;
     }
     // Scales: MN (int32) x packed-K rows; the MN extent is the true row count, so reads past it are zero-filled
@@ -452,7 +471,8 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
     const CUtensorMapDataType d_type = kernel_d_fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 :
                                        p.d_fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     void* d_base = split ? static_cast<void*>(workspace) : a->d;
-    const uint64_t d_rows = split ? static_cast<uint64_t>(cfg.num_splits) * panel_rows : a_rows;
+    const uint64_t d_rows = split ? static_cast<uint64_t>(cfg.num_splits) * panel_rows :
+                            (k_grouped ? static_cast<uint64_t>(p.groups) * p.m : a_rows);
     const uint64_t d_pitch_bytes = split ? ld_ws * 4 : a->ldd * (p.d_fp32 ? 4 : (p.d_fp8 ? 1 : 2));
     if ((rc = encode_2d(&tm_d, d_type, d_base, p.n, d_rows, d_pitch_bytes, lay.store_cols(), 128, d_swizzle)) != DG_OK) return rc;
     if ((rc = encode_2d(&tm_d_full, d_type, d_base, p.n, d_rows, d_pitch_bytes, lay.group_cols(), 128,
@@ -527,6 +547,7 @@ int dg_m_grouped_fp8_fp4_gemm_contiguous(const dg_gemm_args_t* args) {
     return run_gemm(psum ? DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM : DG_GEMM_M_GROUPED_CONTIGUOUS, args);
 }
 int dg_m_grouped_fp8_fp4_gemm_masked(const dg_gemm_args_t* args) { return run_gemm(DG_GEMM_M_GROUPED_MASKED, args); }
+int dg_k_grouped_fp8_gemm_contiguous(const dg_gemm_args_t* args) { return run_gemm(DG_GEMM_K_GROUPED_CONTIGUOUS, args); }
 
 int dg_get_gemm_config(int kind, const dg_gemm_args_t* args, dg_gemm_config_t* config) {
     DG_REQUIRE(config != nullptr);

@@ -72,6 +72,45 @@ pack_fp32_into_ue8m0_kernel(const float* __restrict__ sf, int32_t* __restrict__ 
     }
 }
 
+// K-grouped scales: input FP32 [sf_rows, mn] contiguous (one row per gran_k elements of K, groups one after another,
+// each covering its padded slice), output int32 [packed_rows, mn]: four input rows per word, every group starting a
+// new output row, the unused slots of a group's last row zero.  `layout` holds the slices' lengths or, with `psum`,
+// their prefix sums (slices then start on multiples of `alignment`).  One CTA: one output row x 256 columns; every
+// thread finds the row's group by walking the layout (at most a few hundred entries).
+__global__ void __launch_bounds__(256)
+pack_k_grouped_fp32_into_ue8m0_kernel(const float* __restrict__ sf, int32_t* __restrict__ out, const int* __restrict__ layout,
+                                      int num_groups, int mn, int sf_rows, int gran_k, int alignment, int psum, int* status) {
+    const int out_row = blockIdx.y, col = blockIdx.x * 256 + threadIdx.x;
+    int k_start = 0, in_row0 = 0, out_row0 = 0, group_rows = 0;
+    bool found = false;
+    for (int g = 0; g < num_groups && !found; ++g) {
+        const int v = max(layout[g], 0);
+        const int len = psum ? max(v - k_start, 0) : v;
+        const int padded = (len + alignment - 1) / alignment * alignment;
+        group_rows = padded / gran_k;
+        const int packed = (group_rows + 3) / 4;
+        if (out_row < out_row0 + packed) {
+            found = true;
+        } else {
+            k_start += padded; in_row0 += group_rows; out_row0 += packed;
+        }
+    }
+    if (col >= mn) return;
+    uint32_t word = 0;
+    if (found) {
+        #pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int r = (out_row - out_row0) * 4 + j;
+            if (r < group_rows && in_row0 + r < sf_rows) {
+                const uint32_t bits = __float_as_uint(sf[static_cast<int64_t>(in_row0 + r) * mn + col]);
+                if ((bits & 0x807FFFFFu) != 0 && status != nullptr) atomicCAS(status, 0, static_cast<int>(0x89000000u));
+                word |= (bits >> 23) << (8 * j);
+            }
+        }
+    }
+    out[static_cast<int64_t>(out_row) * mn + col] = static_cast<int32_t>(word);     // rows past the last group: zero
+}
+
 __global__ void __launch_bounds__(256)
 transpose_fp32_kernel(const float* __restrict__ sf, float* __restrict__ out, int mn, int sf_k, int aligned_mn,
                       int64_t sg, int64_t sm, int64_t sk) {
@@ -132,6 +171,24 @@ int dg_pack_fp32_into_ue8m0_psum(const float* sf, int32_t* out, int mn, int sf_k
     pack_fp32_into_ue8m0_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         sf, out, mn, sf_k, packed_k, aligned_mn, 1, 0, in_stride_mn, in_stride_k, state().status_device,
         psum_layout, num_psum_groups, state().mk_alignment);
+    DG_CUDA_RT(cudaGetLastError());
+    return DG_OK;
+}
+
+int dg_pack_k_grouped_fp32_into_ue8m0(const float* sf, int32_t* out, const int32_t* grouped_layout, int num_groups,
+                                      int mn, int sf_rows, int packed_rows, int gran_k, int use_psum_layout, void* stream) {
+    DG_REQUIRE(num_groups > 0 && mn >= 0 && sf_rows >= 0 && packed_rows >= 0);
+    DG_REQUIRE(gran_k == 32 || gran_k == 128);
+    DG_REQUIRE(mn % 4 == 0);                                              // smxx_layout.hpp:229
+    DG_REQUIRE(state().mk_alignment % 128 == 0);
+    if (mn == 0 || packed_rows == 0) return DG_OK;
+    DG_REQUIRE(sf != nullptr && out != nullptr && grouped_layout != nullptr);
+    DG_REQUIRE(packed_rows <= 65535);
+    int rc = ensure_status_word();
+    if (rc != DG_OK) return rc;
+    const dim3 grid(ceil_div(mn, 256), packed_rows, 1);
+    pack_k_grouped_fp32_into_ue8m0_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        sf, out, grouped_layout, num_groups, mn, sf_rows, gran_k, state().mk_alignment, use_psum_layout != 0, state().status_device);
     DG_CUDA_RT(cudaGetLastError());
     return DG_OK;
 }

@@ -46,7 +46,8 @@ typedef enum dg_gemm_kind {
     DG_GEMM_DENSE = 0,
     DG_GEMM_M_GROUPED_CONTIGUOUS = 1,
     DG_GEMM_M_GROUPED_MASKED = 2,
-    DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM = 3     /* the contiguous layout with use_psum_layout (for dg_get_gemm_config / dg_gemm_precompile) */
+    DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM = 3,    /* the contiguous layout with use_psum_layout (for dg_get_gemm_config / dg_gemm_precompile) */
+    DG_GEMM_K_GROUPED_CONTIGUOUS = 4
 } dg_gemm_kind_t;
 
 DG_API const char* dg_last_error(void);
@@ -92,6 +93,16 @@ DG_API int dg_pack_fp32_into_ue8m0(const float* sf_device, int32_t* out_device,
 DG_API int dg_pack_fp32_into_ue8m0_psum(const float* sf_device, int32_t* out_device, int mn, int sf_k,
                                         int64_t in_stride_mn, int64_t in_stride_k,
                                         const int32_t* psum_layout_device, int num_psum_groups, void* stream);
+
+/* K-grouped scales (get_k_grouped_mn_major_tma_aligned_packed_ue8m0_tensor, smxx_layout.hpp:218-283; kernel
+ * pack_fp32_into_ue8m0, impls/smxx_layout.cuh:195-267): FP32 [sf_rows, mn] contiguous, one row per gran_k elements of K,
+ * the groups one after another, each covering its slice padded to the contiguous-layout alignment -> int32
+ * [packed_rows, mn] contiguous: four rows per word, every group starting a new packed row, unused slots zero.
+ * `grouped_layout_device` as in dg_k_grouped_fp8_gemm_contiguous.  packed_rows: sum over groups of
+ * ceil(padded slice / (4 gran_k)); any larger value is allowed and the extra rows are written as zero. */
+DG_API int dg_pack_k_grouped_fp32_into_ue8m0(const float* sf_device, int32_t* out_device, const int32_t* grouped_layout_device,
+                                             int num_groups, int mn, int sf_rows, int packed_rows, int gran_k,
+                                             int use_psum_layout, void* stream);
 
 /* FP32 scales [num_groups, mn, sf_k] (any strides) -> same values MN-major with pitch align(mn,4):
  * get_mn_major_tma_aligned_tensor (smxx_layout.hpp:60-106; kernel smxx_layout.cuh:13).
@@ -167,6 +178,19 @@ DG_API int dg_fp8_fp4_gemm(const dg_gemm_args_t* args);
 DG_API int dg_m_grouped_fp8_fp4_gemm_contiguous(const dg_gemm_args_t* args);
 /* m_grouped_fp8_fp4_gemm_nt_masked (gemm.hpp:269-318). */
 DG_API int dg_m_grouped_fp8_fp4_gemm_masked(const dg_gemm_args_t* args);
+/* k_grouped_fp8_gemm_tn_contiguous (gemm.hpp:320-372; the weight-gradient GEMM of a mixture of experts):
+ * D[g] (+)= A[slice g of K]^T B[slice g of K] for g < num_groups, with
+ *   a, b : float8_e4m3 [k, m] / [k, n] (major_* = DG_MAJOR_MN, lda = m, the reference's layout) or [m, k] / [n, k]
+ *          (DG_MAJOR_K); k = the sum of the (padded) slices; padding rows must be zero;
+ *   d    : [num_groups, m, n] BF16 or FP32, row pitch ldd, groups m rows apart; accumulate != 0 adds into it;
+ *   grouped_layout : int32[num_groups] on the device: each slice's length, a multiple of the contiguous-layout
+ *          alignment, or with use_psum_layout the element where it ends, the next slice starting at the following
+ *          multiple of the alignment (docs/scaling-factor-format.md 5.1);
+ *   sfa, sfb : packed UE8M0 int32 [rows, m] / [rows, n], MN contiguous (pitch sf*_pitch >= mn, mn % 4 == 0), one row per
+ *          4 * gran_k elements of K, every group starting a new row (docs/scaling-factor-format.md 5.2;
+ *          dg_pack_k_grouped_fp32_into_ue8m0 produces it); gran_k_a == gran_k_b.
+ * An empty slice gives D[g] = 0 (leaves it unchanged when accumulating). */
+DG_API int dg_k_grouped_fp8_gemm_contiguous(const dg_gemm_args_t* args);
 
 /* Same operation and arguments as dg_fp8_fp4_gemm, for callers that cannot allocate device memory (inside a stream
  * capture, on a thread that must not block on the allocator, or in a process that freezes its memory footprint after

@@ -26,4 +26,5 @@ from .layout import (  # noqa: F401
 from .gemm import (  # noqa: F401
     calc_diff, dequant_gemm_nt, m_grouped_contiguous_ref, m_grouped_masked_ref,
     make_contiguous_layout, count_bytes, make_psum_layout, m_grouped_psum_ref,
+    k_grouped_slices, k_grouped_pack_sf, k_grouped_ref,
 )

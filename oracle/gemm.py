@@ -11,7 +11,7 @@ from typing import Optional, Sequence
 
 import numpy as np
 
-from .quant import align, cast_back_from_fp4, cast_back_from_fp8
+from .quant import align, cast_back_from_fp4, cast_back_from_fp8, ceil_div, e4m3_decode
 
 
 def calc_diff(x: np.ndarray, y: np.ndarray) -> float:
@@ -111,6 +111,45 @@ def m_grouped_psum_ref(a, sfa, b, sfb, ends: Sequence[int], alignment: int, gran
         if end > start:
             d[start:end] = dequant_gemm_nt(a[start:end], sfa[start:end], b[i], sfb[i], gran_k_a, gran_k_b, False, b_is_fp4)
         start = align(max(end, start), alignment)
+    return d
+
+
+def k_grouped_slices(ks: Sequence[int], alignment: int, psum: bool):
+    """(start, length, padded length) of every group's slice of K and the grouped_layout the GEMM takes
+    (tests/generators.py:551-572, docs/scaling-factor-format.md 5.1): slices start on multiples of the alignment;
+    the layout holds the padded lengths, or with ``psum`` the elements where the slices end."""
+    slices, start = [], 0
+    for k in ks:
+        padded = align(k, alignment)
+        slices.append((start, int(k), padded))
+        start += padded
+    layout = [s0 + k for s0, k, _ in slices] if psum else [p for _, _, p in slices]
+    return slices, np.asarray(layout, dtype=np.int32), start
+
+
+def k_grouped_pack_sf(sf_rows: np.ndarray, slices, gran_k: int) -> np.ndarray:
+    """FP32 power-of-two scales [sum of padded_k / gran_k, mn] -> packed UE8M0 [sum ceil(rows_g / 4), mn] uint32, every
+    group starting a new packed row, unused slots zero (docs/scaling-factor-format.md 5.2, 7.4)."""
+    out, row = [], 0
+    for _, _, padded in slices:
+        rows = padded // gran_k
+        block = np.zeros((ceil_div(rows, 4) * 4, sf_rows.shape[1]), dtype=np.uint32)
+        block[:rows] = sf_rows[row:row + rows].view(np.uint32) >> 23
+        block = block.reshape(-1, 4, sf_rows.shape[1])
+        out.append(block[:, 0] | (block[:, 1] << 8) | (block[:, 2] << 16) | (block[:, 3] << 24))
+        row += rows
+    return np.concatenate(out, axis=0) if out else np.zeros((0, sf_rows.shape[1]), dtype=np.uint32)
+
+
+def k_grouped_ref(a_q, sfa, b_q, sfb, slices, gran_k: int = 128) -> np.ndarray:
+    """D[g] = (dequantised A[slice g])^T (dequantised B[slice g]) in float32 (tests/generators.py:583-587).
+    a_q [sum_k, m] e4m3 bytes with scales sfa [sum_k / gran_k, m] (one per gran_k elements of K and column)."""
+    a = e4m3_decode(a_q) * np.repeat(sfa, gran_k, axis=0)[:a_q.shape[0]]
+    b = e4m3_decode(b_q) * np.repeat(sfb, gran_k, axis=0)[:b_q.shape[0]]
+    d = np.zeros((len(slices), a_q.shape[1], b_q.shape[1]), dtype=np.float32)
+    for g, (s0, k, _) in enumerate(slices):
+        if k:
+            d[g] = a[s0:s0 + k].T.astype(np.float32) @ b[s0:s0 + k].astype(np.float32)
     return d
 
 

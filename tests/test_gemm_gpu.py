@@ -468,6 +468,62 @@ def test_m_grouped_contiguous_nn_takes_mn_major_weights():
 
 
 # ---------------------------------------------------------------------------------------------------
+# k-grouped contiguous (weight gradients of a mixture of experts)
+# ---------------------------------------------------------------------------------------------------
+def _k_grouped_operand(sum_k, mn, slices, gran_k, seed):
+    """[sum_k, mn] operand, zero outside the slices, quantised 1 x gran_k along K (tests/generators.py:576-607)."""
+    x = np.zeros((sum_k, mn), dtype=np.float32)
+    for i, (s0, k, _) in enumerate(slices):
+        x[s0:s0 + k] = seeded_bf16((k, mn), seed + i)
+    q_t, sf_t = oracle.per_token_cast_to_fp8(np.ascontiguousarray(x.T), True, gran_k)        # [mn, sum_k], [mn, sum_k / gran_k]
+    return np.ascontiguousarray(q_t.T), np.ascontiguousarray(sf_t.T)
+
+
+@pytest.mark.parametrize("m,n,ks,psum", [(256, 384, (256, 0, 384, 128), False), (208, 304, (128, 512), False),
+                                         (256, 240, (200, 0, 300, 128, 1), True), (128, 128, (0, 0), True)])
+@pytest.mark.parametrize("gran_k", [128, 32])
+@pytest.mark.parametrize("out_dtype,accumulate", [(torch.float, True), (torch.float, False), (torch.bfloat16, False), (torch.bfloat16, True)])
+def test_k_grouped_contiguous_matches_oracle(m, n, ks, psum, gran_k, out_dtype, accumulate):
+    alignment = 128
+    slices, layout, sum_k = oracle.k_grouped_slices(ks, alignment, psum)
+    g = len(ks)
+    if sum_k == 0:
+        sum_k, slices = 128, slices                                  # operands cannot be empty tensors; every slice stays empty
+        layout = np.zeros(g, dtype=np.int32)
+    qa, sfa = _k_grouped_operand(sum_k, m, slices, gran_k, 60)
+    qb, sfb = _k_grouped_operand(sum_k, n, slices, gran_k, 70)
+    ref = oracle.k_grouped_ref(qa, sfa, qb, sfb, slices, gran_k)
+    c0 = seeded_bf16((g, m, n), 80, 32.0)
+    if accumulate:
+        ref = ref + c0
+    d = torch.from_numpy(c0).cuda().to(out_dtype) if accumulate else torch.full((g, m, n), float("nan"), dtype=out_dtype, device="cuda")
+    layout_dev = torch.from_numpy(layout).cuda()
+    ks_cpu = None if psum else [p for _, _, p in slices] if sum(ks) else [0] * g
+    a = (fp8_cuda(qa), torch.from_numpy(sfa).cuda()); b = (fp8_cuda(qb), torch.from_numpy(sfb).cuda())
+    # the scale packing on its own, against the oracle
+    if sum(ks):
+        packed = dg.get_k_grouped_mn_major_tma_aligned_packed_ue8m0_tensor(a[1], layout_dev, ks_cpu, gran_k, alignment, psum)
+        want = oracle.k_grouped_pack_sf(sfa, slices, gran_k)
+        assert np.array_equal(packed.cpu().numpy().view(np.uint32)[:want.shape[0]], want)
+        assert (packed.cpu().numpy()[want.shape[0]:] == 0).all()
+    dg.reset_kernel_status()
+    dg.k_grouped_fp8_gemm_tn_contiguous(a, b, d, ks_cpu, layout_dev, c=d if accumulate else None, recipe=(1, 1, gran_k),
+                                        use_psum_layout=psum)
+    assert dg.kernel_status() == 0
+    out = d.float().cpu().numpy()
+    assert not np.isnan(out).any()
+    tol = 1e-9 if out_dtype == torch.float else 1e-5
+    for i, (_, k, _) in enumerate(slices):
+        want = ref[i] if out_dtype == torch.float else oracle.bf16_round(ref[i])
+        if k == 0 and not accumulate:
+            assert (out[i] == 0).all()
+        elif out_dtype == torch.float:
+            assert oracle.calc_diff(out[i], want) < tol and np.allclose(out[i], want, rtol=2e-5, atol=2e-3), (i, diff_report(out[i], want))
+        else:
+            assert oracle.calc_diff(out[i], want) < 1e-4, (i, diff_report(out[i], want))
+
+
+# ---------------------------------------------------------------------------------------------------
 # m-grouped masked
 # ---------------------------------------------------------------------------------------------------
 def _masked_case(counts, max_m, n, k):
