@@ -15,7 +15,7 @@ DG_OK = 0
 DG_FP8_E4M3, DG_FP4_E2M1_X2, DG_BF16, DG_FP32 = 0, 1, 2, 3
 DG_MAJOR_K, DG_MAJOR_MN = 0, 1
 DG_GEMM_DENSE, DG_GEMM_M_GROUPED_CONTIGUOUS, DG_GEMM_M_GROUPED_MASKED, DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM = 0, 1, 2, 3
-DG_GEMM_K_GROUPED_CONTIGUOUS = 4
+DG_GEMM_K_GROUPED_CONTIGUOUS, DG_GEMM_BATCHED = 4, 5
 
 
 class GemmArgs(C.Structure):
@@ -31,6 +31,7 @@ class GemmArgs(C.Structure):
         ("grouped_layout", C.c_void_p), ("expected_m", C.c_int32), ("stream", C.c_void_p),
         ("use_psum_layout", C.c_int32), ("ensure_zero_padding", C.c_int32),
         ("sfd", C.c_void_p), ("sfd_pitch", C.c_int64),
+        ("batch_stride_a", C.c_int64), ("batch_stride_b", C.c_int64), ("batch_stride_d", C.c_int64),
     ]
 
 
@@ -73,6 +74,7 @@ SIGNATURES = {
     "dg_m_grouped_fp8_fp4_gemm_contiguous": (C.c_int, [C.POINTER(GemmArgs)]),
     "dg_m_grouped_fp8_fp4_gemm_masked": (C.c_int, [C.POINTER(GemmArgs)]),
     "dg_k_grouped_fp8_gemm_contiguous": (C.c_int, [C.POINTER(GemmArgs)]),
+    "dg_fp8_bmm": (C.c_int, [C.POINTER(GemmArgs)]),
     "dg_gemm_precompile": (C.c_int, [C.c_int, C.POINTER(GemmArgs)]),
     "dg_get_gemm_config": (C.c_int, [C.c_int, C.POINTER(GemmArgs), C.POINTER(GemmConfig)]),
     "dg_enumerate_tiles": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,

@@ -516,6 +516,76 @@ def k_grouped_fp8_gemm_tn_contiguous(a, b, d, ks_cpu, grouped_layout, c=None, re
     check(lib.dg_k_grouped_fp8_gemm_contiguous(C.byref(args)))
 
 
+# ------------------------------------------------------------------------------------------------
+# Batched GEMM and fp8_einsum (csrc/apis/einsum.hpp:183-298)
+# ------------------------------------------------------------------------------------------------
+def _fp8_bmm(a, sfa, b, sfb, d, c, recipe, epilogue) -> None:
+    """D[i] = C[i] + A[i] @ B[i]^T for [B, M, K] x [B, N, K] (any batch strides); d is a tensor or an (e4m3, sfd) pair."""
+    from .epilogue import FP8Quantization
+    if isinstance(d, (tuple, list)):
+        _require(epilogue is None, "The FP8 output pair supports no other epilogue")
+        d, epilogue = d[0], FP8Quantization(d[1])
+    _require(a.stride(-1) == 1 or a.stride(-2) == 1, "a.stride(-1) == 1 or a.stride(-2) == 1")
+    _require(b.stride(-1) == 1 or b.stride(-2) == 1, "b.stride(-1) == 1 or b.stride(-2) == 1")
+    _require(d.stride(-1) == 1, "d_tensor.stride(-1) == 1")
+    major_a = _lib.DG_MAJOR_K if a.stride(-1) == 1 else _lib.DG_MAJOR_MN
+    major_b = _lib.DG_MAJOR_K if b.stride(-1) == 1 else _lib.DG_MAJOR_MN
+    _require(a.dim() == 3 and b.dim() == 3 and d.dim() == 3, "t.dim() == N")
+    batch, m, k = a.shape
+    batch_, n, k_ = b.shape
+    _require(batch == batch_ == d.size(0), "batch_size == batch_size_ and batch_size == batch_size__")
+    _require(m == d.size(1) and n == d.size(2) and k == k_, "m == m_ and n == n_ and k == k_")
+    _require(a.dtype == torch.float8_e4m3fn and b.dtype == torch.float8_e4m3fn, "a.scalar_type() == torch::kFloat8_e4m3fn")
+    sfd = epilogue.sfd if isinstance(epilogue, FP8Quantization) else None
+    if sfd is not None:
+        # the scales are those of a per-token cast of D viewed as [m, batch * n] (einsum.hpp:219-228)
+        _require(c is None and d.dtype == torch.float8_e4m3fn, "FP8 quantization requires a direct E4M3 output")
+        _require(d.stride(0) == n and n % 128 == 0, "d_tensor.stride(0) == n and n % 128 == 0")
+        _check_sf_layout(sfd, m, batch * n, 1, 32, None, tma_stride_check=True, type_check=torch.int)
+    else:
+        _require(d.dtype in (torch.bfloat16, torch.float), "d.scalar_type() == torch::kBFloat16 or d.scalar_type() == torch::kFloat")
+    if batch == 0 or m == 0 or n == 0:
+        return
+    is_cd_same = c is not None and c.data_ptr() == d.data_ptr()
+    if is_cd_same:
+        _require(c.shape == d.shape and c.stride() == d.stride(), "c->sizes() == d.sizes() and c->strides() == d.strides()")
+    if c is not None:
+        _require(d.dtype == c.dtype, "d.scalar_type() == c.value().scalar_type()")
+    if k == 0:
+        if not is_cd_same:
+            d.copy_(c) if c is not None else d.zero_()
+        if sfd is not None:
+            sfd.zero_()
+        return
+    if c is not None and not is_cd_same:
+        d.copy_(c)
+    tsfa, tsfb, gran_k_a, gran_k_b = _transform_sf_pair(sfa, sfb, m, n, k, recipe, None, None, batch, batch, False)
+    _require(_resolve_alpha(None, epilogue) is None, "batched GEMMs take the Identity or FP8Quantization epilogue")
+    args = _fill_args(a, tsfa, b, tsfb, d, m, n, k, batch, major_a, major_b, gran_k_a, gran_k_b, accumulate=c is not None, sfd=sfd)
+    args.batch_stride_a, args.batch_stride_b, args.batch_stride_d = a.stride(0), b.stride(0), d.stride(0)
+    check(lib.dg_fp8_bmm(C.byref(args)))
+
+
+def fp8_einsum(expr: str, a, b, d, c=None, recipe=(1, 128, 128), epilogue=None) -> None:
+    """The three contractions of csrc/apis/einsum.hpp:251-298, each a batched GEMM over permuted views:
+    'bhr,hdr->bhd' (d may be an (e4m3 tensor, sfd) pair), 'bhd,hdr->bhr' and 'bhd,bhr->hdr'."""
+    (a_data, a_sf), (b_data, b_sf) = a, b
+    pair = isinstance(d, (tuple, list))
+    if expr == "bhr,hdr->bhd":          # (batch, m, n, k) = (h, b, d, r)
+        pd = (d[0].permute(1, 0, 2), d[1]) if pair else d.permute(1, 0, 2)
+        _fp8_bmm(a_data.permute(1, 0, 2), a_sf.permute(1, 0, 2), b_data, b_sf, pd,
+                 c.permute(1, 0, 2) if c is not None else None, recipe, epilogue)
+    elif expr == "bhd,hdr->bhr":        # (h, b, r, d)
+        _require(not pair, "std::holds_alternative<torch::Tensor>(d)")
+        _fp8_bmm(a_data.permute(1, 0, 2), a_sf.permute(1, 0, 2), b_data.permute(0, 2, 1), b_sf.permute(0, 2, 1),
+                 d.permute(1, 0, 2), c.permute(1, 0, 2) if c is not None else None, recipe, epilogue)
+    elif expr == "bhd,bhr->hdr":        # (h, d, r, b)
+        _require(not pair, "std::holds_alternative<torch::Tensor>(d)")
+        _fp8_bmm(a_data.permute(1, 2, 0), a_sf.permute(1, 2, 0), b_data.permute(1, 2, 0), b_sf.permute(1, 2, 0), d, c, recipe, epilogue)
+    else:
+        raise RuntimeError(f"Unsupported einsum expression: {expr}")
+
+
 def _t(x):
     return (x[0].transpose(-1, -2), x[1].transpose(-1, -2))
 

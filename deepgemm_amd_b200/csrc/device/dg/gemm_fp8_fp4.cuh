@@ -35,6 +35,10 @@
 // K with every group starting a new row.  The slices are read on the device; an empty slice gives a zero D[g]
 // (nothing, when accumulating).  Rows of a tile beyond M are stored one by one so that D[g + 1] is not touched.
 //
+// batched (type 5; the reference's sm100_fp8_bmm behind fp8_einsum): num_groups GEMMs of one shape; every tensor map
+// is three-dimensional with the batch outermost, so operands and D may have any batch stride (the permuted views of
+// the einsum expressions) and rows beyond M are clipped per batch.
+//
 // DG_SPLIT_K (dense only, for shapes with too few output tiles to fill the GPU): every output tile becomes
 // num_splits work items over slices of K, and the kernel's D is an FP32 workspace of num_splits stacked
 // [rows x N] panels: work item (tile, slice) stores its partial tile into panel `slice`.  A separate kernel
@@ -127,8 +131,9 @@ constexpr uint32_t SF_BLOCK_N = (BLOCK_N + 127) / 128 * 128;
 // 128-byte swizzle requires); the arithmetic lives in gemm_config.hpp, shared with the host heuristics
 constexpr uint32_t kDElemBytes = kDIsFP32 ? 4 : (kDIsFP8 ? 1 : 2);
 static_assert(!(kDIsFP32 && kDIsFP8), "one output type");
-static_assert(!kDIsFP8 || (kGemmType == 0 && !kAccumulate && !kSplitK && BLOCK_N % 32 == 0),
-              "the quantising epilogue serves the plain dense GEMM with tiles of whole 32-column scale groups");
+static_assert(!kDIsFP8 || ((kGemmType == kDense || kGemmType == kBatched) && !kAccumulate && !kSplitK && BLOCK_N % 32 == 0),
+              "the quantising epilogue serves the dense and batched GEMMs with tiles of whole 32-column scale groups");
+static_assert(kGemmType != kBatched || (kCluster == 1 && !kSplitK), "batched: one CTA per tile");
 constexpr GemmLayout kLayout{CTA_M, BLOCK_N, BLOCK_K, kNumStages, kDElemBytes, kCluster, kBMnMajor ? 1u : 0u, kGranKA, kGranKB,
                              DG_SHORT_K};
 constexpr uint32_t kNumSFABuffers = kLayout.sfa_buffers(), kNumSFBBuffers = kLayout.sfb_buffers();
@@ -331,6 +336,20 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
         if (kb % kSFAPeriod == 0) sfa_slot = sfa_slot + 1 == kNumSFABuffers ? 0 : sfa_slot + 1;
         if (kb % kSFBPeriod == 0) sfb_slot = sfb_slot + 1 == kNumSFBBuffers ? 0 : sfb_slot + 1;
     };
+    // Tensor-map copies: two-dimensional, or with the batch as third coordinate
+    auto tma_in = [&](uint32_t dst, const CUtensorMap* map, uint32_t bar, uint32_t x, uint32_t y, uint32_t batch) {
+        if constexpr (kGemmType == kBatched) tma_load_3d(dst, map, bar, static_cast<int32_t>(x), static_cast<int32_t>(y), static_cast<int32_t>(batch));
+        else tma_load_2d(dst, map, bar, static_cast<int32_t>(x), static_cast<int32_t>(y));
+    };
+    auto tma_out = [&](const CUtensorMap* map, uint32_t src, uint32_t x, uint32_t y, uint32_t batch) {
+        if constexpr (kGemmType == kBatched) {
+            if constexpr (kAccumulate) tma_reduce_add_3d(map, src, static_cast<int32_t>(x), static_cast<int32_t>(y), static_cast<int32_t>(batch));
+            else tma_store_3d(map, src, static_cast<int32_t>(x), static_cast<int32_t>(y), static_cast<int32_t>(batch));
+        } else {
+            if constexpr (kAccumulate) tma_reduce_add_2d(map, src, static_cast<int32_t>(x), static_cast<int32_t>(y));
+            else tma_store_2d(map, src, static_cast<int32_t>(x), static_cast<int32_t>(y));
+        }
+    };
     Tile tile;
     uint32_t stage = 0, phase = 0;
     auto advance_stage = [&]() {
@@ -355,16 +374,18 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                     // Row coordinates of this CTA's part of the tile in the 2-D views of A, B and the scale tensors
                     const uint32_t a_row = tile.a_row_base + tile.m_block * TILE_M + cta_rank * CTA_M;
                     const uint32_t sfa_mn = tile.sfa_mn_base + tile.m_block * TILE_M + cta_rank * CTA_M;
-                    const uint32_t sfa_row0 = kGemmType == kKGrouped ? tile.sf_row_base : tile.sfa_group * sfa_rows_per_group;
+                    const uint32_t sfa_row0 = kGemmType == kKGrouped ? tile.sf_row_base : tile.sfa_group * sfa_rows_per_group;   // batched: 0
                     const uint32_t k_base = kGemmType == kKGrouped ? tile.k_base : 0u;      // first element of K of this work item
                     const uint32_t kb0 = kb_begin(tile), num_kb = kb_end(tile) - kb0, num_steps = num_passes_of(tile) * num_kb;
                     for (uint32_t it = 0; it < num_steps; ++it, advance_stage()) {
                         const auto [pass, kb] = step_of(it, kb0, num_kb);
                         const uint32_t b_group = pass == 0 ? tile.group : tile.group1;
                         // k-grouped: B is one [N, sum K] (or [sum K, N]) matrix and the group selects the slice of K
-                        const uint32_t b_row = (kGemmType == kKGrouped ? 0u : b_group * p.shape_n) + tile.n_block * BLOCK_N + cta_rank * LOAD_BLOCK_N;
-                        const uint32_t sfb_row0 = kGemmType == kKGrouped ? tile.sf_row_base : b_group * sfb_rows_per_group;
-                        const uint32_t b_k_base = kGemmType == kKGrouped ? tile.k_base : b_group * p.shape_k;   // MN-major B: row of K
+                        // (batched: the batch is a coordinate of its own)
+                        constexpr bool kOneB = kGemmType == kKGrouped || kGemmType == kBatched;
+                        const uint32_t b_row = (kOneB ? 0u : b_group * p.shape_n) + tile.n_block * BLOCK_N + cta_rank * LOAD_BLOCK_N;
+                        const uint32_t sfb_row0 = kGemmType == kKGrouped ? tile.sf_row_base : (kOneB ? 0u : b_group * sfb_rows_per_group);
+                        const uint32_t b_k_base = kGemmType == kKGrouped ? tile.k_base : (kOneB ? 0u : b_group * p.shape_k);   // MN-major B: row of K
                         DG_PROF_BEGIN(prof_w);
                         if (!mbar_wait(empty_bar(stage), phase ^ 1, ctx, kRoleProducer, 1)) { ok = false; break; }
                         DG_PROF_ADD(prof_wait, prof_w);
@@ -373,18 +394,16 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                         if (kb % kSFBPeriod == 0) sf_bytes += kSFBBytes;
                         mbar_arrive_expect_tx(sf_full_bar(stage), sf_bytes);
                         if (kb % kSFAPeriod == 0)
-                            tma_load_2d(sfa_buffer(), &tm_sfa, sf_full_bar(stage),
-                                        static_cast<int32_t>(sfa_mn), static_cast<int32_t>(sfa_row0 + kb / kSFAPeriod));
+                            tma_in(sfa_buffer(), &tm_sfa, sf_full_bar(stage), sfa_mn, sfa_row0 + kb / kSFAPeriod, tile.group);
                         if (kb % kSFBPeriod == 0)
-                            tma_load_2d(sfb_buffer(), &tm_sfb, sf_full_bar(stage),
-                                        static_cast<int32_t>(tile.n_block * BLOCK_N), static_cast<int32_t>(sfb_row0 + kb / kSFBPeriod));
+                            tma_in(sfb_buffer(), &tm_sfb, sf_full_bar(stage), tile.n_block * BLOCK_N, sfb_row0 + kb / kSFBPeriod, tile.group);
                         // With a cluster the copies land in this CTA and their bytes are counted on CTA 0's barrier,
                         // which expects both CTAs' bytes
                         const uint32_t load_bar = kCluster == 1 ? full_bar(stage) : in_leader(full_bar(stage));
                         if (kCluster == 1 || is_leader) mbar_arrive_expect_tx(full_bar(stage), kTxBytesAB);
                         else mbar_arrive_cluster(load_bar);
                         auto load = [&](uint32_t dst, const CUtensorMap* map, uint32_t x, uint32_t y) {
-                            if constexpr (kCluster == 1) tma_load_2d(dst, map, load_bar, static_cast<int32_t>(x), static_cast<int32_t>(y));
+                            if constexpr (kCluster == 1) tma_in(dst, map, load_bar, x, y, tile.group);
                             else tma_load_2d_2cta(dst, map, load_bar, static_cast<int32_t>(x), static_cast<int32_t>(y));
                         };
                         // K-major: x = K, y = row.  MN-major: x = row (column of the stored matrix), y = K (+ the group's K offset)
@@ -696,9 +715,11 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                             for (uint32_t i = 0; i < 8; ++i)
                                 q8[t * 8 + i] = pack_e4m3x4(bf16_lo(pairs[2 * i]) * inv, bf16_hi(pairs[2 * i]) * inv,
                                                             bf16_lo(pairs[2 * i + 1]) * inv, bf16_hi(pairs[2 * i + 1]) * inv);
+                            // Batched: the scale columns of all batches follow one another, as in D viewed as [m, batches * n]
                             const uint32_t col = n0 + g * kGroupCols + t * 32, d_row = d_row0 + row_in_tile;
+                            const uint32_t sf_col = (kGemmType == kBatched ? tile.group * p.shape_n : 0u) + col;
                             if (d_row < p.shape_m && col < p.shape_n)
-                                reinterpret_cast<uint8_t*>(p.sfd + static_cast<size_t>(col / 128) * p.sfd_pitch + d_row)[(col / 32) % 4] =
+                                reinterpret_cast<uint8_t*>(p.sfd + static_cast<size_t>(sf_col / 128) * p.sfd_pitch + d_row)[(sf_col / 32) % 4] =
                                     static_cast<uint8_t>(ue8m0_code(sf));
                         }
                     }
@@ -760,12 +781,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                         #pragma unroll
                         for (uint32_t box = 0; box < kGroupCols / kStoreCols; ++box) {
                             if (box * cols_per_box < kCols) {
-                                if constexpr (kAccumulate)
-                                    tma_reduce_add_2d(map, stage_addr + box * box_bytes, static_cast<int32_t>(col0 + box * cols_per_box),
-                                                      static_cast<int32_t>(d_row0));
-                                else
-                                    tma_store_2d(map, stage_addr + box * box_bytes, static_cast<int32_t>(col0 + box * cols_per_box),
-                                                 static_cast<int32_t>(d_row0));
+                                tma_out(map, stage_addr + box * box_bytes, col0 + box * cols_per_box, d_row0, tile.group);
                             }
                         }
                         tma_store_commit();

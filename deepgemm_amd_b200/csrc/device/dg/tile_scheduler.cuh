@@ -20,6 +20,8 @@
 //       K-blocks and the first packed scale row of the group.  layout[g] is the slice's length (a multiple
 //       of the alignment) or, in the prefix-sum form, the element where it ends, the next slice starting
 //       at the following multiple of the alignment (scheduler/gemm.cuh:226-250 of the reference).
+//   batched : num_groups independent GEMMs of one shape; tile_id = batch * tiles_per_batch + tile, the
+//       batch being the third tensor-map coordinate of every operand (scheduler/gemm.cuh:251-263).
 #pragma once
 
 #include <cstdint>
@@ -32,7 +34,7 @@
 
 namespace dg {
 
-enum GemmKind : uint32_t { kDense = 0, kMGroupedContiguous = 1, kMGroupedMasked = 2, kMGroupedPsum = 3, kKGrouped = 4 };
+enum GemmKind : uint32_t { kDense = 0, kMGroupedContiguous = 1, kMGroupedMasked = 2, kMGroupedPsum = 3, kKGrouped = 4, kBatched = 5 };
 
 struct Tile {
     uint32_t m_block;       // row block inside the group (masked) or inside A (dense / contiguous)
@@ -112,6 +114,17 @@ struct TileScheduler {
             t.sfa_group = cur_group;
             const uint32_t left = rows - t.m_block * kBlockM;
             t.valid_rows = left < kBlockM ? left : kBlockM;
+            t.split = 0;
+            t.mn_index = tile_id;
+            return true;
+        } else if constexpr (kKind == kBatched) {
+            const uint32_t blocks = num_m_blocks * num_n_blocks;
+            const uint32_t batch = tile_id / blocks;
+            if (batch >= num_groups) return false;
+            rasterise(tile_id - batch * blocks, num_m_blocks, t.m_block, t.n_block);
+            t.group = t.group1 = batch;
+            t.a_row_base = t.d_row_base = t.sfa_mn_base = t.sfa_group = 0;
+            t.valid_rows = kBlockM;              // the batch's own extent in the tensor map clips rows beyond M
             t.split = 0;
             t.mn_index = tile_id;
             return true;

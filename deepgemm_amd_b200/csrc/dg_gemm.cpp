@@ -75,24 +75,36 @@ struct Problem {
 int validate(int kind, const dg_gemm_args_t* a, bool need_pointers, Problem* p) {
     DG_REQUIRE(a != nullptr);
     DG_REQUIRE(kind == DG_GEMM_DENSE || kind == DG_GEMM_M_GROUPED_CONTIGUOUS || kind == DG_GEMM_M_GROUPED_MASKED ||
-               kind == DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM || kind == DG_GEMM_K_GROUPED_CONTIGUOUS);
-    const bool k_grouped = kind == DG_GEMM_K_GROUPED_CONTIGUOUS;
+               kind == DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM || kind == DG_GEMM_K_GROUPED_CONTIGUOUS || kind == DG_GEMM_BATCHED);
+    const bool k_grouped = kind == DG_GEMM_K_GROUPED_CONTIGUOUS, batched = kind == DG_GEMM_BATCHED;
     DG_REQUIRE(a->a_dtype == DG_FP8_E4M3 || a->a_dtype == DG_FP4_E2M1_X2);
     DG_REQUIRE(a->b_dtype == DG_FP8_E4M3 || a->b_dtype == DG_FP4_E2M1_X2);
     DG_REQUIRE(a->d_dtype == DG_BF16 || a->d_dtype == DG_FP32 || a->d_dtype == DG_FP8_E4M3);
-    if (kind != DG_GEMM_DENSE && !k_grouped) DG_REQUIRE(a->d_dtype == DG_BF16);            // gemm.hpp:209,299
+    if (kind != DG_GEMM_DENSE && !k_grouped && !batched) DG_REQUIRE(a->d_dtype == DG_BF16);            // gemm.hpp:209,299
     if (k_grouped) DG_REQUIRE(a->d_dtype == DG_BF16 || a->d_dtype == DG_FP32);
+    if (batched) {
+        // einsum.hpp:183-243: [B, M, K] x [B, N, K]^T -> [B, M, N], any batch strides that a tensor map can express
+        DG_REQUIRE(a->num_groups > 0 && !a->has_alpha);
+        DG_REQUIRE(a->a_dtype == DG_FP8_E4M3 && a->b_dtype == DG_FP8_E4M3);
+        DG_REQUIRE(a->batch_stride_a % 16 == 0 && a->batch_stride_b % 16 == 0);
+        DG_REQUIRE((a->batch_stride_d * (a->d_dtype == DG_FP32 ? 4 : (a->d_dtype == DG_FP8_E4M3 ? 1 : 2))) % 16 == 0);
+        // quantised output: the scale columns of the batches follow one another, so a batch is whole packed words
+        if (a->d_dtype == DG_FP8_E4M3) DG_REQUIRE(a->n % 128 == 0 && a->batch_stride_d == a->n);
+    }
     if (a->d_dtype == DG_FP8_E4M3) {
         // "FP8 quantization requires a direct E4M3 output" (epilogue_class.hpp:84-87); the epilogues do not compose
         DG_REQUIRE(!a->accumulate && !a->has_alpha);
         if (need_pointers) DG_REQUIRE(a->sfd != nullptr && reinterpret_cast<uintptr_t>(a->sfd) % 4 == 0);
         DG_REQUIRE(a->sfd_pitch >= align_up<int64_t>(a->m, 4));
+        DG_REQUIRE(kind == DG_GEMM_DENSE || batched);
     }
     DG_REQUIRE(a->m >= 0 && a->n >= 0 && a->k >= 0);
     DG_REQUIRE(a->gran_k_a == 32 || a->gran_k_a == 128);
     DG_REQUIRE(a->gran_k_b == 32 || a->gran_k_b == 128);
     if (kind == DG_GEMM_DENSE) {
         DG_REQUIRE(a->num_groups == 1);
+    } else if (batched) {
+        DG_REQUIRE(a->n > 0 && a->k > 0);
     } else if (k_grouped) {
         // gemm.hpp:320-372: 1-D scales of one granularity, K slices aligned to whole K-blocks, contiguous operands
         DG_REQUIRE(a->num_groups > 0 && a->gran_k_a == a->gran_k_b);
@@ -137,7 +149,7 @@ int validate(int kind, const dg_gemm_args_t* a, bool need_pointers, Problem* p) 
         DG_REQUIRE(aligned(a->a, p->a_fp4 ? 32 : 16));                        // runtime_utils.hpp:126
         DG_REQUIRE(aligned(a->b, p->b_fp4 ? 32 : 16));
         DG_REQUIRE(aligned(a->sfa, 16) && aligned(a->sfb, 16) && aligned(a->d, 16));
-        if (kind != DG_GEMM_DENSE) DG_REQUIRE(a->grouped_layout != nullptr);
+        if (kind != DG_GEMM_DENSE && !batched) DG_REQUIRE(a->grouped_layout != nullptr);
     }
     // Pitch of the non-contiguous dimension: rows of K bytes (K-major) or K-slices of MN bytes (MN-major)
     const int64_t k_bytes_a = p->a_mn_major ? a->m : (p->a_fp4 ? a->k / 2 : a->k);
@@ -211,6 +223,7 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
         // A CTA pair multiplies all its rows with one B: in the contiguous layout every expert segment must then be a
         // whole number of pair tiles
         if (cluster == 2 && (num_sms % 2 != 0 || p.kind == DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM || p.kind == DG_GEMM_K_GROUPED_CONTIGUOUS ||
+                             p.kind == DG_GEMM_BATCHED ||
                              (p.kind == DG_GEMM_M_GROUPED_CONTIGUOUS && state().mk_alignment % (256 * halves) != 0))) continue;
         // 256 rows per CTA: two 128-row MMAs per K-block on one B stage; K not sliced
         if (forced_block_m ? 128 * halves != forced_block_m : (halves == 2 && p.m <= 128)) continue;
@@ -229,6 +242,8 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
         else if (p.kind == DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM)   // every group may end with a partly filled tile
             m_blocks = ceil_div(p.m, tile_m) + p.groups / 2;
         else if (p.kind == DG_GEMM_K_GROUPED_CONTIGUOUS)        // every group has the full tile grid and a share of K
+            m_blocks = static_cast<int64_t>(p.groups) * ceil_div(p.m, tile_m);
+        else if (p.kind == DG_GEMM_BATCHED)
             m_blocks = static_cast<int64_t>(p.groups) * ceil_div(p.m, tile_m);
         else
             m_blocks = ceil_div(p.m, tile_m);
@@ -362,31 +377,37 @@ std::string generate_source(const Problem& p, const dg_gemm_config_t& cfg) {
     return s.str();
 }
 
+// A tiled tensor map over [outer][inner] elements (row pitch outer_stride_bytes) or, with batches > 0, over
+// [batches][outer][inner] with the batches batch_stride_bytes apart and a box one batch deep.
 int encode_2d(CUtensorMap* map, CUtensorMapDataType dtype, const void* base, uint64_t inner, uint64_t outer,
-              uint64_t outer_stride_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swizzle) {
+              uint64_t outer_stride_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swizzle,
+              uint64_t batches = 0, uint64_t batch_stride_bytes = 0) {
     const Driver& drv = driver();
     if (!drv.ok) return fail(DG_ERR_CUDA, "CUDA driver unavailable: %s", drv.why.c_str());
-    const cuuint64_t dims[2] = {inner, outer};
-    const cuuint64_t strides[1] = {outer_stride_bytes};
-    const cuuint32_t box[2] = {box_inner, box_outer};
-    const cuuint32_t elem_strides[2] = {1, 1};
+    const cuuint32_t rank = batches > 0 ? 3 : 2;
+    const cuuint64_t dims[3] = {inner, outer, batches};
+    const cuuint64_t strides[2] = {outer_stride_bytes, batch_stride_bytes};
+    const cuuint32_t box[3] = {box_inner, box_outer, 1};
+    const cuuint32_t elem_strides[3] = {1, 1, 1};
     if (env_int("PRINT_CONFIGS"))
-        fprintf(stderr, "[dg] tensor map: dtype %d dims (%llu, %llu) stride %llu B box (%u, %u) swizzle %d base %p\n",
+        fprintf(stderr, "[dg] tensor map: dtype %d dims (%llu, %llu, %llu) strides %llu, %llu B box (%u, %u) swizzle %d base %p\n",
                 static_cast<int>(dtype), static_cast<unsigned long long>(inner), static_cast<unsigned long long>(outer),
-                static_cast<unsigned long long>(outer_stride_bytes), box_inner, box_outer, static_cast<int>(swizzle), base);
-    const CUresult r = drv.cuTensorMapEncodeTiled(map, dtype, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
+                static_cast<unsigned long long>(batches), static_cast<unsigned long long>(outer_stride_bytes),
+                static_cast<unsigned long long>(batch_stride_bytes), box_inner, box_outer, static_cast<int>(swizzle), base);
+    const CUresult r = drv.cuTensorMapEncodeTiled(map, dtype, rank, const_cast<void*>(base), dims, strides, box, elem_strides,
                                                   CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
-        return fail(DG_ERR_CUDA, "cuTensorMapEncodeTiled failed: %s (dims %llu x %llu, stride %llu, box %u x %u)", cu_error(r).c_str(),
-                    static_cast<unsigned long long>(inner), static_cast<unsigned long long>(outer),
-                    static_cast<unsigned long long>(outer_stride_bytes), box_inner, box_outer);
+        return fail(DG_ERR_CUDA, "cuTensorMapEncodeTiled failed: %s (dims %llu x %llu x %llu, strides %llu, %llu, box %u x %u)",
+                    cu_error(r).c_str(), static_cast<unsigned long long>(inner), static_cast<unsigned long long>(outer),
+                    static_cast<unsigned long long>(batches), static_cast<unsigned long long>(outer_stride_bytes),
+                    static_cast<unsigned long long>(batch_stride_bytes), box_inner, box_outer);
     return DG_OK;
 }
 
 int get_kernel(const Problem& p, const dg_gemm_config_t& cfg, dg_kernel_t* kernel) {
-    static const char* names[5] = {"gemm_fp8_fp4_dense", "gemm_fp8_fp4_m_grouped_contiguous", "gemm_fp8_fp4_m_grouped_masked",
-                                   "gemm_fp8_fp4_m_grouped_contiguous_psum", "gemm_fp8_fp4_k_grouped_contiguous"};
+    static const char* names[6] = {"gemm_fp8_fp4_dense", "gemm_fp8_fp4_m_grouped_contiguous", "gemm_fp8_fp4_m_grouped_masked",
+                                   "gemm_fp8_fp4_m_grouped_contiguous_psum", "gemm_fp8_fp4_k_grouped_contiguous", "gemm_fp8_fp4_batched"};
     const std::string src = generate_source(p, cfg);
     return dg_jit_compile(names[p.kind], "dg_gemm_fp8_fp4", src.c_str(), "", kernel);
 }
@@ -435,35 +456,44 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
     const bool k_grouped = kind == DG_GEMM_K_GROUPED_CONTIGUOUS;
     const uint64_t a_rows = kind == DG_GEMM_M_GROUPED_MASKED ? static_cast<uint64_t>(p.groups) * p.m : p.m;
     // k-grouped: one B for all groups (the group selects a slice of K); every group starts a new packed scale row
-    const uint64_t b_rows = k_grouped ? p.n : static_cast<uint64_t>(p.groups) * p.n;
-    const uint64_t b_k_rows = k_grouped ? p.k : static_cast<uint64_t>(p.groups) * p.k;
+    const bool one_b = k_grouped || kind == DG_GEMM_BATCHED;        // (batched: the batch is a dimension of its own)
+    const uint64_t b_rows = one_b ? p.n : static_cast<uint64_t>(p.groups) * p.n;
+    const uint64_t b_k_rows = one_b ? p.k : static_cast<uint64_t>(p.groups) * p.k;
     const uint64_t sfa_k = ceil_div(p.k, p.gran_k_a * 4), sfb_k = ceil_div(p.k, p.gran_k_b * 4);
     const uint64_t sfa_rows = kind == DG_GEMM_M_GROUPED_MASKED ? sfa_k * p.groups : (k_grouped ? sfa_k + p.groups : sfa_k);
-    const uint64_t sfb_rows = k_grouped ? sfb_k + p.groups : sfb_k * p.groups;
+    const uint64_t sfb_rows = k_grouped ? sfb_k + p.groups : (kind == DG_GEMM_BATCHED ? sfb_k : sfb_k * p.groups);
 
+    // Batched: every map gets the batch as a third dimension (strides in bytes)
+    const bool batched = kind == DG_GEMM_BATCHED;
+    const uint64_t nb = batched ? p.groups : 0;
+    const uint64_t d_elem_bytes = p.d_fp32 ? 4 : (p.d_fp8 ? 1 : 2);
+    const uint64_t bs_a = batched ? a->batch_stride_a : 0, bs_b = batched ? a->batch_stride_b : 0;
+    const uint64_t bs_d = batched ? a->batch_stride_d * d_elem_bytes : 0;
+    const uint64_t bs_sfa = batched ? a->sfa_pitch * 4 * ceil_div(p.k, p.gran_k_a * 4) : 0;
+    const uint64_t bs_sfb = batched ? a->sfb_pitch * 4 * ceil_div(p.k, p.gran_k_b * 4) : 0;
     CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb, tm_d, tm_d_full;
     // K-major A, B: K (elements) x rows; box = one K-block (128 or 64 elements) x the tile's rows, swizzled over its width.
     const CUtensorMapSwizzle k_major_swizzle = cfg.block_k == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
     // MN-major (FP8 only): MN x (groups x K); box = 128 columns of MN x one K-block.
     if (!p.a_mn_major) {
         if ((rc = encode_2d(&tm_a, p.a_fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, a->a,
-                            p.k, a_rows, a->lda, cfg.block_k, cfg.block_m, k_major_swizzle)) != DG_OK) return rc;
+                            p.k, a_rows, a->lda, cfg.block_k, cfg.block_m, k_major_swizzle, nb, bs_a)) != DG_OK) return rc;
     } else {
         if ((rc = encode_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->a, p.m, p.k, a->lda, 128, 128,
-                            CU_TENSOR_MAP_SWIZZLE_128B)) != DG_OK) return rc;
+                            CU_TENSOR_MAP_SWIZZLE_128B, nb, bs_a)) != DG_OK) return rc;
     }
     if (!p.b_mn_major) {
         if ((rc = encode_2d(&tm_b, p.b_fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, a->b,
-                            p.k, b_rows, a->ldb, cfg.block_k, cfg.block_n / cfg.cluster_size, k_major_swizzle)) != DG_OK) return rc;
+                            p.k, b_rows, a->ldb, cfg.block_k, cfg.block_n / cfg.cluster_size, k_major_swizzle, nb, bs_b)) != DG_OK) return rc;
     } else {
         if ((rc = encode_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->b, p.n, b_k_rows, a->ldb, 128, 128,
-                            CU_TENSOR_MAP_SWIZZLE_128B)) != DG_OK) return rc;
+                            CU_TENSOR_MAP_SWIZZLE_128B, nb, bs_b)) != DG_OK) return rc;
     }
     // Scales: MN (int32) x packed-K rows; the MN extent is the true row count, so reads past it are zero-filled
     if ((rc = encode_2d(&tm_sfa, CU_TENSOR_MAP_DATA_TYPE_INT32, a->sfa, p.m, sfa_rows, a->sfa_pitch * 4, cfg.block_m, 1,
-                        CU_TENSOR_MAP_SWIZZLE_NONE)) != DG_OK) return rc;
+                        CU_TENSOR_MAP_SWIZZLE_NONE, nb, bs_sfa)) != DG_OK) return rc;
     if ((rc = encode_2d(&tm_sfb, CU_TENSOR_MAP_DATA_TYPE_INT32, a->sfb, p.n, sfb_rows, a->sfb_pitch * 4, lay.sf_block_n(), 1,
-                        CU_TENSOR_MAP_SWIZZLE_NONE)) != DG_OK) return rc;
+                        CU_TENSOR_MAP_SWIZZLE_NONE, nb, bs_sfb)) != DG_OK) return rc;
     const CUtensorMapSwizzle d_swizzle = lay.store_row_bytes() == 128 ? CU_TENSOR_MAP_SWIZZLE_128B :
                                          lay.store_row_bytes() == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
     // Two views of D: boxes as wide as an epilogue group (128 or 64 bytes) for complete groups, narrower boxes for the
@@ -474,9 +504,9 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
     const uint64_t d_rows = split ? static_cast<uint64_t>(cfg.num_splits) * panel_rows :
                             (k_grouped ? static_cast<uint64_t>(p.groups) * p.m : a_rows);
     const uint64_t d_pitch_bytes = split ? ld_ws * 4 : a->ldd * (p.d_fp32 ? 4 : (p.d_fp8 ? 1 : 2));
-    if ((rc = encode_2d(&tm_d, d_type, d_base, p.n, d_rows, d_pitch_bytes, lay.store_cols(), 128, d_swizzle)) != DG_OK) return rc;
+    if ((rc = encode_2d(&tm_d, d_type, d_base, p.n, d_rows, d_pitch_bytes, lay.store_cols(), 128, d_swizzle, nb, bs_d)) != DG_OK) return rc;
     if ((rc = encode_2d(&tm_d_full, d_type, d_base, p.n, d_rows, d_pitch_bytes, lay.group_cols(), 128,
-                        lay.group_bytes() == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B)) != DG_OK)
+                        lay.group_bytes() == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, nb, bs_d)) != DG_OK)
         return rc;
 
     GemmParams params;
@@ -548,6 +578,7 @@ int dg_m_grouped_fp8_fp4_gemm_contiguous(const dg_gemm_args_t* args) {
 }
 int dg_m_grouped_fp8_fp4_gemm_masked(const dg_gemm_args_t* args) { return run_gemm(DG_GEMM_M_GROUPED_MASKED, args); }
 int dg_k_grouped_fp8_gemm_contiguous(const dg_gemm_args_t* args) { return run_gemm(DG_GEMM_K_GROUPED_CONTIGUOUS, args); }
+int dg_fp8_bmm(const dg_gemm_args_t* args) { return run_gemm(DG_GEMM_BATCHED, args); }
 
 int dg_get_gemm_config(int kind, const dg_gemm_args_t* args, dg_gemm_config_t* config) {
     DG_REQUIRE(config != nullptr);

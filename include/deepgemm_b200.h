@@ -47,7 +47,8 @@ typedef enum dg_gemm_kind {
     DG_GEMM_M_GROUPED_CONTIGUOUS = 1,
     DG_GEMM_M_GROUPED_MASKED = 2,
     DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM = 3,    /* the contiguous layout with use_psum_layout (for dg_get_gemm_config / dg_gemm_precompile) */
-    DG_GEMM_K_GROUPED_CONTIGUOUS = 4
+    DG_GEMM_K_GROUPED_CONTIGUOUS = 4,
+    DG_GEMM_BATCHED = 5
 } dg_gemm_kind_t;
 
 DG_API const char* dg_last_error(void);
@@ -170,6 +171,12 @@ typedef struct dg_gemm_args {
      * or alpha; words of sfd beyond column n keep the bytes they had. */
     void* sfd;
     int64_t sfd_pitch;
+    /* dg_fp8_bmm only: distance between consecutive batches of A, B and D in storage elements (any value whose byte
+     * count is a multiple of 16: the permuted views of fp8_einsum are expressed this way).  The scale tensors of a
+     * batched GEMM are packed tightly: batch stride = sf*_pitch * ceil(k / (4 gran_k)) int32. */
+    int64_t batch_stride_a;
+    int64_t batch_stride_b;
+    int64_t batch_stride_d;
 } dg_gemm_args_t;
 
 /* fp8_fp4_gemm_nt and, through major_a / major_b, nn / tn / tt (gemm.hpp:78-179). */
@@ -191,6 +198,11 @@ DG_API int dg_m_grouped_fp8_fp4_gemm_masked(const dg_gemm_args_t* args);
  *          dg_pack_k_grouped_fp32_into_ue8m0 produces it); gran_k_a == gran_k_b.
  * An empty slice gives D[g] = 0 (leaves it unchanged when accumulating). */
 DG_API int dg_k_grouped_fp8_gemm_contiguous(const dg_gemm_args_t* args);
+/* fp8_bmm behind fp8_einsum (csrc/apis/einsum.hpp:183-243): D[b] = C[b] + A[b] B[b]^T for b < num_groups, every operand
+ * a [num_groups, rows, K-or-MN] tensor with its own batch stride (batch_stride_* above) and row pitch (lda / ldb / ldd);
+ * FP8 operands, K- or MN-major; D BF16, FP32 or, with sfd, e4m3 (then n % 128 == 0 and batch_stride_d == n: sfd is the
+ * scale tensor of D viewed as [m, num_groups * n]).  Rows beyond m are clipped per batch. */
+DG_API int dg_fp8_bmm(const dg_gemm_args_t* args);
 
 /* Same operation and arguments as dg_fp8_fp4_gemm, for callers that cannot allocate device memory (inside a stream
  * capture, on a thread that must not block on the allocator, or in a process that freezes its memory footprint after

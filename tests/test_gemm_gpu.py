@@ -524,6 +524,89 @@ def test_k_grouped_contiguous_matches_oracle(m, n, ks, psum, gran_k, out_dtype, 
 
 
 # ---------------------------------------------------------------------------------------------------
+# batched GEMM behind fp8_einsum
+# ---------------------------------------------------------------------------------------------------
+def _dq(q, sf_rows, gran_k=128):
+    return oracle.cast_back_from_fp8(q, sf_rows, gran_k)
+
+
+@pytest.mark.parametrize("b", [200, 4])
+@pytest.mark.parametrize("block_m", [128, 256])
+def test_fp8_einsum_bhr_hdr_bhd_with_bf16_fp32_and_quantised_output(b, block_m, monkeypatch):
+    """Batch = h over permuted views (batch stride r, row pitch h * r); rows beyond b are clipped per batch; the FP8
+    output pair equals the BF16 output followed by the 1 x 32 cast of d viewed as [b, h * d] (tests/test_einsum.py:128-186)."""
+    if block_m == 256 and b <= 128:
+        pytest.skip("256-row tiles need more than 128 rows")
+    monkeypatch.setenv("DG_FORCE_BLOCK_M", str(block_m))
+    h, r, d = 3, 256, 384
+    x, y = seeded_bf16((b, h, r), 91), seeded_bf16((h, d, r), 92)
+    qx, sfx = oracle.per_token_cast_to_fp8(x.reshape(b * h, r), True, 128)
+    qx, sfx = qx.reshape(b, h, r), sfx.reshape(b, h, r // 128)
+    qy = np.stack([oracle.per_block_cast_to_fp8(y[i], True)[0] for i in range(h)])
+    sfy = np.stack([oracle.per_block_cast_to_fp8(y[i], True)[1] for i in range(h)])
+    ref = np.stack([_dq(qx[:, i], sfx[:, i]) @ _dq(qy[i], oracle.broadcast_sf_along_mn(sfy[i], d, 128)).T for i in range(h)], axis=1)
+    a = (fp8_cuda(qx), torch.from_numpy(sfx).cuda()); bb = (fp8_cuda(qy), torch.from_numpy(sfy).cuda())
+    z = torch.full((b, h, d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    dg.reset_kernel_status()
+    dg.fp8_einsum("bhr,hdr->bhd", a, bb, z)
+    assert dg.kernel_status() == 0
+    out = z.float().cpu().numpy()
+    assert oracle.calc_diff(out, oracle.bf16_round(ref)) < 1e-5, diff_report(out.reshape(b, -1), ref.reshape(b, -1))
+    # FP32 accumulation into a permuted D
+    tmp = torch.zeros((h, b, d), dtype=torch.float, device="cuda").permute(1, 0, 2)
+    dg.fp8_einsum("bhr,hdr->bhd", a, bb, tmp, c=tmp)
+    dg.fp8_einsum("bhr,hdr->bhd", a, bb, tmp, c=tmp)
+    assert oracle.calc_diff(tmp.cpu().numpy(), 2 * ref) < 1e-9
+    # quantised output pair
+    out_q = torch.zeros((b, h, d), dtype=torch.uint8, device="cuda").view(torch.float8_e4m3fn)
+    amn = dg.get_tma_aligned_size(b, 4)
+    sfd = torch.zeros((h * d // 128, amn), dtype=torch.int, device="cuda").t()[:b]
+    dg.fp8_einsum("bhr,hdr->bhd", a, bb, (out_q, sfd))
+    assert dg.kernel_status() == 0
+    want_q, want_sf = dg.per_token_cast(z.view(b, h * d), "e4m3", gran_k=32, use_packed_ue8m0=True)
+    assert torch.equal(out_q.view(torch.uint8).view(b, h * d), want_q.view(torch.uint8))
+    assert torch.equal(sfd, want_sf)
+
+
+def test_fp8_einsum_bhd_hdr_bhr_reads_b_transposed():
+    b, h, r, d = 136, 3, 304 // 16 * 16, 256
+    x, y = seeded_bf16((b, h, d), 93), seeded_bf16((h, d, r), 94)
+    qx, sfx = oracle.per_token_cast_to_fp8(x.reshape(b * h, d), True, 128)
+    qx, sfx = qx.reshape(b, h, d), sfx.reshape(b, h, d // 128)
+    qy = np.stack([oracle.per_block_cast_to_fp8(y[i], True)[0] for i in range(h)])
+    sfy = np.stack([oracle.per_block_cast_to_fp8(y[i], True)[1] for i in range(h)])          # [h, d / 128, ceil(r / 128)]
+    def dq_y(i):                                                                             # scales per (128 of d, 128 of r)
+        return oracle.e4m3_decode(qy[i]) * np.repeat(np.repeat(sfy[i], 128, axis=0), 128, axis=1)[:d, :r]
+    ref = np.stack([_dq(qx[:, i], sfx[:, i]) @ dq_y(i) for i in range(h)], axis=1)
+    z = torch.full((b, h, r), float("nan"), dtype=torch.bfloat16, device="cuda")
+    dg.reset_kernel_status()
+    dg.fp8_einsum("bhd,hdr->bhr", (fp8_cuda(qx), torch.from_numpy(sfx).cuda()), (fp8_cuda(qy), torch.from_numpy(sfy).cuda()), z)
+    assert dg.kernel_status() == 0
+    out = z.float().cpu().numpy()
+    assert oracle.calc_diff(out, oracle.bf16_round(ref)) < 1e-5, diff_report(out.reshape(b, -1), ref.reshape(b, -1))
+
+
+def test_fp8_einsum_bhd_bhr_hdr_contracts_over_the_batch_dimension():
+    b, h, r, d = 256, 3, 256, 384
+    x, y = seeded_bf16((b, h, d), 95), seeded_bf16((b, h, r), 96)
+    def per_channel(t, cols):                                   # 1 x 128 along b for every (h, column): tests/test_einsum.py:246-249
+        q, sf = oracle.per_token_cast_to_fp8(np.ascontiguousarray(t.reshape(b, h * cols).T), True, 128)
+        return np.ascontiguousarray(q.T).reshape(b, h, cols), np.ascontiguousarray(sf.T).reshape(b // 128, h, cols)
+    qx, sfx = per_channel(x, d)
+    qy, sfy = per_channel(y, r)
+    dqx = oracle.e4m3_decode(qx) * np.repeat(sfx, 128, axis=0)
+    dqy = oracle.e4m3_decode(qy) * np.repeat(sfy, 128, axis=0)
+    z0 = seeded_bf16((h, d, r), 97, 10.0)
+    ref = z0 + np.einsum("bhd,bhr->hdr", dqx.astype(np.float64), dqy.astype(np.float64)).astype(np.float32)
+    z = torch.from_numpy(z0).cuda()
+    dg.reset_kernel_status()
+    dg.fp8_einsum("bhd,bhr->hdr", (fp8_cuda(qx), torch.from_numpy(sfx).cuda()), (fp8_cuda(qy), torch.from_numpy(sfy).cuda()), z, c=z,
+                  recipe=(1, 1, 128))
+    assert dg.kernel_status() == 0
+    assert oracle.calc_diff(z.cpu().numpy(), ref) < 1e-9
+
+
+# ---------------------------------------------------------------------------------------------------
 # m-grouped masked
 # ---------------------------------------------------------------------------------------------------
 def _masked_case(counts, max_m, n, k):
