@@ -32,6 +32,7 @@ class GemmArgs(C.Structure):
         ("use_psum_layout", C.c_int32), ("ensure_zero_padding", C.c_int32),
         ("sfd", C.c_void_p), ("sfd_pitch", C.c_int64),
         ("batch_stride_a", C.c_int64), ("batch_stride_b", C.c_int64), ("batch_stride_d", C.c_int64),
+        ("stochastic_rounding", C.c_int32),
     ]
 
 

@@ -307,7 +307,7 @@ def _ld(t: torch.Tensor, major: int) -> int:
 
 def _fill_args(a, sfa, b, sfb, d, m, n, k, groups, major_a, major_b, gran_k_a, gran_k_b,
                accumulate=False, alpha=None, layout=None, expected_m=0, use_psum_layout=False,
-               ensure_zero_padding=False, sfd=None) -> GemmArgs:
+               ensure_zero_padding=False, sfd=None, stochastic=False) -> GemmArgs:
     args = GemmArgs()
     args.a, args.sfa, args.b, args.sfb, args.d = a.data_ptr(), sfa.data_ptr(), b.data_ptr(), sfb.data_ptr(), d.data_ptr()
     args.m, args.n, args.k, args.num_groups = m, n, k, groups
@@ -325,21 +325,30 @@ def _fill_args(a, sfa, b, sfb, d, m, n, k, groups, major_a, major_b, gran_k_a, g
     args.use_psum_layout, args.ensure_zero_padding = int(use_psum_layout), int(ensure_zero_padding)
     if sfd is not None:
         args.sfd, args.sfd_pitch = sfd.data_ptr(), sfd.stride(-1)
+    args.stochastic_rounding = int(stochastic)
     return args
 
 
 def _resolve_alpha(alpha, epilogue):
     """The epilogue class, `alpha` and the FP8 output pair are exclusive (csrc/jit_kernels/impls/epilogue_class.hpp:111-127)."""
     if epilogue is not None:
-        from .epilogue import Alpha, FP8Quantization, Identity
+        from .epilogue import Alpha, BF16StochasticRounding, FP8Quantization, Identity
         _require(alpha is None, "(epilogue_class != nullptr) + alpha.has_value() + sfd.has_value() <= 1")
-        if isinstance(epilogue, (Identity, FP8Quantization)):
+        if isinstance(epilogue, (Identity, FP8Quantization, BF16StochasticRounding)):
             return None
         if isinstance(epilogue, Alpha):
             return epilogue.alpha
-        raise RuntimeError(f"epilogue {type(epilogue).__name__} is not built (deepgemm_amd_b200): "
-                           "Identity, Alpha and FP8Quantization are")
+        raise RuntimeError(f"unknown epilogue {type(epilogue).__name__}")
     return alpha
+
+
+def _stochastic(epilogue, c, d) -> bool:
+    """BF16StochasticRounding: "Stochastic rounding requires a direct BF16 output" (epilogue_class.hpp:104-107)."""
+    from .epilogue import BF16StochasticRounding
+    if not isinstance(epilogue, BF16StochasticRounding):
+        return False
+    _require(c is None and d.dtype == torch.bfloat16, "Stochastic rounding requires a direct BF16 output")
+    return True
 
 
 def _resolve_sfd(epilogue, c, d, m: int, n: int):
@@ -395,7 +404,7 @@ def fp8_fp4_gemm_nt(a, b, d, c=None, recipe=None, recipe_a=None, recipe_b=None, 
                                                       disable_ue8m0_cast)
     alpha = _resolve_alpha(alpha, epilogue)
     args = _fill_args(a_data, sfa, b_data, sfb, d, m, n, k, 1, major_a, major_b, gran_k_a, gran_k_b,
-                      accumulate=c is not None, alpha=alpha, sfd=sfd)
+                      accumulate=c is not None, alpha=alpha, sfd=sfd, stochastic=_stochastic(epilogue, c, d))
     check(lib.dg_fp8_fp4_gemm(C.byref(args)))
 
 
@@ -484,7 +493,7 @@ def k_grouped_fp8_gemm_tn_contiguous(a, b, d, ks_cpu, grouped_layout, c=None, re
     _require(a_data.is_contiguous() and b_data.is_contiguous() and d.is_contiguous(), "a.first.is_contiguous()")
     _require(c is None or c.is_contiguous(), "not c.has_value() or c.value().is_contiguous()")
     _require(d.dtype in (torch.bfloat16, torch.float), "d.scalar_type() == torch::kBFloat16 or d.scalar_type() == torch::kFloat")
-    _require(_resolve_alpha(None, epilogue) is None, "k-grouped GEMMs take the Identity epilogue only")
+    _require(_resolve_alpha(None, epilogue) is None, "k-grouped GEMMs take the Identity or BF16StochasticRounding epilogue")
     # early_return (gemm.hpp:17-53)
     if m == 0 or n == 0:
         return
@@ -512,6 +521,7 @@ def k_grouped_fp8_gemm_tn_contiguous(a, b, d, ks_cpu, grouped_layout, c=None, re
     args.alpha = 1.0
     args.grouped_layout = grouped_layout.data_ptr()
     args.use_psum_layout = int(use_psum_layout)
+    args.stochastic_rounding = int(_stochastic(epilogue, c, d))
     args.stream = _stream()
     check(lib.dg_k_grouped_fp8_gemm_contiguous(C.byref(args)))
 
@@ -560,8 +570,9 @@ def _fp8_bmm(a, sfa, b, sfb, d, c, recipe, epilogue) -> None:
     if c is not None and not is_cd_same:
         d.copy_(c)
     tsfa, tsfb, gran_k_a, gran_k_b = _transform_sf_pair(sfa, sfb, m, n, k, recipe, None, None, batch, batch, False)
-    _require(_resolve_alpha(None, epilogue) is None, "batched GEMMs take the Identity or FP8Quantization epilogue")
-    args = _fill_args(a, tsfa, b, tsfb, d, m, n, k, batch, major_a, major_b, gran_k_a, gran_k_b, accumulate=c is not None, sfd=sfd)
+    _require(_resolve_alpha(None, epilogue) is None, "batched GEMMs take no alpha")
+    args = _fill_args(a, tsfa, b, tsfb, d, m, n, k, batch, major_a, major_b, gran_k_a, gran_k_b, accumulate=c is not None, sfd=sfd,
+                      stochastic=_stochastic(epilogue, c, d))
     args.batch_stride_a, args.batch_stride_b, args.batch_stride_d = a.stride(0), b.stride(0), d.stride(0)
     check(lib.dg_fp8_bmm(C.byref(args)))
 
@@ -639,10 +650,10 @@ def m_grouped_fp8_fp4_gemm_nt_contiguous(a, b, d, grouped_layout, recipe=None, r
         return
     sfa, sfb, gran_k_a, gran_k_b = _transform_sf_pair(a_sf, b_sf, m, n, k, recipe, recipe_a, recipe_b, None, num_groups,
                                                       disable_ue8m0_cast, grouped_layout if use_psum_layout else None)
-    _require(_resolve_alpha(None, epilogue) is None, "grouped GEMMs take the Identity epilogue only")
+    _require(_resolve_alpha(None, epilogue) is None, "grouped GEMMs take no alpha")
     args = _fill_args(a_data, sfa, b_data, sfb, d, m, n, k, num_groups, major_a, major_b, gran_k_a, gran_k_b,
                       layout=grouped_layout, expected_m=expected_m_for_psum_layout or 0, use_psum_layout=use_psum_layout,
-                      ensure_zero_padding=use_psum_layout and ensure_zero_padding)
+                      ensure_zero_padding=use_psum_layout and ensure_zero_padding, stochastic=_stochastic(epilogue, None, d))
     check(lib.dg_m_grouped_fp8_fp4_gemm_contiguous(C.byref(args)))
 
 
@@ -677,9 +688,9 @@ def m_grouped_fp8_fp4_gemm_nt_masked(a, b, d, masked_m, expected_m: int, recipe=
     _require(masked_m.dtype == torch.int, "masked_m.scalar_type() == torch::kInt")
     _check_cd(d)
     sfa, sfb, gran_k_a, gran_k_b = _transform_sf_pair(a_sf, b_sf, m, n, k, recipe, recipe_a, recipe_b, g, g, disable_ue8m0_cast)
-    _require(_resolve_alpha(None, epilogue) is None, "grouped GEMMs take the Identity epilogue only")
+    _require(_resolve_alpha(None, epilogue) is None, "grouped GEMMs take no alpha")
     args = _fill_args(a_data, sfa, b_data, sfb, d, m, n, k, g, major_a, major_b, gran_k_a, gran_k_b,
-                      layout=masked_m, expected_m=expected_m)
+                      layout=masked_m, expected_m=expected_m, stochastic=_stochastic(epilogue, None, d))
     check(lib.dg_m_grouped_fp8_fp4_gemm_masked(C.byref(args)))
 
 

@@ -91,6 +91,7 @@ constexpr uint32_t kGranKA     = DG_GRAN_K_A;
 constexpr uint32_t kGranKB     = DG_GRAN_K_B;
 constexpr bool     kDIsFP32    = DG_D_FP32 != 0;
 constexpr bool     kDIsFP8     = DG_D_FP8 != 0;
+constexpr bool     kStochastic = DG_STOCHASTIC_ROUNDING != 0;      // BF16 output rounded stochastically (quant_math.cuh)
 constexpr bool     kAccumulate = DG_ACCUMULATE != 0;
 constexpr uint32_t kRasterGroup = DG_RASTER_GROUP;
 constexpr bool     kSplitK     = DG_SPLIT_K != 0;
@@ -131,6 +132,7 @@ constexpr uint32_t SF_BLOCK_N = (BLOCK_N + 127) / 128 * 128;
 // 128-byte swizzle requires); the arithmetic lives in gemm_config.hpp, shared with the host heuristics
 constexpr uint32_t kDElemBytes = kDIsFP32 ? 4 : (kDIsFP8 ? 1 : 2);
 static_assert(!(kDIsFP32 && kDIsFP8), "one output type");
+static_assert(!kStochastic || (!kDIsFP32 && !kDIsFP8 && !kAccumulate), "stochastic rounding writes BF16 directly");
 static_assert(!kDIsFP8 || ((kGemmType == kDense || kGemmType == kBatched) && !kAccumulate && !kSplitK && BLOCK_N % 32 == 0),
               "the quantising epilogue serves the dense and batched GEMMs with tiles of whole 32-column scale groups");
 static_assert(kGemmType != kBatched || (kCluster == 1 && !kSplitK), "batched: one CTA per tile");
@@ -663,10 +665,17 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                     #pragma unroll
                     for (uint32_t l = 0; l < kLoadsPerTrip; ++l)
                         if (b + l < BLOCK_N / 16) {
-                            #pragma unroll
-                            for (uint32_t i = 0; i < 8; ++i)
-                                row[(b + l) * 8 + i] = pack_bf16x2(__uint_as_float(v[l][2 * i]) * p.alpha,
-                                                                   __uint_as_float(v[l][2 * i + 1]) * p.alpha);
+                            if constexpr (kStochastic) {
+                                #pragma unroll
+                                for (uint32_t j = 0; j < 4; ++j)       // quartets are aligned to absolute columns
+                                    stochastic_round_quartet(v[l][4 * j], v[l][4 * j + 1], v[l][4 * j + 2], v[l][4 * j + 3],
+                                                             (n0 + (b + l) * 16) / 4 + j, row[(b + l) * 8 + 2 * j], row[(b + l) * 8 + 2 * j + 1]);
+                            } else {
+                                #pragma unroll
+                                for (uint32_t i = 0; i < 8; ++i)
+                                    row[(b + l) * 8 + i] = pack_bf16x2(__uint_as_float(v[l][2 * i]) * p.alpha,
+                                                                       __uint_as_float(v[l][2 * i + 1]) * p.alpha);
+                            }
                         }
                 }
                 release_tmem();
@@ -735,9 +744,16 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                         for (uint32_t i = 0; i < 4; ++i) out[i] = row[g * (kGroupCols / 2) + c * 4 + i];
                     } else if constexpr (!kDIsFP32) {
                         const uint32_t l = (c * 8) / 16, i0 = (c * 8) % 16;
-                        #pragma unroll
-                        for (uint32_t i = 0; i < 4; ++i)
-                            out[i] = pack_bf16x2(__uint_as_float(v[l][i0 + 2 * i]), __uint_as_float(v[l][i0 + 2 * i + 1]));
+                        if constexpr (kStochastic) {
+                            #pragma unroll
+                            for (uint32_t j = 0; j < 2; ++j)
+                                stochastic_round_quartet(v[l][i0 + 4 * j], v[l][i0 + 4 * j + 1], v[l][i0 + 4 * j + 2], v[l][i0 + 4 * j + 3],
+                                                         (n0 + g * kGroupCols + c * 8) / 4 + j, out[2 * j], out[2 * j + 1]);
+                        } else {
+                            #pragma unroll
+                            for (uint32_t i = 0; i < 4; ++i)
+                                out[i] = pack_bf16x2(__uint_as_float(v[l][i0 + 2 * i]), __uint_as_float(v[l][i0 + 2 * i + 1]));
+                        }
                     } else {
                         const uint32_t l = (c * 4) / 16, i0 = (c * 4) % 16;
                         #pragma unroll

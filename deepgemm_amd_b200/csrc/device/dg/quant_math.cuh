@@ -32,4 +32,21 @@ __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float
 __device__ __forceinline__ float bf16_lo(uint32_t packed) { return __uint_as_float(packed << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t packed) { return __uint_as_float(packed & 0xFFFF0000u); }
 
+// Stochastic rounding of FP32 to BF16 as the reference's BF16StochasticRounding epilogue defines it
+// (tests/utils.py:53-79 of the reference states the arithmetic): the four values of columns 4q .. 4q+3 of a row are
+// hashed together with q into four 16-bit random numbers; each value's low 16 bits plus its random number carry into
+// the high 16 bits, which are the result.  Deterministic in the accumulator bits and the column, so reruns agree.
+__device__ __forceinline__ void stochastic_round_quartet(uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t quartet,
+                                                         uint32_t& packed_ab, uint32_t& packed_cd) {
+    uint32_t h = a * 0x5671d42bu + b * 0x9995e499u + c * 0xace1b8a5u + d * 0xe153538du + quartet;
+    h = (h ^ (h >> 23)) * 0x7feb352du;
+    h ^= h >> 16;
+    uint32_t h1 = h * 0x846ca68bu, h2 = h * 0xd35a2d97u;
+    h1 ^= h1 >> 11;
+    h2 ^= h2 >> 11;
+    auto round = [](uint32_t v, uint32_t random16) { return ((v >> 16) + (((v & 0xFFFFu) + random16) >> 16)) & 0xFFFFu; };
+    packed_ab = round(a, h1 & 0xFFFFu) | (round(b, h1 >> 16) << 16);
+    packed_cd = round(c, h2 & 0xFFFFu) | (round(d, h2 >> 16) << 16);
+}
+
 }  // namespace dg

@@ -70,6 +70,7 @@ struct Problem {
     int expected_m;
     bool write_padding;      // prefix-sum layout: also write the padding rows of D up to the next aligned row
     bool k_psum;             // k-grouped: grouped_layout holds prefix sums
+    bool stochastic;         // BF16 output rounded stochastically
 };
 
 int validate(int kind, const dg_gemm_args_t* a, bool need_pointers, Problem* p) {
@@ -140,6 +141,9 @@ int validate(int kind, const dg_gemm_args_t* a, bool need_pointers, Problem* p) 
     p->expected_m = a->expected_m;
     p->write_padding = kind == DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM && a->ensure_zero_padding != 0;
     p->k_psum = k_grouped && a->use_psum_layout != 0;
+    p->stochastic = a->stochastic_rounding != 0;
+    // "Stochastic rounding requires a direct BF16 output" (epilogue_class.hpp:104-107); the epilogues do not compose
+    if (p->stochastic) DG_REQUIRE(a->d_dtype == DG_BF16 && !a->accumulate && !a->has_alpha);
     if (a->m == 0 || a->n == 0 || a->k == 0) return DG_OK;                    // handled by the caller (gemm.hpp:17-53)
 
     if (p->a_fp4 || p->b_fp4) DG_REQUIRE(a->k % 128 == 0);                   // runtime_utils.hpp:133-135
@@ -251,7 +255,7 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
         // to pull in; slicing K lets wide tiles (little re-reading of A) still spread over all SMs.  Slices hold a
         // multiple of 4 K-blocks (one packed scale word); all work items run in one wave; the second pass costs a
         // launch plus S FP32 panels of traffic.
-        const bool can_split = p.kind == DG_GEMM_DENSE && !p.accumulate && !p.d_fp8 && cluster == 1 && halves == 1 && bk == 128 &&
+        const bool can_split = p.kind == DG_GEMM_DENSE && !p.accumulate && !p.d_fp8 && !p.stochastic && cluster == 1 && halves == 1 && bk == 128 &&
                                forced_splits != 1 && k_blocks >= 16;
         for (int bn = 16; bn <= 240; bn += 16) {
             if (forced_bn && bn != forced_bn) continue;
@@ -367,6 +371,7 @@ std::string generate_source(const Problem& p, const dg_gemm_config_t& cfg) {
       << "#define DG_GRAN_K_B " << p.gran_k_b << "\n"
       << "#define DG_D_FP32 " << ((p.d_fp32 || cfg.num_splits > 1) ? 1 : 0) << "\n"
       << "#define DG_D_FP8 " << (p.d_fp8 ? 1 : 0) << "\n"
+      << "#define DG_STOCHASTIC_ROUNDING " << (p.stochastic ? 1 : 0) << "\n"
       << "#define DG_ACCUMULATE " << (p.accumulate ? 1 : 0) << "\n"
       << "#define DG_RASTER_GROUP " << cfg.raster_group << "\n"
       << "#define DG_SPLIT_K " << (cfg.num_splits > 1 ? 1 : 0) << "\n"

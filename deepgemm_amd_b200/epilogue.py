@@ -1,7 +1,7 @@
 """Epilogue selectors of the reference's `deep_gemm.epilogue` submodule
-(csrc/jit_kernels/impls/epilogue_class.hpp:19-127).  Identity, Alpha and FP8Quantization are built (the last on the
-dense GEMM: D written as e4m3 with one UE8M0 scale per row and 32 columns into `sfd`); the stochastic-rounding epilogue
-is declared so that callers get a clear error instead of an AttributeError."""
+(csrc/jit_kernels/impls/epilogue_class.hpp:19-127): Identity; Alpha (dense GEMM); FP8Quantization (dense and batched
+GEMMs: D written as e4m3 with one UE8M0 scale per row and 32 columns into `sfd`); BF16StochasticRounding (any GEMM with
+a BF16 D that is written directly).  They do not compose."""
 from __future__ import annotations
 
 

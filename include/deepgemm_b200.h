@@ -177,6 +177,11 @@ typedef struct dg_gemm_args {
     int64_t batch_stride_a;
     int64_t batch_stride_b;
     int64_t batch_stride_d;
+    /* BF16StochasticRounding epilogue (epilogue_class.hpp:94-108, epilogue/operators.cuh:32-63): a BF16 D is rounded
+     * stochastically instead of to nearest; the random bits are a hash of the four FP32 accumulators of columns
+     * 4q .. 4q+3 and of q (tests/utils.py:53-79 states it), so the result is reproducible.  BF16 output only, not
+     * combined with accumulate or alpha; K is never sliced. */
+    int32_t stochastic_rounding;
 } dg_gemm_args_t;
 
 /* fp8_fp4_gemm_nt and, through major_a / major_b, nn / tn / tt (gemm.hpp:78-179). */

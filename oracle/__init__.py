@@ -17,7 +17,7 @@ from .quant import (  # noqa: F401
     align, ceil_div, bf16_round, ceil_to_ue8m0, pack_ue8m0_to_int, unpack_ue8m0_from_int,
     e4m3_encode, e4m3_decode, e2m1_encode, e2m1_decode,
     per_token_cast_to_fp8, per_block_cast_to_fp8, per_token_cast_to_fp4,
-    cast_back_from_fp8, cast_back_from_fp4, transpose_packed_fp4, fp4_to_e4m3_bytes,
+    cast_back_from_fp8, cast_back_from_fp4, transpose_packed_fp4, fp4_to_e4m3_bytes, stochastic_round_to_bf16,
 )
 from .layout import (  # noqa: F401
     get_tma_aligned_size, mn_major_tma_aligned_packed_ue8m0, mn_major_tma_aligned_fp32,

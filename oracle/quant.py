@@ -233,3 +233,24 @@ def fp4_to_e4m3_bytes(packed: np.ndarray) -> np.ndarray:
     out[:, 0::2] = _E2M1_TO_E4M3[lo & 7] | ((lo & 8) << 4)
     out[:, 1::2] = _E2M1_TO_E4M3[hi & 7] | ((hi & 8) << 4)
     return out
+
+
+def stochastic_round_to_bf16(x: np.ndarray) -> np.ndarray:
+    """float32 [..., n] (n % 4 == 0) -> bfloat16 bits (uint16) rounded stochastically as the reference's
+    BF16StochasticRounding epilogue does (tests/utils.py:53-79): the four values of columns 4q .. 4q+3 and q are hashed
+    into four 16-bit random numbers that are added to the values' low 16 bits before truncation."""
+    shape = x.shape
+    v = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64).reshape(*shape[:-1], -1, 4)
+    q = np.arange(shape[-1] // 4, dtype=np.uint64)
+    m32 = np.uint64(0xFFFFFFFF)
+    h = (v[..., 0] * np.uint64(0x5671d42b) + v[..., 1] * np.uint64(0x9995e499) + v[..., 2] * np.uint64(0xace1b8a5) +
+         v[..., 3] * np.uint64(0xe153538d) + q) & m32
+    h = ((h ^ (h >> np.uint64(23))) * np.uint64(0x7feb352d)) & m32
+    h ^= h >> np.uint64(16)
+    h1 = (h * np.uint64(0x846ca68b)) & m32
+    h2 = (h * np.uint64(0xd35a2d97)) & m32
+    h1 ^= h1 >> np.uint64(11)
+    h2 ^= h2 >> np.uint64(11)
+    rnd = np.stack((h1 & np.uint64(0xFFFF), h1 >> np.uint64(16), h2 & np.uint64(0xFFFF), h2 >> np.uint64(16)), axis=-1)
+    out = (v >> np.uint64(16)) + (((v & np.uint64(0xFFFF)) + rnd) >> np.uint64(16))
+    return out.astype(np.uint16).reshape(shape)

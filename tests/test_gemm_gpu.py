@@ -295,6 +295,35 @@ def test_fp8_quantising_epilogue_equals_bf16_output_followed_by_the_1x32_cast(m,
         dg.fp8_gemm_nt(a, b, d_bf16, recipe=(1, 1, 128), epilogue=FP8Quantization(sfd))
 
 
+@pytest.mark.parametrize("m,n,k", [(256, 512, 1024), (129, 304, 256), (1000, 2112, 1792)])
+@pytest.mark.parametrize("block_m", [128, 256])
+def test_stochastic_rounding_epilogue_is_the_hash_rounding_of_the_fp32_result(m, n, k, block_m, monkeypatch):
+    """BF16StochasticRounding: every BF16 output is the FP32 accumulator rounded with the random bits the reference's
+    test derives from the accumulators themselves (tests/utils.py:53-79), so the FP32 GEMM fixes it bit for bit."""
+    if block_m == 256 and m <= 128:
+        pytest.skip("256-row tiles need more than 128 rows")
+    from deepgemm_amd_b200.epilogue import BF16StochasticRounding
+    monkeypatch.setenv("DG_FORCE_BLOCK_M", str(block_m))
+    monkeypatch.setenv("DG_FORCE_SPLIT_K", "1")
+    qa, sfa, qb, sfb, _ = quantise_dense(seeded_bf16((m, k), 53), seeded_bf16((n, k), 54))
+    a = (fp8_cuda(qa), packed_sf_cuda(sfa)); b = (fp8_cuda(qb), packed_sf_cuda(sfb))
+    d32 = torch.empty((m, n), dtype=torch.float, device="cuda")
+    dg.fp8_gemm_nt(a, b, d32, recipe=(1, 1, 128))
+    want = oracle.stochastic_round_to_bf16(d32.cpu().numpy())
+    d = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    dg.reset_kernel_status()
+    dg.fp8_gemm_nt(a, b, d, recipe=(1, 1, 128), epilogue=BF16StochasticRounding())
+    assert dg.kernel_status() == 0
+    got = d.view(torch.int16).cpu().numpy().view(np.uint16)
+    assert np.array_equal(got, want)
+    # rounds up and down about equally often, unlike round-to-nearest it is unbiased on average
+    nearest = dg_bf16 = torch.empty_like(d)
+    dg.fp8_gemm_nt(a, b, nearest, recipe=(1, 1, 128))
+    assert (d != nearest).float().mean().item() > 0.2
+    err = (d.float() - d32).double().mean().item()
+    assert abs(err) < 5e-3 * d32.abs().double().mean().item()
+
+
 def test_fp32_scales_are_transformed_on_the_fly_like_the_legacy_recipe():
     # float32 SFA [m, k/128] and SFB [n/128, k/128] with the default recipe (1, 128, 128) (csrc/utils/layout.hpp:85-98)
     m, n, k = 128, 2112, 1024
