@@ -694,6 +694,160 @@ def m_grouped_fp8_fp4_gemm_nt_masked(a, b, d, masked_m, expected_m: int, recipe=
     check(lib.dg_m_grouped_fp8_fp4_gemm_masked(C.byref(args)))
 
 
+# ------------------------------------------------------------------------------------------------
+# BF16 GEMMs (csrc/apis/gemm.hpp:488-730): the same kernel with BF16 operands and no scales
+# ------------------------------------------------------------------------------------------------
+def _bf16_args(a, b, d, m, n, k, groups, major_a, major_b, **kw) -> GemmArgs:
+    args = GemmArgs()
+    args.a, args.b, args.d = a.data_ptr(), b.data_ptr(), d.data_ptr()
+    args.m, args.n, args.k, args.num_groups = m, n, k, groups
+    args.a_dtype = args.b_dtype = _lib.DG_BF16
+    args.d_dtype = _d_dtype(d)
+    args.major_a, args.major_b = major_a, major_b
+    args.lda, args.ldb, args.ldd = _ld(a, major_a), _ld(b, major_b), d.stride(-2)
+    args.gran_k_a = args.gran_k_b = 128
+    args.accumulate = int(kw.get("accumulate", False))
+    alpha = kw.get("alpha")
+    args.has_alpha, args.alpha = int(alpha is not None), float(alpha) if alpha is not None else 1.0
+    layout = kw.get("layout")
+    args.grouped_layout = layout.data_ptr() if layout is not None else None
+    args.expected_m = int(kw.get("expected_m", 0))
+    args.use_psum_layout, args.ensure_zero_padding = int(kw.get("use_psum_layout", False)), int(kw.get("ensure_zero_padding", False))
+    args.stochastic_rounding = int(kw.get("stochastic", False))
+    args.stream = _stream()
+    return args
+
+
+def _require_bf16(*tensors) -> None:
+    for t in tensors:
+        _require(t.dtype == torch.bfloat16, "a.scalar_type() == torch::kBFloat16")
+
+
+def bf16_gemm_nt(a, b, d, c=None, compiled_dims: str = "nk", alpha: Optional[float] = None, epilogue=None) -> None:
+    """D[M,N] = C + alpha * A[M,K] @ B[N,K]^T for BF16 A, B (csrc/apis/gemm.hpp:488-536); D BF16 or FP32."""
+    major_a, major_b = _major_ab(a), _major_ab(b)
+    _check_cd(d)
+    _require(a.dim() == 2 and b.dim() == 2 and d.dim() == 2, "t.dim() == N")
+    (m, k), (n, k_) = (a.shape, b.shape)
+    _require(m == d.size(0) and n == d.size(1) and k == k_, "m == m_ and n == n_ and k == k_")
+    _require_bf16(a, b)
+    _require(d.dtype in (torch.bfloat16, torch.float), "d.scalar_type() == torch::kBFloat16 or d.scalar_type() == torch::kFloat")
+    if m == 0 or n == 0:
+        return
+    is_cd_same = c is not None and c.data_ptr() == d.data_ptr()
+    if is_cd_same:
+        _require(c.shape == d.shape and c.stride() == d.stride(), "c->sizes() == d.sizes() and c->strides() == d.strides()")
+    if c is not None:
+        _check_cd(c)
+        _require(d.dtype == c.dtype, "d.scalar_type() == c.value().scalar_type()")
+    if k == 0:
+        if not is_cd_same:
+            d.copy_(c) if c is not None else d.zero_()
+        return
+    if c is not None and not is_cd_same:
+        d.copy_(c)
+    alpha = _resolve_alpha(alpha, epilogue)
+    args = _bf16_args(a, b, d, m, n, k, 1, major_a, major_b, accumulate=c is not None, alpha=alpha, stochastic=_stochastic(epilogue, c, d))
+    check(lib.dg_fp8_fp4_gemm(C.byref(args)))
+
+
+def bf16_gemm_nn(a, b, d, c=None, compiled_dims: str = "nk", alpha=None, epilogue=None) -> None:
+    bf16_gemm_nt(a, b.transpose(0, 1), d, c, compiled_dims, alpha, epilogue)
+
+
+def bf16_gemm_tn(a, b, d, c=None, compiled_dims: str = "mn", alpha=None, epilogue=None) -> None:
+    bf16_gemm_nt(a.transpose(0, 1), b.transpose(0, 1), d, c, compiled_dims, alpha, epilogue)
+
+
+def bf16_gemm_tt(a, b, d, c=None, compiled_dims: str = "mn", alpha=None, epilogue=None) -> None:
+    bf16_gemm_nt(a.transpose(0, 1), b, d, c, compiled_dims, alpha, epilogue)
+
+
+def m_grouped_bf16_gemm_nt_contiguous(a, b, d, grouped_layout, compiled_dims: str = "nk", use_psum_layout: bool = False,
+                                      ensure_zero_padding: bool = True, expected_m_for_psum_layout: Optional[int] = None,
+                                      epilogue=None) -> None:
+    """csrc/apis/gemm.hpp:562-628: the contiguous grouped GEMM with BF16 operands (either form of grouped_layout)."""
+    major_a, major_b = _major_ab(a), _major_ab(b)
+    _require(major_a == _lib.DG_MAJOR_K, "major_a == cute::UMMA::Major::K")
+    _require(grouped_layout.is_contiguous(), "grouped_layout.is_contiguous()")
+    _require(a.dim() == 2 and b.dim() == 3 and d.dim() == 2, "t.dim() == N")
+    m, k = a.shape
+    num_groups, n, k_ = b.shape
+    _require(m == d.size(0) and n == d.size(1) and k == k_, "m == m_ and n == n_ and k == k_")
+    _require(n > 0 and k > 0 and num_groups > 0, "n > 0 and k > 0 and num_groups > 0")
+    _require_bf16(a, b, d)
+    _require(grouped_layout.dtype == torch.int, "grouped_layout.scalar_type() == torch::kInt")
+    if use_psum_layout:
+        _require(grouped_layout.numel() == num_groups, "num_groups == num_groups_")
+    else:
+        _require(grouped_layout.numel() == m, "m == m__")
+        _require(expected_m_for_psum_layout is None, "not expected_m_for_psum_layout.has_value()")
+    _check_cd(d)
+    if m == 0:
+        return
+    _require(_resolve_alpha(None, epilogue) is None, "grouped GEMMs take no alpha")
+    args = _bf16_args(a, b, d, m, n, k, num_groups, major_a, major_b, layout=grouped_layout,
+                      expected_m=expected_m_for_psum_layout or 0, use_psum_layout=use_psum_layout,
+                      ensure_zero_padding=use_psum_layout and ensure_zero_padding, stochastic=_stochastic(epilogue, None, d))
+    check(lib.dg_m_grouped_fp8_fp4_gemm_contiguous(C.byref(args)))
+
+
+def m_grouped_bf16_gemm_nn_contiguous(a, b, d, grouped_layout, compiled_dims: str = "nk", use_psum_layout: bool = False,
+                                      ensure_zero_padding: bool = True, epilogue=None) -> None:
+    m_grouped_bf16_gemm_nt_contiguous(a, b.transpose(-1, -2), d, grouped_layout, compiled_dims, use_psum_layout, ensure_zero_padding,
+                                      None, epilogue)
+
+
+def m_grouped_bf16_gemm_nt_masked(a, b, d, masked_m, expected_m: int, compiled_dims: str = "nk", epilogue=None) -> None:
+    """csrc/apis/gemm.hpp:630-674."""
+    major_a, major_b = _major_ab(a), _major_ab(b)
+    _require(major_a == _lib.DG_MAJOR_K and major_b == _lib.DG_MAJOR_K, "major_a == cute::UMMA::Major::K and major_b == cute::UMMA::Major::K")
+    _require(masked_m.is_contiguous(), "masked_m.is_contiguous()")
+    _require(a.dim() == 3 and b.dim() == 3 and d.dim() == 3, "t.dim() == N")
+    g, m, k = a.shape
+    g_, n, k_ = b.shape
+    _require(g == g_ == d.size(0) == masked_m.numel(), "num_groups == num_groups_ and num_groups == num_groups__ and num_groups == num_groups___")
+    _require(m == d.size(1) and n == d.size(2) and k == k_, "m == m_ and n == n_ and k == k_")
+    _require(expected_m > 0 and m > 0 and n > 0 and k > 0 and g > 0, "expected_m > 0 and m > 0 and n > 0 and k > 0 and num_groups > 0")
+    _require_bf16(a, b, d)
+    _require(masked_m.dtype == torch.int, "masked_m.scalar_type() == torch::kInt")
+    _check_cd(d)
+    _require(_resolve_alpha(None, epilogue) is None, "grouped GEMMs take no alpha")
+    args = _bf16_args(a, b, d, m, n, k, g, major_a, major_b, layout=masked_m, expected_m=expected_m, stochastic=_stochastic(epilogue, None, d))
+    check(lib.dg_m_grouped_fp8_fp4_gemm_masked(C.byref(args)))
+
+
+def k_grouped_bf16_gemm_tn_contiguous(a, b, d, ks_cpu, grouped_layout, c=None, compiled_dims: str = "mn", use_psum_layout: bool = False,
+                                      epilogue=None) -> None:
+    """csrc/apis/gemm.hpp:676-730: D[g] = C[g] + A[slice g]^T @ B[slice g] for BF16 A [sum_k, M], B [sum_k, N]."""
+    _require(d.dim() == 3 and a.dim() == 2 and b.dim() == 2, "t.dim() == N")
+    num_groups, m, n = d.shape
+    k_alignment = get_mk_alignment_for_contiguous_layout()
+    _require(k_alignment % 128 == 0, "k_alignment % 128 == 0")
+    sum_k = _k_grouped_sizes(ks_cpu, grouped_layout, num_groups, use_psum_layout, k_alignment, a.size(0))
+    _require(m == a.size(1) and n == b.size(1) and sum_k == a.size(0) == b.size(0), "m == m_ and n == n_ and sum_k == sum_k_ and sum_k == sum_k__")
+    _require(a.is_contiguous() and b.is_contiguous() and d.is_contiguous(), "a.is_contiguous()")
+    _require(c is None or c.is_contiguous(), "not c.has_value() or c.value().is_contiguous()")
+    _require_bf16(a, b)
+    _require(d.dtype in (torch.bfloat16, torch.float), "d.scalar_type() == torch::kBFloat16 or d.scalar_type() == torch::kFloat")
+    if m == 0 or n == 0:
+        return
+    is_cd_same = c is not None and c.data_ptr() == d.data_ptr()
+    if c is not None:
+        _require(d.dtype == c.dtype and c.shape == d.shape, "d.scalar_type() == c.value().scalar_type()")
+    if sum_k == 0:
+        if not is_cd_same:
+            d.copy_(c) if c is not None else d.zero_()
+        return
+    if c is not None and not is_cd_same:
+        d.copy_(c)
+    _require(_resolve_alpha(None, epilogue) is None, "k-grouped GEMMs take no alpha")
+    args = _bf16_args(a, b, d.view(num_groups * m, n), m, n, sum_k, num_groups, _lib.DG_MAJOR_MN, _lib.DG_MAJOR_MN,
+                      accumulate=c is not None, layout=grouped_layout, use_psum_layout=use_psum_layout, stochastic=_stochastic(epilogue, c, d))
+    args.lda, args.ldb, args.ldd = m, n, n
+    check(lib.dg_k_grouped_fp8_gemm_contiguous(C.byref(args)))
+
+
 # Aliases registered by the reference (csrc/apis/gemm.hpp:922-930)
 fp8_gemm_nt, fp8_gemm_nn, fp8_gemm_tn, fp8_gemm_tt = fp8_fp4_gemm_nt, fp8_fp4_gemm_nn, fp8_fp4_gemm_tn, fp8_fp4_gemm_tt
 fp4_gemm_nt = fp8_fp4_gemm_nt

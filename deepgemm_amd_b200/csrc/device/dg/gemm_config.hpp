@@ -22,6 +22,8 @@ struct GemmLayout {
     uint32_t b_mn_major = 0;                       // B stored with N contiguous: staged as 128-column atoms of [128 K][128 B]
     uint32_t gran_k_a = 128, gran_k_b = 128;       // elements of K per scale (a packed scale word holds four scales)
     uint32_t short_k = 0;                          // a work item has fewer K-blocks than there are stages
+    uint32_t ab_elem_bytes = 1;                    // 1: FP8 / FP4 operands with block scales; 2: BF16 operands, no scales
+                                                   // (block_k stays the byte width of a K-major stage row)
 
     // A packed scale word covers 4 * gran_k elements of K: it is fetched on every `period`-th K-block of a work item,
     // into the next of a ring of buffers.  A buffer may be refilled once the fetch it held is no longer among the
@@ -31,6 +33,7 @@ struct GemmLayout {
     DG_HDC uint32_t sfa_period() const { return 4 * gran_k_a / block_k; }
     DG_HDC uint32_t sfb_period() const { return 4 * gran_k_b / block_k; }
     DG_HDC uint32_t sf_buffers(uint32_t period) const {
+        if (ab_elem_bytes != 1) return 0;
         const uint32_t n = (num_stages + period - 1) / period + 1;
         return short_k || n > num_stages ? num_stages : n;
     }
@@ -56,8 +59,9 @@ struct GemmLayout {
 
     DG_HDC uint32_t a_bytes() const { return block_m * block_k; }        // one byte per element (FP8, or FP4 in 16-byte containers)
     DG_HDC uint32_t load_block_n() const { return block_n / cluster; }
-    DG_HDC uint32_t b_atoms() const { return (load_block_n() + 127) / 128; }      // MN-major only
-    DG_HDC uint32_t b_bytes() const { return b_mn_major ? b_atoms() * 128 * block_k : load_block_n() * block_k; }
+    // MN-major only: atoms of [block_k / ab_elem_bytes rows of K][128 bytes of N]
+    DG_HDC uint32_t b_atoms() const { return (load_block_n() * ab_elem_bytes + 127) / 128; }
+    DG_HDC uint32_t b_bytes() const { return b_mn_major ? b_atoms() * 128 * (block_k / ab_elem_bytes) : load_block_n() * block_k; }
     DG_HDC uint32_t sfa_bytes() const { return block_m * 4; }
     DG_HDC uint32_t sfb_bytes() const { return sf_block_n() * 4; }
 
@@ -75,7 +79,7 @@ struct GemmLayout {
     // halves of one tile when it is 256), then SFA (4 columns per 128 rows) and SFB (4 columns per 128 columns of the tile)
     DG_HDC uint32_t tmem_col_sfa() const { return 2 * block_n; }
     DG_HDC uint32_t tmem_col_sfb() const { return tmem_col_sfa() + block_m / 32; }
-    DG_HDC uint32_t tmem_cols_used() const { return tmem_col_sfb() + sf_block_n() / 32; }
+    DG_HDC uint32_t tmem_cols_used() const { return ab_elem_bytes != 1 ? 2 * block_n : tmem_col_sfb() + sf_block_n() / 32; }
     DG_HDC uint32_t tmem_cols_alloc() const {
         const uint32_t u = tmem_cols_used();
         return u <= 32 ? 32 : u <= 64 ? 64 : u <= 128 ? 128 : u <= 256 ? 256 : 512;

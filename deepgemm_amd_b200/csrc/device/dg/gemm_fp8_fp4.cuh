@@ -39,6 +39,10 @@
 // is three-dimensional with the batch outermost, so operands and D may have any batch stride (the permuted views of
 // the einsum expressions) and rows beyond M are clipped per batch.
 //
+// DG_AB_BF16: A and B are bfloat16 and there are no scales (the reference's sm100_bf16_gemm family): a stage row is still
+// 128 bytes, now 64 elements of K; the MMA is tcgen05.mma.kind::f16 (16 elements of K per instruction); the scale loads,
+// the rearranging warp's work and the scale columns of tensor memory disappear; MN-major atoms are 64 elements wide.
+//
 // DG_SPLIT_K (dense only, for shapes with too few output tiles to fill the GPU): every output tile becomes
 // num_splits work items over slices of K, and the kernel's D is an FP32 workspace of num_splits stacked
 // [rows x N] panels: work item (tile, slice) stores its partial tile into panel `slice`.  A separate kernel
@@ -80,7 +84,12 @@ namespace dg {
 constexpr uint32_t kGemmType   = DG_GEMM_TYPE;
 constexpr uint32_t BLOCK_M     = 128;
 constexpr uint32_t BLOCK_N     = DG_BLOCK_N;
-constexpr uint32_t BLOCK_K     = DG_BLOCK_K;       // elements of K per pipeline stage (64 or 128)
+constexpr uint32_t BLOCK_K     = DG_BLOCK_K;       // bytes of K per row of a pipeline stage (64 or 128)
+constexpr bool     kABIsBF16   = DG_AB_BF16 != 0;
+constexpr uint32_t kABElemBytes = kABIsBF16 ? 2 : 1;
+constexpr uint32_t BLOCK_K_ELEMS = BLOCK_K / kABElemBytes;         // elements of K per pipeline stage
+constexpr bool     kHasSF      = !kABIsBF16;                       // block-scaled operands
+constexpr uint32_t kAtomElems  = 128 / kABElemBytes;               // MN-major staging: elements of MN per 128-byte atom row
 constexpr uint32_t kNumStages  = DG_NUM_STAGES;
 constexpr uint32_t kCluster    = DG_CLUSTER;       // CTAs cooperating on one tile (1 or 2)
 constexpr bool     kAIsFP4     = DG_A_FP4 != 0;
@@ -107,7 +116,8 @@ constexpr uint32_t kNumThreads = 128 + 128 * kMHalves, kNumEpilogueThreads = 128
 // Tensor memory holds two accumulators: two tiles in flight, or the two halves of one
 constexpr uint32_t kNumAccumStages = kMHalves == 1 ? 2 : 1;
 
-static_assert(BLOCK_N % 16 == 0 && BLOCK_N >= 16 && BLOCK_N <= 240, "UMMA_N must be a multiple of 16 that leaves room for the scales");
+static_assert(BLOCK_N % 16 == 0 && BLOCK_N >= 16 && BLOCK_N <= (kHasSF ? 240 : 256), "UMMA_N must be a multiple of 16 that leaves room for the scales");
+static_assert(!kABIsBF16 || (!kAIsFP4 && !kBIsFP4 && BLOCK_K == 128), "BF16 operands: 128-byte stages");
 static_assert(kGranKA == 32 || kGranKA == 128, "one scale per 32 or 128 elements of K");
 static_assert(kGranKB == 32 || kGranKB == 128, "one scale per 32 or 128 elements of K");
 static_assert(kNumStages >= 2 && kNumStages <= 32, "pipeline depth");
@@ -137,8 +147,8 @@ static_assert(!kDIsFP8 || ((kGemmType == kDense || kGemmType == kBatched) && !kA
               "the quantising epilogue serves the dense and batched GEMMs with tiles of whole 32-column scale groups");
 static_assert(kGemmType != kBatched || (kCluster == 1 && !kSplitK), "batched: one CTA per tile");
 constexpr GemmLayout kLayout{CTA_M, BLOCK_N, BLOCK_K, kNumStages, kDElemBytes, kCluster, kBMnMajor ? 1u : 0u, kGranKA, kGranKB,
-                             DG_SHORT_K};
-constexpr uint32_t kNumSFABuffers = kLayout.sfa_buffers(), kNumSFBBuffers = kLayout.sfb_buffers();
+                             DG_SHORT_K, kABElemBytes};
+constexpr uint32_t kNumSFABuffers = kHasSF ? kLayout.sfa_buffers() : 1, kNumSFBBuffers = kHasSF ? kLayout.sfb_buffers() : 1;
 static_assert(kSFAPeriod >= 1 && kSFBPeriod >= 1 && kSFAPeriod == kLayout.sfa_period() && kSFBPeriod == kLayout.sfb_period(), "scale fetch period");
 constexpr uint32_t kBAtoms = kLayout.b_atoms();            // 128-column atoms of an MN-major B tile
 constexpr uint32_t kStoreRowBytes   = kLayout.store_row_bytes();     // row width of the boxes covering the ragged end of a tile row
@@ -260,7 +270,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
     if (warp_idx == 1 && lane == 0) {
         for (uint32_t s = 0; s < kNumStages; ++s) {
             // per CTA of the cluster: the producer's arrive + the 32 lanes of the scale warp (used in CTA 0 only)
-            mbar_init(full_bar(s), kCluster * (1 + 32));
+            mbar_init(full_bar(s), kCluster * (1 + (kHasSF ? 32 : 0)));
             mbar_init(sf_full_bar(s), 1);
             mbar_init(empty_bar(s), 1);          // tcgen05.commit
         }
@@ -297,7 +307,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
     griddep_wait();
     griddep_launch_dependents();
 
-    const uint32_t num_k_blocks = (p.shape_k + BLOCK_K - 1) / BLOCK_K;
+    const uint32_t num_k_blocks = (p.shape_k + BLOCK_K_ELEMS - 1) / BLOCK_K_ELEMS;
     const uint32_t sfa_rows_per_group = (p.shape_k + kGranKA * 4 - 1) / (kGranKA * 4);   // packed K extent of SFA
     const uint32_t sfb_rows_per_group = (p.shape_k + kGranKB * 4 - 1) / (kGranKB * 4);
 
@@ -312,6 +322,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
         sched.group_alignment = p.group_alignment;
         sched.k_psum = DG_K_PSUM;
         sched.k_per_sf_row = 4 * kGranKA;
+        sched.k_per_block = BLOCK_K_ELEMS;
     }
     // K-blocks [kb_begin, kb_end) of a work item: all of K unless the GEMM is split
     auto kb_begin = [&](const Tile& t) { return kSplitK ? t.split * p.kb_per_split : 0u; };
@@ -391,14 +402,16 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                         DG_PROF_BEGIN(prof_w);
                         if (!mbar_wait(empty_bar(stage), phase ^ 1, ctx, kRoleProducer, 1)) { ok = false; break; }
                         DG_PROF_ADD(prof_wait, prof_w);
-                        uint32_t sf_bytes = 0;
-                        if (kb % kSFAPeriod == 0) sf_bytes += kSFABytes;
-                        if (kb % kSFBPeriod == 0) sf_bytes += kSFBBytes;
-                        mbar_arrive_expect_tx(sf_full_bar(stage), sf_bytes);
-                        if (kb % kSFAPeriod == 0)
-                            tma_in(sfa_buffer(), &tm_sfa, sf_full_bar(stage), sfa_mn, sfa_row0 + kb / kSFAPeriod, tile.group);
-                        if (kb % kSFBPeriod == 0)
-                            tma_in(sfb_buffer(), &tm_sfb, sf_full_bar(stage), tile.n_block * BLOCK_N, sfb_row0 + kb / kSFBPeriod, tile.group);
+                        if constexpr (kHasSF) {
+                            uint32_t sf_bytes = 0;
+                            if (kb % kSFAPeriod == 0) sf_bytes += kSFABytes;
+                            if (kb % kSFBPeriod == 0) sf_bytes += kSFBBytes;
+                            mbar_arrive_expect_tx(sf_full_bar(stage), sf_bytes);
+                            if (kb % kSFAPeriod == 0)
+                                tma_in(sfa_buffer(), &tm_sfa, sf_full_bar(stage), sfa_mn, sfa_row0 + kb / kSFAPeriod, tile.group);
+                            if (kb % kSFBPeriod == 0)
+                                tma_in(sfb_buffer(), &tm_sfb, sf_full_bar(stage), tile.n_block * BLOCK_N, sfb_row0 + kb / kSFBPeriod, tile.group);
+                        }
                         // With a cluster the copies land in this CTA and their bytes are counted on CTA 0's barrier,
                         // which expects both CTAs' bytes
                         const uint32_t load_bar = kCluster == 1 ? full_bar(stage) : in_leader(full_bar(stage));
@@ -410,19 +423,21 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                         };
                         // K-major: x = K, y = row.  MN-major: x = row (column of the stored matrix), y = K (+ the group's K offset)
                         if constexpr (!kAMnMajor) {
-                            load(smem_base + kSmemA + stage * kABytes, &tm_a, k_base + kb * BLOCK_K, a_row);      // one box of CTA_M rows
+                            load(smem_base + kSmemA + stage * kABytes, &tm_a, k_base + kb * BLOCK_K_ELEMS, a_row);      // one box of CTA_M rows
                         } else {
+                            // one box per atom: 128 bytes of M (128 FP8 or 64 BF16 elements) by the stage's rows of K
                             #pragma unroll
-                            for (uint32_t h = 0; h < kMHalves; ++h)
-                                load(smem_base + kSmemA + stage * kABytes + h * BLOCK_M * BLOCK_K, &tm_a, a_row + h * BLOCK_M, k_base + kb * BLOCK_K);
+                            for (uint32_t i = 0; i < CTA_M / kAtomElems; ++i)
+                                load(smem_base + kSmemA + stage * kABytes + i * 128 * BLOCK_K_ELEMS, &tm_a, a_row + i * kAtomElems,
+                                     k_base + kb * BLOCK_K_ELEMS);
                         }
                         if constexpr (!kBMnMajor) {
-                            load(smem_base + kSmemB + stage * kBBytes, &tm_b, k_base + kb * BLOCK_K, b_row);
+                            load(smem_base + kSmemB + stage * kBBytes, &tm_b, k_base + kb * BLOCK_K_ELEMS, b_row);
                         } else {
                             #pragma unroll
                             for (uint32_t i = 0; i < kBAtoms; ++i)
-                                load(smem_base + kSmemB + stage * kBBytes + i * 128 * BLOCK_K, &tm_b,
-                                     tile.n_block * BLOCK_N + cta_rank * LOAD_BLOCK_N + i * 128, b_k_base + kb * BLOCK_K);
+                                load(smem_base + kSmemB + stage * kBBytes + i * 128 * BLOCK_K_ELEMS, &tm_b,
+                                     tile.n_block * BLOCK_N + cta_rank * LOAD_BLOCK_N + i * kAtomElems, b_k_base + kb * BLOCK_K_ELEMS);
                         }
                         advance_sf(kb);
                     }
@@ -435,15 +450,18 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
         } else if (warp_idx == 1) {
             // ================= MMA issuer (CTA 0 of the cluster only) =================
             if (lane == 0 && is_leader) {
-                constexpr uint32_t idesc = make_instr_desc_block_scaled(kAIsFP4 ? kFmtE2M1 : kFmtE4M3, kBIsFP4 ? kFmtE2M1 : kFmtE4M3,
-                                                                        kAMnMajor, kBMnMajor, UMMA_M, UMMA_N);
+                constexpr uint32_t idesc = kABIsBF16 ? make_instr_desc_bf16(kAMnMajor, kBMnMajor, UMMA_M, UMMA_N)
+                                                     : make_instr_desc_block_scaled(kAIsFP4 ? kFmtE2M1 : kFmtE4M3, kBIsFP4 ? kFmtE2M1 : kFmtE4M3,
+                                                                                    kAMnMajor, kBMnMajor, UMMA_M, UMMA_N);
                 // K-major: 8-row groups of BLOCK_K-byte rows (SBO 1024 or 512, swizzle span = the row), +32 B per UMMA along K.
                 // MN-major: atoms of [128 K][128 B]; SBO 1024 = eight K rows, LBO = one atom, +32 rows (4096 B) per UMMA along K.
-                constexpr uint32_t kALbo = kAMnMajor ? 128 * BLOCK_K : 0, kBLbo = kBMnMajor ? 128 * BLOCK_K : 0;
+                constexpr uint32_t kALbo = kAMnMajor ? 128 * BLOCK_K_ELEMS : 0, kBLbo = kBMnMajor ? 128 * BLOCK_K_ELEMS : 0;
                 constexpr uint32_t kASbo = kAMnMajor ? 1024 : 8 * BLOCK_K, kBSbo = kBMnMajor ? 1024 : 8 * BLOCK_K;
                 constexpr uint64_t kASwizzle = kAMnMajor || BLOCK_K == 128 ? kSwizzle128B : kSwizzle64B;
                 constexpr uint64_t kBSwizzle = kBMnMajor || BLOCK_K == 128 ? kSwizzle128B : kSwizzle64B;
-                constexpr uint32_t kAStepK = (kAMnMajor ? UMMA_K * 128 : UMMA_K) >> 4, kBStepK = (kBMnMajor ? UMMA_K * 128 : UMMA_K) >> 4;
+                // (UMMA_K is 32 bytes of K: 32 FP8 or 16 BF16 elements, i.e. that many rows of an MN-major atom)
+                constexpr uint32_t kAStepK = (kAMnMajor ? UMMA_K / kABElemBytes * 128 : UMMA_K) >> 4;
+                constexpr uint32_t kBStepK = (kBMnMajor ? UMMA_K / kABElemBytes * 128 : UMMA_K) >> 4;
                 // A commit reaches the barrier at the same offset in every CTA of the cluster
                 auto commit_all = [&](uint32_t bar) {
                     if constexpr (kCluster == 1) {
@@ -482,13 +500,13 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                         tc_fence_after_sync();
                         // Scales: shared memory (rearranged by warp 2) -> tensor memory, in every CTA of the cluster
                         DG_PROF_BEGIN(prof_i0);
-                        if (kb % kSFAPeriod == 0) {
+                        if (kHasSF && kb % kSFAPeriod == 0) {
                             #pragma unroll
                             for (uint32_t i = 0; i < SF_BLOCK_M / 128; ++i)
                                 tc_cp_32x128b_warpx4<kCluster>(tmem_base + kTmemColSFA + i * 4,
                                                                make_smem_desc(sfa_buffer() + i * 512, 0, 128, kSwizzleNone));
                         }
-                        if (kb % kSFBPeriod == 0) {
+                        if (kHasSF && kb % kSFBPeriod == 0) {
                             #pragma unroll
                             for (uint32_t i = 0; i < SF_BLOCK_N / 128; ++i)
                                 tc_cp_32x128b_warpx4<kCluster>(tmem_base + kTmemColSFB + i * 4,
@@ -511,9 +529,13 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                                 const uint32_t sfa_id = ((kb * BLOCK_K + j * UMMA_K) / kGranKA) % 4;
                                 const uint32_t sfb_id = ((kb * BLOCK_K + j * UMMA_K) / kGranKB) % 4;
                                 // Advancing K moves the start address: +32 B inside the swizzle atom (K-major) or +32 rows (MN-major)
-                                tc_mma_mxf8f6f4<kCluster>(tmem_d, a_desc + h * ((BLOCK_M * BLOCK_K) >> 4) + j * kAStepK, b_desc + j * kBStepK,
-                                                          instr_desc_with_sf_ids(idesc, sfa_id, sfb_id),
-                                                          tmem_base + kTmemColSFA + h * 4, tmem_base + kTmemColSFB, ((kb - kb0) | j) != 0);
+                                if constexpr (kABIsBF16)
+                                    tc_mma_bf16<kCluster>(tmem_d, a_desc + h * ((BLOCK_M * BLOCK_K) >> 4) + j * kAStepK, b_desc + j * kBStepK,
+                                                          idesc, ((kb - kb0) | j) != 0);
+                                else
+                                    tc_mma_mxf8f6f4<kCluster>(tmem_d, a_desc + h * ((BLOCK_M * BLOCK_K) >> 4) + j * kAStepK, b_desc + j * kBStepK,
+                                                              instr_desc_with_sf_ids(idesc, sfa_id, sfb_id),
+                                                              tmem_base + kTmemColSFA + h * 4, tmem_base + kTmemColSFB, ((kb - kb0) | j) != 0);
                             }
                         }
                         DG_PROF_ADD(prof_mma, prof_i1);
@@ -536,7 +558,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                 DG_PROF_FLUSH(kProfMmaIssueMma, prof_mma);
                 DG_PROF_FLUSH(kProfMmaIssueCommit, prof_commit);
             }
-        } else if (warp_idx == 2) {
+        } else if (warp_idx == 2 && kHasSF) {
             // ================= scale rearrangement =================
             // tcgen05.cp reads 32 rows x 16 bytes and writes row r to lane r: the scale word of tile row
             // (c * 32 + r) has to sit at word (r * 4 + c).  TMA delivered the 128 words in row order.

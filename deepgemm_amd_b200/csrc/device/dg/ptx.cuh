@@ -293,6 +293,13 @@ __host__ __device__ constexpr uint32_t make_instr_desc_block_scaled(uint32_t a_f
          | ((umma_n >> 3) << 17) | (1u << 23) | ((umma_m >> 4) << 24);
 }
 
+// Instruction descriptor of kind::f16 (BF16 inputs, FP32 accumulation):
+//   [4,6) D format (1 = F32)   [7,10) A format (1 = BF16)   [10,13) B format   [15] / [16] A / B MN-major
+//   [17,23) N >> 3             [24,29) M >> 4
+__host__ __device__ constexpr uint32_t make_instr_desc_bf16(uint32_t a_mn_major, uint32_t b_mn_major, uint32_t umma_m, uint32_t umma_n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (a_mn_major << 15) | (b_mn_major << 16) | ((umma_n >> 3) << 17) | ((umma_m >> 4) << 24);
+}
+
 __device__ __forceinline__ uint32_t instr_desc_with_sf_ids(uint32_t idesc, uint32_t sfa_id, uint32_t sfb_id) {
     return idesc | (sfb_id << 4) | (sfa_id << 29);
 }
@@ -324,6 +331,21 @@ __device__ __forceinline__ void tc_mma_mxf8f6f4(uint32_t tmem_d, uint64_t desc_a
             "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
             "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
             :: "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb) : "memory");
+}
+
+// D[tmem] (+)= A[smem] * B[smem] for BF16 inputs (K = 16 elements per instruction), no scales.
+template <int kCtaGroup>
+__device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    if constexpr (kCtaGroup == 1)
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            :: "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+    else
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            :: "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
 }
 
 // Make an mbarrier track completion of every tcgen05 operation this thread issued so far.

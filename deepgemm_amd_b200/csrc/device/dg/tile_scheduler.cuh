@@ -50,7 +50,7 @@ struct Tile {
     uint32_t mn_index;      // linear index of the output tile (slot of its split-K partials and counter)
     // k-grouped only
     uint32_t k_base;        // first element of K of the group's slice
-    uint32_t num_kb;        // 128-element K-blocks in the slice (0: an empty group)
+    uint32_t num_kb;        // K-blocks (pipeline stages) in the slice (0: an empty group)
     uint32_t sf_row_base;   // first packed scale row of the group
 };
 
@@ -71,7 +71,7 @@ struct TileScheduler {
     uint32_t group_start, group_alignment, write_padding;
     // k-grouped only: first element of K and first packed scale row of the current group; whether layout holds
     // prefix sums; elements of K per packed scale row (4 scales)
-    uint32_t k_start, sf_row_start, k_psum, k_per_sf_row;
+    uint32_t k_start, sf_row_start, k_psum, k_per_sf_row, k_per_block;     // k_per_block: elements of K per pipeline stage
 
     DG_HD TileScheduler(uint32_t block_m_, uint32_t block_n_, uint32_t raster_group_,
                         uint32_t shape_m_, uint32_t shape_n_, uint32_t num_groups_, const int* layout_,
@@ -80,7 +80,7 @@ struct TileScheduler {
           num_m_blocks((shape_m_ + block_m_ - 1) / block_m_), num_n_blocks((shape_n_ + block_n_ - 1) / block_n_),
           layout(layout_), cta(cta_), num_ctas(num_ctas_), iter(0), num_splits(num_splits_ == 0 ? 1 : num_splits_),
           cur_group(0), group_first_tile(0), group_start(0), group_alignment(128), write_padding(0),
-          k_start(0), sf_row_start(0), k_psum(0), k_per_sf_row(512) {}
+          k_start(0), sf_row_start(0), k_psum(0), k_per_sf_row(512), k_per_block(128) {}
 
     // Linear index inside an (mb x num_n_blocks) grid -> (m, n)
     DG_HD void rasterise(uint32_t idx, uint32_t mb, uint32_t& m, uint32_t& n) const {
@@ -155,7 +155,7 @@ struct TileScheduler {
             t.split = 0;
             t.mn_index = tile_id;
             t.k_base = k_start;
-            t.num_kb = (len + 127) / 128;
+            t.num_kb = (len + k_per_block - 1) / k_per_block;
             t.sf_row_base = sf_row_start;
             return true;
         } else if constexpr (kKind == kMGroupedPsum) {

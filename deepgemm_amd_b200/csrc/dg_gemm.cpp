@@ -65,7 +65,7 @@ unsigned long long* profile_buffer() {
 struct Problem {
     int kind;
     int m, n, k, groups;
-    bool a_fp4, b_fp4, d_fp32, d_fp8, accumulate, a_mn_major, b_mn_major;
+    bool a_fp4, b_fp4, ab_bf16, d_fp32, d_fp8, accumulate, a_mn_major, b_mn_major;
     int gran_k_a, gran_k_b;
     int expected_m;
     bool write_padding;      // prefix-sum layout: also write the padding rows of D up to the next aligned row
@@ -78,16 +78,18 @@ int validate(int kind, const dg_gemm_args_t* a, bool need_pointers, Problem* p) 
     DG_REQUIRE(kind == DG_GEMM_DENSE || kind == DG_GEMM_M_GROUPED_CONTIGUOUS || kind == DG_GEMM_M_GROUPED_MASKED ||
                kind == DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM || kind == DG_GEMM_K_GROUPED_CONTIGUOUS || kind == DG_GEMM_BATCHED);
     const bool k_grouped = kind == DG_GEMM_K_GROUPED_CONTIGUOUS, batched = kind == DG_GEMM_BATCHED;
-    DG_REQUIRE(a->a_dtype == DG_FP8_E4M3 || a->a_dtype == DG_FP4_E2M1_X2);
-    DG_REQUIRE(a->b_dtype == DG_FP8_E4M3 || a->b_dtype == DG_FP4_E2M1_X2);
+    // BF16 operands (no scales): the reference's bf16_gemm_* family, same kernel with the scale path compiled out
+    const bool ab_bf16 = a->a_dtype == DG_BF16 && a->b_dtype == DG_BF16;
+    DG_REQUIRE(ab_bf16 || a->a_dtype == DG_FP8_E4M3 || a->a_dtype == DG_FP4_E2M1_X2);
+    DG_REQUIRE(ab_bf16 || a->b_dtype == DG_FP8_E4M3 || a->b_dtype == DG_FP4_E2M1_X2);
     DG_REQUIRE(a->d_dtype == DG_BF16 || a->d_dtype == DG_FP32 || a->d_dtype == DG_FP8_E4M3);
     if (kind != DG_GEMM_DENSE && !k_grouped && !batched) DG_REQUIRE(a->d_dtype == DG_BF16);            // gemm.hpp:209,299
     if (k_grouped) DG_REQUIRE(a->d_dtype == DG_BF16 || a->d_dtype == DG_FP32);
     if (batched) {
         // einsum.hpp:183-243: [B, M, K] x [B, N, K]^T -> [B, M, N], any batch strides that a tensor map can express
         DG_REQUIRE(a->num_groups > 0 && !a->has_alpha);
-        DG_REQUIRE(a->a_dtype == DG_FP8_E4M3 && a->b_dtype == DG_FP8_E4M3);
-        DG_REQUIRE(a->batch_stride_a % 16 == 0 && a->batch_stride_b % 16 == 0);
+        DG_REQUIRE(ab_bf16 || (a->a_dtype == DG_FP8_E4M3 && a->b_dtype == DG_FP8_E4M3));
+        DG_REQUIRE((a->batch_stride_a * (ab_bf16 ? 2 : 1)) % 16 == 0 && (a->batch_stride_b * (ab_bf16 ? 2 : 1)) % 16 == 0);
         DG_REQUIRE((a->batch_stride_d * (a->d_dtype == DG_FP32 ? 4 : (a->d_dtype == DG_FP8_E4M3 ? 1 : 2))) % 16 == 0);
         // quantised output: the scale columns of the batches follow one another, so a batch is whole packed words
         if (a->d_dtype == DG_FP8_E4M3) DG_REQUIRE(a->n % 128 == 0 && a->batch_stride_d == a->n);
@@ -100,15 +102,17 @@ int validate(int kind, const dg_gemm_args_t* a, bool need_pointers, Problem* p) 
         DG_REQUIRE(kind == DG_GEMM_DENSE || batched);
     }
     DG_REQUIRE(a->m >= 0 && a->n >= 0 && a->k >= 0);
-    DG_REQUIRE(a->gran_k_a == 32 || a->gran_k_a == 128);
-    DG_REQUIRE(a->gran_k_b == 32 || a->gran_k_b == 128);
+    if (!ab_bf16) {
+        DG_REQUIRE(a->gran_k_a == 32 || a->gran_k_a == 128);
+        DG_REQUIRE(a->gran_k_b == 32 || a->gran_k_b == 128);
+    }
     if (kind == DG_GEMM_DENSE) {
         DG_REQUIRE(a->num_groups == 1);
     } else if (batched) {
         DG_REQUIRE(a->n > 0 && a->k > 0);
     } else if (k_grouped) {
         // gemm.hpp:320-372: 1-D scales of one granularity, K slices aligned to whole K-blocks, contiguous operands
-        DG_REQUIRE(a->num_groups > 0 && a->gran_k_a == a->gran_k_b);
+        DG_REQUIRE(a->num_groups > 0 && (ab_bf16 || a->gran_k_a == a->gran_k_b));
         DG_REQUIRE(state().mk_alignment % 128 == 0);
         DG_REQUIRE(!a->has_alpha);
     } else {
@@ -134,10 +138,11 @@ int validate(int kind, const dg_gemm_args_t* a, bool need_pointers, Problem* p) 
     p->m = a->m; p->n = a->n; p->k = a->k; p->groups = a->num_groups;
     p->a_fp4 = a->a_dtype == DG_FP4_E2M1_X2;
     p->b_fp4 = a->b_dtype == DG_FP4_E2M1_X2;
+    p->ab_bf16 = ab_bf16;
     p->d_fp32 = a->d_dtype == DG_FP32;
     p->d_fp8 = a->d_dtype == DG_FP8_E4M3;
     p->accumulate = a->accumulate != 0;
-    p->gran_k_a = a->gran_k_a; p->gran_k_b = a->gran_k_b;
+    p->gran_k_a = ab_bf16 ? 128 : a->gran_k_a; p->gran_k_b = ab_bf16 ? 128 : a->gran_k_b;
     p->expected_m = a->expected_m;
     p->write_padding = kind == DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM && a->ensure_zero_padding != 0;
     p->k_psum = k_grouped && a->use_psum_layout != 0;
@@ -148,23 +153,27 @@ int validate(int kind, const dg_gemm_args_t* a, bool need_pointers, Problem* p) 
 
     if (p->a_fp4 || p->b_fp4) DG_REQUIRE(a->k % 128 == 0);                   // runtime_utils.hpp:133-135
     if (need_pointers) {
-        DG_REQUIRE(a->a != nullptr && a->b != nullptr && a->sfa != nullptr && a->sfb != nullptr && a->d != nullptr);
+        DG_REQUIRE(a->a != nullptr && a->b != nullptr && a->d != nullptr);
+        DG_REQUIRE(ab_bf16 || (a->sfa != nullptr && a->sfb != nullptr));
         const auto aligned = [](const void* ptr, uintptr_t al) { return reinterpret_cast<uintptr_t>(ptr) % al == 0; };
         DG_REQUIRE(aligned(a->a, p->a_fp4 ? 32 : 16));                        // runtime_utils.hpp:126
         DG_REQUIRE(aligned(a->b, p->b_fp4 ? 32 : 16));
-        DG_REQUIRE(aligned(a->sfa, 16) && aligned(a->sfb, 16) && aligned(a->d, 16));
+        DG_REQUIRE(aligned(a->d, 16) && (ab_bf16 || (aligned(a->sfa, 16) && aligned(a->sfb, 16))));
         if (kind != DG_GEMM_DENSE && !batched) DG_REQUIRE(a->grouped_layout != nullptr);
     }
     // Pitch of the non-contiguous dimension: rows of K bytes (K-major) or K-slices of MN bytes (MN-major)
+    // (storage elements: bytes for FP8 / packed FP4, bfloat16 elements for BF16)
     const int64_t k_bytes_a = p->a_mn_major ? a->m : (p->a_fp4 ? a->k / 2 : a->k);
     const int64_t k_bytes_b = p->b_mn_major ? a->n : (p->b_fp4 ? a->k / 2 : a->k);
-    DG_REQUIRE(a->lda >= k_bytes_a && a->lda % (p->a_fp4 ? 32 : 16) == 0);   // TMA: strides are multiples of 16 bytes
-    DG_REQUIRE(a->ldb >= k_bytes_b && a->ldb % (p->b_fp4 ? 32 : 16) == 0);
+    DG_REQUIRE(a->lda >= k_bytes_a && a->lda % (p->a_fp4 ? 32 : (ab_bf16 ? 8 : 16)) == 0);   // TMA: strides are multiples of 16 bytes
+    DG_REQUIRE(a->ldb >= k_bytes_b && a->ldb % (p->b_fp4 ? 32 : (ab_bf16 ? 8 : 16)) == 0);
     const int d_elem = p->d_fp32 ? 4 : (p->d_fp8 ? 1 : 2);
     DG_REQUIRE(a->ldd >= a->n && (a->ldd * d_elem) % 16 == 0);
     // Packed scale tensors: csrc/utils/layout.hpp:121-130
-    DG_REQUIRE(a->sfa_pitch >= align_up<int64_t>(a->m, 4) && a->sfa_pitch % 4 == 0);
-    DG_REQUIRE(a->sfb_pitch >= align_up<int64_t>(a->n, 4) && a->sfb_pitch % 4 == 0);
+    if (!ab_bf16) {
+        DG_REQUIRE(a->sfa_pitch >= align_up<int64_t>(a->m, 4) && a->sfa_pitch % 4 == 0);
+        DG_REQUIRE(a->sfb_pitch >= align_up<int64_t>(a->n, 4) && a->sfb_pitch % 4 == 0);
+    }
     if (kind == DG_GEMM_M_GROUPED_CONTIGUOUS) {
         // Every expert segment is padded to the alignment, which the row blocks must divide
         DG_REQUIRE(state().mk_alignment % 128 == 0);
@@ -209,7 +218,8 @@ GemmLayout fit_stages(GemmLayout lay, int64_t item_kb, int max_stages) {
 int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
     const int num_sms = dg_get_num_sms();
     const int d_elem = p.d_fp32 ? 4 : (p.d_fp8 ? 1 : 2);
-    const int64_t k_blocks = ceil_div(p.k, 128);           // in units of 128 elements, whatever the stage size
+    const int ab_elem = p.ab_bf16 ? 2 : 1;
+    const int64_t k_blocks = ceil_div<int64_t>(static_cast<int64_t>(p.k) * ab_elem, 128);   // in units of 128 bytes of K, whatever the stage size
     const int forced_bn = env_int("FORCE_BLOCK_N"), forced_cluster = env_int("FORCE_CLUSTER"), forced_splits = env_int("FORCE_SPLIT_K");
     const int forced_block_m = env_int("FORCE_BLOCK_M"), forced_block_k = env_int("FORCE_BLOCK_K");
     const int forced_stages = env_int("FORCE_NUM_STAGES");
@@ -236,7 +246,7 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
         // Built and tested, but it measured 0-20 % slower than 128-element stages on every shape tried (the 64-byte
         // rows double the number of L2 requests), so it is used only on request (DG_FORCE_BLOCK_K=64).
         if (bk != (forced_block_k && p.kind != DG_GEMM_K_GROUPED_CONTIGUOUS ? forced_block_k : 128)) continue;
-        if (bk == 64 && (p.a_fp4 || p.b_fp4 || p.a_mn_major || p.b_mn_major || forced_splits > 1)) continue;
+        if (bk == 64 && (p.a_fp4 || p.b_fp4 || p.ab_bf16 || p.a_mn_major || p.b_mn_major || forced_splits > 1)) continue;
         const int tile_m = 128 * cluster * halves, units = num_sms / cluster;
         int64_t m_blocks;
         if (p.kind == DG_GEMM_M_GROUPED_MASKED)
@@ -257,7 +267,7 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
         // launch plus S FP32 panels of traffic.
         const bool can_split = p.kind == DG_GEMM_DENSE && !p.accumulate && !p.d_fp8 && !p.stochastic && cluster == 1 && halves == 1 && bk == 128 &&
                                forced_splits != 1 && k_blocks >= 16;
-        for (int bn = 16; bn <= 240; bn += 16) {
+        for (int bn = 16; bn <= (p.ab_bf16 ? 256 : 240); bn += 16) {
             if (forced_bn && bn != forced_bn) continue;
             if (p.b_mn_major && (bn / cluster) % 16 != 0) continue;       // an MN-major B load starts on a 16-byte boundary
             if (p.d_fp8 && bn % 32 != 0) continue;                        // whole 32-column scale groups per tile
@@ -275,14 +285,16 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
                 const int64_t waves = ceil_div<int64_t>(tiles, units);
                 // The pipeline: as deep as shared memory allows, but no deeper than the K-blocks of two work items
                 // (k-grouped: the groups share K; an average slice stands for all of them)
-                const int64_t item_k = p.kind == DG_GEMM_K_GROUPED_CONTIGUOUS ? std::max<int64_t>(128, p.k / p.groups)
-                                                                               : std::min<int64_t>(p.k, static_cast<int64_t>(kb_per) * 128);
+                // (in bytes of K per row)
+                const int64_t item_k = p.kind == DG_GEMM_K_GROUPED_CONTIGUOUS ? std::max<int64_t>(128, static_cast<int64_t>(p.k) * ab_elem / p.groups)
+                                                                               : std::min<int64_t>(static_cast<int64_t>(p.k) * ab_elem, static_cast<int64_t>(kb_per) * 128);
                 const int64_t item_kb = ceil_div<int64_t>(item_k, bk);
                 int max_stages = static_cast<int>(std::max<int64_t>(2, std::min<int64_t>(32, 2 * item_kb)));
                 if (forced_stages >= 2) max_stages = std::min(max_stages, forced_stages);
                 GemmLayout lay{128u * halves, static_cast<uint32_t>(bn), static_cast<uint32_t>(bk), 2,
                                static_cast<uint32_t>(splits > 1 ? 4 : d_elem), static_cast<uint32_t>(cluster),
-                               p.b_mn_major ? 1u : 0u, static_cast<uint32_t>(p.gran_k_a), static_cast<uint32_t>(p.gran_k_b), 0u};
+                               p.b_mn_major ? 1u : 0u, static_cast<uint32_t>(p.gran_k_a), static_cast<uint32_t>(p.gran_k_b), 0u,
+                               static_cast<uint32_t>(ab_elem)};
                 lay = fit_stages(lay, p.kind == DG_GEMM_K_GROUPED_CONTIGUOUS ? 0 : item_kb, max_stages);   // slices may be one K-block
                 if (lay.num_stages == 0 || lay.tmem_cols_used() > kTmemCapacityCols) continue;
                 // Cycles per pipeline stage: the MMAs; shared memory, which moved ~150 B per cycle in every configuration
@@ -343,13 +355,14 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
 // The layout the kernel of a configuration uses (same arithmetic as choose_config)
 GemmLayout layout_of(const Problem& p, const dg_gemm_config_t& cfg) {
     const bool split = cfg.num_splits > 1;
+    const int64_t ab_elem = p.ab_bf16 ? 2 : 1;
     const int64_t item_kb = p.kind == DG_GEMM_K_GROUPED_CONTIGUOUS ? 0 :
-                            ceil_div<int64_t>(std::min<int64_t>(p.k, static_cast<int64_t>(cfg.kb_per_split) * 128), cfg.block_k);
+                            ceil_div<int64_t>(std::min<int64_t>(p.k * ab_elem, static_cast<int64_t>(cfg.kb_per_split) * 128), cfg.block_k);
     GemmLayout lay{static_cast<uint32_t>(cfg.block_m), static_cast<uint32_t>(cfg.block_n), static_cast<uint32_t>(cfg.block_k),
                    static_cast<uint32_t>(cfg.num_stages), static_cast<uint32_t>((p.d_fp32 || split) ? 4 : (p.d_fp8 ? 1 : 2)),
                    static_cast<uint32_t>(cfg.cluster_size), p.b_mn_major ? 1u : 0u,
                    static_cast<uint32_t>(p.gran_k_a), static_cast<uint32_t>(p.gran_k_b),
-                   item_kb < cfg.num_stages ? 1u : 0u};
+                   item_kb < cfg.num_stages ? 1u : 0u, static_cast<uint32_t>(ab_elem)};
     return lay;
 }
 
@@ -363,6 +376,7 @@ std::string generate_source(const Problem& p, const dg_gemm_config_t& cfg) {
       << "#define DG_SHORT_K " << layout_of(p, cfg).short_k << "\n"
       << "#define DG_NUM_STAGES " << cfg.num_stages << "\n"
       << "#define DG_CLUSTER " << cfg.cluster_size << "\n"
+      << "#define DG_AB_BF16 " << (p.ab_bf16 ? 1 : 0) << "\n"
       << "#define DG_A_FP4 " << (p.a_fp4 ? 1 : 0) << "\n"
       << "#define DG_B_FP4 " << (p.b_fp4 ? 1 : 0) << "\n"
       << "#define DG_MAJOR_A " << (p.a_mn_major ? 1 : 0) << "\n"
@@ -480,25 +494,36 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
     // K-major A, B: K (elements) x rows; box = one K-block (128 or 64 elements) x the tile's rows, swizzled over its width.
     const CUtensorMapSwizzle k_major_swizzle = cfg.block_k == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
     // MN-major (FP8 only): MN x (groups x K); box = 128 columns of MN x one K-block.
+    // BF16 operands: two bytes per element, so a 128-byte stage row is 64 elements and an MN-major atom 64 columns
+    const uint64_t ab_elem = p.ab_bf16 ? 2 : 1;
+    const uint32_t box_k = static_cast<uint32_t>(cfg.block_k / ab_elem), atom_mn = static_cast<uint32_t>(128 / ab_elem);
+    const CUtensorMapDataType a_type = p.ab_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 :
+                                       p.a_fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    const CUtensorMapDataType b_type = p.ab_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 :
+                                       p.b_fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8;
     if (!p.a_mn_major) {
-        if ((rc = encode_2d(&tm_a, p.a_fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, a->a,
-                            p.k, a_rows, a->lda, cfg.block_k, cfg.block_m, k_major_swizzle, nb, bs_a)) != DG_OK) return rc;
+        if ((rc = encode_2d(&tm_a, a_type, a->a, p.k, a_rows, a->lda * ab_elem, box_k, cfg.block_m, k_major_swizzle,
+                            nb, bs_a * ab_elem)) != DG_OK) return rc;
     } else {
-        if ((rc = encode_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->a, p.m, p.k, a->lda, 128, 128,
-                            CU_TENSOR_MAP_SWIZZLE_128B, nb, bs_a)) != DG_OK) return rc;
+        if ((rc = encode_2d(&tm_a, a_type, a->a, p.m, p.k, a->lda * ab_elem, atom_mn, box_k, CU_TENSOR_MAP_SWIZZLE_128B,
+                            nb, bs_a * ab_elem)) != DG_OK) return rc;
     }
     if (!p.b_mn_major) {
-        if ((rc = encode_2d(&tm_b, p.b_fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, a->b,
-                            p.k, b_rows, a->ldb, cfg.block_k, cfg.block_n / cfg.cluster_size, k_major_swizzle, nb, bs_b)) != DG_OK) return rc;
+        if ((rc = encode_2d(&tm_b, b_type, a->b, p.k, b_rows, a->ldb * ab_elem, box_k, cfg.block_n / cfg.cluster_size, k_major_swizzle,
+                            nb, bs_b * ab_elem)) != DG_OK) return rc;
     } else {
-        if ((rc = encode_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->b, p.n, b_k_rows, a->ldb, 128, 128,
-                            CU_TENSOR_MAP_SWIZZLE_128B, nb, bs_b)) != DG_OK) return rc;
+        if ((rc = encode_2d(&tm_b, b_type, a->b, p.n, b_k_rows, a->ldb * ab_elem, atom_mn, box_k, CU_TENSOR_MAP_SWIZZLE_128B,
+                            nb, bs_b * ab_elem)) != DG_OK) return rc;
     }
     // Scales: MN (int32) x packed-K rows; the MN extent is the true row count, so reads past it are zero-filled
-    if ((rc = encode_2d(&tm_sfa, CU_TENSOR_MAP_DATA_TYPE_INT32, a->sfa, p.m, sfa_rows, a->sfa_pitch * 4, cfg.block_m, 1,
-                        CU_TENSOR_MAP_SWIZZLE_NONE, nb, bs_sfa)) != DG_OK) return rc;
-    if ((rc = encode_2d(&tm_sfb, CU_TENSOR_MAP_DATA_TYPE_INT32, a->sfb, p.n, sfb_rows, a->sfb_pitch * 4, lay.sf_block_n(), 1,
-                        CU_TENSOR_MAP_SWIZZLE_NONE, nb, bs_sfb)) != DG_OK) return rc;
+    if (p.ab_bf16) {
+        tm_sfa = tm_sfb = tm_a;                  // never used: the BF16 kernel has no scale loads
+    } else {
+        if ((rc = encode_2d(&tm_sfa, CU_TENSOR_MAP_DATA_TYPE_INT32, a->sfa, p.m, sfa_rows, a->sfa_pitch * 4, cfg.block_m, 1,
+                            CU_TENSOR_MAP_SWIZZLE_NONE, nb, bs_sfa)) != DG_OK) return rc;
+        if ((rc = encode_2d(&tm_sfb, CU_TENSOR_MAP_DATA_TYPE_INT32, a->sfb, p.n, sfb_rows, a->sfb_pitch * 4, lay.sf_block_n(), 1,
+                            CU_TENSOR_MAP_SWIZZLE_NONE, nb, bs_sfb)) != DG_OK) return rc;
+    }
     const CUtensorMapSwizzle d_swizzle = lay.store_row_bytes() == 128 ? CU_TENSOR_MAP_SWIZZLE_128B :
                                          lay.store_row_bytes() == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
     // Two views of D: boxes as wide as an epilogue group (128 or 64 bytes) for complete groups, narrower boxes for the

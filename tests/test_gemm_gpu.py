@@ -706,6 +706,90 @@ def test_m_grouped_masked_in_a_cuda_graph_follows_new_counts():
 
 
 # ---------------------------------------------------------------------------------------------------
+# BF16 operands (no scales): same kernel, tcgen05.mma.kind::f16
+# ---------------------------------------------------------------------------------------------------
+def _bf16_cuda(x):
+    return torch.from_numpy(x).cuda().bfloat16()
+
+
+@pytest.mark.parametrize("variant", ["nt", "nn", "tn", "tt"])
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (256, 512, 1024), (136, 304, 200), (1000, 2112, 1792)])
+@pytest.mark.parametrize("block_m", [128, 256])
+def test_bf16_gemm_all_layouts_match_fp32_matmul(variant, m, n, k, block_m, monkeypatch):
+    if block_m == 256 and m <= 128:
+        pytest.skip("256-row tiles need more than 128 rows")
+    monkeypatch.setenv("DG_FORCE_BLOCK_M", str(block_m))
+    a, b = seeded_bf16((m, k), 101), seeded_bf16((n, k), 102)
+    ref = a.astype(np.float64) @ b.astype(np.float64).T
+    ta = _bf16_cuda(a) if variant[0] == "n" else _bf16_cuda(np.ascontiguousarray(a.T))      # "t": stored [K, M]
+    tb = _bf16_cuda(b) if variant[1] == "t" else _bf16_cuda(np.ascontiguousarray(b.T))      # "n": stored [K, N]
+    d = torch.full((m, n), float("nan"), dtype=torch.float, device="cuda")
+    dg.reset_kernel_status()
+    getattr(dg, f"bf16_gemm_{variant}")(ta, tb, d)
+    assert dg.kernel_status() == 0
+    out = d.cpu().numpy()
+    assert oracle.calc_diff(out, ref) < 1e-9 and np.allclose(out, ref, rtol=1e-5, atol=1e-3), diff_report(out, ref)
+    # BF16 output is the FP32 result rounded once; accumulation adds C
+    d16 = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    getattr(dg, f"bf16_gemm_{variant}")(ta, tb, d16)
+    assert torch.equal(d16, d.bfloat16())
+    c = d.clone()
+    getattr(dg, f"bf16_gemm_{variant}")(ta, tb, c, c=c, alpha=None)
+    assert np.allclose(c.cpu().numpy(), 2 * out, rtol=1e-6, atol=1e-4)
+
+
+def test_bf16_grouped_gemms_match_fp32_matmul():
+    # contiguous, both layout forms
+    g, n, k = 4, 512, 768
+    m, actual, aligned, layout = oracle.make_contiguous_layout(g, 200, 128, actual_ms=[130, 0, 256, 77])
+    a, b = seeded_bf16((m, k), 103), seeded_bf16((g, n, k), 104)
+    a[layout < 0] = 0
+    ref = np.zeros((m, n), dtype=np.float64)
+    for i in range(g):
+        rows = layout == i
+        ref[rows] = a[rows].astype(np.float64) @ b[i].astype(np.float64).T
+    d = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    dg.reset_kernel_status()
+    dg.m_grouped_bf16_gemm_nt_contiguous(_bf16_cuda(a), _bf16_cuda(b), d, torch.from_numpy(layout).cuda())
+    assert dg.kernel_status() == 0
+    out = d.float().cpu().numpy()
+    assert oracle.calc_diff(out[layout >= 0], oracle.bf16_round(ref[layout >= 0].astype(np.float32))) < 1e-5
+    assert (out[layout < 0] == 0).all()
+    _, starts, ends = oracle.make_psum_layout(actual, 128)
+    d2 = torch.full((m, n), SENTINEL, dtype=torch.bfloat16, device="cuda")
+    dg.m_grouped_bf16_gemm_nt_contiguous(_bf16_cuda(a), _bf16_cuda(b), d2, torch.from_numpy(ends).cuda(), use_psum_layout=True,
+                                         ensure_zero_padding=False)
+    assert dg.kernel_status() == 0
+    out2 = d2.float().cpu().numpy()
+    assert np.array_equal(out2[layout >= 0], out[layout >= 0]) and (out2[layout < 0] == SENTINEL).all()
+    # masked
+    counts, max_m = (45, 200, 0, 256), 256
+    a3, b3 = seeded_bf16((4, max_m, k), 105), seeded_bf16((4, n, k), 106)
+    d3 = torch.full((4, max_m, n), SENTINEL, dtype=torch.bfloat16, device="cuda")
+    dg.m_grouped_bf16_gemm_nt_masked(_bf16_cuda(a3), _bf16_cuda(b3), d3, torch.tensor(counts, dtype=torch.int, device="cuda"), 128)
+    assert dg.kernel_status() == 0
+    out3 = d3.float().cpu().numpy()
+    for i, cnt in enumerate(counts):
+        want = oracle.bf16_round((a3[i, :cnt].astype(np.float64) @ b3[i].astype(np.float64).T).astype(np.float32))
+        assert cnt == 0 or oracle.calc_diff(out3[i, :cnt], want) < 1e-5
+        assert (out3[i, cnt:] == SENTINEL).all()
+    # k-grouped
+    ks = (128, 0, 384, 256)
+    slices, klayout, sum_k = oracle.k_grouped_slices(ks, 128, False)
+    mm, nn = 208, 304
+    ak, bk = np.zeros((sum_k, mm), np.float32), np.zeros((sum_k, nn), np.float32)
+    for i, (s0, kk, _) in enumerate(slices):
+        ak[s0:s0 + kk], bk[s0:s0 + kk] = seeded_bf16((kk, mm), 110 + i), seeded_bf16((kk, nn), 120 + i)
+    c0 = seeded_bf16((len(ks), mm, nn), 130, 8.0)
+    dk = torch.from_numpy(c0).cuda()
+    dg.k_grouped_bf16_gemm_tn_contiguous(_bf16_cuda(ak), _bf16_cuda(bk), dk, [p for _, _, p in slices], torch.from_numpy(klayout).cuda(), c=dk)
+    assert dg.kernel_status() == 0
+    for i, (s0, kk, _) in enumerate(slices):
+        want = c0[i] + ak[s0:s0 + kk].astype(np.float64).T @ bk[s0:s0 + kk].astype(np.float64)
+        assert np.allclose(dk[i].cpu().numpy(), want, rtol=1e-5, atol=1e-3)
+
+
+# ---------------------------------------------------------------------------------------------------
 # scale layout kernels and quantisation helpers
 # ---------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("mn,k,groups,gran_k", [(4096, 128, 1, 128), (4097, 7168, 1, 128), (4097, 7296, 2, 32),
