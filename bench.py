@@ -461,6 +461,47 @@ def detail_rows(torch, dg):
     vm = int(masked.sum().item())
     add(f"m-grouped masked (CUDA graph) G{groups} max_m{max_m} valid {vm} n{n} k{k}", t, flops_of(vm, n, k),
         vm * k + groups * n * k + vm * n * 2)
+    del qa, sfa, qb, sfb, d, a, graph
+    # k-grouped contiguous (MoE weight gradients, tests/generators.py:251-254): FP32 D accumulated in place
+    for g, m, n, k_per in ((4, 4096, 7168, 8192), (8, 7168, 2048, 4096)):
+        ks = [k_per] * g
+        ak = torch.randn((g * k_per, m), device="cuda").to(torch.float8_e4m3fn)
+        bk = torch.randn((g * k_per, n), device="cuda").to(torch.float8_e4m3fn)
+        lay = torch.tensor(ks, dtype=torch.int, device="cuda")
+        sfak = torch.ones((g * k_per // 128, m), device="cuda")
+        sfbk = torch.ones((g * k_per // 128, n), device="cuda")
+        dk = torch.zeros((g, m, n), device="cuda")
+        t = bench(lambda: dg.k_grouped_fp8_gemm_tn_contiguous((ak, sfak), (bk, sfbk), dk, ks, lay, c=dk, recipe=(1, 1, 128)), 2, 5)
+        add(f"k-grouped contiguous G{g} m{m} n{n} k{k_per}/group fp32 accumulate", t, flops_of(m, n, g * k_per),
+            g * k_per * (m + n) + 2 * g * m * n * 4)
+        del ak, bk, sfak, sfbk, dk
+    # batched GEMM behind fp8_einsum (tests/test_einsum.py:128-186): BF16 output and the quantised (e4m3, scales) pair
+    b_, h, r, dd = 4096, 8, 4096, 1024
+    x = torch.randn((b_ * h, r), device="cuda", dtype=torch.bfloat16)
+    qx, sfx = per_token_cast_to_fp8(x, True, 128)
+    qx, sfx = qx.view(b_, h, r), sfx.view(b_, h, r // 128)
+    qy, sfy = make_grouped_b(h, dd, r, False, torch, dg)
+    z = torch.empty((b_, h, dd), device="cuda", dtype=torch.bfloat16)
+    t = bench(lambda: dg.fp8_einsum("bhr,hdr->bhd", (qx, sfx), (qy, sfy), z, recipe=(1, 1, 128)), 2, 8)
+    add(f"fp8_einsum bhr,hdr->bhd b{b_} h{h} r{r} d{dd} bf16 out", t, flops_of(b_ * h, dd, r), b_ * h * r + h * dd * r + b_ * h * dd * 2)
+    zq = torch.empty((b_, h, dd), device="cuda", dtype=torch.float8_e4m3fn)
+    sfd = torch.empty((h * dd // 128, b_), device="cuda", dtype=torch.int).t()
+    t = bench(lambda: dg.fp8_einsum("bhr,hdr->bhd", (qx, sfx), (qy, sfy), (zq, sfd), recipe=(1, 1, 128)), 2, 8)
+    add(f"fp8_einsum bhr,hdr->bhd b{b_} h{h} r{r} d{dd} quantised (e4m3 + 1x32 scales) out", t, flops_of(b_ * h, dd, r),
+        b_ * h * r + h * dd * r + b_ * h * dd)
+    del x, qx, sfx, qy, sfy, z, zq, sfd
+    # BF16 operands (the same kernel, kind::f16), with torch.matmul (cuBLAS) timed beside it
+    for n, k in ((4096, 7168), (7168, 2048)):
+        a16 = torch.randn((M_DENSE, k), device="cuda", dtype=torch.bfloat16)
+        b16 = torch.randn((n, k), device="cuda", dtype=torch.bfloat16)
+        d16 = torch.empty((M_DENSE, n), device="cuda", dtype=torch.bfloat16)
+        t = bench(lambda: dg.bf16_gemm_nt(a16, b16, d16), 3, 10)
+        add(f"bf16 dense m{M_DENSE} n{n} k{k}", t, flops_of(M_DENSE, n, k), 2 * (M_DENSE * k + n * k + M_DENSE * n))
+        for _ in range(3):
+            torch.matmul(a16, b16.t(), out=d16)
+        t = bench_kineto(lambda: torch.matmul(a16, b16.t(), out=d16), ("nvjet", "gemm", "cutlass", "sm100", "sm90"), 10)
+        add(f"torch.matmul (cuBLAS) bf16 m{M_DENSE} n{n} k{k}", t, flops_of(M_DENSE, n, k), 2 * (M_DENSE * k + n * k + M_DENSE * n))
+        del a16, b16, d16
     return rows
 
 
