@@ -124,11 +124,9 @@ int validate(int kind, const dg_gemm_args_t* a, bool need_pointers, Problem* p) 
         DG_REQUIRE(a->major_b == DG_MAJOR_K);                                 // gemm.hpp:285
         DG_REQUIRE(a->expected_m > 0 && a->m > 0);                            // gemm.hpp:296
     }
-    // FP4 x FP4 needs the MXF4 MMA kind (K-major only, csrc/utils/layout.hpp:42-45)
-    if (a->a_dtype == DG_FP4_E2M1_X2 && a->b_dtype == DG_FP4_E2M1_X2)
-        return fail(DG_ERR_UNSUPPORTED, "FP4 x FP4 (kind::mxf4) is not built; FP8 x FP8 and FP8 x FP4 are");
-    if (a->a_dtype == DG_FP4_E2M1_X2)
-        return fail(DG_ERR_UNSUPPORTED, "FP4 A with FP8 B is not built; use FP8 A with FP4 B");
+    // FP4 operands on either side go through kind::mxf8f6f4 (E2M1 format, unpacked to one byte per element in shared
+    // memory by the tensor map), FP4 x FP4 included: the same results as the reference's kind::mxf4 path
+    // (csrc/utils/layout.hpp:42-45) at the FP8 rate rather than twice it.
     DG_REQUIRE((a->major_a == DG_MAJOR_K || a->major_a == DG_MAJOR_MN) && (a->major_b == DG_MAJOR_K || a->major_b == DG_MAJOR_MN));
     if ((a->major_a == DG_MAJOR_MN && a->a_dtype == DG_FP4_E2M1_X2) || (a->major_b == DG_MAJOR_MN && a->b_dtype == DG_FP4_E2M1_X2))
         return fail(DG_ERR_UNSUPPORTED, "MN-major packed FP4 operands are not built; FP4 must be K-major");

@@ -91,8 +91,8 @@ def test_argument_validation_fails_like_the_reference_asserts(kw, kind, pattern)
 
 def test_unsupported_combinations_say_so():
     cfg = GemmConfig()
-    rc = lib.dg_get_gemm_config(0, C.byref(_args(a_dtype=_lib.DG_FP4_E2M1_X2, b_dtype=_lib.DG_FP4_E2M1_X2)), C.byref(cfg))
-    assert rc == 4 and "FP4 x FP4" in _lib.last_error()
+    rc = lib.dg_get_gemm_config(0, C.byref(_args(a_dtype=_lib.DG_FP4_E2M1_X2, major_a=_lib.DG_MAJOR_MN, lda=256)), C.byref(cfg))
+    assert rc == 4 and "FP4 must be K-major" in _lib.last_error()
 
 
 SHAPES = [(m, n, k) for m in (1, 64, 128, 129, 4096) for (n, k) in

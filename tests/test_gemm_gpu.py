@@ -324,6 +324,28 @@ def test_stochastic_rounding_epilogue_is_the_hash_rounding_of_the_fp32_result(m,
     assert abs(err) < 5e-3 * d32.abs().double().mean().item()
 
 
+@pytest.mark.parametrize("a_fp4,b_fp4", [(True, False), (True, True)])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 512), (1000, 576, 1792), (4096, 512, 2048)])
+def test_fp4_a_operand_and_fp4_x_fp4_match_oracle(a_fp4, b_fp4, m, n, k):
+    """Packed e2m1 on the A side, alone or with an e2m1 B, scales per 1 x 32 (csrc/utils/layout.hpp:42-45)."""
+    a, b = seeded_bf16((m, k), 141), seeded_bf16((n, k), 142)
+    qa, sfa = oracle.per_token_cast_to_fp4(a, True, 32)
+    if b_fp4:
+        qb, sfb = oracle.per_token_cast_to_fp4(b, True, 32)
+        gkb = 32
+    else:
+        qb, sfb_raw = oracle.per_block_cast_to_fp8(b, True, 128)
+        sfb, gkb = oracle.broadcast_sf_along_mn(sfb_raw, n, 128), 128
+    ref = oracle.dequant_gemm_nt(qa, sfa, qb, sfb, 32, gkb, True, b_fp4)
+    d = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    dg.reset_kernel_status()
+    dg.fp8_fp4_gemm_nt((fp4_cuda(qa), packed_sf_cuda(sfa)), (fp4_cuda(qb) if b_fp4 else fp8_cuda(qb), packed_sf_cuda(sfb)), d,
+                       recipe_a=(1, 32), recipe_b=(1, gkb))
+    assert dg.kernel_status() == 0
+    out = d.float().cpu().numpy()
+    assert oracle.calc_diff(out, oracle.bf16_round(ref)) < 1e-5, diff_report(out, ref)
+
+
 def test_fp32_scales_are_transformed_on_the_fly_like_the_legacy_recipe():
     # float32 SFA [m, k/128] and SFB [n/128, k/128] with the default recipe (1, 128, 128) (csrc/utils/layout.hpp:85-98)
     m, n, k = 128, 2112, 1024
