@@ -15,6 +15,7 @@ import torch
 
 from . import _lib
 from ._lib import GemmArgs, GemmConfig, check, lib
+from .epilogue import Alpha, BF16StochasticRounding, FP8Quantization, Identity
 
 kPackedFP4 = torch.int8          # csrc/utils/math.hpp:11
 Recipe3 = Tuple[int, int, int]
@@ -35,6 +36,10 @@ def align(x: int, y: int) -> int:
 
 
 def _stream() -> int:
+    """Raw handle of PyTorch's current stream (the private accessor costs a fraction of building a Stream object)."""
+    raw = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+    if raw is not None:
+        return raw(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -199,6 +204,10 @@ def transform_sf_into_required_layout(sf: torch.Tensor, mn: int, k: int, recipe:
         gran_mn, gran_k = recipe
     else:
         raise RuntimeError("Invalid recipe")
+    packed = sf.dtype == torch.int and gran_mn == 1 and gran_k in (32, 128)
+    if packed:      # the common production path: validate once, with the stride checks, and return
+        _require(not disable_ue8m0_cast, "disable_ue8m0_cast selects the FP32-scale (SM90) kernels, which this sm_100-only library does not build")
+        return _check_sf_layout(sf, mn, k, gran_mn, gran_k, num_groups, tma_stride_check=True, type_check=torch.int)
     _check_sf_layout(sf, mn, k, gran_mn, gran_k, num_groups)
     if disable_ue8m0_cast:
         raise RuntimeError("disable_ue8m0_cast selects the FP32-scale (SM90) kernels, which this sm_100-only library does not build")
@@ -332,7 +341,6 @@ def _fill_args(a, sfa, b, sfb, d, m, n, k, groups, major_a, major_b, gran_k_a, g
 def _resolve_alpha(alpha, epilogue):
     """The epilogue class, `alpha` and the FP8 output pair are exclusive (csrc/jit_kernels/impls/epilogue_class.hpp:111-127)."""
     if epilogue is not None:
-        from .epilogue import Alpha, BF16StochasticRounding, FP8Quantization, Identity
         _require(alpha is None, "(epilogue_class != nullptr) + alpha.has_value() + sfd.has_value() <= 1")
         if isinstance(epilogue, (Identity, FP8Quantization, BF16StochasticRounding)):
             return None
@@ -344,7 +352,6 @@ def _resolve_alpha(alpha, epilogue):
 
 def _stochastic(epilogue, c, d) -> bool:
     """BF16StochasticRounding: "Stochastic rounding requires a direct BF16 output" (epilogue_class.hpp:104-107)."""
-    from .epilogue import BF16StochasticRounding
     if not isinstance(epilogue, BF16StochasticRounding):
         return False
     _require(c is None and d.dtype == torch.bfloat16, "Stochastic rounding requires a direct BF16 output")
@@ -354,7 +361,6 @@ def _stochastic(epilogue, c, d) -> bool:
 def _resolve_sfd(epilogue, c, d, m: int, n: int):
     """FP8Quantization: D must be e4m3 written directly (epilogue_class.hpp:84-87); its scales go to epilogue.sfd, an
     int32 tensor [m, ceil(n / 128)] in the packed MN-major layout (four 1 x 32 scales per word)."""
-    from .epilogue import FP8Quantization
     if not isinstance(epilogue, FP8Quantization):
         _require(d.dtype in (torch.bfloat16, torch.float), "d.scalar_type() == torch::kBFloat16 or d.scalar_type() == torch::kFloat")
         return None
@@ -531,7 +537,6 @@ def k_grouped_fp8_gemm_tn_contiguous(a, b, d, ks_cpu, grouped_layout, c=None, re
 # ------------------------------------------------------------------------------------------------
 def _fp8_bmm(a, sfa, b, sfb, d, c, recipe, epilogue) -> None:
     """D[i] = C[i] + A[i] @ B[i]^T for [B, M, K] x [B, N, K] (any batch strides); d is a tensor or an (e4m3, sfd) pair."""
-    from .epilogue import FP8Quantization
     if isinstance(d, (tuple, list)):
         _require(epilogue is None, "The FP8 output pair supports no other epilogue")
         d, epilogue = d[0], FP8Quantization(d[1])

@@ -6,7 +6,9 @@
 
 #include <algorithm>
 #include <cstring>
+#include <array>
 #include <map>
+#include <mutex>
 #include <sstream>
 
 #include "device/dg/gemm_config.hpp"
@@ -399,6 +401,28 @@ std::string generate_source(const Problem& p, const dg_gemm_config_t& cfg) {
 int encode_2d(CUtensorMap* map, CUtensorMapDataType dtype, const void* base, uint64_t inner, uint64_t outer,
               uint64_t outer_stride_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swizzle,
               uint64_t batches = 0, uint64_t batch_stride_bytes = 0) {
+    // Encoding costs the driver ~1 us per map and a GEMM needs six; serving loops call with the same buffers over and
+    // over, so the last maps are kept per thread (a map depends on nothing but these arguments)
+    struct Key {
+        const void* base; uint64_t inner, outer, outer_stride, batches, batch_stride; uint32_t box_inner, box_outer; int dtype, swizzle;
+        bool operator==(const Key& o) const {
+            return base == o.base && inner == o.inner && outer == o.outer && outer_stride == o.outer_stride && batches == o.batches &&
+                   batch_stride == o.batch_stride && box_inner == o.box_inner && box_outer == o.box_outer && dtype == o.dtype && swizzle == o.swizzle;
+        }
+    };
+    struct Slot { Key key; CUtensorMap map; bool valid = false; };
+    constexpr size_t kSlots = 256;
+    thread_local std::array<Slot, kSlots> cache;
+    const Key key{base, inner, outer, outer_stride_bytes, batches, batch_stride_bytes, box_inner, box_outer, static_cast<int>(dtype),
+                  static_cast<int>(swizzle)};
+    const size_t h = (reinterpret_cast<uintptr_t>(base) >> 4) * 0x9E3779B97F4A7C15ull + inner * 31 + outer * 131 + box_inner * 7 + box_outer * 3 +
+                     static_cast<size_t>(dtype) * 1009 + static_cast<size_t>(swizzle) * 9176 + outer_stride_bytes + batch_stride_bytes * 17;
+    Slot& slot = cache[(h >> 20) % kSlots];
+    const bool verbose = env_int("PRINT_CONFIGS") != 0;
+    if (slot.valid && slot.key == key && !verbose) {
+        *map = slot.map;
+        return DG_OK;
+    }
     const Driver& drv = driver();
     if (!drv.ok) return fail(DG_ERR_CUDA, "CUDA driver unavailable: %s", drv.why.c_str());
     const cuuint32_t rank = batches > 0 ? 3 : 2;
@@ -406,7 +430,7 @@ int encode_2d(CUtensorMap* map, CUtensorMapDataType dtype, const void* base, uin
     const cuuint64_t strides[2] = {outer_stride_bytes, batch_stride_bytes};
     const cuuint32_t box[3] = {box_inner, box_outer, 1};
     const cuuint32_t elem_strides[3] = {1, 1, 1};
-    if (env_int("PRINT_CONFIGS"))
+    if (verbose)
         fprintf(stderr, "[dg] tensor map: dtype %d dims (%llu, %llu, %llu) strides %llu, %llu B box (%u, %u) swizzle %d base %p\n",
                 static_cast<int>(dtype), static_cast<unsigned long long>(inner), static_cast<unsigned long long>(outer),
                 static_cast<unsigned long long>(batches), static_cast<unsigned long long>(outer_stride_bytes),
@@ -419,6 +443,9 @@ int encode_2d(CUtensorMap* map, CUtensorMapDataType dtype, const void* base, uin
                     cu_error(r).c_str(), static_cast<unsigned long long>(inner), static_cast<unsigned long long>(outer),
                     static_cast<unsigned long long>(batches), static_cast<unsigned long long>(outer_stride_bytes),
                     static_cast<unsigned long long>(batch_stride_bytes), box_inner, box_outer);
+    slot.key = key;
+    slot.map = *map;
+    slot.valid = true;
     return DG_OK;
 }
 
@@ -427,6 +454,44 @@ int get_kernel(const Problem& p, const dg_gemm_config_t& cfg, dg_kernel_t* kerne
                                    "gemm_fp8_fp4_m_grouped_contiguous_psum", "gemm_fp8_fp4_k_grouped_contiguous", "gemm_fp8_fp4_batched"};
     const std::string src = generate_source(p, cfg);
     return dg_jit_compile(names[p.kind], "dg_gemm_fp8_fp4", src.c_str(), "", kernel);
+}
+
+// Choosing a configuration walks a few hundred candidates and finding its kernel hashes the generated source: ~15 us
+// together, more than the kernel time of a decode-sized GEMM.  Both depend only on the problem's descriptor and the
+// settings, so the pair is remembered per descriptor (bounded: cleared when it grows past a few thousand shapes).
+struct Plan {
+    dg_gemm_config_t cfg;
+    dg_kernel_t kernel;
+};
+
+int get_plan(const Problem& p, Plan* plan) {
+    static const char* kEnvNames[] = {"FORCE_BLOCK_N", "FORCE_CLUSTER", "FORCE_SPLIT_K", "FORCE_BLOCK_M", "FORCE_BLOCK_K",
+                                      "FORCE_NUM_STAGES", "FORCE_RASTER_GROUP", "PROFILE"};
+    std::array<int, 32> key{};
+    int i = 0;
+    for (int v : {p.kind, p.m, p.n, p.k, p.groups, static_cast<int>(p.a_fp4), static_cast<int>(p.b_fp4), static_cast<int>(p.ab_bf16),
+                  static_cast<int>(p.d_fp32), static_cast<int>(p.d_fp8), static_cast<int>(p.accumulate), static_cast<int>(p.a_mn_major),
+                  static_cast<int>(p.b_mn_major), p.gran_k_a, p.gran_k_b, p.expected_m, static_cast<int>(p.write_padding),
+                  static_cast<int>(p.k_psum), static_cast<int>(p.stochastic), dg_get_num_sms(), state().mk_alignment})
+        key[i++] = v;
+    for (const char* name : kEnvNames) key[i++] = env_int(name);
+    static std::mutex mu;
+    static std::map<std::array<int, 32>, Plan> plans;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        auto it = plans.find(key);
+        if (it != plans.end()) {
+            *plan = it->second;
+            return DG_OK;
+        }
+    }
+    int rc = choose_config(p, &plan->cfg);
+    if (rc != DG_OK) return rc;
+    if ((rc = get_kernel(p, plan->cfg, &plan->kernel)) != DG_OK) return rc;
+    std::lock_guard<std::mutex> lock(mu);
+    if (plans.size() > 4096) plans.clear();
+    plans[key] = *plan;
+    return DG_OK;
 }
 
 // `fixed_scratch`, when given, replaces the library-owned split-K workspace with a caller-provided device buffer of
@@ -443,14 +508,14 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
     if (p.m == 0 || p.n == 0) return DG_OK;
     if (p.k == 0) return fail(DG_ERR_INVALID_ARGUMENT, "k == 0 must be handled by the caller (zero or copy D)");
 
-    dg_gemm_config_t cfg;
-    if ((rc = choose_config(p, &cfg)) != DG_OK) return rc;
+    Plan plan;
+    if ((rc = get_plan(p, &plan)) != DG_OK) return rc;
+    const dg_gemm_config_t& cfg = plan.cfg;
+    dg_kernel_t kernel = plan.kernel;
     if (env_int("PRINT_CONFIGS"))
         fprintf(stderr, "[dg] kind %d m %d n %d k %d groups %d -> block_m %d block_n %d block_k %d cluster %d stages %d ctas %d smem %d tiles %d splits %d x %d\n",
                 kind, p.m, p.n, p.k, p.groups, cfg.block_m, cfg.block_n, cfg.block_k, cfg.cluster_size, cfg.num_stages, cfg.num_ctas, cfg.smem_bytes, cfg.num_tiles,
                 cfg.num_splits, cfg.kb_per_split);
-    dg_kernel_t kernel = nullptr;
-    if ((rc = get_kernel(p, cfg, &kernel)) != DG_OK) return rc;
     if (fixed_scratch == nullptr && (rc = ensure_status_word()) != DG_OK) return rc;
 
     const bool split = cfg.num_splits > 1;
