@@ -721,6 +721,14 @@ int dg_enumerate_tiles(int kind, int block_n, int raster_group, int shape_m, int
             while (sched.next(t)) { t.m_block += t.a_row_base / 128; emit(); }
             break;
         }
+        case DG_GEMM_K_GROUPED_CONTIGUOUS: {
+            // layout: the slices' lengths (multiples of the alignment); the fourth word is the slice's K-block count
+            TileScheduler<kKGrouped> sched(128, bn, rg, sm, sn, ng, layout_host, c, nc);
+            sched.group_alignment = static_cast<uint32_t>(state().mk_alignment);
+            while (sched.next(t)) { t.valid_rows = t.num_kb; emit(); }
+            break;
+        }
+        case DG_GEMM_BATCHED: walk(TileScheduler<kBatched>(128, bn, rg, sm, sn, ng, layout_host, c, nc)); break;
         default: fail(DG_ERR_INVALID_ARGUMENT, "unknown GEMM kind"); return -DG_ERR_INVALID_ARGUMENT;
     }
     return count;

@@ -15,6 +15,9 @@ splitk_reduce_kernel(const float* __restrict__ ws, void* __restrict__ d, int m, 
                      int64_t ldd, int num_splits, float alpha) {
     const int col = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
     const int row = blockIdx.y;
+    // Launched with programmatic stream serialisation right behind the GEMM that fills the panels: the blocks may
+    // already be resident while that GEMM drains, and wait here until it has completed and its stores are visible
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (col >= n || row >= m) return;
     const float* src = ws + static_cast<int64_t>(row) * ld_ws + col;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -54,11 +57,19 @@ int launch_splitk_reduce(const float* ws, void* d, int m, int n, int64_t ld_ws, 
                          float alpha, bool d_fp32, cudaStream_t stream) {
     const dim3 grid(ceil_div(ceil_div(n, 4), 256), m);
     const int64_t panel_stride = panel_rows * ld_ws;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = dim3(256);
+    config.stream = stream;
+    cudaLaunchAttribute attr = {};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &attr;
+    config.numAttrs = 1;
     if (d_fp32)
-        splitk_reduce_kernel<true><<<grid, 256, 0, stream>>>(ws, d, m, n, ld_ws, panel_stride, ldd, num_splits, alpha);
+        DG_CUDA_RT(cudaLaunchKernelEx(&config, splitk_reduce_kernel<true>, ws, d, m, n, ld_ws, panel_stride, ldd, num_splits, alpha));
     else
-        splitk_reduce_kernel<false><<<grid, 256, 0, stream>>>(ws, d, m, n, ld_ws, panel_stride, ldd, num_splits, alpha);
-    DG_CUDA_RT(cudaGetLastError());
+        DG_CUDA_RT(cudaLaunchKernelEx(&config, splitk_reduce_kernel<false>, ws, d, m, n, ld_ws, panel_stride, ldd, num_splits, alpha));
     return DG_OK;
 }
 

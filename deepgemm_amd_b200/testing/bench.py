@@ -51,11 +51,13 @@ def bench(fn, num_warmups: int = 5, num_tests: int = 20, flush_l2_bytes: int = 2
     return sum(s.elapsed_time(e) for s, e in zip(starts, ends)) / num_tests / 1e3
 
 
-def bench_kineto(fn, kernel_names, num_tests: int = 20, flush_l2_bytes: int = 256 << 20) -> float:
+def bench_kineto(fn, kernel_names, num_tests: int = 20, flush_l2_bytes: int = 256 << 20, span: bool = False) -> float:
     """Mean device seconds per call of fn(), counting only kernels whose name contains one of `kernel_names`
     (a string or a tuple), from the torch profiler's kernel records, with an L2 flush before every call: the method
     of the reference's deep_gemm/testing/bench.py:79-146.  Unlike event timing it excludes launch gaps, which
-    matter for kernels of a few microseconds."""
+    matter for kernels of a few microseconds.  With `span`, a call that launches several matching kernels counts
+    from the start of its first to the end of its last (kernels launched with programmatic dependent launch overlap,
+    so their durations must not be added)."""
     names = (kernel_names,) if isinstance(kernel_names, str) else tuple(kernel_names)
     flush = torch.empty(flush_l2_bytes // 4, dtype=torch.int, device="cuda") if flush_l2_bytes else None
     fn()
@@ -66,9 +68,17 @@ def bench_kineto(fn, kernel_names, num_tests: int = 20, flush_l2_bytes: int = 25
                 flush.zero_()
             fn()
         torch.cuda.synchronize()
-    total_us = 0.0
-    for evt in prof.events():
-        if evt.device_type == torch.autograd.DeviceType.CUDA and any(n in evt.name for n in names):
-            total_us += evt.device_time_total if hasattr(evt, "device_time_total") else evt.cuda_time_total
-    assert total_us > 0, f"no kernel matching {names} was recorded"
+    matched = [evt for evt in prof.events()
+               if evt.device_type == torch.autograd.DeviceType.CUDA and any(n in evt.name for n in names)]
+    assert matched, f"no kernel matching {names} was recorded"
+    if span:
+        matched.sort(key=lambda e: e.time_range.start)
+        per_call, rem = divmod(len(matched), num_tests)
+        assert rem == 0, f"{len(matched)} matching kernels over {num_tests} calls"
+        total_us = 0.0
+        for i in range(num_tests):
+            group = matched[i * per_call:(i + 1) * per_call]
+            total_us += max(e.time_range.end for e in group) - min(e.time_range.start for e in group)
+        return total_us / num_tests / 1e6
+    total_us = sum(evt.device_time_total if hasattr(evt, "device_time_total") else evt.cuda_time_total for evt in matched)
     return total_us / num_tests / 1e6

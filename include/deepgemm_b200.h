@@ -245,8 +245,9 @@ typedef struct dg_gemm_config {
 /* get_best_config<SM100ArchSpec> (heuristics/common.hpp:17-56, sm100.hpp:30-301).  Host only. */
 DG_API int dg_get_gemm_config(int kind, const dg_gemm_args_t* args, dg_gemm_config_t* config);
 
-/* Host model of the device tile scheduler (scheduler/gemm.cuh:108-204 in the reference): lists the
- * tiles CTA `cta` of `num_ctas` visits, four uint32 per tile {m_block, n_block, group, valid_rows}.
+/* Host model of the device tile scheduler (scheduler/gemm.cuh:108-263 in the reference): lists the
+ * tiles CTA `cta` of `num_ctas` visits, four uint32 per tile {m_block, n_block, group, valid_rows}
+ * (prefix-sum layout: m_block counts from row 0 of A; k-grouped: the fourth word is the slice's K-block count).
  * `layout` is a HOST pointer here.  Returns the number of tiles (may exceed max_tiles; only
  * max_tiles are written) or a negative dg_status_t. */
 DG_API int dg_enumerate_tiles(int kind, int block_n, int raster_group, int shape_m, int shape_n, int num_groups,

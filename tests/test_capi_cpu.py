@@ -183,6 +183,17 @@ def test_scheduler_prefix_sum_layout_walks_each_group_from_its_aligned_start(act
         dg.set_mk_alignment_for_contiguous_layout(128)
 
 
+def test_scheduler_k_grouped_and_batched_give_every_group_the_full_tile_grid():
+    m, n, bn = 300, 1000, 112
+    ks = (256, 0, 1024, 128)
+    tiles = _enumerate(4, bn, 16, m, n, len(ks), ks, 37)
+    want = {(g, mb, nb): k // 128 for g, k in enumerate(ks) for mb in range(3) for nb in range(9)}
+    got = {(t[2], t[0], t[1]): t[3] for t in tiles}
+    assert len(tiles) == len(got) == len(want) and got == want
+    tiles = _enumerate(5, bn, 16, m, n, 5, None, 37)
+    assert sorted((t[2], t[0], t[1]) for t in tiles) == sorted((b, mb, nb) for b in range(5) for mb in range(3) for nb in range(9))
+
+
 @pytest.mark.parametrize("counts,max_m", [((45, 83, 0, 256, 129), 256), ((0, 0, 0), 128), ((300, 1), 256), ((64,) * 16, 256)])
 def test_scheduler_masked_follows_device_counts(counts, max_m):
     n, bn = 4096, 240
