@@ -550,7 +550,11 @@ def _fp8_bmm(a, sfa, b, sfb, d, c, recipe, epilogue) -> None:
     batch_, n, k_ = b.shape
     _require(batch == batch_ == d.size(0), "batch_size == batch_size_ and batch_size == batch_size__")
     _require(m == d.size(1) and n == d.size(2) and k == k_, "m == m_ and n == n_ and k == k_")
-    _require(a.dtype == torch.float8_e4m3fn and b.dtype == torch.float8_e4m3fn, "a.scalar_type() == torch::kFloat8_e4m3fn")
+    is_bf16 = sfa is None
+    if is_bf16:
+        _require_bf16(a, b)
+    else:
+        _require(a.dtype == torch.float8_e4m3fn and b.dtype == torch.float8_e4m3fn, "a.scalar_type() == torch::kFloat8_e4m3fn")
     sfd = epilogue.sfd if isinstance(epilogue, FP8Quantization) else None
     if sfd is not None:
         # the scales are those of a per-token cast of D viewed as [m, batch * n] (einsum.hpp:219-228)
@@ -574,10 +578,15 @@ def _fp8_bmm(a, sfa, b, sfb, d, c, recipe, epilogue) -> None:
         return
     if c is not None and not is_cd_same:
         d.copy_(c)
-    tsfa, tsfb, gran_k_a, gran_k_b = _transform_sf_pair(sfa, sfb, m, n, k, recipe, None, None, batch, batch, False)
     _require(_resolve_alpha(None, epilogue) is None, "batched GEMMs take no alpha")
-    args = _fill_args(a, tsfa, b, tsfb, d, m, n, k, batch, major_a, major_b, gran_k_a, gran_k_b, accumulate=c is not None, sfd=sfd,
-                      stochastic=_stochastic(epilogue, c, d))
+    if is_bf16:
+        args = _bf16_args(a, b, d, m, n, k, batch, major_a, major_b, accumulate=c is not None, stochastic=_stochastic(epilogue, c, d))
+        if sfd is not None:
+            args.sfd, args.sfd_pitch = sfd.data_ptr(), sfd.stride(-1)
+    else:
+        tsfa, tsfb, gran_k_a, gran_k_b = _transform_sf_pair(sfa, sfb, m, n, k, recipe, None, None, batch, batch, False)
+        args = _fill_args(a, tsfa, b, tsfb, d, m, n, k, batch, major_a, major_b, gran_k_a, gran_k_b, accumulate=c is not None, sfd=sfd,
+                          stochastic=_stochastic(epilogue, c, d))
     args.batch_stride_a, args.batch_stride_b, args.batch_stride_d = a.stride(0), b.stride(0), d.stride(0)
     check(lib.dg_fp8_bmm(C.byref(args)))
 
@@ -600,6 +609,71 @@ def fp8_einsum(expr: str, a, b, d, c=None, recipe=(1, 128, 128), epilogue=None) 
         _fp8_bmm(a_data.permute(1, 2, 0), a_sf.permute(1, 2, 0), b_data.permute(1, 2, 0), b_sf.permute(1, 2, 0), d, c, recipe, epilogue)
     else:
         raise RuntimeError(f"Unsupported einsum expression: {expr}")
+
+
+def einsum(expr: str, a, b, d, c=None, epilogue=None) -> None:
+    """BF16 contractions of csrc/apis/einsum.hpp:63-181 that are batched GEMMs over permuted views: 'bhr,hdr->bhd',
+    'bhd,hdr->bhr' and 'bhd,bhr->hdr' ('bmk,bnk->mn', a reduction over the batch as well, is not built)."""
+    if expr == "bhr,hdr->bhd":
+        _fp8_bmm(a.permute(1, 0, 2), None, b, None, d.permute(1, 0, 2), c.permute(1, 0, 2) if c is not None else None, None, epilogue)
+    elif expr == "bhd,hdr->bhr":
+        _fp8_bmm(a.permute(1, 0, 2), None, b.permute(0, 2, 1), None, d.permute(1, 0, 2), c.permute(1, 0, 2) if c is not None else None,
+                 None, epilogue)
+    elif expr == "bhd,bhr->hdr":
+        _fp8_bmm(a.permute(1, 2, 0), None, b.permute(1, 2, 0), None, d, c, None, epilogue)
+    else:
+        raise RuntimeError(f"Unsupported einsum expression: {expr}")
+
+
+def k_grouped_fp4_gemm_nt_contiguous(a, b, d, ks_cpu, grouped_layout, c=None, recipe=(1, 1, 32), compiled_dims: str = "mn",
+                                     use_psum_layout: bool = False, epilogue=None) -> None:
+    """csrc/apis/gemm.hpp:414-473: the k-grouped GEMM for packed FP4 operands A [M, sum_k / 2], B [N, sum_k / 2] (K-major,
+    one scale per 32 elements); the contiguous-layout alignment must be a multiple of 256."""
+    (a_data, a_sf), (b_data, b_sf) = a, b
+    recipe = tuple(recipe)
+    _require(recipe == (1, 1, 32), "recipe == std::make_tuple(1, 1, 32)")
+    _require(a_data.dtype == kPackedFP4 and b_data.dtype == kPackedFP4, "a.first.scalar_type() == kPackedFP4 and b.first.scalar_type() == kPackedFP4")
+    _require(a_data.stride(-1) == 1 and b_data.stride(-1) == 1, "major_a == cute::UMMA::Major::K and major_b == cute::UMMA::Major::K")
+    k_alignment = get_mk_alignment_for_contiguous_layout()
+    _require(k_alignment % 256 == 0, "k_alignment % 256 == 0")
+    _require(d.dim() == 3 and a_data.dim() == 2 and b_data.dim() == 2, "t.dim() == N")
+    num_groups, m, n = d.shape
+    sum_k = _k_grouped_sizes(ks_cpu, grouped_layout, num_groups, use_psum_layout, k_alignment, a_data.size(1) * 2)
+    _require(m == a_data.size(0) and n == b_data.size(0) and sum_k == a_data.size(1) * 2 == b_data.size(1) * 2,
+             "m == m_ and n == n_ and sum_k == sum_k_ and sum_k == sum_k__")
+    _require(a_data.is_contiguous() and b_data.is_contiguous() and d.is_contiguous(), "a.first.is_contiguous()")
+    _require(c is None or c.is_contiguous(), "not c.has_value() or c.value().is_contiguous()")
+    _require(d.dtype in (torch.bfloat16, torch.float), "d.scalar_type() == torch::kBFloat16 or d.scalar_type() == torch::kFloat")
+    _require(_resolve_alpha(None, epilogue) is None, "k-grouped GEMMs take no alpha")
+    if m == 0 or n == 0:
+        return
+    is_cd_same = c is not None and c.data_ptr() == d.data_ptr()
+    if c is not None:
+        _require(d.dtype == c.dtype and c.shape == d.shape, "d.scalar_type() == c.value().scalar_type()")
+    if sum_k == 0:
+        if not is_cd_same:
+            d.copy_(c) if c is not None else d.zero_()
+        return
+    if c is not None and not is_cd_same:
+        d.copy_(c)
+    sfa = transform_k_grouped_sf_into_required_layout(a_sf, ks_cpu, grouped_layout, recipe, k_alignment, use_psum_layout)
+    sfb = transform_k_grouped_sf_into_required_layout(b_sf, ks_cpu, grouped_layout, recipe, k_alignment, use_psum_layout)
+    args = GemmArgs()
+    args.a, args.sfa, args.b, args.sfb, args.d = a_data.data_ptr(), sfa.data_ptr(), b_data.data_ptr(), sfb.data_ptr(), d.data_ptr()
+    args.m, args.n, args.k, args.num_groups = m, n, sum_k, num_groups
+    args.a_dtype = args.b_dtype = _lib.DG_FP4_E2M1_X2
+    args.d_dtype = _d_dtype(d)
+    args.major_a = args.major_b = _lib.DG_MAJOR_K
+    args.lda, args.ldb, args.ldd = a_data.stride(0), b_data.stride(0), n
+    args.sfa_pitch, args.sfb_pitch = m, n
+    args.gran_k_a = args.gran_k_b = 32
+    args.accumulate = int(c is not None)
+    args.alpha = 1.0
+    args.grouped_layout = grouped_layout.data_ptr()
+    args.use_psum_layout = int(use_psum_layout)
+    args.stochastic_rounding = int(_stochastic(epilogue, c, d))
+    args.stream = _stream()
+    check(lib.dg_k_grouped_fp8_gemm_contiguous(C.byref(args)))
 
 
 def _t(x):

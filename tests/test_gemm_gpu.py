@@ -811,6 +811,59 @@ def test_bf16_grouped_gemms_match_fp32_matmul():
         assert np.allclose(dk[i].cpu().numpy(), want, rtol=1e-5, atol=1e-3)
 
 
+def test_bf16_einsum_contractions_match_fp32():
+    b, h, r, d = 136, 3, 320, 256
+    x, y = seeded_bf16((b, h, r), 151), seeded_bf16((h, d, r), 152)
+    z = torch.full((b, h, d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    dg.reset_kernel_status()
+    dg.einsum("bhr,hdr->bhd", _bf16_cuda(x), _bf16_cuda(y), z)
+    assert dg.kernel_status() == 0
+    ref = np.einsum("bhr,hdr->bhd", x.astype(np.float64), y.astype(np.float64))
+    assert oracle.calc_diff(z.float().cpu().numpy(), oracle.bf16_round(ref.astype(np.float32))) < 1e-5
+    x2, y2 = seeded_bf16((b, h, d), 153), seeded_bf16((h, d, r), 154)
+    z2 = torch.full((b, h, r), float("nan"), dtype=torch.float, device="cuda")
+    dg.einsum("bhd,hdr->bhr", _bf16_cuda(x2), _bf16_cuda(y2), z2)
+    assert dg.kernel_status() == 0
+    ref2 = np.einsum("bhd,hdr->bhr", x2.astype(np.float64), y2.astype(np.float64))
+    assert oracle.calc_diff(z2.cpu().numpy(), ref2) < 1e-9
+    x3, y3 = seeded_bf16((256, h, d), 155), seeded_bf16((256, h, r), 156)
+    z0 = seeded_bf16((h, d, r), 157, 10.0)
+    z3 = torch.from_numpy(z0).cuda()
+    dg.einsum("bhd,bhr->hdr", _bf16_cuda(x3), _bf16_cuda(y3), z3, c=z3)
+    assert dg.kernel_status() == 0
+    ref3 = z0 + np.einsum("bhd,bhr->hdr", x3.astype(np.float64), y3.astype(np.float64))
+    assert oracle.calc_diff(z3.cpu().numpy(), ref3) < 1e-9
+
+
+def test_k_grouped_fp4_gemm_matches_oracle():
+    alignment = 256
+    dg.set_mk_alignment_for_contiguous_layout(alignment)
+    try:
+        ks = (256, 0, 512)
+        slices, layout, sum_k = oracle.k_grouped_slices(ks, alignment, False)
+        m, n = 208, 304
+        def operand(mn, seed):
+            x = np.zeros((mn, sum_k), dtype=np.float32)
+            for i, (s0, k, _) in enumerate(slices):
+                x[:, s0:s0 + k] = seeded_bf16((mn, k), seed + i)
+            q, sf = oracle.per_token_cast_to_fp4(x, True, 32)                     # [mn, sum_k / 2], [mn, sum_k / 32]
+            return q, sf, oracle.cast_back_from_fp4(q, sf, 32)
+        qa, sfa, da = operand(m, 161)
+        qb, sfb, db = operand(n, 171)
+        d = torch.full((len(ks), m, n), float("nan"), dtype=torch.float, device="cuda")
+        dg.reset_kernel_status()
+        dg.k_grouped_fp4_gemm_nt_contiguous((fp4_cuda(qa), torch.from_numpy(np.ascontiguousarray(sfa.T)).cuda()),
+                                            (fp4_cuda(qb), torch.from_numpy(np.ascontiguousarray(sfb.T)).cuda()), d,
+                                            [p for _, _, p in slices], torch.from_numpy(layout).cuda())
+        assert dg.kernel_status() == 0
+        out = d.cpu().numpy()
+        for i, (s0, k, _) in enumerate(slices):
+            want = da[:, s0:s0 + k].astype(np.float64) @ db[:, s0:s0 + k].astype(np.float64).T
+            assert (out[i] == 0).all() if k == 0 else oracle.calc_diff(out[i], want) < 1e-9
+    finally:
+        dg.set_mk_alignment_for_contiguous_layout(128)
+
+
 # ---------------------------------------------------------------------------------------------------
 # scale layout kernels and quantisation helpers
 # ---------------------------------------------------------------------------------------------------
