@@ -39,7 +39,7 @@ class GemmArgs(C.Structure):
 class GemmConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in (
         "block_m", "block_n", "block_k", "num_stages", "cluster_size", "raster_group", "num_ctas",
-        "smem_bytes", "tmem_cols", "num_tiles", "waves_x100", "num_splits", "kb_per_split")]
+        "smem_bytes", "tmem_cols", "num_tiles", "waves_x100", "num_splits", "kb_per_split", "split_in_cluster")]
 
     def as_dict(self):
         return {n: getattr(self, n) for n, _ in self._fields_}
@@ -82,6 +82,7 @@ SIGNATURES = {
                                      C.c_int, C.c_int, C.c_void_p, C.c_int]),
     "dg_jit_compile": (C.c_int, [C.c_char_p, C.c_char_p, C.c_char_p, C.c_char_p, C.POINTER(C.c_void_p)]),
     "dg_jit_kernel_path": (C.c_char_p, [C.c_void_p]),
+    "dg_jit_max_active_clusters": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(C.c_int)]),
     "dg_jit_launch": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_int, C.c_void_p,
                                 C.POINTER(C.c_void_p)]),
     "dg_kernel_status": (C.c_int, []),

@@ -49,6 +49,13 @@
 // (dg_splitk.cu) then adds the panels in slice order, applies alpha and converts, so the result does not
 // depend on which CTA finished first.
 //
+// DG_SPLIT_CLUSTER = S > 1 (dense only; the form of K slicing used whenever S <= 8 clusters fit the GPU): the S work
+// items of an output tile are the CTAs of one thread-block cluster.  Each CTA runs the main loop over its slice of K;
+// CTAs 1 .. S-1 then park their FP32 accumulator in their own shared memory (the pipeline stages are free by then),
+// the cluster synchronises, and CTA 0 adds the parked tiles to its own accumulator in rank order, reading them through
+// distributed shared memory, before the ordinary epilogue.  No workspace, no second kernel, and the same bits as the
+// two-kernel form (both add the slices in slice order).
+//
 // MN-major operands (the nn / tn / tt variants): the tile is staged as [128 of K][128 B of MN] atoms with the
 // same 128-byte swizzle (one TMA box per 128 columns of MN), the descriptor's leading-dimension offset steps
 // between atoms, and a step of 32 along K is 32 rows = 4096 B.
@@ -104,6 +111,7 @@ constexpr bool     kStochastic = DG_STOCHASTIC_ROUNDING != 0;      // BF16 outpu
 constexpr bool     kAccumulate = DG_ACCUMULATE != 0;
 constexpr uint32_t kRasterGroup = DG_RASTER_GROUP;
 constexpr bool     kSplitK     = DG_SPLIT_K != 0;
+constexpr uint32_t kSplitCluster = DG_SPLIT_CLUSTER;   // CTAs of a cluster sharing one output tile along K (1 = off)
 
 constexpr uint32_t kMHalves    = DG_M_HALVES;      // 128-row MMAs per CTA and K-block (1 or 2)
 
@@ -146,6 +154,9 @@ static_assert(!kStochastic || (!kDIsFP32 && !kDIsFP8 && !kAccumulate), "stochast
 static_assert(!kDIsFP8 || ((kGemmType == kDense || kGemmType == kBatched) && !kAccumulate && !kSplitK && BLOCK_N % 32 == 0),
               "the quantising epilogue serves the dense and batched GEMMs with tiles of whole 32-column scale groups");
 static_assert(kGemmType != kBatched || (kCluster == 1 && !kSplitK), "batched: one CTA per tile");
+static_assert(kSplitCluster >= 1 && kSplitCluster <= 8, "portable cluster sizes");
+static_assert(kSplitCluster == 1 || (kGemmType == kDense && !kSplitK && kCluster == 1 && kMHalves == 1 && !kAccumulate && !kDIsFP8 && !kStochastic),
+              "cluster-reduced K slicing serves the plain dense GEMM");
 constexpr GemmLayout kLayout{CTA_M, BLOCK_N, BLOCK_K, kNumStages, kDElemBytes, kCluster, kBMnMajor ? 1u : 0u, kGranKA, kGranKB,
                              DG_SHORT_K, kABElemBytes};
 constexpr uint32_t kNumSFABuffers = kHasSF ? kLayout.sfa_buffers() : 1, kNumSFBBuffers = kHasSF ? kLayout.sfb_buffers() : 1;
@@ -244,6 +255,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
     const uint32_t smem_base = smem_u32(smem);
     const uint32_t cta_rank = kCluster == 1 ? 0u : cluster_ctarank();
     const bool is_leader = cta_rank == 0;
+    const uint32_t split_rank = kSplitCluster == 1 ? 0u : cluster_ctarank();      // which slice of K this CTA computes
 
     auto full_bar     = [&](uint32_t s) { return smem_base + kSmemBar + s * 8; };
     auto sf_full_bar  = [&](uint32_t s) { return smem_base + kSmemBar + (kNumStages + s) * 8; };
@@ -312,8 +324,10 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
     const uint32_t sfb_rows_per_group = (p.shape_k + kGranKB * 4 - 1) / (kGranKB * 4);
 
     // A cluster walks the tile list as one unit
+    // (cluster-reduced slicing: a cluster has exactly one tile, so the stride past it ends every role's loop)
     TileScheduler<kGemmType> sched(TILE_M, BLOCK_N, kRasterGroup, p.shape_m, p.shape_n, p.num_groups, p.grouped_layout,
-                                   blockIdx.x / kCluster, gridDim.x / kCluster, kSplitK ? p.num_splits : 1u);
+                                   blockIdx.x / (kCluster * kSplitCluster),
+                                   kSplitCluster > 1 ? 0x40000000u : gridDim.x / kCluster, kSplitK ? p.num_splits : 1u);
     if constexpr (kGemmType == kMGroupedPsum) {
         sched.group_alignment = p.group_alignment;
         sched.write_padding = DG_WRITE_PADDING;
@@ -325,11 +339,11 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
         sched.k_per_block = BLOCK_K_ELEMS;
     }
     // K-blocks [kb_begin, kb_end) of a work item: all of K unless the GEMM is split
-    auto kb_begin = [&](const Tile& t) { return kSplitK ? t.split * p.kb_per_split : 0u; };
+    auto kb_begin = [&](const Tile& t) { return kSplitK ? t.split * p.kb_per_split : (kSplitCluster > 1 ? split_rank * p.kb_per_split : 0u); };
     auto kb_end = [&](const Tile& t) {
         if constexpr (kGemmType == kKGrouped) return t.num_kb;
-        if constexpr (!kSplitK) return num_k_blocks;
-        const uint32_t e = (t.split + 1) * p.kb_per_split;
+        if constexpr (!kSplitK && kSplitCluster == 1) return num_k_blocks;
+        const uint32_t e = ((kSplitK ? t.split : split_rank) + 1) * p.kb_per_split;
         return e < num_k_blocks ? e : num_k_blocks;
     };
     // A 256-row tile of the contiguous layout whose halves belong to different experts takes two passes over K:
@@ -603,6 +617,13 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                 DG_PROF_FLUSH(kProfSFTotal, prof_total);
             }
         }
+        if constexpr (kSplitCluster > 1) {
+            // The role warps have nothing to publish: they only take part in the cluster-wide barrier that separates
+            // "every slice is parked" from "CTA 0 adds them up"
+            __syncwarp();
+            cluster_arrive();
+            cluster_wait();
+        }
     } else {
         if constexpr (kMHalves == 2) warpgroup_reg_inc<kEpilogueRegs>();
         // ================= epilogue =================
@@ -625,6 +646,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
         constexpr bool kRowInRegs = kMHalves == 2 && !kDIsFP32;
         constexpr uint32_t kGroupBytes = kLayout.group_bytes();
         bool ok = true;
+        [[maybe_unused]] bool cluster_synced = false;
         uint32_t tile_iter = 0, store_iter = 0;
         DG_PROF_VAR(prof_wait); DG_PROF_VAR(prof_store);
         DG_PROF_BEGIN(prof_t0);
@@ -655,6 +677,83 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
             if (!mbar_wait(tmem_full_bar(accum), accum_phase, ctx, kRoleEpilogue, 1)) { ok = false; break; }
             DG_PROF_ADD(prof_wait, prof_w);
             tc_fence_after_sync();
+
+            // Cluster-reduced K slicing.  Every CTA of the cluster parks its FP32 accumulator in its own shared memory,
+            // over the drained pipeline stages, column by column (word (column * 128 + row): consecutive threads,
+            // consecutive banks).  After a cluster barrier the CTAs share the reduction: CTA r owns the 8-column
+            // chunks r, r + S, ...; for each, a thread adds the S slices of its row in slice order (its own through
+            // the same window), scales, converts and writes the 8 values straight to D.
+            if constexpr (kSplitCluster > 1) {
+                static_assert(kSplitCluster == 1 || BLOCK_N * BLOCK_M * 4 <= kNumStages * (kABytes + kBBytes), "the parked tile fits the stages");
+                const uint32_t park_addr = smem_base + kSmemA + row_in_tile * 4;
+                #pragma unroll
+                for (uint32_t b = 0; b < BLOCK_N / 16; ++b) {
+                    uint32_t v[16];
+                    tmem_ld_32x32b_x16(tmem_base + ((quarter * 32) << 16) + accum * UMMA_N + b * 16, v);
+                    tmem_ld_wait();
+                    #pragma unroll
+                    for (uint32_t i = 0; i < 16; ++i) st_shared_u32(park_addr + (b * 16 + i) * BLOCK_M * 4, v[i]);
+                }
+                tc_fence_before_sync();
+                mbar_arrive(tmem_empty_bar(accum));
+                cluster_arrive();               // release: the parked tile is visible to the cluster
+                cluster_wait();
+                cluster_synced = true;
+
+                const uint32_t d_row = tile.m_block * BLOCK_M + row_in_tile;
+                uint32_t peers[kSplitCluster];
+                #pragma unroll
+                for (uint32_t r = 0; r < kSplitCluster; ++r) peers[r] = map_to_cta(park_addr, r);
+                constexpr uint32_t kChunks = BLOCK_N / 8;
+                if (d_row < p.shape_m) {
+                    uint8_t* drow = reinterpret_cast<uint8_t*>(p.d) + static_cast<size_t>(d_row) * p.ldd * kDElemBytes;
+                    #pragma unroll
+                    for (uint32_t jj = 0; jj < (kChunks + kSplitCluster - 1) / kSplitCluster; ++jj) {
+                        const uint32_t j = jj * kSplitCluster + split_rank;
+                        const uint32_t col = tile.n_block * BLOCK_N + j * 8;
+                        if (j < kChunks && col < p.shape_n) {
+                            uint32_t part[kSplitCluster][8];
+                            #pragma unroll
+                            for (uint32_t r = 0; r < kSplitCluster; ++r) {
+                                #pragma unroll
+                                for (uint32_t i = 0; i < 8; ++i) part[r][i] = ld_shared_cluster_u32(peers[r] + (j * 8 + i) * BLOCK_M * 4);
+                            }
+                            float sum[8];
+                            #pragma unroll
+                            for (uint32_t i = 0; i < 8; ++i) {
+                                sum[i] = 0.0f;                  // (0 + first slice: the same operations as the two-kernel reduction)
+                                #pragma unroll
+                                for (uint32_t r = 0; r < kSplitCluster; ++r) sum[i] += __uint_as_float(part[r][i]);
+                                sum[i] *= p.alpha;
+                            }
+                            if constexpr (kDIsFP32) {
+                                float* out = reinterpret_cast<float*>(drow) + col;
+                                if (col + 8 <= p.shape_n) {
+                                    *reinterpret_cast<float4*>(out) = make_float4(sum[0], sum[1], sum[2], sum[3]);
+                                    *reinterpret_cast<float4*>(out + 4) = make_float4(sum[4], sum[5], sum[6], sum[7]);
+                                } else {
+                                    #pragma unroll
+                                    for (uint32_t i = 0; i < 8; ++i)
+                                        if (col + i < p.shape_n) out[i] = sum[i];
+                                }
+                            } else {
+                                unsigned short* out = reinterpret_cast<unsigned short*>(drow) + col;
+                                uint32_t q[4];
+                                #pragma unroll
+                                for (uint32_t i = 0; i < 4; ++i) q[i] = pack_bf16x2(sum[2 * i], sum[2 * i + 1]);
+                                if (col + 8 <= p.shape_n) {
+                                    *reinterpret_cast<uint4*>(out) = make_uint4(q[0], q[1], q[2], q[3]);
+                                } else {
+                                    #pragma unroll
+                                    for (uint32_t i = 0; i < 8; ++i)
+                                        if (col + i < p.shape_n) out[i] = static_cast<unsigned short>(q[i / 2] >> (16 * (i % 2)));
+                                }
+                            }
+                        }
+                    }
+                }
+                continue;
+            }
 
             const uint32_t n0 = tile.n_block * BLOCK_N;
             const uint32_t d_row0 = tile.d_row_base + tile.m_block * TILE_M + cta_rank * CTA_M + wg * BLOCK_M +
@@ -866,6 +965,12 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                 }
             }
         }
+        if constexpr (kSplitCluster > 1) {
+            if (!cluster_synced) {          // no tile, or a wait ran out: the rest of the cluster must not wait for ever
+                cluster_arrive();
+                cluster_wait();
+            }
+        }
         if (prof_thread) {
             DG_PROF_VAR(prof_total);
             DG_PROF_ADD(prof_total, prof_t0);
@@ -887,8 +992,9 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
         while (global_timer_ns() - t0 < 200000) { }
         __syncthreads();
     }
-    if constexpr (kCluster > 1) {
-        // Neither CTA may exit (or free tensor memory) while its peer can still signal its barriers
+    if constexpr (kCluster > 1 || kSplitCluster > 1) {
+        // Neither CTA may exit (or free tensor memory) while its peer can still signal its barriers or read its
+        // shared memory
         tc_fence_before_sync();
         cluster_arrive();
         cluster_wait();

@@ -43,6 +43,7 @@ struct Driver {
     CUresult (*cuModuleGetFunction)(CUfunction*, CUmodule, const char*) = nullptr;
     CUresult (*cuFuncSetAttribute)(CUfunction, CUfunction_attribute, int) = nullptr;
     CUresult (*cuLaunchKernelEx)(const CUlaunchConfig*, CUfunction, void**, void**) = nullptr;
+    CUresult (*cuOccupancyMaxActiveClusters)(int*, CUfunction, const CUlaunchConfig*) = nullptr;
     CUresult (*cuTensorMapEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                        const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                        CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill) = nullptr;

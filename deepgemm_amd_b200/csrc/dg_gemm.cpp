@@ -215,18 +215,21 @@ GemmLayout fit_stages(GemmLayout lay, int64_t item_kb, int max_stages) {
     return best;
 }
 
-int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
+int choose_config(const Problem& p, dg_gemm_config_t* cfg, bool allow_cluster_split = true) {
     const int num_sms = dg_get_num_sms();
     const int d_elem = p.d_fp32 ? 4 : (p.d_fp8 ? 1 : 2);
     const int ab_elem = p.ab_bf16 ? 2 : 1;
     const int64_t k_blocks = ceil_div<int64_t>(static_cast<int64_t>(p.k) * ab_elem, 128);   // in units of 128 bytes of K, whatever the stage size
     const int forced_bn = env_int("FORCE_BLOCK_N"), forced_cluster = env_int("FORCE_CLUSTER"), forced_splits = env_int("FORCE_SPLIT_K");
+    // DG_FORCE_SPLIT_CLUSTER: 1 = always reduce the slices of K inside a thread-block cluster, -1 = never (two kernels)
+    const int forced_split_cluster = env_int("FORCE_SPLIT_CLUSTER");
     const int forced_block_m = env_int("FORCE_BLOCK_M"), forced_block_k = env_int("FORCE_BLOCK_K");
     const int forced_stages = env_int("FORCE_NUM_STAGES");
 
     struct Candidate {
         double cost = 0;
         int bn = 0, bk = 128, cluster = 1, halves = 1, splits = 1, kb_per_split = 0;
+        bool in_cluster = false;
         int64_t tiles = 0;
         GemmLayout lay{};
     } best;
@@ -281,8 +284,15 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
                     splits = static_cast<int>(ceil_div<int64_t>(k_blocks, kb_per));
                     if (splits != want) continue;                          // same slicing as a smaller request
                 }
+                // The slices of a tile either go to a workspace that a second kernel adds up, or (up to 8 of them) run as
+                // the CTAs of one thread-block cluster whose first CTA adds the others' accumulators out of their shared
+                // memory: no workspace, no second launch, the same sums in the same order.
+                for (int in_cluster = 0; in_cluster <= (splits > 1 ? 1 : 0); ++in_cluster) {
+                if (splits > 1 && forced_split_cluster != 0 && in_cluster != (forced_split_cluster > 0 ? 1 : 0)) continue;
+                if (in_cluster && (!allow_cluster_split || splits > 8)) continue;
                 const int64_t tiles = mn_tiles * splits;
-                const int64_t waves = ceil_div<int64_t>(tiles, units);
+                // Clusters are placed inside one GPC each, so fewer of them fit than SMs / size suggests
+                const int64_t waves = in_cluster ? ceil_div<int64_t>(mn_tiles, std::max(1, (units - 8) / splits)) : ceil_div<int64_t>(tiles, units);
                 // The pipeline: as deep as shared memory allows, but no deeper than the K-blocks of two work items
                 // (k-grouped: the groups share K; an average slice stands for all of them)
                 // (in bytes of K per row)
@@ -292,11 +302,13 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
                 int max_stages = static_cast<int>(std::max<int64_t>(2, std::min<int64_t>(32, 2 * item_kb)));
                 if (forced_stages >= 2) max_stages = std::min(max_stages, forced_stages);
                 GemmLayout lay{128u * halves, static_cast<uint32_t>(bn), static_cast<uint32_t>(bk), 2,
-                               static_cast<uint32_t>(splits > 1 ? 4 : d_elem), static_cast<uint32_t>(cluster),
+                               static_cast<uint32_t>(splits > 1 && !in_cluster ? 4 : d_elem), static_cast<uint32_t>(cluster),
                                p.b_mn_major ? 1u : 0u, static_cast<uint32_t>(p.gran_k_a), static_cast<uint32_t>(p.gran_k_b), 0u,
                                static_cast<uint32_t>(ab_elem)};
                 lay = fit_stages(lay, p.kind == DG_GEMM_K_GROUPED_CONTIGUOUS ? 0 : item_kb, max_stages);   // slices may be one K-block
                 if (lay.num_stages == 0 || lay.tmem_cols_used() > kTmemCapacityCols) continue;
+                // A parked FP32 accumulator (128 rows x bn) has to fit the pipeline stages it overwrites
+                if (in_cluster && static_cast<uint64_t>(bn) * 128 * 4 > static_cast<uint64_t>(lay.num_stages) * (lay.a_bytes() + lay.b_bytes())) continue;
                 // Cycles per pipeline stage: the MMAs; shared memory, which moved ~150 B per cycle in every configuration
                 // measured, TMA writes and tensor-core reads together (a stage is written once, its A rows are read once
                 // and its B rows once per 128-row half), and into which no configuration pulled more than ~67 B per cycle
@@ -316,13 +328,17 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
                 // 256-row tiles have no spare accumulator: the next tile's MMAs start once the epilogue warpgroups have
                 // moved their rows from tensor memory into registers (~1400 cycles, measured)
                 if (halves == 2) cost = static_cast<double>(waves) * (per_tile + 1400.0) + epilogue + 2000.0;
-                if (splits > 1)   // second launch + reading S panels and writing D at a few TB/s (~2000 B per SM clock over the GPU)
+                if (splits > 1 && !in_cluster)   // second launch + reading S panels and writing D at a few TB/s (~2000 B per SM clock over the GPU)
                     cost += 6000.0 + static_cast<double>(splits + 1) * p.m * p.n * 4.0 / 2000.0;
+                if (in_cluster)                  // parking a tile, the cluster barrier, bn loads per thread across the cluster
+                    cost += 1200.0 + bn * 12.0;
                 if (best.bn == 0 || cost < best.cost - 1e-9 || (std::abs(cost - best.cost) <= 1e-9 && bn > best.bn)) {
                     best.cost = cost;
                     best.bn = bn; best.bk = bk; best.cluster = cluster; best.halves = halves;
                     best.tiles = tiles; best.splits = splits; best.kb_per_split = kb_per;
+                    best.in_cluster = in_cluster != 0;
                     best.lay = lay;
+                }
                 }
             }
         }
@@ -343,7 +359,9 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
     cfg->cluster_size = best.cluster;
     const int forced_raster = env_int("FORCE_RASTER_GROUP");
     cfg->raster_group = forced_raster > 0 ? forced_raster : std::max(4, 16 / (best.cluster * best.halves));
-    cfg->num_ctas = best.cluster * (p.kind == DG_GEMM_M_GROUPED_MASKED || p.kind == DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM
+    cfg->split_in_cluster = best.in_cluster ? 1 : 0;
+    cfg->num_ctas = best.in_cluster ? static_cast<int>(best.tiles) :
+                    best.cluster * (p.kind == DG_GEMM_M_GROUPED_MASKED || p.kind == DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM
                                         ? units : static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(units, best.tiles))));
     cfg->smem_bytes = static_cast<int>(best.lay.total_bytes());
     cfg->tmem_cols = static_cast<int>(best.lay.tmem_cols_alloc());
@@ -354,7 +372,7 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg) {
 
 // The layout the kernel of a configuration uses (same arithmetic as choose_config)
 GemmLayout layout_of(const Problem& p, const dg_gemm_config_t& cfg) {
-    const bool split = cfg.num_splits > 1;
+    const bool split = cfg.num_splits > 1 && !cfg.split_in_cluster;
     const int64_t ab_elem = p.ab_bf16 ? 2 : 1;
     const int64_t item_kb = p.kind == DG_GEMM_K_GROUPED_CONTIGUOUS ? 0 :
                             ceil_div<int64_t>(std::min<int64_t>(p.k * ab_elem, static_cast<int64_t>(cfg.kb_per_split) * 128), cfg.block_k);
@@ -383,12 +401,13 @@ std::string generate_source(const Problem& p, const dg_gemm_config_t& cfg) {
       << "#define DG_MAJOR_B " << (p.b_mn_major ? 1 : 0) << "\n"
       << "#define DG_GRAN_K_A " << p.gran_k_a << "\n"
       << "#define DG_GRAN_K_B " << p.gran_k_b << "\n"
-      << "#define DG_D_FP32 " << ((p.d_fp32 || cfg.num_splits > 1) ? 1 : 0) << "\n"
+      << "#define DG_D_FP32 " << ((p.d_fp32 || (cfg.num_splits > 1 && !cfg.split_in_cluster)) ? 1 : 0) << "\n"
       << "#define DG_D_FP8 " << (p.d_fp8 ? 1 : 0) << "\n"
       << "#define DG_STOCHASTIC_ROUNDING " << (p.stochastic ? 1 : 0) << "\n"
       << "#define DG_ACCUMULATE " << (p.accumulate ? 1 : 0) << "\n"
       << "#define DG_RASTER_GROUP " << cfg.raster_group << "\n"
-      << "#define DG_SPLIT_K " << (cfg.num_splits > 1 ? 1 : 0) << "\n"
+      << "#define DG_SPLIT_K " << (cfg.num_splits > 1 && !cfg.split_in_cluster ? 1 : 0) << "\n"
+      << "#define DG_SPLIT_CLUSTER " << (cfg.split_in_cluster ? cfg.num_splits : 1) << "\n"
       << "#define DG_WRITE_PADDING " << (p.write_padding ? 1 : 0) << "\n"
       << "#define DG_K_PSUM " << (p.k_psum ? 1 : 0) << "\n"
       << "#define DG_PROFILE " << env_int("PROFILE") << "\n"
@@ -466,7 +485,7 @@ struct Plan {
 
 int get_plan(const Problem& p, Plan* plan) {
     static const char* kEnvNames[] = {"FORCE_BLOCK_N", "FORCE_CLUSTER", "FORCE_SPLIT_K", "FORCE_BLOCK_M", "FORCE_BLOCK_K",
-                                      "FORCE_NUM_STAGES", "FORCE_RASTER_GROUP", "PROFILE"};
+                                      "FORCE_NUM_STAGES", "FORCE_RASTER_GROUP", "PROFILE", "FORCE_SPLIT_CLUSTER"};
     std::array<int, 32> key{};
     int i = 0;
     for (int v : {p.kind, p.m, p.n, p.k, p.groups, static_cast<int>(p.a_fp4), static_cast<int>(p.b_fp4), static_cast<int>(p.ab_bf16),
@@ -488,6 +507,18 @@ int get_plan(const Problem& p, Plan* plan) {
     int rc = choose_config(p, &plan->cfg);
     if (rc != DG_OK) return rc;
     if ((rc = get_kernel(p, plan->cfg, &plan->kernel)) != DG_OK) return rc;
+    if (plan->cfg.split_in_cluster) {
+        // A cluster is placed inside one GPC: make sure this device can hold one of this size and shared memory at all
+        // (clusters beyond the ones that fit at once simply run later; nothing waits across clusters)
+        int fit = 0;
+        rc = dg_jit_max_active_clusters(plan->kernel, 128 + plan->cfg.block_m, plan->cfg.num_splits, plan->cfg.smem_bytes, &fit);
+        if (env_int("PRINT_CONFIGS"))
+            fprintf(stderr, "[dg] clusters of %d CTAs that fit at once: %d (status %d)\n", plan->cfg.num_splits, fit, rc);
+        if (rc != DG_OK || fit < 1) {
+            if ((rc = choose_config(p, &plan->cfg, false)) != DG_OK) return rc;
+            if ((rc = get_kernel(p, plan->cfg, &plan->kernel)) != DG_OK) return rc;
+        }
+    }
     std::lock_guard<std::mutex> lock(mu);
     if (plans.size() > 4096) plans.clear();
     plans[key] = *plan;
@@ -513,12 +544,13 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
     const dg_gemm_config_t& cfg = plan.cfg;
     dg_kernel_t kernel = plan.kernel;
     if (env_int("PRINT_CONFIGS"))
-        fprintf(stderr, "[dg] kind %d m %d n %d k %d groups %d -> block_m %d block_n %d block_k %d cluster %d stages %d ctas %d smem %d tiles %d splits %d x %d\n",
+        fprintf(stderr, "[dg] kind %d m %d n %d k %d groups %d -> block_m %d block_n %d block_k %d cluster %d stages %d ctas %d smem %d tiles %d splits %d x %d%s\n",
                 kind, p.m, p.n, p.k, p.groups, cfg.block_m, cfg.block_n, cfg.block_k, cfg.cluster_size, cfg.num_stages, cfg.num_ctas, cfg.smem_bytes, cfg.num_tiles,
-                cfg.num_splits, cfg.kb_per_split);
+                cfg.num_splits, cfg.kb_per_split, cfg.split_in_cluster ? " (in a cluster)" : "");
     if (fixed_scratch == nullptr && (rc = ensure_status_word()) != DG_OK) return rc;
 
-    const bool split = cfg.num_splits > 1;
+    const bool split = cfg.num_splits > 1 && !cfg.split_in_cluster;     // through the workspace and a second kernel
+    const int launch_cluster = cfg.split_in_cluster ? cfg.num_splits : cfg.cluster_size;
     const bool kernel_d_fp32 = p.d_fp32 || split;
     const GemmLayout lay = layout_of(p, cfg);
     // Split-K: the kernel's D is the workspace, num_splits panels of [align(m, 128)][align(n, 4)] FP32
@@ -612,7 +644,7 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
     const float alpha = a->has_alpha ? a->alpha : 1.0f;
     params.alpha = split ? 1.0f : alpha;              // split-K applies alpha in the reduction pass
     params.profile = nullptr;
-    params.num_splits = cfg.num_splits;
+    params.num_splits = split ? cfg.num_splits : 1;
     params.kb_per_split = cfg.kb_per_split;
     params.split_panel_rows = static_cast<uint32_t>(panel_rows);
     params.group_alignment = static_cast<uint32_t>(state().mk_alignment);
@@ -624,7 +656,7 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
         params.profile = profile_buffer();
         if (params.profile == nullptr) return fail(DG_ERR_CUDA, "cannot allocate the profile buffer");
         DG_CUDA_RT(cudaMemsetAsync(params.profile, 0, 32 * sizeof(unsigned long long), static_cast<cudaStream_t>(a->stream)));
-        rc = dg_jit_launch(kernel, cfg.num_ctas, 128 + cfg.block_m, cfg.cluster_size, cfg.smem_bytes, state().pdl, a->stream, kargs);
+        rc = dg_jit_launch(kernel, cfg.num_ctas, 128 + cfg.block_m, launch_cluster, cfg.smem_bytes, state().pdl, a->stream, kargs);
         if (rc != DG_OK) return rc;
         unsigned long long h[32];
         DG_CUDA_RT(cudaMemcpyAsync(h, params.profile, sizeof(h), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(a->stream)));
@@ -643,7 +675,7 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
                                         static_cast<cudaStream_t>(a->stream));
         return DG_OK;
     }
-    if ((rc = dg_jit_launch(kernel, cfg.num_ctas, 128 + cfg.block_m, cfg.cluster_size, cfg.smem_bytes, state().pdl, a->stream, kargs)) != DG_OK) return rc;
+    if ((rc = dg_jit_launch(kernel, cfg.num_ctas, 128 + cfg.block_m, launch_cluster, cfg.smem_bytes, state().pdl, a->stream, kargs)) != DG_OK) return rc;
     if (split)
         return launch_splitk_reduce(workspace, a->d, p.m, p.n, ld_ws, panel_rows, a->ldd, cfg.num_splits, alpha, p.d_fp32,
                                     static_cast<cudaStream_t>(a->stream));

@@ -206,11 +206,14 @@ int dg_jit_compile(const char* name, const char* entry, const char* source, cons
 
 const char* dg_jit_kernel_path(dg_kernel_t kernel) { return kernel ? kernel->cubin_path.c_str() : ""; }
 
-int dg_jit_launch(dg_kernel_t kernel, uint32_t grid_x, uint32_t block_x, uint32_t cluster_x,
-                  uint32_t smem_bytes, int enable_pdl, void* stream, void** kernel_args) {
-    DG_REQUIRE(kernel != nullptr && grid_x > 0 && block_x > 0 && cluster_x > 0 && grid_x % cluster_x == 0);
-    const Driver& drv = driver();
-    if (!drv.ok) return fail(DG_ERR_CUDA, "CUDA driver unavailable: %s", drv.why.c_str());
+}  // extern "C"
+
+namespace {
+
+// The kernel's function in the current context, loaded on first use, with enough dynamic shared memory allowed
+int loaded_function(dg_kernel_t kernel, uint32_t smem_bytes, CUfunction* out) {
+    const dg::Driver& drv = dg::driver();
+    if (!drv.ok) return dg::fail(DG_ERR_CUDA, "CUDA driver unavailable: %s", drv.why.c_str());
 
     // Make sure the primary context exists and is current on this thread
     CUcontext ctx = nullptr;
@@ -218,33 +221,70 @@ int dg_jit_launch(dg_kernel_t kernel, uint32_t grid_x, uint32_t block_x, uint32_
     if (ctx == nullptr) {
         DG_CUDA_RT(cudaFree(nullptr));
         DG_CUDA_DRV(drv.cuCtxGetCurrent(&ctx));
-        if (ctx == nullptr) return fail(DG_ERR_CUDA, "no current CUDA context");
+        if (ctx == nullptr) return dg::fail(DG_ERR_CUDA, "no current CUDA context");
     }
 
     CUfunction fn = nullptr;
-    {
-        std::lock_guard<std::mutex> lock(kernel->mu);
-        auto it = kernel->loaded.find(ctx);
-        if (it == kernel->loaded.end()) {
-            const std::string image = read_file(kernel->cubin_path);
-            if (image.empty()) return fail(DG_ERR_JIT, "cached kernel %s is empty or unreadable", kernel->cubin_path.c_str());
-            CUmodule mod = nullptr;
-            CUresult r = drv.cuModuleLoadData(&mod, image.data());
-            if (r != CUDA_SUCCESS)
-                return fail(DG_ERR_JIT, "cuModuleLoadData failed for %s: %s", kernel->cubin_path.c_str(), cu_error(r).c_str());
-            r = drv.cuModuleGetFunction(&fn, mod, kernel->entry.c_str());
-            if (r != CUDA_SUCCESS)
-                return fail(DG_ERR_JIT, "entry %s not found in %s: %s", kernel->entry.c_str(), kernel->cubin_path.c_str(), cu_error(r).c_str());
-            kernel->loaded[ctx] = fn;
-        } else {
-            fn = it->second;
-        }
-        uint32_t& configured = kernel->smem_set[ctx];
-        if (smem_bytes > configured) {
-            DG_CUDA_DRV(drv.cuFuncSetAttribute(fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, static_cast<int>(smem_bytes)));
-            configured = smem_bytes;
-        }
+    std::lock_guard<std::mutex> lock(kernel->mu);
+    auto it = kernel->loaded.find(ctx);
+    if (it == kernel->loaded.end()) {
+        const std::string image = read_file(kernel->cubin_path);
+        if (image.empty()) return dg::fail(DG_ERR_JIT, "cached kernel %s is empty or unreadable", kernel->cubin_path.c_str());
+        CUmodule mod = nullptr;
+        CUresult r = drv.cuModuleLoadData(&mod, image.data());
+        if (r != CUDA_SUCCESS)
+            return dg::fail(DG_ERR_JIT, "cuModuleLoadData failed for %s: %s", kernel->cubin_path.c_str(), dg::cu_error(r).c_str());
+        r = drv.cuModuleGetFunction(&fn, mod, kernel->entry.c_str());
+        if (r != CUDA_SUCCESS)
+            return dg::fail(DG_ERR_JIT, "entry %s not found in %s: %s", kernel->entry.c_str(), kernel->cubin_path.c_str(), dg::cu_error(r).c_str());
+        kernel->loaded[ctx] = fn;
+    } else {
+        fn = it->second;
     }
+    uint32_t& configured = kernel->smem_set[ctx];
+    if (smem_bytes > configured) {
+        DG_CUDA_DRV(drv.cuFuncSetAttribute(fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, static_cast<int>(smem_bytes)));
+        configured = smem_bytes;
+    }
+    *out = fn;
+    return DG_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int dg_jit_max_active_clusters(dg_kernel_t kernel, uint32_t block_x, uint32_t cluster_x, uint32_t smem_bytes, int* num_clusters) {
+    DG_REQUIRE(kernel != nullptr && block_x > 0 && cluster_x > 0 && num_clusters != nullptr);
+    CUfunction fn = nullptr;
+    const int rc = loaded_function(kernel, smem_bytes, &fn);
+    if (rc != DG_OK) return rc;
+    const dg::Driver& drv = dg::driver();
+    CUlaunchConfig cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDimX = cluster_x; cfg.gridDimY = 1; cfg.gridDimZ = 1;
+    cfg.blockDimX = block_x; cfg.blockDimY = 1; cfg.blockDimZ = 1;
+    cfg.sharedMemBytes = smem_bytes;
+    CUlaunchAttribute attr;
+    attr.id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
+    attr.value.clusterDim.x = cluster_x;
+    attr.value.clusterDim.y = 1;
+    attr.value.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    DG_CUDA_DRV(drv.cuOccupancyMaxActiveClusters(num_clusters, fn, &cfg));
+    return DG_OK;
+}
+
+int dg_jit_launch(dg_kernel_t kernel, uint32_t grid_x, uint32_t block_x, uint32_t cluster_x,
+                  uint32_t smem_bytes, int enable_pdl, void* stream, void** kernel_args) {
+    DG_REQUIRE(kernel != nullptr && grid_x > 0 && block_x > 0 && cluster_x > 0 && grid_x % cluster_x == 0);
+    CUfunction fn = nullptr;
+    {
+        const int rc = loaded_function(kernel, smem_bytes, &fn);
+        if (rc != DG_OK) return rc;
+    }
+    const dg::Driver& drv = dg::driver();
 
     CUlaunchConfig cfg;
     memset(&cfg, 0, sizeof(cfg));

@@ -47,6 +47,7 @@ const Driver& driver() {
         sym("cuModuleGetFunction", d.cuModuleGetFunction);
         sym("cuFuncSetAttribute", d.cuFuncSetAttribute);
         sym("cuLaunchKernelEx", d.cuLaunchKernelEx);
+        sym("cuOccupancyMaxActiveClusters", d.cuOccupancyMaxActiveClusters);
         sym("cuTensorMapEncodeTiled", d.cuTensorMapEncodeTiled);
         d.ok = d.why.empty();
     });

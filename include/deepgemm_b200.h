@@ -240,6 +240,8 @@ typedef struct dg_gemm_config {
     int32_t waves_x100;
     int32_t num_splits;        /* slices of K per output tile (dense GEMMs with few tiles); 1 = not split */
     int32_t kb_per_split;      /* K-blocks (128 of K) per slice */
+    int32_t split_in_cluster;  /* 1: the slices of a tile are the CTAs of one thread-block cluster, whose first CTA adds the
+                                  others' accumulators from their shared memory (no workspace, no second kernel) */
 } dg_gemm_config_t;
 
 /* get_best_config<SM100ArchSpec> (heuristics/common.hpp:17-56, sm100.hpp:30-301).  Host only. */
@@ -264,6 +266,11 @@ typedef struct dg_kernel* dg_kernel_t;
 DG_API int dg_jit_compile(const char* name, const char* entry, const char* source, const char* extra_flags, dg_kernel_t* kernel);
 /* Path of the cached cubin of a compiled kernel. */
 DG_API const char* dg_jit_kernel_path(dg_kernel_t kernel);
+/* How many clusters of `cluster_x` CTAs of this kernel (block_x threads, smem_bytes of dynamic shared memory) the
+ * current device can hold at once (cuOccupancyMaxActiveClusters).  Loads the kernel image if needed. */
+DG_API int dg_jit_max_active_clusters(dg_kernel_t kernel, uint32_t block_x, uint32_t cluster_x, uint32_t smem_bytes,
+                                      int* num_clusters);
+
 /* cuLaunchKernelEx on `stream`; loads the module into the current context on first use. */
 DG_API int dg_jit_launch(dg_kernel_t kernel, uint32_t grid_x, uint32_t block_x, uint32_t cluster_x,
                   uint32_t smem_bytes, int enable_pdl, void* stream, void** kernel_args);

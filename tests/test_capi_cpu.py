@@ -117,11 +117,30 @@ def test_heuristics_invariants(fp32):
             assert cfg["kb_per_split"] % 4 == 0 and cfg["kb_per_split"] >= 8
             assert (cfg["num_splits"] - 1) * cfg["kb_per_split"] < kb <= cfg["num_splits"] * cfg["kb_per_split"]
             assert cfg["num_tiles"] <= 148
+            if cfg["split_in_cluster"]:
+                # the slices of a tile are one thread-block cluster: portable size, one CTA per slice, and a parked FP32
+                # accumulator fits the pipeline stages it overwrites
+                assert cfg["num_splits"] <= 8 and cfg["num_ctas"] == cfg["num_tiles"] and cfg["cluster_size"] == 1
+                assert cfg["block_n"] * 128 * 4 <= cfg["num_stages"] * (128 + cfg["block_n"]) * 128
         else:
-            assert cfg["kb_per_split"] == kb
+            assert cfg["kb_per_split"] == kb and not cfg["split_in_cluster"]
     for kind, groups in ((1, 32), (2, 16)):
         cfg = dg.get_gemm_config(kind, 256 if kind == 2 else 32 * 1024, 4096, 7168, num_groups=groups, expected_m=64)
         assert cfg["smem_bytes"] <= 232448 and cfg["num_ctas"] <= 148
+
+
+def test_split_reduction_mode_can_be_forced(monkeypatch):
+    """DG_FORCE_SPLIT_CLUSTER: 1 = slices reduced inside a cluster, -1 = through the workspace and a second kernel."""
+    m, n, k = 128, 2112, 7168
+    monkeypatch.setenv("DG_FORCE_SPLIT_CLUSTER", "1")
+    cfg = dg.get_gemm_config(0, m, n, k)
+    assert cfg["num_splits"] > 1 and cfg["split_in_cluster"] == 1 and cfg["num_splits"] <= 8
+    monkeypatch.setenv("DG_FORCE_SPLIT_CLUSTER", "-1")
+    cfg = dg.get_gemm_config(0, m, n, k)
+    assert cfg["num_splits"] > 1 and cfg["split_in_cluster"] == 0
+    monkeypatch.setenv("DG_FORCE_SPLIT_K", "1")
+    cfg = dg.get_gemm_config(0, m, n, k)
+    assert cfg["num_splits"] == 1 and cfg["split_in_cluster"] == 0
 
 
 def _enumerate(kind, bn, rg, m, n, groups, layout, num_ctas):

@@ -166,12 +166,15 @@ def test_mn_major_operands_through_the_nn_tn_tt_entry_points(variant, m, n, k, c
 @pytest.mark.parametrize("m,n,k,splits", [(128, 2112, 7168, None), (64, 4096, 7168, None), (100, 264, 2176, 2), (128, 128, 4096, 4),
                                           (129, 512, 3200, 3)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float])
-def test_split_k_matches_oracle_and_is_reproducible(m, n, k, splits, out_dtype, monkeypatch):
-    """Few-tile shapes are sliced along K; the last slice to arrive sums the FP32 partials in slice order."""
+@pytest.mark.parametrize("mode", ["cluster", "workspace"])
+def test_split_k_matches_oracle_and_is_reproducible(m, n, k, splits, out_dtype, mode, monkeypatch):
+    """Few-tile shapes are sliced along K.  The slices' FP32 partial tiles are added in slice order, either by the first
+    CTA of a thread-block cluster reading the others' shared memory, or by a second kernel reading a workspace."""
     if splits is not None:
         monkeypatch.setenv("DG_FORCE_SPLIT_K", str(splits))
+    monkeypatch.setenv("DG_FORCE_SPLIT_CLUSTER", "1" if mode == "cluster" else "-1")
     cfg = dg.get_gemm_config(0, m, n, k, d_is_fp32=out_dtype == torch.float)
-    assert cfg["num_splits"] >= 2, cfg
+    assert cfg["num_splits"] >= 2 and cfg["split_in_cluster"] == (mode == "cluster"), cfg
     qa, sfa, qb, sfb, _ = quantise_dense(seeded_bf16((m, k), 18), seeded_bf16((n, k), 19))
     ref = oracle.dequant_gemm_nt(qa, sfa, qb, sfb, alpha=0.5)
     outs = []
@@ -190,7 +193,32 @@ def test_split_k_matches_oracle_and_is_reproducible(m, n, k, splits, out_dtype, 
     assert oracle.calc_diff(out, d1) < 1e-6
 
 
-def test_split_k_inside_a_cuda_graph():
+@pytest.mark.parametrize("m,n,k,block_n,splits", [(128, 2112, 7168, 64, 4), (128, 2112, 7168, 128, 7), (64, 4096, 7168, 64, 2),
+                                                  (100, 264, 2176, 16, 2), (129, 512, 3200, 32, 3), (16, 7168, 2048, 128, 2),
+                                                  (256, 576, 7168, 64, 7), (300, 1000, 16384, 112, 5), (128, 1024, 16384, 64, 8)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float])
+def test_cluster_and_workspace_split_k_give_the_same_bits(m, n, k, block_n, splits, out_dtype, monkeypatch):
+    """Both reductions add the same FP32 partial tiles in the same order and scale the sum once."""
+    monkeypatch.setenv("DG_FORCE_SPLIT_K", str(splits))
+    monkeypatch.setenv("DG_FORCE_BLOCK_N", str(block_n))
+    qa, sfa, qb, sfb, _ = quantise_dense(seeded_bf16((m, k), 181), seeded_bf16((n, k), 191))
+    outs = {}
+    for mode in ("1", "-1"):
+        monkeypatch.setenv("DG_FORCE_SPLIT_CLUSTER", mode)
+        cfg = dg.get_gemm_config(0, m, n, k, d_is_fp32=out_dtype == torch.float)
+        assert cfg["num_splits"] == splits and cfg["split_in_cluster"] == (mode == "1"), cfg
+        dg.reset_kernel_status()
+        outs[mode] = _run_dense(qa, sfa, qb, sfb, out_dtype=out_dtype, alpha=1.25).clone()
+        assert dg.kernel_status() == 0
+    view = torch.int32 if out_dtype == torch.float else torch.int16
+    assert torch.equal(outs["1"].view(view), outs["-1"].view(view))
+    ref = oracle.dequant_gemm_nt(qa, sfa, qb, sfb, alpha=1.25)
+    assert oracle.calc_diff(outs["1"].float().cpu().numpy(), ref) < 1e-5
+
+
+@pytest.mark.parametrize("mode", ["1", "-1"])
+def test_split_k_inside_a_cuda_graph(mode, monkeypatch):
+    monkeypatch.setenv("DG_FORCE_SPLIT_CLUSTER", mode)
     m, n, k = 128, 2112, 7168
     qa, sfa, qb, sfb, _ = quantise_dense(seeded_bf16((m, k), 23), seeded_bf16((n, k), 24))
     a = (fp8_cuda(qa), packed_sf_cuda(sfa)); b = (fp8_cuda(qb), packed_sf_cuda(sfb))
