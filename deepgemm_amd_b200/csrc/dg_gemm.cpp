@@ -7,6 +7,7 @@
 #include <algorithm>
 #include <cstring>
 #include <array>
+#include <atomic>
 #include <map>
 #include <mutex>
 #include <sstream>
@@ -215,6 +216,17 @@ GemmLayout fit_stages(GemmLayout lay, int64_t item_kb, int max_stages) {
     return best;
 }
 
+// How many thread-block clusters of S CTAs (one CTA per SM) run at once.  A cluster lives inside one GPC, so the answer
+// is the sum over GPCs of floor(SMs of the GPC / S), which only the driver knows: the table holds what it reported for
+// kernels launched so far (cuOccupancyMaxActiveClusters), and until then the numbers of one B200, scaled by the SM count.
+std::atomic<int> g_cluster_fit[9];
+int clusters_at_once(int size, int num_sms) {
+    const int known = g_cluster_fit[size].load(std::memory_order_relaxed);
+    if (known > 0) return std::min(known, num_sms / size);
+    static const int kOn148[9] = {0, 148, 74, 45, 33, 26, 22, 15, 15};     // what one 148-SM B200 reported
+    return std::max(1, kOn148[size] * num_sms / 148);
+}
+
 int choose_config(const Problem& p, dg_gemm_config_t* cfg, bool allow_cluster_split = true) {
     const int num_sms = dg_get_num_sms();
     const int d_elem = p.d_fp32 ? 4 : (p.d_fp8 ? 1 : 2);
@@ -292,7 +304,7 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg, bool allow_cluster_sp
                 if (in_cluster && (!allow_cluster_split || splits > 8)) continue;
                 const int64_t tiles = mn_tiles * splits;
                 // Clusters are placed inside one GPC each, so fewer of them fit than SMs / size suggests
-                const int64_t waves = in_cluster ? ceil_div<int64_t>(mn_tiles, std::max(1, (units - 8) / splits)) : ceil_div<int64_t>(tiles, units);
+                const int64_t waves = in_cluster ? ceil_div<int64_t>(mn_tiles, clusters_at_once(splits, num_sms)) : ceil_div<int64_t>(tiles, units);
                 // The pipeline: as deep as shared memory allows, but no deeper than the K-blocks of two work items
                 // (k-grouped: the groups share K; an average slice stands for all of them)
                 // (in bytes of K per row)
@@ -317,7 +329,8 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg, bool allow_cluster_sp
                 const double mma = 2.0 * bn * halves * stage_frac;
                 const double stage_bytes = (128.0 * halves + static_cast<double>(bn) / cluster) * bk;
                 const double read_bytes = (128.0 * halves + halves * static_cast<double>(bn) / cluster) * bk;
-                const double smem_feed = std::max((stage_bytes + read_bytes) / 150.0, stage_bytes / 67.0);
+                // (55 B per cycle fitted the cluster-reduced candidates: few-tile shapes whose B is read once, from HBM)
+                const double smem_feed = std::max((stage_bytes + read_bytes) / 150.0, stage_bytes / (in_cluster ? 55.0 : 67.0));
                 const double ring = (1500.0 + mma) / lay.num_stages;
                 const double epilogue = 300.0 + 150.0 * lay.num_groups() + 20.0 * lay.num_stores() + bn * 2.0;
                 // The epilogue of a tile overlaps the next tile's main loop; it is exposed once per CTA
@@ -331,7 +344,7 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg, bool allow_cluster_sp
                 if (splits > 1 && !in_cluster)   // second launch + reading S panels and writing D at a few TB/s (~2000 B per SM clock over the GPU)
                     cost += 6000.0 + static_cast<double>(splits + 1) * p.m * p.n * 4.0 / 2000.0;
                 if (in_cluster)                  // parking a tile, the cluster barrier, bn loads per thread across the cluster
-                    cost += 1200.0 + bn * 12.0;
+                    cost += 600.0 * splits + 20.0 * bn;     // (fitted to a sweep over sizes and widths on six decode shapes)
                 if (best.bn == 0 || cost < best.cost - 1e-9 || (std::abs(cost - best.cost) <= 1e-9 && bn > best.bn)) {
                     best.cost = cost;
                     best.bn = bn; best.bk = bk; best.cluster = cluster; best.halves = halves;
@@ -507,17 +520,22 @@ int get_plan(const Problem& p, Plan* plan) {
     int rc = choose_config(p, &plan->cfg);
     if (rc != DG_OK) return rc;
     if ((rc = get_kernel(p, plan->cfg, &plan->kernel)) != DG_OK) return rc;
-    if (plan->cfg.split_in_cluster) {
-        // A cluster is placed inside one GPC: make sure this device can hold one of this size and shared memory at all
-        // (clusters beyond the ones that fit at once simply run later; nothing waits across clusters)
+    // The slices of a tile as one cluster: ask the driver how many such clusters the device holds at once.  Clusters
+    // beyond that simply run later (nothing waits across clusters), but the choice assumed one wave: when the driver's
+    // number is smaller than the guess, choose again with the number known (each size is asked once per process).
+    for (int attempt = 0; attempt < 8 && plan->cfg.split_in_cluster; ++attempt) {
+        const int size = plan->cfg.num_splits;
+        if (g_cluster_fit[size].load(std::memory_order_relaxed) > 0) break;
         int fit = 0;
-        rc = dg_jit_max_active_clusters(plan->kernel, 128 + plan->cfg.block_m, plan->cfg.num_splits, plan->cfg.smem_bytes, &fit);
+        rc = dg_jit_max_active_clusters(plan->kernel, 128 + plan->cfg.block_m, size, plan->cfg.smem_bytes, &fit);
         if (env_int("PRINT_CONFIGS"))
-            fprintf(stderr, "[dg] clusters of %d CTAs that fit at once: %d (status %d)\n", plan->cfg.num_splits, fit, rc);
-        if (rc != DG_OK || fit < 1) {
-            if ((rc = choose_config(p, &plan->cfg, false)) != DG_OK) return rc;
-            if ((rc = get_kernel(p, plan->cfg, &plan->kernel)) != DG_OK) return rc;
-        }
+            fprintf(stderr, "[dg] clusters of %d CTAs that fit at once: %d (status %d)\n", size, fit, rc);
+        const bool usable = rc == DG_OK && fit >= 1;
+        const int guessed = clusters_at_once(size, dg_get_num_sms());
+        if (usable) g_cluster_fit[size].store(fit, std::memory_order_relaxed);
+        if (usable && fit >= guessed) break;
+        if ((rc = choose_config(p, &plan->cfg, usable)) != DG_OK) return rc;
+        if ((rc = get_kernel(p, plan->cfg, &plan->kernel)) != DG_OK) return rc;
     }
     std::lock_guard<std::mutex> lock(mu);
     if (plans.size() > 4096) plans.clear();

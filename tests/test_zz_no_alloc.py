@@ -56,7 +56,9 @@ def test_noalloc_entry_point_matches_the_allocating_one_on_two_calls_in_a_row(m,
 
 def test_noalloc_entry_point_rejects_a_problem_beyond_its_fixed_scratch(monkeypatch):
     # two K-slices of a 512 x 4224 output need 2 * 512 * 4224 * 4 bytes = 16.5 MiB of panels
+    # (slices reduced through the workspace: slices reduced inside a thread-block cluster need no scratch at all)
     monkeypatch.setenv("DG_FORCE_SPLIT_K", "2")
+    monkeypatch.setenv("DG_FORCE_SPLIT_CLUSTER", "-1")
     monkeypatch.setenv("DG_FORCE_BLOCK_N", "240")
     m, n, k = 512, 4224, 16384
     cfg = dg.get_gemm_config(0, m, n, k)
@@ -73,3 +75,12 @@ def test_noalloc_entry_point_rejects_a_problem_beyond_its_fixed_scratch(monkeypa
     _lib.check(_lib.lib.dg_fp8_fp4_gemm(C.byref(args)))              # the allocating entry point takes it
     torch.cuda.synchronize()
     assert oracle.calc_diff(d.float().cpu().numpy(), oracle.dequant_gemm_nt(qa, sfa, qb, sfb)) < 1e-3
+    # the same slicing reduced inside clusters fits the entry point that allocates nothing, and gives the same bits
+    monkeypatch.setenv("DG_FORCE_SPLIT_CLUSTER", "1")
+    cfg = dg.get_gemm_config(0, m, n, k)
+    assert cfg["num_splits"] == 2 and cfg["split_in_cluster"] == 1
+    d2 = torch.zeros_like(d)
+    args2, keep2 = _args(qa, sfa, qb, sfb, d2)
+    _lib.check(_lib.lib.dg_fp8_fp4_gemm_noalloc(C.byref(args2)))
+    torch.cuda.synchronize()
+    assert torch.equal(d2.view(torch.int16), d.view(torch.int16))
