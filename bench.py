@@ -230,6 +230,7 @@ def main():
     ap.add_argument("--pdl", action="store_true", help="launch the GEMMs with programmatic dependent launch (set_pdl)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--shapes", default="", help="comma-separated NxK subset of the six dense shapes (profiling runs)")
+    ap.add_argument("--m", type=int, default=M_DENSE, help="rows of A (profiling runs of the M = 64 / 128 shapes; the metric is quoted at 4096)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -256,7 +257,7 @@ def main():
     nk_list = DENSE_NK
     if args.shapes:
         nk_list = [tuple(int(v) for v in s.split("x")) for s in args.shapes.split(",")]
-    cases = [make_dense_case(M_DENSE, n, k, 1000 * rank + i, torch, dg) for i, (n, k) in enumerate(nk_list)]
+    cases = [make_dense_case(args.m, n, k, 1000 * rank + i, torch, dg) for i, (n, k) in enumerate(nk_list)]
     step_flops = sum(flops_of(c["m"], c["n"], c["k"]) for c in cases)
 
     def step():
@@ -353,7 +354,8 @@ def main():
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt_max / args.steps * 1e3, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate, bf16 out)",
         "data": "synthetic",
-        "config": {"workload": "dense_fp8_gemm_nt_m4096 (BASELINE config 2, the six (N,K) at M=4096)",
+        "config": {"workload": "dense_fp8_gemm_nt_m4096 (BASELINE config 2, the six (N,K) at M=4096)" if args.m == M_DENSE and not args.shapes
+                               else f"profiling subset: M={args.m}, {len(nk_list)} of the dense shapes",
                    "shapes_mnk": [[c["m"], c["n"], c["k"]] for c in cases],
                    "scales": "UE8M0 packed int32, A 1x128, B 128x128 pre-broadcast",
                    "pdl": args.pdl,

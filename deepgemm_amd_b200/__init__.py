@@ -16,7 +16,7 @@ from .api import (  # noqa: F401
     transform_k_grouped_sf_into_required_layout, fp8_einsum,
     bf16_gemm_nt, bf16_gemm_nn, bf16_gemm_tn, bf16_gemm_tt,
     m_grouped_bf16_gemm_nt_contiguous, m_grouped_bf16_gemm_nn_contiguous, m_grouped_bf16_gemm_nt_masked,
-    k_grouped_bf16_gemm_tn_contiguous, einsum, k_grouped_fp4_gemm_nt_contiguous,
+    k_grouped_bf16_gemm_tn_contiguous, einsum, k_grouped_fp4_gemm_nt_contiguous, k_grouped_fp8_gemm_nt_contiguous,
     transform_sf_into_required_layout, get_tma_aligned_size, get_mn_major_tma_aligned_tensor,
     get_mn_major_tma_aligned_packed_ue8m0_tensor,
     set_mk_alignment_for_contiguous_layout, get_mk_alignment_for_contiguous_layout,

@@ -478,6 +478,15 @@ def transform_k_grouped_sf_into_required_layout(sf, ks_cpu, grouped_layout, reci
     raise RuntimeError("Unknown cases")
 
 
+def k_grouped_fp8_gemm_nt_contiguous(a, b, d, ks_cpu, grouped_layout, c=None, recipe=(1, 1, 128), compiled_dims: str = "mn",
+                                     use_psum_layout: bool = False, epilogue=None) -> None:
+    """The K-major ("NT") k-grouped GEMM over per-group [M, k_g] blocks is the reference's Hopper form; on compute
+    capability 10 it stops with "Unsupported architecture" (csrc/apis/gemm.hpp:373-427), and so does this: Blackwell
+    callers use k_grouped_fp8_gemm_tn_contiguous with [sum_k, M] / [sum_k, N] operands."""
+    raise RuntimeError("Unsupported architecture: k_grouped_fp8_gemm_nt_contiguous is the SM90 form; "
+                       "use k_grouped_fp8_gemm_tn_contiguous ([sum_k, M] and [sum_k, N] operands)")
+
+
 def k_grouped_fp8_gemm_tn_contiguous(a, b, d, ks_cpu, grouped_layout, c=None, recipe=(1, 1, 128), compiled_dims: str = "mn",
                                      use_psum_layout: bool = False, epilogue=None) -> None:
     """D[g] = C[g] + A[slice g]^T @ B[slice g] for every group g, with A [sum_k, M], B [sum_k, N] (e4m3, contiguous) and

@@ -82,3 +82,36 @@ def bench_kineto(fn, kernel_names, num_tests: int = 20, flush_l2_bytes: int = 25
         return total_us / num_tests / 1e6
     total_us = sum(evt.device_time_total if hasattr(evt, "device_time_total") else evt.cuda_time_total for evt in matched)
     return total_us / num_tests / 1e6
+
+
+class empty_suppress:
+    """Context manager that suppresses nothing (deep_gemm/testing/bench.py: the counterpart of suppress_stdout_stderr)."""
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *_):
+        return False
+
+
+class suppress_stdout_stderr:
+    """Redirects the process's file descriptors 1 and 2 to the null device for the duration of the block, so that output
+    written by native code (a profiler's banner) disappears too; restores them afterwards."""
+
+    def __enter__(self):
+        import os
+        import sys
+        sys.stdout.flush(); sys.stderr.flush()
+        self._null = os.open(os.devnull, os.O_WRONLY)
+        self._saved = (os.dup(1), os.dup(2))
+        os.dup2(self._null, 1); os.dup2(self._null, 2)
+        return self
+
+    def __exit__(self, *_):
+        import os
+        import sys
+        sys.stdout.flush(); sys.stderr.flush()
+        os.dup2(self._saved[0], 1); os.dup2(self._saved[1], 2)
+        for fd in (*self._saved, self._null):
+            os.close(fd)
+        return False

@@ -78,6 +78,34 @@ def per_block_cast_to_fp8(x: torch.Tensor, use_ue8m0: bool, gran_k: int = 128):
     return q, sf.reshape(pr // gran_k, pc // gran_k)
 
 
+def per_channel_cast_to_fp8(x: torch.Tensor, use_ue8m0: bool, gran_k: int = 128):
+    """e4m3 with one scale per column and `gran_k` rows (deep_gemm/utils/math.py:52-59): the quantisation of the
+    [sum_k, M] / [sum_k, N] operands of the k-grouped GEMM, whose K runs down the rows.  Returns (q, sf [rows / gran_k, cols])."""
+    assert x.dim() == 2 and x.size(0) % gran_k == 0
+    rows, cols = x.shape
+    slabs = x.reshape(rows // gran_k, gran_k, cols)
+    sf = _scales(slabs.abs().amax(dim=1), 448.0, use_ue8m0)
+    return (slabs * (1.0 / sf.unsqueeze(1))).to(torch.float8_e4m3fn).reshape(rows, cols), sf
+
+
+def per_custom_dims_cast_to_fp8(x: torch.Tensor, dims: Tuple, use_ue8m0: bool):
+    """e4m3 with one scale per index of the dimensions in `dims` (the maximum is taken over all the others;
+    deep_gemm/utils/math.py:75-81).  Returns (q, sf squeezed to the kept dimensions)."""
+    reduced = tuple(i for i in range(x.dim()) if i not in set(dims))
+    sf = _scales(x.abs().amax(dim=reduced, keepdim=True), 448.0, use_ue8m0)
+    return (x * (1.0 / sf)).to(torch.float8_e4m3fn), sf.squeeze()
+
+
+def transpose_packed_fp4(a: torch.Tensor) -> torch.Tensor:
+    """[rows, cols / 2] int8 holding two e2m1 codes per byte (low nibble first) -> the packed [cols, rows / 2] transpose
+    (deep_gemm/utils/math.py:128-141)."""
+    assert a.dtype == torch.int8 and a.dim() == 2 and a.size(0) % 2 == 0
+    rows, half = a.shape
+    nibbles = torch.stack((a & 0x0F, (a >> 4) & 0x0F), dim=-1).reshape(rows, 2 * half)      # one code per element
+    pairs = nibbles.t().reshape(2 * half, rows // 2, 2)
+    return (pairs[..., 0] | (pairs[..., 1] << 4)).to(torch.int8).contiguous()
+
+
 def _e2m1_codes(x: torch.Tensor) -> torch.Tensor:
     """Nearest e2m1 code, ties to the even mantissa, sign in bit 3 (negative zero is not produced)."""
     mag = x.abs()

@@ -1,0 +1,93 @@
+"""Torch-side helpers of the reference's deep_gemm.utils / deep_gemm.testing that the GEMM path's callers use, checked on
+the CPU against the numpy oracle."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from deepgemm_amd_b200 import testing, utils
+
+
+def _bf16(shape, seed, scale=1.0):
+    rng = np.random.default_rng(seed)
+    return oracle.bf16_round((rng.standard_normal(shape) * scale).astype(np.float32))
+
+
+@pytest.mark.parametrize("gran_k", [32, 128])
+@pytest.mark.parametrize("ue8m0", [True, False])
+def test_per_channel_cast_is_the_per_token_cast_of_the_transpose(gran_k, ue8m0):
+    x = _bf16((256, 72), 5, 2.0)
+    x[:, 3] = 0                                         # an all-zero channel: the 1e-4 clamp
+    q, sf = utils.per_channel_cast_to_fp8(torch.from_numpy(x).bfloat16(), ue8m0, gran_k)
+    want_q, want_sf = oracle.per_token_cast_to_fp8(np.ascontiguousarray(x.T), ue8m0, gran_k)
+    assert q.shape == (256, 72) and sf.shape == (256 // gran_k, 72)
+    assert np.array_equal(q.view(torch.uint8).numpy(), want_q.T)
+    assert np.array_equal(sf.numpy(), want_sf.T)
+
+
+def test_per_custom_dims_cast_keeps_one_scale_per_kept_index():
+    x = _bf16((6, 5, 64), 6, 3.0)
+    xt = torch.from_numpy(x).bfloat16()
+    q, sf = utils.per_custom_dims_cast_to_fp8(xt, (0,), True)
+    assert sf.shape == (6,) and q.shape == x.shape
+    for i in range(6):
+        want_q, want_sf = oracle.per_token_cast_to_fp8(x[i].reshape(1, -1), True, gran_k=x[i].size)
+        assert sf[i].item() == want_sf[0, 0]
+        assert np.array_equal(q[i].view(torch.uint8).numpy().reshape(1, -1), want_q)
+    _, sf2 = utils.per_custom_dims_cast_to_fp8(xt, (0, 1), False)
+    assert sf2.shape == (6, 5)
+    assert torch.allclose(sf2, xt.abs().float().amax(dim=2).clamp(1e-4) / 448.0)
+
+
+def test_transpose_packed_fp4_matches_oracle():
+    x = _bf16((36, 64), 7, 2.0)
+    q, _ = oracle.per_token_cast_to_fp4(x, True, 32)
+    got = utils.transpose_packed_fp4(torch.from_numpy(q))
+    assert got.dtype == torch.int8 and got.shape == (64, 18)
+    assert np.array_equal(got.numpy(), oracle.transpose_packed_fp4(q))
+    assert np.array_equal(utils.transpose_packed_fp4(got).numpy(), q)      # an involution
+
+
+def test_test_script_decorators(monkeypatch, capsys):
+    calls = []
+
+    @testing.test_filter(lambda: False)
+    def skipped():
+        calls.append("skipped")
+
+    @testing.test_filter(lambda: True)
+    def kept():
+        calls.append("kept")
+
+    skipped(); kept()
+    assert calls == ["kept"] and "Filtered by" in capsys.readouterr().out
+
+    monkeypatch.setenv("DG_SOME_SETTING", "7")
+
+    @testing.ignore_env("DG_SOME_SETTING", lambda: True)
+    def without():
+        return os.environ.get("DG_SOME_SETTING")
+
+    @testing.ignore_env("DG_SOME_SETTING", lambda: False)
+    def with_it():
+        return os.environ.get("DG_SOME_SETTING")
+
+    assert without() is None and with_it() == "7" and os.environ["DG_SOME_SETTING"] == "7"
+    with testing.empty_suppress():
+        pass
+
+
+def test_suppress_stdout_stderr_restores_the_descriptors(capfd):
+    with testing.suppress_stdout_stderr():
+        os.write(1, b"hidden\n")
+    os.write(1, b"shown\n")
+    out = capfd.readouterr().out
+    assert "shown" in out and "hidden" not in out
+
+
+def test_k_grouped_nt_form_is_rejected_like_the_reference_on_this_architecture():
+    import deepgemm_amd_b200 as dg
+    with pytest.raises(RuntimeError, match="Unsupported architecture"):
+        dg.k_grouped_fp8_gemm_nt_contiguous(None, None, None, [128], None)
