@@ -133,7 +133,9 @@ static_assert(BLOCK_K == 128 || (BLOCK_K == 64 && !kAIsFP4 && !kBIsFP4 && !kAMnM
               "64-element stages are built for K-major FP8 operands and unsliced K");
 static_assert(kCluster == 1 || kCluster == 2, "one CTA or a CTA pair per tile");
 static_assert(kMHalves == 1 || kMHalves == 2, "128 or 256 rows per CTA");
-static_assert(!(kAIsFP4 && kAMnMajor) && !(kBIsFP4 && kBMnMajor), "packed FP4 operands must be K-major");
+static_assert(!(kAIsFP4 && kAMnMajor), "a packed FP4 A must be K-major");
+static_assert(!(kBIsFP4 && kBMnMajor) || (!kAIsFP4 && BLOCK_N % 128 == 0 && kCluster == 1),
+              "an MN-major packed FP4 B: FP8 x FP4 only; a load of the packed 4-bit type starts on a multiple of 128 elements");
 static_assert(!kBMnMajor || (BLOCK_N / kCluster) % 16 == 0, "an MN-major B load must start on a 16-byte boundary");
 static_assert(!kSplitK || (kGemmType == 0 && kDIsFP32 && !kAccumulate && kMHalves == 1), "split-K serves the plain dense GEMM and writes FP32 partials");
 static_assert(kGemmType != kKGrouped || (BLOCK_K == 128 && kCluster == 1 && kGranKA == kGranKB), "k-grouped: one CTA per tile, 128-element stages, one scale granularity");

@@ -131,8 +131,15 @@ int validate(int kind, const dg_gemm_args_t* a, bool need_pointers, Problem* p) 
     // memory by the tensor map), FP4 x FP4 included: the same results as the reference's kind::mxf4 path
     // (csrc/utils/layout.hpp:42-45) at the FP8 rate rather than twice it.
     DG_REQUIRE((a->major_a == DG_MAJOR_K || a->major_a == DG_MAJOR_MN) && (a->major_b == DG_MAJOR_K || a->major_b == DG_MAJOR_MN));
-    if ((a->major_a == DG_MAJOR_MN && a->a_dtype == DG_FP4_E2M1_X2) || (a->major_b == DG_MAJOR_MN && a->b_dtype == DG_FP4_E2M1_X2))
-        return fail(DG_ERR_UNSUPPORTED, "MN-major packed FP4 operands are not built; FP4 must be K-major");
+    // An MN-major packed FP4 B (two columns of N per byte; the weight-gradient and transposed-weight forms of the FP8 x FP4
+    // GEMM, csrc/utils/layout.hpp:66-83) is unpacked by the tensor map along N exactly as a K-major one is along K
+    if (a->major_a == DG_MAJOR_MN && a->a_dtype == DG_FP4_E2M1_X2)
+        return fail(DG_ERR_UNSUPPORTED, "an MN-major packed FP4 A is not built; FP4 on the A side must be K-major");
+    if (a->major_b == DG_MAJOR_MN && a->b_dtype == DG_FP4_E2M1_X2) {
+        if (a->a_dtype == DG_FP4_E2M1_X2) return fail(DG_ERR_UNSUPPORTED, "FP4 x FP4 takes K-major operands");
+        // (the packed 4-bit tensor-map type wants its contiguous extent in multiples of 128 elements, as K is for K-major FP4)
+        if (a->n % 128 != 0) return fail(DG_ERR_INVALID_ARGUMENT, "an MN-major packed FP4 B needs n % 128 == 0 (n = %d)", a->n);
+    }
     p->kind = kind;
     p->a_mn_major = a->major_a == DG_MAJOR_MN;
     p->b_mn_major = a->major_b == DG_MAJOR_MN;
@@ -165,7 +172,7 @@ int validate(int kind, const dg_gemm_args_t* a, bool need_pointers, Problem* p) 
     // Pitch of the non-contiguous dimension: rows of K bytes (K-major) or K-slices of MN bytes (MN-major)
     // (storage elements: bytes for FP8 / packed FP4, bfloat16 elements for BF16)
     const int64_t k_bytes_a = p->a_mn_major ? a->m : (p->a_fp4 ? a->k / 2 : a->k);
-    const int64_t k_bytes_b = p->b_mn_major ? a->n : (p->b_fp4 ? a->k / 2 : a->k);
+    const int64_t k_bytes_b = p->b_mn_major ? (p->b_fp4 ? a->n / 2 : a->n) : (p->b_fp4 ? a->k / 2 : a->k);
     DG_REQUIRE(a->lda >= k_bytes_a && a->lda % (p->a_fp4 ? 32 : (ab_bf16 ? 8 : 16)) == 0);   // TMA: strides are multiples of 16 bytes
     DG_REQUIRE(a->ldb >= k_bytes_b && a->ldb % (p->b_fp4 ? 32 : (ab_bf16 ? 8 : 16)) == 0);
     const int d_elem = p->d_fp32 ? 4 : (p->d_fp8 ? 1 : 2);
@@ -182,7 +189,6 @@ int validate(int kind, const dg_gemm_args_t* a, bool need_pointers, Problem* p) 
     }
     if (kind == DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM) {
         DG_REQUIRE(state().mk_alignment % 128 == 0);
-        DG_REQUIRE(a->major_b == DG_MAJOR_K);
         DG_REQUIRE(a->expected_m >= 0);
     }
     return DG_OK;
@@ -251,7 +257,7 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg, bool allow_cluster_sp
         if (forced_cluster ? cluster != forced_cluster : !cluster_allowed(p, cluster)) continue;
         // A CTA pair multiplies all its rows with one B: in the contiguous layout every expert segment must then be a
         // whole number of pair tiles
-        if (cluster == 2 && (num_sms % 2 != 0 || p.kind == DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM || p.kind == DG_GEMM_K_GROUPED_CONTIGUOUS ||
+        if (cluster == 2 && (num_sms % 2 != 0 || (p.b_fp4 && p.b_mn_major) || p.kind == DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM || p.kind == DG_GEMM_K_GROUPED_CONTIGUOUS ||
                              p.kind == DG_GEMM_BATCHED ||
                              (p.kind == DG_GEMM_M_GROUPED_CONTIGUOUS && state().mk_alignment % (256 * halves) != 0))) continue;
         // 256 rows per CTA: two 128-row MMAs per K-block on one B stage; K not sliced
@@ -284,7 +290,9 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg, bool allow_cluster_sp
                                forced_splits != 1 && k_blocks >= 16;
         for (int bn = 16; bn <= (p.ab_bf16 ? 256 : 240); bn += 16) {
             if (forced_bn && bn != forced_bn) continue;
-            if (p.b_mn_major && (bn / cluster) % 16 != 0) continue;       // an MN-major B load starts on a 16-byte boundary
+            // An MN-major B load starts on a 16-byte boundary of the row; for the packed 4-bit tensor-map type the
+            // innermost coordinate must be a multiple of 128 elements (K-major loads start on whole K-blocks anyway)
+            if (p.b_mn_major && (bn / cluster) % (p.b_fp4 ? 128 : 16) != 0) continue;
             if (p.d_fp8 && bn % 32 != 0) continue;                        // whole 32-column scale groups per tile
             const int64_t mn_tiles = m_blocks * ceil_div(p.n, bn);
             const int max_splits = can_split ? static_cast<int>(std::min<int64_t>(units / std::max<int64_t>(mn_tiles, 1), k_blocks / 8)) : 1;

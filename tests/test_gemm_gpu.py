@@ -546,6 +546,78 @@ def test_m_grouped_contiguous_nn_takes_mn_major_weights():
     assert oracle.calc_diff(out[valid], ref[valid]) < 1e-5, diff_report(out, ref)
 
 
+@pytest.mark.parametrize("b_fp4", [False, True])
+@pytest.mark.parametrize("zero_padding", [False, True])
+def test_m_grouped_contiguous_prefix_sum_layout_with_mn_major_weights(b_fp4, zero_padding):
+    """tests/generators.py:194-210: the prefix-sum layout is enumerated with K-major and MN-major B alike."""
+    g, n, k = 4, 640, 768
+    actual_ms = [130, 0, 256, 77]
+    m, starts, ends = oracle.make_psum_layout(actual_ms, 128)
+    in_group = np.zeros(m, dtype=bool)
+    for s0, e in zip(starts, ends):
+        in_group[s0:int(e)] = True
+    a = seeded_bf16((m, k), 27)
+    a[~in_group] = 0
+    qa, sfa, qb, sfb = _grouped_inputs(g, n, k, a, b_fp4=b_fp4)
+    gk = 32 if b_fp4 else 128
+    ref = oracle.m_grouped_psum_ref(qa, sfa, qb, sfb, ends, 128, gran_k_b=gk, b_is_fp4=b_fp4) if b_fp4 else \
+        oracle.m_grouped_psum_ref(qa, sfa, qb, sfb, ends, 128)
+    if b_fp4:
+        b_kn = torch.stack([fp4_cuda(oracle.transpose_packed_fp4(qb[i])) for i in range(g)])        # [G, K, N / 2]
+    else:
+        b_kn = fp8_cuda(np.ascontiguousarray(qb.transpose(0, 2, 1)))                                # [G, K, N]
+    sfb_kn = torch.from_numpy(sfb).cuda().transpose(1, 2).contiguous()                              # FP32 [G, K / gk, N]
+    for alias in (True, False):
+        d = torch.full((m, n), SENTINEL, dtype=torch.bfloat16, device="cuda")
+        dg.reset_kernel_status()
+        if alias:
+            dg.m_grouped_fp8_fp4_gemm_nn_contiguous((fp8_cuda(qa), torch.from_numpy(sfa).cuda()), (b_kn, sfb_kn), d, torch.from_numpy(ends).cuda(),
+                                                    recipe_a=(1, 128), recipe_b=(1, gk), use_psum_layout=True, ensure_zero_padding=zero_padding)
+        else:                                                   # the same storage seen as [G, N, K] with N contiguous
+            dg.m_grouped_fp8_fp4_gemm_nt_contiguous((fp8_cuda(qa), torch.from_numpy(sfa).cuda()), (b_kn.mT, sfb_kn.mT), d, torch.from_numpy(ends).cuda(),
+                                                    recipe_a=(1, 128), recipe_b=(1, gk), use_psum_layout=True, ensure_zero_padding=zero_padding)
+        assert dg.kernel_status() == 0
+        out = d.float().cpu().numpy()
+        assert oracle.calc_diff(out[in_group], ref[in_group]) < 1e-5, diff_report(out[in_group], ref[in_group])
+        assert (out[~in_group] == (0 if zero_padding else SENTINEL)).all()
+
+
+@pytest.mark.parametrize("variant", ["nn", "tn", "nt_strided"])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 512), (208, 768, 1152), (4096, 2176, 1024), (304, 4096, 7168)])
+def test_fp8_x_fp4_with_an_mn_major_packed_fp4_b(variant, m, n, k):
+    """B stored [K, N / 2], two columns of N per byte (tests/generators.py:318-326: transpose_packed_fp4(q).T), as the
+    backward GEMMs of an FP8 x FP4 layer pass it; bit-identical to the K-major call."""
+    a, b = seeded_bf16((m, k), 151), seeded_bf16((n, k), 152)
+    qa, sfa = oracle.per_token_cast_to_fp8(a, True, 128)
+    qb, sfb = oracle.per_token_cast_to_fp4(b, True, 32)
+    ref = oracle.dequant_gemm_nt(qa, sfa, qb, sfb, 128, 32, False, True)
+    b_kn = fp4_cuda(oracle.transpose_packed_fp4(qb))                 # [K, N / 2]
+    sfb_t = torch.from_numpy(sfb).cuda()                             # FP32 [N, K / 32]
+    d = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    dg.reset_kernel_status()
+    if variant == "nn":
+        dg.fp8_fp4_gemm_nn((fp8_cuda(qa), torch.from_numpy(sfa).cuda()), (b_kn, sfb_t.T), d, recipe_a=(1, 128), recipe_b=(1, 32))
+    elif variant == "tn":
+        dg.fp8_fp4_gemm_tn((fp8_cuda(qa.T.copy()), torch.from_numpy(sfa).cuda().T), (b_kn, sfb_t.T), d, recipe_a=(1, 128), recipe_b=(1, 32))
+    else:
+        dg.fp8_fp4_gemm_nt((fp8_cuda(qa), torch.from_numpy(sfa).cuda()), (b_kn.T, sfb_t), d, recipe_a=(1, 128), recipe_b=(1, 32))
+    assert dg.kernel_status() == 0
+    out = d.float().cpu().numpy()
+    assert oracle.calc_diff(out, ref) < 1e-5, diff_report(out, ref)
+    d_nt = torch.empty_like(d)
+    dg.fp8_fp4_gemm_nt((fp8_cuda(qa), torch.from_numpy(sfa).cuda()), (fp4_cuda(qb), sfb_t), d_nt, recipe_a=(1, 128), recipe_b=(1, 32))
+    assert torch.equal(d.view(torch.int16), d_nt.view(torch.int16))
+
+
+def test_mn_major_packed_fp4_b_needs_whole_128_column_blocks():
+    m, n, k = 128, 704, 256
+    qa = torch.zeros((m, k), dtype=torch.float8_e4m3fn, device="cuda"); sfa = torch.ones((m, k // 128), device="cuda")
+    b_kn = torch.zeros((k, n // 2), dtype=torch.int8, device="cuda"); sfb = torch.ones((n, k // 32), device="cuda")
+    d = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError, match="n % 128 == 0"):
+        dg.fp8_fp4_gemm_nn((qa, sfa), (b_kn, sfb.T), d, recipe_a=(1, 128), recipe_b=(1, 32))
+
+
 # ---------------------------------------------------------------------------------------------------
 # k-grouped contiguous (weight gradients of a mixture of experts)
 # ---------------------------------------------------------------------------------------------------
