@@ -92,7 +92,15 @@ def test_argument_validation_fails_like_the_reference_asserts(kw, kind, pattern)
 def test_unsupported_combinations_say_so():
     cfg = GemmConfig()
     rc = lib.dg_get_gemm_config(0, C.byref(_args(a_dtype=_lib.DG_FP4_E2M1_X2, major_a=_lib.DG_MAJOR_MN, lda=256)), C.byref(cfg))
-    assert rc == 4 and "FP4 must be K-major" in _lib.last_error()
+    assert rc == 4 and "must be K-major" in _lib.last_error()
+    # an MN-major packed FP4 B is built for FP8 x FP4 with whole 128-column blocks of N; FP4 x FP4 is K-major only
+    rc = lib.dg_get_gemm_config(0, C.byref(_args(b_dtype=_lib.DG_FP4_E2M1_X2, major_b=_lib.DG_MAJOR_MN, n=704, ldb=352, gran_k_b=32)), C.byref(cfg))
+    assert rc == 1 and "n % 128 == 0" in _lib.last_error()
+    rc = lib.dg_get_gemm_config(0, C.byref(_args(b_dtype=_lib.DG_FP4_E2M1_X2, major_b=_lib.DG_MAJOR_MN, n=768, ldb=384, gran_k_b=32)), C.byref(cfg))
+    assert rc == 0 and cfg.block_n == 128, _lib.last_error()
+    rc = lib.dg_get_gemm_config(0, C.byref(_args(a_dtype=_lib.DG_FP4_E2M1_X2, b_dtype=_lib.DG_FP4_E2M1_X2, major_b=_lib.DG_MAJOR_MN, n=768,
+                                                 lda=128, ldb=384, gran_k_a=32, gran_k_b=32)), C.byref(cfg))
+    assert rc == 4 and "K-major" in _lib.last_error()
 
 
 SHAPES = [(m, n, k) for m in (1, 64, 128, 129, 4096) for (n, k) in
