@@ -33,6 +33,7 @@ class GemmArgs(C.Structure):
         ("sfd", C.c_void_p), ("sfd_pitch", C.c_int64),
         ("batch_stride_a", C.c_int64), ("batch_stride_b", C.c_int64), ("batch_stride_d", C.c_int64),
         ("stochastic_rounding", C.c_int32),
+        ("reduce_batches", C.c_int32),
     ]
 
 

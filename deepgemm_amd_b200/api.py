@@ -620,10 +620,40 @@ def fp8_einsum(expr: str, a, b, d, c=None, recipe=(1, 128, 128), epilogue=None) 
         raise RuntimeError(f"Unsupported einsum expression: {expr}")
 
 
+def _bmk_bnk_mn(a, b, d, c, epilogue) -> None:
+    """D[m,n] (+)= sum over the batch s of A[s] @ B[s]^T (csrc/apis/einsum.hpp:22-58): one dense BF16 GEMM whose K loop
+    walks (batch, K-block) pairs.  An FP32 D accumulates (c must be d itself); a BF16 D is written from the FP32 sums."""
+    _require(epilogue is None, "epilogue_class == nullptr and \"Custom epilogues are unsupported for this expression\"")
+    _require(a.dim() == 3 and b.dim() == 3 and d.dim() == 2, "t.dim() == N")
+    _require_bf16(a, b)
+    _require(a.is_contiguous() and b.is_contiguous() and d.is_contiguous(), "a.is_contiguous()")
+    (s, m, k), (s_, n, k_) = a.shape, b.shape
+    _require(s == s_ and k == k_ and d.size(0) == m and d.size(1) == n, "s == s_ and k == k_")
+    _require(k % 64 == 0, "k % block_k == 0")
+    if d.dtype == torch.float:
+        _require(c is not None and c.data_ptr() == d.data_ptr() and c.shape == d.shape and c.stride() == d.stride(),
+                 "c->data_ptr() == d.data_ptr() and c->sizes() == d.sizes() and c->strides() == d.strides()")
+    else:
+        _require(d.dtype == torch.bfloat16, "d.scalar_type() == torch::kBFloat16")
+        _require(c is None, "not c.has_value()")
+    if m == 0 or n == 0 or s == 0 or k == 0:
+        if d.dtype == torch.bfloat16:
+            d.zero_()
+        return
+    out = torch.empty_like(d) if d.dtype == torch.float else d          # the sums, before they are added to an FP32 D
+    args = _bf16_args(a[0], b[0], out, m, n, k, 1, _lib.DG_MAJOR_K, _lib.DG_MAJOR_K)
+    args.reduce_batches, args.batch_stride_a, args.batch_stride_b = s, a.stride(0), b.stride(0)
+    check(lib.dg_fp8_fp4_gemm(C.byref(args)))
+    if out is not d:
+        d.add_(out)
+
+
 def einsum(expr: str, a, b, d, c=None, epilogue=None) -> None:
-    """BF16 contractions of csrc/apis/einsum.hpp:63-181 that are batched GEMMs over permuted views: 'bhr,hdr->bhd',
-    'bhd,hdr->bhr' and 'bhd,bhr->hdr' ('bmk,bnk->mn', a reduction over the batch as well, is not built)."""
-    if expr == "bhr,hdr->bhd":
+    """BF16 contractions of csrc/apis/einsum.hpp:63-181: 'bmk,bnk->mn' (a GEMM reduced over the batch as well) and the
+    three that are batched GEMMs over permuted views, 'bhr,hdr->bhd', 'bhd,hdr->bhr' and 'bhd,bhr->hdr'."""
+    if expr == "bmk,bnk->mn":
+        _bmk_bnk_mn(a, b, d, c, epilogue)
+    elif expr == "bhr,hdr->bhd":
         _fp8_bmm(a.permute(1, 0, 2), None, b, None, d.permute(1, 0, 2), c.permute(1, 0, 2) if c is not None else None, None, epilogue)
     elif expr == "bhd,hdr->bhr":
         _fp8_bmm(a.permute(1, 0, 2), None, b.permute(0, 2, 1), None, d.permute(1, 0, 2), c.permute(1, 0, 2) if c is not None else None,

@@ -111,6 +111,12 @@ constexpr bool     kStochastic = DG_STOCHASTIC_ROUNDING != 0;      // BF16 outpu
 constexpr bool     kAccumulate = DG_ACCUMULATE != 0;
 constexpr uint32_t kRasterGroup = DG_RASTER_GROUP;
 constexpr bool     kSplitK     = DG_SPLIT_K != 0;
+#ifndef DG_BATCH_REDUCE
+#define DG_BATCH_REDUCE 0
+#endif
+// Dense GEMM that also sums over batches: K-block t of the work item is K-block (t mod kb_per_batch) of batch
+// (t / kb_per_batch), the batch being the third coordinate of A's and B's tensor maps (D has none)
+constexpr bool kBatchReduce = DG_BATCH_REDUCE != 0;
 constexpr uint32_t kSplitCluster = DG_SPLIT_CLUSTER;   // CTAs of a cluster sharing one output tile along K (1 = off)
 
 constexpr uint32_t kMHalves    = DG_M_HALVES;      // 128-row MMAs per CTA and K-block (1 or 2)
@@ -156,6 +162,8 @@ static_assert(!kStochastic || (!kDIsFP32 && !kDIsFP8 && !kAccumulate), "stochast
 static_assert(!kDIsFP8 || ((kGemmType == kDense || kGemmType == kBatched) && !kAccumulate && !kSplitK && BLOCK_N % 32 == 0),
               "the quantising epilogue serves the dense and batched GEMMs with tiles of whole 32-column scale groups");
 static_assert(kGemmType != kBatched || (kCluster == 1 && !kSplitK), "batched: one CTA per tile");
+static_assert(!kBatchReduce || (kGemmType == kDense && kABIsBF16 && !kAMnMajor && !kBMnMajor && kCluster == 1),
+              "the batch-reduced GEMM takes K-major BF16 operands, one CTA per tile");
 static_assert(kSplitCluster >= 1 && kSplitCluster <= 8, "portable cluster sizes");
 static_assert(kSplitCluster == 1 || (kGemmType == kDense && !kSplitK && kCluster == 1 && kMHalves == 1 && !kAccumulate && !kDIsFP8 && !kStochastic),
               "cluster-reduced K slicing serves the plain dense GEMM");
@@ -215,6 +223,7 @@ struct GemmParams {
     uint32_t group_alignment;    // prefix-sum layout: every group starts on a multiple of this many rows
     uint32_t* sfd;               // quantising epilogue: packed UE8M0 scales of D, word (row, column / 128) at sfd[(column / 128) * sfd_pitch + row]
     uint32_t sfd_pitch;
+    uint32_t kb_per_batch;       // batch-reduced GEMM: K-blocks in one batch
 };
 
 // Wait-time accounting for tuning: with DG_PROFILE defined every role adds the cycles it spent inside each
@@ -438,6 +447,15 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                             else tma_load_2d_2cta(dst, map, load_bar, static_cast<int32_t>(x), static_cast<int32_t>(y));
                         };
                         // K-major: x = K, y = row.  MN-major: x = row (column of the stored matrix), y = K (+ the group's K offset)
+                        if constexpr (kBatchReduce) {
+                            const uint32_t batch = kb / p.kb_per_batch, kx = (kb - batch * p.kb_per_batch) * BLOCK_K_ELEMS;
+                            tma_load_3d(smem_base + kSmemA + stage * kABytes, &tm_a, load_bar, static_cast<int32_t>(kx),
+                                        static_cast<int32_t>(a_row), static_cast<int32_t>(batch));
+                            tma_load_3d(smem_base + kSmemB + stage * kBBytes, &tm_b, load_bar, static_cast<int32_t>(kx),
+                                        static_cast<int32_t>(b_row), static_cast<int32_t>(batch));
+                            advance_sf(kb);
+                            continue;
+                        }
                         if constexpr (!kAMnMajor) {
                             load(smem_base + kSmemA + stage * kABytes, &tm_a, k_base + kb * BLOCK_K_ELEMS, a_row);      // one box of CTA_M rows
                         } else {

@@ -34,6 +34,7 @@ struct GemmParams {
     uint32_t group_alignment;
     uint32_t* sfd;
     uint32_t sfd_pitch;
+    uint32_t kb_per_batch;
 };
 
 // Split-K scratch: num_splits stacked FP32 [rows x N] panels.  One buffer per device, shared by every stream (a
@@ -74,6 +75,7 @@ struct Problem {
     bool write_padding;      // prefix-sum layout: also write the padding rows of D up to the next aligned row
     bool k_psum;             // k-grouped: grouped_layout holds prefix sums
     bool stochastic;         // BF16 output rounded stochastically
+    int reduce_batches;      // dense BF16 GEMM summed over this many batches as well (k is then batches x K of one batch); 0 = no
 };
 
 int validate(int kind, const dg_gemm_args_t* a, bool need_pointers, Problem* p) {
@@ -140,10 +142,19 @@ int validate(int kind, const dg_gemm_args_t* a, bool need_pointers, Problem* p) 
         // (the packed 4-bit tensor-map type wants its contiguous extent in multiples of 128 elements, as K is for K-major FP4)
         if (a->n % 128 != 0) return fail(DG_ERR_INVALID_ARGUMENT, "an MN-major packed FP4 B needs n % 128 == 0 (n = %d)", a->n);
     }
+    p->reduce_batches = 0;
+    if (a->reduce_batches > 1) {
+        // einsum.hpp:41-47, sm100_bmk_bnk_mn.hpp:23: contiguous K-major BF16 batches, K a whole number of 64-element blocks
+        DG_REQUIRE(kind == DG_GEMM_DENSE && ab_bf16 && a->major_a == DG_MAJOR_K && a->major_b == DG_MAJOR_K);
+        DG_REQUIRE(a->k % 64 == 0 && !a->accumulate && !a->has_alpha && a->d_dtype != DG_FP8_E4M3 && !a->stochastic_rounding);
+        DG_REQUIRE((a->batch_stride_a * 2) % 16 == 0 && (a->batch_stride_b * 2) % 16 == 0);
+        DG_REQUIRE(static_cast<int64_t>(a->k) * a->reduce_batches < (int64_t{1} << 31));
+        p->reduce_batches = a->reduce_batches;
+    }
     p->kind = kind;
     p->a_mn_major = a->major_a == DG_MAJOR_MN;
     p->b_mn_major = a->major_b == DG_MAJOR_MN;
-    p->m = a->m; p->n = a->n; p->k = a->k; p->groups = a->num_groups;
+    p->m = a->m; p->n = a->n; p->k = a->k * std::max(1, p->reduce_batches); p->groups = a->num_groups;
     p->a_fp4 = a->a_dtype == DG_FP4_E2M1_X2;
     p->b_fp4 = a->b_dtype == DG_FP4_E2M1_X2;
     p->ab_bf16 = ab_bf16;
@@ -428,6 +439,7 @@ std::string generate_source(const Problem& p, const dg_gemm_config_t& cfg) {
       << "#define DG_ACCUMULATE " << (p.accumulate ? 1 : 0) << "\n"
       << "#define DG_RASTER_GROUP " << cfg.raster_group << "\n"
       << "#define DG_SPLIT_K " << (cfg.num_splits > 1 && !cfg.split_in_cluster ? 1 : 0) << "\n"
+      << "#define DG_BATCH_REDUCE " << (p.reduce_batches > 1 ? 1 : 0) << "\n"
       << "#define DG_SPLIT_CLUSTER " << (cfg.split_in_cluster ? cfg.num_splits : 1) << "\n"
       << "#define DG_WRITE_PADDING " << (p.write_padding ? 1 : 0) << "\n"
       << "#define DG_K_PSUM " << (p.k_psum ? 1 : 0) << "\n"
@@ -512,7 +524,7 @@ int get_plan(const Problem& p, Plan* plan) {
     for (int v : {p.kind, p.m, p.n, p.k, p.groups, static_cast<int>(p.a_fp4), static_cast<int>(p.b_fp4), static_cast<int>(p.ab_bf16),
                   static_cast<int>(p.d_fp32), static_cast<int>(p.d_fp8), static_cast<int>(p.accumulate), static_cast<int>(p.a_mn_major),
                   static_cast<int>(p.b_mn_major), p.gran_k_a, p.gran_k_b, p.expected_m, static_cast<int>(p.write_padding),
-                  static_cast<int>(p.k_psum), static_cast<int>(p.stochastic), dg_get_num_sms(), state().mk_alignment})
+                  static_cast<int>(p.k_psum), static_cast<int>(p.stochastic), p.reduce_batches > 1 ? 1 : 0, dg_get_num_sms(), state().mk_alignment})
         key[i++] = v;
     for (const char* name : kEnvNames) key[i++] = env_int(name);
     static std::mutex mu;
@@ -605,9 +617,12 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
 
     // Batched: every map gets the batch as a third dimension (strides in bytes)
     const bool batched = kind == DG_GEMM_BATCHED;
+    const bool reduce = p.reduce_batches > 1;               // A and B get the batch as a third coordinate, D does not
     const uint64_t nb = batched ? p.groups : 0;
+    const uint64_t nb_ab = reduce ? p.reduce_batches : nb;
+    const uint64_t k_inner = reduce ? p.k / p.reduce_batches : p.k;
     const uint64_t d_elem_bytes = p.d_fp32 ? 4 : (p.d_fp8 ? 1 : 2);
-    const uint64_t bs_a = batched ? a->batch_stride_a : 0, bs_b = batched ? a->batch_stride_b : 0;
+    const uint64_t bs_a = batched || reduce ? a->batch_stride_a : 0, bs_b = batched || reduce ? a->batch_stride_b : 0;
     const uint64_t bs_d = batched ? a->batch_stride_d * d_elem_bytes : 0;
     const uint64_t bs_sfa = batched ? a->sfa_pitch * 4 * ceil_div(p.k, p.gran_k_a * 4) : 0;
     const uint64_t bs_sfb = batched ? a->sfb_pitch * 4 * ceil_div(p.k, p.gran_k_b * 4) : 0;
@@ -623,15 +638,15 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
     const CUtensorMapDataType b_type = p.ab_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 :
                                        p.b_fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8;
     if (!p.a_mn_major) {
-        if ((rc = encode_2d(&tm_a, a_type, a->a, p.k, a_rows, a->lda * ab_elem, box_k, cfg.block_m, k_major_swizzle,
-                            nb, bs_a * ab_elem)) != DG_OK) return rc;
+        if ((rc = encode_2d(&tm_a, a_type, a->a, k_inner, a_rows, a->lda * ab_elem, box_k, cfg.block_m, k_major_swizzle,
+                            nb_ab, bs_a * ab_elem)) != DG_OK) return rc;
     } else {
         if ((rc = encode_2d(&tm_a, a_type, a->a, p.m, p.k, a->lda * ab_elem, atom_mn, box_k, CU_TENSOR_MAP_SWIZZLE_128B,
                             nb, bs_a * ab_elem)) != DG_OK) return rc;
     }
     if (!p.b_mn_major) {
-        if ((rc = encode_2d(&tm_b, b_type, a->b, p.k, b_rows, a->ldb * ab_elem, box_k, cfg.block_n / cfg.cluster_size, k_major_swizzle,
-                            nb, bs_b * ab_elem)) != DG_OK) return rc;
+        if ((rc = encode_2d(&tm_b, b_type, a->b, k_inner, b_rows, a->ldb * ab_elem, box_k, cfg.block_n / cfg.cluster_size, k_major_swizzle,
+                            nb_ab, bs_b * ab_elem)) != DG_OK) return rc;
     } else {
         if ((rc = encode_2d(&tm_b, b_type, a->b, p.n, b_k_rows, a->ldb * ab_elem, atom_mn, box_k, CU_TENSOR_MAP_SWIZZLE_128B,
                             nb, bs_b * ab_elem)) != DG_OK) return rc;
@@ -676,6 +691,7 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
     params.group_alignment = static_cast<uint32_t>(state().mk_alignment);
     params.sfd = static_cast<uint32_t*>(a->sfd);
     params.sfd_pitch = static_cast<uint32_t>(a->sfd_pitch);
+    params.kb_per_batch = static_cast<uint32_t>(k_inner * ab_elem / cfg.block_k);
     void* kargs[7] = {&tm_a, &tm_b, &tm_sfa, &tm_sfb, &tm_d, &tm_d_full, &params};
     if (env_int("PROFILE")) {
         // synchronous, printing path for tuning only

@@ -182,6 +182,11 @@ typedef struct dg_gemm_args {
      * 4q .. 4q+3 and of q (tests/utils.py:53-79 states it), so the result is reproducible.  BF16 output only, not
      * combined with accumulate or alpha; K is never sliced. */
     int32_t stochastic_rounding;
+    /* einsum 'bmk,bnk->mn' (csrc/apis/einsum.hpp:22-58, csrc/jit_kernels/impls/sm100_bmk_bnk_mn.hpp): with reduce_batches =
+     * S > 1 the dense BF16 GEMM sums over S batches as well, D[m,n] = sum over s of A[s] @ B[s]^T with A [S, M, K] and
+     * B [S, N, K] (K-major, batches batch_stride_a / batch_stride_b elements apart, k % 64 == 0): the K loop walks
+     * (batch, K-block) pairs, so the reduction is one GEMM with K' = S * K.  dg_fp8_fp4_gemm only; D BF16 or FP32. */
+    int32_t reduce_batches;
 } dg_gemm_args_t;
 
 /* fp8_fp4_gemm_nt and, through major_a / major_b, nn / tn / tt (gemm.hpp:78-179). */

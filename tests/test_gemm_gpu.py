@@ -935,6 +935,39 @@ def test_bf16_einsum_contractions_match_fp32():
     assert oracle.calc_diff(z3.cpu().numpy(), ref3) < 1e-9
 
 
+@pytest.mark.parametrize("s,m,n,k", [(5, 128, 384, 128), (129, 256, 256, 256), (257, 384, 128, 384), (33, 100, 200, 64), (1, 128, 128, 64)])
+@pytest.mark.parametrize("dtype", [torch.float, torch.bfloat16])
+def test_bf16_einsum_reduced_over_the_batch(s, m, n, k, dtype):
+    """tests/test_einsum.py:21-41: 'bmk,bnk->mn' sums over the batch too; an FP32 D accumulates, a BF16 D is written."""
+    a, b = seeded_bf16((s, m, k), 161), seeded_bf16((s, n, k), 162)
+    d0 = seeded_bf16((m, n), 163, 10.0)
+    d = torch.from_numpy(d0).cuda().to(dtype)
+    dg.reset_kernel_status()
+    dg.einsum("bmk,bnk->mn", _bf16_cuda(a), _bf16_cuda(b), d, c=d if dtype == torch.float else None)
+    assert dg.kernel_status() == 0
+    sums = np.einsum("smk,snk->mn", a.astype(np.float64), b.astype(np.float64))
+    if dtype == torch.float:
+        assert oracle.calc_diff(d.cpu().numpy(), d0 + sums) < 1e-9
+    else:
+        assert oracle.calc_diff(d.float().cpu().numpy(), oracle.bf16_round(sums.astype(np.float32))) < 1e-5
+    # reproducible: the slices of the combined (batch, K) axis are added in a fixed order
+    d2 = torch.from_numpy(d0).cuda().to(dtype)
+    dg.einsum("bmk,bnk->mn", _bf16_cuda(a), _bf16_cuda(b), d2, c=d2 if dtype == torch.float else None)
+    assert torch.equal(d.view(torch.int32 if dtype == torch.float else torch.int16), d2.view(torch.int32 if dtype == torch.float else torch.int16))
+
+
+def test_bf16_einsum_reduced_over_the_batch_checks_its_arguments():
+    a = torch.zeros((4, 128, 96), dtype=torch.bfloat16, device="cuda"); b = torch.zeros((4, 64, 96), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError, match="k % block_k == 0"):
+        dg.einsum("bmk,bnk->mn", a, b, torch.zeros((128, 64), dtype=torch.bfloat16, device="cuda"))
+    a = torch.zeros((4, 128, 128), dtype=torch.bfloat16, device="cuda"); b = torch.zeros((4, 64, 128), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError, match="c->data_ptr"):          # an FP32 D only accumulates
+        dg.einsum("bmk,bnk->mn", a, b, torch.zeros((128, 64), dtype=torch.float, device="cuda"))
+    with pytest.raises(RuntimeError, match="not c.has_value"):
+        d = torch.zeros((128, 64), dtype=torch.bfloat16, device="cuda")
+        dg.einsum("bmk,bnk->mn", a, b, d, c=d)
+
+
 def test_k_grouped_fp4_gemm_matches_oracle():
     alignment = 256
     dg.set_mk_alignment_for_contiguous_layout(alignment)
