@@ -170,7 +170,9 @@ int validate(int kind, const dg_gemm_args_t* a, bool need_pointers, Problem* p) 
     if (p->stochastic) DG_REQUIRE(a->d_dtype == DG_BF16 && !a->accumulate && !a->has_alpha);
     if (a->m == 0 || a->n == 0 || a->k == 0) return DG_OK;                    // handled by the caller (gemm.hpp:17-53)
 
-    if (p->a_fp4 || p->b_fp4) DG_REQUIRE(a->k % 128 == 0);                   // runtime_utils.hpp:133-135
+    // runtime_utils.hpp:133-135: the contiguous extent of a packed FP4 operand is whole 128-element blocks (K when it is
+    // K-major; N for the MN-major B, checked above)
+    if ((p->a_fp4 && !p->a_mn_major) || (p->b_fp4 && !p->b_mn_major)) DG_REQUIRE(a->k % 128 == 0);
     if (need_pointers) {
         DG_REQUIRE(a->a != nullptr && a->b != nullptr && a->d != nullptr);
         DG_REQUIRE(ab_bf16 || (a->sfa != nullptr && a->sfb != nullptr));

@@ -583,7 +583,7 @@ def test_m_grouped_contiguous_prefix_sum_layout_with_mn_major_weights(b_fp4, zer
 
 
 @pytest.mark.parametrize("variant", ["nn", "tn", "nt_strided"])
-@pytest.mark.parametrize("m,n,k", [(128, 256, 512), (208, 768, 1152), (4096, 2176, 1024), (304, 4096, 7168)])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 512), (208, 768, 1152), (4096, 2176, 1024), (304, 4096, 7168), (512, 1024, 2112), (256, 512, 576)])
 def test_fp8_x_fp4_with_an_mn_major_packed_fp4_b(variant, m, n, k):
     """B stored [K, N / 2], two columns of N per byte (tests/generators.py:318-326: transpose_packed_fp4(q).T), as the
     backward GEMMs of an FP8 x FP4 layer pass it; bit-identical to the K-major call."""
@@ -604,9 +604,10 @@ def test_fp8_x_fp4_with_an_mn_major_packed_fp4_b(variant, m, n, k):
     assert dg.kernel_status() == 0
     out = d.float().cpu().numpy()
     assert oracle.calc_diff(out, ref) < 1e-5, diff_report(out, ref)
-    d_nt = torch.empty_like(d)
-    dg.fp8_fp4_gemm_nt((fp8_cuda(qa), torch.from_numpy(sfa).cuda()), (fp4_cuda(qb), sfb_t), d_nt, recipe_a=(1, 128), recipe_b=(1, 32))
-    assert torch.equal(d.view(torch.int16), d_nt.view(torch.int16))
+    if k % 128 == 0:                                                # (a K-major packed FP4 operand needs whole 128-element blocks of K)
+        d_nt = torch.empty_like(d)
+        dg.fp8_fp4_gemm_nt((fp8_cuda(qa), torch.from_numpy(sfa).cuda()), (fp4_cuda(qb), sfb_t), d_nt, recipe_a=(1, 128), recipe_b=(1, 32))
+        assert torch.equal(d.view(torch.int16), d_nt.view(torch.int16))
 
 
 def test_mn_major_packed_fp4_b_needs_whole_128_column_blocks():
