@@ -9,6 +9,7 @@ transformed scale tensors only; all compute runs in the library's CUDA kernels.
 from __future__ import annotations
 
 import ctypes as C
+import threading
 from typing import Optional, Sequence, Tuple, Union
 
 import torch
@@ -268,6 +269,38 @@ def per_token_cast(x: torch.Tensor, fmt: str = "e4m3", gran_k: int = 128, use_pa
 # ------------------------------------------------------------------------------------------------
 # GEMMs (csrc/apis/gemm.hpp:78-318)
 # ------------------------------------------------------------------------------------------------
+# A serving loop calls the same GEMM with the same tensor geometry over and over, and the argument checks below cost
+# more interpreter time (~15 us) than a decode-sized kernel runs.  What the checks look at is metadata only when the
+# scales arrive already packed (the production path: no transform kernel), so a call whose metadata matches one that
+# passed before reuses that call's filled argument block and only refreshes the pointers and the stream.  Per thread;
+# the key holds every shape, stride, dtype and option a check depends on.
+_validated = threading.local()
+
+
+def _validated_calls() -> dict:
+    cache = getattr(_validated, "calls", None)
+    if cache is None:
+        cache = _validated.calls = {}
+    return cache
+
+
+def _call_key(name, a_data, a_sf, b_data, b_sf, d, recipe, recipe_a, recipe_b, *options):
+    """None when the call is not one the cache serves (FP32 scales need their transform kernel)."""
+    if a_sf.dtype != torch.int or b_sf.dtype != torch.int:
+        return None
+    return (name, a_data.shape, a_data.stride(), a_data.dtype, a_sf.shape, a_sf.stride(), b_data.shape, b_data.stride(), b_data.dtype,
+            b_sf.shape, b_sf.stride(), d.shape, d.stride(), d.dtype, d.device, a_data.device,
+            None if recipe is None else tuple(recipe), None if recipe_a is None else tuple(recipe_a),
+            None if recipe_b is None else tuple(recipe_b), *options)
+
+
+def _remember_call(key, args) -> None:
+    if key is not None:
+        cache = _validated_calls()
+        if len(cache) > 4096:
+            cache.clear()
+        cache[key] = args
+
 def _major_check(t: torch.Tensor) -> None:
     """csrc/utils/layout.hpp:19-27."""
     _require(t.dim() in (2, 3), "dim == 2 or dim == 3")
@@ -377,6 +410,17 @@ def fp8_fp4_gemm_nt(a, b, d, c=None, recipe=None, recipe_a=None, recipe_b=None, 
                     disable_ue8m0_cast: bool = False, alpha: Optional[float] = None, epilogue=None) -> None:
     """D[M,N] = C + alpha * A[M,K] @ B[N,K]^T with a = (data, sf), b = (data, sf) (csrc/apis/gemm.hpp:78-133)."""
     (a_data, a_sf), (b_data, b_sf) = a, b
+    key = None
+    if (c is None or c is d) and epilogue is None:
+        key = _call_key("dense", a_data, a_sf, b_data, b_sf, d, recipe, recipe_a, recipe_b, c is None, disable_ue8m0_cast, alpha is None)
+        args = _validated_calls().get(key) if key is not None else None
+        if args is not None:
+            args.a, args.sfa, args.b, args.sfb, args.d = a_data.data_ptr(), a_sf.data_ptr(), b_data.data_ptr(), b_sf.data_ptr(), d.data_ptr()
+            if alpha is not None:
+                args.alpha = alpha
+            args.stream = _stream()
+            check(lib.dg_fp8_fp4_gemm(C.byref(args)))
+            return
     major_a, major_b = _major_ab(a_data), _major_ab(b_data)
     if a_data.dtype == kPackedFP4 and b_data.dtype == kPackedFP4:
         _require(major_a == _lib.DG_MAJOR_K and major_b == _lib.DG_MAJOR_K, "major == cute::UMMA::Major::K")
@@ -412,6 +456,8 @@ def fp8_fp4_gemm_nt(a, b, d, c=None, recipe=None, recipe_a=None, recipe_b=None, 
     args = _fill_args(a_data, sfa, b_data, sfb, d, m, n, k, 1, major_a, major_b, gran_k_a, gran_k_b,
                       accumulate=c is not None, alpha=alpha, sfd=sfd, stochastic=_stochastic(epilogue, c, d))
     check(lib.dg_fp8_fp4_gemm(C.byref(args)))
+    if sfa is a_sf and sfb is b_sf:
+        _remember_call(key, args)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -746,6 +792,17 @@ def m_grouped_fp8_fp4_gemm_nt_contiguous(a, b, d, grouped_layout, recipe=None, r
     [align(grouped_layout[g-1], mk_alignment), grouped_layout[g]).  With ensure_zero_padding the padding rows of D up to
     the next aligned row are written too (zero for zero A padding); otherwise rows outside the groups are untouched."""
     (a_data, a_sf), (b_data, b_sf) = a, b
+    key = None
+    if epilogue is None:
+        key = _call_key("contiguous", a_data, a_sf, b_data, b_sf, d, recipe, recipe_a, recipe_b, grouped_layout.shape, grouped_layout.stride(),
+                        grouped_layout.dtype, disable_ue8m0_cast, use_psum_layout, ensure_zero_padding, expected_m_for_psum_layout)
+        args = _validated_calls().get(key) if key is not None else None
+        if args is not None:
+            args.a, args.sfa, args.b, args.sfb, args.d = a_data.data_ptr(), a_sf.data_ptr(), b_data.data_ptr(), b_sf.data_ptr(), d.data_ptr()
+            args.grouped_layout = grouped_layout.data_ptr()
+            args.stream = _stream()
+            check(lib.dg_m_grouped_fp8_fp4_gemm_contiguous(C.byref(args)))
+            return
     major_a, major_b = _major_ab(a_data), _major_ab(b_data)
     _require(major_a == _lib.DG_MAJOR_K, "major_a == cute::UMMA::Major::K")
     _require(grouped_layout.is_contiguous(), "grouped_layout.is_contiguous()")
@@ -773,6 +830,8 @@ def m_grouped_fp8_fp4_gemm_nt_contiguous(a, b, d, grouped_layout, recipe=None, r
                       layout=grouped_layout, expected_m=expected_m_for_psum_layout or 0, use_psum_layout=use_psum_layout,
                       ensure_zero_padding=use_psum_layout and ensure_zero_padding, stochastic=_stochastic(epilogue, None, d))
     check(lib.dg_m_grouped_fp8_fp4_gemm_contiguous(C.byref(args)))
+    if sfa is a_sf and sfb is b_sf:
+        _remember_call(key, args)
 
 
 def m_grouped_fp8_fp4_gemm_nn_contiguous(a, b, d, grouped_layout, recipe=None, recipe_a=None, recipe_b=None,
@@ -789,6 +848,17 @@ def m_grouped_fp8_fp4_gemm_nt_masked(a, b, d, masked_m, expected_m: int, recipe=
     """D[g,:masked_m[g],:] = A[g,:masked_m[g],:] @ B[g]^T; masked_m stays on the device, so the call is
     capturable in a CUDA graph; rows at or beyond masked_m[g] are not written (csrc/apis/gemm.hpp:269-318)."""
     (a_data, a_sf), (b_data, b_sf) = a, b
+    key = None
+    if epilogue is None:
+        key = _call_key("masked", a_data, a_sf, b_data, b_sf, d, recipe, recipe_a, recipe_b, masked_m.shape, masked_m.stride(), masked_m.dtype,
+                        disable_ue8m0_cast, expected_m)
+        args = _validated_calls().get(key) if key is not None else None
+        if args is not None:
+            args.a, args.sfa, args.b, args.sfb, args.d = a_data.data_ptr(), a_sf.data_ptr(), b_data.data_ptr(), b_sf.data_ptr(), d.data_ptr()
+            args.grouped_layout = masked_m.data_ptr()
+            args.stream = _stream()
+            check(lib.dg_m_grouped_fp8_fp4_gemm_masked(C.byref(args)))
+            return
     major_a, major_b = _major_ab(a_data), _major_ab(b_data)
     _require(major_a == _lib.DG_MAJOR_K and major_b == _lib.DG_MAJOR_K,
              "major_a == cute::UMMA::Major::K and major_b == cute::UMMA::Major::K")
@@ -810,6 +880,8 @@ def m_grouped_fp8_fp4_gemm_nt_masked(a, b, d, masked_m, expected_m: int, recipe=
     args = _fill_args(a_data, sfa, b_data, sfb, d, m, n, k, g, major_a, major_b, gran_k_a, gran_k_b,
                       layout=masked_m, expected_m=expected_m, stochastic=_stochastic(epilogue, None, d))
     check(lib.dg_m_grouped_fp8_fp4_gemm_masked(C.byref(args)))
+    if sfa is a_sf and sfb is b_sf:
+        _remember_call(key, args)
 
 
 # ------------------------------------------------------------------------------------------------

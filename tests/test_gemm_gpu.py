@@ -1115,6 +1115,40 @@ def test_cast_kernel_feeds_the_gemm_without_a_scale_transform():
 # ---------------------------------------------------------------------------------------------------
 # API behaviour
 # ---------------------------------------------------------------------------------------------------
+def test_repeated_calls_reuse_validated_arguments_but_still_check_new_geometry():
+    """A call whose tensor metadata matches an earlier, validated call skips the Python-side checks; anything else about
+    the call (new buffers, another alpha, a wrong shape) behaves exactly as on a first call."""
+    m, n, k = 128, 512, 1024
+    qa, sfa, qb, sfb, _ = quantise_dense(seeded_bf16((m, k), 201), seeded_bf16((n, k), 202))
+    a = (fp8_cuda(qa), packed_sf_cuda(sfa)); b = (fp8_cuda(qb), packed_sf_cuda(sfb))
+    ref = oracle.dequant_gemm_nt(qa, sfa, qb, sfb)
+    outs = []
+    for i in range(3):                                       # the second and third call take the short path
+        d = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+        dg.fp8_gemm_nt(a, b, d, recipe=(1, 1, 128))
+        outs.append(d)
+    assert all(torch.equal(o.view(torch.int16), outs[0].view(torch.int16)) for o in outs)
+    assert oracle.calc_diff(outs[0].float().cpu().numpy(), ref) < 1e-5
+    # other operands of the same geometry
+    qa2, sfa2, _, _, _ = quantise_dense(seeded_bf16((m, k), 203), seeded_bf16((n, k), 202))
+    d2 = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    dg.fp8_gemm_nt((fp8_cuda(qa2), packed_sf_cuda(sfa2)), b, d2, recipe=(1, 1, 128))
+    assert oracle.calc_diff(d2.float().cpu().numpy(), oracle.dequant_gemm_nt(qa2, sfa2, qb, sfb)) < 1e-5
+    # alpha changes from call to call
+    for alpha in (0.5, -2.0):
+        d3 = torch.empty((m, n), dtype=torch.float, device="cuda")
+        dg.fp8_gemm_nt(a, b, d3, recipe=(1, 1, 128), alpha=alpha)
+        assert oracle.calc_diff(d3.cpu().numpy(), oracle.dequant_gemm_nt(qa, sfa, qb, sfb, alpha=alpha)) < 1e-9
+    # a wrong shape is still rejected
+    with pytest.raises(RuntimeError, match="m == m_ and n == n_"):
+        dg.fp8_gemm_nt(a, b, torch.empty((m, n + 16), dtype=torch.bfloat16, device="cuda"), recipe=(1, 1, 128))
+    # accumulation into d keeps working on the short path
+    acc = torch.zeros((m, n), dtype=torch.float, device="cuda")
+    for _ in range(3):
+        dg.fp8_gemm_nt(a, b, acc, c=acc, recipe=(1, 1, 128))
+    assert oracle.calc_diff(acc.cpu().numpy(), 3 * ref) < 1e-9
+
+
 def test_api_rejects_what_the_reference_rejects():
     m, n, k = 128, 256, 256
     qa, sfa, qb, sfb, _ = quantise_dense(seeded_bf16((m, k), 50), seeded_bf16((n, k), 51))
