@@ -51,6 +51,7 @@ SIGNATURES = {
     "dg_last_error": (C.c_char_p, []),
     "dg_init": (C.c_int, [C.c_char_p]),
     "dg_shutdown": (C.c_int, []),
+    "dg_is_shut_down": (C.c_int, []),
     "dg_set_num_sms": (C.c_int, [C.c_int]),
     "dg_get_num_sms": (C.c_int, []),
     "dg_set_tc_util": (C.c_int, [C.c_int]),

@@ -59,7 +59,13 @@ def set_num_sms(num_sms: int) -> None:
     check(lib.dg_set_num_sms(int(num_sms)))
 
 
+def _alive() -> None:
+    if lib.dg_is_shut_down():
+        raise RuntimeError("the runtime has been shut down (deep_gemm.shutdown())")
+
+
 def get_num_sms() -> int:
+    _alive()
     return lib.dg_get_num_sms()
 
 
@@ -68,6 +74,7 @@ def set_tc_util(tc_util: int) -> None:
 
 
 def get_tc_util() -> int:
+    _alive()
     return lib.dg_get_tc_util()
 
 
@@ -76,6 +83,7 @@ def set_pdl(enabled: bool) -> None:
 
 
 def get_pdl() -> bool:
+    _alive()
     return bool(lib.dg_get_pdl())
 
 

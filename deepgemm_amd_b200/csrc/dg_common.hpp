@@ -70,10 +70,14 @@ struct State {
     int mk_alignment = 128;
     int* status_host = nullptr;      // pinned, mapped: kernels write failure codes here
     int* status_device = nullptr;
+    bool shut_down = false;          // dg_shutdown() was called: buffers released, every later call fails
 };
 State& state();
 int device_num_sms();                // SM count of the current device, 0 if there is none
 int ensure_status_word();            // allocates the host-mapped status word on first GPU use
+void release_split_workspaces();     // frees the library-owned split-K panels of every device
+#define DG_REQUIRE_ALIVE() \
+    do { if (::dg::state().shut_down) return ::dg::fail(DG_ERR_INVALID_ARGUMENT, "the runtime has been shut down (dg_shutdown)"); } while (0)
 
 inline int env_int(const char* name, int dflt = 0) {
     // DG_ prefix first, then DJ_ as the reference's runtime does (README.md:166)

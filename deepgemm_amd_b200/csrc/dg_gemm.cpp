@@ -41,9 +41,12 @@ struct GemmParams {
 // captured graph may replay on any stream, so a per-stream buffer would promise nothing): split-K GEMMs that overlap
 // on the GPU from different streams would race on it; set DG_FORCE_SPLIT_K=1 to keep such workloads unsplit.  The
 // buffer only grows; growing allocates, so the first call of a shape must not be inside a stream capture.
+std::mutex g_workspace_mu;
+std::map<int, std::pair<float*, size_t>> g_workspaces;
+
 int split_workspace(size_t bytes, float** out) {
-    static std::mutex mu;
-    static std::map<int, std::pair<float*, size_t>> per_device;
+    std::mutex& mu = g_workspace_mu;
+    auto& per_device = g_workspaces;
     std::lock_guard<std::mutex> lock(mu);
     int device = 0;
     DG_CUDA_RT(cudaGetDevice(&device));
@@ -573,6 +576,7 @@ struct FixedScratch {
 };
 
 int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratch = nullptr) {
+    DG_REQUIRE_ALIVE();
     Problem p;
     int rc = validate(kind, a, true, &p);
     if (rc != DG_OK) return rc;
@@ -727,6 +731,13 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
 }
 
 }  // namespace
+
+void release_split_workspaces() {
+    std::lock_guard<std::mutex> lock(g_workspace_mu);
+    for (auto& [device, w] : g_workspaces)
+        if (w.first != nullptr) cudaFree(w.first);
+    g_workspaces.clear();
+}
 
 // Called by the no-allocation entry point in dg_splitk.cu, which owns the fixed buffer
 int run_dense_gemm_with_fixed_scratch(const dg_gemm_args_t* args, float* scratch, size_t scratch_bytes) {

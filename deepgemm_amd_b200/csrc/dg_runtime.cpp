@@ -96,9 +96,26 @@ int dg_init(const char* library_root) {
     return DG_OK;
 }
 
-int dg_shutdown(void) { return DG_OK; }
+// csrc/apis/runtime.hpp of the reference: the runtime's resources are released once, a second call is a no-op, and the
+// runtime is not recreated afterwards (every later call fails)
+int dg_shutdown(void) {
+    State& s = state();
+    {
+        std::lock_guard<std::mutex> lock(s.mu);
+        if (s.shut_down) return DG_OK;
+        s.shut_down = true;
+        if (s.status_host != nullptr) cudaFreeHost(s.status_host);
+        s.status_host = s.status_device = nullptr;
+    }
+    release_split_workspaces();
+    cudaGetLastError();
+    return DG_OK;
+}
+
+int dg_is_shut_down(void) { return state().shut_down ? 1 : 0; }
 
 int dg_set_num_sms(int num_sms) {
+    DG_REQUIRE_ALIVE();
     DG_REQUIRE(num_sms > 0 && num_sms % 2 == 0);
     const int dev = device_num_sms();
     if (dev > 0) DG_REQUIRE(num_sms <= dev);
@@ -113,15 +130,18 @@ int dg_get_num_sms(void) {
 }
 
 int dg_set_tc_util(int percent) {
+    DG_REQUIRE_ALIVE();
     DG_REQUIRE(percent > 0 && percent <= 100);
     state().tc_util = percent;
     return DG_OK;
 }
 int dg_get_tc_util(void) { return state().tc_util; }
-int dg_set_pdl(int enabled) { state().pdl = enabled != 0; return DG_OK; }
+int dg_set_pdl(int enabled) {
+    DG_REQUIRE_ALIVE(); state().pdl = enabled != 0; return DG_OK; }
 int dg_get_pdl(void) { return state().pdl; }
 
-int dg_set_mk_alignment_for_contiguous_layout(int alignment) { state().mk_alignment = alignment; return DG_OK; }
+int dg_set_mk_alignment_for_contiguous_layout(int alignment) {
+    DG_REQUIRE_ALIVE(); state().mk_alignment = alignment; return DG_OK; }
 int dg_get_mk_alignment_for_contiguous_layout(void) { return state().mk_alignment; }
 int dg_get_theoretical_mk_alignment_for_contiguous_layout(int) { return 256; }
 

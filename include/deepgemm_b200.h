@@ -58,7 +58,10 @@ DG_API const char* dg_last_error(void);
 /* init(library_root_path): where the device headers (csrc/device) and the in-tree kernel cache live.
  * Touches no CUDA context (deep_gemm/__init__.py:122, tests/test_lazy_init.py:18-19). */
 DG_API int dg_init(const char* library_root);
+/* shutdown(): releases what the library allocated on the devices (split-K panels, the status word); a second call is a
+ * no-op; the runtime is not recreated, every later GEMM or setter fails (tests/test_lazy_init.py:78-90). */
 DG_API int dg_shutdown(void);
+DG_API int dg_is_shut_down(void);                /* 1 after dg_shutdown */
 DG_API int dg_set_num_sms(int num_sms);          /* must be even and at most the device's SM count (heuristics/config.hpp:60) */
 DG_API int dg_get_num_sms(void);                 /* the override, else the device's SM count, else 148 without a device */
 DG_API int dg_set_tc_util(int percent);          /* csrc/runtime/runtime.hpp:88-100; kept for API parity, unused by these kernels */

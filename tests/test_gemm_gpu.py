@@ -2,6 +2,8 @@
 numpy oracle on the same seeded inputs.  Thresholds follow the reference's own tests
 (tests/test_fp8_fp4.py:54-57, tests/generators.py:69-74): calc_diff < 1e-3 against the
 dequantise-then-matmul value for every format; exact indexing for the grouped layouts."""
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -1147,6 +1149,43 @@ def test_repeated_calls_reuse_validated_arguments_but_still_check_new_geometry()
     for _ in range(3):
         dg.fp8_gemm_nt(a, b, acc, c=acc, recipe=(1, 1, 128))
     assert oracle.calc_diff(acc.cpu().numpy(), 3 * ref) < 1e-9
+
+
+def test_shutdown_releases_the_split_workspace_and_is_final():
+    """In a child process (shutdown is for good): the library-owned FP32 panels of the two-kernel K slicing go back to the
+    driver, and a GEMM afterwards fails instead of recreating the runtime (tests/test_lazy_init.py:78-90)."""
+    import subprocess
+    import sys
+    import textwrap
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    child = textwrap.dedent("""
+        import os, torch
+        os.environ["DG_FORCE_SPLIT_CLUSTER"] = "-1"
+        os.environ["DG_FORCE_SPLIT_K"] = "4"
+        os.environ["DG_FORCE_BLOCK_N"] = "128"
+        import deepgemm_amd_b200 as dg
+        from deepgemm_amd_b200.utils import per_token_cast_to_fp8
+        m, n, k = 512, 1024, 16384
+        a = per_token_cast_to_fp8(torch.randn(m, k, device="cuda", dtype=torch.bfloat16), True)
+        b = per_token_cast_to_fp8(torch.randn(n, k, device="cuda", dtype=torch.bfloat16), True)
+        d = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+        assert dg.get_gemm_config(0, m, n, k)["num_splits"] == 4
+        dg.fp8_gemm_nt(a, b, d, recipe_a=(1, 128), recipe_b=(1, 128))
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
+        dg.shutdown(); dg.shutdown()
+        assert torch.cuda.mem_get_info()[0] - free_before >= 4 * m * n * 4          # the four FP32 panels
+        try:
+            dg.fp8_gemm_nt(a, b, d, recipe_a=(1, 128), recipe_b=(1, 128))
+        except RuntimeError as e:
+            assert "shut down" in str(e)
+        else:
+            raise AssertionError("a GEMM ran after shutdown")
+        print("DG_CHILD_OK")
+    """)
+    env = dict(os.environ, PYTHONPATH=root + os.pathsep + os.path.join(root, "tests") + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    result = subprocess.run([sys.executable, "-c", child], env=env, capture_output=True, text=True, timeout=600)
+    assert result.returncode == 0 and "DG_CHILD_OK" in result.stdout, result.stdout + result.stderr
 
 
 def test_api_rejects_what_the_reference_rejects():

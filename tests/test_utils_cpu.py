@@ -91,3 +91,32 @@ def test_k_grouped_nt_form_is_rejected_like_the_reference_on_this_architecture()
     import deepgemm_amd_b200 as dg
     with pytest.raises(RuntimeError, match="Unsupported architecture"):
         dg.k_grouped_fp8_gemm_nt_contiguous(None, None, None, [128], None)
+
+
+def test_import_touches_no_cuda_context_and_shutdown_is_final():
+    """tests/test_lazy_init.py of the reference: importing must leave CUDA uninitialised (worker processes pick their
+    device afterwards); shutdown() may be called twice, and nothing recreates the runtime after it."""
+    import subprocess
+    import sys
+    import textwrap
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    child = textwrap.dedent("""
+        import torch
+        import deepgemm_amd_b200 as dg
+        assert not torch.cuda.is_initialized()
+        assert dg.get_tc_util() == 100
+        dg.set_tc_util(90); assert dg.get_tc_util() == 90
+        assert not torch.cuda.is_initialized()
+        dg.shutdown(); dg.shutdown()
+        for call in (dg.get_tc_util, lambda: dg.set_tc_util(80), dg.get_num_sms, lambda: dg.set_mk_alignment_for_contiguous_layout(256)):
+            try:
+                call()
+            except RuntimeError as e:
+                assert "shut down" in str(e)
+            else:
+                raise AssertionError("the runtime was recreated after shutdown")
+        print("DG_CHILD_OK")
+    """)
+    env = dict(os.environ, PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    result = subprocess.run([sys.executable, "-c", child], env=env, capture_output=True, text=True, timeout=300)
+    assert result.returncode == 0 and "DG_CHILD_OK" in result.stdout, result.stdout + result.stderr
