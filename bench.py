@@ -528,6 +528,13 @@ def detail_rows(torch, dg):
         t = bench_kineto(lambda: torch.matmul(a16, b16.t(), out=d16), ("nvjet", "gemm", "cutlass", "sm100", "sm90"), 10)
         add(f"torch.matmul (cuBLAS) bf16 m{M_DENSE} n{n} k{k}", t, flops_of(M_DENSE, n, k), 2 * (M_DENSE * k + n * k + M_DENSE * n))
         del a16, b16, d16
+    # einsum 'bmk,bnk->mn' (tests/test_einsum.py:21-41): a BF16 GEMM reduced over the batch as well
+    for s_, m_, n_, k_ in ((4096, 256, 256, 256), (8192, 384, 128, 384)):
+        ab, bb = torch.randn((s_, m_, k_), device="cuda", dtype=torch.bfloat16), torch.randn((s_, n_, k_), device="cuda", dtype=torch.bfloat16)
+        acc = torch.zeros((m_, n_), device="cuda", dtype=torch.float)
+        t = bench(lambda: dg.einsum("bmk,bnk->mn", ab, bb, acc, c=acc), 2, 8)
+        add(f"bf16 einsum bmk,bnk->mn b{s_} m{m_} n{n_} k{k_} fp32 accumulate", t, flops_of(m_, n_, s_ * k_), 2 * s_ * (m_ + n_) * k_ + m_ * n_ * 4)
+        del ab, bb, acc
     return rows
 
 
