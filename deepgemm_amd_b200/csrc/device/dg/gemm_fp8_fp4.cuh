@@ -111,6 +111,14 @@ constexpr bool     kStochastic = DG_STOCHASTIC_ROUNDING != 0;      // BF16 outpu
 constexpr bool     kAccumulate = DG_ACCUMULATE != 0;
 constexpr uint32_t kRasterGroup = DG_RASTER_GROUP;
 constexpr bool     kSplitK     = DG_SPLIT_K != 0;
+#ifndef DG_TRANSPOSED_D
+#define DG_TRANSPOSED_D 0
+#endif
+// The caller's operands are passed swapped (its B, the weight, as the 128-row operand; its few rows of A as the tile's
+// columns): the tile is the transpose of the caller's D, and the epilogue writes element (row, column) to D[column][row].
+// For GEMMs with few rows a CTA then pulls M x 128 bytes of activations per K-block next to its 128 rows of weights,
+// instead of 128 rows of (mostly padding) activations next to a narrow slice of the weights.
+constexpr bool kTransposedD = DG_TRANSPOSED_D != 0;
 #ifndef DG_BATCH_REDUCE
 #define DG_BATCH_REDUCE 0
 #endif
@@ -164,6 +172,8 @@ static_assert(!kDIsFP8 || ((kGemmType == kDense || kGemmType == kBatched) && !kA
 static_assert(kGemmType != kBatched || (kCluster == 1 && !kSplitK), "batched: one CTA per tile");
 static_assert(!kBatchReduce || (kGemmType == kDense && kABIsBF16 && !kAMnMajor && !kBMnMajor && kCluster == 1),
               "the batch-reduced GEMM takes K-major BF16 operands, one CTA per tile");
+static_assert(!kTransposedD || (kGemmType == kDense && kCluster == 1 && kMHalves == 1 && !kAccumulate && !kDIsFP8 && !kStochastic && !kSplitK),
+              "the transposed epilogue serves the plain dense GEMM");
 static_assert(kSplitCluster >= 1 && kSplitCluster <= 8, "portable cluster sizes");
 static_assert(kSplitCluster == 1 || (kGemmType == kDense && !kSplitK && kCluster == 1 && kMHalves == 1 && !kAccumulate && !kDIsFP8 && !kStochastic),
               "cluster-reduced K slicing serves the plain dense GEMM");
@@ -720,6 +730,58 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                 cluster_wait();
                 cluster_synced = true;
 
+                if constexpr (kTransposedD) {
+                    // Work items are (column, 8 consecutive rows): 32 contiguous bytes of every parked tile, 8 consecutive
+                    // elements of one row of the caller's D.  CTA r takes items [128 r, 128 r + 128), then S x 128 further on.
+                    uint32_t tiles[kSplitCluster];
+                    #pragma unroll
+                    for (uint32_t r = 0; r < kSplitCluster; ++r) tiles[r] = map_to_cta(smem_base + kSmemA, r);
+                    constexpr uint32_t kItems = BLOCK_N * (BLOCK_M / 8);
+                    #pragma unroll 1
+                    for (uint32_t q = epi_tid + 128 * split_rank; q < kItems; q += 128 * kSplitCluster) {
+                        const uint32_t c = q / (BLOCK_M / 8), r8 = q % (BLOCK_M / 8);
+                        const uint32_t col = tile.n_block * BLOCK_N + c;             // row of the caller's D
+                        const uint32_t row = tile.m_block * BLOCK_M + r8 * 8;        // its first column
+                        if (col >= p.shape_n || row >= p.shape_m) continue;
+                        float sum[8];
+                        #pragma unroll
+                        for (uint32_t i = 0; i < 8; ++i) sum[i] = 0.0f;
+                        #pragma unroll
+                        for (uint32_t r = 0; r < kSplitCluster; ++r) {
+                            const uint4 lo = ld_shared_cluster_v4(tiles[r] + (c * BLOCK_M + r8 * 8) * 4);
+                            const uint4 hi = ld_shared_cluster_v4(tiles[r] + (c * BLOCK_M + r8 * 8) * 4 + 16);
+                            sum[0] += __uint_as_float(lo.x); sum[1] += __uint_as_float(lo.y); sum[2] += __uint_as_float(lo.z); sum[3] += __uint_as_float(lo.w);
+                            sum[4] += __uint_as_float(hi.x); sum[5] += __uint_as_float(hi.y); sum[6] += __uint_as_float(hi.z); sum[7] += __uint_as_float(hi.w);
+                        }
+                        #pragma unroll
+                        for (uint32_t i = 0; i < 8; ++i) sum[i] *= p.alpha;
+                        const size_t at = static_cast<size_t>(col) * p.ldd + row;
+                        if constexpr (kDIsFP32) {
+                            float* out = reinterpret_cast<float*>(p.d) + at;
+                            if (row + 8 <= p.shape_m) {
+                                *reinterpret_cast<float4*>(out) = make_float4(sum[0], sum[1], sum[2], sum[3]);
+                                *reinterpret_cast<float4*>(out + 4) = make_float4(sum[4], sum[5], sum[6], sum[7]);
+                            } else {
+                                #pragma unroll
+                                for (uint32_t i = 0; i < 8; ++i)
+                                    if (row + i < p.shape_m) out[i] = sum[i];
+                            }
+                        } else {
+                            unsigned short* out = reinterpret_cast<unsigned short*>(p.d) + at;
+                            uint32_t w[4];
+                            #pragma unroll
+                            for (uint32_t i = 0; i < 4; ++i) w[i] = pack_bf16x2(sum[2 * i], sum[2 * i + 1]);
+                            if (row + 8 <= p.shape_m) {
+                                *reinterpret_cast<uint4*>(out) = make_uint4(w[0], w[1], w[2], w[3]);
+                            } else {
+                                #pragma unroll
+                                for (uint32_t i = 0; i < 8; ++i)
+                                    if (row + i < p.shape_m) out[i] = static_cast<unsigned short>(w[i / 2] >> (16 * (i % 2)));
+                            }
+                        }
+                    }
+                    continue;
+                }
                 const uint32_t d_row = tile.m_block * BLOCK_M + row_in_tile;
                 uint32_t peers[kSplitCluster];
                 #pragma unroll
@@ -790,6 +852,29 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                 if (kCluster == 1 || is_leader) mbar_arrive(tmem_empty_bar(accum));
                 else mbar_arrive_cluster(in_leader(tmem_empty_bar(accum)));
             };
+
+            if constexpr (kTransposedD) {
+                // Thread = one row of the tile = one column of the caller's D: consecutive lanes write consecutive elements
+                const uint32_t d_col = tile.m_block * BLOCK_M + row_in_tile;
+                #pragma unroll
+                for (uint32_t b = 0; b < BLOCK_N / 16; ++b) {
+                    uint32_t v[16];
+                    tmem_ld_32x32b_x16(tmem_row_addr + b * 16, v);
+                    tmem_ld_wait();
+                    if (b + 1 == BLOCK_N / 16) release_tmem();
+                    #pragma unroll
+                    for (uint32_t i = 0; i < 16; ++i) {
+                        const uint32_t d_row = n0 + b * 16 + i;
+                        if (d_row < p.shape_n && d_col < p.shape_m) {
+                            const float x = __uint_as_float(v[i]) * p.alpha;
+                            const size_t at = static_cast<size_t>(d_row) * p.ldd + d_col;
+                            if constexpr (kDIsFP32) reinterpret_cast<float*>(p.d)[at] = x;
+                            else reinterpret_cast<unsigned short*>(p.d)[at] = static_cast<unsigned short>(pack_bf16x2(x, 0.0f) & 0xFFFFu);
+                        }
+                    }
+                }
+                continue;
+            }
 
             [[maybe_unused]] uint32_t row[kRowInRegs ? BLOCK_N / 2 : 1];        // BF16 pairs: columns (2i, 2i+1) of the tile row
             if constexpr (kRowInRegs) {

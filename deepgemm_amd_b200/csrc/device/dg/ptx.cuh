@@ -391,6 +391,13 @@ __device__ __forceinline__ uint32_t ld_shared_cluster_u32(uint32_t cluster_addr)
     return v;
 }
 
+// Four consecutive words (16-byte aligned) of another CTA's shared memory
+__device__ __forceinline__ uint4 ld_shared_cluster_v4(uint32_t cluster_addr) {
+    uint4 v;
+    asm volatile("ld.shared::cluster.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(cluster_addr) : "memory");
+    return v;
+}
+
 __device__ __forceinline__ void st_shared_u32(uint32_t addr, uint32_t v) {
     asm volatile("st.shared.u32 [%0], %1;" :: "r"(addr), "r"(v) : "memory");
 }

@@ -249,7 +249,32 @@ int clusters_at_once(int size, int num_sms) {
     return std::max(1, kOn148[size] * num_sms / 148);
 }
 
-int choose_config(const Problem& p, dg_gemm_config_t* cfg, bool allow_cluster_split = true) {
+// The same problem with the operands' roles exchanged: the caller's B (the weight) becomes the 128-row operand and its
+// few rows of A the tile's columns; the kernel then writes the transpose of its tile (DG_TRANSPOSED_D)
+Problem swapped(const Problem& p) {
+    Problem q = p;
+    std::swap(q.m, q.n);
+    std::swap(q.a_fp4, q.b_fp4);
+    std::swap(q.a_mn_major, q.b_mn_major);
+    std::swap(q.gran_k_a, q.gran_k_b);
+    return q;
+}
+
+// Whether a dense GEMM may run with its operands swapped (DG_FORCE_SWAP_AB: 1 = whenever this holds, -1 = never)
+bool swap_allowed(const Problem& p) {
+    return p.kind == DG_GEMM_DENSE && !p.ab_bf16 && !p.a_fp4 && !p.b_fp4 && !p.a_mn_major && !p.b_mn_major && !p.accumulate &&
+           !p.d_fp8 && !p.stochastic && p.reduce_batches <= 1 && p.m <= 64 && p.n >= 128 && env_int("FORCE_SWAP_AB") >= 0 &&
+           env_int("FORCE_CLUSTER") <= 1 && env_int("FORCE_BLOCK_M") != 256 && env_int("FORCE_BLOCK_K") != 64;
+}
+
+struct Constraints {
+    bool allow_cluster_split = true;
+    int only_bn = 0;                  // swapped operands: the tile is as wide as the caller's M, rounded up to 16
+    bool swapped = false;             // 128-row tiles, K slices only inside a cluster (the transposed epilogue's two forms)
+};
+
+int choose_config_for(const Problem& p, dg_gemm_config_t* cfg, const Constraints& lim, double* cost_out) {
+    const bool allow_cluster_split = lim.allow_cluster_split;
     const int num_sms = dg_get_num_sms();
     const int d_elem = p.d_fp32 ? 4 : (p.d_fp8 ? 1 : 2);
     const int ab_elem = p.ab_bf16 ? 2 : 1;
@@ -271,6 +296,7 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg, bool allow_cluster_sp
     for (int halves = 1; halves <= 2; ++halves)
     for (int bk = 128; bk >= 64; bk /= 2) {
         if (forced_cluster ? cluster != forced_cluster : !cluster_allowed(p, cluster)) continue;
+        if (lim.swapped && (cluster != 1 || halves != 1 || bk != 128)) continue;
         // A CTA pair multiplies all its rows with one B: in the contiguous layout every expert segment must then be a
         // whole number of pair tiles
         if (cluster == 2 && (num_sms % 2 != 0 || (p.b_fp4 && p.b_mn_major) || p.kind == DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM || p.kind == DG_GEMM_K_GROUPED_CONTIGUOUS ||
@@ -305,7 +331,7 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg, bool allow_cluster_sp
         const bool can_split = p.kind == DG_GEMM_DENSE && !p.accumulate && !p.d_fp8 && !p.stochastic && cluster == 1 && halves == 1 && bk == 128 &&
                                forced_splits != 1 && k_blocks >= 16;
         for (int bn = 16; bn <= (p.ab_bf16 ? 256 : 240); bn += 16) {
-            if (forced_bn && bn != forced_bn) continue;
+            if (lim.only_bn ? bn != lim.only_bn : (forced_bn && bn != forced_bn)) continue;
             // An MN-major B load starts on a 16-byte boundary of the row; for the packed 4-bit tensor-map type the
             // innermost coordinate must be a multiple of 128 elements (K-major loads start on whole K-blocks anyway)
             if (p.b_mn_major && (bn / cluster) % (p.b_fp4 ? 128 : 16) != 0) continue;
@@ -326,6 +352,7 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg, bool allow_cluster_sp
                 for (int in_cluster = 0; in_cluster <= (splits > 1 ? 1 : 0); ++in_cluster) {
                 if (splits > 1 && forced_split_cluster != 0 && in_cluster != (forced_split_cluster > 0 ? 1 : 0)) continue;
                 if (in_cluster && (!allow_cluster_split || splits > 8)) continue;
+                if (lim.swapped && splits > 1 && !in_cluster) continue;
                 const int64_t tiles = mn_tiles * splits;
                 // Clusters are placed inside one GPC each, so fewer of them fit than SMs / size suggests
                 const int64_t waves = in_cluster ? ceil_div<int64_t>(mn_tiles, clusters_at_once(splits, num_sms)) : ceil_div<int64_t>(tiles, units);
@@ -380,6 +407,7 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg, bool allow_cluster_sp
             }
         }
     }
+    if (best.bn == 0 && lim.swapped) return DG_ERR_UNSUPPORTED;
     if (best.bn == 0)
         return fail(DG_ERR_INVALID_ARGUMENT, "no tile configuration: DG_FORCE_BLOCK_N must be a multiple of 16 in [16, 240], "
                                              "DG_FORCE_CLUSTER 1 or 2 (2 needs an even SM count and, for the contiguous layout, expert segments aligned to the pair's rows), "
@@ -397,6 +425,8 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg, bool allow_cluster_sp
     const int forced_raster = env_int("FORCE_RASTER_GROUP");
     cfg->raster_group = forced_raster > 0 ? forced_raster : std::max(4, 16 / (best.cluster * best.halves));
     cfg->split_in_cluster = best.in_cluster ? 1 : 0;
+    cfg->swap_ab = lim.swapped ? 1 : 0;
+    if (cost_out != nullptr) *cost_out = best.cost;
     cfg->num_ctas = best.in_cluster ? static_cast<int>(best.tiles) :
                     best.cluster * (p.kind == DG_GEMM_M_GROUPED_MASKED || p.kind == DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM
                                         ? units : static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(units, best.tiles))));
@@ -405,6 +435,32 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg, bool allow_cluster_sp
     cfg->num_tiles = static_cast<int>(best.tiles);
     cfg->waves_x100 = static_cast<int>(best.tiles * 100 / units);
     return DG_OK;
+}
+
+// The configuration of a problem: the cheaper of the direct form and, for dense GEMMs with few rows, the form with the
+// operands swapped.  Sizes in the result are the kernel's (block_m rows of the weight, block_n = the caller's M rounded up).
+int choose_config(const Problem& p, dg_gemm_config_t* cfg, bool allow_cluster_split = true) {
+    Constraints direct;
+    direct.allow_cluster_split = allow_cluster_split;
+    double direct_cost = 0;
+    const int forced_swap = env_int("FORCE_SWAP_AB");
+    const int rc = choose_config_for(p, cfg, direct, &direct_cost);
+    if (!swap_allowed(p) || !allow_cluster_split) return rc;
+    // Measured on 28 (M, N, K) points: up to 32 rows the swapped form wins wherever the cost model prefers it (by 5-30 %);
+    // at 64 rows the two are within 5 % either way and the transposed epilogue's scalar stores start to show, so it is
+    // used on request only
+    if (forced_swap <= 0 && p.m > 32) return rc;
+    Constraints lim;
+    lim.swapped = true;
+    lim.only_bn = static_cast<int>(align_up<int64_t>(p.m, 16));
+    dg_gemm_config_t other{};
+    double other_cost = 0;
+    if (choose_config_for(swapped(p), &other, lim, &other_cost) != DG_OK) return rc;
+    if (rc != DG_OK || forced_swap > 0 || other_cost < direct_cost) {
+        *cfg = other;
+        return DG_OK;
+    }
+    return rc;
 }
 
 // The layout the kernel of a configuration uses (same arithmetic as choose_config)
@@ -444,6 +500,7 @@ std::string generate_source(const Problem& p, const dg_gemm_config_t& cfg) {
       << "#define DG_ACCUMULATE " << (p.accumulate ? 1 : 0) << "\n"
       << "#define DG_RASTER_GROUP " << cfg.raster_group << "\n"
       << "#define DG_SPLIT_K " << (cfg.num_splits > 1 && !cfg.split_in_cluster ? 1 : 0) << "\n"
+      << "#define DG_TRANSPOSED_D " << (cfg.swap_ab ? 1 : 0) << "\n"
       << "#define DG_BATCH_REDUCE " << (p.reduce_batches > 1 ? 1 : 0) << "\n"
       << "#define DG_SPLIT_CLUSTER " << (cfg.split_in_cluster ? cfg.num_splits : 1) << "\n"
       << "#define DG_WRITE_PADDING " << (p.write_padding ? 1 : 0) << "\n"
@@ -509,7 +566,7 @@ int encode_2d(CUtensorMap* map, CUtensorMapDataType dtype, const void* base, uin
 int get_kernel(const Problem& p, const dg_gemm_config_t& cfg, dg_kernel_t* kernel) {
     static const char* names[6] = {"gemm_fp8_fp4_dense", "gemm_fp8_fp4_m_grouped_contiguous", "gemm_fp8_fp4_m_grouped_masked",
                                    "gemm_fp8_fp4_m_grouped_contiguous_psum", "gemm_fp8_fp4_k_grouped_contiguous", "gemm_fp8_fp4_batched"};
-    const std::string src = generate_source(p, cfg);
+    const std::string src = generate_source(cfg.swap_ab ? swapped(p) : p, cfg);
     return dg_jit_compile(names[p.kind], "dg_gemm_fp8_fp4", src.c_str(), "", kernel);
 }
 
@@ -523,7 +580,7 @@ struct Plan {
 
 int get_plan(const Problem& p, Plan* plan) {
     static const char* kEnvNames[] = {"FORCE_BLOCK_N", "FORCE_CLUSTER", "FORCE_SPLIT_K", "FORCE_BLOCK_M", "FORCE_BLOCK_K",
-                                      "FORCE_NUM_STAGES", "FORCE_RASTER_GROUP", "PROFILE", "FORCE_SPLIT_CLUSTER"};
+                                      "FORCE_NUM_STAGES", "FORCE_RASTER_GROUP", "PROFILE", "FORCE_SPLIT_CLUSTER", "FORCE_SWAP_AB"};
     std::array<int, 32> key{};
     int i = 0;
     for (int v : {p.kind, p.m, p.n, p.k, p.groups, static_cast<int>(p.a_fp4), static_cast<int>(p.b_fp4), static_cast<int>(p.ab_bf16),
@@ -587,6 +644,22 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
     if ((rc = get_plan(p, &plan)) != DG_OK) return rc;
     const dg_gemm_config_t& cfg = plan.cfg;
     dg_kernel_t kernel = plan.kernel;
+    // Operands swapped: from here on "A" is the caller's B and the other way round; D stays the caller's, which the
+    // kernel writes transposed
+    dg_gemm_args_t exchanged;
+    if (cfg.swap_ab) {
+        exchanged = *a;
+        std::swap(exchanged.a, exchanged.b);
+        std::swap(exchanged.sfa, exchanged.sfb);
+        std::swap(exchanged.m, exchanged.n);
+        std::swap(exchanged.a_dtype, exchanged.b_dtype);
+        std::swap(exchanged.major_a, exchanged.major_b);
+        std::swap(exchanged.lda, exchanged.ldb);
+        std::swap(exchanged.sfa_pitch, exchanged.sfb_pitch);
+        std::swap(exchanged.gran_k_a, exchanged.gran_k_b);
+        a = &exchanged;
+        p = swapped(p);
+    }
     if (env_int("PRINT_CONFIGS"))
         fprintf(stderr, "[dg] kind %d m %d n %d k %d groups %d -> block_m %d block_n %d block_k %d cluster %d stages %d ctas %d smem %d tiles %d splits %d x %d%s\n",
                 kind, p.m, p.n, p.k, p.groups, cfg.block_m, cfg.block_n, cfg.block_k, cfg.cluster_size, cfg.num_stages, cfg.num_ctas, cfg.smem_bytes, cfg.num_tiles,
@@ -676,10 +749,14 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
     const uint64_t d_rows = split ? static_cast<uint64_t>(cfg.num_splits) * panel_rows :
                             (k_grouped ? static_cast<uint64_t>(p.groups) * p.m : a_rows);
     const uint64_t d_pitch_bytes = split ? ld_ws * 4 : a->ldd * (p.d_fp32 ? 4 : (p.d_fp8 ? 1 : 2));
-    if ((rc = encode_2d(&tm_d, d_type, d_base, p.n, d_rows, d_pitch_bytes, lay.store_cols(), 128, d_swizzle, nb, bs_d)) != DG_OK) return rc;
-    if ((rc = encode_2d(&tm_d_full, d_type, d_base, p.n, d_rows, d_pitch_bytes, lay.group_cols(), 128,
-                        lay.group_bytes() == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, nb, bs_d)) != DG_OK)
-        return rc;
+    if (cfg.swap_ab) {
+        tm_d = tm_d_full = tm_a;                 // never used: the transposed epilogue stores without a tensor map
+    } else {
+        if ((rc = encode_2d(&tm_d, d_type, d_base, p.n, d_rows, d_pitch_bytes, lay.store_cols(), 128, d_swizzle, nb, bs_d)) != DG_OK) return rc;
+        if ((rc = encode_2d(&tm_d_full, d_type, d_base, p.n, d_rows, d_pitch_bytes, lay.group_cols(), 128,
+                            lay.group_bytes() == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, nb, bs_d)) != DG_OK)
+            return rc;
+    }
 
     GemmParams params;
     params.grouped_layout = a->grouped_layout;

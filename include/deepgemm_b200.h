@@ -250,6 +250,8 @@ typedef struct dg_gemm_config {
     int32_t kb_per_split;      /* K-blocks (128 of K) per slice */
     int32_t split_in_cluster;  /* 1: the slices of a tile are the CTAs of one thread-block cluster, whose first CTA adds the
                                   others' accumulators from their shared memory (no workspace, no second kernel) */
+    int32_t swap_ab;           /* 1: dense GEMM with few rows run with the operands' roles exchanged: block_m counts rows of the
+                                  caller's B, block_n is the caller's M rounded up to 16, and the epilogue writes D transposed */
 } dg_gemm_config_t;
 
 /* get_best_config<SM100ArchSpec> (heuristics/common.hpp:17-56, sm100.hpp:30-301).  Host only. */

@@ -118,7 +118,12 @@ def test_heuristics_invariants(fp32):
         assert cfg["tmem_cols"] in (32, 64, 128, 256, 512) and 2 * cfg["block_n"] + cfg["block_m"] // 32 + 4 * ((cfg["block_n"] + 127) // 128) <= cfg["tmem_cols"]
         assert 2 <= cfg["num_stages"] <= 32
         assert 1 <= cfg["num_ctas"] <= 148
-        assert cfg["num_tiles"] == -(-m // cfg["block_m"]) * -(-n // cfg["block_n"]) * cfg["num_splits"]
+        rows, cols = (n, m) if cfg["swap_ab"] else (m, n)        # operands swapped: the kernel's rows are the caller's N
+        if cfg["swap_ab"]:
+            # few rows only; one tile column as wide as the caller's M; K slices, if any, inside a cluster
+            assert m <= 64 and cfg["block_m"] == 128 and cfg["block_n"] == -(-m // 16) * 16 and cfg["cluster_size"] == 1
+            assert cfg["num_splits"] == 1 or cfg["split_in_cluster"]
+        assert cfg["num_tiles"] == -(-rows // cfg["block_m"]) * -(-cols // cfg["block_n"]) * cfg["num_splits"]
         kb = -(-k // 128)
         if cfg["num_splits"] > 1:
             # slices start on a packed scale word (4 K-blocks), cover K exactly once, and none is empty
@@ -135,6 +140,20 @@ def test_heuristics_invariants(fp32):
     for kind, groups in ((1, 32), (2, 16)):
         cfg = dg.get_gemm_config(kind, 256 if kind == 2 else 32 * 1024, 4096, 7168, num_groups=groups, expected_m=64)
         assert cfg["smem_bytes"] <= 232448 and cfg["num_ctas"] <= 148
+
+
+def test_operand_swap_can_be_forced_and_forbidden(monkeypatch):
+    """DG_FORCE_SWAP_AB: 1 = swap whenever the form applies (dense K-major FP8, M <= 64, no accumulation), -1 = never."""
+    monkeypatch.setenv("DG_FORCE_SWAP_AB", "1")
+    assert dg.get_gemm_config(0, 16, 4096, 7168)["swap_ab"] == 1
+    assert dg.get_gemm_config(0, 65, 4096, 7168)["swap_ab"] == 0            # too many rows
+    assert dg.get_gemm_config(0, 16, 4096, 7168, b_is_fp4=True, gran_k_b=32)["swap_ab"] == 0
+    assert dg.get_gemm_config(1, 4096, 4096, 7168, num_groups=4)["swap_ab"] == 0
+    monkeypatch.setenv("DG_FORCE_SWAP_AB", "-1")
+    assert dg.get_gemm_config(0, 16, 4096, 7168)["swap_ab"] == 0
+    monkeypatch.delenv("DG_FORCE_SWAP_AB")
+    assert dg.get_gemm_config(0, 16, 4096, 7168)["swap_ab"] == 1            # chosen by cost up to 32 rows
+    assert dg.get_gemm_config(0, 64, 4096, 7168)["swap_ab"] == 0            # on request only beyond
 
 
 def test_split_reduction_mode_can_be_forced(monkeypatch):

@@ -218,6 +218,57 @@ def test_cluster_and_workspace_split_k_give_the_same_bits(m, n, k, block_n, spli
     assert oracle.calc_diff(outs["1"].float().cpu().numpy(), ref) < 1e-5
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 2112, 7168), (5, 576, 7168), (16, 4096, 2048), (33, 1000, 512), (64, 2112, 7168), (48, 264, 1152),
+                                   (64, 7168, 16384), (8, 128, 128), (17, 24576, 1536)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float])
+def test_few_row_gemms_with_the_operands_swapped(m, n, k, out_dtype, monkeypatch):
+    """For M <= 64 the weight can be the 128-row operand and the activations the tile's columns; the kernel then writes its
+    tile transposed.  Same products, same slicing rules: the result must match the oracle and the direct form."""
+    qa, sfa, qb, sfb, _ = quantise_dense(seeded_bf16((m, k), 211), seeded_bf16((n, k), 212))
+    ref = oracle.dequant_gemm_nt(qa, sfa, qb, sfb, alpha=0.75)
+    outs = {}
+    for mode in ("1", "-1"):
+        monkeypatch.setenv("DG_FORCE_SWAP_AB", mode)
+        cfg = dg.get_gemm_config(0, m, n, k, d_is_fp32=out_dtype == torch.float)
+        assert cfg["swap_ab"] == (mode == "1"), cfg
+        if mode == "1":
+            assert cfg["block_m"] == 128 and cfg["block_n"] == -(-m // 16) * 16
+        d = torch.full((m + 2, n + 8), SENTINEL, dtype=out_dtype, device="cuda")        # a wider D: the row pitch is the caller's
+        view = d[1:m + 1, :n]
+        if (view.data_ptr() % 16) != 0:
+            view = d[:m, :n]
+        dg.reset_kernel_status()
+        a = (fp8_cuda(qa), packed_sf_cuda(sfa)); b = (fp8_cuda(qb), packed_sf_cuda(sfb))
+        dg.fp8_gemm_nt(a, b, view, recipe=(1, 1, 128), alpha=0.75)
+        assert dg.kernel_status() == 0
+        out = view.float().cpu().numpy()
+        assert oracle.calc_diff(out, ref) < 1e-5, diff_report(out, ref)
+        full = d.float().cpu().numpy()
+        assert (full[:, n:] == SENTINEL).all()                       # nothing written outside the M x N block
+        outs[mode] = view.clone()
+    assert oracle.calc_diff(outs["1"].float().cpu().numpy(), outs["-1"].float().cpu().numpy()) < 1e-6
+
+
+def test_swapped_form_is_reproducible_and_graph_capturable(monkeypatch):
+    monkeypatch.setenv("DG_FORCE_SWAP_AB", "1")
+    m, n, k = 24, 4096, 7168
+    qa, sfa, qb, sfb, _ = quantise_dense(seeded_bf16((m, k), 213), seeded_bf16((n, k), 214))
+    a = (fp8_cuda(qa), packed_sf_cuda(sfa)); b = (fp8_cuda(qb), packed_sf_cuda(sfb))
+    d = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    dg.fp8_gemm_nt(a, b, d, recipe=(1, 1, 128))
+    torch.cuda.synchronize()
+    want = d.clone()
+    stream, graph = torch.cuda.Stream(), torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            dg.fp8_gemm_nt(a, b, d, recipe=(1, 1, 128))
+    for _ in range(5):
+        d.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(d.view(torch.int16), want.view(torch.int16))
+
+
 @pytest.mark.parametrize("mode", ["1", "-1"])
 def test_split_k_inside_a_cuda_graph(mode, monkeypatch):
     monkeypatch.setenv("DG_FORCE_SPLIT_CLUSTER", mode)
