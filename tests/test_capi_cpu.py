@@ -147,7 +147,7 @@ def test_operand_swap_can_be_forced_and_forbidden(monkeypatch):
     monkeypatch.setenv("DG_FORCE_SWAP_AB", "1")
     assert dg.get_gemm_config(0, 16, 4096, 7168)["swap_ab"] == 1
     assert dg.get_gemm_config(0, 65, 4096, 7168)["swap_ab"] == 0            # too many rows
-    assert dg.get_gemm_config(0, 16, 4096, 7168, b_is_fp4=True, gran_k_b=32)["swap_ab"] == 0
+    assert dg.get_gemm_config(0, 16, 4096, 7168, b_is_fp4=True, gran_k_b=32)["swap_ab"] == 1     # an FP4 weight becomes the A side
     assert dg.get_gemm_config(1, 4096, 4096, 7168, num_groups=4)["swap_ab"] == 0
     monkeypatch.setenv("DG_FORCE_SWAP_AB", "-1")
     assert dg.get_gemm_config(0, 16, 4096, 7168)["swap_ab"] == 0

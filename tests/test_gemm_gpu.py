@@ -249,6 +249,29 @@ def test_few_row_gemms_with_the_operands_swapped(m, n, k, out_dtype, monkeypatch
     assert oracle.calc_diff(outs["1"].float().cpu().numpy(), outs["-1"].float().cpu().numpy()) < 1e-6
 
 
+@pytest.mark.parametrize("a_fp4", [False, True])
+@pytest.mark.parametrize("m,n,k", [(1, 2112, 7168), (24, 4096, 2048), (64, 576, 1024)])
+def test_few_row_gemms_with_an_fp4_weight_swapped(a_fp4, m, n, k, monkeypatch):
+    """FP8 x FP4 and FP4 x FP4 decode GEMMs: swapped, the packed FP4 weight is the 128-row operand (scales per 1 x 32)."""
+    a, b = seeded_bf16((m, k), 221), seeded_bf16((n, k), 222)
+    qa, sfa = oracle.per_token_cast_to_fp4(a, True, 32) if a_fp4 else oracle.per_token_cast_to_fp8(a, True, 128)
+    qb, sfb = oracle.per_token_cast_to_fp4(b, True, 32)
+    gka = 32 if a_fp4 else 128
+    ref = oracle.dequant_gemm_nt(qa, sfa, qb, sfb, gka, 32, a_fp4, True)
+    outs = {}
+    for mode in ("1", "-1"):
+        monkeypatch.setenv("DG_FORCE_SWAP_AB", mode)
+        d = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+        dg.reset_kernel_status()
+        dg.fp8_fp4_gemm_nt((fp4_cuda(qa) if a_fp4 else fp8_cuda(qa), packed_sf_cuda(sfa)), (fp4_cuda(qb), packed_sf_cuda(sfb)), d,
+                           recipe_a=(1, gka), recipe_b=(1, 32))
+        assert dg.kernel_status() == 0
+        out = d.float().cpu().numpy()
+        assert oracle.calc_diff(out, ref) < 1e-5, diff_report(out, ref)
+        outs[mode] = out
+    assert oracle.calc_diff(outs["1"], outs["-1"]) < 1e-6
+
+
 def test_swapped_form_is_reproducible_and_graph_capturable(monkeypatch):
     monkeypatch.setenv("DG_FORCE_SWAP_AB", "1")
     m, n, k = 24, 4096, 7168
