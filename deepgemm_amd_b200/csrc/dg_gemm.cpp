@@ -262,7 +262,7 @@ Problem swapped(const Problem& p) {
 
 // Whether a dense GEMM may run with its operands swapped (DG_FORCE_SWAP_AB: 1 = whenever this holds, -1 = never)
 bool swap_allowed(const Problem& p) {
-    return p.kind == DG_GEMM_DENSE && !p.ab_bf16 && !p.a_mn_major && !p.b_mn_major && !p.accumulate &&
+    return p.kind == DG_GEMM_DENSE && !p.a_mn_major && !p.b_mn_major && !p.accumulate &&
            !p.d_fp8 && !p.stochastic && p.reduce_batches <= 1 && p.m <= 64 && p.n >= 128 && env_int("FORCE_SWAP_AB") >= 0 &&
            env_int("FORCE_CLUSTER") <= 1 && env_int("FORCE_BLOCK_M") != 256 && env_int("FORCE_BLOCK_K") != 64;
 }

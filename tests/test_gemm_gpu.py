@@ -272,6 +272,23 @@ def test_few_row_gemms_with_an_fp4_weight_swapped(a_fp4, m, n, k, monkeypatch):
     assert oracle.calc_diff(outs["1"], outs["-1"]) < 1e-6
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 2112, 7168), (16, 4096, 2048), (40, 576, 1024), (64, 7168, 512)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float])
+def test_few_row_bf16_gemms_swapped(m, n, k, out_dtype, monkeypatch):
+    a, b = seeded_bf16((m, k), 231), seeded_bf16((n, k), 232)
+    ref = a.astype(np.float64) @ b.astype(np.float64).T
+    outs = {}
+    for mode in ("1", "-1"):
+        monkeypatch.setenv("DG_FORCE_SWAP_AB", mode)
+        d = torch.full((m, n), float("nan"), dtype=out_dtype, device="cuda")
+        dg.reset_kernel_status()
+        dg.bf16_gemm_nt(_bf16_cuda(a), _bf16_cuda(b), d)
+        assert dg.kernel_status() == 0
+        outs[mode] = d.float().cpu().numpy()
+        assert oracle.calc_diff(outs[mode], ref) < (1e-5 if out_dtype == torch.bfloat16 else 1e-9)
+    assert oracle.calc_diff(outs["1"], outs["-1"]) < 1e-6
+
+
 def test_swapped_form_is_reproducible_and_graph_capturable(monkeypatch):
     monkeypatch.setenv("DG_FORCE_SWAP_AB", "1")
     m, n, k = 24, 4096, 7168
