@@ -418,7 +418,7 @@ def detail_rows(torch, dg):
         rows.append({"case": case, "us": round(t * 1e6, 1), "tflops": round(flops / t / 1e12, 1), "gbs": round(byts / t / 1e9, 0)})
 
     # config 2: dense sweep
-    for m in (64, 128, 4096):
+    for m in (16, 64, 128, 4096):                      # (16: a decode batch, beside the three row counts of config 2)
         for i, (n, k) in enumerate(DENSE_NK):
             c = make_dense_case(m, n, k, 77 + i, torch, dg)
             t = bench(lambda: dg.fp8_gemm_nt(c["a"], c["b"], c["d"], recipe=(1, 1, 128)), 3, 10)
