@@ -24,6 +24,8 @@ struct GemmLayout {
     uint32_t short_k = 0;                          // a work item has fewer K-blocks than there are stages
     uint32_t ab_elem_bytes = 1;                    // 1: FP8 / FP4 operands with block scales; 2: BF16 operands, no scales
                                                    // (block_k stays the byte width of a K-major stage row)
+    uint32_t store_buffers = 2;                    // staging buffers of D per epilogue warpgroup: 2, or 1 where the 8-16 KB
+                                                   // saved buy another pipeline stage (MN-major operands: whole 128-byte atoms)
 
     // A packed scale word covers 4 * gran_k elements of K: it is fetched on every `period`-th K-block of a work item,
     // into the next of a ring of buffers.  A buffer may be refilled once the fetch it held is no longer among the
@@ -55,7 +57,7 @@ struct GemmLayout {
     DG_HDC uint32_t group_cols() const { return group_bytes() / d_elem_bytes; }
     DG_HDC uint32_t num_groups() const { return (block_n + group_cols() - 1) / group_cols(); }
     DG_HDC uint32_t store_stage_bytes() const { return 128 * group_bytes(); }      // staging holds 128 rows of one group
-    DG_HDC uint32_t num_store_stages() const { return 2 * (block_m / 128); }       // two per epilogue warpgroup
+    DG_HDC uint32_t num_store_stages() const { return store_buffers * (block_m / 128); }
 
     DG_HDC uint32_t a_bytes() const { return block_m * block_k; }        // one byte per element (FP8, or FP4 in 16-byte containers)
     DG_HDC uint32_t load_block_n() const { return block_n / cluster; }

@@ -177,8 +177,11 @@ static_assert(!kTransposedD || (kGemmType == kDense && kCluster == 1 && kMHalves
 static_assert(kSplitCluster >= 1 && kSplitCluster <= 8, "portable cluster sizes");
 static_assert(kSplitCluster == 1 || (kGemmType == kDense && !kSplitK && kCluster == 1 && kMHalves == 1 && !kAccumulate && !kDIsFP8 && !kStochastic),
               "cluster-reduced K slicing serves the plain dense GEMM");
+#ifndef DG_STORE_BUFFERS
+#define DG_STORE_BUFFERS 2
+#endif
 constexpr GemmLayout kLayout{CTA_M, BLOCK_N, BLOCK_K, kNumStages, kDElemBytes, kCluster, kBMnMajor ? 1u : 0u, kGranKA, kGranKB,
-                             DG_SHORT_K, kABElemBytes};
+                             DG_SHORT_K, kABElemBytes, DG_STORE_BUFFERS};
 constexpr uint32_t kNumSFABuffers = kHasSF ? kLayout.sfa_buffers() : 1, kNumSFBBuffers = kHasSF ? kLayout.sfb_buffers() : 1;
 static_assert(kSFAPeriod >= 1 && kSFBPeriod >= 1 && kSFAPeriod == kLayout.sfa_period() && kSFBPeriod == kLayout.sfb_period(), "scale fetch period");
 constexpr uint32_t kBAtoms = kLayout.b_atoms();            // 128-column atoms of an MN-major B tile
@@ -667,7 +670,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
         const bool prof_thread = epi_tid == 0 && wg == 0;
         // The staging buffers are divided among the warpgroups, two each
         constexpr uint32_t kBuffersPerWG = kNumStoreStages / kMHalves;
-        static_assert(kBuffersPerWG == 2, "every epilogue warpgroup double-buffers its staging");
+        static_assert(kBuffersPerWG == 2 || kBuffersPerWG == 1, "every epilogue warpgroup has one or two staging buffers");
         const uint32_t staging = smem_base + kSmemD + wg * kBuffersPerWG * kStoreStageBytes;
         // 256-row tiles have no spare accumulator, so the next tile's MMAs wait for this one's tensor-memory reads.
         // With BF16 output a thread therefore first moves its whole accumulator row into registers (packed, BLOCK_N / 2

@@ -368,7 +368,15 @@ int choose_config_for(const Problem& p, dg_gemm_config_t* cfg, const Constraints
                                static_cast<uint32_t>(splits > 1 && !in_cluster ? 4 : d_elem), static_cast<uint32_t>(cluster),
                                p.b_mn_major ? 1u : 0u, static_cast<uint32_t>(p.gran_k_a), static_cast<uint32_t>(p.gran_k_b), 0u,
                                static_cast<uint32_t>(ab_elem)};
+                const GemmLayout unfitted = lay;
                 lay = fit_stages(lay, p.kind == DG_GEMM_K_GROUPED_CONTIGUOUS ? 0 : item_kb, max_stages);   // slices may be one K-block
+                if (lay.num_stages <= 2 && env_int("FORCE_STORE_BUFFERS") != 2) {
+                    // Two stages leave the load latency exposed: give up the second staging buffer of D if that buys a third
+                    GemmLayout single = unfitted;
+                    single.store_buffers = 1;
+                    single = fit_stages(single, p.kind == DG_GEMM_K_GROUPED_CONTIGUOUS ? 0 : item_kb, max_stages);
+                    if (single.num_stages > lay.num_stages) lay = single;
+                }
                 if (lay.num_stages == 0 || lay.tmem_cols_used() > kTmemCapacityCols) continue;
                 // A parked FP32 accumulator (128 rows x bn) has to fit the pipeline stages it overwrites
                 if (in_cluster && static_cast<uint64_t>(bn) * 128 * 4 > static_cast<uint64_t>(lay.num_stages) * (lay.a_bytes() + lay.b_bytes())) continue;
@@ -430,6 +438,7 @@ int choose_config_for(const Problem& p, dg_gemm_config_t* cfg, const Constraints
     cfg->num_ctas = best.in_cluster ? static_cast<int>(best.tiles) :
                     best.cluster * (p.kind == DG_GEMM_M_GROUPED_MASKED || p.kind == DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM
                                         ? units : static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(units, best.tiles))));
+    cfg->store_buffers = static_cast<int>(best.lay.store_buffers);
     cfg->smem_bytes = static_cast<int>(best.lay.total_bytes());
     cfg->tmem_cols = static_cast<int>(best.lay.tmem_cols_alloc());
     cfg->num_tiles = static_cast<int>(best.tiles);
@@ -473,7 +482,7 @@ GemmLayout layout_of(const Problem& p, const dg_gemm_config_t& cfg) {
                    static_cast<uint32_t>(cfg.num_stages), static_cast<uint32_t>((p.d_fp32 || split) ? 4 : (p.d_fp8 ? 1 : 2)),
                    static_cast<uint32_t>(cfg.cluster_size), p.b_mn_major ? 1u : 0u,
                    static_cast<uint32_t>(p.gran_k_a), static_cast<uint32_t>(p.gran_k_b),
-                   item_kb < cfg.num_stages ? 1u : 0u, static_cast<uint32_t>(ab_elem)};
+                   item_kb < cfg.num_stages ? 1u : 0u, static_cast<uint32_t>(ab_elem), static_cast<uint32_t>(cfg.store_buffers)};
     return lay;
 }
 
@@ -500,6 +509,7 @@ std::string generate_source(const Problem& p, const dg_gemm_config_t& cfg) {
       << "#define DG_ACCUMULATE " << (p.accumulate ? 1 : 0) << "\n"
       << "#define DG_RASTER_GROUP " << cfg.raster_group << "\n"
       << "#define DG_SPLIT_K " << (cfg.num_splits > 1 && !cfg.split_in_cluster ? 1 : 0) << "\n"
+      << "#define DG_STORE_BUFFERS " << cfg.store_buffers << "\n"
       << "#define DG_TRANSPOSED_D " << (cfg.swap_ab ? 1 : 0) << "\n"
       << "#define DG_BATCH_REDUCE " << (p.reduce_batches > 1 ? 1 : 0) << "\n"
       << "#define DG_SPLIT_CLUSTER " << (cfg.split_in_cluster ? cfg.num_splits : 1) << "\n"
@@ -580,7 +590,7 @@ struct Plan {
 
 int get_plan(const Problem& p, Plan* plan) {
     static const char* kEnvNames[] = {"FORCE_BLOCK_N", "FORCE_CLUSTER", "FORCE_SPLIT_K", "FORCE_BLOCK_M", "FORCE_BLOCK_K",
-                                      "FORCE_NUM_STAGES", "FORCE_RASTER_GROUP", "PROFILE", "FORCE_SPLIT_CLUSTER", "FORCE_SWAP_AB"};
+                                      "FORCE_NUM_STAGES", "FORCE_RASTER_GROUP", "PROFILE", "FORCE_SPLIT_CLUSTER", "FORCE_SWAP_AB", "FORCE_STORE_BUFFERS"};
     std::array<int, 32> key{};
     int i = 0;
     for (int v : {p.kind, p.m, p.n, p.k, p.groups, static_cast<int>(p.a_fp4), static_cast<int>(p.b_fp4), static_cast<int>(p.ab_bf16),
