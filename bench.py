@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--detail]
 
-A *step* is one pass over the six DeepSeek-V3-shaped dense FP8 GEMMs with M = 4096 that BASELINE.json's
+A *step* is one pass over the six DeepSeek-V3-shaped dense FP8 GEMMs with M = 4096 that the benchmark specification's
 metric is quoted on (its config 2): D[M,N] = A[M,K] @ B[N,K]^T, A quantised per token per 128 of K, B per
 128 x 128 block, UE8M0 scales pre-packed, BF16 output, synthetic N(0,1) data.  `value` is the aggregate
 TFLOP/s (2 M N K over the six shapes / device time) with operands resident in HBM; `e2e` is the same pass
@@ -400,7 +400,7 @@ def make_grouped_b(groups, n, k, fp4, torch, dg):
 
 
 def detail_rows(torch, dg):
-    """Per-case kernel times (torch profiler records, 256 MB L2 flush before every call) for BASELINE configs 2-5.  TFLOP/s counts valid
+    """Per-case kernel times (torch profiler records, 256 MB L2 flush before every call) for benchmark configurations 2-5.  TFLOP/s counts valid
     rows only and GB/s the bytes of A, B, D and scales, as the reference's tests print them
     (tests/test_fp8_fp4.py:108-111,170-174,229-237)."""
     import random

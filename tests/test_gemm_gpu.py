@@ -15,7 +15,7 @@ pytestmark = pytest.mark.gpu
 
 dg = pytest.importorskip("deepgemm_amd_b200")
 
-MAX_DIFF = 1e-3          # BASELINE criterion against the dequantised reference; measured values are ~1.4e-6
+MAX_DIFF = 1e-3          # the benchmark's criterion against the dequantised reference; measured values are ~1.4e-6
 
 
 def _run_dense(qa, sfa_rows, qb, sfb_rows, b_fp4=False, gran_k_a=128, gran_k_b=128, out_dtype=torch.bfloat16, c=None, alpha=None):
@@ -35,7 +35,7 @@ def _run_dense(qa, sfa_rows, qb, sfb_rows, b_fp4=False, gran_k_a=128, gran_k_b=1
     (128, 128, 640),            # K tail inside the second packed word
     (1, 128, 128), (129, 256, 256),     # M tails
     (200, 304, 640), (64, 2112, 1024),  # N tails, multi-tile
-    (128, 2112, 7168),          # BASELINE config 1
+    (128, 2112, 7168),          # benchmark configuration 1
     (4096, 576, 7168 // 4),
 ])
 def test_dense_fp8_matches_oracle(m, n, k):
