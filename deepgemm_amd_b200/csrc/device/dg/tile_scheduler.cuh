@@ -166,6 +166,13 @@ struct TileScheduler {
                 uint32_t end = e < 0 ? 0u : (static_cast<uint32_t>(e) > shape_m ? shape_m : static_cast<uint32_t>(e));
                 if (end < group_start) end = group_start;
                 rows = end - group_start;
+                // With the padding written too, the tiles cover the group up to its aligned end (the alignment may exceed
+                // a tile: rows past the last real one are products of the zero rows the layout requires there)
+                if (write_padding) {
+                    const uint32_t aligned_end = (end + group_alignment - 1) / group_alignment * group_alignment;
+                    const uint32_t cap = aligned_end > shape_m ? shape_m : aligned_end;
+                    rows = cap > group_start ? cap - group_start : 0u;
+                }
                 mb = (rows + kBlockM - 1) / kBlockM;
                 if (tile_id < group_first_tile + mb * num_n_blocks) break;
                 group_first_tile += mb * num_n_blocks;
@@ -176,8 +183,7 @@ struct TileScheduler {
             t.group = t.group1 = cur_group;
             t.a_row_base = t.d_row_base = t.sfa_mn_base = group_start;
             t.sfa_group = 0;
-            const uint32_t writable = write_padding ? (rows + group_alignment - 1) / group_alignment * group_alignment : rows;
-            const uint32_t left = writable - t.m_block * kBlockM;
+            const uint32_t left = rows - t.m_block * kBlockM;            // (rows already reach the aligned end when the padding is written)
             t.valid_rows = left < kBlockM ? left : kBlockM;
             t.split = 0;
             t.mn_index = tile_id;

@@ -575,7 +575,7 @@ def test_m_grouped_contiguous(alignment, cluster, block_m, b_fp4, monkeypatch):
         dg.set_mk_alignment_for_contiguous_layout(128)
 
 
-@pytest.mark.parametrize("alignment,block_m", [(128, 128), (128, 256), (256, 256)])
+@pytest.mark.parametrize("alignment,block_m", [(128, 128), (128, 256), (256, 256), (256, 128), (512, 128)])
 @pytest.mark.parametrize("zero_padding", [False, True])
 @pytest.mark.parametrize("fp32_scales", [False, True])
 def test_m_grouped_contiguous_with_prefix_sum_layout(alignment, block_m, zero_padding, fp32_scales, monkeypatch):
