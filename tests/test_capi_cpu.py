@@ -156,6 +156,16 @@ def test_operand_swap_can_be_forced_and_forbidden(monkeypatch):
     assert dg.get_gemm_config(0, 64, 4096, 7168)["swap_ab"] == 0            # on request only beyond
 
 
+def test_second_staging_buffer_is_given_up_only_for_a_third_stage():
+    """MN-major operands are staged as whole 128-byte atoms (a 240-column B tile takes 32 KB), so 256 x 240 tiles fit two
+    stages beside two D staging buffers per epilogue warpgroup and three beside one; K-major tiles fit three either way."""
+    cfg = GemmConfig()
+    _lib.check(lib.dg_get_gemm_config(0, C.byref(_args(m=4096, n=4096, k=7168, lda=7168, ldb=7168, ldd=4096)), C.byref(cfg)))
+    assert (cfg.block_m, cfg.num_stages, cfg.store_buffers) == (256, 3, 2)
+    _lib.check(lib.dg_get_gemm_config(0, C.byref(_args(m=4096, n=4096, k=7168, lda=7168, ldb=4096, ldd=4096, major_b=_lib.DG_MAJOR_MN)), C.byref(cfg)))
+    assert (cfg.block_m, cfg.num_stages, cfg.store_buffers) == (256, 3, 1) and cfg.smem_bytes <= 232448
+
+
 def test_split_reduction_mode_can_be_forced(monkeypatch):
     """DG_FORCE_SPLIT_CLUSTER: 1 = slices reduced inside a cluster, -1 = through the workspace and a second kernel."""
     m, n, k = 128, 2112, 7168
