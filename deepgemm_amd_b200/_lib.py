@@ -89,6 +89,7 @@ SIGNATURES = {
                                 C.POINTER(C.c_void_p)]),
     "dg_kernel_status": (C.c_int, []),
     "dg_reset_kernel_status": (C.c_int, []),
+    "dg_selftest_bounded_wait": (C.c_int, [C.c_uint32, C.c_void_p, C.POINTER(C.c_uint64)]),
 }
 
 

@@ -1102,3 +1102,13 @@ def kernel_status() -> int:
 
 def reset_kernel_status() -> None:
     lib.dg_reset_kernel_status()
+
+
+def selftest_bounded_wait(timeout_us: int = 1000):
+    """Runs the library's bounded-wait self-test (``dg_selftest_bounded_wait``) on the current stream: a tiny kernel waits
+    on a barrier nobody arrives at with the limit lowered to ``timeout_us``, gives up and returns normally.  Returns
+    (status word, ns the timed-out thread waited, ns the second thread waited before it saw the abort flag).  The status
+    word stays set: clear it with ``reset_kernel_status()``."""
+    elapsed = (C.c_uint64 * 2)()
+    check(lib.dg_selftest_bounded_wait(int(timeout_us), _stream(), elapsed))
+    return lib.dg_kernel_status() & 0xFFFFFFFF, int(elapsed[0]), int(elapsed[1])

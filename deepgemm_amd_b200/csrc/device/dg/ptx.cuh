@@ -90,7 +90,12 @@ __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* p) {
 // ------------------------------------------------------------------------------------------
 // Error reporting: first failure wins.  Code layout: [31:24] role, [23:16] site, [15:0] blockIdx.
 // ------------------------------------------------------------------------------------------
-constexpr uint64_t kWaitTimeoutNs = 1500ull * 1000 * 1000;   // 1.5 s; legitimate waits are < 10 ms
+// 1.5 s; legitimate waits are < 10 ms.  A translation unit may define DG_WAIT_TIMEOUT_NS before including this file
+// (the library's self-test of the expiry path does, with a limit of about a millisecond).
+#ifndef DG_WAIT_TIMEOUT_NS
+#define DG_WAIT_TIMEOUT_NS 1500000000ull
+#endif
+constexpr uint64_t kWaitTimeoutNs = DG_WAIT_TIMEOUT_NS;
 
 struct AbortCtx {
     volatile uint32_t* flag;   // shared memory word, non-zero once any role of this CTA gave up

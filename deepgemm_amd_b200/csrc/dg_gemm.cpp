@@ -593,16 +593,20 @@ struct Plan {
 int get_plan(const Problem& p, Plan* plan) {
     static const char* kEnvNames[] = {"FORCE_BLOCK_N", "FORCE_CLUSTER", "FORCE_SPLIT_K", "FORCE_BLOCK_M", "FORCE_BLOCK_K",
                                       "FORCE_NUM_STAGES", "FORCE_RASTER_GROUP", "PROFILE", "FORCE_SPLIT_CLUSTER", "FORCE_SWAP_AB", "FORCE_STORE_BUFFERS"};
-    std::array<int, 32> key{};
-    int i = 0;
-    for (int v : {p.kind, p.m, p.n, p.k, p.groups, static_cast<int>(p.a_fp4), static_cast<int>(p.b_fp4), static_cast<int>(p.ab_bf16),
-                  static_cast<int>(p.d_fp32), static_cast<int>(p.d_fp8), static_cast<int>(p.accumulate), static_cast<int>(p.a_mn_major),
-                  static_cast<int>(p.b_mn_major), p.gran_k_a, p.gran_k_b, p.expected_m, static_cast<int>(p.write_padding),
-                  static_cast<int>(p.k_psum), static_cast<int>(p.stochastic), p.reduce_batches > 1 ? 1 : 0, dg_get_num_sms(), state().mk_alignment})
-        key[i++] = v;
+    const int fields[] = {p.kind, p.m, p.n, p.k, p.groups, static_cast<int>(p.a_fp4), static_cast<int>(p.b_fp4), static_cast<int>(p.ab_bf16),
+                          static_cast<int>(p.d_fp32), static_cast<int>(p.d_fp8), static_cast<int>(p.accumulate), static_cast<int>(p.a_mn_major),
+                          static_cast<int>(p.b_mn_major), p.gran_k_a, p.gran_k_b, p.expected_m, static_cast<int>(p.write_padding),
+                          static_cast<int>(p.k_psum), static_cast<int>(p.stochastic), p.reduce_batches > 1 ? 1 : 0, dg_get_num_sms(), state().mk_alignment};
+    // The key is sized from what goes into it: every field of the descriptor and every setting the choice reads
+    constexpr size_t kNumFields = sizeof(fields) / sizeof(fields[0]), kNumEnv = sizeof(kEnvNames) / sizeof(kEnvNames[0]);
+    using PlanKey = std::array<int, kNumFields + kNumEnv>;
+    PlanKey key{};
+    size_t i = 0;
+    for (int v : fields) key[i++] = v;
     for (const char* name : kEnvNames) key[i++] = env_int(name);
+    static_assert(std::tuple_size<PlanKey>::value == kNumFields + kNumEnv, "one slot per field and setting");
     static std::mutex mu;
-    static std::map<std::array<int, 32>, Plan> plans;
+    static std::map<PlanKey, Plan> plans;
     {
         std::lock_guard<std::mutex> lock(mu);
         auto it = plans.find(key);
@@ -673,8 +677,8 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
         p = swapped(p);
     }
     if (env_int("PRINT_CONFIGS"))
-        fprintf(stderr, "[dg] kind %d m %d n %d k %d groups %d -> block_m %d block_n %d block_k %d cluster %d stages %d ctas %d smem %d tiles %d splits %d x %d%s\n",
-                kind, p.m, p.n, p.k, p.groups, cfg.block_m, cfg.block_n, cfg.block_k, cfg.cluster_size, cfg.num_stages, cfg.num_ctas, cfg.smem_bytes, cfg.num_tiles,
+        fprintf(stderr, "[dg] kind %d m %d n %d k %d groups %d -> block_m %d block_n %d block_k %d cluster %d stages %d store_buffers %d ctas %d smem %d tiles %d splits %d x %d%s\n",
+                kind, p.m, p.n, p.k, p.groups, cfg.block_m, cfg.block_n, cfg.block_k, cfg.cluster_size, cfg.num_stages, cfg.store_buffers, cfg.num_ctas, cfg.smem_bytes, cfg.num_tiles,
                 cfg.num_splits, cfg.kb_per_split, cfg.split_in_cluster ? " (in a cluster)" : "");
     if (fixed_scratch == nullptr && (rc = ensure_status_word()) != DG_OK) return rc;
 
@@ -788,8 +792,9 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
     params.sfd_pitch = static_cast<uint32_t>(a->sfd_pitch);
     params.kb_per_batch = static_cast<uint32_t>(k_inner * ab_elem / cfg.block_k);
     void* kargs[7] = {&tm_a, &tm_b, &tm_sfa, &tm_sfb, &tm_d, &tm_d_full, &params};
-    if (env_int("PROFILE")) {
-        // synchronous, printing path for tuning only
+    if (env_int("PROFILE") && fixed_scratch == nullptr) {
+        // synchronous, printing path for tuning only (it allocates its counters and waits for the stream, so the entry
+        // point that must not allocate runs the kernel without counters instead)
         params.profile = profile_buffer();
         if (params.profile == nullptr) return fail(DG_ERR_CUDA, "cannot allocate the profile buffer");
         DG_CUDA_RT(cudaMemsetAsync(params.profile, 0, 32 * sizeof(unsigned long long), static_cast<cudaStream_t>(a->stream)));

@@ -161,4 +161,54 @@ int dg_reset_kernel_status(void) {
     return DG_OK;
 }
 
+// Runs the expiry path of the kernels' bounded waits on purpose: a one-CTA kernel built from the same ptx.cuh as the
+// GEMM, with the limit lowered to `timeout_us`, in which one thread waits on an mbarrier that nobody arrives at while a
+// second thread waits on another such barrier and must leave as soon as the first has given up (the CTA-wide abort
+// flag).  The kernel returns normally; the status word then holds the first thread's code (role 7, site 3) and
+// `elapsed_ns`, if given, how long that thread waited.  Synchronises the stream.
+int dg_selftest_bounded_wait(uint32_t timeout_us, void* stream, uint64_t* elapsed_ns) {
+    DG_REQUIRE_ALIVE();
+    DG_REQUIRE(timeout_us >= 100 && timeout_us <= 1000000);
+    int rc = DG_OK;
+    const std::string src =
+        "#define DG_WAIT_TIMEOUT_NS " + std::to_string(static_cast<unsigned long long>(timeout_us) * 1000ull) + "ull\n"
+        "#include <dg/ptx.cuh>\n"
+        "extern \"C\" __global__ void __launch_bounds__(64, 1) dg_selftest_bounded_wait_kernel(int* status, unsigned long long* out) {\n"
+        "    using namespace dg;\n"
+        "    __shared__ __align__(8) unsigned long long bars[2];\n"
+        "    __shared__ uint32_t flag;\n"
+        "    if (threadIdx.x == 0) { flag = 0; mbar_init(smem_u32(&bars[0]), 1); mbar_init(smem_u32(&bars[1]), 1); fence_mbar_init(); }\n"
+        "    __syncthreads();\n"
+        "    const AbortCtx ctx{&flag, status};\n"
+        "    if (threadIdx.x == 0) {\n"
+        "        const uint64_t t0 = global_timer_ns();\n"
+        "        const bool ok = mbar_wait(smem_u32(&bars[0]), 0, ctx, 7, 3);      // nobody arrives: runs out\n"
+        "        out[0] = global_timer_ns() - t0;\n"
+        "        out[1] = ok ? 1 : 0;\n"
+        "    } else if (threadIdx.x == 32) {\n"
+        "        const uint64_t t0 = global_timer_ns();\n"
+        "        const bool ok = mbar_wait(smem_u32(&bars[1]), 0, ctx, 7, 4);      // leaves when the flag is raised\n"
+        "        out[2] = global_timer_ns() - t0;\n"
+        "        out[3] = ok ? 1 : 0;\n"
+        "    }\n"
+        "    __syncthreads();\n"
+        "}\n";
+    dg_kernel_t kernel = nullptr;
+    if ((rc = dg_jit_compile("selftest_bounded_wait", "dg_selftest_bounded_wait_kernel", src.c_str(), "", &kernel)) != DG_OK) return rc;
+    if ((rc = ensure_status_word()) != DG_OK) return rc;
+    // words 2..5 of the host-mapped status block receive the kernel's four results
+    unsigned long long* out_host = reinterpret_cast<unsigned long long*>(state().status_host + 2);
+    unsigned long long* out_dev = reinterpret_cast<unsigned long long*>(state().status_device + 2);
+    for (int i = 0; i < 4; ++i) out_host[i] = ~0ull;
+    int* status_dev = state().status_device;
+    void* kargs[2] = {&status_dev, &out_dev};
+    if ((rc = dg_jit_launch(kernel, 1, 64, 1, 0, 0, stream, kargs)) != DG_OK) return rc;
+    DG_CUDA_RT(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    const volatile unsigned long long* res = out_host;
+    if (res[1] != 0 || res[3] != 0)
+        return fail(DG_ERR_CUDA, "bounded-wait self-test: a wait on a barrier nobody arrives at reported success (%llu, %llu)", res[1], res[3]);
+    if (elapsed_ns != nullptr) { elapsed_ns[0] = res[0]; elapsed_ns[1] = res[2]; }
+    return DG_OK;
+}
+
 }  // extern "C"

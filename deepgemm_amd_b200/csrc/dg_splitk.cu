@@ -76,12 +76,13 @@ int launch_splitk_reduce(const float* ws, void* d, int m, int n, int64_t ld_ws, 
 // ---------------------------------------------------------------------------------------------------------------
 // Dense GEMM for callers that must not allocate
 // ---------------------------------------------------------------------------------------------------------------
-// Some callers run where device allocation is off the table: inside a CUDA stream capture, on a real-time serving
-// thread that may not take the allocator's locks, under a memory budget that was handed out in full at start-up, or
-// in a process that has forbidden cudaMalloc after initialisation so that its footprint stays fixed.  The sliced (split-K) dense
+// Some callers run where device allocation at call time is off the table: a real-time serving thread that may not take
+// the allocator's locks, a process that handed out its whole memory budget at start-up and forbids cudaMalloc afterwards
+// so that its footprint stays fixed, a host application that owns all device memory itself.  The sliced (split-K) dense
 // GEMM normally parks its FP32 partial panels in a library-owned buffer that grows on demand; for those callers the
 // panels go into this fixed array instead.  It is part of the library image: every GPU that loads the library holds
-// these 16 MiB until the process exits.
+// these 16 MiB until the process exits.  One array per device, shared by all calls of the entry point below on that
+// device (calls that overlap on the GPU race on it); dg_fp8_fp4_gemm never touches it.
 constexpr size_t kFixedScratchBytes = 16u << 20;
 static __device__ __align__(256) float g_fixed_splitk_scratch[kFixedScratchBytes / sizeof(float)];
 

@@ -217,17 +217,21 @@ DG_API int dg_k_grouped_fp8_gemm_contiguous(const dg_gemm_args_t* args);
  * scale tensor of D viewed as [m, num_groups * n]).  Rows beyond m are clipped per batch. */
 DG_API int dg_fp8_bmm(const dg_gemm_args_t* args);
 
-/* Same operation and arguments as dg_fp8_fp4_gemm, for callers that cannot allocate device memory (inside a stream
- * capture, on a thread that must not block on the allocator, or in a process that freezes its memory footprint after
- * start-up).  It has no counterpart in the reference.  The scratch of the K-sliced path (FP32 partial panels) lives in
- * a 16 MiB array inside the library image, which every GPU that loads the library keeps until exit; the call performs
- * no cudaMalloc / cudaFree / cudaHostAlloc.  A GEMM whose slicing needs more than 16 MiB of panels
- * (num_splits * align(m,128) * align(n,4) * 4 bytes) is rejected with DG_ERR_INVALID_ARGUMENT.  The first call on a
- * device looks up the array's address (and, like every entry point, the first call of a tile configuration loads its
- * kernel image): make that first call before any stream capture.  All calls share the array and it keeps the last
- * call's panels; nothing in it has to start at zero (every element that is read is written first by the same call),
- * but two calls that overlap on the GPU, from different streams or devices' peers, race on it.  Failed bounded waits
- * are reported through the status word only if another entry point has already created it. */
+/* Same operation and arguments as dg_fp8_fp4_gemm, for callers that cannot allocate device memory at call time: a
+ * serving thread that must never block on the allocator's locks, a process that hands out its whole memory budget at
+ * start-up and forbids cudaMalloc afterwards, a plugin host that owns all device memory itself.  It has no counterpart
+ * in the reference.  The scratch of the K-sliced path (FP32 partial panels) lives in a 16 MiB array inside the library
+ * image, which every GPU that loads the library keeps until exit; the call performs no cudaMalloc / cudaFree /
+ * cudaHostAlloc and calls no allocating library routine (with DG_PROFILE set it runs without the tuning counters, which
+ * would need a buffer).  A GEMM whose slicing needs more than 16 MiB of panels (num_splits * align(m,128) *
+ * align(n,4) * 4 bytes) is rejected with DG_ERR_INVALID_ARGUMENT and nothing is launched.  The first call on a device
+ * looks up the array's device address (and, like every entry point, the first call of a tile configuration loads its
+ * kernel image): make that first call before any stream capture.  There is one array per device, shared by every call
+ * of this entry point on that device, and it keeps the last call's panels; nothing in it has to start at zero (every
+ * element that is read is written first by the same call), but two calls of this entry point that overlap on one GPU
+ * (from two streams) race on it.  Calls of dg_fp8_fp4_gemm use a different, library-owned buffer, so mixing the two
+ * entry points does not race.  Failed bounded waits are reported through the status word only if another entry point
+ * has already created it. */
 DG_API int dg_fp8_fp4_gemm_noalloc(const dg_gemm_args_t* args);
 
 /* Compile (but do not load or launch) the kernel the call above would use, so that a later call
@@ -291,6 +295,13 @@ DG_API int dg_jit_launch(dg_kernel_t kernel, uint32_t grid_x, uint32_t block_x, 
  * unwinds.  Returns the word (0 = no failure) WITHOUT synchronising: call after the stream is idle. */
 DG_API int dg_kernel_status(void);
 DG_API int dg_reset_kernel_status(void);
+/* Exercises the expiry path without a fault: a one-CTA kernel built from the kernels' own wait primitive, with the
+ * limit lowered to timeout_us (100 .. 1e6), waits on a barrier nobody arrives at, gives up, records its code
+ * (role 7, site 3, CTA 0 -> 0x87030000) in the status word and returns normally; a second waiter of the CTA must leave
+ * through the abort flag without reporting.  elapsed_ns (optional, two words) receives how long each waited.
+ * Synchronises `stream`.  The reference's only bounded wait traps after 60 s instead
+ * (deep_gemm/include/deep_gemm/comm/barrier.cuh:11-24). */
+DG_API int dg_selftest_bounded_wait(uint32_t timeout_us, void* stream, uint64_t* elapsed_ns);
 
 #ifdef __cplusplus
 }

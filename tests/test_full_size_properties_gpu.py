@@ -1,6 +1,7 @@
-"""Parity at the full sizes of the benchmark configurations, where the numpy oracle would take hours: the kernels are held
-to properties that do not depend on the size, and to a BF16 tensor-core matmul of the dequantised operands (an FP8 or FP4
-value times a power of two is exact in BF16, so that product differs from ours only in the order of the FP32 sums).
+"""Size-independent properties of the kernels at the full sizes of the benchmark configurations, over every row of
+every expert (the comparison with the CPU oracle itself, on oracle-quantised operands, is test_full_size_oracle_gpu.py).
+The yardstick here is a BF16 tensor-core matmul of the dequantised operands (an FP8 or FP4 value times a power of two is
+exact in BF16, so that product differs from ours only in the order of the FP32 sums):
 
   * calc_diff < 1e-3 against the dequantise-then-matmul value (the criterion of tests/test_fp8_fp4.py:54-57);
   * scaling every scale of A by 2^3 (adding 3 to the UE8M0 exponents) multiplies D by 8 exactly: bit-for-bit in BF16;

@@ -1300,3 +1300,35 @@ def test_api_rejects_what_the_reference_rejects():
     empty_sf = torch.empty((m, 0), dtype=torch.int, device="cuda")
     dg.fp8_gemm_nt((a[0][:, :0], empty_sf), (b[0][:, :0], torch.empty((n, 0), dtype=torch.int, device="cuda")), dz, recipe=(1, 1, 128))
     assert (dz == 0).all()
+
+
+def test_every_setting_that_shapes_the_kernel_is_part_of_the_plan_key(monkeypatch, capfd):
+    """The library remembers the chosen configuration and kernel per problem descriptor *and* settings.  A setting left
+    out of that key would hand back the plan chosen under its old value: toggling the one added last
+    (DG_FORCE_STORE_BUFFERS) between two calls of one shape must change what DG_PRINT_CONFIGS reports for the call."""
+    m, n, k = 1024, 4096, 2048
+    qa, sfa, qb, sfb_rows, sfb_raw = quantise_dense(seeded_bf16((m, k), 90), seeded_bf16((n, k), 91))
+    a = (fp8_cuda(qa), torch.from_numpy(sfa).cuda())
+    b = (fp8_cuda(qb.T.copy()), torch.from_numpy(sfb_raw).cuda().T)          # B stored [K, N]: wide MN-major stages
+    monkeypatch.setenv("DG_PRINT_CONFIGS", "1")
+    seen, outs = [], []
+    for forced in (None, "2", None):
+        if forced is None:
+            monkeypatch.delenv("DG_FORCE_STORE_BUFFERS", raising=False)
+        else:
+            monkeypatch.setenv("DG_FORCE_STORE_BUFFERS", forced)
+        d = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+        capfd.readouterr()
+        dg.fp8_fp4_gemm_nn(a, b, d)
+        torch.cuda.synchronize()
+        lines = [ln for ln in capfd.readouterr().err.splitlines() if "store_buffers" in ln]
+        assert lines, "DG_PRINT_CONFIGS printed no configuration"
+        seen.append(int(lines[-1].split("store_buffers")[1].split()[0]))
+        outs.append(d)
+    assert dg.kernel_status() == 0
+    assert seen[0] == seen[2]
+    if seen[0] == 2:
+        pytest.skip("the heuristics keep two staging buffers for this shape: the setting changes nothing here")
+    assert seen == [1, 2, 1], seen
+    assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))      # same arithmetic either way
+    assert oracle.calc_diff(outs[0].float().cpu().numpy(), oracle.dequant_gemm_nt(qa, sfa, qb, sfb_rows)) < 1e-3

@@ -1,8 +1,8 @@
 """The allocation-free dense GEMM entry point (dg_fp8_fp4_gemm_noalloc), called through the C ABI.
 
-Who needs it: code that is not allowed to allocate device memory when it calls the GEMM -- a call recorded inside a
-CUDA stream capture, a latency-critical serving thread that must never wait on the allocator, or a process that
-hands out its whole memory budget at start-up and forbids cudaMalloc afterwards.  The K-sliced GEMM path keeps its
+Who needs it: code that is not allowed to allocate device memory when it calls the GEMM -- a latency-critical serving
+thread that must never wait on the allocator, a process that hands out its whole memory budget at start-up and forbids
+cudaMalloc afterwards, or a host application that owns all device memory itself.  The K-sliced GEMM path keeps its
 FP32 partial panels in a fixed 16 MiB array inside the library image for these callers.  This file is collected last
 on purpose, so that a run stopping at the first failure has already run every other test.
 """
@@ -84,3 +84,37 @@ def test_noalloc_entry_point_rejects_a_problem_beyond_its_fixed_scratch(monkeypa
     _lib.check(_lib.lib.dg_fp8_fp4_gemm_noalloc(C.byref(args2)))
     torch.cuda.synchronize()
     assert torch.equal(d2.view(torch.int16), d.view(torch.int16))
+
+
+def test_noalloc_entry_point_really_keeps_its_panels_in_the_fixed_array(monkeypatch):
+    """The default slicings above are reduced inside a thread-block cluster and never touch the array.  Here the slices
+    are forced through the workspace form, so the FP32 panels of the GEMM land in the library's fixed array and the
+    second kernel reads them from there.  Two calls in a row with a different shape in between (whose panels overwrite
+    the first shape's) must both give the bits of the allocating entry point, and the second call must leave the
+    device's free memory as it found it."""
+    monkeypatch.setenv("DG_FORCE_SPLIT_CLUSTER", "-1")
+    monkeypatch.setenv("DG_FORCE_SPLIT_K", "4")
+    shapes = [(128, 2112, 7168), (96, 1000, 4096), (128, 2112, 7168)]
+    cases = {}
+    for m, n, k in set(shapes):
+        cfg = dg.get_gemm_config(0, m, n, k)
+        assert cfg["num_splits"] > 1 and cfg["split_in_cluster"] == 0, cfg
+        assert cfg["num_splits"] * (-(-m // 128) * 128) * (-(-n // 4) * 4) * 4 <= FIXED_SCRATCH_BYTES
+        qa, sfa, qb, sfb, _ = quantise_dense(seeded_bf16((m, k), 64 + m), seeded_bf16((n, k), 65 + n))
+        want = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+        args, keep = _args(qa, sfa, qb, sfb, want)
+        _lib.check(_lib.lib.dg_fp8_fp4_gemm(C.byref(args)))          # the allocating entry point, same slicing
+        torch.cuda.synchronize()
+        assert oracle.calc_diff(want.float().cpu().numpy(), oracle.dequant_gemm_nt(qa, sfa, qb, sfb)) < 1e-3
+        cases[(m, n, k)] = (qa, sfa, qb, sfb, want)
+    for call, shape in enumerate(shapes):
+        qa, sfa, qb, sfb, want = cases[shape]
+        got = torch.full(want.shape, float("nan"), dtype=torch.bfloat16, device="cuda")
+        args, keep = _args(qa, sfa, qb, sfb, got)
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
+        _lib.check(_lib.lib.dg_fp8_fp4_gemm_noalloc(C.byref(args)))
+        torch.cuda.synchronize()
+        if call > 0:                                                  # (the first call may load the kernel image)
+            assert torch.cuda.mem_get_info()[0] == free_before, call
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16)), (call, shape)
