@@ -186,6 +186,9 @@ int dg_selftest_bounded_wait(uint32_t timeout_us, void* stream, uint64_t* elapse
         "        out[0] = global_timer_ns() - t0;\n"
         "        out[1] = ok ? 1 : 0;\n"
         "    } else if (threadIdx.x == 32) {\n"
+        "        // starts half a limit later, so that its own limit cannot run out before the first waiter's does\n"
+        "        const uint64_t t_delay = global_timer_ns();\n"
+        "        while (global_timer_ns() - t_delay < DG_WAIT_TIMEOUT_NS / 2) { }\n"
         "        const uint64_t t0 = global_timer_ns();\n"
         "        const bool ok = mbar_wait(smem_u32(&bars[1]), 0, ctx, 7, 4);      // leaves when the flag is raised\n"
         "        out[2] = global_timer_ns() - t0;\n"

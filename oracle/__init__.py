@@ -28,3 +28,4 @@ from .gemm import (  # noqa: F401
     make_contiguous_layout, count_bytes, make_psum_layout, m_grouped_psum_ref,
     k_grouped_slices, k_grouped_pack_sf, k_grouped_ref,
 )
+from .parallel import host_threads, in_row_chunks, seeded_bf16_rows, quantise_dense_parallel  # noqa: F401

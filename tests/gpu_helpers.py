@@ -63,30 +63,6 @@ def diff_report(d: np.ndarray, ref: np.ndarray) -> str:
     return msg
 
 
-def in_row_chunks(fn, x: np.ndarray, rows_per_chunk: int = 512, threads: int | None = None):
-    """Applies an oracle quantiser that treats row blocks independently (`fn(chunk) -> (data, scales)`) to `x` in chunks
-    of rows on a thread pool (numpy releases the GIL inside its loops) and stacks the pieces: the same bytes as one call
-    over the whole array, in a fraction of the time at the benchmark's full sizes.  `rows_per_chunk` must be a multiple
-    of the quantiser's row granularity (128 for the 128 x 128 block cast)."""
-    import os
-    from concurrent.futures import ThreadPoolExecutor
-    if threads is None:
-        try:
-            threads = len(os.sched_getaffinity(0))
-        except AttributeError:
-            threads = os.cpu_count() or 1
-    starts = range(0, x.shape[0], rows_per_chunk)
-    with ThreadPoolExecutor(max_workers=max(1, threads)) as pool:
-        pieces = list(pool.map(lambda s: fn(x[s:s + rows_per_chunk]), starts))
-    return np.concatenate([p[0] for p in pieces]), np.concatenate([p[1] for p in pieces])
-
-
-def quantise_dense_parallel(a: np.ndarray, b: np.ndarray, b_fp4: bool = False):
-    """`quantise_dense` for large operands: the same oracle functions, applied to row chunks in parallel."""
-    qa, sfa = in_row_chunks(lambda x: oracle.per_token_cast_to_fp8(x, True, 128), a)
-    if b_fp4:
-        qb, sfb_rows = in_row_chunks(lambda x: oracle.per_token_cast_to_fp4(x, True, 32), b)
-    else:
-        qb, sfb_raw = in_row_chunks(lambda x: oracle.per_block_cast_to_fp8(x, True, 128), b, 512)
-        sfb_rows = oracle.broadcast_sf_along_mn(sfb_raw, b.shape[0], 128)
-    return qa, sfa, qb, sfb_rows
+# Chunked, threaded forms for the benchmark's full sizes (the same bytes as one call; see oracle/parallel.py)
+in_row_chunks = oracle.in_row_chunks
+quantise_dense_parallel = oracle.quantise_dense_parallel

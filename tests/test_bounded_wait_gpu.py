@@ -27,8 +27,9 @@ def test_a_wait_on_a_barrier_nobody_arrives_at_gives_up_and_reports(timeout_us):
         assert status == 0x87030000, hex(status)
         # the waiter gave up after its limit, not long after it (the limit is checked every 256 polls)
         assert timeout_us * 1000 <= waited_ns < 50 * timeout_us * 1000, waited_ns
-        # the second waiter left through the CTA's abort flag, about when the first gave up, without reporting
-        assert bystander_ns < 50 * timeout_us * 1000, bystander_ns
+        # the second waiter (which starts half a limit later) left through the CTA's abort flag about when the first gave
+        # up, i.e. before its own limit, without reporting
+        assert bystander_ns < timeout_us * 1000, bystander_ns
         assert dg.kernel_status() == 0x87030000          # first failure wins and stays until it is reset
     finally:
         dg.reset_kernel_status()

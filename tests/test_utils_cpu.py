@@ -120,3 +120,25 @@ def test_import_touches_no_cuda_context_and_shutdown_is_final():
     env = dict(os.environ, PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
     result = subprocess.run([sys.executable, "-c", child], env=env, capture_output=True, text=True, timeout=300)
     assert result.returncode == 0 and "DG_CHILD_OK" in result.stdout, result.stdout + result.stderr
+
+
+def test_chunked_parallel_oracle_quantisers_give_the_bytes_of_one_call():
+    """oracle/parallel.py applies the oracle's casts to row chunks on a thread pool; the pieces must stack to exactly what
+    one call over the whole array gives (per-token casts for any chunking, the 128 x 128 block cast for chunks of whole
+    128-row bands), and the chunk-seeded generator must not depend on the thread count."""
+    import numpy as np
+    import oracle
+    a = oracle.seeded_bf16_rows((700, 640), 5, rows_per_chunk=256)
+    assert np.array_equal(a, oracle.seeded_bf16_rows((700, 640), 5, rows_per_chunk=256, threads=1))
+    assert np.array_equal(a, oracle.bf16_round(a)) and abs(float(a.std()) - 1.0) < 0.02
+    b = oracle.seeded_bf16_rows((1000, 640), 6, rows_per_chunk=256)
+    for b_fp4 in (False, True):
+        qa, sfa, qb, sfb = oracle.quantise_dense_parallel(a, b, b_fp4=b_fp4)
+        wa, wsfa = oracle.per_token_cast_to_fp8(a, True, 128)
+        assert np.array_equal(qa, wa) and np.array_equal(sfa, wsfa)
+        if b_fp4:
+            wb, wsfb = oracle.per_token_cast_to_fp4(b, True, 32)
+        else:
+            wb, raw = oracle.per_block_cast_to_fp8(b, True, 128)
+            wsfb = oracle.broadcast_sf_along_mn(raw, b.shape[0], 128)
+        assert np.array_equal(qb, wb) and np.array_equal(sfb, wsfb)
