@@ -209,10 +209,12 @@ def make_dense_case(m, n, k, seed, torch, dg, columns=None):
     lo, hi = columns if columns is not None else (0, n)
     assert lo % 128 == 0
     qb, sfb = qb[lo:hi].contiguous(), sfb[lo // 128:-(-hi // 128)].contiguous()
+    raw = (sfa, sfb)
     sfa = dg.transform_sf_into_required_layout(sfa, m, k, (1, 128))
     sfb = dg.transform_sf_into_required_layout(sfb, hi - lo, k, (128, 128))
     d = torch.empty((m, hi - lo), device="cuda", dtype=torch.bfloat16)
-    return {"m": m, "n": hi - lo, "k": k, "full_n": n, "columns": (lo, hi), "a": (qa, sfa), "b": (qb, sfb), "d": d, "seed": seed}
+    return {"m": m, "n": hi - lo, "k": k, "full_n": n, "columns": (lo, hi), "a": (qa, sfa), "b": (qb, sfb), "d": d, "seed": seed,
+            "scales_fp32": raw}
 
 
 def flat_storage(t, torch):
@@ -245,19 +247,14 @@ def dequant_reference(case, torch):
     """Dequantise-then-matmul value of a dense case on the GPU: a BF16 tensor-core matmul of the dequantised operands
     (an FP8 value times a power of two is exact in BF16), the yardstick of shard_check."""
     from deepgemm_amd_b200.utils import cast_back_from_fp8
-    qa, sfa_packed = case["a"]
-    qb, sfb_packed = case["b"]
-    k = case["k"]
-    a_deq = cast_back_from_fp8(qa, unpack_sf(sfa_packed, -(-k // 128), torch)).bfloat16()
-    b_deq = cast_back_from_fp8(qb, unpack_sf(sfb_packed, -(-k // 128), torch)).bfloat16()
+    qa, qb = case["a"][0], case["b"][0]
+    sfa, sfb = case["scales_fp32"]                       # per token x 128 of K; per 128 x 128 block
+    n, k = qb.shape
+    a_deq = cast_back_from_fp8(qa, sfa).bfloat16()
+    rows = torch.arange(n, device=qb.device) // 128
+    cols = torch.arange(k, device=qb.device) // 128
+    b_deq = (qb.float() * sfb[rows][:, cols]).bfloat16()
     return (a_deq @ b_deq.t()).float()
-
-
-def unpack_sf(packed, sf_k, torch):
-    """Packed MN-major UE8M0 int32 [mn, ceil(sf_k / 4)] -> FP32 scales [mn, sf_k]."""
-    mn = packed.shape[0]
-    by = packed.contiguous().view(torch.uint8).view(mn, -1)[:, :sf_k]
-    return (by.to(torch.int32) << 23).view(torch.float32)
 
 
 def grouped_layout(seed=0, groups=32, expected=8192, alignment=128):
