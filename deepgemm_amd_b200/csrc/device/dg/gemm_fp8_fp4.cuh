@@ -180,6 +180,20 @@ static_assert(kSplitCluster == 1 || (kGemmType == kDense && !kSplitK && kCluster
 #ifndef DG_STORE_BUFFERS
 #define DG_STORE_BUFFERS 2
 #endif
+// The producer's and the MMA issuer's loops are walked by their whole warp (every lane polls the barriers, lane 0
+// issues the copies / the tcgen05 instructions, the warp re-converges every K-block).  A lone lane inside a divergent
+// branch ran the same loops measurably slower: 10 % of the kernel time with 128-row CTA pairs, 1-2 % with 256-row
+// tiles.  0 restores the single-lane form (kept for comparison).
+#ifndef DG_PRODUCER_WHOLE_WARP
+#define DG_PRODUCER_WHOLE_WARP 1
+#endif
+#ifndef DG_MMA_WHOLE_WARP
+#define DG_MMA_WHOLE_WARP 1
+#endif
+// Nanoseconds an epilogue warp sleeps between polls while it waits for its tile's accumulator (0 = poll continuously)
+#ifndef DG_EPILOGUE_BACKOFF_NS
+#define DG_EPILOGUE_BACKOFF_NS 0
+#endif
 constexpr GemmLayout kLayout{CTA_M, BLOCK_N, BLOCK_K, kNumStages, kDElemBytes, kCluster, kBMnMajor ? 1u : 0u, kGranKA, kGranKB,
                              DG_SHORT_K, kABElemBytes, DG_STORE_BUFFERS};
 constexpr uint32_t kNumSFABuffers = kHasSF ? kLayout.sfa_buffers() : 1, kNumSFBBuffers = kHasSF ? kLayout.sfb_buffers() : 1;
@@ -305,8 +319,8 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
     }
     if (warp_idx == 1 && lane == 0) {
         for (uint32_t s = 0; s < kNumStages; ++s) {
-            // per CTA of the cluster: the producer's arrive + the 32 lanes of the scale warp (used in CTA 0 only)
-            mbar_init(full_bar(s), kCluster * (1 + (kHasSF ? 32 : 0)));
+            // per CTA of the cluster: the producer's arrive + one arrive of the scale warp (used in CTA 0 only)
+            mbar_init(full_bar(s), kCluster * (1 + (kHasSF ? 1 : 0)));
             mbar_init(sf_full_bar(s), 1);
             mbar_init(empty_bar(s), 1);          // tcgen05.commit
         }
@@ -417,7 +431,9 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
         if constexpr (kMHalves == 2) warpgroup_reg_dec<kRoleRegs>();
         if (warp_idx == 0) {
             // ================= TMA producer (every CTA loads its own rows of A and its share of B) =================
-            if (lane == 0) {
+            // Either lane 0 alone walks the loop, or (DG_PRODUCER_WHOLE_WARP) the whole warp does and lane 0 issues the copies
+            constexpr bool kProducerWholeWarp = DG_PRODUCER_WHOLE_WARP != 0;
+            if (kProducerWholeWarp || lane == 0) {
                 bool ok = true;
                 DG_PROF_VAR(prof_wait);
                 DG_PROF_BEGIN(prof_t0);
@@ -440,6 +456,8 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                         DG_PROF_BEGIN(prof_w);
                         if (!mbar_wait(empty_bar(stage), phase ^ 1, ctx, kRoleProducer, 1)) { ok = false; break; }
                         DG_PROF_ADD(prof_wait, prof_w);
+                        if constexpr (kProducerWholeWarp) __syncwarp();
+                        if (kProducerWholeWarp && lane != 0) { advance_sf(kb); continue; }
                         if constexpr (kHasSF) {
                             uint32_t sf_bytes = 0;
                             if (kb % kSFAPeriod == 0) sf_bytes += kSFABytes;
@@ -491,12 +509,17 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                 }
                 DG_PROF_VAR(prof_total);
                 DG_PROF_ADD(prof_total, prof_t0);
-                DG_PROF_FLUSH(kProfProducerWaitEmpty, prof_wait);
-                DG_PROF_FLUSH(kProfProducerTotal, prof_total);
+                if (lane == 0) {
+                    DG_PROF_FLUSH(kProfProducerWaitEmpty, prof_wait);
+                    DG_PROF_FLUSH(kProfProducerTotal, prof_total);
+                }
             }
         } else if (warp_idx == 1) {
             // ================= MMA issuer (CTA 0 of the cluster only) =================
-            if (lane == 0 && is_leader) {
+            // Either lane 0 alone walks the loop, or (DG_MMA_WHOLE_WARP) the whole warp does and lane 0 issues
+            constexpr bool kWholeWarp = DG_MMA_WHOLE_WARP != 0;
+            const bool issue_lane = lane == 0;
+            if ((kWholeWarp || lane == 0) && is_leader) {
                 constexpr uint32_t idesc = kABIsBF16 ? make_instr_desc_bf16(kAMnMajor, kBMnMajor, UMMA_M, UMMA_N)
                                                      : make_instr_desc_block_scaled(kAIsFP4 ? kFmtE2M1 : kFmtE4M3, kBIsFP4 ? kFmtE2M1 : kFmtE4M3,
                                                                                     kAMnMajor, kBMnMajor, UMMA_M, UMMA_N);
@@ -514,8 +537,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                     if constexpr (kCluster == 1) {
                         tc_commit(bar);
                     } else {
-                        tc_commit_2cta(map_to_cta(bar, 0));
-                        tc_commit_2cta(map_to_cta(bar, 1));
+                        tc_commit_2cta_mask(bar, 0x3);          // both CTAs' barriers with one instruction
                     }
                 };
                 bool ok = true;
@@ -545,6 +567,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                         DG_PROF_ADD(prof_full, prof_w1);
                         DG_PROF_STAMP(2);                       // first stage arrived
                         tc_fence_after_sync();
+                        if (issue_lane) {
                         // Scales: shared memory (rearranged by warp 2) -> tensor memory, in every CTA of the cluster
                         DG_PROF_BEGIN(prof_i0);
                         if (kHasSF && kb % kSFAPeriod == 0) {
@@ -593,9 +616,12 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                             for (uint32_t h = 0; h < kMHalves; ++h) commit_all(tmem_full_bar(accum + h));
                         }
                         DG_PROF_ADD(prof_commit, prof_i2);
+                        }
+                        if constexpr (kWholeWarp) __syncwarp();
                         advance_sf(kb);
                     }
                 }
+                if (issue_lane) {
                 DG_PROF_VAR(prof_total);
                 DG_PROF_ADD(prof_total, prof_t0);
                 DG_PROF_FLUSH(kProfMmaWaitFull, prof_full);
@@ -604,6 +630,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                 DG_PROF_FLUSH(kProfMmaIssueCp, prof_cp);
                 DG_PROF_FLUSH(kProfMmaIssueMma, prof_mma);
                 DG_PROF_FLUSH(kProfMmaIssueCommit, prof_commit);
+                }
             }
         } else if (warp_idx == 2 && kHasSF) {
             // ================= scale rearrangement =================
@@ -637,9 +664,13 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                         for (uint32_t i = 0; i < SF_BLOCK_N / 128; ++i)
                             rearrange(sfb_buffer() + i * 512);
                     }
+                    // every lane makes its own writes visible to the async proxy; then one lane signals for the warp
                     fence_proxy_async_smem();
-                    if (kCluster == 1 || is_leader) mbar_arrive(full_bar(stage));
-                    else mbar_arrive_cluster(in_leader(full_bar(stage)));
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (kCluster == 1 || is_leader) mbar_arrive(full_bar(stage));
+                        else mbar_arrive_cluster(in_leader(full_bar(stage)));
+                    }
                     advance_sf(kb);
                 }
             }
@@ -707,7 +738,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
             const uint32_t accum = tile_iter % kNumAccumStages + wg, accum_phase = (tile_iter / kNumAccumStages) & 1;
             ++tile_iter;
             DG_PROF_BEGIN(prof_w);
-            if (!mbar_wait(tmem_full_bar(accum), accum_phase, ctx, kRoleEpilogue, 1)) { ok = false; break; }
+            if (!mbar_wait(tmem_full_bar(accum), accum_phase, ctx, kRoleEpilogue, 1, DG_EPILOGUE_BACKOFF_NS)) { ok = false; break; }
             DG_PROF_ADD(prof_wait, prof_w);
             tc_fence_after_sync();
 

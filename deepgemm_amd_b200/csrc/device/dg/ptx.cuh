@@ -146,19 +146,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 
 // Bounded wait.  Returns false if this CTA is unwinding (another role failed) or the wait ran out.
+// The limit is counted in SM clocks (clock64, a register read) rather than read from the nanosecond global timer, whose
+// reads are slow enough to delay a role that a barrier was about to release; at most 2 clocks pass per nanosecond on
+// this part, so a wait gives up no earlier than kWaitTimeoutNs after it began (later when the clock is throttled).
+// `backoff_ns` > 0 makes a waiter that expects to wait long (an epilogue warp during the main loop of its tile) sleep
+// between polls instead of competing for issue slots with the role warps that share its scheduler.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const AbortCtx& ctx,
-                                          uint32_t role, uint32_t site) {
+                                          uint32_t role, uint32_t site, uint32_t backoff_ns = 0) {
     auto poll = [&]() { return mbar_try_wait(bar, parity); };
     #pragma unroll 1
-    for (int i = 0; i < 64; ++i)
+    for (int i = 0; i < (backoff_ns ? 4 : 64); ++i)
         if (poll()) return true;
-    const uint64_t t0 = global_timer_ns();
+    const long long t0 = clock64();
+    constexpr long long kWaitTimeoutClocks = static_cast<long long>(kWaitTimeoutNs) * 2;
     uint32_t spins = 0;
     #pragma unroll 1
     while (!poll()) {
-        if ((++spins & 0xFFu) == 0) {
+        if (backoff_ns) __nanosleep(backoff_ns);
+        if ((++spins & (backoff_ns ? 0xFu : 0xFFu)) == 0) {
             if (*ctx.flag != 0) return false;
-            if (global_timer_ns() - t0 > kWaitTimeoutNs) {
+            if (clock64() - t0 > kWaitTimeoutClocks) {
                 report_failure(ctx, role, site);
                 return false;
             }
@@ -360,6 +367,13 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
 // 2-CTA form; cluster_bar is a shared::cluster address (own or peer CTA).
 __device__ __forceinline__ void tc_commit_2cta(uint32_t cluster_bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(cluster_bar) : "memory");
+}
+// 2-CTA form that signals the barrier at the same shared-memory offset in every CTA of `cta_mask` with ONE instruction
+// (a commit costs the issuing thread ~100 cycles, and a pipeline stage of a CTA pair must be released in both CTAs).
+// This is an mbarrier arrive, not a copy: no data moves between the CTAs.
+__device__ __forceinline__ void tc_commit_2cta_mask(uint32_t bar, uint16_t cta_mask) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 :: "r"(bar), "h"(cta_mask) : "memory");
 }
 
 // One warp reads its 32 lanes x 16 consecutive 32-bit columns.

@@ -9,9 +9,13 @@
 #include <cstdio>
 #include <cstdlib>
 #include <mutex>
+#include <cstring>
 #include <string>
+#include <vector>
 
 #include "../../include/deepgemm_b200.h"
+
+extern "C" char** environ;          // the process environment (unistd.h declares it only with _GNU_SOURCE)
 
 namespace dg {
 
@@ -79,15 +83,55 @@ void release_split_workspaces();     // frees the library-owned split-K panels o
 #define DG_REQUIRE_ALIVE() \
     do { if (::dg::state().shut_down) return ::dg::fail(DG_ERR_INVALID_ARGUMENT, "the runtime has been shut down (dg_shutdown)"); } while (0)
 
+// Settings read from the environment: DG_<name> first, then DJ_<name> as the reference's runtime does (README.md:166).
+// A GEMM call consults some twenty of them, and twenty getenv scans cost more host time than a decode-sized kernel
+// runs, so each thread keeps the DG_* / DJ_* entries of its last look at `environ`; env_refresh() (one pass over
+// `environ`, called at the top of every entry point that reads settings) notices any change through a hash of those
+// entries, so a variable set between two calls is seen by the second.
+struct EnvSnapshot {
+    bool valid = false;
+    uint64_t signature = 0;
+    std::vector<std::pair<std::string, std::string>> vars;       // name without its three-character prefix, value; DG_ entries first
+};
+inline EnvSnapshot& env_snapshot() {
+    thread_local EnvSnapshot snap;
+    return snap;
+}
+inline void env_refresh() {
+    const auto ours = [](const char* s) { return s[0] == 'D' && (s[1] == 'G' || s[1] == 'J') && s[2] == '_'; };
+    uint64_t h = 1469598103934665603ull;
+    for (char** e = environ; e != nullptr && *e != nullptr; ++e) {
+        if (!ours(*e)) continue;
+        for (const char* c = *e; *c; ++c) { h ^= static_cast<unsigned char>(*c); h *= 1099511628211ull; }
+        h ^= 0xFFu; h *= 1099511628211ull;
+    }
+    EnvSnapshot& snap = env_snapshot();
+    if (snap.valid && snap.signature == h) return;
+    snap.vars.clear();
+    for (int pass = 0; pass < 2; ++pass)                 // DG_ entries first, so that they win over DJ_ ones
+        for (char** e = environ; e != nullptr && *e != nullptr; ++e) {
+            const char* s = *e;
+            if (!ours(s) || (s[1] == 'G') != (pass == 0)) continue;
+            const char* eq = std::strchr(s, '=');
+            if (eq == nullptr) continue;
+            snap.vars.emplace_back(std::string(s + 3, eq), std::string(eq + 1));
+        }
+    snap.signature = h;
+    snap.valid = true;
+}
+inline const char* env_raw(const char* name) {
+    EnvSnapshot& snap = env_snapshot();
+    if (!snap.valid) env_refresh();
+    for (const auto& kv : snap.vars)
+        if (kv.first == name) return kv.second.c_str();
+    return nullptr;
+}
 inline int env_int(const char* name, int dflt = 0) {
-    // DG_ prefix first, then DJ_ as the reference's runtime does (README.md:166)
-    const char* v = std::getenv((std::string("DG_") + name).c_str());
-    if (v == nullptr) v = std::getenv((std::string("DJ_") + name).c_str());
+    const char* v = env_raw(name);
     return v ? std::atoi(v) : dflt;
 }
 inline std::string env_str(const char* name) {
-    const char* v = std::getenv((std::string("DG_") + name).c_str());
-    if (v == nullptr) v = std::getenv((std::string("DJ_") + name).c_str());
+    const char* v = env_raw(name);
     return v ? std::string(v) : std::string();
 }
 

@@ -219,10 +219,17 @@ int validate(int kind, const dg_gemm_args_t* a, bool need_pointers, Problem* p) 
 // the tensor core together.  The latter was fitted on this kernel: seven tile widths of the 256-row kernel and the
 // 128-row kernel all ran within 5 % of (bytes written + bytes read) / 150 cycles per K-block.  It is why 256-row tiles
 // win wherever M allows them: their B stage is written once and read by two MMAs' worth of rows.
-// Measured end to end the long-K shapes then sit at the GPU's power limit: variants that need fewer cycles (a second
-// issuing thread, CTA pairs) ran at proportionally lower SM clocks and took the same time, so the CTA-pair variants
-// stay available on request only (DG_FORCE_CLUSTER=2).
-bool cluster_allowed(const Problem&, int cluster) { return cluster == 1; }
+// CTA pairs (tcgen05 cta_group::2) are chosen where they measured faster: each CTA then loads half of B, and B is read
+// from shared memory once per pair.  Two forms: 128 rows per CTA with two accumulators (the epilogue of a tile overlaps
+// the next tile's main loop: best for short K) and 256 rows per CTA (least shared-memory traffic per MMA cycle: best for
+// long K).  Dense GEMMs with block-scaled operands, and the contiguous grouped layout when every expert segment is a
+// whole number of pair tiles (alignment 256 or 512).
+bool cluster_allowed(const Problem& p, int cluster) {
+    if (cluster == 1) return true;
+    if (p.ab_bf16 || p.reduce_batches > 1 || p.a_mn_major || p.b_mn_major) return false;       // (K-major block-scaled operands: what was measured)
+    // (measured at M = 4096; smaller GEMMs keep the one-CTA forms their cost model was fitted on)
+    return (p.kind == DG_GEMM_DENSE && p.m >= 1024) || p.kind == DG_GEMM_M_GROUPED_CONTIGUOUS;
+}
 
 // Layout of a candidate with the deepest pipeline that fits shared memory.  `item_kb` is the number of K-blocks (of
 // block_k elements) one work item walks; fewer than the stage count makes the scale ring one buffer per stage.
@@ -387,15 +394,20 @@ int choose_config_for(const Problem& p, dg_gemm_config_t* cfg, const Constraints
                 const double stage_frac = bk / 128.0;
                 const double mma = 2.0 * bn * halves * stage_frac;
                 const double stage_bytes = (128.0 * halves + static_cast<double>(bn) / cluster) * bk;
-                const double read_bytes = (128.0 * halves + halves * static_cast<double>(bn) / cluster) * bk;
+                // (with a CTA pair the peer's tensor core reads this CTA's half of B as well)
+                const double read_bytes = (128.0 * halves + halves * static_cast<double>(bn) / cluster * (cluster == 2 ? 2.0 : 1.0)) * bk;
                 // (55 B per cycle fitted the cluster-reduced candidates: few-tile shapes whose B is read once, from HBM)
                 const double smem_feed = std::max((stage_bytes + read_bytes) / 150.0, stage_bytes / (in_cluster ? 55.0 : 67.0));
                 const double ring = (1500.0 + mma) / lay.num_stages;
-                const double epilogue = 300.0 + 150.0 * lay.num_groups() + 20.0 * lay.num_stores() + bn * 2.0;
+                // (one epilogue warpgroup drains a 128 x bn accumulator in ~600 + 14 bn cycles, measured on the K = 512 shape
+                //  with 128-row CTA pairs, where it is what bounds a tile)
+                const double epilogue = cluster == 2 && halves == 1 ? 600.0 + 14.0 * bn
+                                                                    : 300.0 + 150.0 * lay.num_groups() + 20.0 * lay.num_stores() + bn * 2.0;
                 // The epilogue of a tile overlaps the next tile's main loop; it is exposed once per CTA
                 // + ~1500 cycles per tile that do not shrink with K (tile hand-over, first loads of a new tile), measured
                 // on the K = 512 and K = 1536 shapes
-                const double per_tile = static_cast<double>(item_kb) * std::max(mma, std::max(smem_feed, ring)) + 1500.0;
+                // (700 for 128-row CTA pairs, whose tile hand-over was measured on the K = 1536 and K = 2048 shapes)
+                const double per_tile = static_cast<double>(item_kb) * std::max(mma, std::max(smem_feed, ring)) + (cluster == 2 && halves == 1 ? 700.0 : 1500.0);
                 double cost = static_cast<double>(waves) * std::max(per_tile, epilogue) + epilogue + 2000.0;
                 // 256-row tiles have no spare accumulator: the next tile's MMAs start once the epilogue warpgroups have
                 // moved their rows from tensor memory into registers (~1400 cycles, measured)
@@ -518,6 +530,9 @@ std::string generate_source(const Problem& p, const dg_gemm_config_t& cfg) {
       << "#define DG_WRITE_PADDING " << (p.write_padding ? 1 : 0) << "\n"
       << "#define DG_K_PSUM " << (p.k_psum ? 1 : 0) << "\n"
       << "#define DG_PROFILE " << env_int("PROFILE") << "\n"
+      << "#define DG_EPILOGUE_BACKOFF_NS " << env_int("EPILOGUE_BACKOFF_NS", 0) << "\n"
+      << "#define DG_MMA_WHOLE_WARP " << env_int("MMA_WHOLE_WARP", 1) << "\n"
+      << "#define DG_PRODUCER_WHOLE_WARP " << env_int("PRODUCER_WHOLE_WARP", 1) << "\n"
       << "#include <dg/gemm_fp8_fp4.cuh>\n";
     return s.str();
 }
@@ -592,7 +607,8 @@ struct Plan {
 
 int get_plan(const Problem& p, Plan* plan) {
     static const char* kEnvNames[] = {"FORCE_BLOCK_N", "FORCE_CLUSTER", "FORCE_SPLIT_K", "FORCE_BLOCK_M", "FORCE_BLOCK_K",
-                                      "FORCE_NUM_STAGES", "FORCE_RASTER_GROUP", "PROFILE", "FORCE_SPLIT_CLUSTER", "FORCE_SWAP_AB", "FORCE_STORE_BUFFERS"};
+                                      "FORCE_NUM_STAGES", "FORCE_RASTER_GROUP", "PROFILE", "FORCE_SPLIT_CLUSTER", "FORCE_SWAP_AB", "FORCE_STORE_BUFFERS",
+                                      "EPILOGUE_BACKOFF_NS", "MMA_WHOLE_WARP", "PRODUCER_WHOLE_WARP"};
     const int fields[] = {p.kind, p.m, p.n, p.k, p.groups, static_cast<int>(p.a_fp4), static_cast<int>(p.b_fp4), static_cast<int>(p.ab_bf16),
                           static_cast<int>(p.d_fp32), static_cast<int>(p.d_fp8), static_cast<int>(p.accumulate), static_cast<int>(p.a_mn_major),
                           static_cast<int>(p.b_mn_major), p.gran_k_a, p.gran_k_b, p.expected_m, static_cast<int>(p.write_padding),
@@ -603,7 +619,7 @@ int get_plan(const Problem& p, Plan* plan) {
     PlanKey key{};
     size_t i = 0;
     for (int v : fields) key[i++] = v;
-    for (const char* name : kEnvNames) key[i++] = env_int(name);
+    for (const char* name : kEnvNames) key[i++] = env_int(name, -12345);       // (unset differs from every value)
     static_assert(std::tuple_size<PlanKey>::value == kNumFields + kNumEnv, "one slot per field and setting");
     static std::mutex mu;
     static std::map<PlanKey, Plan> plans;
@@ -650,6 +666,7 @@ struct FixedScratch {
 
 int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratch = nullptr) {
     DG_REQUIRE_ALIVE();
+    env_refresh();
     Problem p;
     int rc = validate(kind, a, true, &p);
     if (rc != DG_OK) return rc;
@@ -856,6 +873,7 @@ int dg_fp8_bmm(const dg_gemm_args_t* args) { return run_gemm(DG_GEMM_BATCHED, ar
 
 int dg_get_gemm_config(int kind, const dg_gemm_args_t* args, dg_gemm_config_t* config) {
     DG_REQUIRE(config != nullptr);
+    env_refresh();
     Problem p;
     const int rc = validate(kind, args, false, &p);
     if (rc != DG_OK) return rc;
@@ -864,6 +882,7 @@ int dg_get_gemm_config(int kind, const dg_gemm_args_t* args, dg_gemm_config_t* c
 }
 
 int dg_gemm_precompile(int kind, const dg_gemm_args_t* args) {
+    env_refresh();
     Problem p;
     int rc = validate(kind, args, false, &p);
     if (rc != DG_OK) return rc;

@@ -135,6 +135,7 @@ using namespace dg;
 extern "C" {
 
 int dg_jit_compile(const char* name, const char* entry, const char* source, const char* extra_flags, dg_kernel_t* kernel) {
+    env_refresh();
     DG_REQUIRE(name != nullptr && entry != nullptr && source != nullptr && kernel != nullptr);
     const std::string include_dir = state().library_root + "/csrc/device";
     std::string flags = "-std=c++17 -gencode arch=compute_100a,code=sm_100a -O3 --expt-relaxed-constexpr -cubin";

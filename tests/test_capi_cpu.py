@@ -112,7 +112,9 @@ def test_heuristics_invariants(fp32):
     for m, n, k in SHAPES:
         cfg = dg.get_gemm_config(0, m, n, k, d_is_fp32=fp32)
         assert cfg["block_m"] in (128, 256) and cfg["block_k"] in (64, 128)
-        assert cfg["block_m"] == 128 or (m > 128 and cfg["num_splits"] == 1 and cfg["cluster_size"] == 1)
+        assert cfg["block_m"] == 128 or (m > 128 and cfg["num_splits"] == 1)
+        # CTA pairs (one 256- or 512-row tile per pair) only for large dense GEMMs, never sliced along K
+        assert cfg["cluster_size"] == 1 or (cfg["cluster_size"] == 2 and m >= 1024 and cfg["num_splits"] == 1 and cfg["num_ctas"] % 2 == 0)
         assert cfg["block_n"] % 16 == 0 and 16 <= cfg["block_n"] <= 240
         assert cfg["smem_bytes"] <= 232448, (m, n, k, cfg)
         assert cfg["tmem_cols"] in (32, 64, 128, 256, 512) and 2 * cfg["block_n"] + cfg["block_m"] // 32 + 4 * ((cfg["block_n"] + 127) // 128) <= cfg["tmem_cols"]
@@ -123,7 +125,7 @@ def test_heuristics_invariants(fp32):
             # few rows only; one tile column as wide as the caller's M; K slices, if any, inside a cluster
             assert m <= 64 and cfg["block_m"] == 128 and cfg["block_n"] == -(-m // 16) * 16 and cfg["cluster_size"] == 1
             assert cfg["num_splits"] == 1 or cfg["split_in_cluster"]
-        assert cfg["num_tiles"] == -(-rows // cfg["block_m"]) * -(-cols // cfg["block_n"]) * cfg["num_splits"]
+        assert cfg["num_tiles"] == -(-rows // (cfg["block_m"] * cfg["cluster_size"])) * -(-cols // cfg["block_n"]) * cfg["num_splits"]
         kb = -(-k // 128)
         if cfg["num_splits"] > 1:
             # slices start on a packed scale word (4 K-blocks), cover K exactly once, and none is empty
@@ -156,9 +158,10 @@ def test_operand_swap_can_be_forced_and_forbidden(monkeypatch):
     assert dg.get_gemm_config(0, 64, 4096, 7168)["swap_ab"] == 0            # on request only beyond
 
 
-def test_second_staging_buffer_is_given_up_only_for_a_third_stage():
-    """MN-major operands are staged as whole 128-byte atoms (a 240-column B tile takes 32 KB), so 256 x 240 tiles fit two
+def test_second_staging_buffer_is_given_up_only_for_a_third_stage(monkeypatch):
+    """(One CTA per tile.)  MN-major operands are staged as whole 128-byte atoms (a 240-column B tile takes 32 KB), so 256 x 240 tiles fit two
     stages beside two D staging buffers per epilogue warpgroup and three beside one; K-major tiles fit three either way."""
+    monkeypatch.setenv("DG_FORCE_CLUSTER", "1")
     cfg = GemmConfig()
     _lib.check(lib.dg_get_gemm_config(0, C.byref(_args(m=4096, n=4096, k=7168, lda=7168, ldb=7168, ldd=4096)), C.byref(cfg)))
     assert (cfg.block_m, cfg.num_stages, cfg.store_buffers) == (256, 3, 2)
