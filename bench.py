@@ -43,11 +43,12 @@ NOMINAL_FP8_TFLOPS = 4500.0
 FP8_FLOP_PER_CLK_PER_SM = 16384          # dense FP8 tensor rate of one SM: 8192 multiply-adds per clock
 DEFAULT_PASSES = 128
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of dg_gemm_fp8_fp4 at M = 4096 on one GPU, from one ncu
-# capture of this script (profiles/dg_gemm_fp8_fp4_dense_m4096.md), with the tile the capture ran: the figure is
-# reported only while the heuristics still choose that tile (D written late in a launch may still sit in L2 when it ends).
-NCU_DRAM_BYTES = {(2112, 7168): (46332928, (256, 240, 8)), (24576, 1536): (231155456, (256, 224, 8)),
-                  (32768, 512): (247204352, (256, 240, 8)), (7168, 16384): (461400576, (256, 208, 8)),
-                  (4096, 7168): (62027264, (256, 240, 8)), (7168, 2048): (31307264, (256, 208, 8))}
+# capture of this script (profiles/dg_gemm_fp8_fp4_dense_m4096.md), with the tile the capture ran (rows per CTA, tile
+# columns, raster group, CTAs per tile): the figure is reported only while the heuristics still choose that tile (D
+# written late in a launch may still sit in L2 when it ends).
+NCU_DRAM_BYTES = {(2112, 7168): (46539264, (256, 240, 4, 2)), (24576, 1536): (229246720, (128, 240, 8, 2)),
+                  (32768, 512): (247148288, (256, 240, 4, 2)), (7168, 16384): (530350848, (128, 224, 8, 2)),
+                  (4096, 7168): (71331840, (256, 240, 4, 2)), (7168, 2048): (31581440, (128, 224, 8, 2))}
 
 
 def flops_of(m, n, k):
@@ -569,7 +570,7 @@ def main():
         for c in cases:
             cfg = dg.get_gemm_config(0, c["m"], c["n"], c["k"])
             ent = NCU_DRAM_BYTES.get((c["n"], c["k"]))
-            known.append(ent[0] if ent is not None and ent[1] == (cfg["block_m"], cfg["block_n"], cfg["raster_group"]) else None)
+            known.append(ent[0] if ent is not None and ent[1] == (cfg["block_m"], cfg["block_n"], cfg["raster_group"], cfg["cluster_size"]) else None)
         traffic = None if any(v is None for v in known) else round(sum(known) / len(known))
     launches_per_step = args.passes * len(cases)
     algorithmic = sum(dense_bytes(c["m"], c["n"], c["k"]) for c in cases) / max(len(cases), 1)
@@ -839,7 +840,8 @@ def sustained_rows(torch, dg, device_index, num_sms, seconds=1.5):
     for i, (n, k) in enumerate(DENSE_NK):
         c = make_dense_case(M_DENSE, n, k, 300 + i, torch, dg)
         cfg = dg.get_gemm_config(0, M_DENSE, n, k)
-        run(f"dense m{M_DENSE} n{n} k{k} [{cfg['block_m']}x{cfg['block_n']}, {cfg['num_stages']} stages, raster {cfg['raster_group']}]",
+        tile = f"{cfg['block_m'] * cfg['cluster_size']}x{cfg['block_n']} per {'CTA pair' if cfg['cluster_size'] == 2 else 'CTA'}"
+        run(f"dense m{M_DENSE} n{n} k{k} [{tile}, {cfg['num_stages']} stages]",
             lambda: dg.fp8_gemm_nt(c["a"], c["b"], c["d"], recipe=(1, 1, 128)), flops_of(M_DENSE, n, k))
         x8, w8, one = c["a"][0], c["b"][0], torch.ones((), device="cuda")
         run(f"torch._scaled_mm (cuBLASLt, per-tensor scales) m{M_DENSE} n{n} k{k}",
