@@ -385,6 +385,45 @@ def run_grouped_ep(torch, dist, dg, rank, world, barrier, check):
     return out, checks
 
 
+def run_reference_gpu(timeout_s=420):
+    """The UNMODIFIED reference's own sm_100 kernel on this GPU, for the same six shapes: baseline/reference_arm.py in a
+    child process (the reference installed by baseline/build_ref.py into the git-ignored baseline/_ref; its JIT runtime,
+    an un-vendored submodule, is replaced by the stand-in under baseline/deep_jit_standin).  Burst = its own bench_kineto
+    (profiler kernel time, L2 flushed before every call); sustained = the same back-to-back loop as `sustained_rows`."""
+    import subprocess
+    import tempfile
+    script = os.path.join(ROOT, "baseline", "reference_arm.py")
+    if not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "deep_gemm")):
+        return {"unavailable": "baseline/_ref holds no reference installation on this machine (built by baseline/build_ref.py where the reference tree exists)"}
+    with tempfile.NamedTemporaryFile(suffix=".json", delete=False) as f:
+        out_path = f.name
+    try:
+        res = subprocess.run([sys.executable, script, "--stage", "dense", "--m", str(M_DENSE), "--sustained", "--out", out_path],
+                             capture_output=True, text=True, timeout=timeout_s)
+        if res.returncode != 0 or not os.path.getsize(out_path):
+            tail = (res.stderr or res.stdout).strip().splitlines()[-1:] or ["no output"]
+            return {"unavailable": f"reference_arm.py exited {res.returncode}: {tail[0][:160]}"}
+        data = json.load(open(out_path))
+    except subprocess.TimeoutExpired:
+        return {"unavailable": f"reference_arm.py did not finish within {timeout_s} s"}
+    finally:
+        try:
+            os.unlink(out_path)
+        except OSError:
+            pass
+    rows = data.get("dense", [])
+    if len(rows) != len(DENSE_NK):
+        return {"unavailable": "reference_arm.py returned no dense rows", "detail": {k: v for k, v in data.items() if k != "dense"}}
+    flops = sum(flops_of(M_DENSE, n, k) for n, k in DENSE_NK)
+    burst = sum(r["us"] for r in rows) * 1e-6
+    sustained = sum(r.get("sustained_us", 0.0) for r in rows) * 1e-6
+    return {"what": "the reference's sm100_fp8_fp4_gemm_1d1d_impl through its own Python API, heuristics and launcher (DeepGEMM "
+                    + str(data.get("reference_version")) + ", DeepJIT replaced by a stand-in)",
+            "burst_tflops": round(flops / burst / 1e12, 1), "sustained_tflops": round(flops / sustained / 1e12, 1) if sustained else None,
+            "bitwise_equal_to_this_repository": all(r.get("bitwise_equal_to_this_repository") for r in rows),
+            "rows": [{k: r.get(k) for k in ("case", "us", "tflops", "sustained_us", "sustained_tflops", "sm_mhz", "power_w")} for r in rows]}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -395,6 +434,7 @@ def main():
     ap.add_argument("--detail", action="store_true", help="also time each shape of configs 2-5 on its own (rank 0)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-grouped", action="store_true", help="skip the grouped_ep record (profiling runs)")
+    ap.add_argument("--no-reference-gpu", action="store_true", help="skip the run of the reference's own GPU kernel (N = 1 only)")
     ap.add_argument("--no-graph", action="store_true", help="launch every GEMM from Python instead of replaying one CUDA graph per step")
     ap.add_argument("--pdl", action="store_true", help="launch the GEMMs with programmatic dependent launch (set_pdl)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
@@ -615,6 +655,11 @@ def main():
         tflops, cdt, threads = time_cpu(1, 0)
         line["cpu_baseline"] = {"value": round(tflops, 4), "unit": "TFLOP/s", "cores": threads, "kind": "port",
                                 "sample": f"one pass over all six M={M_DENSE} shapes, {cdt:.1f} s of dequantise + FP32 matmul on the host"}
+    if world == 1 and not args.no_reference_gpu and not args.shapes and args.m == M_DENSE:
+        # our own six shapes in the same two regimes, then the reference's kernel: both after the timed regions above
+        ours = sustained_rows(torch, dg, local_rank, num_sms, dense_only=True, with_library=False)
+        line["per_shape_sustained"] = ours
+        line["reference_gpu"] = run_reference_gpu()
     if args.detail:
         line["detail"] = detail_rows(torch, dg)
         line["sustained"] = sustained_rows(torch, dg, local_rank, num_sms)
@@ -695,6 +740,18 @@ def detail_rows(torch, dg):
         d = torch.empty((M_DENSE, n), device="cuda", dtype=torch.bfloat16)
         t = bench(lambda: dg.fp8_fp4_gemm_nt((qa, sfa), (qb, sfb), d, recipe_a=(1, 128), recipe_b=(1, 32)), 3, 10)
         add(f"fp8xfp4 dense m{M_DENSE} n{n} k{k}", t, flops_of(M_DENSE, n, k), M_DENSE * k + n * k // 2 + M_DENSE * n * 2)
+        del a, w, qa, qb, d
+    # FP4 x FP4 through kind::mxf4 (packed operands in shared memory, twice the FP8 tensor rate; nominal dense FP4 peak 9000 TFLOP/s)
+    for n, k in ((7168, 2048), (4096, 7168), (7168, 16384)):
+        a = torch.randn((M_DENSE, k), device="cuda", dtype=torch.bfloat16)
+        w = torch.randn((n, k), device="cuda", dtype=torch.bfloat16)
+        qa, sfa = per_token_cast_to_fp4(a, True, 32)
+        qb, sfb = per_token_cast_to_fp4(w, True, 32)
+        sfa = dg.transform_sf_into_required_layout(sfa, M_DENSE, k, (1, 32))
+        sfb = dg.transform_sf_into_required_layout(sfb, n, k, (1, 32))
+        d = torch.empty((M_DENSE, n), device="cuda", dtype=torch.bfloat16)
+        t = bench(lambda: dg.fp4_gemm_nt((qa, sfa), (qb, sfb), d, recipe_a=(1, 32), recipe_b=(1, 32)), 3, 10)
+        add(f"fp4xfp4 (kind::mxf4) dense m{M_DENSE} n{n} k{k}", t, flops_of(M_DENSE, n, k), (M_DENSE + n) * k // 2 + M_DENSE * n * 2)
         del a, w, qa, qb, d
     # configs 3 and 5 (grouped): 32 experts, tokens per expert int(8192 U(0.7, 1.3)) aligned to 128
     rng = random.Random(0)
@@ -792,7 +849,7 @@ def detail_rows(torch, dg):
     return rows
 
 
-def sustained_rows(torch, dg, device_index, num_sms, seconds=1.5):
+def sustained_rows(torch, dg, device_index, num_sms, seconds=1.5, dense_only=False, with_library=True):
     """The M = 4096 dense shapes and the two config-3 grouped shapes, each run back to back for ~`seconds` (CUDA graph of
     20 launches replayed), with the SM clock and board power sampled meanwhile: time, TFLOP/s, median MHz, median W,
     thousands of SM cycles per launch (time x clock) and the fraction of the FP8 tensor rate at that clock.  The library
@@ -844,9 +901,12 @@ def sustained_rows(torch, dg, device_index, num_sms, seconds=1.5):
         run(f"dense m{M_DENSE} n{n} k{k} [{tile}, {cfg['num_stages']} stages]",
             lambda: dg.fp8_gemm_nt(c["a"], c["b"], c["d"], recipe=(1, 1, 128)), flops_of(M_DENSE, n, k))
         x8, w8, one = c["a"][0], c["b"][0], torch.ones((), device="cuda")
-        run(f"torch._scaled_mm (cuBLASLt, per-tensor scales) m{M_DENSE} n{n} k{k}",
-            lambda: torch._scaled_mm(x8, w8.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16), flops_of(M_DENSE, n, k))
+        if with_library:
+            run(f"torch._scaled_mm (cuBLASLt, per-tensor scales) m{M_DENSE} n{n} k{k}",
+                lambda: torch._scaled_mm(x8, w8.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16), flops_of(M_DENSE, n, k))
         del c, x8, w8
+    if dense_only:
+        return rows
     actual, aligned = grouped_layout()
     for n, k in GROUPED_NK:
         sh = make_contiguous_shard(n, k, (0, 32), actual, aligned, torch, dg)

@@ -26,14 +26,22 @@ struct GemmLayout {
                                                    // (block_k stays the byte width of a K-major stage row)
     uint32_t store_buffers = 2;                    // staging buffers of D per epilogue warpgroup: 2, or 1 where the 8-16 KB
                                                    // saved buy another pipeline stage (MN-major operands: whole 128-byte atoms)
+    uint32_t mxf4 = 0;                             // FP4 x FP4 through kind::mxf4: operands stay packed in shared memory (two
+                                                   // elements per byte), so a 128-byte stage row holds 256 elements of K
 
     // A packed scale word covers 4 * gran_k elements of K: it is fetched on every `period`-th K-block of a work item,
     // into the next of a ring of buffers.  A buffer may be refilled once the fetch it held is no longer among the
     // last num_stages pipeline steps (the producer is never further ahead of the MMAs).  num_stages consecutive steps
     // span at most two work items when every item has at least num_stages K-blocks, and then hold at most
     // ceil(num_stages / period) + 1 fetches; with shorter items every step may fetch.
-    DG_HDC uint32_t sfa_period() const { return 4 * gran_k_a / block_k; }
-    DG_HDC uint32_t sfb_period() const { return 4 * gran_k_b / block_k; }
+    // (a stage that holds more than 4 * gran_k elements fetches several words per K-block instead: sf_words)
+    DG_HDC uint32_t k_elems() const { return block_k * (mxf4 ? 2 : 1) / ab_elem_bytes; }      // elements of K per pipeline stage
+    DG_HDC uint32_t sf_period(uint32_t gran) const { return 4 * gran / k_elems() ? 4 * gran / k_elems() : 1; }
+    DG_HDC uint32_t sf_words(uint32_t gran) const { return k_elems() / (4 * gran) ? k_elems() / (4 * gran) : 1; }
+    DG_HDC uint32_t sfa_period() const { return sf_period(gran_k_a); }
+    DG_HDC uint32_t sfb_period() const { return sf_period(gran_k_b); }
+    DG_HDC uint32_t sfa_words() const { return sf_words(gran_k_a); }
+    DG_HDC uint32_t sfb_words() const { return sf_words(gran_k_b); }
     DG_HDC uint32_t sf_buffers(uint32_t period) const {
         if (ab_elem_bytes != 1) return 0;
         const uint32_t n = (num_stages + period - 1) / period + 1;
@@ -64,8 +72,8 @@ struct GemmLayout {
     // MN-major only: atoms of [block_k / ab_elem_bytes rows of K][128 bytes of N]
     DG_HDC uint32_t b_atoms() const { return (load_block_n() * ab_elem_bytes + 127) / 128; }
     DG_HDC uint32_t b_bytes() const { return b_mn_major ? b_atoms() * 128 * (block_k / ab_elem_bytes) : load_block_n() * block_k; }
-    DG_HDC uint32_t sfa_bytes() const { return block_m * 4; }
-    DG_HDC uint32_t sfb_bytes() const { return sf_block_n() * 4; }
+    DG_HDC uint32_t sfa_bytes() const { return block_m * 4 * sfa_words(); }          // [word of K][row] int32
+    DG_HDC uint32_t sfb_bytes() const { return sf_block_n() * 4 * sfb_words(); }
 
     DG_HDC uint32_t off_d() const { return 0; }
     DG_HDC uint32_t off_a() const { return (num_store_stages() * store_stage_bytes() + 1023) / 1024 * 1024; }
@@ -80,8 +88,9 @@ struct GemmLayout {
     // Tensor memory: two accumulators of block_n columns (two tiles in flight when block_m is 128, the two 128-row
     // halves of one tile when it is 256), then SFA (4 columns per 128 rows) and SFB (4 columns per 128 columns of the tile)
     DG_HDC uint32_t tmem_col_sfa() const { return 2 * block_n; }
-    DG_HDC uint32_t tmem_col_sfb() const { return tmem_col_sfa() + block_m / 32; }
-    DG_HDC uint32_t tmem_cols_used() const { return ab_elem_bytes != 1 ? 2 * block_n : tmem_col_sfb() + sf_block_n() / 32; }
+    // (per packed word of a stage: kind::mxf4 stages hold two)
+    DG_HDC uint32_t tmem_col_sfb() const { return tmem_col_sfa() + block_m / 32 * sfa_words(); }
+    DG_HDC uint32_t tmem_cols_used() const { return ab_elem_bytes != 1 ? 2 * block_n : tmem_col_sfb() + sf_block_n() / 32 * sfb_words(); }
     DG_HDC uint32_t tmem_cols_alloc() const {
         const uint32_t u = tmem_cols_used();
         return u <= 32 ? 32 : u <= 64 ? 64 : u <= 128 ? 128 : u <= 256 ? 256 : 512;

@@ -94,7 +94,16 @@ constexpr uint32_t BLOCK_N     = DG_BLOCK_N;
 constexpr uint32_t BLOCK_K     = DG_BLOCK_K;       // bytes of K per row of a pipeline stage (64 or 128)
 constexpr bool     kABIsBF16   = DG_AB_BF16 != 0;
 constexpr uint32_t kABElemBytes = kABIsBF16 ? 2 : 1;
-constexpr uint32_t BLOCK_K_ELEMS = BLOCK_K / kABElemBytes;         // elements of K per pipeline stage
+#ifndef DG_MXF4
+#define DG_MXF4 0
+#endif
+// FP4 x FP4 through tcgen05.mma.kind::mxf4 (the reference's kIsMXF4, impls/sm100_fp8_fp4_gemm_1d1d.cuh:51-54): the
+// operands stay packed in shared memory (two E2M1 values per byte), so a 128-byte stage row is 256 elements of K, an MMA
+// covers 64 of them, a stage carries two packed scale words per row (one scale per 32 elements), and the tensor cores run
+// at twice the FP8 rate.  Without it FP4 operands are unpacked to one byte per element on the way into shared memory and
+// multiplied by kind::mxf8f6f4.
+constexpr bool     kMXF4       = DG_MXF4 != 0;
+constexpr uint32_t BLOCK_K_ELEMS = BLOCK_K * (kMXF4 ? 2 : 1) / kABElemBytes;         // elements of K per pipeline stage
 constexpr bool     kHasSF      = !kABIsBF16;                       // block-scaled operands
 constexpr uint32_t kAtomElems  = 128 / kABElemBytes;               // MN-major staging: elements of MN per 128-byte atom row
 constexpr uint32_t kNumStages  = DG_NUM_STAGES;
@@ -153,12 +162,16 @@ static_assert(!(kBIsFP4 && kBMnMajor) || (!kAIsFP4 && BLOCK_N % 128 == 0 && kClu
 static_assert(!kBMnMajor || (BLOCK_N / kCluster) % 16 == 0, "an MN-major B load must start on a 16-byte boundary");
 static_assert(!kSplitK || (kGemmType == 0 && kDIsFP32 && !kAccumulate && kMHalves == 1), "split-K serves the plain dense GEMM and writes FP32 partials");
 static_assert(kGemmType != kKGrouped || (BLOCK_K == 128 && kCluster == 1 && kGranKA == kGranKB), "k-grouped: one CTA per tile, 128-element stages, one scale granularity");
+static_assert(!kMXF4 || (DG_A_FP4 && DG_B_FP4 && !DG_MAJOR_A && !DG_MAJOR_B && kGranKA == 32 && kGranKB == 32 && BLOCK_K == 128 &&
+                         kGemmType != kKGrouped && kGemmType != kBatched && !DG_BATCH_REDUCE),
+              "kind::mxf4: K-major packed FP4 on both sides, one scale per 32 elements of K");
 
 // Scales: a packed int32 holds 4 scales, so it spans 4 * gran_k elements of K and is fetched on every
 // (4 * gran_k / BLOCK_K)-th K-block: every 4th (8th with 64-element stages) at one scale per 128 K, every (2nd) one
 // at one per 32 K.
-constexpr uint32_t kSFAPeriod = 4 * kGranKA / BLOCK_K;
-constexpr uint32_t kSFBPeriod = 4 * kGranKB / BLOCK_K;
+// (a kind::mxf4 stage holds 256 elements of K: two words per row and K-block, fetched on every K-block)
+constexpr uint32_t kSFAPeriod = 4 * kGranKA / BLOCK_K_ELEMS ? 4 * kGranKA / BLOCK_K_ELEMS : 1;
+constexpr uint32_t kSFBPeriod = 4 * kGranKB / BLOCK_K_ELEMS ? 4 * kGranKB / BLOCK_K_ELEMS : 1;
 constexpr uint32_t SF_BLOCK_M = CTA_M;
 constexpr uint32_t SF_BLOCK_N = (BLOCK_N + 127) / 128 * 128;
 
@@ -195,7 +208,11 @@ static_assert(kSplitCluster == 1 || (kGemmType == kDense && !kSplitK && kCluster
 #define DG_EPILOGUE_BACKOFF_NS 0
 #endif
 constexpr GemmLayout kLayout{CTA_M, BLOCK_N, BLOCK_K, kNumStages, kDElemBytes, kCluster, kBMnMajor ? 1u : 0u, kGranKA, kGranKB,
-                             DG_SHORT_K, kABElemBytes, DG_STORE_BUFFERS};
+                             DG_SHORT_K, kABElemBytes, DG_STORE_BUFFERS, kMXF4 ? 1u : 0u};
+constexpr uint32_t kSFAWords = kHasSF ? kLayout.sfa_words() : 1, kSFBWords = kHasSF ? kLayout.sfb_words() : 1;   // packed words per row and stage
+// K coordinate of a K-major load advances by this much per K-block: elements of the tensor map's type (bytes for the
+// packed operands of kind::mxf4, whose maps are plain byte maps)
+constexpr uint32_t kLoadXPerKBlock = kMXF4 ? BLOCK_K : BLOCK_K_ELEMS;
 constexpr uint32_t kNumSFABuffers = kHasSF ? kLayout.sfa_buffers() : 1, kNumSFBBuffers = kHasSF ? kLayout.sfb_buffers() : 1;
 static_assert(kSFAPeriod >= 1 && kSFBPeriod >= 1 && kSFAPeriod == kLayout.sfa_period() && kSFBPeriod == kLayout.sfb_period(), "scale fetch period");
 constexpr uint32_t kBAtoms = kLayout.b_atoms();            // 128-column atoms of an MN-major B tile
@@ -224,7 +241,7 @@ static_assert(kStoreCols % 16 == 0 || kDIsFP32, "a store covers whole 16-column 
 
 // Bytes the TMA engine reports per stage, summed over the CTAs of the cluster (packed FP4 counts its
 // global-memory bytes)
-constexpr uint32_t kTxBytesAB = kCluster * (kABytes / (kAIsFP4 ? 2 : 1) + kBBytes / (kBIsFP4 ? 2 : 1));
+constexpr uint32_t kTxBytesAB = kCluster * (kABytes / (kAIsFP4 && !kMXF4 ? 2 : 1) + kBBytes / (kBIsFP4 && !kMXF4 ? 2 : 1));
 
 constexpr uint32_t kTmemColSFA = kLayout.tmem_col_sfa();
 constexpr uint32_t kTmemColSFB = kLayout.tmem_col_sfb();
@@ -464,9 +481,9 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                             if (kb % kSFBPeriod == 0) sf_bytes += kSFBBytes;
                             mbar_arrive_expect_tx(sf_full_bar(stage), sf_bytes);
                             if (kb % kSFAPeriod == 0)
-                                tma_in(sfa_buffer(), &tm_sfa, sf_full_bar(stage), sfa_mn, sfa_row0 + kb / kSFAPeriod, tile.group);
+                                tma_in(sfa_buffer(), &tm_sfa, sf_full_bar(stage), sfa_mn, sfa_row0 + kb / kSFAPeriod * kSFAWords, tile.group);
                             if (kb % kSFBPeriod == 0)
-                                tma_in(sfb_buffer(), &tm_sfb, sf_full_bar(stage), tile.n_block * BLOCK_N, sfb_row0 + kb / kSFBPeriod, tile.group);
+                                tma_in(sfb_buffer(), &tm_sfb, sf_full_bar(stage), tile.n_block * BLOCK_N, sfb_row0 + kb / kSFBPeriod * kSFBWords, tile.group);
                         }
                         // With a cluster the copies land in this CTA and their bytes are counted on CTA 0's barrier,
                         // which expects both CTAs' bytes
@@ -488,7 +505,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                             continue;
                         }
                         if constexpr (!kAMnMajor) {
-                            load(smem_base + kSmemA + stage * kABytes, &tm_a, k_base + kb * BLOCK_K_ELEMS, a_row);      // one box of CTA_M rows
+                            load(smem_base + kSmemA + stage * kABytes, &tm_a, k_base + kb * kLoadXPerKBlock, a_row);      // one box of CTA_M rows
                         } else {
                             // one box per atom: 128 bytes of M (128 FP8 or 64 BF16 elements) by the stage's rows of K
                             #pragma unroll
@@ -497,7 +514,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                                      k_base + kb * BLOCK_K_ELEMS);
                         }
                         if constexpr (!kBMnMajor) {
-                            load(smem_base + kSmemB + stage * kBBytes, &tm_b, k_base + kb * BLOCK_K_ELEMS, b_row);
+                            load(smem_base + kSmemB + stage * kBBytes, &tm_b, k_base + kb * kLoadXPerKBlock, b_row);
                         } else {
                             #pragma unroll
                             for (uint32_t i = 0; i < kBAtoms; ++i)
@@ -521,6 +538,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
             const bool issue_lane = lane == 0;
             if ((kWholeWarp || lane == 0) && is_leader) {
                 constexpr uint32_t idesc = kABIsBF16 ? make_instr_desc_bf16(kAMnMajor, kBMnMajor, UMMA_M, UMMA_N)
+                                           : kMXF4 ? make_instr_desc_block_scaled(kFmtMxf4E2M1, kFmtMxf4E2M1, 0, 0, UMMA_M, UMMA_N)
                                                      : make_instr_desc_block_scaled(kAIsFP4 ? kFmtE2M1 : kFmtE4M3, kBIsFP4 ? kFmtE2M1 : kFmtE4M3,
                                                                                     kAMnMajor, kBMnMajor, UMMA_M, UMMA_N);
                 // K-major: 8-row groups of BLOCK_K-byte rows (SBO 1024 or 512, swizzle span = the row), +32 B per UMMA along K.
@@ -572,13 +590,13 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                         DG_PROF_BEGIN(prof_i0);
                         if (kHasSF && kb % kSFAPeriod == 0) {
                             #pragma unroll
-                            for (uint32_t i = 0; i < SF_BLOCK_M / 128; ++i)
+                            for (uint32_t i = 0; i < kSFAWords * SF_BLOCK_M / 128; ++i)      // chunk (word w, rows 128 r ..): index w * (rows / 128) + r
                                 tc_cp_32x128b_warpx4<kCluster>(tmem_base + kTmemColSFA + i * 4,
                                                                make_smem_desc(sfa_buffer() + i * 512, 0, 128, kSwizzleNone));
                         }
                         if (kHasSF && kb % kSFBPeriod == 0) {
                             #pragma unroll
-                            for (uint32_t i = 0; i < SF_BLOCK_N / 128; ++i)
+                            for (uint32_t i = 0; i < kSFBWords * SF_BLOCK_N / 128; ++i)
                                 tc_cp_32x128b_warpx4<kCluster>(tmem_base + kTmemColSFB + i * 4,
                                                                make_smem_desc(sfb_buffer() + i * 512, 0, 128, kSwizzleNone));
                         }
@@ -602,6 +620,12 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                                 if constexpr (kABIsBF16)
                                     tc_mma_bf16<kCluster>(tmem_d, a_desc + h * ((BLOCK_M * BLOCK_K) >> 4) + j * kAStepK, b_desc + j * kBStepK,
                                                           idesc, ((kb - kb0) | j) != 0);
+                                else if constexpr (kMXF4)
+                                    // 64 elements of K per instruction: word j / 2 of the stage, scale bytes 0-1 or 2-3 of it
+                                    tc_mma_mxf4<kCluster>(tmem_d, a_desc + h * ((BLOCK_M * BLOCK_K) >> 4) + j * kAStepK, b_desc + j * kBStepK,
+                                                          instr_desc_with_sf_ids(idesc, (j % 2) * 2, (j % 2) * 2),
+                                                          tmem_base + kTmemColSFA + (j / 2) * (SF_BLOCK_M / 32) + h * 4,
+                                                          tmem_base + kTmemColSFB + (j / 2) * (SF_BLOCK_N / 32), ((kb - kb0) | j) != 0);
                                 else
                                     tc_mma_mxf8f6f4<kCluster>(tmem_d, a_desc + h * ((BLOCK_M * BLOCK_K) >> 4) + j * kAStepK, b_desc + j * kBStepK,
                                                               instr_desc_with_sf_ids(idesc, sfa_id, sfb_id),
@@ -656,12 +680,12 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                     DG_PROF_ADD(prof_wait, prof_w);
                     if (kb % kSFAPeriod == 0) {
                         #pragma unroll
-                        for (uint32_t i = 0; i < SF_BLOCK_M / 128; ++i)
+                        for (uint32_t i = 0; i < kSFAWords * SF_BLOCK_M / 128; ++i)
                             rearrange(sfa_buffer() + i * 512);
                     }
                     if (kb % kSFBPeriod == 0) {
                         #pragma unroll
-                        for (uint32_t i = 0; i < SF_BLOCK_N / 128; ++i)
+                        for (uint32_t i = 0; i < kSFBWords * SF_BLOCK_N / 128; ++i)
                             rearrange(sfb_buffer() + i * 512);
                     }
                     // every lane makes its own writes visible to the async proxy; then one lane signals for the warp

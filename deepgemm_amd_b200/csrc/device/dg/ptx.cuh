@@ -296,7 +296,8 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t 
 //   [15]   A is MN-major              [16]   B is MN-major
 //   [17,23) N >> 3                    [23]   scale format (1 = UE8M0)
 //   [24,29) M >> 4                    [29,31) A scale-factor byte id
-enum : uint32_t { kFmtE4M3 = 0, kFmtE2M1 = 5 };
+// (kind::mxf8f6f4 formats; kind::mxf4 has its own numbering, in which E2M1 is 1)
+enum : uint32_t { kFmtE4M3 = 0, kFmtE2M1 = 5, kFmtMxf4E2M1 = 1 };
 
 __host__ __device__ constexpr uint32_t make_instr_desc_block_scaled(uint32_t a_fmt, uint32_t b_fmt,
                                                                      uint32_t a_mn_major, uint32_t b_mn_major,
@@ -342,6 +343,24 @@ __device__ __forceinline__ void tc_mma_mxf8f6f4(uint32_t tmem_d, uint64_t desc_a
         asm volatile(
             "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
             "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+            :: "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb) : "memory");
+}
+
+// D[tmem] (+)= A[smem] * B[smem] for packed FP4 inputs (two E2M1 values per byte, K = 64 elements = 32 bytes per
+// instruction) with one UE8M0 scale per 32 elements of K: two scale bytes of the word in tensor memory per instruction,
+// bytes 0-1 or 2-3 as the scale-factor id (0 or 2) of the instruction descriptor says.  Twice the FP8 rate.
+template <int kCtaGroup>
+__device__ __forceinline__ void tc_mma_mxf4(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                            uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+    if constexpr (kCtaGroup == 1)
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.block32 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+            :: "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb) : "memory");
+    else
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::mxf4.block_scale.block32 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
             :: "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb) : "memory");
 }
 

@@ -79,6 +79,7 @@ struct Problem {
     bool k_psum;             // k-grouped: grouped_layout holds prefix sums
     bool stochastic;         // BF16 output rounded stochastically
     int reduce_batches;      // dense BF16 GEMM summed over this many batches as well (k is then batches x K of one batch); 0 = no
+    bool mxf4;               // FP4 x FP4 through kind::mxf4 (packed operands in shared memory, 256 elements of K per stage)
 };
 
 int validate(int kind, const dg_gemm_args_t* a, bool need_pointers, Problem* p) {
@@ -169,6 +170,12 @@ int validate(int kind, const dg_gemm_args_t* a, bool need_pointers, Problem* p) 
     p->write_padding = kind == DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM && a->ensure_zero_padding != 0;
     p->k_psum = k_grouped && a->use_psum_layout != 0;
     p->stochastic = a->stochastic_rounding != 0;
+    // FP4 x FP4 with K-major operands and one scale per 32 elements of K runs through kind::mxf4 at twice the FP8 rate
+    // (the reference's is_mxf4_mma, csrc/jit_kernels/impls/sm100_fp8_fp4_gemm_1d1d.hpp:36-39); other FP4 combinations
+    // are unpacked to bytes and multiplied by kind::mxf8f6f4.  DG_DISABLE_MXF4=1 sends FP4 x FP4 down that path as well.
+    p->mxf4 = p->a_fp4 && p->b_fp4 && !p->a_mn_major && !p->b_mn_major && p->gran_k_a == 32 && p->gran_k_b == 32 &&
+              (kind == DG_GEMM_DENSE || kind == DG_GEMM_M_GROUPED_CONTIGUOUS || kind == DG_GEMM_M_GROUPED_MASKED ||
+               kind == DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM) && env_int("DISABLE_MXF4") == 0;
     // "Stochastic rounding requires a direct BF16 output" (epilogue_class.hpp:104-107); the epilogues do not compose
     if (p->stochastic) DG_REQUIRE(a->d_dtype == DG_BF16 && !a->accumulate && !a->has_alpha);
     if (a->m == 0 || a->n == 0 || a->k == 0) return DG_OK;                    // handled by the caller (gemm.hpp:17-53)
@@ -285,7 +292,10 @@ int choose_config_for(const Problem& p, dg_gemm_config_t* cfg, const Constraints
     const int num_sms = dg_get_num_sms();
     const int d_elem = p.d_fp32 ? 4 : (p.d_fp8 ? 1 : 2);
     const int ab_elem = p.ab_bf16 ? 2 : 1;
-    const int64_t k_blocks = ceil_div<int64_t>(static_cast<int64_t>(p.k) * ab_elem, 128);   // in units of 128 bytes of K, whatever the stage size
+    // bytes of K per operand row in shared memory: one per FP8 / unpacked FP4 element, two per BF16 element, half a byte
+    // per element of the packed operands of kind::mxf4
+    const int64_t k_row_bytes = p.mxf4 ? static_cast<int64_t>(p.k) / 2 : static_cast<int64_t>(p.k) * ab_elem;
+    const int64_t k_blocks = ceil_div<int64_t>(k_row_bytes, 128);   // in units of 128 bytes of K, whatever the stage size
     const int forced_bn = env_int("FORCE_BLOCK_N"), forced_cluster = env_int("FORCE_CLUSTER"), forced_splits = env_int("FORCE_SPLIT_K");
     // DG_FORCE_SPLIT_CLUSTER: 1 = always reduce the slices of K inside a thread-block cluster, -1 = never (two kernels)
     const int forced_split_cluster = env_int("FORCE_SPLIT_CLUSTER");
@@ -367,14 +377,14 @@ int choose_config_for(const Problem& p, dg_gemm_config_t* cfg, const Constraints
                 // (k-grouped: the groups share K; an average slice stands for all of them)
                 // (in bytes of K per row)
                 const int64_t item_k = p.kind == DG_GEMM_K_GROUPED_CONTIGUOUS ? std::max<int64_t>(128, static_cast<int64_t>(p.k) * ab_elem / p.groups)
-                                                                               : std::min<int64_t>(static_cast<int64_t>(p.k) * ab_elem, static_cast<int64_t>(kb_per) * 128);
+                                                                               : std::min<int64_t>(k_row_bytes, static_cast<int64_t>(kb_per) * 128);
                 const int64_t item_kb = ceil_div<int64_t>(item_k, bk);
                 int max_stages = static_cast<int>(std::max<int64_t>(2, std::min<int64_t>(32, 2 * item_kb)));
                 if (forced_stages >= 2) max_stages = std::min(max_stages, forced_stages);
                 GemmLayout lay{128u * halves, static_cast<uint32_t>(bn), static_cast<uint32_t>(bk), 2,
                                static_cast<uint32_t>(splits > 1 && !in_cluster ? 4 : d_elem), static_cast<uint32_t>(cluster),
                                p.b_mn_major ? 1u : 0u, static_cast<uint32_t>(p.gran_k_a), static_cast<uint32_t>(p.gran_k_b), 0u,
-                               static_cast<uint32_t>(ab_elem)};
+                               static_cast<uint32_t>(ab_elem), 2u, p.mxf4 ? 1u : 0u};
                 const GemmLayout unfitted = lay;
                 lay = fit_stages(lay, p.kind == DG_GEMM_K_GROUPED_CONTIGUOUS ? 0 : item_kb, max_stages);   // slices may be one K-block
                 if (lay.num_stages <= 2 && env_int("FORCE_STORE_BUFFERS") != 2) {
@@ -490,13 +500,15 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg, bool allow_cluster_sp
 GemmLayout layout_of(const Problem& p, const dg_gemm_config_t& cfg) {
     const bool split = cfg.num_splits > 1 && !cfg.split_in_cluster;
     const int64_t ab_elem = p.ab_bf16 ? 2 : 1;
+    const int64_t k_row_bytes = p.mxf4 ? p.k / 2 : p.k * ab_elem;
     const int64_t item_kb = p.kind == DG_GEMM_K_GROUPED_CONTIGUOUS ? 0 :
-                            ceil_div<int64_t>(std::min<int64_t>(p.k * ab_elem, static_cast<int64_t>(cfg.kb_per_split) * 128), cfg.block_k);
+                            ceil_div<int64_t>(std::min<int64_t>(k_row_bytes, static_cast<int64_t>(cfg.kb_per_split) * 128), cfg.block_k);
     GemmLayout lay{static_cast<uint32_t>(cfg.block_m), static_cast<uint32_t>(cfg.block_n), static_cast<uint32_t>(cfg.block_k),
                    static_cast<uint32_t>(cfg.num_stages), static_cast<uint32_t>((p.d_fp32 || split) ? 4 : (p.d_fp8 ? 1 : 2)),
                    static_cast<uint32_t>(cfg.cluster_size), p.b_mn_major ? 1u : 0u,
                    static_cast<uint32_t>(p.gran_k_a), static_cast<uint32_t>(p.gran_k_b),
-                   item_kb < cfg.num_stages ? 1u : 0u, static_cast<uint32_t>(ab_elem), static_cast<uint32_t>(cfg.store_buffers)};
+                   item_kb < cfg.num_stages ? 1u : 0u, static_cast<uint32_t>(ab_elem), static_cast<uint32_t>(cfg.store_buffers),
+                   p.mxf4 ? 1u : 0u};
     return lay;
 }
 
@@ -513,6 +525,7 @@ std::string generate_source(const Problem& p, const dg_gemm_config_t& cfg) {
       << "#define DG_AB_BF16 " << (p.ab_bf16 ? 1 : 0) << "\n"
       << "#define DG_A_FP4 " << (p.a_fp4 ? 1 : 0) << "\n"
       << "#define DG_B_FP4 " << (p.b_fp4 ? 1 : 0) << "\n"
+      << "#define DG_MXF4 " << (p.mxf4 ? 1 : 0) << "\n"
       << "#define DG_MAJOR_A " << (p.a_mn_major ? 1 : 0) << "\n"
       << "#define DG_MAJOR_B " << (p.b_mn_major ? 1 : 0) << "\n"
       << "#define DG_GRAN_K_A " << p.gran_k_a << "\n"
@@ -612,7 +625,8 @@ int get_plan(const Problem& p, Plan* plan) {
     const int fields[] = {p.kind, p.m, p.n, p.k, p.groups, static_cast<int>(p.a_fp4), static_cast<int>(p.b_fp4), static_cast<int>(p.ab_bf16),
                           static_cast<int>(p.d_fp32), static_cast<int>(p.d_fp8), static_cast<int>(p.accumulate), static_cast<int>(p.a_mn_major),
                           static_cast<int>(p.b_mn_major), p.gran_k_a, p.gran_k_b, p.expected_m, static_cast<int>(p.write_padding),
-                          static_cast<int>(p.k_psum), static_cast<int>(p.stochastic), p.reduce_batches > 1 ? 1 : 0, dg_get_num_sms(), state().mk_alignment};
+                          static_cast<int>(p.k_psum), static_cast<int>(p.stochastic), p.reduce_batches > 1 ? 1 : 0, dg_get_num_sms(), state().mk_alignment,
+                          static_cast<int>(p.mxf4)};
     // The key is sized from what goes into it: every field of the descriptor and every setting the choice reads
     constexpr size_t kNumFields = sizeof(fields) / sizeof(fields[0]), kNumEnv = sizeof(kEnvNames) / sizeof(kEnvNames[0]);
     using PlanKey = std::array<int, kNumFields + kNumEnv>;
@@ -749,14 +763,20 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
                                        p.a_fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8;
     const CUtensorMapDataType b_type = p.ab_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 :
                                        p.b_fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8;
-    if (!p.a_mn_major) {
+    if (p.mxf4) {
+        // packed operands as plain byte matrices [rows, K / 2]: a 128-byte box row is 256 elements of K
+        if ((rc = encode_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->a, p.k / 2, a_rows, a->lda, 128, cfg.block_m, CU_TENSOR_MAP_SWIZZLE_128B)) != DG_OK) return rc;
+    } else if (!p.a_mn_major) {
         if ((rc = encode_2d(&tm_a, a_type, a->a, k_inner, a_rows, a->lda * ab_elem, box_k, cfg.block_m, k_major_swizzle,
                             nb_ab, bs_a * ab_elem)) != DG_OK) return rc;
     } else {
         if ((rc = encode_2d(&tm_a, a_type, a->a, p.m, p.k, a->lda * ab_elem, atom_mn, box_k, CU_TENSOR_MAP_SWIZZLE_128B,
                             nb, bs_a * ab_elem)) != DG_OK) return rc;
     }
-    if (!p.b_mn_major) {
+    if (p.mxf4) {
+        if ((rc = encode_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->b, p.k / 2, b_rows, a->ldb, 128, cfg.block_n / cfg.cluster_size,
+                            CU_TENSOR_MAP_SWIZZLE_128B)) != DG_OK) return rc;
+    } else if (!p.b_mn_major) {
         if ((rc = encode_2d(&tm_b, b_type, a->b, k_inner, b_rows, a->ldb * ab_elem, box_k, cfg.block_n / cfg.cluster_size, k_major_swizzle,
                             nb_ab, bs_b * ab_elem)) != DG_OK) return rc;
     } else {
@@ -767,9 +787,10 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
     if (p.ab_bf16) {
         tm_sfa = tm_sfb = tm_a;                  // never used: the BF16 kernel has no scale loads
     } else {
-        if ((rc = encode_2d(&tm_sfa, CU_TENSOR_MAP_DATA_TYPE_INT32, a->sfa, p.m, sfa_rows, a->sfa_pitch * 4, cfg.block_m, 1,
+        // (one packed word per row and K-block, two for the 256-element stages of kind::mxf4)
+        if ((rc = encode_2d(&tm_sfa, CU_TENSOR_MAP_DATA_TYPE_INT32, a->sfa, p.m, sfa_rows, a->sfa_pitch * 4, cfg.block_m, lay.sfa_words(),
                             CU_TENSOR_MAP_SWIZZLE_NONE, nb, bs_sfa)) != DG_OK) return rc;
-        if ((rc = encode_2d(&tm_sfb, CU_TENSOR_MAP_DATA_TYPE_INT32, a->sfb, p.n, sfb_rows, a->sfb_pitch * 4, lay.sf_block_n(), 1,
+        if ((rc = encode_2d(&tm_sfb, CU_TENSOR_MAP_DATA_TYPE_INT32, a->sfb, p.n, sfb_rows, a->sfb_pitch * 4, lay.sf_block_n(), lay.sfb_words(),
                             CU_TENSOR_MAP_SWIZZLE_NONE, nb, bs_sfb)) != DG_OK) return rc;
     }
     const CUtensorMapSwizzle d_swizzle = lay.store_row_bytes() == 128 ? CU_TENSOR_MAP_SWIZZLE_128B :
