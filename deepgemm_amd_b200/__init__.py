@@ -24,7 +24,7 @@ from .api import (  # noqa: F401
     get_m_alignment_for_contiguous_layout, get_k_alignment_for_contiguous_layout,
     init, shutdown, set_num_sms, get_num_sms, set_tc_util, get_tc_util, set_pdl, get_pdl,
     use_deterministic_algorithms, set_ignore_compile_dims, set_block_size_multiple_of,
-    get_gemm_config, precompile_gemm, kernel_status, reset_kernel_status, per_token_cast, selftest_bounded_wait,
+    get_gemm_config, precompile_gemm, kernel_status, reset_kernel_status, per_token_cast, selftest_bounded_wait, HAS_COMPILED_BINDING,
 )
 
 __version__ = "0.1.0"

@@ -9,6 +9,7 @@ transformed scale tensors only; all compute runs in the library's CUDA kernels.
 from __future__ import annotations
 
 import ctypes as C
+import os as _os
 import threading
 from typing import Optional, Sequence, Tuple, Union
 
@@ -17,6 +18,17 @@ import torch
 from . import _lib
 from ._lib import GemmArgs, GemmConfig, check, lib
 from .epilogue import Alpha, BF16StochasticRounding, FP8Quantization, Identity
+
+# The compiled binding (csrc/python_binding.cpp) serves the calls a serving loop repeats: packed scales, no epilogue
+# object.  It is built with the library; without it (or with DG_DISABLE_COMPILED_BINDING=1) the same calls go through the
+# ctypes path below, which applies the same checks.
+try:
+    if _os.environ.get("DG_DISABLE_COMPILED_BINDING", "0") not in ("", "0"):
+        raise ImportError("disabled by DG_DISABLE_COMPILED_BINDING")
+    from . import _C
+except ImportError:
+    _C = None
+HAS_COMPILED_BINDING = _C is not None
 
 kPackedFP4 = torch.int8          # csrc/utils/math.hpp:11
 Recipe3 = Tuple[int, int, int]
@@ -302,6 +314,28 @@ def _call_key(name, a_data, a_sf, b_data, b_sf, d, recipe, recipe_a, recipe_b, *
             None if recipe_b is None else tuple(recipe_b), *options)
 
 
+def _packed_grans(a_sf, b_sf, recipe, recipe_a, recipe_b, disable_ue8m0_cast):
+    """(gran_k_a, gran_k_b) when both scale tensors arrive packed (int32, one scale per row of MN) and the recipe is one
+    the compiled binding serves (csrc/apis/layout.hpp:11-87 reduce to layout checks then); None sends the call through
+    the general path, which also words every error."""
+    if _C is None or disable_ue8m0_cast or a_sf.dtype != torch.int or b_sf.dtype != torch.int:
+        return None
+    if recipe_a is None and recipe_b is None:
+        if recipe is None:
+            return 128, 128                          # default recipe for packed scales: (1, 1, 128)
+        recipe = tuple(recipe)
+        if len(recipe) == 3 and recipe[0] == 1 and recipe[1] == 1 and recipe[2] in (32, 128):
+            return recipe[2], recipe[2]
+        return None
+    if recipe is not None or recipe_a is None or recipe_b is None:
+        return None
+    recipe_a, recipe_b = tuple(recipe_a), tuple(recipe_b)
+    if len(recipe_a) == 2 and len(recipe_b) == 2 and recipe_a[0] == 1 and recipe_b[0] == 1 \
+            and recipe_a[1] in (32, 128) and recipe_b[1] in (32, 128):
+        return recipe_a[1], recipe_b[1]
+    return None
+
+
 def _remember_call(key, args) -> None:
     if key is not None:
         cache = _validated_calls()
@@ -420,6 +454,10 @@ def fp8_fp4_gemm_nt(a, b, d, c=None, recipe=None, recipe_a=None, recipe_b=None, 
     (a_data, a_sf), (b_data, b_sf) = a, b
     key = None
     if (c is None or c is d) and epilogue is None:
+        grans = _packed_grans(a_sf, b_sf, recipe, recipe_a, recipe_b, disable_ue8m0_cast)
+        if grans is not None:
+            _C.dense_nt(a_data, a_sf, b_data, b_sf, d, grans[0], grans[1], c is not None, alpha)
+            return
         key = _call_key("dense", a_data, a_sf, b_data, b_sf, d, recipe, recipe_a, recipe_b, c is None, disable_ue8m0_cast, alpha is None)
         args = _validated_calls().get(key) if key is not None else None
         if args is not None:
@@ -802,6 +840,11 @@ def m_grouped_fp8_fp4_gemm_nt_contiguous(a, b, d, grouped_layout, recipe=None, r
     (a_data, a_sf), (b_data, b_sf) = a, b
     key = None
     if epilogue is None:
+        grans = _packed_grans(a_sf, b_sf, recipe, recipe_a, recipe_b, disable_ue8m0_cast)
+        if grans is not None:
+            _C.m_grouped_contiguous(a_data, a_sf, b_data, b_sf, d, grouped_layout, grans[0], grans[1], use_psum_layout,
+                                    ensure_zero_padding, expected_m_for_psum_layout)
+            return
         key = _call_key("contiguous", a_data, a_sf, b_data, b_sf, d, recipe, recipe_a, recipe_b, grouped_layout.shape, grouped_layout.stride(),
                         grouped_layout.dtype, disable_ue8m0_cast, use_psum_layout, ensure_zero_padding, expected_m_for_psum_layout)
         args = _validated_calls().get(key) if key is not None else None
@@ -858,6 +901,10 @@ def m_grouped_fp8_fp4_gemm_nt_masked(a, b, d, masked_m, expected_m: int, recipe=
     (a_data, a_sf), (b_data, b_sf) = a, b
     key = None
     if epilogue is None:
+        grans = _packed_grans(a_sf, b_sf, recipe, recipe_a, recipe_b, disable_ue8m0_cast)
+        if grans is not None:
+            _C.m_grouped_masked(a_data, a_sf, b_data, b_sf, d, masked_m, expected_m, grans[0], grans[1])
+            return
         key = _call_key("masked", a_data, a_sf, b_data, b_sf, d, recipe, recipe_a, recipe_b, masked_m.shape, masked_m.stride(), masked_m.dtype,
                         disable_ue8m0_cast, expected_m)
         args = _validated_calls().get(key) if key is not None else None
@@ -1061,14 +1108,15 @@ m_grouped_fp4_gemm_nt_masked = m_grouped_fp8_fp4_gemm_nt_masked
 # ------------------------------------------------------------------------------------------------
 def get_gemm_config(kind: int, m: int, n: int, k: int, num_groups: int = 1, expected_m: int = 0,
                     b_is_fp4: bool = False, d_is_fp32: bool = False, gran_k_a: int = 128, gran_k_b: int = 128,
-                    d_is_fp8: bool = False) -> dict:
+                    d_is_fp8: bool = False, a_is_fp4: bool = False) -> dict:
     """The tile configuration the heuristics choose for a problem (host only, needs no GPU)."""
     args = GemmArgs()
     args.m, args.n, args.k, args.num_groups = m, n, k, num_groups
-    args.a_dtype, args.b_dtype = _lib.DG_FP8_E4M3, (_lib.DG_FP4_E2M1_X2 if b_is_fp4 else _lib.DG_FP8_E4M3)
+    args.a_dtype = _lib.DG_FP4_E2M1_X2 if a_is_fp4 else _lib.DG_FP8_E4M3
+    args.b_dtype = _lib.DG_FP4_E2M1_X2 if b_is_fp4 else _lib.DG_FP8_E4M3
     args.d_dtype = _lib.DG_FP32 if d_is_fp32 else (_lib.DG_FP8_E4M3 if d_is_fp8 else _lib.DG_BF16)
     args.sfd_pitch = align(m, 4)
-    args.lda, args.ldb, args.ldd = k, (k // 2 if b_is_fp4 else k), n
+    args.lda, args.ldb, args.ldd = (k // 2 if a_is_fp4 else k), (k // 2 if b_is_fp4 else k), n
     args.sfa_pitch, args.sfb_pitch = align(m, 4), align(n, 4)
     args.gran_k_a, args.gran_k_b = gran_k_a, gran_k_b
     args.expected_m = expected_m
@@ -1079,14 +1127,15 @@ def get_gemm_config(kind: int, m: int, n: int, k: int, num_groups: int = 1, expe
 
 def precompile_gemm(kind: int, m: int, n: int, k: int, num_groups: int = 1, expected_m: int = 0,
                     b_is_fp4: bool = False, d_is_fp32: bool = False, accumulate: bool = False,
-                    gran_k_a: int = 128, gran_k_b: int = 128, d_is_fp8: bool = False) -> None:
+                    gran_k_a: int = 128, gran_k_b: int = 128, d_is_fp8: bool = False, a_is_fp4: bool = False) -> None:
     """Compile the kernel a GEMM of this shape would use into the cache (needs nvcc, no GPU)."""
     args = GemmArgs()
     args.m, args.n, args.k, args.num_groups = m, n, k, num_groups
-    args.a_dtype, args.b_dtype = _lib.DG_FP8_E4M3, (_lib.DG_FP4_E2M1_X2 if b_is_fp4 else _lib.DG_FP8_E4M3)
+    args.a_dtype = _lib.DG_FP4_E2M1_X2 if a_is_fp4 else _lib.DG_FP8_E4M3
+    args.b_dtype = _lib.DG_FP4_E2M1_X2 if b_is_fp4 else _lib.DG_FP8_E4M3
     args.d_dtype = _lib.DG_FP32 if d_is_fp32 else (_lib.DG_FP8_E4M3 if d_is_fp8 else _lib.DG_BF16)
     args.sfd_pitch = align(m, 4)
-    args.lda, args.ldb, args.ldd = k, (k // 2 if b_is_fp4 else k), n
+    args.lda, args.ldb, args.ldd = (k // 2 if a_is_fp4 else k), (k // 2 if b_is_fp4 else k), n
     args.sfa_pitch, args.sfb_pitch = align(m, 4), align(n, 4)
     args.gran_k_a, args.gran_k_b = gran_k_a, gran_k_b
     args.expected_m = expected_m

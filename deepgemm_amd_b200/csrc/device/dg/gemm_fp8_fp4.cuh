@@ -137,6 +137,7 @@ constexpr bool kBatchReduce = DG_BATCH_REDUCE != 0;
 constexpr uint32_t kSplitCluster = DG_SPLIT_CLUSTER;   // CTAs of a cluster sharing one output tile along K (1 = off)
 
 constexpr uint32_t kMHalves    = DG_M_HALVES;      // 128-row MMAs per CTA and K-block (1 or 2)
+constexpr uint32_t kL2Hint     = DG_L2_HINT;
 
 constexpr uint32_t UMMA_M = 128 * kCluster, UMMA_N = BLOCK_N, UMMA_K = 32;
 constexpr uint32_t LOAD_BLOCK_N = BLOCK_N / kCluster;      // rows of B each CTA loads
@@ -197,6 +198,10 @@ static_assert(kSplitCluster == 1 || (kGemmType == kDense && !kSplitK && kCluster
 // issues the copies / the tcgen05 instructions, the warp re-converges every K-block).  A lone lane inside a divergent
 // branch ran the same loops measurably slower: 10 % of the kernel time with 128-row CTA pairs, 1-2 % with 256-row
 // tiles.  0 restores the single-lane form (kept for comparison).
+// L2 eviction hints on the operand loads (0 none; 1 keep A, stream B; 2 keep B, stream A)
+#ifndef DG_L2_HINT
+#define DG_L2_HINT 0
+#endif
 #ifndef DG_PRODUCER_WHOLE_WARP
 #define DG_PRODUCER_WHOLE_WARP 1
 #endif
@@ -452,6 +457,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
             constexpr bool kProducerWholeWarp = DG_PRODUCER_WHOLE_WARP != 0;
             if (kProducerWholeWarp || lane == 0) {
                 bool ok = true;
+                [[maybe_unused]] const uint64_t policy_keep = kL2Hint ? l2_policy_evict_last() : 0, policy_stream = kL2Hint ? l2_policy_evict_first() : 0;
                 DG_PROF_VAR(prof_wait);
                 DG_PROF_BEGIN(prof_t0);
                 while (ok && sched.next(tile)) {
@@ -491,8 +497,16 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                         if (kCluster == 1 || is_leader) mbar_arrive_expect_tx(full_bar(stage), kTxBytesAB);
                         else mbar_arrive_cluster(load_bar);
                         auto load = [&](uint32_t dst, const CUtensorMap* map, uint32_t x, uint32_t y) {
-                            if constexpr (kCluster == 1) tma_in(dst, map, load_bar, x, y, tile.group);
-                            else tma_load_2d_2cta(dst, map, load_bar, static_cast<int32_t>(x), static_cast<int32_t>(y));
+                            if constexpr (kL2Hint != 0 && kGemmType != kBatched) {
+                                // DG_L2_HINT 1: A stays (evict_last), B streams (evict_first); 2: the other way round
+                                const uint64_t policy = ((map == &tm_a) == (kL2Hint == 1)) ? policy_keep : policy_stream;
+                                if constexpr (kCluster == 1) tma_load_2d_hint(dst, map, load_bar, static_cast<int32_t>(x), static_cast<int32_t>(y), policy);
+                                else tma_load_2d_2cta_hint(dst, map, load_bar, static_cast<int32_t>(x), static_cast<int32_t>(y), policy);
+                            } else if constexpr (kCluster == 1) {
+                                tma_in(dst, map, load_bar, x, y, tile.group);
+                            } else {
+                                tma_load_2d_2cta(dst, map, load_bar, static_cast<int32_t>(x), static_cast<int32_t>(y));
+                            }
                         };
                         // K-major: x = K, y = row.  MN-major: x = row (column of the stored matrix), y = K (+ the group's K offset)
                         if constexpr (kBatchReduce) {

@@ -546,6 +546,7 @@ std::string generate_source(const Problem& p, const dg_gemm_config_t& cfg) {
       << "#define DG_EPILOGUE_BACKOFF_NS " << env_int("EPILOGUE_BACKOFF_NS", 0) << "\n"
       << "#define DG_MMA_WHOLE_WARP " << env_int("MMA_WHOLE_WARP", 1) << "\n"
       << "#define DG_PRODUCER_WHOLE_WARP " << env_int("PRODUCER_WHOLE_WARP", 1) << "\n"
+      << "#define DG_L2_HINT " << env_int("L2_HINT", 0) << "\n"
       << "#include <dg/gemm_fp8_fp4.cuh>\n";
     return s.str();
 }
@@ -621,7 +622,7 @@ struct Plan {
 int get_plan(const Problem& p, Plan* plan) {
     static const char* kEnvNames[] = {"FORCE_BLOCK_N", "FORCE_CLUSTER", "FORCE_SPLIT_K", "FORCE_BLOCK_M", "FORCE_BLOCK_K",
                                       "FORCE_NUM_STAGES", "FORCE_RASTER_GROUP", "PROFILE", "FORCE_SPLIT_CLUSTER", "FORCE_SWAP_AB", "FORCE_STORE_BUFFERS",
-                                      "EPILOGUE_BACKOFF_NS", "MMA_WHOLE_WARP", "PRODUCER_WHOLE_WARP"};
+                                      "EPILOGUE_BACKOFF_NS", "MMA_WHOLE_WARP", "PRODUCER_WHOLE_WARP", "L2_HINT"};
     const int fields[] = {p.kind, p.m, p.n, p.k, p.groups, static_cast<int>(p.a_fp4), static_cast<int>(p.b_fp4), static_cast<int>(p.ab_bf16),
                           static_cast<int>(p.d_fp32), static_cast<int>(p.d_fp8), static_cast<int>(p.accumulate), static_cast<int>(p.a_mn_major),
                           static_cast<int>(p.b_mn_major), p.gran_k_a, p.gran_k_b, p.expected_m, static_cast<int>(p.write_padding),
