@@ -314,28 +314,6 @@ def _call_key(name, a_data, a_sf, b_data, b_sf, d, recipe, recipe_a, recipe_b, *
             None if recipe_b is None else tuple(recipe_b), *options)
 
 
-def _packed_grans(a_sf, b_sf, recipe, recipe_a, recipe_b, disable_ue8m0_cast):
-    """(gran_k_a, gran_k_b) when both scale tensors arrive packed (int32, one scale per row of MN) and the recipe is one
-    the compiled binding serves (csrc/apis/layout.hpp:11-87 reduce to layout checks then); None sends the call through
-    the general path, which also words every error."""
-    if _C is None or disable_ue8m0_cast or a_sf.dtype != torch.int or b_sf.dtype != torch.int:
-        return None
-    if recipe_a is None and recipe_b is None:
-        if recipe is None:
-            return 128, 128                          # default recipe for packed scales: (1, 1, 128)
-        recipe = tuple(recipe)
-        if len(recipe) == 3 and recipe[0] == 1 and recipe[1] == 1 and recipe[2] in (32, 128):
-            return recipe[2], recipe[2]
-        return None
-    if recipe is not None or recipe_a is None or recipe_b is None:
-        return None
-    recipe_a, recipe_b = tuple(recipe_a), tuple(recipe_b)
-    if len(recipe_a) == 2 and len(recipe_b) == 2 and recipe_a[0] == 1 and recipe_b[0] == 1 \
-            and recipe_a[1] in (32, 128) and recipe_b[1] in (32, 128):
-        return recipe_a[1], recipe_b[1]
-    return None
-
-
 def _remember_call(key, args) -> None:
     if key is not None:
         cache = _validated_calls()
@@ -451,13 +429,11 @@ def _resolve_sfd(epilogue, c, d, m: int, n: int):
 def fp8_fp4_gemm_nt(a, b, d, c=None, recipe=None, recipe_a=None, recipe_b=None, compiled_dims: str = "nk",
                     disable_ue8m0_cast: bool = False, alpha: Optional[float] = None, epilogue=None) -> None:
     """D[M,N] = C + alpha * A[M,K] @ B[N,K]^T with a = (data, sf), b = (data, sf) (csrc/apis/gemm.hpp:78-133)."""
+    if _C is not None and _C.dense_nt(a, b, d, c, recipe, recipe_a, recipe_b, disable_ue8m0_cast, alpha, epilogue):
+        return
     (a_data, a_sf), (b_data, b_sf) = a, b
     key = None
     if (c is None or c is d) and epilogue is None:
-        grans = _packed_grans(a_sf, b_sf, recipe, recipe_a, recipe_b, disable_ue8m0_cast)
-        if grans is not None:
-            _C.dense_nt(a_data, a_sf, b_data, b_sf, d, grans[0], grans[1], c is not None, alpha)
-            return
         key = _call_key("dense", a_data, a_sf, b_data, b_sf, d, recipe, recipe_a, recipe_b, c is None, disable_ue8m0_cast, alpha is None)
         args = _validated_calls().get(key) if key is not None else None
         if args is not None:
@@ -837,14 +813,12 @@ def m_grouped_fp8_fp4_gemm_nt_contiguous(a, b, d, grouped_layout, recipe=None, r
     per row (-1 on padding rows) or, with use_psum_layout, the row where each group ends: group g then occupies rows
     [align(grouped_layout[g-1], mk_alignment), grouped_layout[g]).  With ensure_zero_padding the padding rows of D up to
     the next aligned row are written too (zero for zero A padding); otherwise rows outside the groups are untouched."""
+    if _C is not None and _C.m_grouped_contiguous(a, b, d, grouped_layout, recipe, recipe_a, recipe_b, disable_ue8m0_cast, use_psum_layout,
+                                                  ensure_zero_padding, expected_m_for_psum_layout, epilogue):
+        return
     (a_data, a_sf), (b_data, b_sf) = a, b
     key = None
     if epilogue is None:
-        grans = _packed_grans(a_sf, b_sf, recipe, recipe_a, recipe_b, disable_ue8m0_cast)
-        if grans is not None:
-            _C.m_grouped_contiguous(a_data, a_sf, b_data, b_sf, d, grouped_layout, grans[0], grans[1], use_psum_layout,
-                                    ensure_zero_padding, expected_m_for_psum_layout)
-            return
         key = _call_key("contiguous", a_data, a_sf, b_data, b_sf, d, recipe, recipe_a, recipe_b, grouped_layout.shape, grouped_layout.stride(),
                         grouped_layout.dtype, disable_ue8m0_cast, use_psum_layout, ensure_zero_padding, expected_m_for_psum_layout)
         args = _validated_calls().get(key) if key is not None else None
@@ -898,13 +872,11 @@ def m_grouped_fp8_fp4_gemm_nt_masked(a, b, d, masked_m, expected_m: int, recipe=
                                      compiled_dims: str = "nk", disable_ue8m0_cast: bool = False, epilogue=None) -> None:
     """D[g,:masked_m[g],:] = A[g,:masked_m[g],:] @ B[g]^T; masked_m stays on the device, so the call is
     capturable in a CUDA graph; rows at or beyond masked_m[g] are not written (csrc/apis/gemm.hpp:269-318)."""
+    if _C is not None and _C.m_grouped_masked(a, b, d, masked_m, expected_m, recipe, recipe_a, recipe_b, disable_ue8m0_cast, epilogue):
+        return
     (a_data, a_sf), (b_data, b_sf) = a, b
     key = None
     if epilogue is None:
-        grans = _packed_grans(a_sf, b_sf, recipe, recipe_a, recipe_b, disable_ue8m0_cast)
-        if grans is not None:
-            _C.m_grouped_masked(a_data, a_sf, b_data, b_sf, d, masked_m, expected_m, grans[0], grans[1])
-            return
         key = _call_key("masked", a_data, a_sf, b_data, b_sf, d, recipe, recipe_a, recipe_b, masked_m.shape, masked_m.stride(), masked_m.dtype,
                         disable_ue8m0_cast, expected_m)
         args = _validated_calls().get(key) if key is not None else None

@@ -4,6 +4,8 @@
 
 #include <dlfcn.h>
 
+#include <atomic>
+
 namespace dg {
 
 std::string& last_error() {
@@ -61,9 +63,14 @@ std::string cu_error(CUresult r) {
 }
 
 int device_num_sms() {
+    // asked on every GEMM call (the count is part of the plan's key): the attribute of a device never changes
+    constexpr int kMaxDevices = 64;
+    static std::atomic<int> counts[kMaxDevices];
     int dev = 0, n = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return 0; }
+    if (dev >= 0 && dev < kMaxDevices && (n = counts[dev].load(std::memory_order_relaxed)) > 0) return n;
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) { cudaGetLastError(); return 0; }
+    if (dev >= 0 && dev < kMaxDevices) counts[dev].store(n, std::memory_order_relaxed);
     return n;
 }
 

@@ -3,19 +3,24 @@
 // C++ on torch tensors, so that a call costs the host a few microseconds instead of an interpreter's worth of attribute
 // lookups.  It is the counterpart of the reference's pybind11 module (csrc/python_api.cpp:24-47) for the calls a serving
 // loop makes: dense, m-grouped contiguous and m-grouped masked GEMMs whose scales arrive already packed (int32 UE8M0,
-// MN-major), without an epilogue object.  Everything else (FP32 scales that need their transform kernel, epilogue
-// objects, the einsum / k-grouped / BF16 families, settings) stays in deepgemm_amd_b200/api.py, which calls into this
-// module when the call qualifies.  The checks and their messages are the ones api.py applies to the same call.
+// MN-major), without an epilogue object.  Each function takes the Python call's arguments as they are and returns
+// false, untouched, when the call is not of that kind; deepgemm_amd_b200/api.py then runs it through its own path, as it
+// does everything else (FP32 scales that need their transform kernel, epilogue objects, the einsum / k-grouped / BF16
+// families, settings).  The checks and their messages are the ones api.py applies to the same call.
 #include <torch/extension.h>
 
 #include <c10/cuda/CUDAStream.h>
 
 #include <optional>
 #include <sstream>
+#include <utility>
+#include <vector>
 #include <stdexcept>
 #include <string>
 
 #include "../../include/deepgemm_b200.h"
+
+namespace py = pybind11;
 
 namespace {
 
@@ -93,6 +98,43 @@ void fill_common(dg_gemm_args_t& g, const torch::Tensor& a, const torch::Tensor&
     g.stream = c10::cuda::getCurrentCUDAStream().stream();
 }
 
+// The granularities along K when both scale tensors arrive packed (int32, one scale per row of MN) and the recipe is
+// one this module serves; csrc/apis/layout.hpp:11-87 reduce to layout checks then.  false sends the call back to the
+// interpreter path, which also words every recipe error.
+bool packed_grans(const torch::Tensor& sfa, const torch::Tensor& sfb, const py::object& recipe, const py::object& recipe_a,
+                  const py::object& recipe_b, bool disable_ue8m0_cast, int* gran_k_a, int* gran_k_b) {
+    if (disable_ue8m0_cast || sfa.scalar_type() != torch::kInt || sfb.scalar_type() != torch::kInt) return false;
+    const auto ints = [](const py::object& o, std::vector<int>* out) {
+        try {
+            for (const auto& item : py::reinterpret_borrow<py::sequence>(o)) out->push_back(py::cast<int>(item));
+            return true;
+        } catch (const std::exception&) {
+            return false;
+        }
+    };
+    const auto fine = [](int g) { return g == 32 || g == 128; };
+    if (recipe_a.is_none() && recipe_b.is_none()) {
+        if (recipe.is_none()) {
+            *gran_k_a = *gran_k_b = 128;              // default recipe for packed scales: (1, 1, 128)
+            return true;
+        }
+        std::vector<int> r;
+        if (!ints(recipe, &r) || r.size() != 3 || r[0] != 1 || r[1] != 1 || !fine(r[2])) return false;
+        *gran_k_a = *gran_k_b = r[2];
+        return true;
+    }
+    if (!recipe.is_none() || recipe_a.is_none() || recipe_b.is_none()) return false;
+    std::vector<int> ra, rb;
+    if (!ints(recipe_a, &ra) || !ints(recipe_b, &rb) || ra.size() != 2 || rb.size() != 2 || ra[0] != 1 || rb[0] != 1 ||
+        !fine(ra[1]) || !fine(rb[1]))
+        return false;
+    *gran_k_a = ra[1];
+    *gran_k_b = rb[1];
+    return true;
+}
+
+using TensorPair = std::pair<torch::Tensor, torch::Tensor>;
+
 void check_rc(int rc) {
     if (rc != DG_OK) {
         const char* msg = dg_last_error();
@@ -100,9 +142,17 @@ void check_rc(int rc) {
     }
 }
 
-// fp8_fp4_gemm_nt with packed scales: D = [D +] alpha A B^T  (csrc/apis/gemm.hpp:78-133)
-void dense_nt(const torch::Tensor& a, const torch::Tensor& sfa, const torch::Tensor& b, const torch::Tensor& sfb, const torch::Tensor& d,
-              int gran_k_a, int gran_k_b, bool accumulate, std::optional<double> alpha) {
+// fp8_fp4_gemm_nt with packed scales: D = [D +] alpha A B^T  (csrc/apis/gemm.hpp:78-133).  Takes the arguments of the
+// Python function as they come; returns false, having done nothing, when the call is not one this module serves.
+bool dense_nt(const TensorPair& a_pair, const TensorPair& b_pair, const torch::Tensor& d, const std::optional<torch::Tensor>& c,
+              const py::object& recipe, const py::object& recipe_a, const py::object& recipe_b, bool disable_ue8m0_cast,
+              std::optional<double> alpha, const py::object& epilogue) {
+    const torch::Tensor &a = a_pair.first, &sfa = a_pair.second, &b = b_pair.first, &sfb = b_pair.second;
+    int gran_k_a = 0, gran_k_b = 0;
+    if (!epilogue.is_none() || (c.has_value() && c->unsafeGetTensorImpl() != d.unsafeGetTensorImpl()) ||
+        !packed_grans(sfa, sfb, recipe, recipe_a, recipe_b, disable_ue8m0_cast, &gran_k_a, &gran_k_b))
+        return false;
+    const bool accumulate = c.has_value();
     const Operand oa = describe(a, 2), ob = describe(b, 2);
     if (oa.dtype == DG_FP4_E2M1_X2 && ob.dtype == DG_FP4_E2M1_X2)
         DG_BIND_REQUIRE(oa.major == DG_MAJOR_K && ob.major == DG_MAJOR_K, "major == cute::UMMA::Major::K");
@@ -112,10 +162,10 @@ void dense_nt(const torch::Tensor& a, const torch::Tensor& sfa, const torch::Ten
     DG_BIND_REQUIRE(m == d.size(0) && n == d.size(1) && k == ob.k, "m == m_ and n == n_ and k == k_");
     DG_BIND_REQUIRE(d.scalar_type() == torch::kBFloat16 || d.scalar_type() == torch::kFloat,
                     "d.scalar_type() == torch::kBFloat16 or d.scalar_type() == torch::kFloat");
-    if (m == 0 || n == 0) return;                    // early_return, gemm.hpp:17-53
+    if (m == 0 || n == 0) return true;               // early_return, gemm.hpp:17-53
     if (k == 0) {
         if (!accumulate) d.zero_();
-        return;
+        return true;
     }
     check_packed_sf(sfa, m, k, gran_k_a, std::nullopt);
     check_packed_sf(sfb, n, k, gran_k_b, std::nullopt);
@@ -127,12 +177,17 @@ void dense_nt(const torch::Tensor& a, const torch::Tensor& sfa, const torch::Ten
     g.has_alpha = alpha.has_value() ? 1 : 0;
     g.alpha = alpha.has_value() ? static_cast<float>(*alpha) : 1.0f;
     check_rc(dg_fp8_fp4_gemm(&g));
+    return true;
 }
 
 // m_grouped_fp8_fp4_gemm_nt_contiguous with packed scales (csrc/apis/gemm.hpp:181-250)
-void m_grouped_contiguous(const torch::Tensor& a, const torch::Tensor& sfa, const torch::Tensor& b, const torch::Tensor& sfb,
-                          const torch::Tensor& d, const torch::Tensor& grouped_layout, int gran_k_a, int gran_k_b,
-                          bool use_psum_layout, bool ensure_zero_padding, std::optional<int64_t> expected_m_for_psum_layout) {
+bool m_grouped_contiguous(const TensorPair& a_pair, const TensorPair& b_pair, const torch::Tensor& d, const torch::Tensor& grouped_layout,
+                          const py::object& recipe, const py::object& recipe_a, const py::object& recipe_b, bool disable_ue8m0_cast,
+                          bool use_psum_layout, bool ensure_zero_padding, std::optional<int64_t> expected_m_for_psum_layout,
+                          const py::object& epilogue) {
+    const torch::Tensor &a = a_pair.first, &sfa = a_pair.second, &b = b_pair.first, &sfb = b_pair.second;
+    int gran_k_a = 0, gran_k_b = 0;
+    if (!epilogue.is_none() || !packed_grans(sfa, sfb, recipe, recipe_a, recipe_b, disable_ue8m0_cast, &gran_k_a, &gran_k_b)) return false;
     const Operand oa = describe(a, 2);
     DG_BIND_REQUIRE(oa.major == DG_MAJOR_K, "major_a == cute::UMMA::Major::K");
     DG_BIND_REQUIRE(grouped_layout.is_contiguous(), "grouped_layout.is_contiguous()");
@@ -151,7 +206,7 @@ void m_grouped_contiguous(const torch::Tensor& a, const torch::Tensor& sfa, cons
         DG_BIND_REQUIRE(!expected_m_for_psum_layout.has_value(), "not expected_m_for_psum_layout.has_value()");
     }
     check_cd(d);
-    if (m == 0) return;
+    if (m == 0) return true;
     check_packed_sf(sfa, m, k, gran_k_a, std::nullopt);
     check_packed_sf(sfb, n, k, gran_k_b, num_groups);
     dg_gemm_args_t g{};
@@ -163,11 +218,16 @@ void m_grouped_contiguous(const torch::Tensor& a, const torch::Tensor& sfa, cons
     g.use_psum_layout = use_psum_layout ? 1 : 0;
     g.ensure_zero_padding = use_psum_layout && ensure_zero_padding ? 1 : 0;
     check_rc(dg_m_grouped_fp8_fp4_gemm_contiguous(&g));
+    return true;
 }
 
 // m_grouped_fp8_fp4_gemm_nt_masked with packed scales (csrc/apis/gemm.hpp:269-318)
-void m_grouped_masked(const torch::Tensor& a, const torch::Tensor& sfa, const torch::Tensor& b, const torch::Tensor& sfb,
-                      const torch::Tensor& d, const torch::Tensor& masked_m, int64_t expected_m, int gran_k_a, int gran_k_b) {
+bool m_grouped_masked(const TensorPair& a_pair, const TensorPair& b_pair, const torch::Tensor& d, const torch::Tensor& masked_m,
+                      int64_t expected_m, const py::object& recipe, const py::object& recipe_a, const py::object& recipe_b,
+                      bool disable_ue8m0_cast, const py::object& epilogue) {
+    const torch::Tensor &a = a_pair.first, &sfa = a_pair.second, &b = b_pair.first, &sfb = b_pair.second;
+    int gran_k_a = 0, gran_k_b = 0;
+    if (!epilogue.is_none() || !packed_grans(sfa, sfb, recipe, recipe_a, recipe_b, disable_ue8m0_cast, &gran_k_a, &gran_k_b)) return false;
     DG_BIND_REQUIRE(a.dim() == 3 && b.dim() == 3 && d.dim() == 3, "t.dim() == N");
     const Operand oa = describe(a, 3), ob = describe(b, 3);
     DG_BIND_REQUIRE(oa.major == DG_MAJOR_K && ob.major == DG_MAJOR_K, "major_a == cute::UMMA::Major::K and major_b == cute::UMMA::Major::K");
@@ -190,6 +250,7 @@ void m_grouped_masked(const torch::Tensor& a, const torch::Tensor& sfa, const to
     g.grouped_layout = masked_m.data_ptr<int32_t>();
     g.expected_m = static_cast<int32_t>(expected_m);
     check_rc(dg_m_grouped_fp8_fp4_gemm_masked(&g));
+    return true;
 }
 
 }  // namespace

@@ -18,25 +18,35 @@ def test_binding_is_built_and_loaded():
 
 
 def test_binding_words_its_failures_like_the_reference():
-    t = torch.zeros(4, 4)
+    t, sf = torch.zeros(4, 4), torch.zeros(4, 1, dtype=torch.int)
     with pytest.raises(RuntimeError, match=r"Assertion error \(deepgemm_amd_b200/csrc/python_binding.cpp:\d+\): t.is_cuda\(\)"):
-        api._C.dense_nt(t, t, t, t, t, 128, 128, False, None)
+        api._C.dense_nt((t, sf), (t, sf), t, None, None, None, None, False, None, None)
     with pytest.raises(RuntimeError, match="Assertion error"):
-        api._C.m_grouped_masked(t, t, t, t, t, t, 1, 128, 128)
+        api._C.m_grouped_masked((t, sf), (t, sf), t, sf, 1, None, None, None, False, None)
+    with pytest.raises(RuntimeError, match="Assertion error"):
+        api._C.m_grouped_contiguous((t, sf), (t, sf), t, sf, None, None, None, False, False, True, None, None)
 
 
-def test_recipes_the_binding_serves():
-    i32, f32 = torch.zeros(1, dtype=torch.int), torch.zeros(1)
-    assert api._packed_grans(i32, i32, None, None, None, False) == (128, 128)
-    assert api._packed_grans(i32, i32, (1, 1, 32), None, None, False) == (32, 32)
-    assert api._packed_grans(i32, i32, None, (1, 32), (1, 128), False) == (32, 128)
-    # everything else keeps the general path, which words the error or runs the transform kernel
-    assert api._packed_grans(f32, i32, None, None, None, False) is None
-    assert api._packed_grans(i32, i32, (1, 128, 128), None, None, False) is None
-    assert api._packed_grans(i32, i32, (1, 1, 128), (1, 128), (1, 128), False) is None
-    assert api._packed_grans(i32, i32, None, (1, 128), None, False) is None
-    assert api._packed_grans(i32, i32, None, (1, 64), (1, 128), False) is None
-    assert api._packed_grans(i32, i32, None, None, None, True) is None
+def test_calls_the_binding_serves():
+    """Packed scales with gran_mn == 1 and no epilogue object; everything else is handed back untouched (False), and the
+    interpreter path words the error or runs the transform kernel."""
+    t, i32, f32 = torch.zeros(4, 4), torch.zeros(4, 1, dtype=torch.int), torch.zeros(4, 1)
+
+    def served(sfa=i32, sfb=i32, recipe=None, recipe_a=None, recipe_b=None, disable=False, epilogue=None, c=None):
+        try:
+            return api._C.dense_nt((t, sfa), (t, sfb), t, c, recipe, recipe_a, recipe_b, disable, None, epilogue)
+        except RuntimeError as e:           # accepted: the first check then refuses the CPU tensors
+            assert "t.is_cuda()" in str(e)
+            return True
+
+    assert served() and served(recipe=(1, 1, 32)) and served(recipe=[1, 1, 128]) and served(recipe_a=(1, 32), recipe_b=(1, 128))
+    assert served(c=t)
+    assert not served(sfa=f32) and not served(sfb=f32)
+    assert not served(recipe=(1, 128, 128)) and not served(recipe=(1, 1, 64)) and not served(recipe=(1, 1))
+    assert not served(recipe=(1, 1, 128), recipe_a=(1, 128), recipe_b=(1, 128))
+    assert not served(recipe_a=(1, 128)) and not served(recipe_a=(1, 64), recipe_b=(1, 128)) and not served(recipe_a=(2, 128), recipe_b=(1, 128))
+    assert not served(recipe="abc") and not served(disable=True) and not served(epilogue=dg.epilogue.Identity())
+    assert not served(c=torch.zeros(4, 4))              # a C that is not D itself is copied by the general path
 
 
 # ------------------------------------------------------------------------------------------------------------------
@@ -120,7 +130,7 @@ def test_grouped_same_bits_as_the_ctypes_path(monkeypatch):
 
 @pytest.mark.gpu
 def test_binding_refuses_what_the_ctypes_path_refuses():
-    a, b = _dense_inputs(128, 256, 512)
+    a, b = _dense_inputs(128, 256, 1024)          # two packed scale words per row
     d = torch.empty((128, 256), dtype=torch.bfloat16, device="cuda")
     with pytest.raises(RuntimeError, match="m == m_ and n == n_ and k == k_"):
         dg.fp8_fp4_gemm_nt(a, b, d[:, :128], recipe_a=(1, 128), recipe_b=(1, 128))
