@@ -40,7 +40,7 @@ class GemmArgs(C.Structure):
 class GemmConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in (
         "block_m", "block_n", "block_k", "num_stages", "cluster_size", "raster_group", "num_ctas",
-        "smem_bytes", "tmem_cols", "num_tiles", "waves_x100", "num_splits", "kb_per_split", "split_in_cluster", "swap_ab", "store_buffers")]
+        "smem_bytes", "tmem_cols", "num_tiles", "waves_x100", "num_splits", "kb_per_split", "split_in_cluster", "swap_ab", "store_buffers", "a_rows")]
 
     def as_dict(self):
         return {n: getattr(self, n) for n, _ in self._fields_}

@@ -28,6 +28,9 @@ struct GemmLayout {
                                                    // saved buy another pipeline stage (MN-major operands: whole 128-byte atoms)
     uint32_t mxf4 = 0;                             // FP4 x FP4 through kind::mxf4: operands stay packed in shared memory (two
                                                    // elements per byte), so a 128-byte stage row holds 256 elements of K
+    uint32_t a_rows = 0;                           // rows of A a stage holds when the whole GEMM has fewer than block_m (0: block_m).
+                                                   // The MMA still reads 128 rows: the rest is whatever follows in shared
+                                                   // memory and lands in accumulator rows that are never stored
 
     // A packed scale word covers 4 * gran_k elements of K: it is fetched on every `period`-th K-block of a work item,
     // into the next of a ring of buffers.  A buffer may be refilled once the fetch it held is no longer among the
@@ -67,7 +70,8 @@ struct GemmLayout {
     DG_HDC uint32_t store_stage_bytes() const { return 128 * group_bytes(); }      // staging holds 128 rows of one group
     DG_HDC uint32_t num_store_stages() const { return store_buffers * (block_m / 128); }
 
-    DG_HDC uint32_t a_bytes() const { return block_m * block_k; }        // one byte per element (FP8, or FP4 in 16-byte containers)
+    DG_HDC uint32_t a_stage_rows() const { return a_rows ? a_rows : block_m; }
+    DG_HDC uint32_t a_bytes() const { return a_stage_rows() * block_k; }  // one byte per element (FP8, or FP4 in 16-byte containers)
     DG_HDC uint32_t load_block_n() const { return block_n / cluster; }
     // MN-major only: atoms of [block_k / ab_elem_bytes rows of K][128 bytes of N]
     DG_HDC uint32_t b_atoms() const { return (load_block_n() * ab_elem_bytes + 127) / 128; }

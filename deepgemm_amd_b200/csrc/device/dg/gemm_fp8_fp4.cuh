@@ -212,8 +212,13 @@ static_assert(kSplitCluster == 1 || (kGemmType == kDense && !kSplitK && kCluster
 #ifndef DG_EPILOGUE_BACKOFF_NS
 #define DG_EPILOGUE_BACKOFF_NS 0
 #endif
+#ifndef DG_A_ROWS
+#define DG_A_ROWS 0
+#endif
 constexpr GemmLayout kLayout{CTA_M, BLOCK_N, BLOCK_K, kNumStages, kDElemBytes, kCluster, kBMnMajor ? 1u : 0u, kGranKA, kGranKB,
-                             DG_SHORT_K, kABElemBytes, DG_STORE_BUFFERS, kMXF4 ? 1u : 0u};
+                             DG_SHORT_K, kABElemBytes, DG_STORE_BUFFERS, kMXF4 ? 1u : 0u, DG_A_ROWS};
+static_assert(DG_A_ROWS == 0 || (DG_A_ROWS % 8 == 0 && DG_A_ROWS < 128 && kGemmType == kDense && kCluster == 1 && kMHalves == 1 && !kAMnMajor),
+              "a shortened A stage: dense GEMMs with fewer rows than one tile, K-major A, one CTA per tile");
 constexpr uint32_t kSFAWords = kHasSF ? kLayout.sfa_words() : 1, kSFBWords = kHasSF ? kLayout.sfb_words() : 1;   // packed words per row and stage
 // K coordinate of a K-major load advances by this much per K-block: elements of the tensor map's type (bytes for the
 // packed operands of kind::mxf4, whose maps are plain byte maps)
@@ -230,6 +235,11 @@ constexpr uint32_t kNumStoreStages  = kLayout.num_store_stages();
 constexpr uint32_t kStoreStageBytes = kLayout.store_stage_bytes();
 constexpr uint32_t kSmemD   = kLayout.off_d();
 constexpr uint32_t kSmemA   = kLayout.off_a();
+// Cluster-reduced K slicing: columns of the tile a CTA owns (whole 8-column chunks, dealt round robin), and the bytes it
+// receives for them from the S slices.  The receive area starts where the D staging buffers do.
+constexpr uint32_t kRecvCols = (BLOCK_N / 8 + kSplitCluster - 1) / kSplitCluster * 8;
+constexpr uint32_t kRecvBytes = kSplitCluster * kRecvCols * 128 * 4;
+constexpr bool kRecvOverStages = kRecvBytes > kSmemA;
 constexpr uint32_t kABytes  = kLayout.a_bytes();
 constexpr uint32_t kBBytes  = kLayout.b_bytes();
 constexpr uint32_t kSmemB   = kLayout.off_b();
@@ -289,8 +299,13 @@ enum ProfileSlot : uint32_t {
 #define DG_PROF_FLUSH(slot, acc) do { if (p.profile != nullptr) atomicAdd(p.profile + (slot), static_cast<unsigned long long>(acc)); } while (0)
 // Timeline of CTA 0 in nanoseconds (globaltimer): slots 16.. hold absolute stamps, first writer wins
 #define DG_PROF_STAMP(slot) do { if (p.profile != nullptr && blockIdx.x == 0) atomicCAS(p.profile + 16 + (slot), 0ull, global_timer_ns()); } while (0)
+// over all CTAs: the earliest / latest time an event happened anywhere in the grid
+#define DG_PROF_STAMP_MIN(slot) do { if (p.profile != nullptr) atomicMin(p.profile + 16 + (slot), global_timer_ns()); } while (0)
+#define DG_PROF_STAMP_MAX(slot) do { if (p.profile != nullptr) atomicMax(p.profile + 16 + (slot), global_timer_ns()); } while (0)
 #else
 #define DG_PROF_STAMP(slot) do { } while (0)
+#define DG_PROF_STAMP_MIN(slot) do { } while (0)
+#define DG_PROF_STAMP_MAX(slot) do { } while (0)
 #define DG_PROF_VAR(name) do { } while (0)
 #define DG_PROF_BEGIN(var) do { } while (0)
 #define DG_PROF_ADD(acc, var) do { } while (0)
@@ -331,6 +346,8 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
     // ---- set-up -------------------------------------------------------------------------------
     if (threadIdx.x == 0) {
         DG_PROF_STAMP(0);                                   // kernel entry
+        DG_PROF_STAMP_MIN(9);                               // first CTA to enter
+        DG_PROF_STAMP_MAX(10);                              // last CTA to enter
         *abort_flag = 0;
         prefetch_tensormap(&tm_a);
         prefetch_tensormap(&tm_b);
@@ -372,6 +389,9 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
     }
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_base_slot;
+    // Cluster-reduced K slicing whose receive area lies outside the pipeline stages: peers may write to this CTA as soon
+    // as it runs, which the first half of a split barrier announces here (the epilogue waits for it before sending)
+    if constexpr (kSplitCluster > 1 && !kRecvOverStages) cluster_arrive_relaxed();
     if (threadIdx.x == 0) DG_PROF_STAMP(1);                 // set-up done (barriers, tensor memory)
     // Everything above touched no global memory, so with programmatic dependent launch it overlapped the tail of the
     // kernel before this one; from here on its results (and its reads of D) must be complete.  The kernel after
@@ -598,6 +618,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                         if (!mbar_wait(full_bar(stage), phase, ctx, kRoleMma, 2)) { ok = false; break; }
                         DG_PROF_ADD(prof_full, prof_w1);
                         DG_PROF_STAMP(2);                       // first stage arrived
+                        if (it == 0 && tile_iter == 1 && lane == 0) DG_PROF_STAMP_MAX(12);      // ... in the last CTA to see one
                         tc_fence_after_sync();
                         if (issue_lane) {
                         // Scales: shared memory (rearranged by warp 2) -> tensor memory, in every CTA of the cluster
@@ -720,9 +741,11 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
             }
         }
         if constexpr (kSplitCluster > 1) {
-            // The role warps have nothing to publish: they only take part in the cluster-wide barrier that separates
-            // "every slice is parked" from "CTA 0 adds them up"
+            // The role warps have nothing to publish: they only take part in the two cluster-wide barriers of the
+            // epilogue ("every CTA may be written to", "every slice has arrived")
             __syncwarp();
+            if constexpr (kRecvOverStages) cluster_arrive();
+            cluster_wait();
             cluster_arrive();
             cluster_wait();
         }
@@ -748,7 +771,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
         constexpr bool kRowInRegs = kMHalves == 2 && !kDIsFP32;
         constexpr uint32_t kGroupBytes = kLayout.group_bytes();
         bool ok = true;
-        [[maybe_unused]] bool cluster_synced = false;
+        [[maybe_unused]] uint32_t cluster_barriers_done = 0;
         uint32_t tile_iter = 0, store_iter = 0;
         DG_PROF_VAR(prof_wait); DG_PROF_VAR(prof_store);
         DG_PROF_BEGIN(prof_t0);
@@ -779,49 +802,69 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
             if (!mbar_wait(tmem_full_bar(accum), accum_phase, ctx, kRoleEpilogue, 1, DG_EPILOGUE_BACKOFF_NS)) { ok = false; break; }
             DG_PROF_ADD(prof_wait, prof_w);
             tc_fence_after_sync();
+            if (prof_thread) DG_PROF_STAMP(3);              // first accumulator complete
+            if (epi_tid == 0 && wg == 0 && tile_iter == 1) DG_PROF_STAMP_MAX(13);          // ... in the last CTA to have one
 
-            // Cluster-reduced K slicing.  Every CTA of the cluster parks its FP32 accumulator in its own shared memory,
-            // over the drained pipeline stages, column by column (word (column * 128 + row): consecutive threads,
-            // consecutive banks).  After a cluster barrier the CTAs share the reduction: CTA r owns the 8-column
-            // chunks r, r + S, ...; for each, a thread adds the S slices of its row in slice order (its own through
-            // the same window), scales, converts and writes the 8 values straight to D.
+            // Cluster-reduced K slicing.  The CTAs of the cluster share the reduction by columns: CTA r owns the 8-column
+            // chunks r, r + S, ... of the tile.  Every CTA sends each column of its FP32 accumulator straight from tensor
+            // memory into the owner's shared memory (distributed shared memory stores: posted, so their latency is not
+            // waited for), one cluster barrier makes all of it visible, and then every CTA adds the S slices of its own
+            // columns out of its OWN shared memory, in slice order, scales, converts and writes them to D.  After that
+            // barrier no CTA touches a peer's memory again, so none has to outlive its peers.
+            // Receive area of a CTA: [slice][owned column][row] words from the start of dynamic shared memory: the D
+            // staging buffers, which this form does not use, and beyond them the drained pipeline stages.
             if constexpr (kSplitCluster > 1) {
-                static_assert(kSplitCluster == 1 || BLOCK_N * BLOCK_M * 4 <= kNumStages * (kABytes + kBBytes), "the parked tile fits the stages");
-                const uint32_t park_addr = smem_base + kSmemA + row_in_tile * 4;
+                static_assert(kSplitCluster == 1 || kRecvBytes <= kSmemA + kNumStages * (kABytes + kBBytes), "the receive area fits the staging buffers and stages");
+                if constexpr (kRecvOverStages) {
+                    // Peers write over this CTA's pipeline stages: they may start once every CTA's MMAs have read theirs
+                    cluster_arrive();
+                    cluster_wait();
+                } else {
+                    cluster_wait();             // (arrived at set-up) every CTA of the cluster is running
+                }
+                ++cluster_barriers_done;
+                uint32_t owners[kSplitCluster];
+                #pragma unroll
+                for (uint32_t r = 0; r < kSplitCluster; ++r)
+                    owners[r] = map_to_cta(smem_base + kSmemD + (split_rank * kRecvCols * BLOCK_M + row_in_tile) * 4, r);
                 #pragma unroll
                 for (uint32_t b = 0; b < BLOCK_N / 16; ++b) {
                     uint32_t v[16];
                     tmem_ld_32x32b_x16(tmem_base + ((quarter * 32) << 16) + accum * UMMA_N + b * 16, v);
                     tmem_ld_wait();
                     #pragma unroll
-                    for (uint32_t i = 0; i < 16; ++i) st_shared_u32(park_addr + (b * 16 + i) * BLOCK_M * 4, v[i]);
+                    for (uint32_t i = 0; i < 16; ++i) {
+                        const uint32_t chunk = (b * 16 + i) / 8, owned_col = chunk / kSplitCluster * 8 + i % 8;
+                        st_shared_cluster_u32(owners[chunk % kSplitCluster] + owned_col * BLOCK_M * 4, v[i]);
+                    }
                 }
                 tc_fence_before_sync();
                 mbar_arrive(tmem_empty_bar(accum));
-                cluster_arrive();               // release: the parked tile is visible to the cluster
+                if (prof_thread) DG_PROF_STAMP(7);          // accumulator sent
+                cluster_arrive();               // release: what this CTA sent is visible to its owners
                 cluster_wait();
-                cluster_synced = true;
+                ++cluster_barriers_done;
+                if (prof_thread) DG_PROF_STAMP(8);          // every slice of the cluster has arrived
+                const uint32_t recv = smem_base + kSmemD;
 
                 if constexpr (kTransposedD) {
-                    // Work items are (column, 8 consecutive rows): 32 contiguous bytes of every parked tile, 8 consecutive
-                    // elements of one row of the caller's D.  CTA r takes items [128 r, 128 r + 128), then S x 128 further on.
-                    uint32_t tiles[kSplitCluster];
-                    #pragma unroll
-                    for (uint32_t r = 0; r < kSplitCluster; ++r) tiles[r] = map_to_cta(smem_base + kSmemA, r);
-                    constexpr uint32_t kItems = BLOCK_N * (BLOCK_M / 8);
+                    // Work items are (owned column, 8 consecutive rows): 32 contiguous bytes of every slice, 8 consecutive
+                    // elements of one row of the caller's D
+                    constexpr uint32_t kItems = kRecvCols * (BLOCK_M / 8);
                     #pragma unroll 1
-                    for (uint32_t q = epi_tid + 128 * split_rank; q < kItems; q += 128 * kSplitCluster) {
-                        const uint32_t c = q / (BLOCK_M / 8), r8 = q % (BLOCK_M / 8);
+                    for (uint32_t q = epi_tid; q < kItems; q += 128) {
+                        const uint32_t oc = q / (BLOCK_M / 8), r8 = q % (BLOCK_M / 8);
+                        const uint32_t c = (oc / 8 * kSplitCluster + split_rank) * 8 + oc % 8;      // column of the tile
                         const uint32_t col = tile.n_block * BLOCK_N + c;             // row of the caller's D
                         const uint32_t row = tile.m_block * BLOCK_M + r8 * 8;        // its first column
-                        if (col >= p.shape_n || row >= p.shape_m) continue;
+                        if (c >= BLOCK_N || col >= p.shape_n || row >= p.shape_m) continue;
                         float sum[8];
                         #pragma unroll
                         for (uint32_t i = 0; i < 8; ++i) sum[i] = 0.0f;
                         #pragma unroll
                         for (uint32_t r = 0; r < kSplitCluster; ++r) {
-                            const uint4 lo = ld_shared_cluster_v4(tiles[r] + (c * BLOCK_M + r8 * 8) * 4);
-                            const uint4 hi = ld_shared_cluster_v4(tiles[r] + (c * BLOCK_M + r8 * 8) * 4 + 16);
+                            const uint4 lo = ld_shared_v4(recv + ((r * kRecvCols + oc) * BLOCK_M + r8 * 8) * 4);
+                            const uint4 hi = ld_shared_v4(recv + ((r * kRecvCols + oc) * BLOCK_M + r8 * 8) * 4 + 16);
                             sum[0] += __uint_as_float(lo.x); sum[1] += __uint_as_float(lo.y); sum[2] += __uint_as_float(lo.z); sum[3] += __uint_as_float(lo.w);
                             sum[4] += __uint_as_float(hi.x); sum[5] += __uint_as_float(hi.y); sum[6] += __uint_as_float(hi.z); sum[7] += __uint_as_float(hi.w);
                         }
@@ -855,29 +898,20 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                     continue;
                 }
                 const uint32_t d_row = tile.m_block * BLOCK_M + row_in_tile;
-                uint32_t peers[kSplitCluster];
-                #pragma unroll
-                for (uint32_t r = 0; r < kSplitCluster; ++r) peers[r] = map_to_cta(park_addr, r);
-                constexpr uint32_t kChunks = BLOCK_N / 8;
                 if (d_row < p.shape_m) {
                     uint8_t* drow = reinterpret_cast<uint8_t*>(p.d) + static_cast<size_t>(d_row) * p.ldd * kDElemBytes;
                     #pragma unroll
-                    for (uint32_t jj = 0; jj < (kChunks + kSplitCluster - 1) / kSplitCluster; ++jj) {
+                    for (uint32_t jj = 0; jj < kRecvCols / 8; ++jj) {
                         const uint32_t j = jj * kSplitCluster + split_rank;
                         const uint32_t col = tile.n_block * BLOCK_N + j * 8;
-                        if (j < kChunks && col < p.shape_n) {
-                            uint32_t part[kSplitCluster][8];
-                            #pragma unroll
-                            for (uint32_t r = 0; r < kSplitCluster; ++r) {
-                                #pragma unroll
-                                for (uint32_t i = 0; i < 8; ++i) part[r][i] = ld_shared_cluster_u32(peers[r] + (j * 8 + i) * BLOCK_M * 4);
-                            }
+                        if (j < BLOCK_N / 8 && col < p.shape_n) {
                             float sum[8];
                             #pragma unroll
                             for (uint32_t i = 0; i < 8; ++i) {
                                 sum[i] = 0.0f;                  // (0 + first slice: the same operations as the two-kernel reduction)
                                 #pragma unroll
-                                for (uint32_t r = 0; r < kSplitCluster; ++r) sum[i] += __uint_as_float(part[r][i]);
+                                for (uint32_t r = 0; r < kSplitCluster; ++r)
+                                    sum[i] += __uint_as_float(ld_shared_u32(recv + ((r * kRecvCols + jj * 8 + i) * BLOCK_M + row_in_tile) * 4));
                                 sum[i] *= p.alpha;
                             }
                             if constexpr (kDIsFP32) {
@@ -1143,7 +1177,13 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
             }
         }
         if constexpr (kSplitCluster > 1) {
-            if (!cluster_synced) {          // no tile, or a wait ran out: the rest of the cluster must not wait for ever
+            // no tile, or a wait ran out: the rest of the cluster must not wait for ever
+            if (cluster_barriers_done == 0) {
+                if constexpr (kRecvOverStages) cluster_arrive();
+                cluster_wait();
+                ++cluster_barriers_done;
+            }
+            if (cluster_barriers_done == 1) {
                 cluster_arrive();
                 cluster_wait();
             }
@@ -1169,9 +1209,9 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
         while (global_timer_ns() - t0 < 200000) { }
         __syncthreads();
     }
-    if constexpr (kCluster > 1 || kSplitCluster > 1) {
-        // Neither CTA may exit (or free tensor memory) while its peer can still signal its barriers or read its
-        // shared memory
+    if constexpr (kCluster > 1) {
+        // Neither CTA of a pair may exit (or free tensor memory) while its peer can still signal its barriers or read
+        // its shared memory.  (The CTAs of a K-sliced cluster are done with one another after the epilogue's barrier.)
         tc_fence_before_sync();
         cluster_arrive();
         cluster_wait();
@@ -1181,4 +1221,5 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
         tmem_dealloc<kCluster>(tmem_base, kTmemCols);
     }
     if (threadIdx.x == 0) DG_PROF_STAMP(6);                 // exit
+    if (threadIdx.x == 0) DG_PROF_STAMP_MAX(11);            // last CTA to leave
 }

@@ -328,6 +328,12 @@ int choose_config_for(const Problem& p, dg_gemm_config_t* cfg, const Constraints
         if (bk != (forced_block_k && p.kind != DG_GEMM_K_GROUPED_CONTIGUOUS ? forced_block_k : 128)) continue;
         if (bk == 64 && (p.a_fp4 || p.b_fp4 || p.ab_bf16 || p.a_mn_major || p.b_mn_major || forced_splits > 1)) continue;
         const int tile_m = 128 * cluster * halves, units = num_sms / cluster;
+        // A dense GEMM with at most 64 rows stages only those rows of A (16, 32 or 64; the box of its tensor map): the
+        // bytes saved per stage become more stages, i.e. more of B in flight.  DG_FORCE_A_ROWS=128 keeps whole tiles.
+        int a_rows = 0;
+        if (p.kind == DG_GEMM_DENSE && cluster == 1 && halves == 1 && bk == 128 && !p.a_mn_major && p.reduce_batches <= 1 && p.m <= 64 &&
+            env_int("FORCE_A_ROWS") != 128)
+            a_rows = p.m <= 16 ? 16 : (p.m <= 32 ? 32 : 64);
         int64_t m_blocks;
         if (p.kind == DG_GEMM_M_GROUPED_MASKED)
             m_blocks = static_cast<int64_t>(p.groups) * ceil_div(std::min(std::max(p.expected_m, 1), p.m), tile_m);
@@ -384,7 +390,7 @@ int choose_config_for(const Problem& p, dg_gemm_config_t* cfg, const Constraints
                 GemmLayout lay{128u * halves, static_cast<uint32_t>(bn), static_cast<uint32_t>(bk), 2,
                                static_cast<uint32_t>(splits > 1 && !in_cluster ? 4 : d_elem), static_cast<uint32_t>(cluster),
                                p.b_mn_major ? 1u : 0u, static_cast<uint32_t>(p.gran_k_a), static_cast<uint32_t>(p.gran_k_b), 0u,
-                               static_cast<uint32_t>(ab_elem), 2u, p.mxf4 ? 1u : 0u};
+                               static_cast<uint32_t>(ab_elem), 2u, p.mxf4 ? 1u : 0u, static_cast<uint32_t>(a_rows)};
                 const GemmLayout unfitted = lay;
                 lay = fit_stages(lay, p.kind == DG_GEMM_K_GROUPED_CONTIGUOUS ? 0 : item_kb, max_stages);   // slices may be one K-block
                 if (lay.num_stages <= 2 && env_int("FORCE_STORE_BUFFERS") != 2) {
@@ -395,8 +401,21 @@ int choose_config_for(const Problem& p, dg_gemm_config_t* cfg, const Constraints
                     if (single.num_stages > lay.num_stages) lay = single;
                 }
                 if (lay.num_stages == 0 || lay.tmem_cols_used() > kTmemCapacityCols) continue;
-                // A parked FP32 accumulator (128 rows x bn) has to fit the pipeline stages it overwrites
-                if (in_cluster && static_cast<uint64_t>(bn) * 128 * 4 > static_cast<uint64_t>(lay.num_stages) * (lay.a_bytes() + lay.b_bytes())) continue;
+                // The cost model was fitted on whole-tile A stages: a shortened A stage keeps the model's choice of tile
+                // and slicing and only deepens that candidate's pipeline
+                uint32_t model_stages = lay.num_stages;
+                if (a_rows) {
+                    GemmLayout whole = unfitted;
+                    whole.a_rows = 0;
+                    whole.store_buffers = lay.store_buffers;
+                    whole = fit_stages(whole, item_kb, max_stages);
+                    if (whole.num_stages == 0) continue;
+                    model_stages = whole.num_stages;
+                }
+                // What a CTA receives from the cluster (S slices of the columns it owns: whole 8-column chunks of 128 FP32 rows)
+                // has to fit the D staging buffers and the pipeline stages behind them
+                if (in_cluster && static_cast<uint64_t>(splits) * ceil_div(bn / 8, splits) * 8 * 128 * 4 >
+                                      lay.off_a() + static_cast<uint64_t>(lay.num_stages) * (lay.a_bytes() + lay.b_bytes())) continue;
                 // Cycles per pipeline stage: the MMAs; shared memory, which moved ~150 B per cycle in every configuration
                 // measured, TMA writes and tensor-core reads together (a stage is written once, its A rows are read once
                 // and its B rows once per 128-row half), and into which no configuration pulled more than ~67 B per cycle
@@ -408,7 +427,7 @@ int choose_config_for(const Problem& p, dg_gemm_config_t* cfg, const Constraints
                 const double read_bytes = (128.0 * halves + halves * static_cast<double>(bn) / cluster * (cluster == 2 ? 2.0 : 1.0)) * bk;
                 // (55 B per cycle fitted the cluster-reduced candidates: few-tile shapes whose B is read once, from HBM)
                 const double smem_feed = std::max((stage_bytes + read_bytes) / 150.0, stage_bytes / (in_cluster ? 55.0 : 67.0));
-                const double ring = (1500.0 + mma) / lay.num_stages;
+                const double ring = (1500.0 + mma) / model_stages;
                 // (one epilogue warpgroup drains a 128 x bn accumulator in ~600 + 14 bn cycles, measured on the K = 512 shape
                 //  with 128-row CTA pairs, where it is what bounds a tile)
                 const double epilogue = cluster == 2 && halves == 1 ? 600.0 + 14.0 * bn
@@ -461,6 +480,7 @@ int choose_config_for(const Problem& p, dg_gemm_config_t* cfg, const Constraints
                     best.cluster * (p.kind == DG_GEMM_M_GROUPED_MASKED || p.kind == DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM
                                         ? units : static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(units, best.tiles))));
     cfg->store_buffers = static_cast<int>(best.lay.store_buffers);
+    cfg->a_rows = static_cast<int>(best.lay.a_stage_rows());
     cfg->smem_bytes = static_cast<int>(best.lay.total_bytes());
     cfg->tmem_cols = static_cast<int>(best.lay.tmem_cols_alloc());
     cfg->num_tiles = static_cast<int>(best.tiles);
@@ -508,7 +528,7 @@ GemmLayout layout_of(const Problem& p, const dg_gemm_config_t& cfg) {
                    static_cast<uint32_t>(cfg.cluster_size), p.b_mn_major ? 1u : 0u,
                    static_cast<uint32_t>(p.gran_k_a), static_cast<uint32_t>(p.gran_k_b),
                    item_kb < cfg.num_stages ? 1u : 0u, static_cast<uint32_t>(ab_elem), static_cast<uint32_t>(cfg.store_buffers),
-                   p.mxf4 ? 1u : 0u};
+                   p.mxf4 ? 1u : 0u, cfg.a_rows > 0 && cfg.a_rows < cfg.block_m ? static_cast<uint32_t>(cfg.a_rows) : 0u};
     return lay;
 }
 
@@ -537,6 +557,7 @@ std::string generate_source(const Problem& p, const dg_gemm_config_t& cfg) {
       << "#define DG_RASTER_GROUP " << cfg.raster_group << "\n"
       << "#define DG_SPLIT_K " << (cfg.num_splits > 1 && !cfg.split_in_cluster ? 1 : 0) << "\n"
       << "#define DG_STORE_BUFFERS " << cfg.store_buffers << "\n"
+      << "#define DG_A_ROWS " << (cfg.a_rows > 0 && cfg.a_rows < cfg.block_m ? cfg.a_rows : 0) << "\n"
       << "#define DG_TRANSPOSED_D " << (cfg.swap_ab ? 1 : 0) << "\n"
       << "#define DG_BATCH_REDUCE " << (p.reduce_batches > 1 ? 1 : 0) << "\n"
       << "#define DG_SPLIT_CLUSTER " << (cfg.split_in_cluster ? cfg.num_splits : 1) << "\n"
@@ -621,7 +642,7 @@ struct Plan {
 
 int get_plan(const Problem& p, Plan* plan) {
     static const char* kEnvNames[] = {"FORCE_BLOCK_N", "FORCE_CLUSTER", "FORCE_SPLIT_K", "FORCE_BLOCK_M", "FORCE_BLOCK_K",
-                                      "FORCE_NUM_STAGES", "FORCE_RASTER_GROUP", "PROFILE", "FORCE_SPLIT_CLUSTER", "FORCE_SWAP_AB", "FORCE_STORE_BUFFERS",
+                                      "FORCE_NUM_STAGES", "FORCE_RASTER_GROUP", "PROFILE", "FORCE_SPLIT_CLUSTER", "FORCE_SWAP_AB", "FORCE_STORE_BUFFERS", "FORCE_A_ROWS",
                                       "EPILOGUE_BACKOFF_NS", "MMA_WHOLE_WARP", "PRODUCER_WHOLE_WARP", "L2_HINT"};
     const int fields[] = {p.kind, p.m, p.n, p.k, p.groups, static_cast<int>(p.a_fp4), static_cast<int>(p.b_fp4), static_cast<int>(p.ab_bf16),
                           static_cast<int>(p.d_fp32), static_cast<int>(p.d_fp8), static_cast<int>(p.accumulate), static_cast<int>(p.a_mn_major),
@@ -709,8 +730,8 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
         p = swapped(p);
     }
     if (env_int("PRINT_CONFIGS"))
-        fprintf(stderr, "[dg] kind %d m %d n %d k %d groups %d -> block_m %d block_n %d block_k %d cluster %d stages %d store_buffers %d ctas %d smem %d tiles %d splits %d x %d%s\n",
-                kind, p.m, p.n, p.k, p.groups, cfg.block_m, cfg.block_n, cfg.block_k, cfg.cluster_size, cfg.num_stages, cfg.store_buffers, cfg.num_ctas, cfg.smem_bytes, cfg.num_tiles,
+        fprintf(stderr, "[dg] kind %d m %d n %d k %d groups %d -> block_m %d block_n %d block_k %d cluster %d stages %d store_buffers %d a_rows %d ctas %d smem %d tiles %d splits %d x %d%s\n",
+                kind, p.m, p.n, p.k, p.groups, cfg.block_m, cfg.block_n, cfg.block_k, cfg.cluster_size, cfg.num_stages, cfg.store_buffers, cfg.a_rows, cfg.num_ctas, cfg.smem_bytes, cfg.num_tiles,
                 cfg.num_splits, cfg.kb_per_split, cfg.split_in_cluster ? " (in a cluster)" : "");
     if (fixed_scratch == nullptr && (rc = ensure_status_word()) != DG_OK) return rc;
 
@@ -766,9 +787,9 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
                                        p.b_fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8;
     if (p.mxf4) {
         // packed operands as plain byte matrices [rows, K / 2]: a 128-byte box row is 256 elements of K
-        if ((rc = encode_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->a, p.k / 2, a_rows, a->lda, 128, cfg.block_m, CU_TENSOR_MAP_SWIZZLE_128B)) != DG_OK) return rc;
+        if ((rc = encode_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->a, p.k / 2, a_rows, a->lda, 128, lay.a_stage_rows(), CU_TENSOR_MAP_SWIZZLE_128B)) != DG_OK) return rc;
     } else if (!p.a_mn_major) {
-        if ((rc = encode_2d(&tm_a, a_type, a->a, k_inner, a_rows, a->lda * ab_elem, box_k, cfg.block_m, k_major_swizzle,
+        if ((rc = encode_2d(&tm_a, a_type, a->a, k_inner, a_rows, a->lda * ab_elem, box_k, lay.a_stage_rows(), k_major_swizzle,
                             nb_ab, bs_a * ab_elem)) != DG_OK) return rc;
     } else {
         if ((rc = encode_2d(&tm_a, a_type, a->a, p.m, p.k, a->lda * ab_elem, atom_mn, box_k, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -837,6 +858,7 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
         params.profile = profile_buffer();
         if (params.profile == nullptr) return fail(DG_ERR_CUDA, "cannot allocate the profile buffer");
         DG_CUDA_RT(cudaMemsetAsync(params.profile, 0, 32 * sizeof(unsigned long long), static_cast<cudaStream_t>(a->stream)));
+        DG_CUDA_RT(cudaMemsetAsync(params.profile + 16 + 9, 0xFF, sizeof(unsigned long long), static_cast<cudaStream_t>(a->stream)));   // (a minimum)
         rc = dg_jit_launch(kernel, cfg.num_ctas, 128 + cfg.block_m, launch_cluster, cfg.smem_bytes, state().pdl, a->stream, kargs);
         if (rc != DG_OK) return rc;
         unsigned long long h[32];
@@ -847,10 +869,12 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
                         "issue cp %.0f mma %.0f commit %.0f / %.0f | sf wait %.0f / %.0f | epilogue wait_tmem_full %.0f store_wait %.0f / %.0f\n",
                 h[0] / ctas, h[1] / ctas, h[2] / leaders, h[3] / leaders, h[10] / leaders, h[11] / leaders, h[12] / leaders,
                 h[4] / leaders, h[5] / ctas, h[6] / ctas, h[7] / ctas, h[9] / ctas, h[8] / ctas);
+        const auto since_entry = [&](int slot) { return h[16 + slot] == 0 ? -1ll : (long long)(h[16 + slot] - h[16]); };
         fprintf(stderr, "[dg profile] CTA 0 timeline (ns after entry): set-up %lld | first stage %lld | first accumulator %lld | "
-                        "last store issued %lld | stores complete %lld | exit %lld\n",
-                (long long)(h[17] - h[16]), (long long)(h[18] - h[16]), (long long)(h[19] - h[16]), (long long)(h[20] - h[16]),
-                (long long)(h[21] - h[16]), (long long)(h[22] - h[16]));
+                        "parked %lld | cluster parked %lld | last store issued %lld | stores complete %lld | exit %lld\n",
+                since_entry(1), since_entry(2), since_entry(3), since_entry(7), since_entry(8), since_entry(4), since_entry(5), since_entry(6));
+        fprintf(stderr, "[dg profile] all CTAs (ns after the first entered): last entry %lld | last first-stage %lld | last first-accumulator %lld | last exit %lld\n",
+                (long long)(h[16 + 10] - h[16 + 9]), (long long)(h[16 + 12] - h[16 + 9]), (long long)(h[16 + 13] - h[16 + 9]), (long long)(h[16 + 11] - h[16 + 9]));
         if (split)
             return launch_splitk_reduce(workspace, a->d, p.m, p.n, ld_ws, panel_rows, a->ldd, cfg.num_splits, alpha, p.d_fp32,
                                         static_cast<cudaStream_t>(a->stream));

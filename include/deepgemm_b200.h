@@ -257,6 +257,8 @@ typedef struct dg_gemm_config {
     int32_t swap_ab;           /* 1: dense GEMM with few rows run with the operands' roles exchanged: block_m counts rows of the
                                   caller's B, block_n is the caller's M rounded up to 16, and the epilogue writes D transposed */
     int32_t store_buffers;     /* staging buffers of D per epilogue warpgroup (2; 1 where that buys a third pipeline stage) */
+    int32_t a_rows;            /* rows of A a pipeline stage holds: block_m, or fewer (16/32/64) when the whole GEMM has no more rows,
+                                  which leaves room for more stages */
 } dg_gemm_config_t;
 
 /* get_best_config<SM100ArchSpec> (heuristics/common.hpp:17-56, sm100.hpp:30-301).  Host only. */
