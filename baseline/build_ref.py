@@ -12,8 +12,9 @@ cutlass with the CUTLASS/CuTe headers that ship inside the image's flashinfer wh
     pip install --no-index --no-build-isolation --no-deps --target baseline/_ref <scratch copy>
 
 Nothing of the reference's own sources is edited.  baseline/_ref is git-ignored (it holds the reference's package, its
-headers and the built extension) and is left out of multi-GPU runs (.gpurunignore.multi): it is used on one GPU only.
-Needs /root/reference; without it the script reports that and leaves an existing installation alone.
+headers and the built extension) and is left out of multi-GPU runs: it is used on one GPU only.
+Needs the reference's source tree (DG_REFERENCE_TREE); without it the script reports that and leaves an existing
+installation alone.
 """
 from __future__ import annotations
 

@@ -35,7 +35,7 @@ DENSE_NK = [(2112, 7168), (24576, 1536), (32768, 512), (7168, 16384), (4096, 716
 
 def load_reference():
     if not os.path.isfile(os.path.join(REF_PKG, "__init__.py")):
-        raise SystemExit(json.dumps({"unavailable": "baseline/_ref holds no reference installation (run baseline/build_ref.py where /root/reference exists)"}))
+        raise SystemExit(json.dumps({"unavailable": "baseline/_ref holds no reference installation (run baseline/build_ref.py where the reference's source tree is mounted)"}))
     os.environ.setdefault("DG_JIT_CACHE_DIR", os.path.join(HERE, "_ref", "jit_cache"))
     spec = importlib.util.spec_from_file_location("deep_gemm_reference", os.path.join(REF_PKG, "__init__.py"),
                                                   submodule_search_locations=[REF_PKG])
