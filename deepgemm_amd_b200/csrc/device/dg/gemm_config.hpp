@@ -87,7 +87,12 @@ struct GemmLayout {
     DG_HDC uint32_t off_barriers() const { return off_sfb() + sfb_buffers() * sfb_bytes(); }
     DG_HDC uint32_t num_barriers() const { return 3 * num_stages + 2 * 2; }
     DG_HDC uint32_t off_misc() const { return off_barriers() + num_barriers() * 8; }
-    DG_HDC uint32_t total_bytes() const { return off_misc() + 16; }      // tensor-memory base, abort flag
+    // (tensor-memory base, abort flag).  With shortened A stages the MMA of the last stage still reads block_m rows from
+    // that stage's base: the allocation reaches at least that far, so the read stays inside this CTA's shared memory
+    DG_HDC uint32_t total_bytes() const {
+        const uint32_t used = off_misc() + 16, a_read_end = off_a() + (num_stages - 1) * a_bytes() + block_m * block_k;
+        return a_rows && a_read_end > used ? a_read_end : used;
+    }
 
     // Tensor memory: two accumulators of block_n columns (two tiles in flight when block_m is 128, the two 128-row
     // halves of one tile when it is 256), then SFA (4 columns per 128 rows) and SFB (4 columns per 128 columns of the tile)

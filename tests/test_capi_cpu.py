@@ -136,12 +136,33 @@ def test_heuristics_invariants(fp32):
                 # the slices of a tile are one thread-block cluster: portable size, one CTA per slice, and a parked FP32
                 # accumulator fits the pipeline stages it overwrites
                 assert cfg["num_splits"] <= 8 and cfg["num_ctas"] == cfg["num_tiles"] and cfg["cluster_size"] == 1
-                assert cfg["block_n"] * 128 * 4 <= cfg["num_stages"] * (128 + cfg["block_n"]) * 128
+                # (what it receives: the slices of the 8-column chunks it owns; the area starts at the D staging buffers)
+                recv = cfg["num_splits"] * -(-(cfg["block_n"] // 8) // cfg["num_splits"]) * 8 * 128 * 4
+                assert recv <= cfg["store_buffers"] * 16384 + cfg["num_stages"] * (cfg["a_rows"] + cfg["block_n"]) * 128
         else:
             assert cfg["kb_per_split"] == kb and not cfg["split_in_cluster"]
     for kind, groups in ((1, 32), (2, 16)):
         cfg = dg.get_gemm_config(kind, 256 if kind == 2 else 32 * 1024, 4096, 7168, num_groups=groups, expected_m=64)
         assert cfg["smem_bytes"] <= 232448 and cfg["num_ctas"] <= 148
+
+
+@pytest.mark.parametrize("shape", [(8, 128, 128), (1, 16, 128), (16, 2112, 7168), (33, 1000, 512), (40, 128, 128), (64, 16, 128),
+                                   (64, 7168, 2048), (48, 264, 1152), (64, 24576, 1536)])
+def test_shortened_a_stages_keep_the_mma_read_inside_shared_memory(shape, monkeypatch):
+    """A dense GEMM with at most 64 rows stages 16, 32 or 64 rows of A, but the MMA of every stage still reads 128 rows
+    from the stage's base: the dynamic shared memory the kernel is launched with must reach the end of that read for the
+    last stage too (small shapes have little behind the A stages)."""
+    m, n, k = shape
+    for swap in ("-1", "1"):
+        monkeypatch.setenv("DG_FORCE_SWAP_AB", swap)
+        cfg = dg.get_gemm_config(0, m, n, k)
+        rows = n if cfg["swap_ab"] else m
+        assert cfg["a_rows"] == (128 if rows > 64 else 16 if rows <= 16 else 32 if rows <= 32 else 64), cfg
+        a_base = cfg["store_buffers"] * 16384                       # the A stages follow the D staging buffers
+        assert cfg["smem_bytes"] >= a_base + (cfg["num_stages"] - 1) * cfg["a_rows"] * 128 + 128 * 128, cfg
+        assert cfg["smem_bytes"] <= 232448
+    monkeypatch.setenv("DG_FORCE_A_ROWS", "128")
+    assert dg.get_gemm_config(0, m, n, k)["a_rows"] == 128
 
 
 def test_operand_swap_can_be_forced_and_forbidden(monkeypatch):
