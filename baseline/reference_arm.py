@@ -4,6 +4,7 @@ its own sm_100 kernel `sm100_fp8_fp4_gemm_1d1d_impl` through its own Python API,
 for the shapes of the benchmark configurations, timed the way this repository's kernels are timed.
 
     python baseline/reference_arm.py --stage layout|small|dense|grouped|all [--out rows.json] [--sustained]
+    python baseline/reference_arm.py --stage probe [--m 4096]     # three plain calls per dense shape, for a profiler
 
 Stages go from harmless to heavy so that a first run on a new machine can stop early:
   layout   only the reference's scale-packing kernel (plain CUDA, no TMA, no barriers), compared bit for bit with this
@@ -169,6 +170,19 @@ def stage_dense(ref, torch, out, with_sustained, ms):
     out["dense"] = rows
 
 
+def stage_probe(ref, torch, out, ms):
+    """Three plain calls of the reference's GEMM per dense shape and nothing else on the GPU in between: what a
+    counter capture of its kernel (one launch per shape) runs."""
+    for m in ms:
+        for i, (n, k) in enumerate(DENSE_NK):
+            c = make_dense(ref, m, n, k, 77 + i, torch)
+            for _ in range(3):
+                ref.fp8_gemm_nt((c["qa"], c["psfa"]), (c["qb"], c["psfb"]), c["d"], recipe=(1, 1, 128))
+            torch.cuda.synchronize()
+            del c
+    out["probe"] = {"calls_per_shape": 3, "m": ms, "shapes_nk": [list(x) for x in DENSE_NK]}
+
+
 def stage_grouped(ref, torch, out, with_sustained):
     rows = []
     rng = random.Random(0)
@@ -247,7 +261,7 @@ def stage_grouped(ref, torch, out, with_sustained):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--stage", default="all", choices=["layout", "small", "dense", "grouped", "all"])
+    ap.add_argument("--stage", default="all", choices=["layout", "small", "dense", "grouped", "all", "probe"])
     ap.add_argument("--sustained", action="store_true")
     ap.add_argument("--m", default="4096", help="comma-separated row counts of the dense stage")
     ap.add_argument("--out", default="")
@@ -260,6 +274,11 @@ def main():
            "device": torch.cuda.get_device_name(0)}
     log("reference", ref.__version__, "loaded; num_sms", ref.get_num_sms())
     order = ["layout", "small", "dense", "grouped"]
+    if args.stage == "probe":
+        stage_probe(ref, torch, out, [int(v) for v in args.m.split(",")])
+        out["ok"] = True
+        print(json.dumps(out), flush=True)
+        return
     upto = order if args.stage == "all" else order[:order.index(args.stage) + 1]
     ok = True
     if "layout" in upto:

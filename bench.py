@@ -198,13 +198,24 @@ def run_reference_arm(args, rank):
 # ----------------------------------------------------------------------------------------------------
 # GPU arm
 # ----------------------------------------------------------------------------------------------------
-def make_dense_case(m, n, k, seed, torch, dg, columns=None):
+def make_dense_case(m, n, k, seed, torch, dg, columns=None, fp4=False):
     """One dense case; with `columns = (lo, hi)` only that column shard of the problem: rows [lo, hi) of B and of its
-    scales (cut on multiples of 128, so the 128 x 128 scale blocks are those of the whole matrix) and D[:, lo:hi]."""
-    from deepgemm_amd_b200.utils import per_block_cast_to_fp8, per_token_cast_to_fp8
+    scales (cut on multiples of 128, so the 128 x 128 scale blocks are those of the whole matrix) and D[:, lo:hi].
+    `fp4`: both operands packed E2M1 with 1 x 32 scales (the kind::mxf4 kernel; profiling runs on one GPU)."""
+    from deepgemm_amd_b200.utils import per_block_cast_to_fp8, per_token_cast_to_fp4, per_token_cast_to_fp8
     g = torch.Generator(device="cuda").manual_seed(seed)
     a = torch.randn((m, k), device="cuda", dtype=torch.bfloat16, generator=g)
     b = torch.randn((n, k), device="cuda", dtype=torch.bfloat16, generator=g)
+    if fp4:
+        assert columns is None
+        qa, sfa = per_token_cast_to_fp4(a, True, 32)
+        qb, sfb = per_token_cast_to_fp4(b, True, 32)
+        raw = (sfa, sfb)
+        sfa = dg.transform_sf_into_required_layout(sfa, m, k, (1, 32))
+        sfb = dg.transform_sf_into_required_layout(sfb, n, k, (1, 32))
+        d = torch.empty((m, n), device="cuda", dtype=torch.bfloat16)
+        return {"m": m, "n": n, "k": k, "full_n": n, "columns": (0, n), "a": (qa, sfa), "b": (qb, sfb), "d": d, "seed": seed,
+                "scales_fp32": raw, "recipe": {"recipe_a": (1, 32), "recipe_b": (1, 32)}}
     qa, sfa = per_token_cast_to_fp8(a, True, 128)
     qb, sfb = per_block_cast_to_fp8(b, True)
     lo, hi = columns if columns is not None else (0, n)
@@ -215,7 +226,7 @@ def make_dense_case(m, n, k, seed, torch, dg, columns=None):
     sfb = dg.transform_sf_into_required_layout(sfb, hi - lo, k, (128, 128))
     d = torch.empty((m, hi - lo), device="cuda", dtype=torch.bfloat16)
     return {"m": m, "n": hi - lo, "k": k, "full_n": n, "columns": (lo, hi), "a": (qa, sfa), "b": (qb, sfb), "d": d, "seed": seed,
-            "scales_fp32": raw}
+            "scales_fp32": raw, "recipe": {"recipe": (1, 1, 128)}}
 
 
 def flat_storage(t, torch):
@@ -439,6 +450,7 @@ def main():
     ap.add_argument("--pdl", action="store_true", help="launch the GEMMs with programmatic dependent launch (set_pdl)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--shapes", default="", help="comma-separated NxK subset of the six dense shapes (profiling runs)")
+    ap.add_argument("--fp4", action="store_true", help="both operands FP4 with 1 x 32 scales: the kind::mxf4 kernel (profiling runs, one GPU)")
     ap.add_argument("--m", type=int, default=M_DENSE, help="rows of A (profiling runs of the M = 64 / 128 shapes; the metric is quoted at 4096)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -474,12 +486,12 @@ def main():
         cols = shard_columns(n, world, rank) if world > 1 else None
         if cols is not None and cols[1] <= cols[0]:
             continue                                   # fewer 128-column blocks than ranks: this rank idles on this shape
-        cases.append(make_dense_case(args.m, n, k, 1000 + i, torch, dg, cols))
+        cases.append(make_dense_case(args.m, n, k, 1000 + i, torch, dg, cols, fp4=args.fp4))
     pass_flops = sum(flops_of(args.m, n, k) for n, k in nk_list)            # of the WHOLE problem, whatever the split
 
     def one_pass():
         for c in cases:
-            dg.fp8_gemm_nt(c["a"], c["b"], c["d"], recipe=(1, 1, 128))
+            dg.fp8_fp4_gemm_nt(c["a"], c["b"], c["d"], **c["recipe"])
 
     # The library's launch option (the reference's set_pdl): a GEMM's set-up overlaps the tail of the one before.
     # Off by default, as in the library: on this step it measured 2 % slower.
@@ -548,7 +560,7 @@ def main():
             with torch.cuda.stream(s_mm):
                 s_mm.wait_event(ev_in[i])
                 s_mm.wait_event(ev_out[i])                # the previous pass's read-back of this D is complete
-                dg.fp8_gemm_nt(c["a"], c["b"], c["d"], recipe=(1, 1, 128))
+                dg.fp8_fp4_gemm_nt(c["a"], c["b"], c["d"], **c["recipe"])
                 ev_mm[i].record(s_mm)
             with torch.cuda.stream(s_out):
                 s_out.wait_event(ev_mm[i])
@@ -619,8 +631,8 @@ def main():
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt_max / args.steps * 1e3, 4),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate, bf16 out)",
         "data": "synthetic",
-        "config": {"workload": "dense_fp8_gemm_nt_m4096 (BASELINE config 2, the six (N,K) at M=4096)" if args.m == M_DENSE and not args.shapes
-                               else f"profiling subset: M={args.m}, {len(nk_list)} of the dense shapes",
+        "config": {"workload": "dense_fp8_gemm_nt_m4096 (BASELINE config 2, the six (N,K) at M=4096)" if args.m == M_DENSE and not args.shapes and not args.fp4
+                               else f"profiling subset: M={args.m}, {len(nk_list)} of the dense shapes" + (", FP4 x FP4 (kind::mxf4)" if args.fp4 else ""),
                    "shapes_mnk": [[args.m, n, k] for n, k in nk_list],
                    "passes_per_step": args.passes,
                    "scales": "UE8M0 packed int32, A 1x128, B 128x128 pre-broadcast",
