@@ -46,9 +46,9 @@ DEFAULT_PASSES = 128
 # capture of this script (profiles/dg_gemm_fp8_fp4_dense_m4096.md), with the tile the capture ran (rows per CTA, tile
 # columns, raster group, CTAs per tile): the figure is reported only while the heuristics still choose that tile (D
 # written late in a launch may still sit in L2 when it ends).
-NCU_DRAM_BYTES = {(2112, 7168): (46539264, (256, 240, 4, 2)), (24576, 1536): (229246720, (128, 240, 8, 2)),
-                  (32768, 512): (247148288, (256, 240, 4, 2)), (7168, 16384): (530350848, (128, 224, 8, 2)),
-                  (4096, 7168): (71331840, (256, 240, 4, 2)), (7168, 2048): (31581440, (128, 224, 8, 2))}
+NCU_DRAM_BYTES = {(2112, 7168): (46705920, (256, 240, 4, 2)), (24576, 1536): (229373696, (128, 240, 8, 2)),
+                  (32768, 512): (247539968, (256, 240, 4, 2)), (7168, 16384): (535451904, (128, 224, 8, 2)),
+                  (4096, 7168): (72103424, (256, 240, 4, 2)), (7168, 2048): (31843328, (128, 224, 8, 2))}
 
 
 def flops_of(m, n, k):
