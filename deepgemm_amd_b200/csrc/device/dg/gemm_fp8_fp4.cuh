@@ -186,7 +186,7 @@ static_assert(!kDIsFP8 || ((kGemmType == kDense || kGemmType == kBatched) && !kA
 static_assert(kGemmType != kBatched || (kCluster == 1 && !kSplitK), "batched: one CTA per tile");
 static_assert(!kBatchReduce || (kGemmType == kDense && kABIsBF16 && !kAMnMajor && !kBMnMajor && kCluster == 1),
               "the batch-reduced GEMM takes K-major BF16 operands, one CTA per tile");
-static_assert(!kTransposedD || (kGemmType == kDense && kCluster == 1 && kMHalves == 1 && !kAccumulate && !kDIsFP8 && !kStochastic && !kSplitK),
+static_assert(!kTransposedD || (kGemmType == kDense && (kCluster == 1 || kSplitCluster == 1) && kMHalves == 1 && !kAccumulate && !kDIsFP8 && !kStochastic && !kSplitK),
               "the transposed epilogue serves the plain dense GEMM");
 static_assert(kSplitCluster >= 1 && kSplitCluster <= 8, "portable cluster sizes");
 static_assert(kSplitCluster == 1 || (kGemmType == kDense && !kSplitK && kCluster == 1 && kMHalves == 1 && !kAccumulate && !kDIsFP8 && !kStochastic),
@@ -240,6 +240,8 @@ constexpr uint32_t kSmemA   = kLayout.off_a();
 constexpr uint32_t kRecvCols = (BLOCK_N / 8 + kSplitCluster - 1) / kSplitCluster * 8;
 constexpr uint32_t kRecvBytes = kSplitCluster * kRecvCols * 128 * 4;
 constexpr bool kRecvOverStages = kRecvBytes > kSmemA;
+// Transposed output: rows of D (columns of the tile) staged per TMA store, as many as the D staging buffers hold
+constexpr uint32_t kTransposedRows = BLOCK_N * 128 * kDElemBytes <= kSmemA ? BLOCK_N : (kSmemA / (128 * kDElemBytes)) / 16 * 16;
 constexpr uint32_t kABytes  = kLayout.a_bytes();
 constexpr uint32_t kBBytes  = kLayout.b_bytes();
 constexpr uint32_t kSmemB   = kLayout.off_b();
@@ -960,23 +962,41 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
             };
 
             if constexpr (kTransposedD) {
-                // Thread = one row of the tile = one column of the caller's D: consecutive lanes write consecutive elements
-                const uint32_t d_col = tile.m_block * BLOCK_M + row_in_tile;
+                // Thread = one row of the tile = one column of the caller's D.  The tile leaves transposed through shared
+                // memory: chunk by chunk of `kTRows` rows of D (= columns of the tile), every thread writes its element of
+                // each row (consecutive lanes, consecutive addresses), and one TMA store per chunk takes the
+                // [kTRows][128] block to D, which also clips rows beyond the caller's M and columns beyond its N.
+                constexpr uint32_t kTRowBytes = 128 * kDElemBytes;
+                constexpr uint32_t kTRows = kTransposedRows;
+                const uint32_t t_stage = smem_base + kSmemD;
+                const uint32_t d_col0 = tile.m_block * TILE_M + cta_rank * CTA_M;       // first column of D this CTA writes
                 #pragma unroll
-                for (uint32_t b = 0; b < BLOCK_N / 16; ++b) {
-                    uint32_t v[16];
-                    tmem_ld_32x32b_x16(tmem_row_addr + b * 16, v);
-                    tmem_ld_wait();
-                    if (b + 1 == BLOCK_N / 16) release_tmem();
+                for (uint32_t c0 = 0; c0 < BLOCK_N; c0 += kTRows) {
+                    // the staging block is free once the previous chunk's store has read it
+                    if (store_iter > 0) {
+                        if (epi_tid == 0) tma_store_wait_read<0>();
+                        named_barrier_sync(bar_id, kNumEpilogueThreads);
+                    }
+                    ++store_iter;
                     #pragma unroll
-                    for (uint32_t i = 0; i < 16; ++i) {
-                        const uint32_t d_row = n0 + b * 16 + i;
-                        if (d_row < p.shape_n && d_col < p.shape_m) {
+                    for (uint32_t b = c0 / 16; b < (c0 + kTRows < BLOCK_N ? c0 + kTRows : BLOCK_N) / 16; ++b) {
+                        uint32_t v[16];
+                        tmem_ld_32x32b_x16(tmem_row_addr + b * 16, v);
+                        tmem_ld_wait();
+                        if (b + 1 == BLOCK_N / 16) release_tmem();
+                        #pragma unroll
+                        for (uint32_t i = 0; i < 16; ++i) {
                             const float x = __uint_as_float(v[i]) * p.alpha;
-                            const size_t at = static_cast<size_t>(d_row) * p.ldd + d_col;
-                            if constexpr (kDIsFP32) reinterpret_cast<float*>(p.d)[at] = x;
-                            else reinterpret_cast<unsigned short*>(p.d)[at] = static_cast<unsigned short>(pack_bf16x2(x, 0.0f) & 0xFFFFu);
+                            const uint32_t at = t_stage + (b * 16 + i - c0) * kTRowBytes + row_in_tile * kDElemBytes;
+                            if constexpr (kDIsFP32) st_shared_u32(at, __float_as_uint(x));
+                            else st_shared_u16(at, pack_bf16x2(x, 0.0f) & 0xFFFFu);
                         }
+                    }
+                    fence_proxy_async_smem();
+                    named_barrier_sync(bar_id, kNumEpilogueThreads);
+                    if (epi_tid == 0) {
+                        tma_store_2d(&tm_d, t_stage, static_cast<int32_t>(d_col0), static_cast<int32_t>(n0 + c0));
+                        tma_store_commit();
                     }
                 }
                 continue;

@@ -277,14 +277,15 @@ Problem swapped(const Problem& p) {
 // Whether a dense GEMM may run with its operands swapped (DG_FORCE_SWAP_AB: 1 = whenever this holds, -1 = never)
 bool swap_allowed(const Problem& p) {
     return p.kind == DG_GEMM_DENSE && !p.a_mn_major && !p.b_mn_major && !p.accumulate &&
-           !p.d_fp8 && !p.stochastic && p.reduce_batches <= 1 && p.m <= 64 && p.n >= 128 && env_int("FORCE_SWAP_AB") >= 0 &&
-           env_int("FORCE_CLUSTER") <= 1 && env_int("FORCE_BLOCK_M") != 256 && env_int("FORCE_BLOCK_K") != 64;
+           !p.d_fp8 && !p.stochastic && p.reduce_batches <= 1 && p.m <= 128 && p.n >= 128 && env_int("FORCE_SWAP_AB") >= 0 &&
+           env_int("FORCE_BLOCK_M") != 256 && env_int("FORCE_BLOCK_K") != 64;
 }
 
 struct Constraints {
     bool allow_cluster_split = true;
     int only_bn = 0;                  // swapped operands: the tile is as wide as the caller's M, rounded up to 16
     bool swapped = false;             // 128-row tiles, K slices only inside a cluster (the transposed epilogue's two forms)
+    bool swapped_pairs = false;       // CTA pairs are candidates of the swapped form (each CTA loads half of the activations' tile)
 };
 
 int choose_config_for(const Problem& p, dg_gemm_config_t* cfg, const Constraints& lim, double* cost_out) {
@@ -313,7 +314,9 @@ int choose_config_for(const Problem& p, dg_gemm_config_t* cfg, const Constraints
     for (int halves = 1; halves <= 2; ++halves)
     for (int bk = 128; bk >= 64; bk /= 2) {
         if (forced_cluster ? cluster != forced_cluster : !cluster_allowed(p, cluster)) continue;
-        if (lim.swapped && (cluster != 1 || halves != 1 || bk != 128)) continue;
+        // (swapped: 128-row CTAs, alone or as a pair that shares the activations' tile; a pair's K is not sliced)
+        if (lim.swapped && (halves != 1 || bk != 128)) continue;
+        if (lim.swapped && cluster == 2 && !(forced_cluster == 2 || lim.swapped_pairs)) continue;
         // A CTA pair multiplies all its rows with one B: in the contiguous layout every expert segment must then be a
         // whole number of pair tiles
         if (cluster == 2 && (num_sms % 2 != 0 || (p.b_fp4 && p.b_mn_major) || p.kind == DG_GEMM_M_GROUPED_CONTIGUOUS_PSUM || p.kind == DG_GEMM_K_GROUPED_CONTIGUOUS ||
@@ -497,19 +500,23 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg, bool allow_cluster_sp
     const int forced_swap = env_int("FORCE_SWAP_AB");
     const int rc = choose_config_for(p, cfg, direct, &direct_cost);
     if (!swap_allowed(p) || !allow_cluster_split) return rc;
-    // Measured on 28 (M, N, K) points: up to 32 rows the swapped form wins wherever the cost model prefers it (by 5-30 %);
-    // at 64 rows the two are within 5 % either way and the transposed epilogue's scalar stores start to show, so it is
-    // used on request only
-    if (forced_swap <= 0 && p.m > 32) return rc;
+    // Measured on 28 (M, N, K) points: up to 32 rows the swapped form wins wherever the cost model prefers it (by 5-30 %).
+    // From 33 to 64 rows the two are closer (the swapped tile carries as many activation bytes as weight bytes per
+    // column): there the swapped form has to be modelled 7 % cheaper, which on the six benchmark shapes at M = 64 picks
+    // it where it measured 1-7 % faster and not where it measured 3 % slower.  Above 64 rows (up to 128) on request only.
+    if (forced_swap <= 0 && p.m > 64) return rc;
     Constraints lim;
     lim.swapped = true;
     lim.only_bn = static_cast<int>(align_up<int64_t>(p.m, 16));
     dg_gemm_config_t other{};
     double other_cost = 0;
     if (choose_config_for(swapped(p), &other, lim, &other_cost) != DG_OK) return rc;
+    if (env_int("PRINT_CONFIGS"))
+        fprintf(stderr, "[dg] m %d n %d k %d: modelled cycles direct %.0f (block_n %d x%d), operands swapped %.0f (x%d)\n", p.m, p.n, p.k,
+                direct_cost, cfg->block_n, cfg->num_splits, other_cost, other.num_splits);
     // (up to 16 rows the swapped form was the faster or an equal one on all 14 shapes timed, also where the model's wave
     // count speaks against its many small tiles)
-    if (rc != DG_OK || forced_swap > 0 || p.m <= 16 || other_cost < direct_cost) {
+    if (rc != DG_OK || forced_swap > 0 || p.m <= 16 || other_cost < direct_cost * (p.m > 32 ? 0.93 : 1.0)) {
         *cfg = other;
         return DG_OK;
     }
@@ -826,7 +833,14 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
                             (k_grouped ? static_cast<uint64_t>(p.groups) * p.m : a_rows);
     const uint64_t d_pitch_bytes = split ? ld_ws * 4 : a->ldd * (p.d_fp32 ? 4 : (p.d_fp8 ? 1 : 2));
     if (cfg.swap_ab) {
-        tm_d = tm_d_full = tm_a;                 // never used: the transposed epilogue stores without a tensor map
+        // The transposed epilogue stages [rows of the caller's D][128 of its columns] blocks (plain row-major, as many rows
+        // as the D staging buffers hold) and stores them through this map: the caller's D as it is, N (here p.m) contiguous.
+        // K slices reduced inside a cluster write D directly and do not use it.
+        const uint64_t d_elem = p.d_fp32 ? 4 : 2;
+        const uint32_t t_rows = static_cast<uint64_t>(cfg.block_n) * 128 * d_elem <= lay.off_a()
+                                    ? static_cast<uint32_t>(cfg.block_n) : static_cast<uint32_t>(lay.off_a() / (128 * d_elem) / 16 * 16);
+        if ((rc = encode_2d(&tm_d, d_type, a->d, p.m, p.n, a->ldd * d_elem, 128, t_rows, CU_TENSOR_MAP_SWIZZLE_NONE)) != DG_OK) return rc;
+        tm_d_full = tm_d;
     } else {
         if ((rc = encode_2d(&tm_d, d_type, d_base, p.n, d_rows, d_pitch_bytes, lay.store_cols(), 128, d_swizzle, nb, bs_d)) != DG_OK) return rc;
         if ((rc = encode_2d(&tm_d_full, d_type, d_base, p.n, d_rows, d_pitch_bytes, lay.group_cols(), 128,

@@ -123,7 +123,7 @@ def test_heuristics_invariants(fp32):
         rows, cols = (n, m) if cfg["swap_ab"] else (m, n)        # operands swapped: the kernel's rows are the caller's N
         if cfg["swap_ab"]:
             # few rows only; one tile column as wide as the caller's M; K slices, if any, inside a cluster
-            assert m <= 64 and cfg["block_m"] == 128 and cfg["block_n"] == -(-m // 16) * 16 and cfg["cluster_size"] == 1
+            assert m <= 128 and cfg["block_m"] == 128 and cfg["block_n"] == -(-m // 16) * 16
             assert cfg["num_splits"] == 1 or cfg["split_in_cluster"]
         assert cfg["num_tiles"] == -(-rows // (cfg["block_m"] * cfg["cluster_size"])) * -(-cols // cfg["block_n"]) * cfg["num_splits"]
         kb = -(-k // 128)
@@ -166,17 +166,20 @@ def test_shortened_a_stages_keep_the_mma_read_inside_shared_memory(shape, monkey
 
 
 def test_operand_swap_can_be_forced_and_forbidden(monkeypatch):
-    """DG_FORCE_SWAP_AB: 1 = swap whenever the form applies (dense K-major FP8, M <= 64, no accumulation), -1 = never."""
+    """DG_FORCE_SWAP_AB: 1 = swap whenever the form applies (dense K-major FP8, M <= 128, no accumulation), -1 = never."""
     monkeypatch.setenv("DG_FORCE_SWAP_AB", "1")
     assert dg.get_gemm_config(0, 16, 4096, 7168)["swap_ab"] == 1
-    assert dg.get_gemm_config(0, 65, 4096, 7168)["swap_ab"] == 0            # too many rows
+    assert dg.get_gemm_config(0, 128, 4096, 7168)["swap_ab"] == 1           # up to 128 rows on request
+    assert dg.get_gemm_config(0, 129, 4096, 7168)["swap_ab"] == 0           # too many rows
     assert dg.get_gemm_config(0, 16, 4096, 7168, b_is_fp4=True, gran_k_b=32)["swap_ab"] == 1     # an FP4 weight becomes the A side
     assert dg.get_gemm_config(1, 4096, 4096, 7168, num_groups=4)["swap_ab"] == 0
     monkeypatch.setenv("DG_FORCE_SWAP_AB", "-1")
     assert dg.get_gemm_config(0, 16, 4096, 7168)["swap_ab"] == 0
     monkeypatch.delenv("DG_FORCE_SWAP_AB")
-    assert dg.get_gemm_config(0, 16, 4096, 7168)["swap_ab"] == 1            # chosen by cost up to 32 rows
-    assert dg.get_gemm_config(0, 64, 4096, 7168)["swap_ab"] == 0            # on request only beyond
+    assert dg.get_gemm_config(0, 16, 4096, 7168)["swap_ab"] == 1            # chosen by cost up to 64 rows
+    assert dg.get_gemm_config(0, 64, 4096, 7168)["swap_ab"] == 1            # (here: modelled 19 % cheaper)
+    assert dg.get_gemm_config(0, 64, 24576, 1536)["swap_ab"] == 0           # (here: modelled dearer)
+    assert dg.get_gemm_config(0, 65, 4096, 7168)["swap_ab"] == 0            # on request only beyond
 
 
 def test_second_staging_buffer_is_given_up_only_for_a_third_stage(monkeypatch):

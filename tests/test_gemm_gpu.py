@@ -249,6 +249,40 @@ def test_few_row_gemms_with_the_operands_swapped(m, n, k, out_dtype, monkeypatch
     assert oracle.calc_diff(outs["1"].float().cpu().numpy(), outs["-1"].float().cpu().numpy()) < 1e-6
 
 
+@pytest.mark.parametrize("m,n,k", [(128, 7168, 2048), (64, 2112, 1024), (100, 1000, 640), (128, 384, 256), (80, 4096, 512), (33, 520, 128)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float])
+def test_swapped_form_as_cta_pairs(m, n, k, out_dtype, monkeypatch):
+    """The swapped form run by CTA pairs (up to 128 rows): the weight is the 256-row operand of a pair, each CTA loads
+    half of the activations' tile, and both write their 128 columns of D through the staged transposed store, which must
+    clip at the caller's M and N (a wider D around the block stays untouched)."""
+    qa, sfa, qb, sfb, _ = quantise_dense(seeded_bf16((m, k), 311), seeded_bf16((n, k), 312))
+    ref = oracle.dequant_gemm_nt(qa, sfa, qb, sfb, alpha=1.25)
+    monkeypatch.setenv("DG_FORCE_SWAP_AB", "1")
+    monkeypatch.setenv("DG_FORCE_CLUSTER", "2")
+    cfg = dg.get_gemm_config(0, m, n, k, d_is_fp32=out_dtype == torch.float)
+    assert cfg["swap_ab"] == 1 and cfg["cluster_size"] == 2 and cfg["block_n"] == -(-m // 16) * 16 and cfg["num_splits"] == 1, cfg
+    d = torch.full((m + 2, n + 8), SENTINEL, dtype=out_dtype, device="cuda")
+    view = d[:m, :n]
+    a = (fp8_cuda(qa), packed_sf_cuda(sfa)); b = (fp8_cuda(qb), packed_sf_cuda(sfb))
+    outs = []
+    for _ in range(2):
+        dg.reset_kernel_status()
+        dg.fp8_gemm_nt(a, b, view, recipe=(1, 1, 128), alpha=1.25)
+        assert dg.kernel_status() == 0
+        outs.append(view.clone())
+    out = outs[0].float().cpu().numpy()
+    assert oracle.calc_diff(out, ref) < 1e-5, diff_report(out, ref)
+    full = d.float().cpu().numpy()
+    assert (full[:, n:] == SENTINEL).all() and (full[m:, :] == SENTINEL).all()
+    assert torch.equal(outs[0].view(torch.uint8), outs[1].view(torch.uint8))
+    monkeypatch.setenv("DG_FORCE_SWAP_AB", "-1")
+    monkeypatch.setenv("DG_FORCE_CLUSTER", "1")
+    monkeypatch.setenv("DG_FORCE_SPLIT_K", "1")
+    direct = torch.empty((m, n), dtype=out_dtype, device="cuda")
+    dg.fp8_gemm_nt(a, b, direct, recipe=(1, 1, 128), alpha=1.25)
+    assert oracle.calc_diff(out, direct.float().cpu().numpy()) < 1e-6
+
+
 @pytest.mark.parametrize("a_fp4", [False, True])
 @pytest.mark.parametrize("m,n,k", [(1, 2112, 7168), (24, 4096, 2048), (64, 576, 1024)])
 def test_few_row_gemms_with_an_fp4_weight_swapped(a_fp4, m, n, k, monkeypatch):
