@@ -769,28 +769,34 @@ def detail_rows(torch, dg):
     rng = random.Random(0)
     groups = 32
     actual = [int(8192 * rng.uniform(0.7, 1.3)) for _ in range(groups)]
-    aligned = [-(-x // 128) * 128 for x in actual]
-    m_total, valid = sum(aligned), sum(actual)
-    layout = torch.full((m_total,), -1, dtype=torch.int, device="cuda")
-    start = 0
-    for g, (am, al) in enumerate(zip(actual, aligned)):
-        layout[start:start + am] = g
-        start += al
-    for n, k in ((4096, 7168), (7168, 2048)):
-        a = torch.randn((m_total, k), device="cuda", dtype=torch.bfloat16)
-        a[layout < 0] = 0
-        qa, sfa = per_token_cast_to_fp8(a, True, 128)
-        del a
-        sfa = dg.transform_sf_into_required_layout(sfa, m_total, k, (1, 128))
-        d = torch.empty((m_total, n), device="cuda", dtype=torch.bfloat16)
-        for fp4 in (False, True):
-            qb, sfb = make_grouped_b(groups, n, k, fp4, torch, dg)
-            rb = (1, 32) if fp4 else (1, 128)
-            t = bench(lambda: dg.m_grouped_fp8_fp4_gemm_nt_contiguous((qa, sfa), (qb, sfb), d, layout, recipe_a=(1, 128), recipe_b=rb), 2, 5)
-            add(f"{'fp8xfp4 ' if fp4 else ''}m-grouped contiguous G{groups} M{m_total} (valid {valid}) n{n} k{k}", t,
-                flops_of(valid, n, k), m_total * k + groups * n * k // (2 if fp4 else 1) + m_total * n * 2)
-            del qb, sfb
-        del qa, sfa, d
+    valid = sum(actual)
+    # (alignment 128: the configuration as written; 256: what get_theoretical_mk_alignment_for_contiguous_layout() recommends
+    #  on sm_100 and what lets CTA pairs run: a pair multiplies 256 consecutive rows with one expert's weights)
+    for alignment in (128, 256):
+        aligned = [-(-x // alignment) * alignment for x in actual]
+        m_total = sum(aligned)
+        layout = torch.full((m_total,), -1, dtype=torch.int, device="cuda")
+        start = 0
+        for g, (am, al) in enumerate(zip(actual, aligned)):
+            layout[start:start + am] = g
+            start += al
+        dg.set_mk_alignment_for_contiguous_layout(alignment)
+        for n, k in ((4096, 7168), (7168, 2048)):
+            a = torch.randn((m_total, k), device="cuda", dtype=torch.bfloat16)
+            a[layout < 0] = 0
+            qa, sfa = per_token_cast_to_fp8(a, True, 128)
+            del a
+            sfa = dg.transform_sf_into_required_layout(sfa, m_total, k, (1, 128))
+            d = torch.empty((m_total, n), device="cuda", dtype=torch.bfloat16)
+            for fp4 in ((False, True) if alignment == 128 else (False,)):
+                qb, sfb = make_grouped_b(groups, n, k, fp4, torch, dg)
+                rb = (1, 32) if fp4 else (1, 128)
+                t = bench(lambda: dg.m_grouped_fp8_fp4_gemm_nt_contiguous((qa, sfa), (qb, sfb), d, layout, recipe_a=(1, 128), recipe_b=rb), 2, 5)
+                add(f"{'fp8xfp4 ' if fp4 else ''}m-grouped contiguous G{groups}{'' if alignment == 128 else ' alignment 256'} M{m_total} (valid {valid}) n{n} k{k}", t,
+                    flops_of(valid, n, k), m_total * k + groups * n * k // (2 if fp4 else 1) + m_total * n * 2)
+                del qb, sfb
+            del qa, sfa, d
+    dg.set_mk_alignment_for_contiguous_layout(128)
     # config 4: masked decode GEMM replayed from a CUDA graph
     groups, max_m, n, k = 16, 256, 4096, 7168
     masked = torch.tensor([rng.randint(45, 83) for _ in range(groups)], dtype=torch.int, device="cuda")
