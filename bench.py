@@ -343,7 +343,7 @@ def run_grouped_ep(torch, dist, dg, rank, world, barrier, check):
             sh = make_contiguous_shard(n, k, (g0, g1), actual, aligned, torch, dg)
             call = lambda: dg.m_grouped_fp8_gemm_nt_contiguous(sh["a"], sh["b"], sh["d"], sh["layout"], recipe=(1, 1, 128))
             barrier()
-            t = bench_events(call, 2, 5)
+            t = bench_events(call, 3, 10)
         else:
             sh, t = None, 0.0
         t_max = max_over_ranks(t, torch, dist, world)
@@ -393,6 +393,7 @@ def run_grouped_ep(torch, dist, dg, rank, world, barrier, check):
             dg.m_grouped_fp8_gemm_nt_masked(full["a"], full["b"], full["d"], full["masked"], 64, recipe=(1, 1, 128))
             checks[name] = {"bitwise_equal_to_single_gpu": bool(torch.equal(gathered.view(torch.int16), full["d"].view(torch.int16)))}
     out["scaling"] = "strong (the whole problem is split over the ranks)"
+    out["timing"] = "mean of 10 calls (C4: 20 graph replays), a 256 MB L2 flush before each, device events, max over ranks"
     return out, checks
 
 
