@@ -292,7 +292,7 @@ struct GemmParams {
 enum ProfileSlot : uint32_t {
     kProfProducerWaitEmpty = 0, kProfProducerTotal = 1, kProfMmaWaitFull = 2, kProfMmaWaitTmemEmpty = 3, kProfMmaTotal = 4,
     kProfSFWait = 5, kProfSFTotal = 6, kProfEpiWaitTmemFull = 7, kProfEpiTotal = 8, kProfEpiStoreWait = 9,
-    kProfMmaIssueCp = 10, kProfMmaIssueMma = 11, kProfMmaIssueCommit = 12, kProfNumSlots = 16
+    kProfMmaIssueCp = 10, kProfMmaIssueMma = 11, kProfMmaIssueCommit = 12, kProfMmaFence = 13, kProfMmaTail = 14, kProfNumSlots = 16
 };
 #if defined(DG_PROFILE) && DG_PROFILE
 #define DG_PROF_VAR(name) long long name = 0
@@ -597,6 +597,7 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                 bool ok = true;
                 uint32_t tile_iter = 0;
                 DG_PROF_VAR(prof_full); DG_PROF_VAR(prof_tmem); DG_PROF_VAR(prof_cp); DG_PROF_VAR(prof_mma); DG_PROF_VAR(prof_commit);
+                DG_PROF_VAR(prof_fence); DG_PROF_VAR(prof_tail);
                 DG_PROF_BEGIN(prof_t0);
                 while (ok && sched.next(tile)) {
                     if (kGemmType == kKGrouped && tile.num_kb == 0) continue;      // an empty group: the epilogue writes zeros
@@ -619,9 +620,11 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                         DG_PROF_BEGIN(prof_w1);
                         if (!mbar_wait(full_bar(stage), phase, ctx, kRoleMma, 2)) { ok = false; break; }
                         DG_PROF_ADD(prof_full, prof_w1);
-                        DG_PROF_STAMP(2);                       // first stage arrived
+                        if (it == 0) DG_PROF_STAMP(2);          // first stage arrived
                         if (it == 0 && tile_iter == 1 && lane == 0) DG_PROF_STAMP_MAX(12);      // ... in the last CTA to see one
+                        DG_PROF_BEGIN(prof_f0);
                         tc_fence_after_sync();
+                        DG_PROF_ADD(prof_fence, prof_f0);
                         if (issue_lane) {
                         // Scales: shared memory (rearranged by warp 2) -> tensor memory, in every CTA of the cluster
                         DG_PROF_BEGIN(prof_i0);
@@ -678,8 +681,10 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                         }
                         DG_PROF_ADD(prof_commit, prof_i2);
                         }
+                        DG_PROF_BEGIN(prof_t1);
                         if constexpr (kWholeWarp) __syncwarp();
                         advance_sf(kb);
+                        DG_PROF_ADD(prof_tail, prof_t1);
                     }
                 }
                 if (issue_lane) {
@@ -691,6 +696,8 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                 DG_PROF_FLUSH(kProfMmaIssueCp, prof_cp);
                 DG_PROF_FLUSH(kProfMmaIssueMma, prof_mma);
                 DG_PROF_FLUSH(kProfMmaIssueCommit, prof_commit);
+                DG_PROF_FLUSH(kProfMmaFence, prof_fence);
+                DG_PROF_FLUSH(kProfMmaTail, prof_tail);
                 }
             }
         } else if (warp_idx == 2 && kHasSF) {

@@ -880,9 +880,9 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
         DG_CUDA_RT(cudaStreamSynchronize(static_cast<cudaStream_t>(a->stream)));
         const double ctas = cfg.num_ctas, leaders = ctas / cfg.cluster_size;
         fprintf(stderr, "[dg profile] cycles per CTA: producer wait_empty %.0f / %.0f | mma wait_full %.0f wait_tmem_empty %.0f "
-                        "issue cp %.0f mma %.0f commit %.0f / %.0f | sf wait %.0f / %.0f | epilogue wait_tmem_full %.0f store_wait %.0f / %.0f\n",
+                        "issue cp %.0f mma %.0f commit %.0f fence %.0f tail %.0f / %.0f | sf wait %.0f / %.0f | epilogue wait_tmem_full %.0f store_wait %.0f / %.0f\n",
                 h[0] / ctas, h[1] / ctas, h[2] / leaders, h[3] / leaders, h[10] / leaders, h[11] / leaders, h[12] / leaders,
-                h[4] / leaders, h[5] / ctas, h[6] / ctas, h[7] / ctas, h[9] / ctas, h[8] / ctas);
+                h[13] / leaders, h[14] / leaders, h[4] / leaders, h[5] / ctas, h[6] / ctas, h[7] / ctas, h[9] / ctas, h[8] / ctas);
         const auto since_entry = [&](int slot) { return h[16 + slot] == 0 ? -1ll : (long long)(h[16 + slot] - h[16]); };
         fprintf(stderr, "[dg profile] CTA 0 timeline (ns after entry): set-up %lld | first stage %lld | first accumulator %lld | "
                         "parked %lld | cluster parked %lld | last store issued %lld | stores complete %lld | exit %lld\n",
