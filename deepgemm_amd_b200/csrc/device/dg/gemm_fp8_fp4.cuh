@@ -299,6 +299,15 @@ enum ProfileSlot : uint32_t {
 #define DG_PROF_BEGIN(var) const long long var = clock64()
 #define DG_PROF_ADD(acc, var) acc += clock64() - var
 #define DG_PROF_FLUSH(slot, acc) do { if (p.profile != nullptr) atomicAdd(p.profile + (slot), static_cast<unsigned long long>(acc)); } while (0)
+// (the segments inside the MMA warp's K loop cost ten clock reads per K-block, enough to make that warp the bottleneck
+//  of small tiles: DG_PROFILE=2 leaves them out and keeps the waits and totals)
+#if DG_PROFILE == 1
+#define DG_PROF_FINE_BEGIN(var) const long long var = clock64()
+#define DG_PROF_FINE_ADD(acc, var) acc += clock64() - var
+#else
+#define DG_PROF_FINE_BEGIN(var) do { } while (0)
+#define DG_PROF_FINE_ADD(acc, var) do { } while (0)
+#endif
 // Timeline of CTA 0 in nanoseconds (globaltimer): slots 16.. hold absolute stamps, first writer wins
 #define DG_PROF_STAMP(slot) do { if (p.profile != nullptr && blockIdx.x == 0) atomicCAS(p.profile + 16 + (slot), 0ull, global_timer_ns()); } while (0)
 // over all CTAs: the earliest / latest time an event happened anywhere in the grid
@@ -309,6 +318,8 @@ enum ProfileSlot : uint32_t {
 #define DG_PROF_STAMP_MIN(slot) do { } while (0)
 #define DG_PROF_STAMP_MAX(slot) do { } while (0)
 #define DG_PROF_VAR(name) do { } while (0)
+#define DG_PROF_FINE_BEGIN(var) do { } while (0)
+#define DG_PROF_FINE_ADD(acc, var) do { } while (0)
 #define DG_PROF_BEGIN(var) do { } while (0)
 #define DG_PROF_ADD(acc, var) do { } while (0)
 #define DG_PROF_FLUSH(slot, acc) do { } while (0)
@@ -622,12 +633,12 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                         DG_PROF_ADD(prof_full, prof_w1);
                         if (it == 0) DG_PROF_STAMP(2);          // first stage arrived
                         if (it == 0 && tile_iter == 1 && lane == 0) DG_PROF_STAMP_MAX(12);      // ... in the last CTA to see one
-                        DG_PROF_BEGIN(prof_f0);
+                        DG_PROF_FINE_BEGIN(prof_f0);
                         tc_fence_after_sync();
-                        DG_PROF_ADD(prof_fence, prof_f0);
+                        DG_PROF_FINE_ADD(prof_fence, prof_f0);
                         if (issue_lane) {
                         // Scales: shared memory (rearranged by warp 2) -> tensor memory, in every CTA of the cluster
-                        DG_PROF_BEGIN(prof_i0);
+                        DG_PROF_FINE_BEGIN(prof_i0);
                         if (kHasSF && kb % kSFAPeriod == 0) {
                             #pragma unroll
                             for (uint32_t i = 0; i < kSFAWords * SF_BLOCK_M / 128; ++i)      // chunk (word w, rows 128 r ..): index w * (rows / 128) + r
@@ -640,8 +651,8 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                                 tc_cp_32x128b_warpx4<kCluster>(tmem_base + kTmemColSFB + i * 4,
                                                                make_smem_desc(sfb_buffer() + i * 512, 0, 128, kSwizzleNone));
                         }
-                        DG_PROF_ADD(prof_cp, prof_i0);
-                        DG_PROF_BEGIN(prof_i1);
+                        DG_PROF_FINE_ADD(prof_cp, prof_i0);
+                        DG_PROF_FINE_BEGIN(prof_i1);
                         const uint64_t a_desc = make_smem_desc(smem_base + kSmemA + stage * kABytes, kALbo, kASbo, kASwizzle);
                         const uint64_t b_desc = make_smem_desc(smem_base + kSmemB + stage * kBBytes, kBLbo, kBSbo, kBSwizzle);
                         #pragma unroll
@@ -672,19 +683,19 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                                                               tmem_base + kTmemColSFA + h * 4, tmem_base + kTmemColSFB, ((kb - kb0) | j) != 0);
                             }
                         }
-                        DG_PROF_ADD(prof_mma, prof_i1);
-                        DG_PROF_BEGIN(prof_i2);
+                        DG_PROF_FINE_ADD(prof_mma, prof_i1);
+                        DG_PROF_FINE_BEGIN(prof_i2);
                         commit_all(empty_bar(stage));                      // releases the stage once its MMAs have read it
                         if (it + 1 == num_steps) {                         // accumulator(s) complete
                             #pragma unroll
                             for (uint32_t h = 0; h < kMHalves; ++h) commit_all(tmem_full_bar(accum + h));
                         }
-                        DG_PROF_ADD(prof_commit, prof_i2);
+                        DG_PROF_FINE_ADD(prof_commit, prof_i2);
                         }
-                        DG_PROF_BEGIN(prof_t1);
+                        DG_PROF_FINE_BEGIN(prof_t1);
                         if constexpr (kWholeWarp) __syncwarp();
                         advance_sf(kb);
-                        DG_PROF_ADD(prof_tail, prof_t1);
+                        DG_PROF_FINE_ADD(prof_tail, prof_t1);
                     }
                 }
                 if (issue_lane) {
