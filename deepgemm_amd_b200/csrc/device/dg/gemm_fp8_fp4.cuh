@@ -91,7 +91,7 @@ namespace dg {
 constexpr uint32_t kGemmType   = DG_GEMM_TYPE;
 constexpr uint32_t BLOCK_M     = 128;
 constexpr uint32_t BLOCK_N     = DG_BLOCK_N;
-constexpr uint32_t BLOCK_K     = DG_BLOCK_K;       // bytes of K per row of a pipeline stage (64 or 128)
+constexpr uint32_t BLOCK_K     = DG_BLOCK_K;       // bytes of K per row of a pipeline stage (64, 128 or 256)
 constexpr bool     kABIsBF16   = DG_AB_BF16 != 0;
 constexpr uint32_t kABElemBytes = kABIsBF16 ? 2 : 1;
 #ifndef DG_MXF4
@@ -153,8 +153,16 @@ static_assert(!kABIsBF16 || (!kAIsFP4 && !kBIsFP4 && BLOCK_K == 128), "BF16 oper
 static_assert(kGranKA == 32 || kGranKA == 128, "one scale per 32 or 128 elements of K");
 static_assert(kGranKB == 32 || kGranKB == 128, "one scale per 32 or 128 elements of K");
 static_assert(kNumStages >= 2 && kNumStages <= 32, "pipeline depth");
-static_assert(BLOCK_K == 128 || (BLOCK_K == 64 && !kAIsFP4 && !kBIsFP4 && !kAMnMajor && !kBMnMajor && !kSplitK),
+static_assert(BLOCK_K == 128 || BLOCK_K == 256 || (BLOCK_K == 64 && !kAIsFP4 && !kBIsFP4 && !kAMnMajor && !kBMnMajor && !kSplitK),
               "64-element stages are built for K-major FP8 operands and unsliced K");
+// A 256-byte stage is two 128-byte swizzle atoms side by side, [atom of K][row][128 bytes]: two copies per operand on one
+// barrier and eight MMAs per wait.  Narrow tiles are bound by the MMA warp's walk around its loop (barrier poll, fence,
+// commit, re-convergence), not by the MMAs or the loads, and this halves the walks per byte of K.
+static_assert(BLOCK_K != 256 || (DG_GEMM_TYPE == 0 && !DG_AB_BF16 && !DG_A_FP4 && !DG_B_FP4 && !DG_MAJOR_A && !DG_MAJOR_B && DG_GRAN_K_A == 128 &&
+                                 DG_GRAN_K_B == 128 && DG_CLUSTER == 1 && DG_M_HALVES == 1),
+              "256-element stages are built for the dense GEMM of K-major FP8 operands with one scale per 128 elements, one 128-row CTA per tile");
+constexpr uint32_t kKAtoms = BLOCK_K > 128 ? BLOCK_K / 128 : 1;      // 128-byte swizzle atoms along K per K-major stage row
+constexpr uint32_t kKAtomBytes = BLOCK_K / kKAtoms;                  // width of one (the swizzle span): 64 or 128
 static_assert(kCluster == 1 || kCluster == 2, "one CTA or a CTA pair per tile");
 static_assert(kMHalves == 1 || kMHalves == 2, "128 or 256 rows per CTA");
 static_assert(!(kAIsFP4 && kAMnMajor), "a packed FP4 A must be K-major");
@@ -253,6 +261,9 @@ constexpr uint32_t kSmemBar = kLayout.off_barriers();   // full, sf_full, empty 
 constexpr uint32_t kSmemMisc = kLayout.off_misc();      // tensor-memory base address, abort flag
 constexpr uint32_t kSmemTotal = kLayout.total_bytes();
 static_assert(kABytes % (8 * BLOCK_K) == 0 && kBBytes % (8 * BLOCK_K) == 0, "every stage starts on a swizzle-pattern boundary (eight rows)");
+// Bytes between the K atoms of a stage: the rows the stage holds, 128 bytes each
+constexpr uint32_t kAAtomStride = kABytes / kKAtoms, kBAtomStride = kBBytes / kKAtoms;
+static_assert(kKAtoms == 1 || (kAAtomStride % 1024 == 0 && kBAtomStride % 1024 == 0), "every K atom starts on a swizzle-pattern boundary");
 static_assert(kSmemTotal <= kSmemCapacity, "shared memory budget exceeded");
 static_assert(kStoreCols % 16 == 0 || kDIsFP32, "a store covers whole 16-column tensor-memory loads");
 
@@ -279,7 +290,7 @@ struct GemmParams {
     float alpha;
     unsigned long long* profile; // optional cycle counters (kernels built with DG_PROFILE only), else null
     uint32_t num_splits;         // slices of K per output tile (1 = no split)
-    uint32_t kb_per_split;       // K-blocks per slice, a multiple of 4 so every slice starts on a packed scale word
+    uint32_t kb_per_split;       // K-blocks per slice, a multiple of 512 elements so every slice starts on a packed scale word
     uint32_t split_panel_rows;   // split-K: rows between consecutive slices' panels in the workspace D points to
     uint32_t group_alignment;    // prefix-sum layout: every group starts on a multiple of this many rows
     uint32_t* sfd;               // quantising epilogue: packed UE8M0 scales of D, word (row, column / 128) at sfd[(column / 128) * sfd_pitch + row]
@@ -552,7 +563,9 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                             continue;
                         }
                         if constexpr (!kAMnMajor) {
-                            load(smem_base + kSmemA + stage * kABytes, &tm_a, k_base + kb * kLoadXPerKBlock, a_row);      // one box of CTA_M rows
+                            #pragma unroll
+                            for (uint32_t ka = 0; ka < kKAtoms; ++ka)       // one box of the stage's rows per 128 bytes of K
+                                load(smem_base + kSmemA + stage * kABytes + ka * kAAtomStride, &tm_a, k_base + kb * kLoadXPerKBlock + ka * 128, a_row);
                         } else {
                             // one box per atom: 128 bytes of M (128 FP8 or 64 BF16 elements) by the stage's rows of K
                             #pragma unroll
@@ -561,7 +574,9 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                                      k_base + kb * BLOCK_K_ELEMS);
                         }
                         if constexpr (!kBMnMajor) {
-                            load(smem_base + kSmemB + stage * kBBytes, &tm_b, k_base + kb * kLoadXPerKBlock, b_row);
+                            #pragma unroll
+                            for (uint32_t ka = 0; ka < kKAtoms; ++ka)
+                                load(smem_base + kSmemB + stage * kBBytes + ka * kBAtomStride, &tm_b, k_base + kb * kLoadXPerKBlock + ka * 128, b_row);
                         } else {
                             #pragma unroll
                             for (uint32_t i = 0; i < kBAtoms; ++i)
@@ -591,12 +606,16 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                 // K-major: 8-row groups of BLOCK_K-byte rows (SBO 1024 or 512, swizzle span = the row), +32 B per UMMA along K.
                 // MN-major: atoms of [128 K][128 B]; SBO 1024 = eight K rows, LBO = one atom, +32 rows (4096 B) per UMMA along K.
                 constexpr uint32_t kALbo = kAMnMajor ? 128 * BLOCK_K_ELEMS : 0, kBLbo = kBMnMajor ? 128 * BLOCK_K_ELEMS : 0;
-                constexpr uint32_t kASbo = kAMnMajor ? 1024 : 8 * BLOCK_K, kBSbo = kBMnMajor ? 1024 : 8 * BLOCK_K;
-                constexpr uint64_t kASwizzle = kAMnMajor || BLOCK_K == 128 ? kSwizzle128B : kSwizzle64B;
-                constexpr uint64_t kBSwizzle = kBMnMajor || BLOCK_K == 128 ? kSwizzle128B : kSwizzle64B;
+                constexpr uint32_t kASbo = kAMnMajor ? 1024 : 8 * kKAtomBytes, kBSbo = kBMnMajor ? 1024 : 8 * kKAtomBytes;
+                constexpr uint64_t kASwizzle = kAMnMajor || kKAtomBytes == 128 ? kSwizzle128B : kSwizzle64B;
+                constexpr uint64_t kBSwizzle = kBMnMajor || kKAtomBytes == 128 ? kSwizzle128B : kSwizzle64B;
                 // (UMMA_K is 32 bytes of K: 32 FP8 or 16 BF16 elements, i.e. that many rows of an MN-major atom)
                 constexpr uint32_t kAStepK = (kAMnMajor ? UMMA_K / kABElemBytes * 128 : UMMA_K) >> 4;
                 constexpr uint32_t kBStepK = (kBMnMajor ? UMMA_K / kABElemBytes * 128 : UMMA_K) >> 4;
+                // (256-byte stages: MMA j works on atom j / 4 of the stage, 32 (j mod 4) bytes into its rows)
+                constexpr uint32_t kMmasPerAtom = kKAtomBytes / UMMA_K;
+                auto a_step = [&](uint32_t j) { return kKAtoms == 1 ? j * kAStepK : (j / kMmasPerAtom) * (kAAtomStride >> 4) + (j % kMmasPerAtom) * kAStepK; };
+                auto b_step = [&](uint32_t j) { return kKAtoms == 1 ? j * kBStepK : (j / kMmasPerAtom) * (kBAtomStride >> 4) + (j % kMmasPerAtom) * kBStepK; };
                 // A commit reaches the barrier at the same offset in every CTA of the cluster
                 auto commit_all = [&](uint32_t bar) {
                     if constexpr (kCluster == 1) {
@@ -669,16 +688,16 @@ dg_gemm_fp8_fp4(const __grid_constant__ CUtensorMap tm_a,
                                 const uint32_t sfb_id = ((kb * BLOCK_K + j * UMMA_K) / kGranKB) % 4;
                                 // Advancing K moves the start address: +32 B inside the swizzle atom (K-major) or +32 rows (MN-major)
                                 if constexpr (kABIsBF16)
-                                    tc_mma_bf16<kCluster>(tmem_d, a_desc + h * ((BLOCK_M * BLOCK_K) >> 4) + j * kAStepK, b_desc + j * kBStepK,
+                                    tc_mma_bf16<kCluster>(tmem_d, a_desc + h * ((BLOCK_M * BLOCK_K) >> 4) + a_step(j), b_desc + b_step(j),
                                                           idesc, ((kb - kb0) | j) != 0);
                                 else if constexpr (kMXF4)
                                     // 64 elements of K per instruction: word j / 2 of the stage, scale bytes 0-1 or 2-3 of it
-                                    tc_mma_mxf4<kCluster>(tmem_d, a_desc + h * ((BLOCK_M * BLOCK_K) >> 4) + j * kAStepK, b_desc + j * kBStepK,
+                                    tc_mma_mxf4<kCluster>(tmem_d, a_desc + h * ((BLOCK_M * BLOCK_K) >> 4) + a_step(j), b_desc + b_step(j),
                                                           instr_desc_with_sf_ids(idesc, (j % 2) * 2, (j % 2) * 2),
                                                           tmem_base + kTmemColSFA + (j / 2) * (SF_BLOCK_M / 32) + h * 4,
                                                           tmem_base + kTmemColSFB + (j / 2) * (SF_BLOCK_N / 32), ((kb - kb0) | j) != 0);
                                 else
-                                    tc_mma_mxf8f6f4<kCluster>(tmem_d, a_desc + h * ((BLOCK_M * BLOCK_K) >> 4) + j * kAStepK, b_desc + j * kBStepK,
+                                    tc_mma_mxf8f6f4<kCluster>(tmem_d, a_desc + h * ((BLOCK_M * BLOCK_K) >> 4) + a_step(j), b_desc + b_step(j),
                                                               instr_desc_with_sf_ids(idesc, sfa_id, sfb_id),
                                                               tmem_base + kTmemColSFA + h * 4, tmem_base + kTmemColSFB, ((kb - kb0) | j) != 0);
                             }

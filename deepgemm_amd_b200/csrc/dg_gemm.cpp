@@ -312,10 +312,10 @@ int choose_config_for(const Problem& p, dg_gemm_config_t* cfg, const Constraints
     } best;
     for (int cluster = 1; cluster <= 2; ++cluster)
     for (int halves = 1; halves <= 2; ++halves)
-    for (int bk = 128; bk >= 64; bk /= 2) {
+    for (int bk = 256; bk >= 64; bk /= 2) {
         if (forced_cluster ? cluster != forced_cluster : !cluster_allowed(p, cluster)) continue;
         // (swapped: 128-row CTAs, alone or as a pair that shares the activations' tile; a pair's K is not sliced)
-        if (lim.swapped && (halves != 1 || bk != 128)) continue;
+        if (lim.swapped && (halves != 1 || bk < 128)) continue;
         if (lim.swapped && cluster == 2 && !(forced_cluster == 2 || lim.swapped_pairs)) continue;
         // A CTA pair multiplies all its rows with one B: in the contiguous layout every expert segment must then be a
         // whole number of pair tiles
@@ -330,11 +330,15 @@ int choose_config_for(const Problem& p, dg_gemm_config_t* cfg, const Constraints
         // rows double the number of L2 requests), so it is used only on request (DG_FORCE_BLOCK_K=64).
         if (bk != (forced_block_k && p.kind != DG_GEMM_K_GROUPED_CONTIGUOUS ? forced_block_k : 128)) continue;
         if (bk == 64 && (p.a_fp4 || p.b_fp4 || p.ab_bf16 || p.a_mn_major || p.b_mn_major || forced_splits > 1)) continue;
+        // Stages of 256 elements of K (two swizzle atoms side by side, eight MMAs per barrier wait): the dense GEMM of
+        // K-major FP8 operands with one scale per 128 elements, 128-row CTAs, K a whole number of such stages
+        if (bk == 256 && (p.kind != DG_GEMM_DENSE || p.a_fp4 || p.b_fp4 || p.ab_bf16 || p.mxf4 || p.a_mn_major || p.b_mn_major || p.gran_k_a != 128 ||
+                          p.gran_k_b != 128 || p.reduce_batches > 1 || cluster != 1 || halves != 1 || p.k % 256 != 0)) continue;
         const int tile_m = 128 * cluster * halves, units = num_sms / cluster;
         // A dense GEMM with at most 64 rows stages only those rows of A (16, 32 or 64; the box of its tensor map): the
         // bytes saved per stage become more stages, i.e. more of B in flight.  DG_FORCE_A_ROWS=128 keeps whole tiles.
         int a_rows = 0;
-        if (p.kind == DG_GEMM_DENSE && cluster == 1 && halves == 1 && bk == 128 && !p.a_mn_major && p.reduce_batches <= 1 && p.m <= 64 &&
+        if (p.kind == DG_GEMM_DENSE && cluster == 1 && halves == 1 && bk >= 128 && !p.a_mn_major && p.reduce_batches <= 1 && p.m <= 64 &&
             env_int("FORCE_A_ROWS") != 128)
             a_rows = p.m <= 16 ? 16 : (p.m <= 32 ? 32 : 64);
         int64_t m_blocks;
@@ -354,7 +358,7 @@ int choose_config_for(const Problem& p, dg_gemm_config_t* cfg, const Constraints
         // to pull in; slicing K lets wide tiles (little re-reading of A) still spread over all SMs.  Slices hold a
         // multiple of 4 K-blocks (one packed scale word); all work items run in one wave; the second pass costs a
         // launch plus S FP32 panels of traffic.
-        const bool can_split = p.kind == DG_GEMM_DENSE && !p.accumulate && !p.d_fp8 && !p.stochastic && cluster == 1 && halves == 1 && bk == 128 &&
+        const bool can_split = p.kind == DG_GEMM_DENSE && !p.accumulate && !p.d_fp8 && !p.stochastic && cluster == 1 && halves == 1 && bk >= 128 &&
                                forced_splits != 1 && k_blocks >= 16;
         for (int bn = 16; bn <= (p.ab_bf16 ? 256 : 240); bn += 16) {
             if (lim.only_bn ? bn != lim.only_bn : (forced_bn && bn != forced_bn)) continue;
@@ -464,7 +468,8 @@ int choose_config_for(const Problem& p, dg_gemm_config_t* cfg, const Constraints
         return fail(DG_ERR_INVALID_ARGUMENT, "no tile configuration: DG_FORCE_BLOCK_N must be a multiple of 16 in [16, 240], "
                                              "DG_FORCE_CLUSTER 1 or 2 (2 needs an even SM count and, for the contiguous layout, expert segments aligned to the pair's rows), "
                                              "DG_FORCE_BLOCK_M 128 or 256 (256 only with K not sliced), "
-                                             "DG_FORCE_BLOCK_K 64 or 128 (64 only for K-major FP8 operands and K not sliced)");
+                                             "DG_FORCE_BLOCK_K 64, 128 or 256 (64 only for K-major FP8 operands and K not sliced; 256 only for dense K-major FP8 GEMMs with "
+                                             "one scale per 128 elements and K a multiple of 256)");
 
     const int units = num_sms / best.cluster;
     cfg->num_splits = best.splits;
@@ -782,12 +787,13 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
     const uint64_t bs_sfa = batched ? a->sfa_pitch * 4 * ceil_div(p.k, p.gran_k_a * 4) : 0;
     const uint64_t bs_sfb = batched ? a->sfb_pitch * 4 * ceil_div(p.k, p.gran_k_b * 4) : 0;
     CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb, tm_d, tm_d_full;
-    // K-major A, B: K (elements) x rows; box = one K-block (128 or 64 elements) x the tile's rows, swizzled over its width.
-    const CUtensorMapSwizzle k_major_swizzle = cfg.block_k == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+    // K-major A, B: K (elements) x rows; box = one K-block (at most 128 bytes of it) x the tile's rows, swizzled over its width.
+    const CUtensorMapSwizzle k_major_swizzle = cfg.block_k >= 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
     // MN-major (FP8 only): MN x (groups x K); box = 128 columns of MN x one K-block.
     // BF16 operands: two bytes per element, so a 128-byte stage row is 64 elements and an MN-major atom 64 columns
     const uint64_t ab_elem = p.ab_bf16 ? 2 : 1;
-    const uint32_t box_k = static_cast<uint32_t>(cfg.block_k / ab_elem), atom_mn = static_cast<uint32_t>(128 / ab_elem);
+    // (a 256-byte stage is filled by two boxes of 128)
+    const uint32_t box_k = static_cast<uint32_t>(std::min(cfg.block_k, 128) / ab_elem), atom_mn = static_cast<uint32_t>(128 / ab_elem);
     const CUtensorMapDataType a_type = p.ab_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 :
                                        p.a_fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8;
     const CUtensorMapDataType b_type = p.ab_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 :
@@ -859,7 +865,7 @@ int run_gemm(int kind, const dg_gemm_args_t* a, const FixedScratch* fixed_scratc
     params.alpha = split ? 1.0f : alpha;              // split-K applies alpha in the reduction pass
     params.profile = nullptr;
     params.num_splits = split ? cfg.num_splits : 1;
-    params.kb_per_split = cfg.kb_per_split;
+    params.kb_per_split = cfg.block_k > 128 ? cfg.kb_per_split * 128 / cfg.block_k : cfg.kb_per_split;    // the kernel counts stages
     params.split_panel_rows = static_cast<uint32_t>(panel_rows);
     params.group_alignment = static_cast<uint32_t>(state().mk_alignment);
     params.sfd = static_cast<uint32_t*>(a->sfd);

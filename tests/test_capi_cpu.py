@@ -165,6 +165,33 @@ def test_shortened_a_stages_keep_the_mma_read_inside_shared_memory(shape, monkey
     assert dg.get_gemm_config(0, m, n, k)["a_rows"] == 128
 
 
+def test_256_element_k_stages_on_request(monkeypatch):
+    """DG_FORCE_BLOCK_K=256: a stage row is two 128-byte swizzle atoms side by side, [atom][row][128 bytes].  Served for
+    dense K-major FP8 GEMMs with one scale per 128 elements and K a multiple of 256, by 128-row CTAs; K may be sliced
+    (slices stay multiples of 512 elements) and the operands swapped."""
+    monkeypatch.setenv("DG_FORCE_BLOCK_K", "256")
+    for m, n, k in [(128, 2112, 7168), (16, 2112, 7168), (64, 24576, 1536), (4096, 4096, 7168), (32, 4096, 512)]:
+        cfg = dg.get_gemm_config(0, m, n, k)
+        assert cfg["block_k"] == 256 and cfg["block_m"] == 128 and cfg["cluster_size"] == 1, cfg
+        assert 2 <= cfg["num_stages"] and cfg["smem_bytes"] <= 232448
+        # the MMAs on the second atom of the last stage read 128 rows of 128 bytes, starting one atom into the stage
+        rows, a_base = cfg["a_rows"], cfg["store_buffers"] * 16384
+        assert cfg["smem_bytes"] >= a_base + (cfg["num_stages"] - 1) * rows * 256 + rows * 128 + 128 * 128, cfg
+        assert cfg["num_splits"] == 1 or cfg["kb_per_split"] % 4 == 0
+    assert dg.get_gemm_config(0, 16, 2112, 7168)["swap_ab"] == 1
+    monkeypatch.setenv("DG_FORCE_SWAP_AB", "-1")
+    for m, n, k in [(16, 2112, 2048), (32, 384, 512), (8, 128, 256)]:
+        cfg = dg.get_gemm_config(0, m, n, k)
+        rows, a_base = cfg["a_rows"], cfg["store_buffers"] * 16384
+        assert cfg["block_k"] == 256 and rows == (16 if m <= 16 else 32), cfg
+        assert cfg["smem_bytes"] >= a_base + (cfg["num_stages"] - 1) * rows * 256 + rows * 128 + 128 * 128, cfg
+    monkeypatch.delenv("DG_FORCE_SWAP_AB")
+    for kw in (dict(kind=0, m=128, n=2112, k=7168 + 128), dict(kind=0, m=128, n=2112, k=7168, b_is_fp4=True, gran_k_b=32),
+               dict(kind=1, m=4096, n=4096, k=7168, num_groups=4)):
+        with pytest.raises(RuntimeError, match="no tile configuration"):
+            dg.get_gemm_config(**kw)
+
+
 def test_operand_swap_can_be_forced_and_forbidden(monkeypatch):
     """DG_FORCE_SWAP_AB: 1 = swap whenever the form applies (dense K-major FP8, M <= 128, no accumulation), -1 = never."""
     monkeypatch.setenv("DG_FORCE_SWAP_AB", "1")

@@ -137,6 +137,32 @@ def test_64_element_k_stages_match_oracle_and_the_128_element_kernel(m, n, k, bl
     assert np.array_equal(d, d1)
 
 
+@pytest.mark.parametrize("m,n,k,slicing", [(128, 128, 256, None), (200, 304, 768, None), (129, 256, 1280, None), (4096, 576, 1792, None),
+                                           (16, 2112, 2048, None), (64, 576, 4096, None), (128, 576, 4096, "cluster"),
+                                           (100, 704, 4096, "workspace"), (8, 640, 8192, "cluster"), (16, 2112, 2048, "direct"), (32, 384, 512, "direct")])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float])
+def test_256_element_k_stages_match_oracle_and_the_128_element_kernel(m, n, k, slicing, out_dtype, monkeypatch):
+    """Two swizzle atoms per stage row (two copies per operand on one barrier, eight MMAs per wait): whole and shortened A
+    stages, the operands swapped, K sliced inside a cluster and through the workspace.  The MMAs run in the same order
+    as with 128-element stages, so the bits are the same."""
+    if slicing == "direct":                         # operands not swapped: A stages of 16 and 32 rows, atoms that far apart
+        monkeypatch.setenv("DG_FORCE_SWAP_AB", "-1")
+        slicing = None
+    if slicing is not None:
+        monkeypatch.setenv("DG_FORCE_SPLIT_K", "4")
+        monkeypatch.setenv("DG_FORCE_SPLIT_CLUSTER", "1" if slicing == "cluster" else "-1")
+    qa, sfa, qb, sfb, _ = quantise_dense(seeded_bf16((m, k), 8), seeded_bf16((n, k), 9))
+    ref = oracle.dequant_gemm_nt(qa, sfa, qb, sfb)
+    outs = []
+    for block_k in (256, 128):
+        monkeypatch.setenv("DG_FORCE_BLOCK_K", str(block_k))
+        cfg = dg.get_gemm_config(0, m, n, k, d_is_fp32=out_dtype == torch.float)
+        assert cfg["block_k"] == block_k and (slicing is None or cfg["num_splits"] > 1), cfg
+        outs.append(_run_dense(qa, sfa, qb, sfb, out_dtype=out_dtype).float().cpu().numpy())
+    assert oracle.calc_diff(outs[0], ref) < 1e-5, diff_report(outs[0], ref)
+    assert np.array_equal(outs[0], outs[1])
+
+
 @pytest.mark.parametrize("variant", ["nn", "tn", "tt"])
 @pytest.mark.parametrize("m,n,k,cluster", [(128, 256, 512, 1), (208, 720, 1152, 1), (256, 2112, 1024, 1), (384, 704, 640, 2),
                                            (400, 704, 640, -256)])
