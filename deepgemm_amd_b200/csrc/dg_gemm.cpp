@@ -286,6 +286,7 @@ struct Constraints {
     int only_bn = 0;                  // swapped operands: the tile is as wide as the caller's M, rounded up to 16
     bool swapped = false;             // 128-row tiles, K slices only inside a cluster (the transposed epilogue's two forms)
     bool swapped_pairs = false;       // CTA pairs are candidates of the swapped form (each CTA loads half of the activations' tile)
+    int block_k = 128;                // bytes of K per stage row when DG_FORCE_BLOCK_K does not say
 };
 
 int choose_config_for(const Problem& p, dg_gemm_config_t* cfg, const Constraints& lim, double* cost_out) {
@@ -328,7 +329,7 @@ int choose_config_for(const Problem& p, dg_gemm_config_t* cfg, const Constraints
         // Stages of 64 elements of K (twice as many, each half the bytes): K-major FP8 operands and unsliced K only.
         // Built and tested, but it measured 0-20 % slower than 128-element stages on every shape tried (the 64-byte
         // rows double the number of L2 requests), so it is used only on request (DG_FORCE_BLOCK_K=64).
-        if (bk != (forced_block_k && p.kind != DG_GEMM_K_GROUPED_CONTIGUOUS ? forced_block_k : 128)) continue;
+        if (bk != (forced_block_k && p.kind != DG_GEMM_K_GROUPED_CONTIGUOUS ? forced_block_k : lim.block_k)) continue;
         if (bk == 64 && (p.a_fp4 || p.b_fp4 || p.ab_bf16 || p.a_mn_major || p.b_mn_major || forced_splits > 1)) continue;
         // Stages of 256 elements of K (two swizzle atoms side by side, eight MMAs per barrier wait): the dense GEMM of
         // K-major FP8 operands with one scale per 128 elements, 128-row CTAs, K a whole number of such stages
@@ -523,6 +524,18 @@ int choose_config(const Problem& p, dg_gemm_config_t* cfg, bool allow_cluster_sp
     // count speaks against its many small tiles)
     if (rc != DG_OK || forced_swap > 0 || p.m <= 16 || other_cost < direct_cost * (p.m > 32 ? 0.93 : 1.0)) {
         *cfg = other;
+        // Tiles of 16 or 32 columns spend more time on the MMA warp's walk around its loop than on the MMAs: where a work
+        // item has at least 12 K-blocks, stages of 256 elements of K (half as many walks; measured 2-4 % faster on the
+        // benchmark shapes, equal or slower with shorter items) replace the 128-element ones, everything else unchanged
+        const int item_kb = other.num_splits > 1 ? other.kb_per_split : static_cast<int>(ceil_div<int64_t>(p.k, 128));
+        if (p.m <= 32 && item_kb >= 12 && env_int("FORCE_BLOCK_K") == 0) {
+            Constraints wide = lim;
+            wide.block_k = 256;
+            dg_gemm_config_t longer{};
+            if (choose_config_for(swapped(p), &longer, wide, nullptr) == DG_OK && longer.num_splits == other.num_splits &&
+                longer.split_in_cluster == other.split_in_cluster && longer.num_stages >= 4)
+                *cfg = longer;
+        }
         return DG_OK;
     }
     return rc;

@@ -111,7 +111,11 @@ SHAPES = [(m, n, k) for m in (1, 64, 128, 129, 4096) for (n, k) in
 def test_heuristics_invariants(fp32):
     for m, n, k in SHAPES:
         cfg = dg.get_gemm_config(0, m, n, k, d_is_fp32=fp32)
-        assert cfg["block_m"] in (128, 256) and cfg["block_k"] in (64, 128)
+        assert cfg["block_m"] in (128, 256) and cfg["block_k"] in (128, 256)
+        # stages of 256 elements of K: only the swapped form's 16- and 32-column tiles, where a work item has 12 K-blocks or more
+        if cfg["block_k"] == 256:
+            assert cfg["swap_ab"] and m <= 32 and k % 256 == 0 and cfg["num_stages"] >= 4
+            assert (cfg["kb_per_split"] if cfg["num_splits"] > 1 else -(-k // 128)) >= 12
         assert cfg["block_m"] == 128 or (m > 128 and cfg["num_splits"] == 1)
         # CTA pairs (one 256- or 512-row tile per pair) only for large dense GEMMs, never sliced along K
         assert cfg["cluster_size"] == 1 or (cfg["cluster_size"] == 2 and m >= 1024 and cfg["num_splits"] == 1 and cfg["num_ctas"] % 2 == 0)
@@ -138,7 +142,7 @@ def test_heuristics_invariants(fp32):
                 assert cfg["num_splits"] <= 8 and cfg["num_ctas"] == cfg["num_tiles"] and cfg["cluster_size"] == 1
                 # (what it receives: the slices of the 8-column chunks it owns; the area starts at the D staging buffers)
                 recv = cfg["num_splits"] * -(-(cfg["block_n"] // 8) // cfg["num_splits"]) * 8 * 128 * 4
-                assert recv <= cfg["store_buffers"] * 16384 + cfg["num_stages"] * (cfg["a_rows"] + cfg["block_n"]) * 128
+                assert recv <= cfg["store_buffers"] * 16384 + cfg["num_stages"] * (cfg["a_rows"] + cfg["block_n"]) * cfg["block_k"]
         else:
             assert cfg["kb_per_split"] == kb and not cfg["split_in_cluster"]
     for kind, groups in ((1, 32), (2, 16)):
@@ -159,13 +163,13 @@ def test_shortened_a_stages_keep_the_mma_read_inside_shared_memory(shape, monkey
         rows = n if cfg["swap_ab"] else m
         assert cfg["a_rows"] == (128 if rows > 64 else 16 if rows <= 16 else 32 if rows <= 32 else 64), cfg
         a_base = cfg["store_buffers"] * 16384                       # the A stages follow the D staging buffers
-        assert cfg["smem_bytes"] >= a_base + (cfg["num_stages"] - 1) * cfg["a_rows"] * 128 + 128 * 128, cfg
+        assert cfg["smem_bytes"] >= a_base + (cfg["num_stages"] - 1) * cfg["a_rows"] * cfg["block_k"] + 128 * cfg["block_k"], cfg
         assert cfg["smem_bytes"] <= 232448
     monkeypatch.setenv("DG_FORCE_A_ROWS", "128")
     assert dg.get_gemm_config(0, m, n, k)["a_rows"] == 128
 
 
-def test_256_element_k_stages_on_request(monkeypatch):
+def test_256_element_k_stages(monkeypatch):
     """DG_FORCE_BLOCK_K=256: a stage row is two 128-byte swizzle atoms side by side, [atom][row][128 bytes].  Served for
     dense K-major FP8 GEMMs with one scale per 128 elements and K a multiple of 256, by 128-row CTAs; K may be sliced
     (slices stay multiples of 512 elements) and the operands swapped."""
@@ -179,6 +183,13 @@ def test_256_element_k_stages_on_request(monkeypatch):
         assert cfg["smem_bytes"] >= a_base + (cfg["num_stages"] - 1) * rows * 256 + rows * 128 + 128 * 128, cfg
         assert cfg["num_splits"] == 1 or cfg["kb_per_split"] % 4 == 0
     assert dg.get_gemm_config(0, 16, 2112, 7168)["swap_ab"] == 1
+    monkeypatch.delenv("DG_FORCE_BLOCK_K")
+    # without the request: chosen for the swapped form's narrow tiles when a work item is 12 K-blocks or longer
+    assert [dg.get_gemm_config(0, m, n, k)["block_k"] for m, n, k in
+            [(16, 2112, 7168), (32, 4096, 7168), (8, 24576, 1536), (16, 7168, 2048), (16, 32768, 512), (16, 4096, 7168 + 128), (64, 4096, 7168)]] == \
+           [256, 256, 256, 128, 128, 128, 128]
+    assert dg.get_gemm_config(0, 16, 4096, 7168, b_is_fp4=True, gran_k_b=32)["block_k"] == 128
+    monkeypatch.setenv("DG_FORCE_BLOCK_K", "256")
     monkeypatch.setenv("DG_FORCE_SWAP_AB", "-1")
     for m, n, k in [(16, 2112, 2048), (32, 384, 512), (8, 128, 256)]:
         cfg = dg.get_gemm_config(0, m, n, k)
