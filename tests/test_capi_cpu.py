@@ -170,7 +170,7 @@ def test_shortened_a_stages_keep_the_mma_read_inside_shared_memory(shape, monkey
 
 
 def test_256_element_k_stages(monkeypatch):
-    """DG_FORCE_BLOCK_K=256: a stage row is two 128-byte swizzle atoms side by side, [atom][row][128 bytes].  Served for
+    """Stages of 256 elements of K: a stage row is two 128-byte swizzle atoms side by side, [atom][row][128 bytes].  Served for
     dense K-major FP8 GEMMs with one scale per 128 elements and K a multiple of 256, by 128-row CTAs; K may be sliced
     (slices stay multiples of 512 elements) and the operands swapped."""
     monkeypatch.setenv("DG_FORCE_BLOCK_K", "256")
